@@ -1,0 +1,388 @@
+"""Operator module: the callables the reference exports from its compiled
+``thriftattention._C`` extension (csrc/bindings.cpp:1454-1671), implemented over the
+C ABI of ``libthrift_sm100.so``.
+
+Names, positional argument order, argument meaning and error conditions follow the
+reference bindings; outputs and workspaces are allocated here with torch and handed
+to the library as raw pointers together with the current CUDA stream.  Errors from
+argument checks are ``RuntimeError`` like the reference's ``TORCH_CHECK`` failures.
+
+Additions (no reference counterpart, used by the sm100 backend): ``block_stats``,
+``select_prefill_blocks``, ``select_decode_blocks``, ``pack_topk_mask``,
+``prefill_attention``, ``decode_attention`` and ``merge_decode_partials``.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+_lib.load()  # fail at import time when the CUDA library is missing
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _ptr(t: torch.Tensor | None):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(t: torch.Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _scale_dtype(is_mx: bool):
+    return torch.float8_e8m0fnu if is_mx else torch.float8_e4m3fn
+
+
+# ---------------------------------------------------------------------------------------------
+# Quantisers  (bindings.cpp:893-1097)
+# ---------------------------------------------------------------------------------------------
+def _quantize(x: torch.Tensor, is_bf16: bool, is_mx: bool, layout: int):
+    _check(x.is_cuda, "x must be a CUDA tensor")
+    _check(x.is_contiguous(), "x must be contiguous")
+    _check(x.dim() == 4, "x must be 4D [batch, heads, seq, head_dim]")
+    b, h, s, d = x.shape
+    _check(d in (64, 128), f"head_dim must be 64 or 128, got {d}")
+    _check(x.dtype == (torch.bfloat16 if is_bf16 else torch.float16), "x dtype must match is_bf16")
+    g = 32 if is_mx else 16
+    if layout >= 2:
+        padded = (s + 127) // 128 * 128
+        codes = torch.empty(b, h, d, padded // 2, dtype=torch.uint8, device=x.device)
+        scales = torch.empty(b, h, d, padded // g, dtype=torch.uint8, device=x.device)
+    else:
+        codes = torch.empty(b, h, s, d // 2, dtype=torch.uint8, device=x.device)
+        scales = torch.empty(b, h, s, d // g, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().ta100_quantize(_ptr(x), _ptr(codes), _ptr(scales), b * h, s, d, int(is_mx), int(is_bf16),
+                                        layout, _stream(x))
+    _lib.check(rc, "quantize")
+    return [codes, scales.view(_scale_dtype(is_mx))]
+
+
+def nvfp4_quantize(x, is_bf16=False):
+    return _quantize(x, is_bf16, False, 0)
+
+
+def nvfp4_quantize_permuted(x, is_bf16=False):
+    return _quantize(x, is_bf16, False, 1)
+
+
+def nvfp4_quantize_transposed(x, is_bf16=False):
+    return _quantize(x, is_bf16, False, 2)
+
+
+def nvfp4_quantize_transposed_permuted(x, is_bf16=False):
+    return _quantize(x, is_bf16, False, 3)
+
+
+def mxfp4_quantize(x, is_bf16=False):
+    return _quantize(x, is_bf16, True, 0)
+
+
+def mxfp4_quantize_permuted(x, is_bf16=False):
+    return _quantize(x, is_bf16, True, 1)
+
+
+def mxfp4_quantize_transposed(x, is_bf16=False):
+    return _quantize(x, is_bf16, True, 2)
+
+
+def mxfp4_quantize_transposed_permuted(x, is_bf16=False):
+    return _quantize(x, is_bf16, True, 3)
+
+
+# ---------------------------------------------------------------------------------------------
+# Block statistics and selection  (bindings.cpp:1100-1452)
+# ---------------------------------------------------------------------------------------------
+def block_stats(x: torch.Tensor, block_size: int, *, mean=False, minmax=False):
+    """Per-block fp32 mean (cast to x.dtype), min and max of ``x`` [B,H,S,D] in one pass.
+
+    Fuses the PyTorch pre-reductions of the reference (selection/block_mean.py:44-54,
+    selection/quest.py:11-24) without materialising an fp32 copy.  Returns a tuple
+    ``(mean|None, min|None, max|None)`` of [B,H,S/block,D] tensors.
+    """
+    _check(x.is_cuda and x.is_contiguous() and x.dim() == 4, "x must be a contiguous 4D CUDA tensor")
+    b, h, s, d = x.shape
+    _check(d in (64, 128), f"head_dim must be 64 or 128, got {d}")
+    _check(s % block_size == 0, f"sequence length must be divisible by {block_size}")
+    nb = s // block_size
+    mk = lambda: torch.empty(b, h, nb, d, dtype=x.dtype, device=x.device)
+    o_mean = mk() if mean else None
+    o_min = mk() if minmax else None
+    o_max = mk() if minmax else None
+    with torch.cuda.device(x.device):
+        rc = _lib.load().ta100_block_stats(_ptr(x), _ptr(o_mean), _ptr(o_min), _ptr(o_max), b * h, s, d, block_size,
+                                           int(x.dtype == torch.bfloat16), _stream(x))
+    _lib.check(rc, "block_stats")
+    return o_mean, o_min, o_max
+
+
+def select_prefill_blocks(q_mean, k_a, k_b, topk_count, causal=True, is_bf16=False, sink=0, local=0):
+    """Per-q-block selection.  ``k_b is None`` -> block-mean score with ``k_a = k_mean``;
+    otherwise Quest with ``k_a = k_min``, ``k_b = k_max``.  K statistics may be given per
+    KV head ([B,Hkv,nk,D]) or already expanded per Q head.  ``sink``/``local`` force the
+    first/last valid blocks (extension; 0 reproduces the reference)."""
+    ts = [q_mean, k_a] + ([k_b] if k_b is not None else [])
+    _check(all(t.is_cuda for t in ts), "selection inputs must be CUDA tensors")
+    _check(all(t.is_contiguous() for t in ts), "selection inputs must be contiguous")
+    _check(all(t.dim() == 4 for t in ts), "selection inputs must be 4D tensors")
+    _check(k_b is None or k_a.shape == k_b.shape, "k_min and k_max shapes must match")
+    _check(q_mean.size(0) == k_a.size(0), "batch dimensions must match")
+    _check(q_mean.size(1) % k_a.size(1) == 0, "q heads must be divisible by key stat heads")
+    _check(q_mean.size(3) == k_a.size(3), "head_dim must match")
+    b, hq, nq, d = q_mean.shape
+    nk = k_a.size(2)
+    _check(d in (64, 128), f"head_dim must be 64 or 128, got {d}")
+    _check(nk <= 2048, f"block selector supports <= 2048 KV blocks, got {nk}")
+    _check(0 <= topk_count <= nk, "topk_count must be in [0, num_kv_blocks]")
+    width = sink + local + topk_count
+    out = torch.empty(b * hq, nq, width, dtype=torch.int32, device=q_mean.device)
+    if width == 0:
+        return out
+    with torch.cuda.device(q_mean.device):
+        rc = _lib.load().ta100_select_prefill(_ptr(q_mean), _ptr(k_a), _ptr(k_b), _ptr(out), b * hq, hq // k_a.size(1),
+                                              nq, nk, d, topk_count, int(causal), int(k_b is not None), int(is_bf16),
+                                              sink, local, _stream(q_mean))
+    _lib.check(rc, "select_prefill")
+    return out
+
+
+def block_mean_topk(q_mean, k_mean, topk_count, causal=True, is_bf16=False):
+    return select_prefill_blocks(q_mean, k_mean, None, topk_count, causal, is_bf16)
+
+
+def quest_block_topk(q_mean, k_min, k_max, topk_count, causal=True, is_bf16=False):
+    return select_prefill_blocks(q_mean, k_min, k_max, topk_count, causal, is_bf16)
+
+
+def select_decode_blocks(q_grouped, k_a, k_b, topk_count, num_kv_blocks, is_bf16=False, sink=0, local=0, out=None):
+    ts = [q_grouped, k_a] + ([k_b] if k_b is not None else [])
+    _check(all(t.is_cuda for t in ts), "selection inputs must be CUDA tensors")
+    _check(all(t.is_contiguous() for t in ts), "selection inputs must be contiguous")
+    _check(all(t.dim() == 4 for t in ts), "selection inputs must be 4D tensors")
+    _check(k_b is None or k_a.shape == k_b.shape, "k_min and k_max shapes must match")
+    _check(q_grouped.size(0) == k_a.size(0), "batch dimensions must match")
+    _check(q_grouped.size(1) == k_a.size(1), "KV-head dimensions must match")
+    _check(q_grouped.size(3) == k_a.size(3), "head_dim must match")
+    b, hkv, groups, d = q_grouped.shape
+    cap = k_a.size(2)
+    _check(1 <= groups <= 16, f"grouped single-query selector expects groups in [1, 16], got {groups}")
+    _check(d in (64, 128), f"head_dim must be 64 or 128, got {d}")
+    _check(0 <= num_kv_blocks <= cap, "num_kv_blocks must be in [0, key stat capacity]")
+    _check(num_kv_blocks <= 2048, f"single-query block selector supports <= 2048 KV blocks, got {num_kv_blocks}")
+    _check(0 <= topk_count <= num_kv_blocks, "topk_count must be in [0, num_kv_blocks]")
+    width = sink + local + topk_count
+    if out is None:
+        out = torch.empty(b * hkv, width, dtype=torch.int32, device=q_grouped.device)
+    if width == 0:
+        return out
+    with torch.cuda.device(q_grouped.device):
+        rc = _lib.load().ta100_select_decode(_ptr(q_grouped), _ptr(k_a), _ptr(k_b), _ptr(out), b * hkv, groups,
+                                             num_kv_blocks, cap, d, topk_count, int(k_b is not None), int(is_bf16),
+                                             sink, local, _stream(q_grouped))
+    _lib.check(rc, "select_decode")
+    return out
+
+
+def single_query_key_mean_topk(q_grouped, k_mean, topk_count, num_kv_blocks, is_bf16=False):
+    return select_decode_blocks(q_grouped, k_mean, None, topk_count, num_kv_blocks, is_bf16)
+
+
+def single_query_quest_topk(q_grouped, k_min, k_max, topk_count, num_kv_blocks, is_bf16=False):
+    return select_decode_blocks(q_grouped, k_min, k_max, topk_count, num_kv_blocks, is_bf16)
+
+
+def single_query_key_mean_topk_into(q_grouped, k_mean, topk, local_scores, local_indices, done_counts, num_kv_blocks,
+                                    is_bf16=False):
+    """Writes the selection into the caller's ``topk`` tensor.  The three workspace tensors of
+    the reference's chunked variant are accepted and validated but not needed: one CTA per
+    KV head scores all blocks and selects in place."""
+    for t in (topk, local_scores, local_indices, done_counts):
+        _check(t.is_cuda and t.is_contiguous(), "top-k workspace tensors must be contiguous CUDA tensors")
+    _check(topk.dtype == torch.int32 and local_indices.dtype == torch.int32 and done_counts.dtype == torch.int32,
+           "topk, local_indices, and done_counts must be int32")
+    _check(local_scores.dtype == torch.float32, "local_scores must be float32")
+    flat = q_grouped.size(0) * q_grouped.size(1)
+    _check(topk.dim() == 2 and topk.size(0) == flat, "topk must be shaped [batch * kv_heads, topk_count]")
+    _check(done_counts.dim() == 1 and done_counts.size(0) == flat, "done_counts must be shaped [batch * kv_heads]")
+    return select_decode_blocks(q_grouped, k_mean, None, topk.size(1), num_kv_blocks, is_bf16, out=topk)
+
+
+def local_block_topk(q, num_kv_blocks, topk_count, causal=True, block_size=64):
+    _check(q.is_cuda, "q must be a CUDA tensor")
+    _check(q.dim() == 4, "q must be 4D [batch, heads, seq, head_dim]")
+    _check(block_size > 0 and q.size(2) % block_size == 0, "q sequence length must be divisible by block_size")
+    _check(0 <= topk_count <= num_kv_blocks, "topk_count must be in [0, num_kv_blocks]")
+    flat, nq = q.size(0) * q.size(1), q.size(2) // block_size
+    out = torch.empty(flat, nq, topk_count, dtype=torch.int32, device=q.device)
+    with torch.cuda.device(q.device):
+        rc = _lib.load().ta100_local_block_topk(_ptr(out), flat, nq, num_kv_blocks, topk_count, int(causal), _stream(q))
+    _lib.check(rc, "local_block_topk")
+    return out
+
+
+def single_query_local_topk(q_grouped, topk_count, num_kv_blocks):
+    _check(q_grouped.is_cuda, "q_grouped must be a CUDA tensor")
+    _check(q_grouped.dim() == 4, "q_grouped must be 4D [batch, kv_heads, groups, head_dim]")
+    _check(0 <= topk_count <= num_kv_blocks, "topk_count must be in [0, num_kv_blocks]")
+    flat = q_grouped.size(0) * q_grouped.size(1)
+    out = torch.empty(flat, topk_count, dtype=torch.int32, device=q_grouped.device)
+    with torch.cuda.device(q_grouped.device):
+        rc = _lib.load().ta100_single_query_local_topk(_ptr(out), flat, num_kv_blocks, topk_count, _stream(q_grouped))
+    _lib.check(rc, "single_query_local_topk")
+    return out
+
+
+def pack_topk_mask(selected_blocks: torch.Tensor, num_kv_blocks: int) -> torch.Tensor:
+    """Index list [..., k] -> int64 bitset [..., ceil(nk/64)] (bindings.cpp:537-542)."""
+    _check(selected_blocks.is_cuda and selected_blocks.is_contiguous() and selected_blocks.dtype == torch.int32,
+           "selected_blocks must be a contiguous int32 CUDA tensor")
+    words = (num_kv_blocks + 63) // 64
+    _check(words <= 32, f"at most 2048 KV blocks are supported, got {num_kv_blocks}")
+    k = selected_blocks.size(-1)
+    rows = selected_blocks.numel() // k if k else int(torch.Size(selected_blocks.shape[:-1]).numel())
+    mask = torch.zeros(*selected_blocks.shape[:-1], words, dtype=torch.int64, device=selected_blocks.device)
+    if k == 0 or rows == 0:
+        return mask
+    with torch.cuda.device(mask.device):
+        rc = _lib.load().ta100_pack_topk_mask(_ptr(selected_blocks), _ptr(mask), rows, k, num_kv_blocks, words,
+                                              _stream(mask))
+    _lib.check(rc, "pack_topk_mask")
+    return mask
+
+
+# ---------------------------------------------------------------------------------------------
+# Prefill attention  (bindings.cpp:249-292, 487-695)
+# ---------------------------------------------------------------------------------------------
+def _check_hi(q, k, v):
+    _check(q.is_cuda and k.is_cuda and v.is_cuda, "Q/K/V must be CUDA tensors")
+    _check(q.dim() == 4 and k.dim() == 4 and v.dim() == 4, "Q/K/V must be 4D [batch, heads, seq, head_dim]")
+    _check(q.size(0) == k.size(0) == v.size(0), "Q/K/V batch dimensions must match")
+    _check(k.size(1) == v.size(1), "K and V head dimensions must match")
+    _check(k.size(2) == v.size(2), "K and V sequence lengths must match")
+    _check(q.size(3) == k.size(3) == v.size(3), "Q/K/V head dimensions must match")
+
+
+def _check_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t):
+    _check(q_packed.is_cuda and k_packed.is_cuda and v_packed_t.is_cuda, "packed Q/K/V must be CUDA tensors")
+    _check(q_scale.is_cuda and k_scale.is_cuda and v_scale_t.is_cuda, "Q/K/V scales must be CUDA tensors")
+    _check(q_packed.dim() == 4 and k_packed.dim() == 4 and v_packed_t.dim() == 4, "packed Q/K/V must be 4D tensors")
+    _check(q_packed.size(0) == k_packed.size(0), "packed Q/K batch dimensions must match")
+    _check(q_packed.size(1) % k_packed.size(1) == 0, "Q heads must be divisible by KV heads")
+    _check(q_packed.size(3) == k_packed.size(3), "packed Q/K head dimensions must match")
+
+
+_workspaces: dict = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    """Per-(device, stream) scratch buffer, grown on demand and reused across calls."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def prefill_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, *,
+                      causal, is_mx, is_bf16=False, block_size=64, k_permuted=True, round_partial=True, max_ctas=0,
+                      check_status=False):
+    """Fused mixed-precision prefill attention (one kernel for the FP4 pass and the 16-bit pass).
+
+    ``selected_blocks`` is ``None`` (pure FP4) or int32 ``[B*Hq, Sq/block_size, W]`` with -1
+    padding.  ``k_permuted`` says whether ``k_packed`` uses the reference's row-permuted layout.
+    """
+    _check_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t)
+    b, hq, sq, dh = q_packed.shape
+    hkv, skv = k_packed.size(1), k_packed.size(2)
+    d = dh * 2
+    _check(q_packed.is_contiguous() and q_scale.is_contiguous(), "packed Q and its scales must be contiguous")
+    _check(k_packed.stride(3) == 1 and k_packed.stride(2) == dh, "packed K rows must be dense")
+    kv_cap = k_packed.stride(1) // dh if hkv > 1 or b > 1 else max(skv, k_packed.stride(1) // dh)
+    width = 0
+    if selected_blocks is not None:
+        _check_hi(q_hi, k_hi, v_hi)
+        _check(selected_blocks.is_cuda, "selected_blocks must be a CUDA tensor")
+        _check(selected_blocks.dtype == torch.int32, "selected_blocks must be int32")
+        _check(selected_blocks.is_contiguous(), "selected_blocks must be contiguous")
+        _check(selected_blocks.dim() == 3, "selected_blocks must be [batch * heads, q_blocks, top_k]")
+        _check(selected_blocks.size(0) == b * hq, "selected_blocks first dimension must equal batch * Q heads")
+        _check(selected_blocks.size(1) == (sq + block_size - 1) // block_size,
+               "selected_blocks second dimension must equal number of Q blocks")
+        _check((skv + 63) // 64 <= 2048, f"ThriftAttention supports at most 2048 64-token KV blocks, got {(skv + 63) // 64}")
+        width = selected_blocks.size(2)
+        _check(q_hi.is_contiguous() and k_hi.is_contiguous() and v_hi.is_contiguous(), "Q/K/V must be contiguous")
+    out = torch.empty(b, hq, sq, d, dtype=torch.bfloat16 if is_bf16 else torch.float16, device=q_packed.device)
+    lib = _lib.load()
+    with torch.cuda.device(out.device):
+        nbytes = lib.ta100_prefill_workspace_bytes(b, hq, hkv, sq, skv, d, int(is_mx))
+        ws = _workspace(out.device, nbytes)
+        sel = selected_blocks if width > 0 else None
+        rc = lib.ta100_prefill_attention(
+            _ptr(q_hi) if sel is not None else None, _ptr(k_hi) if sel is not None else None,
+            _ptr(v_hi) if sel is not None else None, _ptr(sel), width, block_size, _ptr(q_packed), _ptr(k_packed),
+            _ptr(v_packed_t), _ptr(q_scale), _ptr(k_scale), _ptr(v_scale_t), _ptr(out), _ptr(ws), ws.numel(), b, hq, hkv,
+            sq, skv, kv_cap, d, int(causal), int(is_mx), int(is_bf16), int(k_permuted), int(round_partial), max_ctas,
+            _stream(out))
+        _lib.check(rc, "prefill_attention")
+        if check_status:
+            _lib.check(lib.ta100_prefill_status(_ptr(ws), b, hq, hkv, sq, skv, d, int(is_mx), _stream(out)),
+                       "prefill_attention (device)")
+    return out
+
+
+def _fp4_tiled(packed, causal, is_mx, is_bf16):
+    q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t = packed
+    return prefill_attention(None, None, None, None, q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t,
+                             causal=causal, is_mx=is_mx, is_bf16=is_bf16)
+
+
+def fp4_attention_causal_nvfp4_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, is_bf16=False):
+    return _fp4_tiled((q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t), True, False, is_bf16)
+
+
+def fp4_attention_noncausal_nvfp4_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, is_bf16=False):
+    return _fp4_tiled((q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t), False, False, is_bf16)
+
+
+def fp4_attention_causal_mxfp4_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, is_bf16=False):
+    return _fp4_tiled((q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t), True, True, is_bf16)
+
+
+def fp4_attention_noncausal_mxfp4_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, is_bf16=False):
+    return _fp4_tiled((q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t), False, True, is_bf16)
+
+
+def _thrift_tiled(args, causal, is_mx, is_bf16):
+    q_hi, k_hi, v_hi, selected_blocks = args[:4]
+    return prefill_attention(q_hi, k_hi, v_hi, selected_blocks, *args[4:], causal=causal, is_mx=is_mx, is_bf16=is_bf16)
+
+
+def thrift_attention_causal_nvfp4_packed(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale,
+                                         k_scale, v_scale_t, is_bf16=False):
+    return _thrift_tiled((q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale,
+                          v_scale_t), True, False, is_bf16)
+
+
+def thrift_attention_noncausal_nvfp4_packed(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale,
+                                            k_scale, v_scale_t, is_bf16=False):
+    return _thrift_tiled((q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale,
+                          v_scale_t), False, False, is_bf16)
+
+
+def thrift_attention_causal_mxfp4_packed(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale,
+                                         k_scale, v_scale_t, is_bf16=False):
+    return _thrift_tiled((q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale,
+                          v_scale_t), True, True, is_bf16)
+
+
+def thrift_attention_noncausal_mxfp4_packed(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale,
+                                            k_scale, v_scale_t, is_bf16=False):
+    return _thrift_tiled((q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale,
+                          v_scale_t), False, True, is_bf16)

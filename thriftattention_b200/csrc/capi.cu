@@ -1,0 +1,101 @@
+// C ABI of libthrift_sm100.so.  Declarations and contracts: include/thrift_sm100.h.
+#include <cstddef>
+#include <cstdint>
+
+#include "common.cuh"
+
+namespace ta100 {
+int quantize_dispatch(const void*, void*, void*, long long, int, int, int, int, int, cudaStream_t);
+int block_stats_dispatch(const void*, void*, void*, void*, long long, int, int, int, int, cudaStream_t);
+int select_prefill_dispatch(const void*, const void*, const void*, void*, int, int, int, int, int, int, int, int, int, int,
+                            int, cudaStream_t);
+int select_decode_dispatch(const void*, const void*, const void*, void*, int, int, int, int, int, int, int, int, int, int,
+                           cudaStream_t);
+int local_prefill_dispatch(void*, long long, int, int, int, int, cudaStream_t);
+int local_decode_dispatch(void*, long long, int, int, cudaStream_t);
+int pack_mask_dispatch(const void*, void*, long long, int, int, int, cudaStream_t);
+size_t prefill_workspace_bytes(int, int, int, int, int, int, int);
+int prefill_dispatch(const void*, const void*, const void*, const void*, int, int, const void*, const void*, const void*,
+                     const void*, const void*, const void*, void*, void*, size_t, int, int, int, int, int, int, int, int,
+                     int, int, int, int, int, cudaStream_t);
+int prefill_status(const void*, int, int, int, int, int, int, int, cudaStream_t);
+}  // namespace ta100
+
+using namespace ta100;
+static inline cudaStream_t S(void* s) { return static_cast<cudaStream_t>(s); }
+
+extern "C" {
+
+int ta100_version(void) { return 100; }
+
+const char* ta100_status_string(int status) {
+    switch (status) {
+        case TA100_OK: return "ok";
+        case TA100_ERR_NULL: return "null pointer argument";
+        case TA100_ERR_SHAPE: return "inconsistent or unsupported shape";
+        case TA100_ERR_UNSUPPORTED: return "unsupported head_dim, block size or format";
+        case TA100_ERR_ALIGN: return "pointer is not sufficiently aligned";
+        case TA100_ERR_WORKSPACE: return "workspace too small";
+        case TA100_ERR_TENSOR_MAP: return "tensor map creation failed";
+        case TA100_ERR_DEVICE_TIMEOUT: return "a device-side wait timed out";
+        case TA100_ERR_LIMIT: return "size beyond a compiled-in limit";
+        default: return status > 0 ? cudaGetErrorString(static_cast<cudaError_t>(status)) : "unknown status";
+    }
+}
+
+int ta100_quantize(const void* x, void* codes, void* scales, long long bs, int seq, int head_dim, int is_mxfp4,
+                   int is_bf16, int layout, void* stream) {
+    return quantize_dispatch(x, codes, scales, bs, seq, head_dim, is_mxfp4, is_bf16, layout, S(stream));
+}
+
+int ta100_block_stats(const void* x, void* mean, void* mn, void* mx, long long heads, int seq, int head_dim, int block,
+                      int is_bf16, void* stream) {
+    return block_stats_dispatch(x, mean, mn, mx, heads, seq, head_dim, block, is_bf16, S(stream));
+}
+
+int ta100_select_prefill(const void* q_mean, const void* k_a, const void* k_b, void* out, int heads, int group, int nq,
+                         int nk, int head_dim, int k, int causal, int quest, int is_bf16, int sink, int local,
+                         void* stream) {
+    return select_prefill_dispatch(q_mean, k_a, k_b, out, heads, group, nq, nk, head_dim, k, causal, quest, is_bf16, sink,
+                                   local, S(stream));
+}
+
+int ta100_select_decode(const void* q_grouped, const void* k_a, const void* k_b, void* out, int flat_kv_heads, int group,
+                        int nk, int cap_blocks, int head_dim, int k, int quest, int is_bf16, int sink, int local,
+                        void* stream) {
+    return select_decode_dispatch(q_grouped, k_a, k_b, out, flat_kv_heads, group, nk, cap_blocks, head_dim, k, quest,
+                                  is_bf16, sink, local, S(stream));
+}
+
+int ta100_local_block_topk(void* out, long long flat_heads, int nq, int nk, int k, int causal, void* stream) {
+    return local_prefill_dispatch(out, flat_heads, nq, nk, k, causal, S(stream));
+}
+
+int ta100_single_query_local_topk(void* out, long long flat_heads, int nk, int k, void* stream) {
+    return local_decode_dispatch(out, flat_heads, nk, k, S(stream));
+}
+
+int ta100_pack_topk_mask(const void* sel, void* mask, long long rows, int k, int nk, int words, void* stream) {
+    return pack_mask_dispatch(sel, mask, rows, k, nk, words, S(stream));
+}
+
+size_t ta100_prefill_workspace_bytes(int batch, int hq, int hkv, int sq, int skv, int head_dim, int is_mxfp4) {
+    return prefill_workspace_bytes(batch, hq, hkv, sq, skv, head_dim, is_mxfp4);
+}
+
+int ta100_prefill_attention(const void* q_hi, const void* k_hi, const void* v_hi, const void* sel, int width, int block,
+                            const void* q4, const void* k4, const void* v4t, const void* qs, const void* ks,
+                            const void* vst, void* out, void* workspace, size_t workspace_bytes, int batch, int hq,
+                            int hkv, int sq, int skv, int kv_cap, int head_dim, int causal, int is_mxfp4, int is_bf16,
+                            int k_permuted, int round_partial, int max_ctas, void* stream) {
+    return prefill_dispatch(q_hi, k_hi, v_hi, sel, width, block, q4, k4, v4t, qs, ks, vst, out, workspace, workspace_bytes,
+                            batch, hq, hkv, sq, skv, kv_cap, head_dim, causal, is_mxfp4, is_bf16, k_permuted,
+                            round_partial, max_ctas, S(stream));
+}
+
+int ta100_prefill_status(const void* workspace, int batch, int hq, int hkv, int sq, int skv, int head_dim, int is_mxfp4,
+                         void* stream) {
+    return prefill_status(workspace, batch, hq, hkv, sq, skv, head_dim, is_mxfp4, S(stream));
+}
+
+}  // extern "C"

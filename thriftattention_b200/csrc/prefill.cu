@@ -1,0 +1,869 @@
+// Fused selective mixed-precision prefill attention for sm_100a.
+//
+// One persistent CTA per SM walks (q head, 128-row q tile) work items, longest
+// first.  Per item the KV sequence is consumed in 64-column steps:
+//   phase A  every step whose KV block is NOT selected: block-scaled FP4
+//            tcgen05 MMAs (S = Q4 K4^T, O += P4 V4) with P quantised to e2m1;
+//   phase B  the selected blocks in list order: f16/bf16 tcgen05 MMAs.
+// Both phases share one online softmax whose state (row max, row sum) lives in
+// registers and whose accumulator O lives in tensor memory for the whole item.
+//
+// Warp roles (192 threads): warp 0 = TMA producer (+ builds the per-item block
+// bitsets), warp 1 = MMA issuer and tensor-memory owner, warps 2..5 = softmax
+// (one thread per q row; warp w owns tensor-memory lanes 32*(w%4)..+31).
+//
+// Every mbarrier wait is bounded; a timeout raises a CTA-wide abort flag, all
+// roles drain, tensor memory is released and a status word is set.
+#include <cfloat>
+#include <climits>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace ta100 {
+
+namespace {
+
+constexpr int QTILE = 128;
+constexpr int STEP = 64;
+constexpr int NSTAGES = 4;
+constexpr int STAGE_BYTES = 32768;
+constexpr int NUM_THREADS = 192;
+
+// tensor-memory columns
+constexpr uint32_t TM_O = 0;
+constexpr uint32_t TM_S = 128;      // two buffers of 64 columns
+constexpr uint32_t TM_SFA_Q = 256;  // up to 8 columns
+constexpr uint32_t TM_SFB_K = 264;  // two slots of 8 columns
+constexpr uint32_t TM_SFA_P = 280;  // 4 columns, constant
+constexpr uint32_t TM_SFB_V = 284;  // two slots of 4 columns
+constexpr uint32_t TM_COLS = 512;
+
+struct PrefillParams {
+    int batch, hq_per_b, hkv_per_b, group;
+    int sq, skv;
+    int block;      // selection block size in tokens (64 or 128)
+    int width;      // entries per selection row (0: pure FP4)
+    int causal, round_partial;
+    int n_qtiles, n_items, nsteps_total, nkb;
+    const int32_t* sel;
+    const uint8_t* q_sf;
+    const uint8_t* k_sf;
+    const uint8_t* v_sf;
+    uint16_t* out;
+    int* status;
+    float c2;  // (1/sqrt(d)) * log2(e)
+    long long budget;
+};
+
+// shared-memory carve-up (offsets from a 1024-byte aligned base)
+template <int D>
+struct Smem {
+    static constexpr int Q4 = 0;                       // 128 x D/2
+    static constexpr int QSF = Q4 + QTILE * D / 2;     // up to 2 atoms
+    static constexpr int Q16 = QSF + 1024;             // 128 x D x 2
+    static constexpr int P = Q16 + QTILE * D * 2;      // 16 KB
+    static constexpr int CSF = P + 16384;              // constant scale atom
+    static constexpr int STAGES = CSF + 1024;
+    static constexpr int BITS = STAGES + NSTAGES * STAGE_BYTES;  // 2 buffers x 2 halves x 64 words
+    static constexpr int TOTAL = BITS + 2 * 2 * 64 * 4;
+    // inside a stage
+    static constexpr int K4 = 0, V4 = 4096, KSF = 8192, VSF = 9216;
+    static constexpr int K16 = 0, V16 = 16384;
+};
+
+struct Bars {
+    uint64_t q_full, q_empty;
+    uint64_t sched_full[2], sched_empty[2];
+    uint64_t kv_full[NSTAGES], kv_empty[NSTAGES];
+    uint64_t s_full[2], s_free[2];
+    uint64_t p_full, o_ready;
+};
+
+struct Step {
+    int st;  // 64-column step index
+    bool fp16, p0, p1;
+};
+
+// Deterministic walk over the steps of one work item; every role runs its own
+// copy and sees the same sequence.  All 32 lanes of the warp must call next().
+struct StepIter {
+    const int32_t* list0;
+    const int32_t* list1;
+    const uint32_t* bits0;
+    const uint32_t* bits1;
+    int width, spb_shift, spb, nkb, nsteps, nsteps_total, last0, last1;
+    bool has_sel, two;
+    int phase, s, li, sub, cur_id;
+    int32_t cache;
+
+    __device__ __forceinline__ static bool bit(const uint32_t* b, int i) { return (b[i >> 5] >> (i & 31)) & 1u; }
+
+    __device__ bool next(Step& out, int lane) {
+        while (true) {
+            if (phase == 0) {
+                while (s < nsteps) {
+                    const int st = s++;
+                    const int blk = st >> spb_shift;
+                    const bool p0 = (st * STEP <= last0) && !(has_sel && bit(bits0, blk));
+                    const bool p1 = (st * STEP <= last1) && !(has_sel && bit(bits1, blk));
+                    if (p0 | p1) { out = {st, false, p0, p1}; return true; }
+                }
+                phase = has_sel ? 1 : 3;
+                li = 0; sub = 0;
+                continue;
+            }
+            if (phase == 1 || phase == 2) {
+                const int32_t* list = phase == 1 ? list0 : list1;
+                while (li < width) {
+                    if (sub == 0) {
+                        if ((li & 31) == 0) cache = (li + lane < width) ? list[li + lane] : -1;
+                        cur_id = __shfl_sync(0xFFFFFFFFu, cache, li & 31);
+                    }
+                    const int id = cur_id;
+                    bool ok = id >= 0 && id < nkb;
+                    if (ok && phase == 2 && bit(bits0, id)) ok = false;  // already walked with list0
+                    if (ok) {
+                        const int st = (id << spb_shift) + sub;
+                        bool p0, p1;
+                        if (phase == 1) {
+                            p0 = st * STEP <= last0;
+                            p1 = (st * STEP <= last1) && (!two || bit(bits1, id));
+                        } else {
+                            p0 = false;
+                            p1 = st * STEP <= last1;
+                        }
+                        if (++sub == spb) { sub = 0; ++li; }
+                        if ((p0 | p1) && st < nsteps_total) { out = {st, true, p0, p1}; return true; }
+                        continue;
+                    }
+                    sub = 0; ++li;
+                }
+                phase = (phase == 1 && two) ? 2 : 3;
+                li = 0; sub = 0;
+                continue;
+            }
+            return false;
+        }
+    }
+};
+
+struct ItemInfo {
+    int h, t, kvh;
+};
+
+__device__ __forceinline__ ItemInfo decode_item(const PrefillParams& p, int item) {
+    const int hq_flat = p.batch * p.hq_per_b;
+    ItemInfo it;
+    it.t = p.n_qtiles - 1 - item / hq_flat;  // longest (latest) tiles first
+    it.h = item % hq_flat;
+    const int b = it.h / p.hq_per_b;
+    it.kvh = b * p.hkv_per_b + (it.h % p.hq_per_b) / p.group;
+    return it;
+}
+
+__device__ __forceinline__ void init_iter(StepIter& itr, const PrefillParams& p, const ItemInfo& it,
+                                          const uint32_t* bits /* [2][64] */) {
+    const int nqb = p.sq / p.block;
+    const int row0 = it.t * QTILE;
+    const int qb0 = row0 / p.block;
+    const int qb1 = min((row0 + 64) / p.block, nqb - 1);
+    itr.two = (qb1 != qb0);
+    itr.has_sel = p.width > 0;
+    itr.width = p.width;
+    itr.list0 = itr.has_sel ? p.sel + (static_cast<long long>(it.h) * nqb + qb0) * p.width : nullptr;
+    itr.list1 = itr.has_sel ? p.sel + (static_cast<long long>(it.h) * nqb + qb1) * p.width : nullptr;
+    itr.bits0 = bits;
+    itr.bits1 = itr.two ? bits + 64 : bits;
+    itr.spb = p.block / STEP;
+    itr.spb_shift = (p.block == 128) ? 1 : 0;
+    itr.nkb = p.nkb;
+    itr.nsteps_total = p.nsteps_total;
+    if (p.causal) {
+        itr.last0 = row0 + 63;
+        itr.last1 = row0 + 127;
+        itr.nsteps = min(p.nsteps_total, itr.last1 / STEP + 1);
+    } else {
+        itr.last0 = INT_MAX;
+        itr.last1 = INT_MAX;
+        itr.nsteps = p.nsteps_total;
+    }
+    itr.phase = 0; itr.s = 0; itr.li = 0; itr.sub = 0; itr.cur_id = -1; itr.cache = -1;
+}
+
+// Column maps inside a 64-column step.  With the "permuted" K layout physical
+// row p of every 32-row group holds logical row perm32(p); logi[p] is the logical
+// column of physical column p and phys[l] its inverse.
+template <bool KPERM>
+struct ColMap {
+    int logi[STEP];
+    int phys[STEP];
+    constexpr ColMap() : logi(), phys() {
+        for (int p = 0; p < STEP; ++p) {
+            const int l = KPERM ? (p / 32) * 32 + perm32(p % 32) : p;
+            logi[p] = l;
+            phys[l] = p;
+        }
+    }
+};
+
+template <int D, bool MX, bool BF16, bool CAUSAL, bool KPERM>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4, const __grid_constant__ CUtensorMap mapK4,
+               const __grid_constant__ CUtensorMap mapV4, const __grid_constant__ CUtensorMap mapQ16,
+               const __grid_constant__ CUtensorMap mapK16, const __grid_constant__ CUtensorMap mapV16) {
+    using L = Smem<D>;
+    constexpr int QK_ATOMS = MX ? 1 : D / 64;     // 512-byte scale atoms per tile for Q and K
+    constexpr int KBLK = D / 64;                   // K=64 MMAs per QK^T (FP4)
+    constexpr uint32_t ROW4 = D / 2;               // bytes per FP4 row of Q / K
+    constexpr uint32_t SWZ_QK = (ROW4 == 64) ? SWZ_64B : SWZ_32B;
+    constexpr uint32_t SBO_QK = 8 * ROW4;
+    constexpr int HALVES = D / 64;                 // 64-column halves of a 16-bit row
+    constexpr float CSCALE = MX ? 6.0f : 2688.0f;
+    constexpr float CSCALE_INV = MX ? (1.0f / 6.0f) : (1.0f / 2688.0f);
+    constexpr ColMap<KPERM> cmap{};
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    __shared__ Bars bars;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const uint32_t sbase = smem_u32(smem);
+    volatile int* abortp = &abort_flag;
+    const long long budget = p.budget;
+
+    if (tid == 0) {
+        mbar_init(smem_u32(&bars.q_full), 1);
+        mbar_init(smem_u32(&bars.q_empty), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&bars.sched_full[i]), 1);
+            mbar_init(smem_u32(&bars.sched_empty[i]), 5);
+            mbar_init(smem_u32(&bars.s_full[i]), 1);
+            mbar_init(smem_u32(&bars.s_free[i]), 128);
+        }
+        for (int i = 0; i < NSTAGES; ++i) {
+            mbar_init(smem_u32(&bars.kv_full[i]), 1);
+            mbar_init(smem_u32(&bars.kv_empty[i]), 1);
+        }
+        mbar_init(smem_u32(&bars.p_full), 128);
+        mbar_init(smem_u32(&bars.o_ready), 1);
+        mbar_fence_init();
+        abort_flag = 0;
+    }
+    // constant scale atom for P: 448 (E4M3 0x7E) or 1.0 (E8M0 0x7F)
+    for (int i = tid; i < 512 / 4; i += NUM_THREADS)
+        reinterpret_cast<uint32_t*>(smem + L::CSF)[i] = MX ? 0x7F7F7F7Fu : 0x7E7E7E7Eu;
+    fence_proxy_async_smem();
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_s), TM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = tmem_base_s;
+
+    const int hkv_flat = p.batch * p.hkv_per_b;
+    (void)hkv_flat;
+
+    if (warp == 0) {
+        // =========================== producer ===========================
+        if (lane == 0) {
+            tma_prefetch_desc(&mapQ4); tma_prefetch_desc(&mapK4); tma_prefetch_desc(&mapV4);
+            tma_prefetch_desc(&mapQ16); tma_prefetch_desc(&mapK16); tma_prefetch_desc(&mapV16);
+        }
+        uint32_t gstep = 0;
+        int n_item = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
+            const ItemInfo it = decode_item(p, item);
+            const int sb = n_item & 1;
+            uint32_t* bits = reinterpret_cast<uint32_t*>(smem + L::BITS) + sb * 128;
+            // ---- block bitsets for this item ----
+            ok = mbar_wait(smem_u32(&bars.sched_empty[sb]), ((n_item >> 1) & 1) ^ 1, abortp, budget);
+            if (!ok) break;
+            StepIter itr;
+            init_iter(itr, p, it, bits);
+            for (int i = lane; i < 128; i += 32) bits[i] = 0u;
+            __syncwarp();
+            if (itr.has_sel) {
+                for (int half = 0; half < (itr.two ? 2 : 1); ++half) {
+                    const int32_t* list = half ? itr.list1 : itr.list0;
+                    for (int i = lane; i < p.width; i += 32) {
+                        const int id = list[i];
+                        if (id >= 0 && id < p.nkb) atomicOr(&bits[half * 64 + (id >> 5)], 1u << (id & 31));
+                    }
+                }
+            }
+            __syncwarp();
+            __threadfence_block();
+            if (lane == 0) mbar_arrive(smem_u32(&bars.sched_full[sb]));
+            // ---- Q tile ----
+            ok = mbar_wait(smem_u32(&bars.q_empty), (n_item & 1) ^ 1, abortp, budget);
+            if (!ok) break;
+            if (lane == 0) {
+                const uint32_t bar = smem_u32(&bars.q_full);
+                const uint32_t bytes = QTILE * ROW4 + QK_ATOMS * 512 + (itr.has_sel ? QTILE * D * 2 : 0);
+                mbar_expect_tx(bar, bytes);
+                tma_load_3d(sbase + L::Q4, &mapQ4, bar, 0, it.t * QTILE, it.h);
+                bulk_load(sbase + L::QSF, p.q_sf + (static_cast<long long>(it.h) * p.n_qtiles + it.t) * QK_ATOMS * 512,
+                          QK_ATOMS * 512, bar);
+                if (itr.has_sel)
+                    for (int hf = 0; hf < HALVES; ++hf)
+                        tma_load_3d(sbase + L::Q16 + hf * QTILE * 128, &mapQ16, bar, hf * 64, it.t * QTILE, it.h);
+            }
+            // ---- K/V steps ----
+            Step stp;
+            while (itr.next(stp, lane)) {
+                const uint32_t stage = gstep % NSTAGES;
+                ok = mbar_wait(smem_u32(&bars.kv_empty[stage]), ((gstep / NSTAGES) & 1) ^ 1, abortp, budget);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t bar = smem_u32(&bars.kv_full[stage]);
+                    const uint32_t sa = sbase + L::STAGES + stage * STAGE_BYTES;
+                    if (!stp.fp16) {
+                        mbar_expect_tx(bar, STEP * ROW4 + D * 32 + QK_ATOMS * 512 + 512);
+                        tma_load_3d(sa + L::K4, &mapK4, bar, 0, stp.st * STEP, it.kvh);
+                        tma_load_3d(sa + L::V4, &mapV4, bar, stp.st * (STEP / 2), 0, it.kvh);
+                        bulk_load(sa + L::KSF,
+                                  p.k_sf + (static_cast<long long>(it.kvh) * p.nsteps_total + stp.st) * QK_ATOMS * 512,
+                                  QK_ATOMS * 512, bar);
+                        bulk_load(sa + L::VSF, p.v_sf + (static_cast<long long>(it.kvh) * p.nsteps_total + stp.st) * 512,
+                                  512, bar);
+                    } else {
+                        mbar_expect_tx(bar, 2 * STEP * D * 2);
+                        for (int hf = 0; hf < HALVES; ++hf) {
+                            tma_load_3d(sa + L::K16 + hf * STEP * 128, &mapK16, bar, hf * 64, stp.st * STEP, it.kvh);
+                            tma_load_3d(sa + L::V16 + hf * STEP * 128, &mapV16, bar, hf * 64, stp.st * STEP, it.kvh);
+                        }
+                    }
+                }
+                ++gstep;
+            }
+        }
+    } else if (warp == 1) {
+        // =========================== MMA issuer ===========================
+        if (lane == 0) tmem_cp_sf(tmem + TM_SFA_P, make_smem_desc(sbase + L::CSF, 0, 128, SWZ_NONE));
+        uint32_t gstep = 0;
+        int n_item = 0;
+        bool ok = true;
+        const uint32_t idesc_qk4 = make_idesc_fp4(128, STEP, MX ? 1 : 0, 0, 0);
+        const uint32_t idesc_pv4 = make_idesc_fp4(128, D, MX ? 1 : 0, 0, 0);
+        const uint32_t idesc_qk16 = make_idesc_f16(128, STEP, BF16 ? 1 : 0, 0, 0);
+        const uint32_t idesc_pv16 = make_idesc_f16(128, D, BF16 ? 1 : 0, 0, 1);
+
+        auto issue_qk = [&](const Step& s, uint32_t g) {
+            const uint32_t stage = g % NSTAGES, buf = g & 1;
+            const uint32_t sa = sbase + L::STAGES + stage * STAGE_BYTES;
+            const uint32_t d_t = tmem + TM_S + buf * STEP;
+            if (!s.fp16) {
+                const uint32_t sfb = tmem + TM_SFB_K + buf * 8;
+                for (int a = 0; a < QK_ATOMS; ++a)
+                    tmem_cp_sf(sfb + a * 4, make_smem_desc(sa + L::KSF + a * 512, 0, 128, SWZ_NONE));
+                for (int kb = 0; kb < KBLK; ++kb) {
+                    const uint64_t ad = make_smem_desc(sbase + L::Q4 + kb * 32, 16, SBO_QK, SWZ_QK);
+                    const uint64_t bd = make_smem_desc(sa + L::K4 + kb * 32, 16, SBO_QK, SWZ_QK);
+                    if constexpr (MX)
+                        mma_mxfp4(d_t, ad, bd, make_idesc_fp4(128, STEP, 1, kb * 2, kb * 2), tmem + TM_SFA_Q, sfb, kb > 0);
+                    else
+                        mma_nvfp4(d_t, ad, bd, idesc_qk4, tmem + TM_SFA_Q + kb * 4, sfb + kb * 4, kb > 0);
+                }
+            } else {
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t hf = ks / 4, kk = ks % 4;
+                    const uint64_t ad = make_smem_desc(sbase + L::Q16 + hf * QTILE * 128 + kk * 32, 16, 1024, SWZ_128B);
+                    const uint64_t bd = make_smem_desc(sa + L::K16 + hf * STEP * 128 + kk * 32, 16, 1024, SWZ_128B);
+                    mma_f16(d_t, ad, bd, idesc_qk16, ks > 0);
+                }
+            }
+            tc_commit(smem_u32(&bars.s_full[buf]));
+        };
+
+        for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
+            const ItemInfo it = decode_item(p, item);
+            const int sb = n_item & 1;
+            const uint32_t* bits = reinterpret_cast<const uint32_t*>(smem + L::BITS) + sb * 128;
+            ok = mbar_wait(smem_u32(&bars.sched_full[sb]), (n_item >> 1) & 1, abortp, budget);
+            if (!ok) break;
+            StepIter itr;
+            init_iter(itr, p, it, bits);
+            ok = mbar_wait(smem_u32(&bars.q_full), n_item & 1, abortp, budget);
+            if (!ok) break;
+            tc_fence_after_sync();
+            if (lane == 0)
+                for (int a = 0; a < QK_ATOMS; ++a)
+                    tmem_cp_sf(tmem + TM_SFA_Q + a * 4, make_smem_desc(sbase + L::QSF + a * 512, 0, 128, SWZ_NONE));
+
+            Step cur, nxt;
+            bool have_cur = itr.next(cur, lane);
+            bool first_pv = true;
+            if (!have_cur && lane == 0) mbar_arrive(smem_u32(&bars.q_empty));
+            if (have_cur) {
+                // QK for the first step
+                const uint32_t stage = gstep % NSTAGES, buf = gstep & 1;
+                ok = mbar_wait(smem_u32(&bars.kv_full[stage]), (gstep / NSTAGES) & 1, abortp, budget) &&
+                     mbar_wait(smem_u32(&bars.s_free[buf]), ((gstep >> 1) & 1) ^ 1, abortp, budget);
+                if (ok) {
+                    tc_fence_after_sync();
+                    if (lane == 0) issue_qk(cur, gstep);
+                    __syncwarp();
+                }
+            }
+            while (have_cur && ok) {
+                const bool have_nxt = itr.next(nxt, lane);
+                if (have_nxt) {
+                    const uint32_t g1 = gstep + 1;
+                    const uint32_t stage = g1 % NSTAGES, buf = g1 & 1;
+                    ok = mbar_wait(smem_u32(&bars.kv_full[stage]), (g1 / NSTAGES) & 1, abortp, budget) &&
+                         mbar_wait(smem_u32(&bars.s_free[buf]), ((g1 >> 1) & 1) ^ 1, abortp, budget);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    if (lane == 0) issue_qk(nxt, g1);
+                    __syncwarp();
+                }
+                // PV for the current step
+                ok = mbar_wait(smem_u32(&bars.p_full), gstep & 1, abortp, budget);
+                if (!ok) break;
+                tc_fence_after_sync();
+                if (lane == 0) {
+                    const uint32_t stage = gstep % NSTAGES, buf = gstep & 1;
+                    const uint32_t sa = sbase + L::STAGES + stage * STAGE_BYTES;
+                    const uint32_t d_t = tmem + TM_O;
+                    if (!cur.fp16) {
+                        const uint32_t sfb = tmem + TM_SFB_V + buf * 4;
+                        tmem_cp_sf(sfb, make_smem_desc(sa + L::VSF, 0, 128, SWZ_NONE));
+                        const uint64_t ad = make_smem_desc(sbase + L::P, 16, 256, SWZ_32B);
+                        const uint64_t bd = make_smem_desc(sa + L::V4, 16, 256, SWZ_32B);
+                        if constexpr (MX) mma_mxfp4(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, first_pv ? 0 : 1);
+                        else mma_nvfp4(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, first_pv ? 0 : 1);
+                    } else {
+                        for (int ks = 0; ks < STEP / 16; ++ks) {
+                            const uint64_t ad = make_smem_desc(sbase + L::P + ks * 32, 16, 1024, SWZ_128B);
+                            const uint64_t bd = make_smem_desc(sa + L::V16 + ks * 2048, STEP * 128, 1024, SWZ_128B);
+                            mma_f16(d_t, ad, bd, idesc_pv16, (first_pv && ks == 0) ? 0 : 1);
+                        }
+                    }
+                    tc_commit(smem_u32(&bars.kv_empty[stage]));
+                    tc_commit(smem_u32(&bars.o_ready));
+                    if (!have_nxt) tc_commit(smem_u32(&bars.q_empty));
+                }
+                __syncwarp();
+                first_pv = false;
+                ++gstep;
+                cur = nxt;
+                have_cur = have_nxt;
+            }
+            if (lane == 0) mbar_arrive(smem_u32(&bars.sched_empty[sb]));
+        }
+    } else {
+        // =========================== softmax ===========================
+        const int sub = warp & 3;                 // tensor-memory sub-partition
+        const int row = sub * 32 + lane;          // row inside the q tile
+        const int half = sub >> 1;                // 0: rows 0..63, 1: rows 64..127
+        const uint32_t lane_addr = static_cast<uint32_t>(sub * 32) << 16;
+        uint32_t gstep = 0;
+        int n_item = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
+            const ItemInfo it = decode_item(p, item);
+            const int sb = n_item & 1;
+            const uint32_t* bits = reinterpret_cast<const uint32_t*>(smem + L::BITS) + sb * 128;
+            ok = mbar_wait(smem_u32(&bars.sched_full[sb]), (n_item >> 1) & 1, abortp, budget);
+            if (!ok) break;
+            StepIter itr;
+            init_iter(itr, p, it, bits);
+            const int grow = it.t * QTILE + row;  // absolute query row
+            float m_run = -FLT_MAX, l_run = 0.0f;
+            int n_done = 0;
+            bool prev_fp4 = false;
+            Step stp;
+            while (itr.next(stp, lane)) {
+                const uint32_t buf = gstep & 1;
+                ok = mbar_wait(smem_u32(&bars.s_full[buf]), (gstep >> 1) & 1, abortp, budget);
+                if (!ok) break;
+                tc_fence_after_sync();
+                float s[STEP];
+                {
+                    uint32_t r0[32], r1[32];
+                    tmem_ld32(tmem + lane_addr + TM_S + buf * STEP, r0);
+                    tmem_ld32(tmem + lane_addr + TM_S + buf * STEP + 32, r1);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) { s[j] = __uint_as_float(r0[j]); s[32 + j] = __uint_as_float(r1[j]); }
+                }
+                tc_fence_before_sync();
+                mbar_arrive(smem_u32(&bars.s_free[buf]));
+
+                const bool part = half ? stp.p1 : stp.p0;
+                const int col0 = stp.st * STEP;
+                float rescale = 1.0f;
+                bool changed = false;
+                float mneg = 0.0f;
+                if (part) {
+                    if (CAUSAL && (col0 + STEP - 1 > grow)) {
+#pragma unroll
+                        for (int j = 0; j < STEP; ++j) {
+                            const int lc = stp.fp16 ? j : cmap.logi[j];
+                            if (col0 + lc > grow) s[j] = -INFINITY;
+                        }
+                    }
+                    float mx = -FLT_MAX;
+#pragma unroll
+                    for (int j = 0; j < STEP; ++j) mx = fmaxf(mx, s[j]);
+                    const float m_new = fmaxf(m_run, mx);
+                    changed = m_new > m_run;
+                    rescale = ex2((m_run - m_new) * p.c2);
+                    m_run = m_new;
+                    mneg = -m_new * p.c2;
+                }
+                // previous PV must be complete before O or the P buffer is touched
+                if (gstep > 0) {
+                    ok = mbar_wait(smem_u32(&bars.o_ready), (gstep - 1) & 1, abortp, budget);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                }
+                // state rounding between the FP4 and the 16-bit phase
+                const bool transition = stp.fp16 && prev_fp4 && p.round_partial;
+                if (transition) {
+                    const float norm = l_run > 0.0f ? __fdiv_rn(CSCALE_INV, l_run) : 0.0f;
+                    const float back = l_run * CSCALE;
+#pragma unroll 1
+                    for (int c = 0; c < D; c += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(tmem + lane_addr + TM_O + c, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float v = __uint_as_float(r[j]) * norm;
+                            r[j] = __float_as_uint(In16<BF16>::to_f(In16<BF16>::from_f(v)) * back);
+                        }
+                        tmem_st32(tmem + lane_addr + TM_O + c, r);
+                    }
+                    tmem_wait_st();
+                }
+                if (__any_sync(0xFFFFFFFFu, changed && n_done > 0)) {
+#pragma unroll 1
+                    for (int c = 0; c < D; c += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(tmem + lane_addr + TM_O + c, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rescale);
+                        tmem_st32(tmem + lane_addr + TM_O + c, r);
+                    }
+                    tmem_wait_st();
+                }
+                // probabilities, row sum, P tile
+                uint8_t* prow = smem + L::P;
+                if (!stp.fp16) {
+                    uint32_t w[STEP / 8];
+                    if (part) {
+                        float sum = 0.0f;
+#pragma unroll
+                        for (int j = 0; j < STEP; ++j) {
+                            s[j] = ex2(fmaf(s[j], p.c2, mneg));
+                            sum += s[j];
+                        }
+                        l_run = l_run * rescale + sum;
+#pragma unroll
+                        for (int g = 0; g < STEP / 8; ++g) {
+                            float v[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[e] = s[cmap.phys[g * 8 + e]] * 6.0f;
+                            w[g] = e2m1x8(v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < STEP / 8; ++g) w[g] = 0u;
+                    }
+                    // 128 rows x 32 bytes, 32-byte swizzle
+                    const uint32_t r8 = row & 7;
+                    uint8_t* base = prow + (row >> 3) * 256 + r8 * 32;
+                    const uint32_t x = (r8 >> 2) & 1;
+                    *reinterpret_cast<uint4*>(base + ((0 ^ x) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(base + ((1 ^ x) * 16)) = make_uint4(w[4], w[5], w[6], w[7]);
+                } else {
+                    uint32_t w[STEP / 2];
+                    if (part) {
+                        float sum = 0.0f;
+#pragma unroll
+                        for (int j = 0; j < STEP; ++j) {
+                            s[j] = ex2(fmaf(s[j], p.c2, mneg));
+                            sum += s[j];
+                        }
+                        l_run = l_run * rescale + sum;
+#pragma unroll
+                        for (int j = 0; j < STEP / 2; ++j) w[j] = In16<BF16>::pack2(s[2 * j] * CSCALE, s[2 * j + 1] * CSCALE);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < STEP / 2; ++j) w[j] = 0u;
+                    }
+                    // 128 rows x 128 bytes, 128-byte swizzle
+                    const uint32_t r8 = row & 7;
+                    uint8_t* base = prow + (row >> 3) * 1024 + r8 * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        *reinterpret_cast<uint4*>(base + ((c ^ r8) * 16)) =
+                            make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+                }
+                fence_proxy_async_smem();
+                tc_fence_before_sync();
+                mbar_arrive(smem_u32(&bars.p_full));
+                prev_fp4 = !stp.fp16;
+                ++n_done;
+                ++gstep;
+            }
+            if (!ok) break;
+            // ---- epilogue ----
+            uint16_t* orow = p.out + (static_cast<long long>(it.h) * p.sq + grow) * D;
+            if (n_done > 0) {
+                ok = mbar_wait(smem_u32(&bars.o_ready), (gstep - 1) & 1, abortp, budget);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const float norm = l_run > 0.0f ? __fdiv_rn(CSCALE_INV, l_run) : 0.0f;
+#pragma unroll 1
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem + lane_addr + TM_O + c, r);
+                    tmem_wait_ld();
+                    if (grow < p.sq) {
+#pragma unroll
+                        for (int v4 = 0; v4 < 4; ++v4) {
+                            uint32_t o[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                o[e] = In16<BF16>::pack2(__uint_as_float(r[v4 * 8 + 2 * e]) * norm,
+                                                         __uint_as_float(r[v4 * 8 + 2 * e + 1]) * norm);
+                            *reinterpret_cast<uint4*>(orow + c + v4 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                        }
+                    }
+                }
+                tc_fence_before_sync();
+            } else if (grow < p.sq) {
+                for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars.sched_empty[sb]));
+        }
+    }
+
+    // ---- common exit ----
+    if (abort_flag != 0) __nanosleep(20000);  // let copies already in flight land
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, TM_COLS);
+    if (tid == 0 && abort_flag != 0) atomicExch(p.status, 1);
+}
+
+// ---------------------------------------------------------------------------
+// Scale-factor re-tiling: row-major scale bytes -> 512-byte tcgen05 atoms
+//   atom[m0 * 16 + m1 * 4 + j] = scale(row = 32 * m1 + m0, j)
+// ---------------------------------------------------------------------------
+__global__ void retile_row_scales_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int heads,
+                                         int rows_valid, long long head_stride_rows, int spr, int tile_rows,
+                                         int ntiles, int natoms, int per_atom) {
+    const long long total = static_cast<long long>(heads) * ntiles * natoms * 128;  // 4-byte words
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int wi = static_cast<int>(i & 127);
+        const int m0 = wi >> 2, m1 = wi & 3;
+        long long rest = i >> 7;
+        const int atom = static_cast<int>(rest % natoms); rest /= natoms;
+        const int tile = static_cast<int>(rest % ntiles);
+        const int head = static_cast<int>(rest / ntiles);
+        const int r_in_tile = 32 * m1 + m0;
+        const long long row = static_cast<long long>(tile) * tile_rows + r_in_tile;
+        uint32_t word = 0;
+        if (r_in_tile < tile_rows && row < rows_valid) {
+            const uint8_t* s = src + (head * head_stride_rows + row) * spr + atom * per_atom;
+            for (int j = 0; j < per_atom; ++j) word |= static_cast<uint32_t>(s[j]) << (8 * j);
+        }
+        reinterpret_cast<uint32_t*>(dst)[i] = word;
+    }
+}
+
+// v_scale_t [heads, D, pg] -> atoms [heads, nsteps, 512]: scale(d = 32*m1+m0, step*per + j)
+__global__ void retile_v_scales_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int heads, int d,
+                                       int pg, int nsteps, int per) {
+    const long long total = static_cast<long long>(heads) * nsteps * 128;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int wi = static_cast<int>(i & 127);
+        const int m0 = wi >> 2, m1 = wi & 3;
+        const long long rest = i >> 7;
+        const int step = static_cast<int>(rest % nsteps);
+        const int head = static_cast<int>(rest / nsteps);
+        const int ch = 32 * m1 + m0;
+        uint32_t word = 0;
+        if (ch < d) {
+            const uint8_t* s = src + (static_cast<long long>(head) * d + ch) * pg + step * per;
+            for (int j = 0; j < per; ++j)
+                if (step * per + j < pg) word |= static_cast<uint32_t>(s[j]) << (8 * j);
+        }
+        reinterpret_cast<uint32_t*>(dst)[i] = word;
+    }
+}
+
+struct WsLayout {
+    size_t q_sf, k_sf, v_sf, status, total;
+};
+
+WsLayout ws_layout(int hq_flat, int hkv_flat, int sq, int skv, int d, int is_mx) {
+    const int atoms = is_mx ? 1 : d / 64;
+    const size_t n_qtiles = cdiv(sq, QTILE), nsteps = cdiv(skv, STEP);
+    WsLayout w;
+    w.q_sf = 0;
+    w.k_sf = w.q_sf + static_cast<size_t>(hq_flat) * n_qtiles * atoms * 512;
+    w.v_sf = w.k_sf + static_cast<size_t>(hkv_flat) * nsteps * atoms * 512;
+    w.status = w.v_sf + static_cast<size_t>(hkv_flat) * nsteps * 512;
+    w.total = w.status + 256;
+    return w;
+}
+
+template <int D, bool MX, bool BF16, bool CAUSAL, bool KPERM>
+int launch_prefill_t(const PrefillParams& p, const CUtensorMap* maps, int grid, cudaStream_t stream) {
+    auto kern = prefill_kernel<D, MX, BF16, CAUSAL, KPERM>;
+    const int smem = Smem<D>::TOTAL + 1024;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    kern<<<grid, NUM_THREADS, smem, stream>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);
+    return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace
+
+size_t prefill_workspace_bytes(int batch, int hq, int hkv, int sq, int skv, int d, int is_mx) {
+    return ws_layout(batch * hq, batch * hkv, sq, skv, d, is_mx).total;
+}
+
+// See include/thrift_sm100.h (ta100_prefill_attention) for the contract.
+int prefill_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const void* sel, int width, int block,
+                     const void* q4, const void* k4, const void* v4t, const void* qs, const void* ks, const void* vst,
+                     void* out, void* workspace, size_t workspace_bytes, int batch, int hq, int hkv, int sq, int skv,
+                     int kv_cap, int d, int causal, int is_mx, int is_bf16, int k_permuted, int round_partial,
+                     int max_ctas, cudaStream_t stream) {
+    if (!q4 || !k4 || !v4t || !qs || !ks || !vst || !out || !workspace) return TA100_ERR_NULL;
+    if (width > 0 && (!q_hi || !k_hi || !v_hi || !sel)) return TA100_ERR_NULL;
+    if (d != 128) return TA100_ERR_UNSUPPORTED;
+    if (block != 64 && block != 128) return TA100_ERR_UNSUPPORTED;
+    if (batch <= 0 || hq <= 0 || hkv <= 0 || hq % hkv != 0 || sq <= 0 || skv <= 0) return TA100_ERR_SHAPE;
+    if (sq % 64 != 0 || skv % 64 != 0 || kv_cap < skv) return TA100_ERR_SHAPE;
+    if (width > 0 && (sq % block != 0 || skv % block != 0)) return TA100_ERR_SHAPE;
+    if (skv / 64 > 2048 || width > 2048) return TA100_ERR_LIMIT;
+    const int hq_flat = batch * hq, hkv_flat = batch * hkv;
+    const WsLayout w = ws_layout(hq_flat, hkv_flat, sq, skv, d, is_mx);
+    if (workspace_bytes < w.total) return TA100_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return TA100_ERR_ALIGN;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    const int G = is_mx ? 32 : 16;
+    const int spr = d / G;
+    const int atoms = is_mx ? 1 : d / 64;
+    const int per_atom = is_mx ? spr : 4;
+    const int n_qtiles = cdiv(sq, QTILE), nsteps = cdiv(skv, STEP);
+    const int P = cdiv(kv_cap, 128) * 128;
+
+    cudaError_t e = cudaMemsetAsync(ws + w.status, 0, 4, stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    {
+        long long words = static_cast<long long>(hq_flat) * n_qtiles * atoms * 128;
+        retile_row_scales_kernel<<<grid_for(words, 256, 8), 256, 0, stream>>>(
+            static_cast<const uint8_t*>(qs), ws + w.q_sf, hq_flat, sq, sq, spr, QTILE, n_qtiles, atoms, per_atom);
+        words = static_cast<long long>(hkv_flat) * nsteps * atoms * 128;
+        retile_row_scales_kernel<<<grid_for(words, 256, 8), 256, 0, stream>>>(
+            static_cast<const uint8_t*>(ks), ws + w.k_sf, hkv_flat, skv, kv_cap, spr, STEP, nsteps, atoms, per_atom);
+        words = static_cast<long long>(hkv_flat) * nsteps * 128;
+        retile_v_scales_kernel<<<grid_for(words, 256, 8), 256, 0, stream>>>(
+            static_cast<const uint8_t*>(vst), ws + w.v_sf, hkv_flat, d, P / G, nsteps, STEP / G);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return static_cast<int>(e);
+    }
+
+    CUtensorMap maps[6];
+    memset(maps, 0, sizeof(maps));
+    {
+        const CUtensorMapSwizzle sw4 = (d / 2 == 64) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+        int rc = 0;
+        {
+            uint64_t dims[3] = {static_cast<uint64_t>(d / 2), static_cast<uint64_t>(sq), static_cast<uint64_t>(hq_flat)};
+            uint64_t str[2] = {static_cast<uint64_t>(d / 2), static_cast<uint64_t>(sq) * (d / 2)};
+            uint32_t box[3] = {static_cast<uint32_t>(d / 2), QTILE, 1};
+            rc |= make_tensor_map(&maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, q4, dims, str, box, sw4);
+        }
+        {
+            uint64_t dims[3] = {static_cast<uint64_t>(d / 2), static_cast<uint64_t>(skv), static_cast<uint64_t>(hkv_flat)};
+            uint64_t str[2] = {static_cast<uint64_t>(d / 2), static_cast<uint64_t>(kv_cap) * (d / 2)};
+            uint32_t box[3] = {static_cast<uint32_t>(d / 2), STEP, 1};
+            rc |= make_tensor_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, k4, dims, str, box, sw4);
+        }
+        {
+            uint64_t dims[3] = {static_cast<uint64_t>(P / 2), static_cast<uint64_t>(d), static_cast<uint64_t>(hkv_flat)};
+            uint64_t str[2] = {static_cast<uint64_t>(P / 2), static_cast<uint64_t>(d) * (P / 2)};
+            uint32_t box[3] = {STEP / 2, static_cast<uint32_t>(d), 1};
+            rc |= make_tensor_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, v4t, dims, str, box,
+                                  CU_TENSOR_MAP_SWIZZLE_32B);
+        }
+        if (width > 0) {
+            const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+            {
+                uint64_t dims[3] = {static_cast<uint64_t>(d), static_cast<uint64_t>(sq), static_cast<uint64_t>(hq_flat)};
+                uint64_t str[2] = {static_cast<uint64_t>(d) * 2, static_cast<uint64_t>(sq) * d * 2};
+                uint32_t box[3] = {64, QTILE, 1};
+                rc |= make_tensor_map(&maps[3], dt, 3, q_hi, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+            }
+            uint64_t dims[3] = {static_cast<uint64_t>(d), static_cast<uint64_t>(skv), static_cast<uint64_t>(hkv_flat)};
+            uint64_t str[2] = {static_cast<uint64_t>(d) * 2, static_cast<uint64_t>(skv) * d * 2};
+            uint32_t box[3] = {64, STEP, 1};
+            rc |= make_tensor_map(&maps[4], dt, 3, k_hi, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+            rc |= make_tensor_map(&maps[5], dt, 3, v_hi, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        } else {
+            maps[3] = maps[0]; maps[4] = maps[0]; maps[5] = maps[0];
+        }
+        if (rc != 0) return TA100_ERR_TENSOR_MAP;
+    }
+
+    PrefillParams p;
+    p.batch = batch; p.hq_per_b = hq; p.hkv_per_b = hkv; p.group = hq / hkv;
+    p.sq = sq; p.skv = skv; p.block = block; p.width = width;
+    p.causal = causal; p.round_partial = round_partial;
+    p.n_qtiles = n_qtiles; p.n_items = n_qtiles * hq_flat; p.nsteps_total = nsteps; p.nkb = skv / block;
+    p.sel = static_cast<const int32_t*>(sel);
+    p.q_sf = ws + w.q_sf; p.k_sf = ws + w.k_sf; p.v_sf = ws + w.v_sf;
+    p.out = static_cast<uint16_t*>(out);
+    p.status = reinterpret_cast<int*>(ws + w.status);
+    p.c2 = static_cast<float>((1.0 / sqrt(static_cast<double>(d))) * 1.4426950408889634);
+    p.budget = 1000000000LL;
+
+    int dev = 0, sms = NUM_SMS_HINT;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int grid = p.n_items < sms ? p.n_items : sms;
+    if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+
+#define TA100_PF(MXX, BFF, CC, KP) launch_prefill_t<128, MXX, BFF, CC, KP>(p, maps, grid, stream)
+#define TA100_PF2(MXX, BFF)                                                                    \
+    (causal ? (k_permuted ? TA100_PF(MXX, BFF, true, true) : TA100_PF(MXX, BFF, true, false))  \
+            : (k_permuted ? TA100_PF(MXX, BFF, false, true) : TA100_PF(MXX, BFF, false, false)))
+    int rc;
+    if (is_mx) rc = is_bf16 ? TA100_PF2(true, true) : TA100_PF2(true, false);
+    else rc = is_bf16 ? TA100_PF2(false, true) : TA100_PF2(false, false);
+#undef TA100_PF2
+#undef TA100_PF
+    return rc;
+}
+
+// Reads back the device status word written by the last prefill launch that
+// used `workspace` (synchronises the stream).
+int prefill_status(const void* workspace, int batch, int hq, int hkv, int sq, int skv, int d, int is_mx,
+                   cudaStream_t stream) {
+    const WsLayout w = ws_layout(batch * hq, batch * hkv, sq, skv, d, is_mx);
+    int st = 0;
+    cudaError_t e = cudaMemcpyAsync(&st, static_cast<const uint8_t*>(workspace) + w.status, 4, cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    return st ? TA100_ERR_DEVICE_TIMEOUT : TA100_OK;
+}
+
+}  // namespace ta100

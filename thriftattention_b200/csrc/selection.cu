@@ -1,0 +1,396 @@
+// Block selection: per-block statistics (mean / min / max), block-mean and
+// Quest scoring with an exact warp top-k, decode variants with group-max
+// scores, closed-form local windows and the index-list -> bitset packer.
+//
+// Score arithmetic is fixed so that results are reproducible bit for bit:
+// lane l of a warp accumulates channels l, l+32, ... with fused multiply-adds,
+// then the 32 partial sums are combined by an xor butterfly (deltas 16..1).
+// Top-k is k rounds of arg-max with knock-out; ties go to the candidate whose
+// index modulo 32 has the smallest 5-bit bit-reversal, then to the smaller index.
+#include <cfloat>
+
+#include "common.cuh"
+
+namespace ta100 {
+
+// ---------------------------------------------------------------------------
+// Block statistics
+// ---------------------------------------------------------------------------
+// x [heads, seq, D] -> mean/min/max [heads, seq/block, D] (any may be null).
+// Eight row groups accumulate rows r = g (mod 8) in ascending order in fp32; the
+// eight partial sums are then added left to right and divided by `block`.
+template <int D, bool BF16>
+__global__ void __launch_bounds__(D) block_stats_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ mean,
+                                                        uint16_t* __restrict__ mn, uint16_t* __restrict__ mx,
+                                                        long long n_blocks, int block) {
+    constexpr int CHUNKS = D / 8;  // 16-byte chunks per row
+    __shared__ float s_sum[8][D];
+    __shared__ float s_min[8][D];
+    __shared__ float s_max[8][D];
+    const int cc = threadIdx.x % CHUNKS;
+    const int rg = threadIdx.x / CHUNKS;  // 0..7
+    for (long long blk = blockIdx.x; blk < n_blocks; blk += gridDim.x) {
+        float sum[8], lo[8], hi[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { sum[i] = 0.0f; lo[i] = INFINITY; hi[i] = -INFINITY; }
+        const uint16_t* base = x + blk * block * D;
+#pragma unroll 4
+        for (int r = rg; r < block; r += 8) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(base + static_cast<long long>(r) * D) + cc);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float a = In16<BF16>::to_f(static_cast<uint16_t>(w[i] & 0xFFFFu));
+                const float b = In16<BF16>::to_f(static_cast<uint16_t>(w[i] >> 16));
+                sum[2 * i] = __fadd_rn(sum[2 * i], a);
+                sum[2 * i + 1] = __fadd_rn(sum[2 * i + 1], b);
+                lo[2 * i] = fminf(lo[2 * i], a); lo[2 * i + 1] = fminf(lo[2 * i + 1], b);
+                hi[2 * i] = fmaxf(hi[2 * i], a); hi[2 * i + 1] = fmaxf(hi[2 * i + 1], b);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            s_sum[rg][cc * 8 + i] = sum[i];
+            s_min[rg][cc * 8 + i] = lo[i];
+            s_max[rg][cc * 8 + i] = hi[i];
+        }
+        __syncthreads();
+        {
+            const int c = threadIdx.x;  // one channel per thread
+            float total = s_sum[0][c], l = s_min[0][c], h = s_max[0][c];
+#pragma unroll
+            for (int g = 1; g < 8; ++g) {
+                total = __fadd_rn(total, s_sum[g][c]);
+                l = fminf(l, s_min[g][c]);
+                h = fmaxf(h, s_max[g][c]);
+            }
+            const long long o = blk * D + c;
+            if (mean) mean[o] = In16<BF16>::from_f(__fdiv_rn(total, static_cast<float>(block)));
+            if (mn) mn[o] = In16<BF16>::from_f(l);
+            if (mx) mx[o] = In16<BF16>::from_f(h);
+        }
+        __syncthreads();
+    }
+}
+
+int block_stats_dispatch(const void* x, void* mean, void* mn, void* mx, long long heads, int seq, int d, int block,
+                         int is_bf16, cudaStream_t stream) {
+    if (!x) return TA100_ERR_NULL;
+    if (d != 64 && d != 128) return TA100_ERR_UNSUPPORTED;
+    if (block <= 0 || seq % block != 0) return TA100_ERR_SHAPE;
+    const long long n_blocks = heads * (seq / block);
+    if (n_blocks == 0) return TA100_OK;
+    const int grid = static_cast<int>(n_blocks < NUM_SMS_HINT * 16LL ? n_blocks : NUM_SMS_HINT * 16LL);
+    auto X = static_cast<const uint16_t*>(x);
+    auto A = static_cast<uint16_t*>(mean);
+    auto B = static_cast<uint16_t*>(mn);
+    auto C = static_cast<uint16_t*>(mx);
+    if (d == 128) {
+        if (is_bf16) block_stats_kernel<128, true><<<grid, 128, 0, stream>>>(X, A, B, C, n_blocks, block);
+        else block_stats_kernel<128, false><<<grid, 128, 0, stream>>>(X, A, B, C, n_blocks, block);
+    } else {
+        if (is_bf16) block_stats_kernel<64, true><<<grid, 64, 0, stream>>>(X, A, B, C, n_blocks, block);
+        else block_stats_kernel<64, false><<<grid, 64, 0, stream>>>(X, A, B, C, n_blocks, block);
+    }
+    return static_cast<int>(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------
+// Scoring and top-k
+// ---------------------------------------------------------------------------
+template <int D, bool BF16, bool QUEST>
+__device__ __forceinline__ float warp_score(const float (&q)[D / 32], const uint16_t* __restrict__ ka,
+                                            const uint16_t* __restrict__ kb, int lane) {
+    float dot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) {
+        const int e = lane + 32 * i;
+        float k;
+        if constexpr (QUEST) k = q[i] >= 0.0f ? In16<BF16>::to_f(kb[e]) : In16<BF16>::to_f(ka[e]);
+        else k = In16<BF16>::to_f(ka[e]);
+        dot = __fmaf_rn(q[i], k, dot);
+    }
+#pragma unroll
+    for (int delta = 16; delta >= 1; delta >>= 1) dot = __fadd_rn(dot, __shfl_xor_sync(0xFFFFFFFFu, dot, delta));
+    return dot;
+}
+
+// k rounds of arg-max over `scores[0..n)` (shared memory, one warp).
+template <int ITEMS>
+__device__ __forceinline__ void warp_topk_rounds(const float* scores, int n, int k, bool pad, int32_t* out, int lane) {
+    float val[ITEMS];
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const int idx = i * 32 + lane;
+        val[i] = idx < n ? scores[idx] : -FLT_MAX;
+    }
+    for (int r = 0; r < k; ++r) {
+        float best = val[0];
+        int best_idx = lane;
+#pragma unroll
+        for (int i = 1; i < ITEMS; ++i)
+            if (val[i] > best) { best = val[i]; best_idx = i * 32 + lane; }
+#pragma unroll
+        for (int delta = 16; delta >= 1; delta >>= 1) {
+            const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, delta);
+            const int oi = __shfl_xor_sync(0xFFFFFFFFu, best_idx, delta);
+            if (ob > best) { best = ob; best_idx = oi; }
+        }
+        best = __shfl_sync(0xFFFFFFFFu, best, 0);
+        best_idx = __shfl_sync(0xFFFFFFFFu, best_idx, 0);
+        const bool found = best > -FLT_MAX * 0.5f;
+        if (lane == 0) out[r] = (found || !pad) ? best_idx : -1;
+        if (found || !pad) {
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i)
+                if (i * 32 + lane == best_idx) val[i] = -FLT_MAX;
+        }
+    }
+}
+
+__device__ __forceinline__ void topk_dispatch(const float* scores, int n, int k, bool pad, int32_t* out, int lane) {
+    if (n <= 128) warp_topk_rounds<4>(scores, n, k, pad, out, lane);
+    else if (n <= 512) warp_topk_rounds<16>(scores, n, k, pad, out, lane);
+    else if (n <= 1024) warp_topk_rounds<32>(scores, n, k, pad, out, lane);
+    else warp_topk_rounds<64>(scores, n, k, pad, out, lane);
+}
+
+// Prefill: one warp per (q head, q block); a CTA of 8 warps covers 8 consecutive
+// q blocks of one head and shares the K statistics through shared memory.
+// q_mean [heads, nq, D]; ka/kb [kv_heads, nk, D] (not expanded per q head).
+// out [heads, nq, sink + local + k]: forced sink ids, forced local ids, then the
+// top-k by rank, -1 padded.
+constexpr int SEL_WARPS = 8;
+constexpr int SEL_KTILE = 32;
+
+template <int D, bool BF16, bool QUEST>
+__global__ void __launch_bounds__(SEL_WARPS * 32) select_prefill_kernel(
+    const uint16_t* __restrict__ q_mean, const uint16_t* __restrict__ ka, const uint16_t* __restrict__ kb,
+    int32_t* __restrict__ out, int heads, int group, int nq, int nk, int k, int causal, int sink, int local) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    float* scores = reinterpret_cast<float*>(smem_raw);                              // [SEL_WARPS][nk_pad]
+    const int nk_pad = (nk + 31) & ~31;
+    uint16_t* s_ka = reinterpret_cast<uint16_t*>(scores + SEL_WARPS * nk_pad);        // [SEL_KTILE][D]
+    uint16_t* s_kb = s_ka + SEL_KTILE * D;
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int q_tiles = cdiv(nq, SEL_WARPS);
+    const int width = sink + local + k;
+
+    for (int work = blockIdx.x; work < heads * q_tiles; work += gridDim.x) {
+        const int h = work / q_tiles;
+        const int qb = (work - h * q_tiles) * SEL_WARPS + warp;
+        const int kvh = h / group;
+        const bool active = qb < nq;
+        float q[D / 32];
+        if (active) {
+#pragma unroll
+            for (int i = 0; i < D / 32; ++i)
+                q[i] = In16<BF16>::to_f(q_mean[(static_cast<long long>(h) * nq + qb) * D + lane + 32 * i]);
+        }
+        const int qb_hi = min((work - h * q_tiles) * SEL_WARPS + SEL_WARPS - 1, nq - 1);
+        const int nk_need = causal ? min(nk, qb_hi + 1) : nk;
+        const int nvalid = active ? (causal ? min(qb + 1, nk) : nk) : 0;
+        const int n_sink = min(sink, nvalid);
+        const int local_lo = max(nvalid - local, n_sink);
+        float* my = scores + warp * nk_pad;
+        for (int b0 = 0; b0 < nk_need; b0 += SEL_KTILE) {
+            const int nb = min(SEL_KTILE, nk_need - b0);
+            __syncthreads();
+            for (int i = threadIdx.x; i < nb * (D / 8); i += blockDim.x) {
+                const long long g = (static_cast<long long>(kvh) * nk + b0) * D + static_cast<long long>(i) * 8;
+                reinterpret_cast<uint4*>(s_ka)[i] = __ldg(reinterpret_cast<const uint4*>(ka + g));
+                if constexpr (QUEST) reinterpret_cast<uint4*>(s_kb)[i] = __ldg(reinterpret_cast<const uint4*>(kb + g));
+            }
+            __syncthreads();
+            if (active) {
+                for (int j = 0; j < nb; ++j) {
+                    const int b = b0 + j;
+                    if (b >= nvalid) break;
+                    const float s = warp_score<D, BF16, QUEST>(q, s_ka + j * D, s_kb + j * D, lane);
+                    if (lane == 0) my[b] = (b < n_sink || b >= local_lo) ? -FLT_MAX : s;
+                }
+            }
+        }
+        __syncwarp();
+        if (active) {
+            int32_t* row = out + (static_cast<long long>(h) * nq + qb) * width;
+            const int forced = n_sink + (nvalid - local_lo);
+            for (int i = lane; i < forced; i += 32) row[i] = i < n_sink ? i : local_lo + (i - n_sink);
+            topk_dispatch(my, nvalid, k, true, row + forced, lane);
+            for (int i = forced + k + lane; i < width; i += 32) row[i] = -1;
+        }
+        __syncthreads();
+    }
+}
+
+// Decode: one CTA per flat KV head.  All warps score pages (max over the query
+// group), warp 0 then runs the top-k rounds.  q [flat, group, D]; ka/kb
+// [flat, cap_blocks, D]; out [flat, sink + local + k].
+template <int D, bool BF16, bool QUEST>
+__global__ void __launch_bounds__(256) select_decode_kernel(const uint16_t* __restrict__ q,
+                                                            const uint16_t* __restrict__ ka,
+                                                            const uint16_t* __restrict__ kb,
+                                                            int32_t* __restrict__ out, int group, int nk,
+                                                            int cap_blocks, int k, int sink, int local) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    float* scores = reinterpret_cast<float*>(smem_raw);
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, nwarps = blockDim.x / 32;
+    const int h = blockIdx.x;
+    const int n_sink = min(sink, nk);
+    const int local_lo = max(nk - local, n_sink);
+    const int width = sink + local + k;
+    for (int b = warp; b < nk; b += nwarps) {
+        const uint16_t* ra = ka + (static_cast<long long>(h) * cap_blocks + b) * D;
+        const uint16_t* rb = QUEST ? kb + (static_cast<long long>(h) * cap_blocks + b) * D : nullptr;
+        float best = -FLT_MAX;
+        for (int g = 0; g < group; ++g) {
+            float qv[D / 32];
+#pragma unroll
+            for (int i = 0; i < D / 32; ++i)
+                qv[i] = In16<BF16>::to_f(q[(static_cast<long long>(h) * group + g) * D + lane + 32 * i]);
+            const float s = warp_score<D, BF16, QUEST>(qv, ra, rb, lane);
+            if (s > best) best = s;
+        }
+        if (lane == 0) scores[b] = (b < n_sink || b >= local_lo) ? -FLT_MAX : best;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int32_t* row = out + static_cast<long long>(h) * width;
+        const int forced = n_sink + (nk - local_lo);
+        for (int i = lane; i < forced; i += 32) row[i] = i < n_sink ? i : local_lo + (i - n_sink);
+        topk_dispatch(scores, nk, k, (sink + local) > 0, row + forced, lane);
+        for (int i = forced + k + lane; i < width; i += 32) row[i] = -1;
+    }
+}
+
+int select_prefill_dispatch(const void* q_mean, const void* ka, const void* kb, void* out, int heads, int group, int nq,
+                            int nk, int d, int k, int causal, int quest, int is_bf16, int sink, int local,
+                            cudaStream_t stream) {
+    if (!q_mean || !ka || !out || (quest && !kb)) return TA100_ERR_NULL;
+    if (d != 64 && d != 128) return TA100_ERR_UNSUPPORTED;
+    if (nk > 2048 || nk < 0 || k < 0 || group <= 0 || heads % group != 0) return TA100_ERR_SHAPE;
+    if (sink + local + k == 0 || heads == 0 || nq == 0) return TA100_OK;
+    const int nk_pad = (nk + 31) & ~31;
+    const size_t smem = sizeof(float) * SEL_WARPS * nk_pad + 2ull * SEL_KTILE * d * 2;
+    const long long work = static_cast<long long>(heads) * cdiv(nq, SEL_WARPS);
+    const int grid = static_cast<int>(work < NUM_SMS_HINT * 8LL ? work : NUM_SMS_HINT * 8LL);
+#define TA100_SEL(DD, BFF, QQ)                                                                                   \
+    do {                                                                                                         \
+        cudaFuncSetAttribute(select_prefill_kernel<DD, BFF, QQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                             static_cast<int>(smem));                                                            \
+        select_prefill_kernel<DD, BFF, QQ><<<grid, SEL_WARPS * 32, smem, stream>>>(                              \
+            static_cast<const uint16_t*>(q_mean), static_cast<const uint16_t*>(ka),                              \
+            static_cast<const uint16_t*>(kb), static_cast<int32_t*>(out), heads, group, nq, nk, k, causal, sink, \
+            local);                                                                                              \
+    } while (0)
+    if (d == 128) {
+        if (is_bf16) { if (quest) TA100_SEL(128, true, true); else TA100_SEL(128, true, false); }
+        else { if (quest) TA100_SEL(128, false, true); else TA100_SEL(128, false, false); }
+    } else {
+        if (is_bf16) { if (quest) TA100_SEL(64, true, true); else TA100_SEL(64, true, false); }
+        else { if (quest) TA100_SEL(64, false, true); else TA100_SEL(64, false, false); }
+    }
+#undef TA100_SEL
+    return static_cast<int>(cudaGetLastError());
+}
+
+int select_decode_dispatch(const void* q, const void* ka, const void* kb, void* out, int flat_heads, int group, int nk,
+                           int cap_blocks, int d, int k, int quest, int is_bf16, int sink, int local,
+                           cudaStream_t stream) {
+    if (!q || !ka || !out || (quest && !kb)) return TA100_ERR_NULL;
+    if (d != 64 && d != 128) return TA100_ERR_UNSUPPORTED;
+    if (nk > 2048 || nk < 0 || k < 0 || nk > cap_blocks || group <= 0) return TA100_ERR_SHAPE;
+    if ((sink + local) == 0 && k > nk) return TA100_ERR_SHAPE;
+    if (sink + local + k == 0 || flat_heads == 0) return TA100_OK;
+    const size_t smem = sizeof(float) * ((nk + 31) & ~31);
+#define TA100_SELD(DD, BFF, QQ)                                                                               \
+    select_decode_kernel<DD, BFF, QQ><<<flat_heads, 256, smem, stream>>>(                                      \
+        static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(ka), static_cast<const uint16_t*>(kb),   \
+        static_cast<int32_t*>(out), group, nk, cap_blocks, k, sink, local)
+    if (d == 128) {
+        if (is_bf16) { if (quest) TA100_SELD(128, true, true); else TA100_SELD(128, true, false); }
+        else { if (quest) TA100_SELD(128, false, true); else TA100_SELD(128, false, false); }
+    } else {
+        if (is_bf16) { if (quest) TA100_SELD(64, true, true); else TA100_SELD(64, true, false); }
+        else { if (quest) TA100_SELD(64, false, true); else TA100_SELD(64, false, false); }
+    }
+#undef TA100_SELD
+    return static_cast<int>(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------
+// Local windows and bitset packing
+// ---------------------------------------------------------------------------
+__global__ void local_prefill_kernel(int32_t* __restrict__ out, long long rows, int nq, int nk, int k, int causal) {
+    const long long total = rows * k;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long row = i / k;
+        const int rank = static_cast<int>(i - row * k);
+        const int qb = static_cast<int>(row % nq);
+        int start, valid = k;
+        if (causal) {
+            const int end = min(qb, nk - 1);
+            valid = min(end + 1, k);
+            start = max(0, end - k + 1);
+        } else {
+            const int center = min(qb, nk - 1);
+            const int max_start = max(nk - k, 0);
+            start = min(max(center - k / 2, 0), max_start);
+        }
+        out[i] = rank < valid ? start + rank : -1;
+    }
+}
+
+__global__ void local_decode_kernel(int32_t* __restrict__ out, long long rows, int nk, int k) {
+    const long long total = rows * k;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+        out[i] = nk - k + static_cast<int>(i % k);
+}
+
+// sel [rows, k] -> mask [rows, words] (64-bit words, bit b of word w = block 64w + b).
+__global__ void __launch_bounds__(128) pack_mask_kernel(const int32_t* __restrict__ sel,
+                                                        unsigned long long* __restrict__ mask, long long rows, int k,
+                                                        int nk, int words) {
+    __shared__ unsigned long long s_words[32];
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        if (threadIdx.x < 32) s_words[threadIdx.x] = 0ull;
+        __syncthreads();
+        for (int i = threadIdx.x; i < k; i += blockDim.x) {
+            const int b = sel[row * k + i];
+            if (b >= 0 && b < nk && (b >> 6) < words && (b >> 6) < 32) atomicOr(&s_words[b >> 6], 1ull << (b & 63));
+        }
+        __syncthreads();
+        if (threadIdx.x < words && threadIdx.x < 32) mask[row * words + threadIdx.x] = s_words[threadIdx.x];
+        __syncthreads();
+    }
+}
+
+int local_prefill_dispatch(void* out, long long rows_heads, int nq, int nk, int k, int causal, cudaStream_t stream) {
+    if (k == 0 || rows_heads * nq == 0) return TA100_OK;
+    if (!out) return TA100_ERR_NULL;
+    const long long rows = rows_heads * nq;
+    local_prefill_kernel<<<grid_for(rows * k, 256, 8), 256, 0, stream>>>(static_cast<int32_t*>(out), rows, nq, nk, k, causal);
+    return static_cast<int>(cudaGetLastError());
+}
+
+int local_decode_dispatch(void* out, long long rows, int nk, int k, cudaStream_t stream) {
+    if (k == 0 || rows == 0) return TA100_OK;
+    if (!out) return TA100_ERR_NULL;
+    if (k > nk) return TA100_ERR_SHAPE;
+    local_decode_kernel<<<grid_for(rows * k, 256, 8), 256, 0, stream>>>(static_cast<int32_t*>(out), rows, nk, k);
+    return static_cast<int>(cudaGetLastError());
+}
+
+int pack_mask_dispatch(const void* sel, void* mask, long long rows, int k, int nk, int words, cudaStream_t stream) {
+    if (rows == 0 || words == 0) return TA100_OK;
+    if (!sel || !mask) return TA100_ERR_NULL;
+    if (words > 32) return TA100_ERR_LIMIT;
+    const int grid = static_cast<int>(rows < NUM_SMS_HINT * 16LL ? rows : NUM_SMS_HINT * 16LL);
+    pack_mask_kernel<<<grid, 128, 0, stream>>>(static_cast<const int32_t*>(sel), static_cast<unsigned long long*>(mask),
+                                               rows, k, nk, words);
+    return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace ta100
