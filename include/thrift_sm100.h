@@ -1,0 +1,140 @@
+/*
+ * libthrift_sm100 — C ABI of the sm_100a (B200) selective mixed-precision
+ * attention library.
+ *
+ * This header replaces the compiled boundary of the reference project: the
+ * plain-C++ kernel launchers that its csrc/bindings.cpp declares (lines 56-247)
+ * and calls from the 27 pybind11 functions (lines 1454-1671).  Every entry point
+ * takes raw device pointers, sizes and a CUDA stream (as void*), allocates
+ * nothing unless stated, holds no global mutable state and returns an int:
+ *   0 = ok, < 0 = argument error (TA100_ERR_*), > 0 = a cudaError_t value.
+ * Calls are asynchronous with respect to the host unless stated otherwise.
+ *
+ * Conventions
+ *   - "16-bit" inputs are IEEE half (is_bf16 = 0) or bfloat16 (is_bf16 = 1).
+ *   - NVFP4: e2m1 codes, one E4M3 scale per 16 values.  MXFP4: e2m1 codes, one
+ *     E8M0 scale per 32 values (is_mxfp4 = 1).
+ *   - Packed codes: byte i holds element 2i in bits 0..3 and 2i+1 in bits 4..7.
+ *   - Row layouts: codes [heads, seq, D/2], scales [heads, seq, D/G].
+ *   - Transposed layout (V): codes [heads, D, P/2], scales [heads, D, P/G] with
+ *     P = ceil(seq/128)*128, groups running along the sequence.
+ *   - Selection lists are int32, rank ordered, -1 padded.
+ */
+#ifndef THRIFT_SM100_H
+#define THRIFT_SM100_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TA100_OK 0
+#define TA100_ERR_NULL (-1)
+#define TA100_ERR_SHAPE (-2)
+#define TA100_ERR_UNSUPPORTED (-3)
+#define TA100_ERR_ALIGN (-4)
+#define TA100_ERR_WORKSPACE (-5)
+#define TA100_ERR_TENSOR_MAP (-6)
+#define TA100_ERR_DEVICE_TIMEOUT (-7)
+#define TA100_ERR_LIMIT (-8)
+
+int ta100_version(void);
+const char* ta100_status_string(int status);
+
+/*
+ * Quantise x [bs, seq, head_dim] (16-bit) to packed FP4 codes and block scales.
+ * layout: 0 plain rows, 1 rows permuted inside every 32-row group (physical row p
+ * holds logical row (p/8)*2 + ((p%8)/2)*8 + p%2), 2 transposed, 3 transposed +
+ * permuted.  head_dim 64 or 128.
+ * Replaces nvfp4_quantise / nvfp4_quantise_permute_seq / nvfp4_quantise_transpose /
+ * nvfp4_quantise_transpose_permute_seq and the four mxfp4_* twins
+ * (bindings.cpp:149-179; kernels csrc/cuda/sm120/nvfp4/quantization.cu:16,162,315,493
+ * and csrc/cuda/sm120/mxfp4/quantization.cu:24,185,351,542).
+ */
+int ta100_quantize(const void* x, void* codes, void* scales, long long bs, int seq, int head_dim, int is_mxfp4,
+                   int is_bf16, int layout, void* stream);
+
+/*
+ * Per-block statistics of x [heads, seq, head_dim]: fp32 mean cast to the 16-bit
+ * type, min and max, each [heads, seq/block, head_dim]; any output may be NULL.
+ * Replaces the PyTorch pre-reductions of the reference (block_means,
+ * src/thriftattention/selection/block_mean.py:44-54; block_minmax,
+ * src/thriftattention/selection/quest.py:11-24).
+ */
+int ta100_block_stats(const void* x, void* mean, void* mn, void* mx, long long heads, int seq, int head_dim, int block,
+                      int is_bf16, void* stream);
+
+/*
+ * Prefill block selection.  q_mean [heads, nq, D]; k_a / k_b [heads/group, nk, D].
+ * quest = 0: score = q_mean . k_a (k_a = block means); quest = 1: Quest bound with
+ * k_a = block minima, k_b = block maxima.  causal: blocks kb <= qb only.
+ * out [heads, nq, sink + local + k]: the first `sink` and last `local` valid blocks
+ * (forced, extension; pass 0 for the reference behaviour), then the k best of the
+ * remaining blocks in rank order; -1 padded.  nk <= 2048.
+ * Replaces block_mean_topk and quest_block_topk (bindings.cpp:181-203,
+ * csrc/cuda/sm120/shared/block_selection.cu:24,231).
+ */
+int ta100_select_prefill(const void* q_mean, const void* k_a, const void* k_b, void* out, int heads, int group, int nq,
+                         int nk, int head_dim, int k, int causal, int quest, int is_bf16, int sink, int local,
+                         void* stream);
+
+/*
+ * Decode block selection.  q_grouped [flat_kv_heads, group, D]; k_a / k_b
+ * [flat_kv_heads, cap_blocks, D]; score = max over the group; out
+ * [flat_kv_heads, sink + local + k].  Replaces single_query_key_mean_topk,
+ * single_query_key_mean_topk_chunked and single_query_quest_topk
+ * (bindings.cpp:205-247, block_selection.cu:127,339,450).
+ */
+int ta100_select_decode(const void* q_grouped, const void* k_a, const void* k_b, void* out, int flat_kv_heads, int group,
+                        int nk, int cap_blocks, int head_dim, int k, int quest, int is_bf16, int sink, int local,
+                        void* stream);
+
+/* Local windows: out [flat_heads, nq, k] (block_selection.cu:629) and
+ * [flat_heads, k] (block_selection.cu:662); replace local_block_topk and
+ * single_query_local_topk (bindings.cpp:213-224). */
+int ta100_local_block_topk(void* out, long long flat_heads, int nq, int nk, int k, int causal, void* stream);
+int ta100_single_query_local_topk(void* out, long long flat_heads, int nk, int k, void* stream);
+
+/* sel [rows, k] -> mask [rows, words] of 64-bit words; replaces pack_topk_mask
+ * (bindings.cpp:226-232, block_selection.cu:1260). */
+int ta100_pack_topk_mask(const void* sel, void* mask, long long rows, int k, int nk, int words, void* stream);
+
+/*
+ * Fused prefill attention: the FP4 pass over non-selected KV blocks and the 16-bit
+ * pass over the selected ones in ONE kernel (TMA -> shared memory -> tcgen05 MMA ->
+ * tensor memory), online softmax in 64-column steps.
+ *   q_hi [B*hq, sq, D], k_hi/v_hi [B*hkv, skv, D]  16-bit, needed when width > 0
+ *   sel  [B*hq, sq/block, width] selected KV blocks of `block` (64 or 128) tokens;
+ *        width = 0 -> pure FP4 attention
+ *   q4/qs rows layout [B*hq, sq, ..]; k4/ks rows layout with head stride kv_cap rows
+ *        (k_permuted = 1 when produced with layout 1); v4t/vst transposed layout with
+ *        P = ceil(kv_cap/128)*128
+ *   out  [B*hq, sq, D] 16-bit
+ *   workspace: ta100_prefill_workspace_bytes(...) bytes, 256-byte aligned; holds
+ *        re-tiled scale factors and a device status word
+ *   round_partial = 1 rounds the running state to the 16-bit type between the two
+ *        passes as the reference's two-kernel pipeline does
+ *   max_ctas: 0 = one CTA per SM
+ * sq and skv multiples of 64, head_dim 128, skv <= 131072.  causal assumes query
+ * row r sees keys <= r.
+ * Replaces fp4_attention_{causal,noncausal}_{nvfp4,mxfp4} and
+ * thrift_attention_{causal,noncausal}_{nvfp4,mxfp4} (bindings.cpp:56-147; kernels
+ * csrc/cuda/sm120/nvfp4/fp4_attention.cu:18, thrift_attention.cu:22,454 and twins).
+ */
+size_t ta100_prefill_workspace_bytes(int batch, int hq, int hkv, int sq, int skv, int head_dim, int is_mxfp4);
+int ta100_prefill_attention(const void* q_hi, const void* k_hi, const void* v_hi, const void* sel, int width, int block,
+                            const void* q4, const void* k4, const void* v4t, const void* qs, const void* ks,
+                            const void* vst, void* out, void* workspace, size_t workspace_bytes, int batch, int hq,
+                            int hkv, int sq, int skv, int kv_cap, int head_dim, int causal, int is_mxfp4, int is_bf16,
+                            int k_permuted, int round_partial, int max_ctas, void* stream);
+/* Synchronises `stream` and reports TA100_ERR_DEVICE_TIMEOUT if a bounded wait
+ * inside the last prefill launch on this workspace gave up. */
+int ta100_prefill_status(const void* workspace, int batch, int hq, int hkv, int sq, int skv, int head_dim, int is_mxfp4,
+                         void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* THRIFT_SM100_H */

@@ -62,8 +62,8 @@ struct Smem {
     static constexpr int Q4 = 0;                       // 128 x D/2
     static constexpr int QSF = Q4 + QTILE * D / 2;     // up to 2 atoms
     static constexpr int Q16 = QSF + 1024;             // 128 x D x 2
-    static constexpr int P = Q16 + QTILE * D * 2;      // 16 KB
-    static constexpr int CSF = P + 16384;              // constant scale atom
+    static constexpr int P = Q16 + QTILE * D * 2;      // two buffers of 16 KB
+    static constexpr int CSF = P + 2 * 16384;          // constant scale atom
     static constexpr int STAGES = CSF + 1024;
     static constexpr int BITS = STAGES + NSTAGES * STAGE_BYTES;  // 2 buffers x 2 halves x 64 words
     static constexpr int TOTAL = BITS + 2 * 2 * 64 * 4;
@@ -77,7 +77,7 @@ struct Bars {
     uint64_t sched_full[2], sched_empty[2];
     uint64_t kv_full[NSTAGES], kv_empty[NSTAGES];
     uint64_t s_full[2], s_free[2];
-    uint64_t p_full, o_ready;
+    uint64_t p_full[2], p_free[2];
 };
 
 struct Step {
@@ -247,8 +247,10 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
             mbar_init(smem_u32(&bars.kv_full[i]), 1);
             mbar_init(smem_u32(&bars.kv_empty[i]), 1);
         }
-        mbar_init(smem_u32(&bars.p_full), 128);
-        mbar_init(smem_u32(&bars.o_ready), 1);
+        mbar_init(smem_u32(&bars.p_full[0]), 128);
+        mbar_init(smem_u32(&bars.p_full[1]), 128);
+        mbar_init(smem_u32(&bars.p_free[0]), 1);
+        mbar_init(smem_u32(&bars.p_free[1]), 1);
         mbar_fence_init();
         abort_flag = 0;
     }
@@ -424,7 +426,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                     __syncwarp();
                 }
                 // PV for the current step
-                ok = mbar_wait(smem_u32(&bars.p_full), gstep & 1, abortp, budget);
+                ok = mbar_wait(smem_u32(&bars.p_full[gstep & 1]), (gstep >> 1) & 1, abortp, budget);
                 if (!ok) break;
                 tc_fence_after_sync();
                 if (lane == 0) {
@@ -434,19 +436,19 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                     if (!cur.fp16) {
                         const uint32_t sfb = tmem + TM_SFB_V + buf * 4;
                         tmem_cp_sf(sfb, make_smem_desc(sa + L::VSF, 0, 128, SWZ_NONE));
-                        const uint64_t ad = make_smem_desc(sbase + L::P, 16, 256, SWZ_32B);
+                        const uint64_t ad = make_smem_desc(sbase + L::P + buf * 16384, 16, 256, SWZ_32B);
                         const uint64_t bd = make_smem_desc(sa + L::V4, 16, 256, SWZ_32B);
                         if constexpr (MX) mma_mxfp4(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, first_pv ? 0 : 1);
                         else mma_nvfp4(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, first_pv ? 0 : 1);
                     } else {
                         for (int ks = 0; ks < STEP / 16; ++ks) {
-                            const uint64_t ad = make_smem_desc(sbase + L::P + ks * 32, 16, 1024, SWZ_128B);
+                            const uint64_t ad = make_smem_desc(sbase + L::P + buf * 16384 + ks * 32, 16, 1024, SWZ_128B);
                             const uint64_t bd = make_smem_desc(sa + L::V16 + ks * 2048, STEP * 128, 1024, SWZ_128B);
                             mma_f16(d_t, ad, bd, idesc_pv16, (first_pv && ks == 0) ? 0 : 1);
                         }
                     }
                     tc_commit(smem_u32(&bars.kv_empty[stage]));
-                    tc_commit(smem_u32(&bars.o_ready));
+                    tc_commit(smem_u32(&bars.p_free[buf]));
                     if (!have_nxt) tc_commit(smem_u32(&bars.q_empty));
                 }
                 __syncwarp();
@@ -518,14 +520,19 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                     m_run = m_new;
                     mneg = -m_new * p.c2;
                 }
-                // previous PV must be complete before O or the P buffer is touched
-                if (gstep > 0) {
-                    ok = mbar_wait(smem_u32(&bars.o_ready), (gstep - 1) & 1, abortp, budget);
+                // the PV that last read this P buffer (two steps ago) must be complete
+                ok = mbar_wait(smem_u32(&bars.p_free[buf]), ((gstep >> 1) & 1) ^ 1, abortp, budget);
+                if (!ok) break;
+                // state rounding between the FP4 and the 16-bit phase
+                const bool transition = stp.fp16 && prev_fp4 && p.round_partial;
+                const bool need_rescale = __any_sync(0xFFFFFFFFu, changed && n_done > 0);
+                if (transition || need_rescale) {
+                    // O is about to be modified: the previous PV (step gstep-1, which
+                    // signals the other P buffer's barrier) must be complete
+                    ok = mbar_wait(smem_u32(&bars.p_free[(gstep - 1) & 1]), ((gstep - 1) >> 1) & 1, abortp, budget);
                     if (!ok) break;
                     tc_fence_after_sync();
                 }
-                // state rounding between the FP4 and the 16-bit phase
-                const bool transition = stp.fp16 && prev_fp4 && p.round_partial;
                 if (transition) {
                     const float norm = l_run > 0.0f ? __fdiv_rn(CSCALE_INV, l_run) : 0.0f;
                     const float back = l_run * CSCALE;
@@ -543,7 +550,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                     }
                     tmem_wait_st();
                 }
-                if (__any_sync(0xFFFFFFFFu, changed && n_done > 0)) {
+                if (need_rescale) {
 #pragma unroll 1
                     for (int c = 0; c < D; c += 32) {
                         uint32_t r[32];
@@ -556,7 +563,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                     tmem_wait_st();
                 }
                 // probabilities, row sum, P tile
-                uint8_t* prow = smem + L::P;
+                uint8_t* prow = smem + L::P + buf * 16384;
                 if (!stp.fp16) {
                     uint32_t w[STEP / 8];
                     if (part) {
@@ -610,7 +617,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                 }
                 fence_proxy_async_smem();
                 tc_fence_before_sync();
-                mbar_arrive(smem_u32(&bars.p_full));
+                mbar_arrive(smem_u32(&bars.p_full[buf]));
                 prev_fp4 = !stp.fp16;
                 ++n_done;
                 ++gstep;
@@ -619,7 +626,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
             // ---- epilogue ----
             uint16_t* orow = p.out + (static_cast<long long>(it.h) * p.sq + grow) * D;
             if (n_done > 0) {
-                ok = mbar_wait(smem_u32(&bars.o_ready), (gstep - 1) & 1, abortp, budget);
+                ok = mbar_wait(smem_u32(&bars.p_free[(gstep - 1) & 1]), ((gstep - 1) >> 1) & 1, abortp, budget);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const float norm = l_run > 0.0f ? __fdiv_rn(CSCALE_INV, l_run) : 0.0f;
