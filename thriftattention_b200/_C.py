@@ -386,3 +386,128 @@ def thrift_attention_noncausal_mxfp4_packed(q_hi, k_hi, v_hi, selected_blocks, q
                                             k_scale, v_scale_t, is_bf16=False):
     return _thrift_tiled((q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale,
                           v_scale_t), False, True, is_bf16)
+
+
+# ---------------------------------------------------------------------------------------------
+# Decode (single query) attention  (bindings.cpp:420-486, 731-891)
+# ---------------------------------------------------------------------------------------------
+def decode_pick_splits(flat_kv_heads: int, num_pages: int) -> int:
+    """Number of sequential KV chains per (sequence, KV head) the decode kernel uses by default."""
+    return _lib.load().ta100_decode_pick_splits(flat_kv_heads, num_pages)
+
+
+def decode_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, *,
+                     is_mx, is_bf16=False, num_splits=0, kv_len=None, page_table=None, return_partials=False):
+    """Split-KV decode attention over 64-token pages.
+
+    q_* are grouped: [B, Hkv, G, ...] with G <= 8 query heads per KV head.  K/V are either the
+    reference's contiguous, capacity-strided cache tensors (``page_table is None``) or page pools
+    ``[n_pages, Hkv, 64, ...]`` (K rows, 16-bit K/V) and ``[n_pages, Hkv, D, 32]`` (V codes) addressed
+    through ``page_table`` int32 [B, max_pages].  ``selected_blocks`` is ``None`` or int32 [B*Hkv, W].
+    Returns [B, Hkv, G, D]; with ``return_partials`` also the un-merged ``(o, ml)`` partials
+    ([B*Hkv, splits, G, D] in units of C and [B*Hkv, splits, G, 2] = (row max, row sum)).
+    """
+    _check(q_packed.is_cuda and k_packed.is_cuda and v_packed_t.is_cuda, "packed Q/K/V must be CUDA tensors")
+    _check(q_scale.is_cuda and k_scale.is_cuda and v_scale_t.is_cuda, "Q/K/V scales must be CUDA tensors")
+    _check(q_packed.dim() == 4, "packed Q must be 4D [batch, kv_heads, groups, head_dim / 2]")
+    b, hkv, g, dh = q_packed.shape
+    d = dh * 2
+    _check(1 <= g <= 16, f"single-query ThriftAttention expects grouped query length in [1, 16], got {g}")
+    _check(q_packed.is_contiguous() and q_scale.is_contiguous(), "packed Q and its scales must be contiguous")
+    if page_table is None:
+        _check(k_packed.dim() == 4 and k_packed.size(0) == b and k_packed.size(1) == hkv, "packed K shape mismatch")
+        skv = k_packed.size(2) if kv_len is None else kv_len
+        _check(k_packed.stride(3) == 1 and k_packed.stride(2) == dh, "packed K rows must be dense")
+        kv_cap = max(skv, k_packed.stride(1) // dh)
+        _check((kv_cap + 127) // 128 * 128 // 2 == v_packed_t.stride(2) or v_packed_t.size(3) * 1 == v_packed_t.stride(2),
+               "packed V row stride must equal the padded cache capacity / 2")
+        max_pages = 0
+    else:
+        _check(kv_len is not None, "kv_len is required with a page table")
+        _check(page_table.is_cuda and page_table.dtype == torch.int32 and page_table.is_contiguous()
+               and page_table.dim() == 2 and page_table.size(0) == b, "page_table must be int32 [batch, max_pages]")
+        skv, kv_cap, max_pages = kv_len, kv_len, page_table.size(1)
+    _check(skv % 64 == 0, "k sequence length must be divisible by 64")
+    npages = skv // 64
+    width = 0
+    if selected_blocks is not None:
+        _check(selected_blocks.is_cuda, "selected_blocks must be a CUDA tensor")
+        _check(selected_blocks.dtype == torch.int32, "selected_blocks must be int32")
+        _check(selected_blocks.is_contiguous(), "selected_blocks must be contiguous")
+        _check(selected_blocks.dim() == 2, "selected_blocks must be [batch * grouped_heads, top_k]")
+        _check(selected_blocks.size(0) == b * hkv, "selected_blocks first dimension must equal batch * grouped_heads")
+        width = selected_blocks.size(1)
+        _check(0 <= width <= npages, "selected block count must be in [0, number of KV blocks]")
+        if width:
+            _check(q_hi is not None and q_hi.shape == (b, hkv, g, d), "q_hi shape must match packed Q")
+            _check(q_hi.is_contiguous() and k_hi.is_contiguous() and v_hi.is_contiguous(), "Q/K/V must be contiguous")
+    lib = _lib.load()
+    dev = q_packed.device
+    splits = num_splits if num_splits > 0 else lib.ta100_decode_pick_splits(b * hkv, npages)
+    splits = max(1, min(splits, npages))
+    out = torch.empty(b, hkv, g, d, dtype=torch.bfloat16 if is_bf16 else torch.float16, device=dev)
+    part_o = torch.empty(b * hkv, splits, g, d, dtype=torch.float32, device=dev)
+    part_ml = torch.empty(b * hkv, splits, g, 2, dtype=torch.float32, device=dev)
+    sel = selected_blocks if width else None
+    with torch.cuda.device(dev):
+        rc = lib.ta100_decode_attention(
+            _ptr(q_hi) if sel is not None else None, _ptr(k_hi) if sel is not None else None,
+            _ptr(v_hi) if sel is not None else None, _ptr(sel), width, _ptr(q_packed), _ptr(k_packed), _ptr(v_packed_t),
+            _ptr(q_scale), _ptr(k_scale), _ptr(v_scale_t), _ptr(page_table), max_pages, _ptr(out), _ptr(part_o),
+            _ptr(part_ml), b, hkv, g, skv, kv_cap, d, int(is_mx), int(is_bf16), splits, 1, _stream(out))
+    _lib.check(rc, "decode_attention")
+    if return_partials:
+        return out, part_o, part_ml
+    return out
+
+
+def merge_decode_partials(part_o: torch.Tensor, part_ml: torch.Tensor, *, is_mx: bool, is_bf16: bool = False):
+    """LSE merge of decode partials gathered from several shards.
+
+    part_o [shards, heads, splits, G, D] fp32 (units of C), part_ml [shards, heads, splits, G, 2]
+    -> [heads, G, D] 16-bit.  Same formula as the in-kernel merge of the reference
+    (csrc/cuda/sm120/nvfp4/single_query_attention.cu:1562-1593).
+    """
+    _check(part_o.is_cuda and part_ml.is_cuda and part_o.is_contiguous() and part_ml.is_contiguous(),
+           "partials must be contiguous CUDA tensors")
+    _check(part_o.dtype == torch.float32 and part_ml.dtype == torch.float32, "partials must be float32")
+    shards, heads, splits, g, d = part_o.shape
+    out = torch.empty(heads, g, d, dtype=torch.bfloat16 if is_bf16 else torch.float16, device=part_o.device)
+    with torch.cuda.device(out.device):
+        rc = _lib.load().ta100_merge_partials(_ptr(part_o), _ptr(part_ml), _ptr(out), shards, heads, splits, g, d,
+                                              int(is_mx), int(is_bf16), _stream(out))
+    _lib.check(rc, "merge_partials")
+    return out
+
+
+def _fp4_single(packed, is_mx, is_bf16):
+    q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t = packed
+    _check_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t)
+    return decode_attention(None, None, None, None, q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t,
+                            is_mx=is_mx, is_bf16=is_bf16)
+
+
+def fp4_attention_single_query_nvfp4_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, is_bf16=False):
+    return _fp4_single((q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t), False, is_bf16)
+
+
+def fp4_attention_single_query_mxfp4_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, is_bf16=False):
+    return _fp4_single((q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t), True, is_bf16)
+
+
+def _thrift_single(q_hi, k_hi, v_hi, selected_blocks, packed, is_mx, is_bf16):
+    _check_hi(q_hi, k_hi, v_hi)
+    _check_packed(*packed)
+    return decode_attention(q_hi, k_hi, v_hi, selected_blocks, *packed, is_mx=is_mx, is_bf16=is_bf16)
+
+
+def thrift_attention_single_query_nvfp4_packed(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale,
+                                               k_scale, v_scale_t, is_bf16=False):
+    return _thrift_single(q_hi, k_hi, v_hi, selected_blocks, (q_packed, k_packed, v_packed_t, q_scale, k_scale,
+                                                              v_scale_t), False, is_bf16)
+
+
+def thrift_attention_single_query_mxfp4_packed(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale,
+                                               k_scale, v_scale_t, is_bf16=False):
+    return _thrift_single(q_hi, k_hi, v_hi, selected_blocks, (q_packed, k_packed, v_packed_t, q_scale, k_scale,
+                                                              v_scale_t), True, is_bf16)

@@ -19,6 +19,12 @@ int prefill_dispatch(const void*, const void*, const void*, const void*, int, in
                      const void*, const void*, const void*, void*, void*, size_t, int, int, int, int, int, int, int, int,
                      int, int, int, int, int, cudaStream_t);
 int prefill_status(const void*, int, int, int, int, int, int, int, cudaStream_t);
+int decode_pick_splits(int, int);
+size_t decode_workspace_bytes(int, int, int, int);
+int decode_dispatch(const void*, const void*, const void*, const void*, int, const void*, const void*, const void*,
+                    const void*, const void*, const void*, const void*, int, void*, void*, void*, int, int, int, int, int,
+                    int, int, int, int, int, cudaStream_t);
+int merge_dispatch(const void*, const void*, void*, int, long long, int, int, int, int, int, cudaStream_t);
 }  // namespace ta100
 
 using namespace ta100;
@@ -96,6 +102,28 @@ int ta100_prefill_attention(const void* q_hi, const void* k_hi, const void* v_hi
 int ta100_prefill_status(const void* workspace, int batch, int hq, int hkv, int sq, int skv, int head_dim, int is_mxfp4,
                          void* stream) {
     return prefill_status(workspace, batch, hq, hkv, sq, skv, head_dim, is_mxfp4, S(stream));
+}
+
+int ta100_decode_pick_splits(int flat_kv_heads, int npages) { return decode_pick_splits(flat_kv_heads, npages); }
+
+size_t ta100_decode_workspace_bytes(int flat_kv_heads, int group, int head_dim, int splits) {
+    return decode_workspace_bytes(flat_kv_heads, group, head_dim, splits);
+}
+
+int ta100_decode_attention(const void* q_hi, const void* k_hi, const void* v_hi, const void* sel, int width,
+                           const void* q4, const void* k4, const void* v4, const void* qs, const void* ks, const void* vs,
+                           const void* page_table, int max_pages, void* out, void* part_o, void* part_ml, int batch,
+                           int hkv, int group, int kv_len, int kv_cap, int head_dim, int is_mxfp4, int is_bf16, int splits,
+                           int write_out, void* stream) {
+    return decode_dispatch(q_hi, k_hi, v_hi, sel, width, q4, k4, v4, qs, ks, vs, page_table, max_pages, out, part_o,
+                           part_ml, batch, hkv, group, kv_len, kv_cap, head_dim, is_mxfp4, is_bf16, splits, write_out,
+                           S(stream));
+}
+
+int ta100_merge_partials(const void* part_o, const void* part_ml, void* out, int shards, long long flat_kv_heads,
+                         int splits, int group, int head_dim, int is_mxfp4, int is_bf16, void* stream) {
+    return merge_dispatch(part_o, part_ml, out, shards, flat_kv_heads, splits, group, head_dim, is_mxfp4, is_bf16,
+                          S(stream));
 }
 
 }  // extern "C"
