@@ -134,6 +134,44 @@ int ta100_prefill_attention(const void* q_hi, const void* k_hi, const void* v_hi
 int ta100_prefill_status(const void* workspace, int batch, int hq, int hkv, int sq, int skv, int head_dim, int is_mxfp4,
                          void* stream);
 
+/*
+ * Decode (single query token) attention over 64-token pages, split over the KV sequence.
+ * Rows are the `group` (<= 8) query heads that share a KV head:
+ *   q_hi [B*hkv, group, D] 16-bit and its rows-layout quantisation q4 / qs
+ *   K/V, contiguous cache (page_table = NULL): k4 / ks rows layout with head stride kv_cap rows
+ *        (plain, not permuted), v4 / vs transposed layout with P = ceil(kv_cap/128)*128,
+ *        k_hi / v_hi [B*hkv, kv_len, D]
+ *   K/V, paged pools (page_table int32 [B, max_pages] -> physical page): k4 [pages, hkv, 64, D/2],
+ *        ks [pages, hkv, 64, D/G], v4 [pages, hkv, D, 32], vs [pages, hkv, D, 64/G],
+ *        k_hi / v_hi [pages, hkv, 64, D]
+ *   sel  [B*hkv, width] page ids kept in 16-bit (-1 entries ignored); width = 0 -> pure FP4
+ * Chain s of `splits` walks pages [s*n/splits, (s+1)*n/splits): FP4 pages ascending, then the
+ * selected pages ascending.  Partial results go to part_o [B*hkv, splits, group, D] (fp32,
+ * un-normalised, in units of C = 2688 NVFP4 / 6 MXFP4) and part_ml [B*hkv, splits, group, 2]
+ * (row max, row sum); with write_out = 1 they are merged into out [B*hkv, group, D] on the same
+ * stream.  kv_len a multiple of 64, head_dim 128.
+ * Replaces fp4_attention_single_query_{nvfp4,mxfp4} and thrift_attention_single_query_{nvfp4,mxfp4}
+ * (bindings.cpp:79-92, 132-147; kernels csrc/cuda/sm120/nvfp4/single_query_attention.cu:795,1196,
+ * single_query_fp4_attention.cu:718,1116 and twins).  The scratch the reference's binding allocates
+ * per call (bindings.cpp:804-807) is the caller-provided part_o / part_ml.
+ */
+int ta100_decode_pick_splits(int flat_kv_heads, int npages);
+size_t ta100_decode_workspace_bytes(int flat_kv_heads, int group, int head_dim, int splits);
+int ta100_decode_attention(const void* q_hi, const void* k_hi, const void* v_hi, const void* sel, int width,
+                           const void* q4, const void* k4, const void* v4, const void* qs, const void* ks, const void* vs,
+                           const void* page_table, int max_pages, void* out, void* part_o, void* part_ml, int batch,
+                           int hkv, int group, int kv_len, int kv_cap, int head_dim, int is_mxfp4, int is_bf16, int splits,
+                           int write_out, void* stream);
+
+/*
+ * Log-sum-exp merge of decode partials from `shards` producers (e.g. GPUs that each hold a slice
+ * of the KV sequence): part_o [shards, flat_kv_heads, splits, group, D], part_ml [.., 2] ->
+ * out [flat_kv_heads, group, D].  Same formula as the reference's in-kernel merge
+ * (csrc/cuda/sm120/nvfp4/single_query_attention.cu:1562-1593).
+ */
+int ta100_merge_partials(const void* part_o, const void* part_ml, void* out, int shards, long long flat_kv_heads,
+                         int splits, int group, int head_dim, int is_mxfp4, int is_bf16, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,59 @@
+"""The C-ABI library loads on a machine without a GPU and exports every symbol that
+include/thrift_sm100.h declares.  No compute calls here."""
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "thrift_sm100.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ta100_\w+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported():
+    from thriftattention_b200 import _lib
+
+    lib = _lib.load()
+    names = _declared_symbols()
+    assert len(names) >= 15
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+    assert set(_lib.SIGNATURES) == set(names)
+
+
+def test_version_and_status_strings():
+    from thriftattention_b200 import _lib
+
+    lib = _lib.load()
+    assert lib.ta100_version() >= 100
+    assert lib.ta100_status_string(0) == b"ok"
+    for code in range(-8, 0):
+        assert lib.ta100_status_string(code) not in (b"ok", b"unknown status")
+
+
+def test_argument_errors_are_reported_without_a_gpu():
+    from thriftattention_b200 import _lib
+
+    lib = _lib.load()
+    # null pointers / bad head_dim are rejected before any CUDA call
+    assert lib.ta100_quantize(None, None, None, 1, 64, 128, 0, 0, 0, None) == -1
+    buf = ctypes.create_string_buffer(256)
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    assert lib.ta100_quantize(p, p, p, 1, 64, 96, 0, 0, 0, None) == -3
+    assert lib.ta100_block_stats(p, None, None, None, 1, 100, 128, 64, 0, None) == -2
+    assert lib.ta100_prefill_workspace_bytes(1, 32, 8, 131072, 131072, 128, 0) > 0
+    assert lib.ta100_decode_workspace_bytes(256, 4, 128, 16) == 256 * 16 * 4 * 130 * 4
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    import pytest
+
+    from thriftattention_b200 import _lib
+
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "_LIB_PATH", tmp_path / "nope.so")
+    with pytest.raises(ImportError, match="not built"):
+        _lib.load()

@@ -1,0 +1,395 @@
+"""GPU parity tests (B200): every CUDA entry point against the CPU oracle on identical seeded
+inputs, through the C ABI.  Bit-exact for codes, scales, statistics and indices; attention within
+max-abs 2e-3 / mean-abs 2e-4 for fp16 outputs (one bf16 ulp, 2^-7 relative, for bf16 outputs)."""
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+FP16_MAX_ABS, MEAN_ABS = 2e-3, 2e-4
+
+
+def _tol(dtype, ref):
+    if dtype == torch.bfloat16:
+        return max(FP16_MAX_ABS, 2.0 ** -7 * float(ref.float().abs().max()))
+    return FP16_MAX_ABS
+
+
+def _ext():
+    from thriftattention_b200._extension import get_extension
+
+    return get_extension()
+
+
+def _u8(t):
+    return t.view(torch.uint8)
+
+
+# ------------------------------------------------------------------------------------ quantisers
+LAYOUTS = [("plain", "quantize"), ("permuted", "quantize_permuted"), ("transposed", "quantize_transposed"),
+           ("transposed_permuted", "quantize_transposed_permuted")]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+@pytest.mark.parametrize("layout,op", LAYOUTS)
+@pytest.mark.parametrize("shape", [(2, 3, 200, 128), (1, 2, 256, 64), (1, 1, 64, 128)])
+def test_quantiser_bit_exact(cuda_device, dtype, fmt, layout, op, shape):
+    torch.manual_seed(0)
+    x = torch.randn(*shape)
+    x[0, 0, :5] = 0.0                       # all-zero groups -> scale 0, codes 0
+    x[0, -1, 7] *= 1000.0                   # saturates the scale range
+    x[0, -1, 9] *= 1e-4
+    x[0, 0, 11, ::2] = -0.0
+    x = x.to(dtype)
+    codes_ref, scale_ref = oracle.quantize(x, fmt, layout)
+    codes, scale = getattr(_ext(), f"{fmt}_{op}")(x.to(cuda_device), dtype == torch.bfloat16)
+    assert codes.shape == codes_ref.shape and scale.shape == scale_ref.shape
+    assert scale.dtype == (torch.float8_e8m0fnu if fmt == "mxfp4" else torch.float8_e4m3fn)
+    assert torch.equal(codes.cpu(), codes_ref)
+    assert torch.equal(_u8(scale).cpu(), _u8(scale_ref))
+
+
+def test_quantiser_e2m1_ties_and_saturation(cuda_device):
+    # values that sit exactly on e2m1 rounding ties once divided by a power-of-two scale
+    base = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -6.0])
+    x = base.repeat(1, 1, 64, 8).reshape(1, 1, 64, 128).half()
+    for fmt in ("nvfp4", "mxfp4"):
+        c_ref, s_ref = oracle.quantize(x, fmt, "plain")
+        c, s = getattr(_ext(), f"{fmt}_quantize")(x.to(cuda_device), False)
+        assert torch.equal(c.cpu(), c_ref) and torch.equal(_u8(s).cpu(), _u8(s_ref))
+
+
+def test_quantiser_idempotent_at_scale(cuda_device):
+    """Size-independent property on a large tensor: quantising the dequantised tensor returns the same codes."""
+    torch.manual_seed(1)
+    x = torch.randn(1, 8, 32768, 128, device=cuda_device, dtype=torch.float16)
+    ext = _ext()
+    codes, scale = ext.nvfp4_quantize(x, False)
+    lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], device=cuda_device)
+    lo, hi = lut[(codes & 15).long()], lut[(codes >> 4).long()]
+    deq = torch.stack([lo, hi], -1).reshape(x.shape) * scale.float().repeat_interleave(16, dim=-1)
+    codes2, scale2 = ext.nvfp4_quantize(deq.half(), False)
+    assert torch.equal(_u8(scale2), _u8(scale))
+    same = (codes2 == codes) | ((codes2 & 0x77) == (codes & 0x77))  # the sign of a zero code may differ
+    assert bool(same.all())
+    err = (deq - x.float()).abs().amax() / x.float().abs().amax()
+    assert float(err) < 0.2
+
+
+# ------------------------------------------------------------------------------------ statistics + selection
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("block", [64, 128])
+def test_block_stats_and_prefill_selection_bit_exact(cuda_device, dtype, block):
+    torch.manual_seed(2)
+    q = torch.randn(1, 8, 2048, 128).to(dtype)
+    k = torch.randn(1, 2, 2048, 128).to(dtype)
+    ext = _ext()
+    qm, = oracle.block_stats(q, block, ("mean",))
+    km, kmin, kmax = oracle.block_stats(k, block, ("mean", "min", "max"))
+    gqm, _, _ = ext.block_stats(q.to(cuda_device), block, mean=True)
+    gkm, gkmin, gkmax = ext.block_stats(k.to(cuda_device), block, mean=True, minmax=True)
+    for a, b in ((gqm, qm), (gkm, km), (gkmin, kmin), (gkmax, kmax)):
+        assert torch.equal(a.cpu(), b)
+    nk = 2048 // block
+    bf = dtype == torch.bfloat16
+    for causal in (True, False):
+        for top_k, sink, local in ((3, 0, 0), (5, 1, 2), (nk, 0, 0)):
+            ref = oracle.select_prefill(qm, kmin, kmax, k=top_k, causal=causal, sink=sink, local=local)
+            got = ext.select_prefill_blocks(gqm, gkmin, gkmax, top_k, causal, bf, sink, local)
+            assert torch.equal(got.cpu(), ref)
+            ref = oracle.select_prefill(qm, km, None, k=top_k, causal=causal, sink=sink, local=local)
+            got = ext.select_prefill_blocks(gqm, gkm, None, top_k, causal, bf, sink, local)
+            assert torch.equal(got.cpu(), ref)
+    # reference-named operators, K statistics expanded per Q head as the reference passes them
+    exp = lambda t: t.repeat_interleave(4, dim=1).contiguous()
+    got = ext.quest_block_topk(gqm, exp(gkmin), exp(gkmax), 4, True, bf)
+    assert torch.equal(got.cpu(), oracle.select_prefill(qm, kmin, kmax, k=4, causal=True))
+    got = ext.block_mean_topk(gqm, exp(gkm), 4, True, bf)
+    assert torch.equal(got.cpu(), oracle.select_prefill(qm, km, None, k=4, causal=True))
+    sel = oracle.select_prefill(qm, kmin, kmax, k=5, causal=True)
+    assert torch.equal(ext.pack_topk_mask(sel.to(cuda_device), nk).cpu(), oracle.pack_mask(sel, nk))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_decode_selection_bit_exact(cuda_device, dtype):
+    torch.manual_seed(3)
+    ext = _ext()
+    bf = dtype == torch.bfloat16
+    qg = torch.randn(2, 2, 4, 128).to(dtype)
+    k = torch.randn(2, 2, 8192, 128).to(dtype)
+    km, kmin, kmax = oracle.block_stats(k, 64, ("mean", "min", "max"))
+    dq, dkm, dkmin, dkmax = (t.to(cuda_device) for t in (qg, km, kmin, kmax))
+    for top_k, sink, local, nk in ((6, 0, 0, 60), (6, 2, 3, 128), (13, 0, 0, 128), (40, 4, 16, 128)):
+        ref = oracle.select_decode(qg, kmin, kmax, k=top_k, num_kv_blocks=nk, sink=sink, local=local)
+        got = ext.select_decode_blocks(dq, dkmin, dkmax, top_k, nk, bf, sink, local)
+        assert torch.equal(got.cpu(), ref)
+        ref = oracle.select_decode(qg, km, None, k=top_k, num_kv_blocks=nk, sink=sink, local=local)
+        got = ext.select_decode_blocks(dq, dkm, None, top_k, nk, bf, sink, local)
+        assert torch.equal(got.cpu(), ref)
+    assert torch.equal(ext.single_query_quest_topk(dq, dkmin, dkmax, 5, 100, bf).cpu(),
+                       oracle.select_decode(qg, kmin, kmax, k=5, num_kv_blocks=100))
+    assert torch.equal(ext.single_query_key_mean_topk(dq, dkm, 5, 100, bf).cpu(),
+                       oracle.select_decode(qg, km, None, k=5, num_kv_blocks=100))
+    topk = torch.empty(4, 5, dtype=torch.int32, device=cuda_device)
+    ws_s = torch.empty(4, 2, 5, device=cuda_device)
+    ws_i = torch.empty(4, 2, 5, dtype=torch.int32, device=cuda_device)
+    done = torch.zeros(4, dtype=torch.int32, device=cuda_device)
+    ext.single_query_key_mean_topk_into(dq, dkm, topk, ws_s, ws_i, done, 100, bf)
+    assert torch.equal(topk.cpu(), oracle.select_decode(qg, km, None, k=5, num_kv_blocks=100))
+
+
+def test_reference_known_answers_on_gpu(cuda_device):
+    """The reference tests' small known answers (tests/test_selection.py:37-129,
+    tests/test_cuda_bf16_correctness.py:125-139), embedded in head_dim 64."""
+    ext = _ext()
+
+    def pad(t):
+        out = torch.zeros(*t.shape[:-1], 64, dtype=t.dtype)
+        out[..., : t.shape[-1]] = t
+        return out.to(cuda_device)
+
+    q = pad(torch.tensor([[[[1.0, -1.0], [1.0, -1.0], [-1.0, 1.0], [-1.0, 1.0]]]], dtype=torch.float16))
+    k = pad(torch.tensor([[[[2.0, -4.0], [1.0, -3.0], [-3.0, 5.0], [-2.0, 6.0]]]], dtype=torch.float16))
+    qm, _, _ = ext.block_stats(q, 2, mean=True)
+    _, lo, hi = ext.block_stats(k, 2, minmax=True)
+    assert ext.quest_block_topk(qm, lo, hi, 2, True, False).tolist() == [[[0, -1], [1, 0]]]
+    q = pad(torch.tensor([[[[1.0, -2.0]]]], dtype=torch.float16)).reshape(1, 1, 1, 64)
+    k = pad(torch.tensor([[[[4.0, -3.0], [2.0, -1.0], [1.0, -1.0], [0.0, 0.0], [3.0, 2.0], [3.0, 1.0]]]], dtype=torch.float16))
+    _, lo, hi = ext.block_stats(k, 2, minmax=True)
+    assert ext.single_query_quest_topk(q, lo, hi, 1, 3, False).tolist() == [[0]]
+    q = torch.zeros(1, 1, 1, 64, dtype=torch.float16, device=cuda_device)
+    q[..., 0] = 1.0
+    km = torch.zeros(1, 1, 8, 64, dtype=torch.float16, device=cuda_device)
+    km[0, 0, :, 0] = torch.arange(8, dtype=torch.float16)
+    assert ext.single_query_key_mean_topk(q, km, 3, 8, False).tolist() == [[7, 6, 5]]
+
+
+def test_local_windows_on_gpu(cuda_device):
+    ext = _ext()
+    for flat, nq, nk, k, causal in ((2, 5, 5, 3, True), (2, 5, 5, 3, False), (6, 4, 7, 5, True), (1, 6, 3, 3, True), (1, 8, 8, 8, False)):
+        q = torch.empty(1, flat, nq * 64, 64, dtype=torch.float16, device=cuda_device)
+        assert torch.equal(ext.local_block_topk(q, nk, k, causal, 64).cpu(), oracle.local_prefill(flat, nq, nk, k, causal))
+    qg = torch.empty(1, 3, 2, 64, dtype=torch.float16, device=cuda_device)
+    assert ext.single_query_local_topk(qg, 3, 7).tolist() == [[4, 5, 6]] * 3
+
+
+# ------------------------------------------------------------------------------------ prefill attention
+def _prefill_case(dev, dtype, fmt, block, S, hq, hkv, frac, causal, kperm, seed=0, outlier=False, sq=None):
+    torch.manual_seed(seed)
+    sq = S if sq is None else sq
+    q = torch.randn(1, hq, sq, 128)
+    k = torch.randn(1, hkv, S, 128)
+    v = torch.randn(1, hkv, S, 128)
+    if outlier:
+        k[:, :, :, torch.randperm(128)[:4]] *= 10
+    q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+    bf, mx = dtype == torch.bfloat16, fmt == "mxfp4"
+    ext = _ext()
+    nk = S // block
+    top_k = oracle.resolve_top_k(nk, causal=causal, fraction=frac) if frac > 0 else 0
+    sel = None
+    if top_k:
+        qm, = oracle.block_stats(q, block, ("mean",))
+        kmin, kmax = oracle.block_stats(k, block, ("min", "max"))
+        sel = oracle.select_prefill(qm, kmin, kmax, k=top_k, causal=causal)
+    ref = oracle.prefill_attention(q, k, v, sel, fmt=fmt, block=block, causal=causal)
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    q4, qs = getattr(ext, f"{fmt}_quantize")(qd, bf)
+    k4, ks = getattr(ext, f"{fmt}_quantize_permuted" if kperm else f"{fmt}_quantize")(kd, bf)
+    v4, vs = getattr(ext, f"{fmt}_quantize_transposed")(vd, bf)
+    out = ext.prefill_attention(qd, kd, vd, sel.to(dev) if sel is not None else None, q4, k4, v4, qs, ks, vs,
+                                causal=causal, is_mx=mx, is_bf16=bf, block_size=block, k_permuted=kperm, check_status=True)
+    err = (out.float().cpu() - ref.float()).abs()
+    assert not torch.isnan(out).any()
+    assert err.max().item() <= _tol(dtype, ref), f"max abs {err.max().item()}"
+    assert err.mean().item() <= MEAN_ABS
+    return out, ref, (q, k, v)
+
+
+PREFILL_CASES = [
+    (torch.float16, "nvfp4", 128, 256, 1, 1, 0.0, True, False),
+    (torch.float16, "nvfp4", 128, 256, 1, 1, 0.5, True, False),
+    (torch.float16, "nvfp4", 128, 1024, 2, 1, 0.1, True, True),
+    (torch.float16, "nvfp4", 64, 1024, 2, 1, 0.1, True, True),
+    (torch.float16, "nvfp4", 64, 1024, 2, 1, 0.1, False, True),
+    (torch.float16, "nvfp4", 64, 1024, 2, 1, 1.0, True, True),     # every block selected: pure 16-bit pass
+    (torch.bfloat16, "nvfp4", 64, 1024, 2, 2, 0.25, True, True),
+    (torch.float16, "mxfp4", 64, 1024, 4, 2, 0.1, True, True),
+    (torch.bfloat16, "mxfp4", 128, 1024, 4, 2, 0.1, True, False),
+    (torch.float16, "nvfp4", 64, 2048, 8, 8, 0.1, True, True),     # configuration 1 shape (8 q = 8 kv heads, 2048)
+    (torch.float16, "nvfp4", 128, 4096, 8, 2, 0.1, True, True),    # several work items per CTA
+    (torch.float16, "nvfp4", 64, 1088, 1, 1, 0.1, True, True),     # q_len not a multiple of the 128-row tile
+]
+
+
+@pytest.mark.parametrize("dtype,fmt,block,S,hq,hkv,frac,causal,kperm", PREFILL_CASES)
+def test_prefill_attention_matches_oracle(cuda_device, dtype, fmt, block, S, hq, hkv, frac, causal, kperm):
+    out, ref, (q, k, v) = _prefill_case(cuda_device, dtype, fmt, block, S, hq, hkv, frac, causal, kperm, outlier=(S >= 2048))
+    # the reference's own bar: cosine similarity > 0.95 against fp32 SDPA (tests/test_cuda_bf16_correctness.py:84-85)
+    if frac >= 0.1:
+        g = hq // hkv
+        sd = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float().repeat_interleave(g, 1),
+                                                              v.float().repeat_interleave(g, 1), is_causal=causal)
+        cos = torch.nn.functional.cosine_similarity(out.float().cpu().flatten(), sd.flatten(), dim=0)
+        assert float(cos) > 0.95
+
+
+def test_prefill_noncausal_rectangular(cuda_device):
+    _prefill_case(cuda_device, torch.float16, "nvfp4", 64, 1024, 2, 1, 0.1, False, True, sq=256)
+
+
+def test_prefill_is_deterministic_and_reference_named_ops_agree(cuda_device):
+    torch.manual_seed(4)
+    ext = _ext()
+    q = torch.randn(1, 4, 1024, 128, device=cuda_device).half()
+    k = torch.randn(1, 2, 1024, 128, device=cuda_device).half()
+    v = torch.randn(1, 2, 1024, 128, device=cuda_device).half()
+    qm, _, _ = ext.block_stats(q, 64, mean=True)
+    km, _, _ = ext.block_stats(k, 64, mean=True)
+    sel = ext.block_mean_topk(qm, km, 3, True, False)
+    packed = (ext.nvfp4_quantize(q)[0], ext.nvfp4_quantize_permuted(k)[0], ext.nvfp4_quantize_transposed(v)[0],
+              ext.nvfp4_quantize(q)[1], ext.nvfp4_quantize_permuted(k)[1], ext.nvfp4_quantize_transposed(v)[1])
+    a = ext.thrift_attention_causal_nvfp4_packed(q, k, v, sel, *packed, False)
+    b = ext.thrift_attention_causal_nvfp4_packed(q, k, v, sel, *packed, False)
+    assert torch.equal(a, b)
+    empty = sel[:, :, :0].contiguous()
+    c = ext.thrift_attention_causal_nvfp4_packed(q, k, v, empty, *packed, False)
+    d = ext.fp4_attention_causal_nvfp4_packed(*packed, False)
+    assert torch.equal(c, d)  # topk_count == 0 falls back to pure FP4 (bindings.cpp:525-528 of the reference)
+
+
+def test_public_attention_api(cuda_device):
+    import thriftattention_b200 as ta
+
+    torch.manual_seed(5)
+    q = torch.randn(1, 4, 512, 128).half()
+    k = torch.randn(1, 2, 512, 128).half()
+    v = torch.randn(1, 2, 512, 128).half()
+    for selection in ("block_mean", "quest", "local"):
+        cfg = ta.AttentionConfig(selection=selection, top_k=2, block_size=64)
+        out = ta.attention(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), config=cfg)
+        if selection == "local":
+            sel = oracle.local_prefill(4, 8, 8, 2, True)
+        else:
+            qm, = oracle.block_stats(q, 64, ("mean",))
+            km, kmin, kmax = oracle.block_stats(k, 64, ("mean", "min", "max"))
+            sel = oracle.select_prefill(qm, kmin, kmax, k=2, causal=True) if selection == "quest" else \
+                oracle.select_prefill(qm, km, None, k=2, causal=True)
+        ref = oracle.prefill_attention(q, k, v, sel, fmt="nvfp4", block=64, causal=True)
+        err = (out.float().cpu() - ref.float()).abs()
+        assert err.max().item() <= FP16_MAX_ABS and err.mean().item() <= MEAN_ABS
+    out = ta.attention(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device),
+                       config=ta.AttentionConfig(method="fp4", quant_format="mxfp4"))
+    ref = oracle.prefill_attention(q, k, v, None, fmt="mxfp4", block=64, causal=True)
+    assert (out.float().cpu() - ref.float()).abs().max().item() <= FP16_MAX_ABS
+    with pytest.raises(ValueError, match="divisible"):
+        ta.attention(q[:, :, :100].to(cuda_device), k.to(cuda_device), v.to(cuda_device))
+    with pytest.raises(ValueError, match="CUDA"):
+        ta.attention(q, k, v)
+
+
+def test_prefill_long_context_slice_matches_oracle(cuda_device):
+    """Configuration-2 shape (32q/8kv, 32768 tokens, 128-token blocks, top-10%, outlier keys): the whole
+    problem runs on the GPU, the oracle recomputes one q head's selection and a slice of its rows."""
+    import thriftattention_b200 as ta
+
+    S, block = 32768, 128
+    g = torch.Generator(device=cuda_device).manual_seed(0)
+    q = torch.randn(1, 32, S, 128, device=cuda_device, dtype=torch.float16, generator=g)
+    k = torch.randn(1, 8, S, 128, device=cuda_device, dtype=torch.float16, generator=g)
+    v = torch.randn(1, 8, S, 128, device=cuda_device, dtype=torch.float16, generator=g)
+    k[:, :, :, torch.tensor([3, 40, 77, 101], device=cuda_device)] *= 10
+    cfg = ta.AttentionConfig(selection="quest", fraction=0.10, block_size=block, quant_format="nvfp4")
+    out = ta.attention(q, k, v, config=cfg)
+    top_k = oracle.resolve_top_k(S // block, causal=True, fraction=0.10)
+    assert top_k == 13
+    for head in (5, 30):
+        qh, kh, vh = q[:, head:head + 1].cpu(), k[:, head // 4:head // 4 + 1].cpu(), v[:, head // 4:head // 4 + 1].cpu()
+        qm, = oracle.block_stats(qh, block, ("mean",))
+        kmin, kmax = oracle.block_stats(kh, block, ("min", "max"))
+        sel = oracle.select_prefill(qm, kmin, kmax, k=top_k, causal=True)
+        for lo in (0, 16384, S - 256):
+            ref = oracle.prefill_attention(qh, kh, vh, sel, fmt="nvfp4", block=block, causal=True, rows=(lo, lo + 256))
+            err = (out[0, head, lo:lo + 256].float().cpu() - ref[0, 0, lo:lo + 256].float()).abs()
+            assert err.max().item() <= FP16_MAX_ABS and err.mean().item() <= MEAN_ABS
+
+
+# ------------------------------------------------------------------------------------ decode attention
+DECODE_CASES = [
+    (torch.float16, "nvfp4", 1, 1, 4, 256, 0, 1),
+    (torch.float16, "nvfp4", 1, 1, 4, 256, 1, 1),
+    (torch.float16, "nvfp4", 2, 2, 8, 4096, 6, 5),
+    (torch.float16, "nvfp4", 1, 2, 1, 1024, 2, 3),
+    (torch.bfloat16, "nvfp4", 2, 2, 4, 1024, 3, 2),
+    (torch.float16, "mxfp4", 2, 2, 4, 1024, 3, 2),
+    (torch.bfloat16, "mxfp4", 2, 2, 4, 2048, 5, 4),
+    (torch.float16, "nvfp4", 2, 8, 4, 8192, 13, 7),
+]
+
+
+@pytest.mark.parametrize("dtype,fmt,B,hkv,G,S,top_k,splits", DECODE_CASES)
+def test_decode_attention_matches_oracle(cuda_device, dtype, fmt, B, hkv, G, S, top_k, splits):
+    torch.manual_seed(6)
+    ext = _ext()
+    bf, mx = dtype == torch.bfloat16, fmt == "mxfp4"
+    q = torch.randn(B, hkv, G, 128).to(dtype)
+    k = torch.randn(B, hkv, S, 128).to(dtype)
+    v = torch.randn(B, hkv, S, 128).to(dtype)
+    sel = None
+    if top_k:
+        kmin, kmax = oracle.block_stats(k, 64, ("min", "max"))
+        sel = oracle.select_decode(q, kmin, kmax, k=top_k, num_kv_blocks=S // 64)
+    ref, ref_o, ref_ml = oracle.decode_attention(q, k, v, sel, fmt=fmt, splits=splits, return_partials=True)
+    qd, kd, vd = q.to(cuda_device), k.to(cuda_device), v.to(cuda_device)
+    q4, qs = getattr(ext, f"{fmt}_quantize")(qd, bf)
+    k4, ks = getattr(ext, f"{fmt}_quantize")(kd, bf)
+    v4, vs = getattr(ext, f"{fmt}_quantize_transposed")(vd, bf)
+    out, po, pml = ext.decode_attention(qd, kd, vd, sel.to(cuda_device) if sel is not None else None, q4, k4, v4, qs, ks, vs,
+                                        is_mx=mx, is_bf16=bf, num_splits=splits, return_partials=True)
+    err = (out.float().cpu() - ref.float()).abs()
+    assert err.max().item() <= _tol(dtype, ref) and err.mean().item() <= MEAN_ABS
+    assert (pml.cpu() - ref_ml).abs().max().item() < 1e-3
+    merged = ext.merge_decode_partials(po.unsqueeze(0).contiguous(), pml.unsqueeze(0).contiguous(), is_mx=mx, is_bf16=bf)
+    assert torch.equal(merged.view_as(out), out)
+    # two half-sequence "shards" merged with the shard-merge entry point reproduce a 2-chain run
+    if splits == 2:
+        o2 = po.permute(1, 0, 2, 3).unsqueeze(2).contiguous()
+        m2 = pml.permute(1, 0, 2, 3).unsqueeze(2).contiguous()
+        assert torch.equal(ext.merge_decode_partials(o2, m2, is_mx=mx, is_bf16=bf).view_as(out), out)
+
+
+def test_decode_through_public_api_and_reference_named_ops(cuda_device):
+    import thriftattention_b200 as ta
+
+    torch.manual_seed(7)
+    ext = _ext()
+    q = torch.randn(2, 8, 1, 128).half()
+    k = torch.randn(2, 2, 2048, 128).half()
+    v = torch.randn(2, 2, 2048, 128).half()
+    out = ta.attention(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device),
+                       config=ta.AttentionConfig(selection="quest", top_k=4))
+    qg = q.reshape(2, 2, 4, 128)
+    kmin, kmax = oracle.block_stats(k, 64, ("min", "max"))
+    sel = oracle.select_decode(qg, kmin, kmax, k=4, num_kv_blocks=32)
+    splits = ext.decode_pick_splits(4, 32)
+    ref = oracle.decode_attention(qg, k, v, sel, fmt="nvfp4", splits=splits).reshape(2, 8, 1, 128)
+    err = (out.float().cpu() - ref.float()).abs()
+    assert err.max().item() <= FP16_MAX_ABS and err.mean().item() <= MEAN_ABS
+    out4 = ta.attention(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), config=ta.AttentionConfig(method="fp4"))
+    ref4 = oracle.decode_attention(qg, k, v, None, fmt="nvfp4", splits=splits).reshape(2, 8, 1, 128)
+    assert (out4.float().cpu() - ref4.float()).abs().max().item() <= FP16_MAX_ABS
+
+
+def test_argument_errors_raise(cuda_device):
+    ext = _ext()
+    x = torch.randn(1, 1, 64, 96, device=cuda_device).half()
+    with pytest.raises(RuntimeError, match="head_dim"):
+        ext.nvfp4_quantize(x, False)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        ext.nvfp4_quantize(torch.randn(1, 1, 256, 128, device=cuda_device).half()[:, :, ::2], False)
+    qm = torch.randn(1, 1, 4, 64, device=cuda_device).half()
+    with pytest.raises(RuntimeError, match="topk_count"):
+        ext.block_mean_topk(qm, qm, 9, True, False)
