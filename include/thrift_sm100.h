@@ -39,6 +39,7 @@ extern "C" {
 #define TA100_ERR_TENSOR_MAP (-6)
 #define TA100_ERR_DEVICE_TIMEOUT (-7)
 #define TA100_ERR_LIMIT (-8)
+#define TA100_ERR_STATIC_SCRATCH (-9)
 
 int ta100_version(void);
 const char* ta100_status_string(int status);
@@ -162,6 +163,34 @@ int ta100_decode_attention(const void* q_hi, const void* k_hi, const void* v_hi,
                            const void* page_table, int max_pages, void* out, void* part_o, void* part_ml, int batch,
                            int hkv, int group, int kv_len, int kv_cap, int head_dim, int is_mxfp4, int is_bf16, int splits,
                            int write_out, void* stream);
+
+/*
+ * Decode attention for callers that cannot allocate device memory (no counterpart in the
+ * reference, whose binding allocates its split-KV workspace on every call).
+ *
+ * Meant for hosts that gave all free HBM to their own memory pool at start-up, so that a later
+ * cudaMalloc would fail, and for latency-critical decode loops that must not take the device-wide
+ * synchronisation cudaMalloc / cudaFree imply.  Inputs, `sel` and `out` are still the caller's;
+ * only the split-KV partials (what ta100_decode_attention takes as part_o / part_ml) are kept in
+ * a fixed 16 MiB device array inside the library, resident on every GPU that loads the library
+ * until the process exits.  The call returns TA100_ERR_STATIC_SCRATCH when
+ *   batch*hkv*splits*group*(head_dim + 2)*4 bytes (+ alignment)  >  ta100_decode_static_scratch_bytes(),
+ * in which case lower `splits` or use ta100_decode_attention.  It never calls cudaMalloc, cudaFree
+ * or any allocating routine.
+ *
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
+ * device current) and caches it; make that first call before starting any stream capture.  All
+ * calls on a device share the array and it keeps the last call's contents: every call rewrites
+ * each entry it reads, so no clearing is needed, but two calls that overlap on the GPU (for
+ * example on different streams) race on it.  Results are identical to ta100_decode_attention with
+ * write_out = 1 and the same `splits`.
+ */
+size_t ta100_decode_static_scratch_bytes(void);
+int ta100_decode_attention_static(const void* q_hi, const void* k_hi, const void* v_hi, const void* sel, int width,
+                                  const void* q4, const void* k4, const void* v4, const void* qs, const void* ks,
+                                  const void* vs, const void* page_table, int max_pages, void* out, int batch, int hkv,
+                                  int group, int kv_len, int kv_cap, int head_dim, int is_mxfp4, int is_bf16, int splits,
+                                  void* stream);
 
 /*
  * Log-sum-exp merge of decode partials from `shards` producers (e.g. GPUs that each hold a slice

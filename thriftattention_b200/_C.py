@@ -511,3 +511,37 @@ def thrift_attention_single_query_mxfp4_packed(q_hi, k_hi, v_hi, selected_blocks
                                                k_scale, v_scale_t, is_bf16=False):
     return _thrift_single(q_hi, k_hi, v_hi, selected_blocks, (q_packed, k_packed, v_packed_t, q_scale, k_scale,
                                                               v_scale_t), True, is_bf16)
+
+
+def decode_attention_noalloc(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale,
+                             v_scale_t, out, *, is_mx, is_bf16=False, num_splits=0):
+    """Decode attention that allocates nothing: the caller passes ``out`` ([B, Hkv, G, D], 16-bit) and
+    the split-KV partials live in a fixed 16 MiB array inside the CUDA library.
+
+    For processes that cannot allocate device memory at call time — all free HBM already belongs to
+    their own pool, or a ``cudaMalloc`` stall is not acceptable inside the decode loop.  Same result
+    as ``decode_attention`` with the same ``num_splits``.  Calls on one device share the scratch, so
+    do not let two of them overlap on the GPU; make the first call on a device outside stream
+    capture.  Raises ``RuntimeError`` when the problem needs more scratch than the fixed array holds.
+    Contiguous (non-paged) caches only in this wrapper.
+    """
+    b, hkv, g, dh = q_packed.shape
+    d = dh * 2
+    skv = k_packed.size(2)
+    _check(skv % 64 == 0, "k sequence length must be divisible by 64")
+    _check(out.is_cuda and out.is_contiguous() and tuple(out.shape) == (b, hkv, g, d), "out must be contiguous [B, Hkv, G, D]")
+    _check(out.dtype == (torch.bfloat16 if is_bf16 else torch.float16), "out dtype must match is_bf16")
+    kv_cap = max(skv, k_packed.stride(1) // dh)
+    width = 0 if selected_blocks is None else selected_blocks.size(1)
+    lib = _lib.load()
+    splits = num_splits if num_splits > 0 else lib.ta100_decode_pick_splits(b * hkv, skv // 64)
+    splits = max(1, min(splits, skv // 64))
+    sel = selected_blocks if width else None
+    with torch.cuda.device(out.device):
+        rc = lib.ta100_decode_attention_static(
+            _ptr(q_hi) if sel is not None else None, _ptr(k_hi) if sel is not None else None,
+            _ptr(v_hi) if sel is not None else None, _ptr(sel), width, _ptr(q_packed), _ptr(k_packed), _ptr(v_packed_t),
+            _ptr(q_scale), _ptr(k_scale), _ptr(v_scale_t), None, 0, _ptr(out), b, hkv, g, skv, kv_cap, d, int(is_mx),
+            int(is_bf16), splits, _stream(out))
+    _lib.check(rc, "decode_attention_noalloc")
+    return out

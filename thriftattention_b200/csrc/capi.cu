@@ -25,6 +25,10 @@ int decode_dispatch(const void*, const void*, const void*, const void*, int, con
                     const void*, const void*, const void*, const void*, int, void*, void*, void*, int, int, int, int, int,
                     int, int, int, int, int, cudaStream_t);
 int merge_dispatch(const void*, const void*, void*, int, long long, int, int, int, int, int, cudaStream_t);
+size_t decode_static_scratch_bytes();
+int decode_static_dispatch(const void*, const void*, const void*, const void*, int, const void*, const void*, const void*,
+                           const void*, const void*, const void*, const void*, int, void*, int, int, int, int, int, int, int,
+                           int, int, cudaStream_t);
 }  // namespace ta100
 
 using namespace ta100;
@@ -45,6 +49,8 @@ const char* ta100_status_string(int status) {
         case TA100_ERR_TENSOR_MAP: return "tensor map creation failed";
         case TA100_ERR_DEVICE_TIMEOUT: return "a device-side wait timed out";
         case TA100_ERR_LIMIT: return "size beyond a compiled-in limit";
+        case TA100_ERR_STATIC_SCRATCH:
+            return "problem needs more split-KV scratch than the library's fixed 16 MiB array; use ta100_decode_attention";
         default: return status > 0 ? cudaGetErrorString(static_cast<cudaError_t>(status)) : "unknown status";
     }
 }
@@ -124,6 +130,17 @@ int ta100_merge_partials(const void* part_o, const void* part_ml, void* out, int
                          int splits, int group, int head_dim, int is_mxfp4, int is_bf16, void* stream) {
     return merge_dispatch(part_o, part_ml, out, shards, flat_kv_heads, splits, group, head_dim, is_mxfp4, is_bf16,
                           S(stream));
+}
+
+size_t ta100_decode_static_scratch_bytes(void) { return decode_static_scratch_bytes(); }
+
+int ta100_decode_attention_static(const void* q_hi, const void* k_hi, const void* v_hi, const void* sel, int width,
+                                  const void* q4, const void* k4, const void* v4, const void* qs, const void* ks,
+                                  const void* vs, const void* page_table, int max_pages, void* out, int batch, int hkv,
+                                  int group, int kv_len, int kv_cap, int head_dim, int is_mxfp4, int is_bf16, int splits,
+                                  void* stream) {
+    return decode_static_dispatch(q_hi, k_hi, v_hi, sel, width, q4, k4, v4, qs, ks, vs, page_table, max_pages, out, batch,
+                                  hkv, group, kv_len, kv_cap, head_dim, is_mxfp4, is_bf16, splits, S(stream));
 }
 
 }  // extern "C"

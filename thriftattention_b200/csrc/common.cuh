@@ -21,6 +21,7 @@ enum Status : int {
     TA100_ERR_TENSOR_MAP = -6,
     TA100_ERR_DEVICE_TIMEOUT = -7,
     TA100_ERR_LIMIT = -8,
+    TA100_ERR_STATIC_SCRATCH = -9,
 };
 
 constexpr int NUM_SMS_HINT = 148;

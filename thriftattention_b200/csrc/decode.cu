@@ -13,6 +13,7 @@
 // per 32-wide group) and multiplied with mma.sync.m16n8k16, with the KV tokens
 // (or head channels) on the M side and the query heads on the N side.
 #include <cfloat>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -642,6 +643,67 @@ int merge_dispatch(const void* part_o, const void* part_ml, void* out, int shard
         merge_kernel<false><<<mgrid, 128, 0, stream>>>(static_cast<const float*>(part_o), static_cast<const float*>(part_ml),
                                                        static_cast<uint16_t*>(out), shards, so, sml, splits, G, d, rows, c);
     return static_cast<int>(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------
+// Allocation-free decode entry
+// ---------------------------------------------------------------------------
+// Some hosts cannot give this library device memory at call time: a serving
+// process that has handed every free byte of HBM to its own pool at start-up
+// (so a later cudaMalloc fails), or a latency-critical decode loop in which the
+// implicit device-wide synchronisation of cudaMalloc / cudaFree is not
+// acceptable.  For them the split-KV partials live in this fixed array, which
+// every GPU that loads the library holds from load until process exit.
+constexpr size_t STATIC_SCRATCH_BYTES = size_t(16) << 20;  // 16 MiB
+static __device__ __align__(256) unsigned char g_decode_static_scratch[STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+void* g_static_scratch_ptr[MAX_DEVICES] = {};
+std::mutex g_static_scratch_mutex;
+
+// The array's name is only a host-side handle: the device address has to be
+// looked up, once per device, while that device is current.
+int static_scratch_address(void** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev < 0 || dev >= MAX_DEVICES) return TA100_ERR_LIMIT;
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        g_static_scratch_ptr[dev] = p;
+    }
+    *out = g_static_scratch_ptr[dev];
+    return TA100_OK;
+}
+}  // namespace
+
+size_t decode_static_scratch_bytes() { return STATIC_SCRATCH_BYTES; }
+
+// Same computation as decode_dispatch with write_out = 1, but the partials go to
+// the library's fixed scratch array instead of caller memory.  Nothing is
+// allocated or freed here.  The scratch is shared by every call on the device
+// and keeps the previous call's contents; each call overwrites every entry it
+// later reads, so nothing needs clearing, but two calls that overlap on the GPU
+// (different streams) would race on it.
+int decode_static_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const void* sel, int width, const void* q4,
+                           const void* k4, const void* v4, const void* qs, const void* ks, const void* vs,
+                           const void* page_table, int max_pages, void* out, int batch, int hkv, int G, int kv_len,
+                           int kv_cap, int d, int is_mx, int is_bf16, int splits, cudaStream_t stream) {
+    if (batch <= 0 || hkv <= 0 || G <= 0 || splits <= 0 || d <= 0) return TA100_ERR_SHAPE;
+    const size_t n_o = static_cast<size_t>(batch) * hkv * splits * G * d * sizeof(float);
+    const size_t n_ml = static_cast<size_t>(batch) * hkv * splits * G * 2 * sizeof(float);
+    const size_t off_ml = (n_o + 255) & ~static_cast<size_t>(255);
+    if (off_ml + n_ml > STATIC_SCRATCH_BYTES) return TA100_ERR_STATIC_SCRATCH;
+    void* base = nullptr;
+    const int rc = static_scratch_address(&base);
+    if (rc != TA100_OK) return rc;
+    unsigned char* b = static_cast<unsigned char*>(base);
+    return decode_dispatch(q_hi, k_hi, v_hi, sel, width, q4, k4, v4, qs, ks, vs, page_table, max_pages, out, b, b + off_ml,
+                           batch, hkv, G, kv_len, kv_cap, d, is_mx, is_bf16, splits, 1, stream);
 }
 
 }  // namespace ta100
