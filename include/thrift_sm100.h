@@ -117,7 +117,7 @@ int ta100_pack_topk_mask(const void* sel, void* mask, long long rows, int k, int
  *        re-tiled scale factors and a device status word
  *   round_partial = 1 rounds the running state to the 16-bit type between the two
  *        passes as the reference's two-kernel pipeline does
- *   max_ctas: 0 = one CTA per SM
+ *   max_ctas: 0 = two persistent CTAs per SM
  * sq and skv multiples of 64, head_dim 128, skv <= 131072.  causal assumes query
  * row r sees keys <= r.
  * Replaces fp4_attention_{causal,noncausal}_{nvfp4,mxfp4} and

@@ -1,6 +1,6 @@
 // Fused selective mixed-precision prefill attention for sm_100a.
 //
-// One persistent CTA per SM walks (q head, 128-row q tile) work items, longest
+// Persistent CTAs (two per SM) walk (q head, 128-row q tile) work items, longest
 // first.  Per item the KV sequence is consumed in 64-column steps:
 //   phase A  every step whose KV block is NOT selected: block-scaled FP4
 //            tcgen05 MMAs (S = Q4 K4^T, O += P4 V4) with P quantised to e2m1;
@@ -8,9 +8,11 @@
 // Both phases share one online softmax whose state (row max, row sum) lives in
 // registers and whose accumulator O lives in tensor memory for the whole item.
 //
-// Warp roles (192 threads): warp 0 = TMA producer (+ builds the per-item block
-// bitsets), warp 1 = MMA issuer and tensor-memory owner, warps 2..5 = softmax
-// (one thread per q row; warp w owns tensor-memory lanes 32*(w%4)..+31).
+// Warp roles (192 threads): warp 0 = TMA producer (it also builds the item's
+// step list in shared memory), warp 1 = MMA issuer and tensor-memory owner,
+// warps 2..5 = softmax (one thread per q row; warp w owns tensor-memory lanes
+// 32*(w%4)..+31).  Two CTAs share an SM so that the softmax warps of one hide
+// the tensor-memory and barrier latencies of the other.
 //
 // Every mbarrier wait is bounded; a timeout raises a CTA-wide abort flag, all
 // roles drain, tensor memory is released and a status word is set.
@@ -24,20 +26,38 @@ namespace ta100 {
 
 namespace {
 
+// Optional phase timers for the softmax warps (development aid; compiled out by default).
+#ifdef TA100_PROFILE_SOFTMAX
+__device__ long long g_prof[16];
+#define TA100_PROF_DECL long long prof_t = clock64(), prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long prof_steps = 0;
+#define TA100_PROF(i) { const long long now_ = clock64(); prof_acc[i] += now_ - prof_t; prof_t = now_; }
+#define TA100_PROF_STEP ++prof_steps;
+#define TA100_PROF_DUMP if (blockIdx.x == 0 && warp == 2 && lane == 0) { for (int i_ = 0; i_ < 10; ++i_) g_prof[i_] = prof_acc[i_]; g_prof[10] = prof_steps; }
+#else
+#define TA100_PROF_DECL
+#define TA100_PROF(i)
+#define TA100_PROF_STEP
+#define TA100_PROF_DUMP
+#endif
+
 constexpr int QTILE = 128;
 constexpr int STEP = 64;
-constexpr int NSTAGES = 4;
-constexpr int STAGE_BYTES = 32768;
+constexpr int NSLOTS = 3;            // K/V ring slots
+constexpr int SLOT_BYTES = 16384;    // one FP4 step (K4, V4, scale atoms) or one 16-bit K or V tile
 constexpr int NUM_THREADS = 192;
+constexpr int SCHED_CAP = 2944;      // step-list entries per work item
 
-// tensor-memory columns
+// tensor-memory columns (256 allocated per CTA)
 constexpr uint32_t TM_O = 0;
-constexpr uint32_t TM_S = 128;      // two buffers of 64 columns
-constexpr uint32_t TM_SFA_Q = 256;  // up to 8 columns
-constexpr uint32_t TM_SFB_K = 264;  // two slots of 8 columns
-constexpr uint32_t TM_SFA_P = 280;  // 4 columns, constant
-constexpr uint32_t TM_SFB_V = 284;  // two slots of 4 columns
-constexpr uint32_t TM_COLS = 512;
+constexpr uint32_t TM_S = 128;       // 64 columns
+constexpr uint32_t TM_SFA_Q = 192;   // up to 8 columns
+constexpr uint32_t TM_SFB_K = 200;   // 8 columns
+constexpr uint32_t TM_SFA_P = 208;   // 4 columns, constant
+constexpr uint32_t TM_SFB_V = 212;   // two slots of 4 columns
+constexpr uint32_t TM_COLS = 256;
+
+// step-list entry: bits 0..11 step index, 12 = 16-bit step, 13 / 14 = rows 0..63 / 64..127 take part
+constexpr uint32_t E_FP16 = 1u << 12, E_P0 = 1u << 13, E_P1 = 1u << 14;
 
 struct PrefillParams {
     int batch, hq_per_b, hkv_per_b, group;
@@ -62,91 +82,28 @@ struct Smem {
     static constexpr int Q4 = 0;                       // 128 x D/2
     static constexpr int QSF = Q4 + QTILE * D / 2;     // up to 2 atoms
     static constexpr int Q16 = QSF + 1024;             // 128 x D x 2
-    static constexpr int P = Q16 + QTILE * D * 2;      // two buffers of 16 KB
-    static constexpr int CSF = P + 2 * 16384;          // constant scale atom
-    static constexpr int STAGES = CSF + 1024;
-    static constexpr int BITS = STAGES + NSTAGES * STAGE_BYTES;  // 2 buffers x 2 halves x 64 words
-    static constexpr int TOTAL = BITS + 2 * 2 * 64 * 4;
-    // inside a stage
+    static constexpr int P = Q16 + QTILE * D * 2;      // 16 KB: two 4 KB FP4 buffers or one 16-bit tile
+    static constexpr int SLOTS = P + 16384;
+    static constexpr int CSF = SLOTS + NSLOTS * SLOT_BYTES;    // constant scale atom (512 B)
+    static constexpr int BITS = CSF + 512;                     // 2 halves x 64 words
+    static constexpr int BARS = BITS + 2 * 64 * 4;             // mbarriers and CTA-wide flags (256 B)
+    static constexpr int SCHED = BARS + 256;                   // SCHED_CAP x u16
+    static constexpr int TOTAL = SCHED + SCHED_CAP * 2;        // 112 KB: two CTAs fit one SM
+    // inside an FP4 slot
     static constexpr int K4 = 0, V4 = 4096, KSF = 8192, VSF = 9216;
-    static constexpr int K16 = 0, V16 = 16384;
 };
 
 struct Bars {
     uint64_t q_full, q_empty;
-    uint64_t sched_full[2], sched_empty[2];
-    uint64_t kv_full[NSTAGES], kv_empty[NSTAGES];
-    uint64_t s_full[2], s_free[2];
+    uint64_t sched_full, sched_empty;
+    uint64_t slot_full[NSLOTS], slot_empty[NSLOTS];
+    uint64_t s_full, s_free;
     uint64_t p_full[2], p_free[2];
+    int sched_n;
+    uint32_t tmem_base;
+    int abort_flag;
 };
-
-struct Step {
-    int st;  // 64-column step index
-    bool fp16, p0, p1;
-};
-
-// Deterministic walk over the steps of one work item; every role runs its own
-// copy and sees the same sequence.  All 32 lanes of the warp must call next().
-struct StepIter {
-    const int32_t* list0;
-    const int32_t* list1;
-    const uint32_t* bits0;
-    const uint32_t* bits1;
-    int width, spb_shift, spb, nkb, nsteps, nsteps_total, last0, last1;
-    bool has_sel, two;
-    int phase, s, li, sub, cur_id;
-    int32_t cache;
-
-    __device__ __forceinline__ static bool bit(const uint32_t* b, int i) { return (b[i >> 5] >> (i & 31)) & 1u; }
-
-    __device__ bool next(Step& out, int lane) {
-        while (true) {
-            if (phase == 0) {
-                while (s < nsteps) {
-                    const int st = s++;
-                    const int blk = st >> spb_shift;
-                    const bool p0 = (st * STEP <= last0) && !(has_sel && bit(bits0, blk));
-                    const bool p1 = (st * STEP <= last1) && !(has_sel && bit(bits1, blk));
-                    if (p0 | p1) { out = {st, false, p0, p1}; return true; }
-                }
-                phase = has_sel ? 1 : 3;
-                li = 0; sub = 0;
-                continue;
-            }
-            if (phase == 1 || phase == 2) {
-                const int32_t* list = phase == 1 ? list0 : list1;
-                while (li < width) {
-                    if (sub == 0) {
-                        if ((li & 31) == 0) cache = (li + lane < width) ? list[li + lane] : -1;
-                        cur_id = __shfl_sync(0xFFFFFFFFu, cache, li & 31);
-                    }
-                    const int id = cur_id;
-                    bool ok = id >= 0 && id < nkb;
-                    if (ok && phase == 2 && bit(bits0, id)) ok = false;  // already walked with list0
-                    if (ok) {
-                        const int st = (id << spb_shift) + sub;
-                        bool p0, p1;
-                        if (phase == 1) {
-                            p0 = st * STEP <= last0;
-                            p1 = (st * STEP <= last1) && (!two || bit(bits1, id));
-                        } else {
-                            p0 = false;
-                            p1 = st * STEP <= last1;
-                        }
-                        if (++sub == spb) { sub = 0; ++li; }
-                        if ((p0 | p1) && st < nsteps_total) { out = {st, true, p0, p1}; return true; }
-                        continue;
-                    }
-                    sub = 0; ++li;
-                }
-                phase = (phase == 1 && two) ? 2 : 3;
-                li = 0; sub = 0;
-                continue;
-            }
-            return false;
-        }
-    }
-};
+static_assert(sizeof(Bars) <= 256, "barrier block must fit its shared-memory slot");
 
 struct ItemInfo {
     int h, t, kvh;
@@ -162,33 +119,99 @@ __device__ __forceinline__ ItemInfo decode_item(const PrefillParams& p, int item
     return it;
 }
 
-__device__ __forceinline__ void init_iter(StepIter& itr, const PrefillParams& p, const ItemInfo& it,
-                                          const uint32_t* bits /* [2][64] */) {
+__device__ __forceinline__ bool bit_of(const uint32_t* b, int i) { return (b[i >> 5] >> (i & 31)) & 1u; }
+
+// Builds the step list of one work item (whole warp).  Order: every step whose
+// block is not selected, ascending; then the selected blocks of the first
+// 64-row half in list order; then those of the second half that were not
+// already visited.  Returns the number of entries, or -1 if the list overflows.
+__device__ int build_schedule(const PrefillParams& p, const ItemInfo& it, uint32_t* bits, uint16_t* sched, int lane) {
     const int nqb = p.sq / p.block;
     const int row0 = it.t * QTILE;
     const int qb0 = row0 / p.block;
     const int qb1 = min((row0 + 64) / p.block, nqb - 1);
-    itr.two = (qb1 != qb0);
-    itr.has_sel = p.width > 0;
-    itr.width = p.width;
-    itr.list0 = itr.has_sel ? p.sel + (static_cast<long long>(it.h) * nqb + qb0) * p.width : nullptr;
-    itr.list1 = itr.has_sel ? p.sel + (static_cast<long long>(it.h) * nqb + qb1) * p.width : nullptr;
-    itr.bits0 = bits;
-    itr.bits1 = itr.two ? bits + 64 : bits;
-    itr.spb = p.block / STEP;
-    itr.spb_shift = (p.block == 128) ? 1 : 0;
-    itr.nkb = p.nkb;
-    itr.nsteps_total = p.nsteps_total;
+    const bool two = qb1 != qb0;
+    const bool has_sel = p.width > 0;
+    const int spb_shift = (p.block == 128) ? 1 : 0, spb = 1 << spb_shift;
+    const int32_t* list0 = has_sel ? p.sel + (static_cast<long long>(it.h) * nqb + qb0) * p.width : nullptr;
+    const int32_t* list1 = has_sel ? p.sel + (static_cast<long long>(it.h) * nqb + qb1) * p.width : nullptr;
+    uint32_t* bits0 = bits;
+    uint32_t* bits1 = two ? bits + 64 : bits;
+    int last0, last1, nsteps;
     if (p.causal) {
-        itr.last0 = row0 + 63;
-        itr.last1 = row0 + 127;
-        itr.nsteps = min(p.nsteps_total, itr.last1 / STEP + 1);
+        last0 = row0 + 63; last1 = row0 + 127;
+        nsteps = min(p.nsteps_total, last1 / STEP + 1);
     } else {
-        itr.last0 = INT_MAX;
-        itr.last1 = INT_MAX;
-        itr.nsteps = p.nsteps_total;
+        last0 = INT_MAX; last1 = INT_MAX;
+        nsteps = p.nsteps_total;
     }
-    itr.phase = 0; itr.s = 0; itr.li = 0; itr.sub = 0; itr.cur_id = -1; itr.cache = -1;
+    // ---- bitsets of the selected blocks ----
+    for (int i = lane; i < 128; i += 32) bits[i] = 0u;
+    __syncwarp();
+    if (has_sel) {
+        for (int half = 0; half < (two ? 2 : 1); ++half) {
+            const int32_t* list = half ? list1 : list0;
+            for (int i = lane; i < p.width; i += 32) {
+                const int id = list[i];
+                if (id >= 0 && id < p.nkb) atomicOr(&bits[half * 64 + (id >> 5)], 1u << (id & 31));
+            }
+        }
+    }
+    __syncwarp();
+    const uint32_t lt = (1u << lane) - 1u;
+    int n = 0;
+    // ---- phase A ----
+    for (int base = 0; base < nsteps; base += 32) {
+        const int st = base + lane;
+        bool p0 = false, p1 = false;
+        if (st < nsteps) {
+            const int blk = st >> spb_shift;
+            p0 = (st * STEP <= last0) && !(has_sel && bit_of(bits0, blk));
+            p1 = (st * STEP <= last1) && !(has_sel && bit_of(bits1, blk));
+        }
+        const bool keep = p0 | p1;
+        const uint32_t m = __ballot_sync(0xFFFFFFFFu, keep);
+        const int pos = n + __popc(m & lt);
+        if (keep && pos < SCHED_CAP) sched[pos] = static_cast<uint16_t>(st | (p0 ? E_P0 : 0) | (p1 ? E_P1 : 0));
+        n += __popc(m);
+    }
+    // ---- phase B ----
+    if (has_sel) {
+        for (int pass = 0; pass < (two ? 2 : 1); ++pass) {
+            const int32_t* list = pass ? list1 : list0;
+            for (int base = 0; base < p.width; base += 32) {
+                const int i = base + lane;
+                const int id = i < p.width ? list[i] : -1;
+                bool ok = id >= 0 && id < p.nkb;
+                if (ok && pass == 1 && bit_of(bits0, id)) ok = false;  // already visited with the first half's list
+                uint32_t e[2] = {0, 0};
+                bool keep[2] = {false, false};
+                if (ok) {
+                    for (int sub = 0; sub < spb; ++sub) {
+                        const int st = (id << spb_shift) + sub;
+                        bool p0, p1;
+                        if (pass == 0) {
+                            p0 = st * STEP <= last0;
+                            p1 = (st * STEP <= last1) && (!two || bit_of(bits1, id));
+                        } else {
+                            p0 = false;
+                            p1 = st * STEP <= last1;
+                        }
+                        keep[sub] = (p0 | p1) && st < p.nsteps_total;
+                        e[sub] = st | E_FP16 | (p0 ? E_P0 : 0) | (p1 ? E_P1 : 0);
+                    }
+                }
+                const uint32_t m0 = __ballot_sync(0xFFFFFFFFu, keep[0]);
+                const uint32_t m1 = __ballot_sync(0xFFFFFFFFu, keep[1]);
+                int pos = n + __popc(m0 & lt) + __popc(m1 & lt);
+                if (keep[0]) { if (pos < SCHED_CAP) sched[pos] = static_cast<uint16_t>(e[0]); ++pos; }
+                if (keep[1] && pos < SCHED_CAP) sched[pos] = static_cast<uint16_t>(e[1]);
+                n += __popc(m0) + __popc(m1);
+            }
+        }
+    }
+    __syncwarp();
+    return n <= SCHED_CAP ? n : -1;
 }
 
 // Column maps inside a 64-column step.  With the "permuted" K layout physical
@@ -207,8 +230,51 @@ struct ColMap {
     }
 };
 
+// packed fp32x2 arithmetic (two lanes per instruction)
+__device__ __forceinline__ uint64_t pack2f(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2f(uint64_t v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// p_j * scale for 64 logits: s[j] <- 2^(s[j] * c2 + bias); returns the sum of the results.
+__device__ __forceinline__ float exp_scaled_64(float (&s)[STEP], float c2, float bias) {
+    const uint64_t c2p = pack2f(c2, c2), bp = pack2f(bias, bias);
+    uint64_t acc0 = pack2f(0.0f, 0.0f), acc1 = acc0;
+#pragma unroll
+    for (int j = 0; j < STEP; j += 4) {
+        float a, b, c, d;
+        unpack2f(fma2(pack2f(s[j], s[j + 1]), c2p, bp), a, b);
+        unpack2f(fma2(pack2f(s[j + 2], s[j + 3]), c2p, bp), c, d);
+        s[j] = ex2(a); s[j + 1] = ex2(b); s[j + 2] = ex2(c); s[j + 3] = ex2(d);
+        acc0 = add2(acc0, pack2f(s[j], s[j + 1]));
+        acc1 = add2(acc1, pack2f(s[j + 2], s[j + 3]));
+    }
+    float x, y;
+    unpack2f(add2(acc0, acc1), x, y);
+    return x + y;
+}
+
 template <int D, bool MX, bool BF16, bool CAUSAL, bool KPERM>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS, 2)
 prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4, const __grid_constant__ CUtensorMap mapK4,
                const __grid_constant__ CUtensorMap mapV4, const __grid_constant__ CUtensorMap mapQ16,
                const __grid_constant__ CUtensorMap mapK16, const __grid_constant__ CUtensorMap mapV16) {
@@ -223,36 +289,36 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
     constexpr float CSCALE_INV = MX ? (1.0f / 6.0f) : (1.0f / 2688.0f);
     constexpr ColMap<KPERM> cmap{};
 
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    __shared__ Bars bars;
-    __shared__ uint32_t tmem_base_s;
-    __shared__ int abort_flag;
+    // No static shared memory: the dynamic window then starts 1024-byte aligned, which the
+    // 128-byte swizzled tiles need (checked below).
+    extern __shared__ __align__(1024) uint8_t smem[];
+    Bars& bars = *reinterpret_cast<Bars*>(smem + L::BARS);
+    int& abort_flag = bars.abort_flag;
+    uint32_t& tmem_base_s = bars.tmem_base;
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const uint32_t sbase = smem_u32(smem);
     volatile int* abortp = &abort_flag;
     const long long budget = p.budget;
+    uint16_t* sched = reinterpret_cast<uint16_t*>(smem + L::SCHED);
 
     if (tid == 0) {
         mbar_init(smem_u32(&bars.q_full), 1);
         mbar_init(smem_u32(&bars.q_empty), 1);
+        mbar_init(smem_u32(&bars.sched_full), 1);
+        mbar_init(smem_u32(&bars.sched_empty), 5);
+        mbar_init(smem_u32(&bars.s_full), 1);
+        mbar_init(smem_u32(&bars.s_free), 128);
+        for (int i = 0; i < NSLOTS; ++i) {
+            mbar_init(smem_u32(&bars.slot_full[i]), 1);
+            mbar_init(smem_u32(&bars.slot_empty[i]), 1);
+        }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&bars.sched_full[i]), 1);
-            mbar_init(smem_u32(&bars.sched_empty[i]), 5);
-            mbar_init(smem_u32(&bars.s_full[i]), 1);
-            mbar_init(smem_u32(&bars.s_free[i]), 128);
+            mbar_init(smem_u32(&bars.p_full[i]), 128);
+            mbar_init(smem_u32(&bars.p_free[i]), 1);
         }
-        for (int i = 0; i < NSTAGES; ++i) {
-            mbar_init(smem_u32(&bars.kv_full[i]), 1);
-            mbar_init(smem_u32(&bars.kv_empty[i]), 1);
-        }
-        mbar_init(smem_u32(&bars.p_full[0]), 128);
-        mbar_init(smem_u32(&bars.p_full[1]), 128);
-        mbar_init(smem_u32(&bars.p_free[0]), 1);
-        mbar_init(smem_u32(&bars.p_free[1]), 1);
         mbar_fence_init();
-        abort_flag = 0;
+        abort_flag = (sbase & 1023u) ? 1 : 0;
     }
     // constant scale atom for P: 448 (E4M3 0x7E) or 1.0 (E8M0 0x7F)
     for (int i = tid; i < 512 / 4; i += NUM_THREADS)
@@ -267,88 +333,80 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
     tc_fence_after_sync();
     const uint32_t tmem = tmem_base_s;
 
-    const int hkv_flat = p.batch * p.hkv_per_b;
-    (void)hkv_flat;
-
     if (warp == 0) {
         // =========================== producer ===========================
         if (lane == 0) {
             tma_prefetch_desc(&mapQ4); tma_prefetch_desc(&mapK4); tma_prefetch_desc(&mapV4);
             tma_prefetch_desc(&mapQ16); tma_prefetch_desc(&mapK16); tma_prefetch_desc(&mapV16);
         }
-        uint32_t gstep = 0;
+        uint32_t gslot = 0;
         int n_item = 0;
         bool ok = true;
         for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
             const ItemInfo it = decode_item(p, item);
-            const int sb = n_item & 1;
-            uint32_t* bits = reinterpret_cast<uint32_t*>(smem + L::BITS) + sb * 128;
-            // ---- block bitsets for this item ----
-            ok = mbar_wait(smem_u32(&bars.sched_empty[sb]), ((n_item >> 1) & 1) ^ 1, abortp, budget);
+            // ---- step list (consumers must be done with the previous one) ----
+            ok = mbar_wait(smem_u32(&bars.sched_empty), (n_item & 1) ^ 1, abortp, budget);
             if (!ok) break;
-            StepIter itr;
-            init_iter(itr, p, it, bits);
-            for (int i = lane; i < 128; i += 32) bits[i] = 0u;
-            __syncwarp();
-            if (itr.has_sel) {
-                for (int half = 0; half < (itr.two ? 2 : 1); ++half) {
-                    const int32_t* list = half ? itr.list1 : itr.list0;
-                    for (int i = lane; i < p.width; i += 32) {
-                        const int id = list[i];
-                        if (id >= 0 && id < p.nkb) atomicOr(&bits[half * 64 + (id >> 5)], 1u << (id & 31));
-                    }
-                }
-            }
+            const int n = build_schedule(p, it, reinterpret_cast<uint32_t*>(smem + L::BITS), sched, lane);
+            if (n < 0) { abort_flag = 1; ok = false; break; }
+            if (lane == 0) bars.sched_n = n;
             __syncwarp();
             __threadfence_block();
-            if (lane == 0) mbar_arrive(smem_u32(&bars.sched_full[sb]));
+            if (lane == 0) mbar_arrive(smem_u32(&bars.sched_full));
+            const bool has_sel = p.width > 0;
             // ---- Q tile ----
             ok = mbar_wait(smem_u32(&bars.q_empty), (n_item & 1) ^ 1, abortp, budget);
             if (!ok) break;
             if (lane == 0) {
                 const uint32_t bar = smem_u32(&bars.q_full);
-                const uint32_t bytes = QTILE * ROW4 + QK_ATOMS * 512 + (itr.has_sel ? QTILE * D * 2 : 0);
-                mbar_expect_tx(bar, bytes);
+                mbar_expect_tx(bar, QTILE * ROW4 + QK_ATOMS * 512 + (has_sel ? QTILE * D * 2 : 0));
                 tma_load_3d(sbase + L::Q4, &mapQ4, bar, 0, it.t * QTILE, it.h);
                 bulk_load(sbase + L::QSF, p.q_sf + (static_cast<long long>(it.h) * p.n_qtiles + it.t) * QK_ATOMS * 512,
                           QK_ATOMS * 512, bar);
-                if (itr.has_sel)
+                if (has_sel)
                     for (int hf = 0; hf < HALVES; ++hf)
                         tma_load_3d(sbase + L::Q16 + hf * QTILE * 128, &mapQ16, bar, hf * 64, it.t * QTILE, it.h);
             }
             // ---- K/V steps ----
-            Step stp;
-            while (itr.next(stp, lane)) {
-                const uint32_t stage = gstep % NSTAGES;
-                ok = mbar_wait(smem_u32(&bars.kv_empty[stage]), ((gstep / NSTAGES) & 1) ^ 1, abortp, budget);
-                if (!ok) break;
-                if (lane == 0) {
-                    const uint32_t bar = smem_u32(&bars.kv_full[stage]);
-                    const uint32_t sa = sbase + L::STAGES + stage * STAGE_BYTES;
-                    if (!stp.fp16) {
+            for (int i = 0; i < n && ok; ++i) {
+                const uint32_t e = sched[i];
+                const int st = e & 0xFFF;
+                if (!(e & E_FP16)) {
+                    const uint32_t slot = gslot % NSLOTS;
+                    ok = mbar_wait(smem_u32(&bars.slot_empty[slot]), ((gslot / NSLOTS) & 1) ^ 1, abortp, budget);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        const uint32_t bar = smem_u32(&bars.slot_full[slot]);
+                        const uint32_t sa = sbase + L::SLOTS + slot * SLOT_BYTES;
                         mbar_expect_tx(bar, STEP * ROW4 + D * 32 + QK_ATOMS * 512 + 512);
-                        tma_load_3d(sa + L::K4, &mapK4, bar, 0, stp.st * STEP, it.kvh);
-                        tma_load_3d(sa + L::V4, &mapV4, bar, stp.st * (STEP / 2), 0, it.kvh);
-                        bulk_load(sa + L::KSF,
-                                  p.k_sf + (static_cast<long long>(it.kvh) * p.nsteps_total + stp.st) * QK_ATOMS * 512,
+                        tma_load_3d(sa + L::K4, &mapK4, bar, 0, st * STEP, it.kvh);
+                        tma_load_3d(sa + L::V4, &mapV4, bar, st * (STEP / 2), 0, it.kvh);
+                        bulk_load(sa + L::KSF, p.k_sf + (static_cast<long long>(it.kvh) * p.nsteps_total + st) * QK_ATOMS * 512,
                                   QK_ATOMS * 512, bar);
-                        bulk_load(sa + L::VSF, p.v_sf + (static_cast<long long>(it.kvh) * p.nsteps_total + stp.st) * 512,
-                                  512, bar);
-                    } else {
-                        mbar_expect_tx(bar, 2 * STEP * D * 2);
-                        for (int hf = 0; hf < HALVES; ++hf) {
-                            tma_load_3d(sa + L::K16 + hf * STEP * 128, &mapK16, bar, hf * 64, stp.st * STEP, it.kvh);
-                            tma_load_3d(sa + L::V16 + hf * STEP * 128, &mapV16, bar, hf * 64, stp.st * STEP, it.kvh);
+                        bulk_load(sa + L::VSF, p.v_sf + (static_cast<long long>(it.kvh) * p.nsteps_total + st) * 512, 512, bar);
+                    }
+                    gslot += 1;
+                } else {
+                    for (int which = 0; which < 2 && ok; ++which) {  // K tile, then V tile
+                        const uint32_t slot = gslot % NSLOTS;
+                        ok = mbar_wait(smem_u32(&bars.slot_empty[slot]), ((gslot / NSLOTS) & 1) ^ 1, abortp, budget);
+                        if (!ok) break;
+                        if (lane == 0) {
+                            const uint32_t bar = smem_u32(&bars.slot_full[slot]);
+                            const uint32_t sa = sbase + L::SLOTS + slot * SLOT_BYTES;
+                            mbar_expect_tx(bar, STEP * D * 2);
+                            for (int hf = 0; hf < HALVES; ++hf)
+                                tma_load_3d(sa + hf * STEP * 128, which ? &mapV16 : &mapK16, bar, hf * 64, st * STEP, it.kvh);
                         }
+                        gslot += 1;
                     }
                 }
-                ++gstep;
             }
         }
     } else if (warp == 1) {
         // =========================== MMA issuer ===========================
         if (lane == 0) tmem_cp_sf(tmem + TM_SFA_P, make_smem_desc(sbase + L::CSF, 0, 128, SWZ_NONE));
-        uint32_t gstep = 0;
+        uint32_t gstep = 0, gslot = 0;
         int n_item = 0;
         bool ok = true;
         const uint32_t idesc_qk4 = make_idesc_fp4(128, STEP, MX ? 1 : 0, 0, 0);
@@ -356,12 +414,12 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
         const uint32_t idesc_qk16 = make_idesc_f16(128, STEP, BF16 ? 1 : 0, 0, 0);
         const uint32_t idesc_pv16 = make_idesc_f16(128, D, BF16 ? 1 : 0, 0, 1);
 
-        auto issue_qk = [&](const Step& s, uint32_t g) {
-            const uint32_t stage = g % NSTAGES, buf = g & 1;
-            const uint32_t sa = sbase + L::STAGES + stage * STAGE_BYTES;
-            const uint32_t d_t = tmem + TM_S + buf * STEP;
-            if (!s.fp16) {
-                const uint32_t sfb = tmem + TM_SFB_K + buf * 8;
+        // S = Q K^T for the step described by `e`, operands in ring slot `slot` (one thread)
+        auto issue_qk = [&](uint32_t e, uint32_t slot) {
+            const uint32_t sa = sbase + L::SLOTS + slot * SLOT_BYTES;
+            const uint32_t d_t = tmem + TM_S;
+            if (!(e & E_FP16)) {
+                const uint32_t sfb = tmem + TM_SFB_K;
                 for (int a = 0; a < QK_ATOMS; ++a)
                     tmem_cp_sf(sfb + a * 4, make_smem_desc(sa + L::KSF + a * 512, 0, 128, SWZ_NONE));
                 for (int kb = 0; kb < KBLK; ++kb) {
@@ -376,88 +434,87 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t hf = ks / 4, kk = ks % 4;
                     const uint64_t ad = make_smem_desc(sbase + L::Q16 + hf * QTILE * 128 + kk * 32, 16, 1024, SWZ_128B);
-                    const uint64_t bd = make_smem_desc(sa + L::K16 + hf * STEP * 128 + kk * 32, 16, 1024, SWZ_128B);
+                    const uint64_t bd = make_smem_desc(sa + hf * STEP * 128 + kk * 32, 16, 1024, SWZ_128B);
                     mma_f16(d_t, ad, bd, idesc_qk16, ks > 0);
                 }
+                tc_commit(smem_u32(&bars.slot_empty[slot]));  // the K tile is free once S is computed
             }
-            tc_commit(smem_u32(&bars.s_full[buf]));
+            tc_commit(smem_u32(&bars.s_full));
         };
 
         for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
-            const ItemInfo it = decode_item(p, item);
-            const int sb = n_item & 1;
-            const uint32_t* bits = reinterpret_cast<const uint32_t*>(smem + L::BITS) + sb * 128;
-            ok = mbar_wait(smem_u32(&bars.sched_full[sb]), (n_item >> 1) & 1, abortp, budget);
+            ok = mbar_wait(smem_u32(&bars.sched_full), n_item & 1, abortp, budget);
             if (!ok) break;
-            StepIter itr;
-            init_iter(itr, p, it, bits);
+            const int n = bars.sched_n;
             ok = mbar_wait(smem_u32(&bars.q_full), n_item & 1, abortp, budget);
             if (!ok) break;
             tc_fence_after_sync();
             if (lane == 0)
                 for (int a = 0; a < QK_ATOMS; ++a)
                     tmem_cp_sf(tmem + TM_SFA_Q + a * 4, make_smem_desc(sbase + L::QSF + a * 512, 0, 128, SWZ_NONE));
+            if (n == 0 && lane == 0) mbar_arrive(smem_u32(&bars.q_empty));
 
-            Step cur, nxt;
-            bool have_cur = itr.next(cur, lane);
-            bool first_pv = true;
-            if (!have_cur && lane == 0) mbar_arrive(smem_u32(&bars.q_empty));
-            if (have_cur) {
-                // QK for the first step
-                const uint32_t stage = gstep % NSTAGES, buf = gstep & 1;
-                ok = mbar_wait(smem_u32(&bars.kv_full[stage]), (gstep / NSTAGES) & 1, abortp, budget) &&
-                     mbar_wait(smem_u32(&bars.s_free[buf]), ((gstep >> 1) & 1) ^ 1, abortp, budget);
+            // slot bookkeeping: an FP4 step owns one slot, a 16-bit step a K slot then a V slot
+            uint32_t qk_slot = gslot;        // slot of the step whose QK is issued next
+            if (n > 0) {
+                const uint32_t e0 = sched[0];
+                ok = mbar_wait(smem_u32(&bars.slot_full[qk_slot % NSLOTS]), (qk_slot / NSLOTS) & 1, abortp, budget) &&
+                     mbar_wait(smem_u32(&bars.s_free), (gstep & 1) ^ 1, abortp, budget);
                 if (ok) {
                     tc_fence_after_sync();
-                    if (lane == 0) issue_qk(cur, gstep);
+                    if (lane == 0) issue_qk(e0, qk_slot % NSLOTS);
                     __syncwarp();
                 }
             }
-            while (have_cur && ok) {
-                const bool have_nxt = itr.next(nxt, lane);
-                if (have_nxt) {
-                    const uint32_t g1 = gstep + 1;
-                    const uint32_t stage = g1 % NSTAGES, buf = g1 & 1;
-                    ok = mbar_wait(smem_u32(&bars.kv_full[stage]), (g1 / NSTAGES) & 1, abortp, budget) &&
-                         mbar_wait(smem_u32(&bars.s_free[buf]), ((g1 >> 1) & 1) ^ 1, abortp, budget);
+            for (int i = 0; i < n && ok; ++i) {
+                const uint32_t e = sched[i];
+                const bool fp16 = e & E_FP16;
+                const uint32_t my_slot = qk_slot;                 // FP4: the step's slot; 16-bit: its K slot
+                const uint32_t pv_slot = fp16 ? my_slot + 1 : my_slot;
+                qk_slot = pv_slot + 1;
+                // look ahead: S of the next step as soon as the softmax warps have read this one
+                if (i + 1 < n) {
+                    const uint32_t e1 = sched[i + 1];
+                    ok = mbar_wait(smem_u32(&bars.slot_full[qk_slot % NSLOTS]), (qk_slot / NSLOTS) & 1, abortp, budget) &&
+                         mbar_wait(smem_u32(&bars.s_free), ((gstep + 1) & 1) ^ 1, abortp, budget);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    if (lane == 0) issue_qk(nxt, g1);
+                    if (lane == 0) issue_qk(e1, qk_slot % NSLOTS);
                     __syncwarp();
                 }
-                // PV for the current step
-                ok = mbar_wait(smem_u32(&bars.p_full[gstep & 1]), (gstep >> 1) & 1, abortp, budget);
+                // O += P V for the current step
+                const uint32_t buf = gstep & 1;
+                ok = mbar_wait(smem_u32(&bars.p_full[buf]), (gstep >> 1) & 1, abortp, budget);
+                if (ok && fp16) ok = mbar_wait(smem_u32(&bars.slot_full[pv_slot % NSLOTS]), (pv_slot / NSLOTS) & 1, abortp, budget);
                 if (!ok) break;
                 tc_fence_after_sync();
                 if (lane == 0) {
-                    const uint32_t stage = gstep % NSTAGES, buf = gstep & 1;
-                    const uint32_t sa = sbase + L::STAGES + stage * STAGE_BYTES;
+                    const uint32_t sa = sbase + L::SLOTS + (pv_slot % NSLOTS) * SLOT_BYTES;
                     const uint32_t d_t = tmem + TM_O;
-                    if (!cur.fp16) {
+                    const uint32_t acc = i > 0 ? 1u : 0u;
+                    if (!fp16) {
                         const uint32_t sfb = tmem + TM_SFB_V + buf * 4;
                         tmem_cp_sf(sfb, make_smem_desc(sa + L::VSF, 0, 128, SWZ_NONE));
-                        const uint64_t ad = make_smem_desc(sbase + L::P + buf * 16384, 16, 256, SWZ_32B);
+                        const uint64_t ad = make_smem_desc(sbase + L::P + buf * 4096, 16, 256, SWZ_32B);
                         const uint64_t bd = make_smem_desc(sa + L::V4, 16, 256, SWZ_32B);
-                        if constexpr (MX) mma_mxfp4(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, first_pv ? 0 : 1);
-                        else mma_nvfp4(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, first_pv ? 0 : 1);
+                        if constexpr (MX) mma_mxfp4(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
+                        else mma_nvfp4(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
                     } else {
                         for (int ks = 0; ks < STEP / 16; ++ks) {
-                            const uint64_t ad = make_smem_desc(sbase + L::P + buf * 16384 + ks * 32, 16, 1024, SWZ_128B);
-                            const uint64_t bd = make_smem_desc(sa + L::V16 + ks * 2048, STEP * 128, 1024, SWZ_128B);
-                            mma_f16(d_t, ad, bd, idesc_pv16, (first_pv && ks == 0) ? 0 : 1);
+                            const uint64_t ad = make_smem_desc(sbase + L::P + ks * 32, 16, 1024, SWZ_128B);
+                            const uint64_t bd = make_smem_desc(sa + ks * 2048, STEP * 128, 1024, SWZ_128B);
+                            mma_f16(d_t, ad, bd, idesc_pv16, (acc == 0 && ks == 0) ? 0 : 1);
                         }
                     }
-                    tc_commit(smem_u32(&bars.kv_empty[stage]));
+                    tc_commit(smem_u32(&bars.slot_empty[pv_slot % NSLOTS]));
                     tc_commit(smem_u32(&bars.p_free[buf]));
-                    if (!have_nxt) tc_commit(smem_u32(&bars.q_empty));
+                    if (i + 1 == n) tc_commit(smem_u32(&bars.q_empty));
                 }
                 __syncwarp();
-                first_pv = false;
                 ++gstep;
-                cur = nxt;
-                have_cur = have_nxt;
             }
-            if (lane == 0) mbar_arrive(smem_u32(&bars.sched_empty[sb]));
+            gslot = qk_slot;
+            if (lane == 0) mbar_arrive(smem_u32(&bars.sched_empty));
         }
     } else {
         // =========================== softmax ===========================
@@ -468,38 +525,39 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
         uint32_t gstep = 0;
         int n_item = 0;
         bool ok = true;
+        bool prev_fp16 = false;                   // kind of the previous step (across items)
+        TA100_PROF_DECL
         for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
             const ItemInfo it = decode_item(p, item);
-            const int sb = n_item & 1;
-            const uint32_t* bits = reinterpret_cast<const uint32_t*>(smem + L::BITS) + sb * 128;
-            ok = mbar_wait(smem_u32(&bars.sched_full[sb]), (n_item >> 1) & 1, abortp, budget);
+            ok = mbar_wait(smem_u32(&bars.sched_full), n_item & 1, abortp, budget);
             if (!ok) break;
-            StepIter itr;
-            init_iter(itr, p, it, bits);
+            const int n = bars.sched_n;
             const int grow = it.t * QTILE + row;  // absolute query row
             float m_run = -FLT_MAX, l_run = 0.0f;
-            int n_done = 0;
-            bool prev_fp4 = false;
-            Step stp;
-            while (itr.next(stp, lane)) {
-                const uint32_t buf = gstep & 1;
-                ok = mbar_wait(smem_u32(&bars.s_full[buf]), (gstep >> 1) & 1, abortp, budget);
+            TA100_PROF(9)
+            for (int i = 0; i < n; ++i) {
+                const uint32_t e = sched[i];
+                const bool fp16 = e & E_FP16;
+                const int col0 = (e & 0xFFF) * STEP;
+                const bool part = e & (half ? E_P1 : E_P0);
+                TA100_PROF(0)
+                ok = mbar_wait(smem_u32(&bars.s_full), gstep & 1, abortp, budget);
                 if (!ok) break;
                 tc_fence_after_sync();
+                TA100_PROF(1)
                 float s[STEP];
                 {
                     uint32_t r0[32], r1[32];
-                    tmem_ld32(tmem + lane_addr + TM_S + buf * STEP, r0);
-                    tmem_ld32(tmem + lane_addr + TM_S + buf * STEP + 32, r1);
+                    tmem_ld32(tmem + lane_addr + TM_S, r0);
+                    tmem_ld32(tmem + lane_addr + TM_S + 32, r1);
                     tmem_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) { s[j] = __uint_as_float(r0[j]); s[32 + j] = __uint_as_float(r1[j]); }
                 }
                 tc_fence_before_sync();
-                mbar_arrive(smem_u32(&bars.s_free[buf]));
+                mbar_arrive(smem_u32(&bars.s_free));
+                TA100_PROF(2)
 
-                const bool part = half ? stp.p1 : stp.p0;
-                const int col0 = stp.st * STEP;
                 float rescale = 1.0f;
                 bool changed = false;
                 float mneg = 0.0f;
@@ -507,33 +565,41 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                     if (CAUSAL && (col0 + STEP - 1 > grow)) {
 #pragma unroll
                         for (int j = 0; j < STEP; ++j) {
-                            const int lc = stp.fp16 ? j : cmap.logi[j];
+                            const int lc = fp16 ? j : cmap.logi[j];
                             if (col0 + lc > grow) s[j] = -INFINITY;
                         }
                     }
-                    float mx = -FLT_MAX;
+                    float mx0 = -FLT_MAX, mx1 = -FLT_MAX, mx2 = -FLT_MAX, mx3 = -FLT_MAX;
 #pragma unroll
-                    for (int j = 0; j < STEP; ++j) mx = fmaxf(mx, s[j]);
-                    const float m_new = fmaxf(m_run, mx);
+                    for (int j = 0; j < STEP; j += 8) {
+                        mx0 = max3(mx0, s[j], s[j + 1]);
+                        mx1 = max3(mx1, s[j + 2], s[j + 3]);
+                        mx2 = max3(mx2, s[j + 4], s[j + 5]);
+                        mx3 = max3(mx3, s[j + 6], s[j + 7]);
+                    }
+                    const float m_new = max3(m_run, fmaxf(mx0, mx1), fmaxf(mx2, mx3));
                     changed = m_new > m_run;
                     rescale = ex2((m_run - m_new) * p.c2);
                     m_run = m_new;
                     mneg = -m_new * p.c2;
                 }
-                // the PV that last read this P buffer (two steps ago) must be complete
+                TA100_PROF(3)
+                const uint32_t buf = gstep & 1;
+                // the PV that last read this P buffer must be complete: two steps ago for the FP4
+                // double buffer; the previous step whenever a 16-bit P tile (which spans the
+                // whole P region) is involved
                 ok = mbar_wait(smem_u32(&bars.p_free[buf]), ((gstep >> 1) & 1) ^ 1, abortp, budget);
                 if (!ok) break;
-                // state rounding between the FP4 and the 16-bit phase
-                const bool transition = stp.fp16 && prev_fp4 && p.round_partial;
-                const bool need_rescale = __any_sync(0xFFFFFFFFu, changed && n_done > 0);
-                if (transition || need_rescale) {
-                    // O is about to be modified: the previous PV (step gstep-1, which
-                    // signals the other P buffer's barrier) must be complete
+                const bool transition = fp16 && i > 0 && !prev_fp16 && p.round_partial;
+                const bool need_rescale = __any_sync(0xFFFFFFFFu, changed && i > 0);
+                if ((transition || need_rescale || fp16 || prev_fp16) && gstep > 0) {
                     ok = mbar_wait(smem_u32(&bars.p_free[(gstep - 1) & 1]), ((gstep - 1) >> 1) & 1, abortp, budget);
                     if (!ok) break;
-                    tc_fence_after_sync();
                 }
+                tc_fence_after_sync();
+                TA100_PROF(4)
                 if (transition) {
+                    // state rounding between the FP4 and the 16-bit phase
                     const float norm = l_run > 0.0f ? __fdiv_rn(CSCALE_INV, l_run) : 0.0f;
                     const float back = l_run * CSCALE;
 #pragma unroll 1
@@ -552,80 +618,78 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                 }
                 if (need_rescale) {
 #pragma unroll 1
-                    for (int c = 0; c < D; c += 32) {
-                        uint32_t r[32];
-                        tmem_ld32(tmem + lane_addr + TM_O + c, r);
+                    for (int c = 0; c < D; c += 64) {
+                        uint32_t ra[32], rb[32];
+                        tmem_ld32(tmem + lane_addr + TM_O + c, ra);
+                        tmem_ld32(tmem + lane_addr + TM_O + c + 32, rb);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rescale);
-                        tmem_st32(tmem + lane_addr + TM_O + c, r);
+                        for (int j = 0; j < 32; ++j) {
+                            ra[j] = __float_as_uint(__uint_as_float(ra[j]) * rescale);
+                            rb[j] = __float_as_uint(__uint_as_float(rb[j]) * rescale);
+                        }
+                        tmem_st32(tmem + lane_addr + TM_O + c, ra);
+                        tmem_st32(tmem + lane_addr + TM_O + c + 32, rb);
                     }
                     tmem_wait_st();
                 }
+                TA100_PROF(5)
                 // probabilities, row sum, P tile
-                uint8_t* prow = smem + L::P + buf * 16384;
-                if (!stp.fp16) {
+                if (!fp16) {
                     uint32_t w[STEP / 8];
                     if (part) {
-                        float sum = 0.0f;
+                        // 6 p = 2^(s c2 - m c2 + log2 6): the e2m1 input directly
+                        const float sum6 = exp_scaled_64(s, p.c2, mneg + 2.5849625007211562f);
+                        l_run = fmaf(sum6, 1.0f / 6.0f, l_run * rescale);
 #pragma unroll
-                        for (int j = 0; j < STEP; ++j) {
-                            s[j] = ex2(fmaf(s[j], p.c2, mneg));
-                            sum += s[j];
-                        }
-                        l_run = l_run * rescale + sum;
-#pragma unroll
-                        for (int g = 0; g < STEP / 8; ++g) {
-                            float v[8];
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) v[e] = s[cmap.phys[g * 8 + e]] * 6.0f;
-                            w[g] = e2m1x8(v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7]);
-                        }
+                        for (int g = 0; g < STEP / 8; ++g)
+                            w[g] = e2m1x8(s[cmap.phys[g * 8 + 0]], s[cmap.phys[g * 8 + 1]], s[cmap.phys[g * 8 + 2]],
+                                          s[cmap.phys[g * 8 + 3]], s[cmap.phys[g * 8 + 4]], s[cmap.phys[g * 8 + 5]],
+                                          s[cmap.phys[g * 8 + 6]], s[cmap.phys[g * 8 + 7]]);
                     } else {
 #pragma unroll
                         for (int g = 0; g < STEP / 8; ++g) w[g] = 0u;
                     }
-                    // 128 rows x 32 bytes, 32-byte swizzle
+                    // 128 rows x 32 bytes, 32-byte swizzle; FP4 steps alternate between two 4 KB buffers
                     const uint32_t r8 = row & 7;
-                    uint8_t* base = prow + (row >> 3) * 256 + r8 * 32;
+                    uint8_t* base = smem + L::P + buf * 4096 + (row >> 3) * 256 + r8 * 32;
                     const uint32_t x = (r8 >> 2) & 1;
                     *reinterpret_cast<uint4*>(base + ((0 ^ x) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
                     *reinterpret_cast<uint4*>(base + ((1 ^ x) * 16)) = make_uint4(w[4], w[5], w[6], w[7]);
                 } else {
                     uint32_t w[STEP / 2];
                     if (part) {
-                        float sum = 0.0f;
+                        // C p = 2^(s c2 - m c2 + log2 C): the 16-bit P operand directly
+                        constexpr float LOG2_C = MX ? 2.5849625007211562f : 11.392317422778761f;
+                        const float sum_c = exp_scaled_64(s, p.c2, mneg + LOG2_C);
+                        l_run = fmaf(sum_c, CSCALE_INV, l_run * rescale);
 #pragma unroll
-                        for (int j = 0; j < STEP; ++j) {
-                            s[j] = ex2(fmaf(s[j], p.c2, mneg));
-                            sum += s[j];
-                        }
-                        l_run = l_run * rescale + sum;
-#pragma unroll
-                        for (int j = 0; j < STEP / 2; ++j) w[j] = In16<BF16>::pack2(s[2 * j] * CSCALE, s[2 * j + 1] * CSCALE);
+                        for (int j = 0; j < STEP / 2; ++j) w[j] = In16<BF16>::pack2(s[2 * j], s[2 * j + 1]);
                     } else {
 #pragma unroll
                         for (int j = 0; j < STEP / 2; ++j) w[j] = 0u;
                     }
-                    // 128 rows x 128 bytes, 128-byte swizzle
+                    // 128 rows x 128 bytes, 128-byte swizzle; one buffer for 16-bit steps
                     const uint32_t r8 = row & 7;
-                    uint8_t* base = prow + (row >> 3) * 1024 + r8 * 128;
+                    uint8_t* base = smem + L::P + (row >> 3) * 1024 + r8 * 128;
 #pragma unroll
                     for (int c = 0; c < 8; ++c)
                         *reinterpret_cast<uint4*>(base + ((c ^ r8) * 16)) =
                             make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
                 }
+                TA100_PROF(6)
                 fence_proxy_async_smem();
                 tc_fence_before_sync();
                 mbar_arrive(smem_u32(&bars.p_full[buf]));
-                prev_fp4 = !stp.fp16;
-                ++n_done;
+                TA100_PROF(7)
+                TA100_PROF_STEP
+                prev_fp16 = fp16;
                 ++gstep;
             }
             if (!ok) break;
             // ---- epilogue ----
             uint16_t* orow = p.out + (static_cast<long long>(it.h) * p.sq + grow) * D;
-            if (n_done > 0) {
+            if (n > 0) {
                 ok = mbar_wait(smem_u32(&bars.p_free[(gstep - 1) & 1]), ((gstep - 1) >> 1) & 1, abortp, budget);
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -640,9 +704,9 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                         for (int v4 = 0; v4 < 4; ++v4) {
                             uint32_t o[4];
 #pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                o[e] = In16<BF16>::pack2(__uint_as_float(r[v4 * 8 + 2 * e]) * norm,
-                                                         __uint_as_float(r[v4 * 8 + 2 * e + 1]) * norm);
+                            for (int e2 = 0; e2 < 4; ++e2)
+                                o[e2] = In16<BF16>::pack2(__uint_as_float(r[v4 * 8 + 2 * e2]) * norm,
+                                                          __uint_as_float(r[v4 * 8 + 2 * e2 + 1]) * norm);
                             *reinterpret_cast<uint4*>(orow + c + v4 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
                         }
                     }
@@ -652,8 +716,10 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                 for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars.sched_empty[sb]));
+            if (lane == 0) mbar_arrive(smem_u32(&bars.sched_empty));
+            TA100_PROF(8)
         }
+        TA100_PROF_DUMP
     }
 
     // ---- common exit ----
@@ -732,8 +798,10 @@ WsLayout ws_layout(int hq_flat, int hkv_flat, int sq, int skv, int d, int is_mx)
 template <int D, bool MX, bool BF16, bool CAUSAL, bool KPERM>
 int launch_prefill_t(const PrefillParams& p, const CUtensorMap* maps, int grid, cudaStream_t stream) {
     auto kern = prefill_kernel<D, MX, BF16, CAUSAL, KPERM>;
-    const int smem = Smem<D>::TOTAL + 1024;
+    const int smem = Smem<D>::TOTAL;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (e != cudaSuccess) return static_cast<int>(e);
     kern<<<grid, NUM_THREADS, smem, stream>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);
     return static_cast<int>(cudaGetLastError());
@@ -845,7 +913,7 @@ int prefill_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const
     int dev = 0, sms = NUM_SMS_HINT;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int grid = p.n_items < sms ? p.n_items : sms;
+    int grid = p.n_items < 2 * sms ? p.n_items : 2 * sms;
     if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
 
 #define TA100_PF(MXX, BFF, CC, KP) launch_prefill_t<128, MXX, BFF, CC, KP>(p, maps, grid, stream)
@@ -859,6 +927,12 @@ int prefill_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const
 #undef TA100_PF
     return rc;
 }
+
+#ifdef TA100_PROFILE_SOFTMAX
+int prefill_profile_read(long long* out16) {
+    return static_cast<int>(cudaMemcpyFromSymbol(out16, g_prof, sizeof(long long) * 16));
+}
+#endif
 
 // Reads back the device status word written by the last prefill launch that
 // used `workspace` (synchronises the stream).
