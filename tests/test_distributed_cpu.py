@@ -1,0 +1,100 @@
+"""Host-side logic of the multi-GPU paths, run as two gloo ranks on CPU: partition plans,
+output gather, candidate exchange + deterministic global top-k, partial exchange."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from thriftattention_b200 import distributed as tad
+
+
+def test_head_shard_plan():
+    shards = tad.plan_head_shards(32, 8, 4)
+    assert [(s.kv_begin, s.kv_end, s.q_begin, s.q_end) for s in shards] == [(0, 2, 0, 8), (2, 4, 8, 16), (4, 6, 16, 24), (6, 8, 24, 32)]
+    with pytest.raises(ValueError):
+        tad.plan_head_shards(32, 8, 3)
+    q, k, v = torch.arange(32).view(1, 32, 1, 1), torch.arange(8).view(1, 8, 1, 1), torch.arange(8).view(1, 8, 1, 1)
+    ql, kl, _ = tad.shard_heads(q, k, v, shards[2])
+    assert ql.flatten().tolist() == list(range(16, 24)) and kl.flatten().tolist() == [4, 5]
+
+
+def test_page_shard_plan_covers_every_page_once():
+    for n, w in ((2048, 8), (2047, 4), (5, 8), (64, 1)):
+        shards = tad.plan_page_shards(n, w)
+        assert shards[0].page_begin == 0 and shards[-1].page_end == n
+        assert all(a.page_end == b.page_begin for a, b in zip(shards, shards[1:]))
+        assert sum(s.num_pages for s in shards) == n
+
+
+def test_merge_topk_candidates_matches_global_topk_and_kernel_tie_order():
+    g = torch.Generator().manual_seed(0)
+    scores = torch.randn(6, 256, generator=g)
+    pages = torch.arange(256, dtype=torch.int32).repeat(6, 1)
+    # per-shard top-k then merge == global top-k
+    k = 9
+    parts_s, parts_p = [], []
+    for sh in tad.plan_page_shards(256, 4):
+        t = torch.topk(scores[:, sh.page_begin:sh.page_end], k, dim=1)
+        parts_s.append(t.values)
+        parts_p.append((t.indices + sh.page_begin).to(torch.int32))
+    merged = tad.merge_topk_candidates(torch.cat(parts_s, 1), torch.cat(parts_p, 1), k)
+    assert torch.equal(merged.long(), torch.topk(scores, k, dim=1).indices)
+    # exact ties: smallest bit-reversed (page mod 32) first, then the smaller page
+    s = torch.zeros(1, 64)
+    p = torch.arange(64, dtype=torch.int32).view(1, 64)
+    assert tad.merge_topk_candidates(s, p, 6).tolist() == [[0, 32, 16, 48, 8, 40]]
+    # padding entries never win
+    p2 = p.clone(); p2[0, :60] = -1
+    assert sorted(tad.merge_topk_candidates(s, p2, 6).tolist()[0]) == [-1, -1, 60, 61, 62, 63]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # output gather: rank r holds heads [2r, 2r+2)
+        local = torch.full((1, 2, 3, 4), float(rank)) + torch.arange(2).view(1, 2, 1, 1) * 0.5
+        full = tad.gather_heads(local)
+        ok1 = full.shape == (1, 4, 3, 4) and full[0, :, 0, 0].tolist() == [0.0, 0.5, 1.0, 1.5]
+        # candidate exchange + global selection is identical on both ranks and equals the global top-k
+        g = torch.Generator().manual_seed(7)
+        scores = torch.randn(3, 40, generator=g)
+        sh = tad.plan_page_shards(40, world)[rank]
+        t = torch.topk(scores[:, sh.page_begin:sh.page_end], 5, dim=1)
+        s_all, p_all = tad.exchange_candidates(t.values.contiguous(), (t.indices + sh.page_begin).to(torch.int32).contiguous())
+        sel = tad.merge_topk_candidates(s_all, p_all, 5)
+        ok2 = torch.equal(sel.long(), torch.topk(scores, 5, dim=1).indices)
+        # partial exchange keeps shard order
+        po = torch.full((2, 1, 4, 8), float(rank))
+        pml = torch.full((2, 1, 4, 2), float(rank))
+        ao, aml = tad.exchange_partials(po, pml)
+        ok3 = ao.shape == (world, 2, 1, 4, 8) and ao[:, 0, 0, 0, 0].tolist() == [0.0, 1.0] and aml.shape == (world, 2, 1, 4, 2)
+        q.put((rank, bool(ok1), bool(ok2), bool(ok3)))
+    except Exception as exc:  # report instead of leaving the parent waiting
+        q.put((rank, repr(exc), False, False))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_exchange_over_gloo():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=90) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(results) == [(0, True, True, True), (1, True, True, True)]

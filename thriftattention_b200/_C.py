@@ -397,7 +397,8 @@ def decode_pick_splits(flat_kv_heads: int, num_pages: int) -> int:
 
 
 def decode_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, *,
-                     is_mx, is_bf16=False, num_splits=0, kv_len=None, page_table=None, return_partials=False):
+                     is_mx, is_bf16=False, num_splits=0, kv_len=None, page_table=None, return_partials=False,
+                     allow_padded_selection=False):
     """Split-KV decode attention over 64-token pages.
 
     q_* are grouped: [B, Hkv, G, ...] with G <= 8 query heads per KV head.  K/V are either the
@@ -437,7 +438,10 @@ def decode_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_pa
         _check(selected_blocks.dim() == 2, "selected_blocks must be [batch * grouped_heads, top_k]")
         _check(selected_blocks.size(0) == b * hkv, "selected_blocks first dimension must equal batch * grouped_heads")
         width = selected_blocks.size(1)
-        _check(0 <= width <= npages, "selected block count must be in [0, number of KV blocks]")
+        # a shard of a longer sequence may receive a list wider than its own page count (entries of other
+        # shards are -1)
+        _check(allow_padded_selection or 0 <= width <= npages,
+               "selected block count must be in [0, number of KV blocks]")
         if width:
             _check(q_hi is not None and q_hi.shape == (b, hkv, g, d), "q_hi shape must match packed Q")
             _check(q_hi.is_contiguous() and k_hi.is_contiguous() and v_hi.is_contiguous(), "Q/K/V must be contiguous")

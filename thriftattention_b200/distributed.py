@@ -1,0 +1,207 @@
+"""Multi-GPU partitioning of the attention path (one process per GPU, ``torch.distributed``).
+
+The reference has no distributed code; these are the two decompositions the path admits:
+
+* prefill — KV-head groups are independent (statistics, selection, quantisation and attention of
+  one KV head and its query heads never look at another group), so ranks take whole groups and
+  the only collective is an optional ``all_gather`` of the outputs;
+* decode — the KV sequence is split into contiguous page ranges, one per rank.  Each rank scores
+  its own pages, the ranks exchange their local top-k candidates (a global top-k element is always
+  inside its shard's top-k), every rank derives the same global selection, runs the split-KV kernel
+  over its pages and contributes un-normalised partials ``(o, m, l)``; after an ``all_gather`` the
+  log-sum-exp merge kernel produces the output on every rank.
+
+The planning helpers are pure Python / device-agnostic tensor code so that they can be exercised
+with the ``gloo`` backend on CPU; the kernels themselves need a GPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+def _all_gather_stack(x: torch.Tensor, group=None) -> torch.Tensor:
+    """``all_gather`` of equally shaped tensors, stacked on a new leading rank dimension."""
+    world = dist.get_world_size(group)
+    x = x.contiguous()
+    flat = torch.empty((world * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(flat, x, group=group)
+    return flat.view((world,) + tuple(x.shape))
+
+
+# --------------------------------------------------------------------------------------------- prefill
+@dataclass(frozen=True)
+class HeadShard:
+    """Heads owned by one rank: KV heads [kv_begin, kv_end) and their query heads."""
+
+    rank: int
+    world: int
+    kv_begin: int
+    kv_end: int
+    q_begin: int
+    q_end: int
+
+
+def plan_head_shards(num_q_heads: int, num_kv_heads: int, world: int) -> list[HeadShard]:
+    """Contiguous, balanced split of the KV-head groups over ``world`` ranks."""
+    if num_q_heads % num_kv_heads:
+        raise ValueError("q heads must be divisible by KV heads")
+    if world < 1 or num_kv_heads % world:
+        raise ValueError(f"the number of ranks ({world}) must divide the number of KV heads ({num_kv_heads})")
+    group = num_q_heads // num_kv_heads
+    per = num_kv_heads // world
+    return [HeadShard(r, world, r * per, (r + 1) * per, r * per * group, (r + 1) * per * group) for r in range(world)]
+
+
+def shard_heads(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, shard: HeadShard):
+    """Slices of full ``[B,H,S,D]`` tensors owned by ``shard`` (views, no copy)."""
+    return (q[:, shard.q_begin:shard.q_end], k[:, shard.kv_begin:shard.kv_end], v[:, shard.kv_begin:shard.kv_end])
+
+
+def gather_heads(local_out: torch.Tensor, group=None) -> torch.Tensor:
+    """``all_gather`` of per-rank outputs ``[B, Hq/N, S, D]`` into ``[B, Hq, S, D]`` (rank order = head order)."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return local_out
+    buf = _all_gather_stack(local_out, group)
+    b, h, s, d = local_out.shape
+    return buf.permute(1, 0, 2, 3, 4).reshape(b, world * h, s, d)
+
+
+def attention_head_sharded(q, k, v, *, config=None, group=None, gather: bool = True):
+    """``attention`` on this rank's KV-head groups of replicated (or pre-sliced) inputs.
+
+    ``q, k, v`` are the FULL tensors; each rank computes its slice.  With ``gather`` the full
+    output is returned on every rank, otherwise the local slice.
+    """
+    from thriftattention_b200.functional import attention
+
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    shard = plan_head_shards(q.shape[1], k.shape[1], world)[rank]
+    ql, kl, vl = shard_heads(q, k, v, shard)
+    out = attention(ql.contiguous(), kl.contiguous(), vl.contiguous(), config=config)
+    return gather_heads(out, group) if (gather and world > 1) else out
+
+
+# --------------------------------------------------------------------------------------------- decode
+@dataclass(frozen=True)
+class PageShard:
+    """Pages (64-token blocks) of every sequence owned by one rank: [page_begin, page_end)."""
+
+    rank: int
+    world: int
+    page_begin: int
+    page_end: int
+
+    @property
+    def num_pages(self) -> int:
+        return self.page_end - self.page_begin
+
+
+def plan_page_shards(num_pages: int, world: int) -> list[PageShard]:
+    """Contiguous split of ``num_pages`` pages; the same rule as the in-kernel chains
+    (shard r covers [r*n/N, (r+1)*n/N))."""
+    if world < 1:
+        raise ValueError("world must be positive")
+    return [PageShard(r, world, r * num_pages // world, (r + 1) * num_pages // world) for r in range(world)]
+
+
+def _bitrev5(x: torch.Tensor) -> torch.Tensor:
+    r = torch.zeros_like(x)
+    for i in range(5):
+        r |= ((x >> i) & 1) << (4 - i)
+    return r
+
+
+def merge_topk_candidates(scores: torch.Tensor, pages: torch.Tensor, k: int) -> torch.Tensor:
+    """Global top-k from gathered per-shard candidates.
+
+    ``scores`` / ``pages``: ``[rows, n_candidates]`` (fp32 scores, global page ids, -1 for padding).
+    Returns int32 ``[rows, k]`` in rank order.  Ties are broken the way the selection kernel breaks
+    them on a single GPU: smallest 5-bit bit-reversal of ``page mod 32``, then smallest ``page div 32``
+    — so every rank derives the same list, equal to the single-GPU result.
+    """
+    valid = pages >= 0
+    s = torch.where(valid, scores, torch.full_like(scores, float("-inf")))
+    pg = pages.to(torch.int64)
+    tie = _bitrev5(pg & 31) * 65536 + (pg >> 5)
+    # sort by (score desc, tie asc): stable sort on the secondary key first, then on the primary
+    order = torch.argsort(tie, dim=1, stable=True)
+    s_sorted = torch.gather(s, 1, order)
+    order2 = torch.argsort(s_sorted, dim=1, descending=True, stable=True)
+    final = torch.gather(order, 1, order2)[:, :k]
+    out = torch.gather(pages, 1, final).to(torch.int32)
+    ok = torch.gather(valid, 1, final)
+    return torch.where(ok, out, torch.full_like(out, -1))
+
+
+def exchange_candidates(local_scores: torch.Tensor, local_pages: torch.Tensor, group=None):
+    """``all_gather`` of per-rank candidate lists ``[rows, c]`` -> ``[rows, world*c]`` (scores, pages)."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return local_scores, local_pages
+    s_buf = _all_gather_stack(local_scores, group)
+    p_buf = _all_gather_stack(local_pages, group)
+    rows = local_scores.shape[0]
+    return s_buf.permute(1, 0, 2).reshape(rows, -1), p_buf.permute(1, 0, 2).reshape(rows, -1)
+
+
+def exchange_partials(part_o: torch.Tensor, part_ml: torch.Tensor, group=None):
+    """``all_gather`` of decode partials -> ``[world, heads, splits, G, D]`` and ``[world, heads, splits, G, 2]``."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return part_o.unsqueeze(0), part_ml.unsqueeze(0)
+    return _all_gather_stack(part_o, group), _all_gather_stack(part_ml, group)
+
+
+def quest_page_scores(q_grouped: torch.Tensor, k_min: torch.Tensor, k_max: torch.Tensor) -> torch.Tensor:
+    """Quest upper-bound score of every local page, max over the grouped query heads:
+    ``[B*Hkv, pages]`` fp32 (tensor code; used only to rank this shard's candidates for the exchange)."""
+    qf = q_grouped.float().unsqueeze(3)                                   # [B,Hkv,G,1,D]
+    bound = torch.where(qf >= 0, k_max.float().unsqueeze(2), k_min.float().unsqueeze(2))
+    s = (qf * bound).sum(-1).amax(dim=2)                                  # [B,Hkv,pages]
+    return s.reshape(-1, s.shape[-1])
+
+
+def decode_kv_sharded(q, k_local, v_local, *, shard: PageShard, total_pages: int, top_k: int, quant_format="nvfp4",
+                      num_splits: int = 0, group=None):
+    """One decode step with the KV sequence sharded over ranks.
+
+    ``q`` ``[B, Hq, 1, D]`` replicated; ``k_local`` / ``v_local`` ``[B, Hkv, shard.num_pages*64, D]`` are this
+    rank's slice of the cache.  Quest selection of ``top_k`` pages over the WHOLE sequence, mixed attention
+    over the local pages, LSE merge across ranks.  Returns ``[B, Hq, 1, D]`` on every rank.
+    """
+    from thriftattention_b200._extension import get_extension
+
+    ext = get_extension()
+    is_bf16 = q.dtype == torch.bfloat16
+    is_mx = quant_format == "mxfp4"
+    b, hq, _, d = q.shape
+    hkv = k_local.shape[1]
+    q_grouped = q.reshape(b, hkv, hq // hkv, d).contiguous()
+    n_local = shard.num_pages
+    # 1. local page statistics and scores, 2. candidate exchange, 3. identical global selection everywhere
+    _, k_min, k_max = ext.block_stats(k_local.contiguous(), 64, minmax=True)
+    scores = quest_page_scores(q_grouped, k_min, k_max)
+    c = min(top_k, n_local)
+    top = torch.topk(scores, c, dim=1)
+    cand_pages = (top.indices + shard.page_begin).to(torch.int32)
+    all_s, all_p = exchange_candidates(top.values.contiguous(), cand_pages.contiguous(), group)
+    global_sel = merge_topk_candidates(all_s, all_p, min(top_k, total_pages))
+    mine = (global_sel >= shard.page_begin) & (global_sel < shard.page_end)
+    local_sel = torch.where(mine, global_sel - shard.page_begin, torch.full_like(global_sel, -1)).contiguous()
+    # 4. local split-KV attention -> partials, 5. exchange + merge
+    quant = getattr(ext, f"{quant_format}_quantize")
+    quant_t = getattr(ext, f"{quant_format}_quantize_transposed")
+    q4, qs = quant(q_grouped, is_bf16)
+    k4, ks = quant(k_local.contiguous(), is_bf16)
+    v4, vs = quant_t(v_local.contiguous(), is_bf16)
+    _, part_o, part_ml = ext.decode_attention(q_grouped, k_local.contiguous(), v_local.contiguous(), local_sel, q4, k4,
+                                              v4, qs, ks, vs, is_mx=is_mx, is_bf16=is_bf16, num_splits=num_splits,
+                                              return_partials=True, allow_padded_selection=True)
+    all_o, all_ml = exchange_partials(part_o, part_ml, group)
+    out = ext.merge_decode_partials(all_o.contiguous(), all_ml.contiguous(), is_mx=is_mx, is_bf16=is_bf16)
+    return out.reshape(b, hq, 1, d)
