@@ -68,6 +68,29 @@ int ta100_block_stats(const void* x, void* mean, void* mn, void* mx, long long h
                       int is_bf16, void* stream);
 
 /*
+ * Fused KV-cache append: one launch stores count new 16-bit K and V rows at token positions
+ * [start, start + count) of a capacity-strided cache and brings every derived tensor up to date.
+ *   k_new, v_new   [heads, k_count | v_count, D] 16-bit, contiguous; NULL = zero rows, or with
+ *                  flags bit 0 (K) / bit 1 (V) = keep the cached rows and only re-quantise them
+ *   k_hi, v_hi     [heads, capacity, D] 16-bit caches
+ *   k_codes/k_scales   [heads, capacity, D/2] / [heads, capacity, D/G]   (plain row layout)
+ *   v_codes_t/v_scales_t [heads, D, capacity/2] / [heads, D, capacity/G] (groups along tokens);
+ *                  every G-token group touched by [start, start + v_count) is re-quantised, its
+ *                  other tokens being read from v_hi
+ *   k_mean, k_min, k_max [heads, capacity/stat_block, D] 16-bit, each may be NULL; refreshed for
+ *                  the statistics blocks that [start, start + k_count) completes
+ * capacity must be a multiple of 128; stat_block 64 or 128; G = 16 (NVFP4) or 32 (MXFP4).
+ * Replaces ThriftAttentionCacheLayer.update and its helpers _quantize_k_range,
+ * _quantize_v_range and _refresh_k_means
+ * (src/thriftattention/integrations/transformers_cache.py:87-123, 308-351) and, with NULL
+ * inputs, the re-quantisation of the zeroed tail in _zero_physical_tail (:237-253).
+ */
+int ta100_cache_append(const void* k_new, const void* v_new, void* k_hi, void* v_hi, void* k_codes, void* k_scales,
+                       void* v_codes_t, void* v_scales_t, void* k_mean, void* k_min, void* k_max, long long heads,
+                       int start, int k_count, int v_count, int capacity, int head_dim, int stat_block, int is_mxfp4,
+                       int is_bf16, int flags, void* stream);
+
+/*
  * Prefill block selection.  q_mean [heads, nq, D]; k_a / k_b [heads/group, nk, D].
  * quest = 0: score = q_mean . k_a (k_a = block means); quest = 1: Quest bound with
  * k_a = block minima, k_b = block maxima.  causal: blocks kb <= qb only.
@@ -106,7 +129,7 @@ int ta100_pack_topk_mask(const void* sel, void* mask, long long rows, int k, int
  * Fused prefill attention: the FP4 pass over non-selected KV blocks and the 16-bit
  * pass over the selected ones in ONE kernel (TMA -> shared memory -> tcgen05 MMA ->
  * tensor memory), online softmax in 64-column steps.
- *   q_hi [B*hq, sq, D], k_hi/v_hi [B*hkv, skv, D]  16-bit, needed when width > 0
+ *   q_hi [B*hq, sq, D], k_hi/v_hi [B*hkv, skv, D] with head stride kv_cap rows;  16-bit, needed when width > 0
  *   sel  [B*hq, sq/block, width] selected KV blocks of `block` (64 or 128) tokens;
  *        width = 0 -> pure FP4 attention
  *   q4/qs rows layout [B*hq, sq, ..]; k4/ks rows layout with head stride kv_cap rows
@@ -141,7 +164,7 @@ int ta100_prefill_status(const void* workspace, int batch, int hq, int hkv, int 
  *   q_hi [B*hkv, group, D] 16-bit and its rows-layout quantisation q4 / qs
  *   K/V, contiguous cache (page_table = NULL): k4 / ks rows layout with head stride kv_cap rows
  *        (plain, not permuted), v4 / vs transposed layout with P = ceil(kv_cap/128)*128,
- *        k_hi / v_hi [B*hkv, kv_len, D]
+ *        k_hi / v_hi [B*hkv, kv_len, D] with head stride kv_cap rows
  *   K/V, paged pools (page_table int32 [B, max_pages] -> physical page): k4 [pages, hkv, 64, D/2],
  *        ks [pages, hkv, 64, D/G], v4 [pages, hkv, D, 32], vs [pages, hkv, D, 64/G],
  *        k_hi / v_hi [pages, hkv, 64, D]

@@ -1,0 +1,223 @@
+"""GPU tests of the generation cache: the fused append kernel is bit-exact against the CPU oracle's
+quantisers and block statistics however the sequence is cut into appends; crop re-zeroes the rounded
+tail; decode and prefill over the cache match the oracle's attention on the same (zero-padded) K/V."""
+import pytest
+import torch
+
+import oracle
+import thriftattention_b200 as ta
+from thriftattention_b200.integrations import transformers_cache as tc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _u8(t):
+    return t.view(torch.uint8).cpu()
+
+
+def _check_layer_against_oracle(layer, k_ref, v_ref, fmt):
+    """Every derived tensor of ``layer`` equals the oracle's function of its 16-bit content ``k_ref`` / ``v_ref``
+    ([B,H,n,D] CPU tensors, n = layer.seq_len)."""
+    n = layer.seq_len
+    g = 32 if fmt == "mxfp4" else 16
+    assert torch.equal(layer.key_view().cpu(), k_ref) and torch.equal(layer.value_view().cpu(), v_ref)
+    codes, scales = oracle.quantize(k_ref, fmt, "plain")
+    assert torch.equal(layer.k_packed[:, :, :n].cpu(), codes)
+    assert torch.equal(_u8(layer.k_scale[:, :, :n]), _u8(scales))
+    # V groups: tokens beyond n inside the last group are zero rows of the cache
+    ng = -(-n // g) * g
+    v_pad = torch.zeros(v_ref.shape[0], v_ref.shape[1], ng, v_ref.shape[3], dtype=v_ref.dtype)
+    v_pad[:, :, :n] = v_ref
+    vcodes, vscales = oracle.quantize(v_pad, fmt, "transposed")
+    assert torch.equal(layer.v_packed_t[:, :, :, : ng // 2].cpu(), vcodes[:, :, :, : ng // 2])
+    assert torch.equal(_u8(layer.v_scale_t[:, :, :, : ng // g]), _u8(vscales[:, :, :, : ng // g]))
+    nb = n // 64
+    if nb:
+        mean, lo, hi = oracle.block_stats(k_ref[:, :, : nb * 64], 64)
+        assert torch.equal(layer.k_mean[:, :, :nb].cpu(), mean)
+        if layer.k_min is not None:
+            assert torch.equal(layer.k_min[:, :, :nb].cpu(), lo) and torch.equal(layer.k_max[:, :, :nb].cpu(), hi)
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("d", [128, 64])
+def test_append_any_chunking_is_bit_exact(fmt, dtype, d):
+    torch.manual_seed(5)
+    total = 700
+    k = (torch.randn(2, 3, total, d) * 1.5).to(dtype)
+    v = torch.randn(2, 3, total, d).to(dtype)
+    k[0, 0, 100:116] = 0                      # an all-zero group -> scale byte 0, codes 0
+    v[1, 2, 32:64, 5] = 0
+    k[0, 1, 7, :16] = 5000.0                  # beyond 448 * 6: the scale saturates
+    for chunks in ([700], [1] * 40 + [660], [70, 1, 1, 57, 3, 200, 33, 31, 1, 303], [64, 64, 128, 444]):
+        layer = tc.ThriftAttentionCacheLayer(quant_format=fmt, track_minmax=True)
+        pos = 0
+        for c in chunks:
+            layer.update(k[:, :, pos:pos + c].to(DEV), v[:, :, pos:pos + c].to(DEV))
+            pos += c
+            if c > 1 or pos % 16 == 0:
+                _check_layer_against_oracle(layer, k[:, :, :pos], v[:, :, :pos], fmt)
+        assert pos == total and layer.capacity == 1024
+        _check_layer_against_oracle(layer, k, v, fmt)
+
+
+def test_append_with_fixed_capacity_and_positions():
+    torch.manual_seed(6)
+    k = torch.randn(1, 2, 200, 128).half()
+    v = torch.randn(1, 2, 200, 128).half()
+    layer = tc.ThriftAttentionCacheLayer(max_cache_len=200)
+    layer.update(k[:, :, :150].to(DEV), v[:, :, :150].to(DEV), {"cache_position": torch.arange(150, device=DEV)})
+    assert layer.capacity == 256
+    # overwrite a range in the middle, then continue at the end
+    k2, v2 = k.clone(), v.clone()
+    k2[:, :, 60:90] = torch.randn(1, 2, 30, 128).half()
+    v2[:, :, 60:90] = torch.randn(1, 2, 30, 128).half()
+    layer.update(k2[:, :, 60:90].to(DEV), v2[:, :, 60:90].to(DEV), {"cache_position": torch.arange(60, 90)})
+    assert layer.seq_len == 150
+    layer.update(k2[:, :, 150:].to(DEV), v2[:, :, 150:].to(DEV))
+    n = layer.seq_len
+    assert n == 200
+    codes, scales = oracle.quantize(k2, "nvfp4", "plain")
+    assert torch.equal(layer.k_packed[:, :, :n].cpu(), codes) and torch.equal(_u8(layer.k_scale[:, :, :n]), _u8(scales))
+    v_pad = torch.zeros(1, 2, 208, 128).half()
+    v_pad[:, :, :200] = v2
+    vcodes, _ = oracle.quantize(v_pad, "nvfp4", "transposed")
+    assert torch.equal(layer.v_packed_t[:, :, :, :104].cpu(), vcodes[:, :, :, :104])
+    # statistics are refreshed for the blocks that END inside the written range: block 0 here
+    # (tokens 60..63 changed); block 1 keeps its old statistics although tokens 64..89 changed
+    mean = oracle.block_stats(k2[:, :, :64], 64, ("mean",))[0]
+    assert torch.equal(layer.k_mean[:, :, :1].cpu(), mean)
+
+
+def test_crop_rezeroes_tail_and_requantises():
+    torch.manual_seed(7)
+    k = torch.randn(1, 2, 128, 128).half()
+    v = torch.randn(1, 2, 128, 128).half()
+    layer = tc.ThriftAttentionCacheLayer()
+    layer.update(k.to(DEV), v.to(DEV))
+    layer.crop(70)
+    assert layer.seq_len == 70
+    assert layer.k_fp16[:, :, 70:128].abs().sum() == 0 and layer.v_fp16[:, :, 70:128].abs().sum() == 0
+    assert layer.k_packed[:, :, 70:128].sum() == 0 and _u8(layer.k_scale[:, :, 70:128]).sum() == 0
+    _check_layer_against_oracle(layer, k[:, :, :70], v[:, :, :70], "nvfp4")
+    assert layer.v_packed_t[:, :, :, 40:64].sum() == 0           # groups entirely beyond token 80
+    # decode continues from the cropped length
+    layer.update(k[:, :, 100:101].to(DEV), v[:, :, 100:101].to(DEV))
+    k3 = torch.cat([k[:, :, :70], k[:, :, 100:101]], 2)
+    v3 = torch.cat([v[:, :, :70], v[:, :, 100:101]], 2)
+    _check_layer_against_oracle(layer, k3, v3, "nvfp4")
+
+
+def test_cache_append_argument_errors():
+    ext = ta._extension.get_extension()
+    layer = tc.ThriftAttentionCacheLayer()
+    layer.update(torch.zeros(1, 1, 10, 128, device=DEV).half(), torch.zeros(1, 1, 10, 128, device=DEV).half())
+    args = (layer.k_fp16, layer.v_fp16, layer.k_packed, layer.k_scale, layer.v_packed_t, layer.v_scale_t)
+    new = torch.zeros(1, 1, 200, 128, device=DEV).half()
+    with pytest.raises(RuntimeError, match="cache_append"):
+        ext.cache_append(new, new, *args, start=0)                # 200 rows into a 128-row cache
+    with pytest.raises(RuntimeError):
+        ext.cache_append(new[:, :, :4].bfloat16(), new[:, :, :4].bfloat16(), *args, start=0)
+    with pytest.raises(RuntimeError):
+        ext.cache_append(new[:, :, :4], new[:, :, :4], *args, start=0, k_mean=torch.zeros(1, 1, 1, 128, device=DEV).half())
+
+
+# ------------------------------------------------------------------------------- attention over the cache
+def _filled_cache(cfg, k, v, chunks):
+    cache = ta.ThriftAttentionCache(config=cfg)
+    pos = 0
+    for c in chunks:
+        cache.update(k[:, :, pos:pos + c].to(DEV), v[:, :, pos:pos + c].to(DEV), 0)
+        pos += c
+    return cache
+
+
+def _zero_padded(x, multiple=64):
+    n = x.shape[2]
+    p = max(multiple, -(-n // multiple) * multiple)
+    out = torch.zeros(x.shape[0], x.shape[1], p, x.shape[3], dtype=x.dtype)
+    out[:, :, :n] = x
+    return out
+
+
+@pytest.mark.parametrize("fmt,selection,dtype", [("nvfp4", "block_mean", torch.float16), ("nvfp4", "quest", torch.bfloat16),
+                                                 ("mxfp4", "quest", torch.float16), ("nvfp4", "local", torch.float16)])
+def test_cached_decode_matches_oracle(fmt, selection, dtype):
+    torch.manual_seed(11)
+    b, hq, hkv, n, d = 2, 8, 2, 64 * 9 + 17, 128
+    k = torch.randn(b, hkv, n, d).to(dtype)
+    v = torch.randn(b, hkv, n, d).to(dtype)
+    q = torch.randn(b, hq, 1, d).to(dtype)
+    cfg = ta.AttentionConfig(selection=selection, top_k=3, quant_format=fmt)
+    cache = _filled_cache(cfg, k, v, [500, 1, 1, n - 502])
+    out = tc.cached_decode_attention(q.to(DEV), cache, 0, cfg)
+    assert out.shape == (b, hq, 1, d) and out.dtype == dtype
+
+    # oracle: same K/V, zero rows up to the next multiple of 64; only the 9 complete blocks are candidates
+    kp, vp = _zero_padded(k), _zero_padded(v)
+    qg = q.reshape(b, hkv, hq // hkv, d)
+    if selection == "local":
+        sel = oracle.local_decode(b * hkv, 9, 3)
+    else:
+        mean, lo, hi = oracle.block_stats(kp, 64)
+        sel = (oracle.select_decode(qg, lo, hi, k=3, num_kv_blocks=9) if selection == "quest"
+               else oracle.select_decode(qg, mean, k=3, num_kv_blocks=9))
+    got_sel = tc.select_cached_decode_blocks(qg.to(DEV), cache.layers[0], cfg).cpu()
+    assert torch.equal(got_sel, sel)
+    splits = ta._extension.get_extension().decode_pick_splits(b * hkv, 10)
+    ref = oracle.decode_attention(qg, kp, vp, sel, fmt=fmt, splits=min(splits, 10)).reshape(b, hq, 1, d)
+    err = (out.float().cpu() - ref.float()).abs()
+    tol = 2e-3 if dtype == torch.float16 else max(2e-3, 2.0 ** -7 * ref.float().abs().max().item())
+    assert err.max().item() <= tol, err.max().item()
+
+    # pure FP4 over the same cache
+    cfg4 = ta.AttentionConfig(method="fp4", quant_format=fmt)
+    out4 = tc.cached_decode_attention(q.to(DEV), cache, 0, cfg4)
+    ref4 = oracle.decode_attention(qg, kp, vp, None, fmt=fmt, splits=min(splits, 10)).reshape(b, hq, 1, d)
+    assert (out4.float().cpu() - ref4.float()).abs().max().item() <= tol
+
+
+@pytest.mark.parametrize("fmt,selection,block", [("nvfp4", "block_mean", 64), ("mxfp4", "quest", 64), ("nvfp4", "quest", 128)])
+def test_cached_prefill_matches_oracle(fmt, selection, block):
+    torch.manual_seed(12)
+    b, hq, hkv, n, d = 1, 4, 2, 512, 128
+    q = torch.randn(b, hq, n, d).half()
+    k = torch.randn(b, hkv, n, d).half()
+    v = torch.randn(b, hkv, n, d).half()
+    cfg = ta.AttentionConfig(selection=selection, top_k=2, quant_format=fmt, block_size=block)
+    cache = ta.ThriftAttentionCache(config=cfg, max_cache_len=n + 100)      # capacity 640 > n: strided views
+    cache.update(k.to(DEV), v.to(DEV), 0)
+    assert cache.layers[0].capacity == 640
+    out = tc.cached_prefill_attention(q.to(DEV), cache, 0, cfg)
+    qm, = oracle.block_stats(q, block, ("mean",))
+    mean, lo, hi = oracle.block_stats(k, block)
+    sel = (oracle.select_prefill(qm, lo, hi, k=2, causal=True) if selection == "quest"
+           else oracle.select_prefill(qm, mean, k=2, causal=True))
+    ref = oracle.prefill_attention(q, k, v, sel, fmt=fmt, block=block, causal=True)
+    err = (out.float().cpu() - ref.float()).abs()
+    assert err.max().item() <= 2e-3 and err.mean().item() <= 2e-4, (err.max().item(), err.mean().item())
+    # the route without a cache (K/V quantised again, K in the permuted layout) agrees
+    again = ta.attention(q.to(DEV), k.to(DEV), v.to(DEV), config=cfg)
+    assert (again.float() - out.float()).abs().max().item() <= 1e-3
+
+
+def test_cached_prefill_ignores_prompt_padding_in_selection():
+    torch.manual_seed(13)
+    n, real = 256, 150
+    q = torch.randn(1, 2, n, 128).half()
+    k = torch.randn(1, 2, n, 128).half()
+    v = torch.randn(1, 2, n, 128).half()
+    cfg = ta.AttentionConfig(top_k=1)
+    cache = ta.ThriftAttentionCache(config=cfg)
+    cache.prefill_real_seq_len = real
+    cache.update(k.to(DEV), v.to(DEV), 0)
+    sel = tc.select_cached_prefill_blocks(q.to(DEV), cache.layers[0].key_view(), cache.layers[0], cfg, real_q_len=real).cpu()
+    qm, = oracle.block_stats(q, 64, ("mean",))
+    qm[:, :, 2] = (q[:, :, 128:150].float().sum(2) / 22).half()
+    qm[:, :, 3] = 0
+    mean, = oracle.block_stats(k, 64, ("mean",))
+    ref = oracle.select_prefill(qm, mean, k=1, causal=True)
+    assert torch.equal(sel[:, :2], ref[:, :2])          # blocks made only of real rows: identical arithmetic
+    assert sel.shape == ref.shape

@@ -1,0 +1,85 @@
+"""Two-GPU tests (skipped on a single-GPU machine): head-sharded prefill and KV-sequence-sharded
+decode over NCCL, checked against the CPU oracle.  NVLS is switched off for the test processes."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    import oracle
+    import thriftattention_b200 as ta
+    from thriftattention_b200 import distributed as tad
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        res = {}
+        # ---- prefill: 8 q / 4 kv heads split over the ranks, gathered output equals the oracle ----
+        torch.manual_seed(0)
+        q = torch.randn(1, 8, 1024, 128).half()
+        k = torch.randn(1, 4, 1024, 128).half()
+        v = torch.randn(1, 4, 1024, 128).half()
+        cfg = ta.AttentionConfig(selection="quest", top_k=3, block_size=64)
+        out = tad.attention_head_sharded(q.to(dev), k.to(dev), v.to(dev), config=cfg)
+        qm, = oracle.block_stats(q, 64, ("mean",))
+        kmin, kmax = oracle.block_stats(k, 64, ("min", "max"))
+        sel = oracle.select_prefill(qm, kmin, kmax, k=3, causal=True)
+        ref = oracle.prefill_attention(q, k, v, sel, fmt="nvfp4", block=64, causal=True)
+        err = (out.float().cpu() - ref.float()).abs()
+        res["prefill"] = (tuple(out.shape) == (1, 8, 1024, 128)) and err.max().item() <= 2e-3 and err.mean().item() <= 2e-4
+        # ---- decode: 4096 cached tokens = 64 pages, 32 per rank; global Quest top-6 ----
+        torch.manual_seed(1)
+        qd = torch.randn(2, 8, 1, 128).half()
+        kd = torch.randn(2, 2, 4096, 128).half()
+        vd = torch.randn(2, 2, 4096, 128).half()
+        shard = tad.plan_page_shards(64, world)[rank]
+        lo, hi = shard.page_begin * 64, shard.page_end * 64
+        splits = 2
+        out_d = tad.decode_kv_sharded(qd.to(dev), kd[:, :, lo:hi].contiguous().to(dev), vd[:, :, lo:hi].contiguous().to(dev),
+                                      shard=shard, total_pages=64, top_k=6, num_splits=splits)
+        qg = qd.reshape(2, 2, 4, 128)
+        kmin, kmax = oracle.block_stats(kd, 64, ("min", "max"))
+        sel_d = oracle.select_decode(qg, kmin, kmax, k=6, num_kv_blocks=64)
+        ref_d = oracle.decode_attention(qg, kd, vd, sel_d, fmt="nvfp4", splits=world * splits).reshape(2, 8, 1, 128)
+        err = (out_d.float().cpu() - ref_d.float()).abs()
+        res["decode"] = err.max().item() <= 2e-3 and err.mean().item() <= 2e-4
+        res["decode_err"] = err.max().item()
+        results.put((rank, res))
+    except Exception as exc:
+        results.put((rank, repr(exc)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_prefill_and_decode():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    results_q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, results_q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(results_q.get(timeout=240) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    for rank in (0, 1):
+        assert isinstance(results[rank], dict), results[rank]
+        assert results[rank]["prefill"], results[rank]
+        assert results[rank]["decode"], results[rank]

@@ -122,6 +122,48 @@ def block_stats(x: torch.Tensor, block_size: int, *, mean=False, minmax=False):
     return o_mean, o_min, o_max
 
 
+def cache_append(k_new, v_new, k_hi, v_hi, k_codes, k_scales, v_codes_t, v_scales_t, *, start, k_count=None, v_count=None,
+                 k_mean=None, k_min=None, k_max=None, is_mx=False, stat_block=64, keep_k=False, keep_v=False):
+    """Fused KV-cache append (one launch): stores ``k_new`` / ``v_new`` [B, H, T, D] at token positions
+    ``[start, start + T)`` of the capacity-strided caches ``k_hi`` / ``v_hi`` [B, H, cap, D], quantises the
+    new K rows, re-quantises the V groups they touch and refreshes the statistics of completed blocks.
+
+    ``k_new`` / ``v_new`` may be ``None`` with an explicit count: zero rows are stored, or with
+    ``keep_k`` / ``keep_v`` the cached rows are kept and only re-quantised.  Stands in for
+    ``ThriftAttentionCacheLayer.update`` and its three helpers
+    (integrations/transformers_cache.py:87-123, 308-351).
+    """
+    _check(k_hi.is_cuda and k_hi.dim() == 4 and k_hi.is_contiguous(), "k cache must be a contiguous 4D CUDA tensor")
+    b, h, cap, d = k_hi.shape
+    is_bf16 = k_hi.dtype == torch.bfloat16
+    _check(k_hi.dtype in (torch.float16, torch.bfloat16), "KV cache tensors must be float16 or bfloat16")
+    g = 32 if is_mx else 16
+    for name, new, count in (("key_states", k_new, k_count), ("value_states", v_new, v_count)):
+        if new is not None:
+            _check(new.is_cuda and new.is_contiguous() and new.dtype == k_hi.dtype, f"{name} must be contiguous CUDA tensors "
+                   "of the cache dtype")
+            _check(new.dim() == 4 and new.shape[0] == b and new.shape[1] == h and new.shape[3] == d,
+                   f"{name} must be [batch, heads, tokens, head_dim] matching the cache")
+            _check(count is None or count == new.shape[2], f"{name} count does not match its tensor")
+    k_count = k_new.shape[2] if k_new is not None else int(k_count or 0)
+    v_count = v_new.shape[2] if v_new is not None else int(v_count or 0)
+    expect = {"v_hi": (v_hi, (b, h, cap, d)), "k_codes": (k_codes, (b, h, cap, d // 2)),
+              "k_scales": (k_scales, (b, h, cap, d // g)), "v_codes_t": (v_codes_t, (b, h, d, cap // 2)),
+              "v_scales_t": (v_scales_t, (b, h, d, cap // g))}
+    for name, (t, shape) in expect.items():
+        _check(t.is_cuda and t.is_contiguous() and tuple(t.shape) == shape, f"{name} must be contiguous {shape}")
+    for name, t in (("k_mean", k_mean), ("k_min", k_min), ("k_max", k_max)):
+        _check(t is None or (t.is_cuda and t.is_contiguous() and tuple(t.shape) == (b, h, cap // stat_block, d)
+                             and t.dtype == k_hi.dtype), f"{name} must be contiguous [B, H, cap/{stat_block}, D] of the cache dtype")
+    flags = (1 if keep_k else 0) | (2 if keep_v else 0)
+    with torch.cuda.device(k_hi.device):
+        rc = _lib.load().ta100_cache_append(_ptr(k_new), _ptr(v_new), _ptr(k_hi), _ptr(v_hi), _ptr(k_codes), _ptr(k_scales),
+                                            _ptr(v_codes_t), _ptr(v_scales_t), _ptr(k_mean), _ptr(k_min), _ptr(k_max),
+                                            b * h, int(start), k_count, v_count, cap, d, stat_block, int(is_mx),
+                                            int(is_bf16), flags, _stream(k_hi))
+    _lib.check(rc, "cache_append")
+
+
 def select_prefill_blocks(q_mean, k_a, k_b, topk_count, causal=True, is_bf16=False, sink=0, local=0):
     """Per-q-block selection.  ``k_b is None`` -> block-mean score with ``k_a = k_mean``;
     otherwise Quest with ``k_a = k_min``, ``k_b = k_max``.  K statistics may be given per
@@ -317,7 +359,11 @@ def prefill_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_p
                "selected_blocks second dimension must equal number of Q blocks")
         _check((skv + 63) // 64 <= 2048, f"ThriftAttention supports at most 2048 64-token KV blocks, got {(skv + 63) // 64}")
         width = selected_blocks.size(2)
-        _check(q_hi.is_contiguous() and k_hi.is_contiguous() and v_hi.is_contiguous(), "Q/K/V must be contiguous")
+        _check(q_hi.is_contiguous(), "Q must be contiguous")
+        want = (hkv * kv_cap * d, kv_cap * d, d, 1)
+        for t in (k_hi, v_hi):
+            _check((t.is_contiguous() and t.size(2) == kv_cap) or tuple(t.stride()) == want,
+                   "16-bit K/V must be contiguous or views of a cache with the packed K's capacity")
     out = torch.empty(b, hq, sq, d, dtype=torch.bfloat16 if is_bf16 else torch.float16, device=q_packed.device)
     lib = _lib.load()
     with torch.cuda.device(out.device):
@@ -444,7 +490,15 @@ def decode_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_pa
                "selected block count must be in [0, number of KV blocks]")
         if width:
             _check(q_hi is not None and q_hi.shape == (b, hkv, g, d), "q_hi shape must match packed Q")
-            _check(q_hi.is_contiguous() and k_hi.is_contiguous() and v_hi.is_contiguous(), "Q/K/V must be contiguous")
+            _check(q_hi.is_contiguous(), "Q must be contiguous")
+            if page_table is None:
+                # 16-bit K/V may be views of a longer cache, as long as they share the packed K's capacity
+                want = (hkv * kv_cap * d, kv_cap * d, d, 1)
+                for t in (k_hi, v_hi):
+                    _check(t.dim() == 4 and (t.is_contiguous() and t.size(2) == kv_cap or tuple(t.stride()) == want),
+                           "16-bit K/V must be contiguous or views of a cache with the packed K's capacity")
+            else:
+                _check(k_hi.is_contiguous() and v_hi.is_contiguous(), "Q/K/V must be contiguous")
     lib = _lib.load()
     dev = q_packed.device
     splits = num_splits if num_splits > 0 else lib.ta100_decode_pick_splits(b * hkv, npages)

@@ -1,0 +1,258 @@
+// Fused KV-cache append for generation.
+//
+// One launch per layer and step does what the reference cache does with several PyTorch slice
+// copies and three extension calls (integrations/transformers_cache.py:87-123, 308-351):
+//   * store the new 16-bit K and V rows at [start, start + count) of the capacity-strided cache,
+//   * quantise the new K rows (plain row layout: codes [cap, D/2], scales [cap, D/G]),
+//   * re-quantise every V group (G = 16 NVFP4 / 32 MXFP4 tokens, transposed layout
+//     codes [D, cap/2], scales [D, cap/G]) that the new rows touch — tokens of such a group that
+//     are not new are read back from the 16-bit cache,
+//   * recompute mean / min / max of every statistics block that the new rows complete.
+// The arithmetic of each piece is the one of the stand-alone quantise and block-statistics
+// kernels, so a cache filled in any number of appends equals one filled in a single pass.
+//
+// Work is cut into independent CTA-sized items (K row bundles, 128-token V tiles, statistics
+// blocks); an item reads new rows from the inputs and old rows from the cache, never a row that
+// another item of the same launch writes, so no ordering between CTAs is needed.
+#include "common.cuh"
+
+namespace ta100 {
+
+struct AppendParams {
+    const uint16_t* k_new;
+    const uint16_t* v_new;
+    uint16_t* k_hi;
+    uint16_t* v_hi;
+    uint8_t* k_codes;
+    uint8_t* k_scales;
+    uint8_t* v_codes;
+    uint8_t* v_scales;
+    uint16_t* k_mean;
+    uint16_t* k_min;
+    uint16_t* k_max;
+    int start, k_count, v_count, cap;
+    int k_keep, v_keep;           // with a null input: 1 = re-quantise the cached rows, 0 = store zero rows
+    int n_k_items, n_v_items, n_s_items;
+    int v_begin, v_end;           // group-aligned token range whose V groups are re-quantised
+    int s_first, stat_block;
+};
+
+// 16-byte chunk `cv` of token `tok`: from the new rows when the token is being appended, else from the cache.
+template <int D>
+__device__ __forceinline__ uint4 row_chunk(const uint16_t* __restrict__ fresh, const uint16_t* cache, int keep,
+                                           int start, int count, int cap, long long head, int tok, int cv,
+                                           bool& is_new) {
+    is_new = false;
+    if (tok >= start && tok < start + count && !(fresh == nullptr && keep)) {
+        is_new = true;
+        if (fresh == nullptr) return make_uint4(0u, 0u, 0u, 0u);
+        return __ldg(reinterpret_cast<const uint4*>(fresh + (head * count + (tok - start)) * D) + cv);
+    }
+    return *(reinterpret_cast<const uint4*>(cache + (head * cap + tok) * D) + cv);
+}
+
+template <int D, bool MX, bool BF16>
+__global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p) {
+    constexpr int G = MX ? 32 : 16;
+    constexpr int GPR = D / G;        // groups per row
+    constexpr int ROWS = 128 / GPR;   // K rows per item
+    constexpr int VEC = D / 8;        // 16-byte chunks per row
+    constexpr int TILE_BYTES = 128 * (D + 8) * 2;
+    __shared__ __align__(16) unsigned char smem[TILE_BYTES + D * 64 + D * 8];
+
+    const int items = p.n_k_items + p.n_v_items + p.n_s_items;
+    const long long head = blockIdx.x / items;
+    int it = blockIdx.x % items;
+    const int tid = threadIdx.x;
+
+    if (it < p.n_k_items) {
+        // ---------------------------------------------------------------- K rows: one thread per group
+        const int row = it * ROWS + tid / GPR;
+        const int c = tid % GPR;
+        if (row >= p.k_count) return;
+        const int tok = p.start + row;
+        uint32_t raw[G / 2];
+        bool is_new = false;
+#pragma unroll
+        for (int i = 0; i < G / 8; ++i) {
+            const uint4 t = row_chunk<D>(p.k_new, p.k_hi, p.k_keep, p.start, p.k_count, p.cap, head, tok,
+                                         c * (G / 8) + i, is_new);
+            raw[4 * i + 0] = t.x; raw[4 * i + 1] = t.y; raw[4 * i + 2] = t.z; raw[4 * i + 3] = t.w;
+            if (is_new) *(reinterpret_cast<uint4*>(p.k_hi + (head * p.cap + tok) * D) + c * (G / 8) + i) = t;
+        }
+        uint32_t out[G / 8];
+        uint8_t sb;
+        quantise_group_regs<MX, BF16>(raw, out, sb);
+        const long long gid = (head * p.cap + tok) * GPR + c;
+        if constexpr (MX) *reinterpret_cast<uint4*>(p.k_codes + gid * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+        else *reinterpret_cast<uint2*>(p.k_codes + gid * 8) = make_uint2(out[0], out[1]);
+        p.k_scales[gid] = sb;
+        return;
+    }
+    it -= p.n_k_items;
+
+    if (it < p.n_v_items) {
+        // ---------------------------------------------------------------- V: groups of one 128-token tile
+        auto tile = reinterpret_cast<uint16_t(*)[D + 8]>(smem);
+        auto out_codes = reinterpret_cast<uint8_t(*)[64]>(smem + TILE_BYTES);
+        auto out_scales = reinterpret_cast<uint8_t(*)[8]>(smem + TILE_BYTES + D * 64);
+        const int tok0 = (p.v_begin / 128 + it) * 128;
+        const int lo = max(p.v_begin, tok0);
+        const int hi = min(p.v_end, tok0 + 128);
+        for (int i = tid; i < (hi - lo) * VEC; i += 128) {
+            const int r = i / VEC, cv = i % VEC;
+            const int tok = lo + r;
+            bool is_new;
+            const uint4 val = row_chunk<D>(p.v_new, p.v_hi, p.v_keep, p.start, p.v_count, p.cap, head, tok, cv, is_new);
+            if (is_new) *(reinterpret_cast<uint4*>(p.v_hi + (head * p.cap + tok) * D) + cv) = val;
+            *reinterpret_cast<uint4*>(&tile[tok - tok0][cv * 8]) = val;
+        }
+        __syncthreads();
+        const int g_first = (lo - tok0) / G;
+        const int n_groups = (hi - lo) / G;
+        for (int i = tid; i < D * n_groups; i += 128) {
+            const int ch = i % D, grp = g_first + i / D;
+            uint32_t raw[G / 2];
+#pragma unroll
+            for (int j = 0; j < G / 2; ++j) {
+                const uint32_t a = tile[grp * G + 2 * j][ch];
+                const uint32_t b = tile[grp * G + 2 * j + 1][ch];
+                raw[j] = a | (b << 16);
+            }
+            uint32_t out[G / 8];
+            uint8_t sb;
+            quantise_group_regs<MX, BF16>(raw, out, sb);
+#pragma unroll
+            for (int w = 0; w < G / 8; ++w) *reinterpret_cast<uint32_t*>(&out_codes[ch][grp * (G / 2) + 4 * w]) = out[w];
+            out_scales[ch][grp] = sb;
+        }
+        __syncthreads();
+        // 8-byte pieces (16 tokens); consecutive threads write consecutive pieces of one channel row
+        const int pc_first = (lo - tok0) / 16;
+        const int n_pieces = (hi - lo) / 16;
+        for (int i = tid; i < D * n_pieces; i += 128) {
+            const int ch = i / n_pieces, pc = pc_first + i % n_pieces;
+            *reinterpret_cast<uint2*>(p.v_codes + (head * D + ch) * (p.cap / 2) + tok0 / 2 + pc * 8) =
+                *reinterpret_cast<const uint2*>(&out_codes[ch][pc * 8]);
+        }
+        for (int i = tid; i < D * n_groups; i += 128) {
+            const int ch = i / n_groups, g = g_first + i % n_groups;
+            p.v_scales[(head * D + ch) * (p.cap / G) + tok0 / G + g] = out_scales[ch][g];
+        }
+        return;
+    }
+    it -= p.n_v_items;
+
+    {
+        // ---------------------------------------------------------------- statistics of one completed block
+        // Same summation order as block_stats_kernel: eight row groups (row mod 8) accumulate in ascending
+        // row order, the eight partial sums are added left to right, then divided by the block length.
+        auto s_sum = reinterpret_cast<float(*)[D]>(smem);
+        auto s_min = reinterpret_cast<float(*)[D]>(smem + 8 * D * 4);
+        auto s_max = reinterpret_cast<float(*)[D]>(smem + 16 * D * 4);
+        const int blk = p.s_first + it;
+        if (tid < D) {
+            const int cc = tid % VEC, rg = tid / VEC;
+            float sum[8], lo[8], hi[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { sum[i] = 0.0f; lo[i] = INFINITY; hi[i] = -INFINITY; }
+            for (int r = rg; r < p.stat_block; r += 8) {
+                bool is_new;
+                const uint4 v = row_chunk<D>(p.k_new, p.k_hi, p.k_keep, p.start, p.k_count, p.cap, head,
+                                             blk * p.stat_block + r, cc, is_new);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float a = In16<BF16>::to_f(static_cast<uint16_t>(w[i] & 0xFFFFu));
+                    const float b = In16<BF16>::to_f(static_cast<uint16_t>(w[i] >> 16));
+                    sum[2 * i] = __fadd_rn(sum[2 * i], a);
+                    sum[2 * i + 1] = __fadd_rn(sum[2 * i + 1], b);
+                    lo[2 * i] = fminf(lo[2 * i], a); lo[2 * i + 1] = fminf(lo[2 * i + 1], b);
+                    hi[2 * i] = fmaxf(hi[2 * i], a); hi[2 * i + 1] = fmaxf(hi[2 * i + 1], b);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                s_sum[rg][cc * 8 + i] = sum[i];
+                s_min[rg][cc * 8 + i] = lo[i];
+                s_max[rg][cc * 8 + i] = hi[i];
+            }
+        }
+        __syncthreads();
+        if (tid < D) {
+            float total = s_sum[0][tid], l = s_min[0][tid], h = s_max[0][tid];
+#pragma unroll
+            for (int g = 1; g < 8; ++g) {
+                total = __fadd_rn(total, s_sum[g][tid]);
+                l = fminf(l, s_min[g][tid]);
+                h = fmaxf(h, s_max[g][tid]);
+            }
+            const long long o = (head * (p.cap / p.stat_block) + blk) * D + tid;
+            if (p.k_mean) p.k_mean[o] = In16<BF16>::from_f(__fdiv_rn(total, static_cast<float>(p.stat_block)));
+            if (p.k_min) p.k_min[o] = In16<BF16>::from_f(l);
+            if (p.k_max) p.k_max[o] = In16<BF16>::from_f(h);
+        }
+    }
+}
+
+int cache_append_dispatch(const void* k_new, const void* v_new, void* k_hi, void* v_hi, void* k_codes, void* k_scales,
+                          void* v_codes_t, void* v_scales_t, void* k_mean, void* k_min, void* k_max, long long heads,
+                          int start, int k_count, int v_count, int capacity, int head_dim, int stat_block, int is_mx,
+                          int is_bf16, int flags, cudaStream_t stream) {
+    if (head_dim != 64 && head_dim != 128) return TA100_ERR_UNSUPPORTED;
+    if (heads < 0 || start < 0 || k_count < 0 || v_count < 0 || capacity <= 0 || capacity % 128 != 0)
+        return TA100_ERR_SHAPE;
+    if (stat_block != 64 && stat_block != 128) return TA100_ERR_SHAPE;
+    if (static_cast<long long>(start) + (k_count > v_count ? k_count : v_count) > capacity) return TA100_ERR_SHAPE;
+    if (k_count > 0 && (!k_hi || !k_codes || !k_scales)) return TA100_ERR_NULL;
+    if (v_count > 0 && (!v_hi || !v_codes_t || !v_scales_t)) return TA100_ERR_NULL;
+    const uintptr_t all = reinterpret_cast<uintptr_t>(k_new) | reinterpret_cast<uintptr_t>(v_new) |
+                          reinterpret_cast<uintptr_t>(k_hi) | reinterpret_cast<uintptr_t>(v_hi) |
+                          reinterpret_cast<uintptr_t>(k_codes) | reinterpret_cast<uintptr_t>(v_codes_t);
+    if (all & 15) return TA100_ERR_ALIGN;
+    if (heads == 0 || (k_count == 0 && v_count == 0)) return TA100_OK;
+
+    const int G = is_mx ? 32 : 16;
+    AppendParams p{};
+    p.k_new = static_cast<const uint16_t*>(k_new);
+    p.v_new = static_cast<const uint16_t*>(v_new);
+    p.k_hi = static_cast<uint16_t*>(k_hi);
+    p.v_hi = static_cast<uint16_t*>(v_hi);
+    p.k_codes = static_cast<uint8_t*>(k_codes);
+    p.k_scales = static_cast<uint8_t*>(k_scales);
+    p.v_codes = static_cast<uint8_t*>(v_codes_t);
+    p.v_scales = static_cast<uint8_t*>(v_scales_t);
+    p.k_mean = static_cast<uint16_t*>(k_mean);
+    p.k_min = static_cast<uint16_t*>(k_min);
+    p.k_max = static_cast<uint16_t*>(k_max);
+    p.start = start; p.k_count = k_count; p.v_count = v_count; p.cap = capacity;
+    p.k_keep = (flags & 1) ? 1 : 0;
+    p.v_keep = (flags & 2) ? 1 : 0;
+    p.stat_block = stat_block;
+    const int rows_per_item = 128 / (head_dim / G);
+    p.n_k_items = cdiv(k_count, rows_per_item);
+    if (v_count > 0) {
+        p.v_begin = start / G * G;
+        p.v_end = cdiv(start + v_count, G) * G;
+        p.n_v_items = cdiv(p.v_end, 128) - p.v_begin / 128;
+    }
+    if (k_count > 0 && (k_mean || k_min || k_max)) {
+        p.s_first = start / stat_block;
+        const int last = (start + k_count) / stat_block;
+        p.n_s_items = last > p.s_first ? last - p.s_first : 0;
+    }
+    const long long grid = heads * (p.n_k_items + p.n_v_items + p.n_s_items);
+    if (grid > 0x7FFFFFFFLL) return TA100_ERR_LIMIT;
+#define TA100_APPEND(DD, MXX, BFF) cache_append_kernel<DD, MXX, BFF><<<static_cast<unsigned>(grid), 128, 0, stream>>>(p)
+    if (head_dim == 128) {
+        if (is_mx) { if (is_bf16) TA100_APPEND(128, true, true); else TA100_APPEND(128, true, false); }
+        else { if (is_bf16) TA100_APPEND(128, false, true); else TA100_APPEND(128, false, false); }
+    } else {
+        if (is_mx) { if (is_bf16) TA100_APPEND(64, true, true); else TA100_APPEND(64, true, false); }
+        else { if (is_bf16) TA100_APPEND(64, false, true); else TA100_APPEND(64, false, false); }
+    }
+#undef TA100_APPEND
+    return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace ta100

@@ -29,6 +29,8 @@ size_t decode_static_scratch_bytes();
 int decode_static_dispatch(const void*, const void*, const void*, const void*, int, const void*, const void*, const void*,
                            const void*, const void*, const void*, const void*, int, void*, int, int, int, int, int, int, int,
                            int, int, cudaStream_t);
+int cache_append_dispatch(const void*, const void*, void*, void*, void*, void*, void*, void*, void*, void*, void*, long long,
+                          int, int, int, int, int, int, int, int, int, cudaStream_t);
 }  // namespace ta100
 
 using namespace ta100;
@@ -63,6 +65,15 @@ int ta100_quantize(const void* x, void* codes, void* scales, long long bs, int s
 int ta100_block_stats(const void* x, void* mean, void* mn, void* mx, long long heads, int seq, int head_dim, int block,
                       int is_bf16, void* stream) {
     return block_stats_dispatch(x, mean, mn, mx, heads, seq, head_dim, block, is_bf16, S(stream));
+}
+
+int ta100_cache_append(const void* k_new, const void* v_new, void* k_hi, void* v_hi, void* k_codes, void* k_scales,
+                       void* v_codes_t, void* v_scales_t, void* k_mean, void* k_min, void* k_max, long long heads,
+                       int start, int k_count, int v_count, int capacity, int head_dim, int stat_block, int is_mxfp4,
+                       int is_bf16, int flags, void* stream) {
+    return cache_append_dispatch(k_new, v_new, k_hi, v_hi, k_codes, k_scales, v_codes_t, v_scales_t, k_mean, k_min, k_max,
+                                 heads, start, k_count, v_count, capacity, head_dim, stat_block, is_mxfp4, is_bf16, flags,
+                                 S(stream));
 }
 
 int ta100_select_prefill(const void* q_mean, const void* k_a, const void* k_b, void* out, int heads, int group, int nq,

@@ -888,7 +888,8 @@ int prefill_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const
                 rc |= make_tensor_map(&maps[3], dt, 3, q_hi, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
             }
             uint64_t dims[3] = {static_cast<uint64_t>(d), static_cast<uint64_t>(skv), static_cast<uint64_t>(hkv_flat)};
-            uint64_t str[2] = {static_cast<uint64_t>(d) * 2, static_cast<uint64_t>(skv) * d * 2};
+            // the 16-bit K/V share the capacity (row stride between heads) of the packed K
+            uint64_t str[2] = {static_cast<uint64_t>(d) * 2, static_cast<uint64_t>(kv_cap) * d * 2};
             uint32_t box[3] = {64, STEP, 1};
             rc |= make_tensor_map(&maps[4], dt, 3, k_hi, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
             rc |= make_tensor_map(&maps[5], dt, 3, v_hi, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);

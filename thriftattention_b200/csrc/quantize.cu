@@ -10,30 +10,6 @@
 
 namespace ta100 {
 
-template <bool MX, bool BF16>
-__device__ __forceinline__ void quantise_group_regs(const uint32_t* raw /* G/2 words of 2x16-bit */,
-                                                    uint32_t* codes /* G/8 words */, uint8_t& scale_byte) {
-    constexpr int G = MX ? 32 : 16;
-    float v[G];
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < G / 2; ++i) {
-        v[2 * i] = In16<BF16>::to_f(static_cast<uint16_t>(raw[i] & 0xFFFFu));
-        v[2 * i + 1] = In16<BF16>::to_f(static_cast<uint16_t>(raw[i] >> 16));
-        amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
-    }
-    const float sf = __fdiv_rn(amax, 6.0f);
-    scale_byte = encode_scale<MX>(sf);
-    const float sfq = decode_scale<MX>(scale_byte);
-    const float inv = (sfq == 0.0f) ? 0.0f : __fdiv_rn(1.0f, sfq);
-#pragma unroll
-    for (int w = 0; w < G / 8; ++w) {
-        codes[w] = e2m1x8(__fmul_rn(v[8 * w + 0], inv), __fmul_rn(v[8 * w + 1], inv), __fmul_rn(v[8 * w + 2], inv),
-                          __fmul_rn(v[8 * w + 3], inv), __fmul_rn(v[8 * w + 4], inv), __fmul_rn(v[8 * w + 5], inv),
-                          __fmul_rn(v[8 * w + 6], inv), __fmul_rn(v[8 * w + 7], inv));
-    }
-}
-
 // Row layouts.  x [bs, seq, d] -> codes [bs, seq, d/2], scales [bs, seq, d/G].
 // One thread per group; consecutive threads take consecutive groups so loads,
 // code stores and scale stores are all contiguous across a warp.

@@ -1,0 +1,652 @@
+"""Generation cache for Hugging Face Transformers models: 16-bit K/V plus the FP4 codes, block
+scales and per-block key statistics that the decode kernel reads, kept current by ONE fused
+kernel launch per layer and step.
+
+Interface and semantics follow the reference's ``integrations/transformers_cache.py``
+(``ThriftAttentionCacheLayer`` :70-475, ``ThriftAttentionCache`` :478-567, ``cached_decode_attention``
+:570-619, ``cached_prefill_attention`` :622-680, the selection helpers :683-831):
+
+* physical capacity is a multiple of 128 tokens, grown by doubling or fixed by ``max_cache_len``;
+* ``seq_len`` is the logical length; the packed views handed to the kernels are rounded up to 64
+  tokens (V to 128) and the rounded tail holds zero rows;
+* only complete 64-token blocks can be promoted to 16-bit — the trailing partial block stays FP4;
+* ``crop`` zeroes and re-quantises the rounded tail.
+
+Beyond the reference: MXFP4 caches, Quest selection (block minima / maxima are maintained next to
+the means), forced sink / local blocks, and a prefill that reads the cache's own FP4 tensors
+instead of quantising K and V a second time.
+"""
+from __future__ import annotations
+
+from contextlib import contextmanager
+from contextvars import ContextVar
+from dataclasses import dataclass
+from typing import Any, Iterator
+
+import torch
+
+from .._extension import get_extension
+from ..backends.single_query import _group_single_query, _ungroup_single_query
+from ..config import AttentionConfig
+from ..quant.formats import get_quant_format
+from ..selection import resolve_top_k
+from ..selection.local import select_local_block_pairs
+
+PAGE = 64            # tokens per selectable KV block of the decode kernel
+CAPACITY_QUANTUM = 128
+
+_ACTIVE_CACHE: ContextVar["ThriftAttentionCache | None"] = ContextVar("thriftattention_active_cache", default=None)
+
+
+def get_active_thriftattention_cache() -> "ThriftAttentionCache | None":
+    return _ACTIVE_CACHE.get()
+
+
+@contextmanager
+def use_thriftattention_cache(cache: "ThriftAttentionCache") -> Iterator["ThriftAttentionCache"]:
+    """Make ``cache`` the one the registered attention function routes through (context-local)."""
+    token = _ACTIVE_CACHE.set(cache)
+    try:
+        yield cache
+    finally:
+        _ACTIVE_CACHE.reset(token)
+
+
+def is_thriftattention_cache(value: object) -> bool:
+    return isinstance(value, ThriftAttentionCache)
+
+
+def _round_up(value: int, multiple: int) -> int:
+    return -(-value // multiple) * multiple
+
+
+def _cache_position_start(cache_kwargs: dict[str, Any] | None, fallback: int) -> int:
+    """First position of an update: ``cache_kwargs['cache_position']`` (must be consecutive) or ``fallback``."""
+    position = (cache_kwargs or {}).get("cache_position")
+    if position is None:
+        return fallback
+    if not isinstance(position, torch.Tensor):
+        return int(position)
+    flat = position.reshape(-1)
+    if flat.numel() == 0:
+        return fallback
+    first = int(flat[0].item())
+    if flat.numel() > 1:
+        expected = torch.arange(first, first + flat.numel(), device=flat.device, dtype=flat.dtype)
+        if not torch.equal(flat, expected):
+            raise ValueError("ThriftAttentionCache requires contiguous cache_position values")
+    return first
+
+
+def _scale_dtype(quant_format: str) -> torch.dtype:
+    return torch.float8_e8m0fnu if quant_format == "mxfp4" else torch.float8_e4m3fn
+
+
+def _group_size(quant_format: str) -> int:
+    return 32 if quant_format == "mxfp4" else 16
+
+
+@dataclass
+class ThriftAttentionCacheLayer:
+    """K/V of one attention layer: 16-bit rows, FP4 codes + scales (K by rows, V transposed) and
+    per-64-token-block key statistics, all ``[batch, kv_heads, capacity, ...]``-strided."""
+
+    max_cache_len: int | None = None
+    quant_format: str = "nvfp4"
+    track_minmax: bool = False
+
+    k_fp16: torch.Tensor | None = None
+    v_fp16: torch.Tensor | None = None
+    k_packed: torch.Tensor | None = None
+    k_scale: torch.Tensor | None = None
+    v_packed_t: torch.Tensor | None = None
+    v_scale_t: torch.Tensor | None = None
+    k_mean: torch.Tensor | None = None
+    k_min: torch.Tensor | None = None
+    k_max: torch.Tensor | None = None
+    selected_blocks: torch.Tensor | None = None
+    seq_len: int = 0
+    capacity: int = 0
+
+    # ------------------------------------------------------------------------------------------ update
+    def update(self, key_states: torch.Tensor, value_states: torch.Tensor,
+               cache_kwargs: dict[str, Any] | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """Append (or overwrite from ``cache_position``) and return the logical 16-bit K/V views.
+
+        The whole update — 16-bit stores, K quantisation, V group re-quantisation, block statistics —
+        is one kernel launch (the reference issues slice copies plus three extension calls,
+        transformers_cache.py:87-123)."""
+        if key_states.ndim != 4 or value_states.ndim != 4:
+            raise ValueError("KV cache tensors must be [batch, heads, seq, head_dim]")
+        if key_states.shape != value_states.shape:
+            raise ValueError("key_states and value_states must have identical shapes")
+        if key_states.dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError("KV cache tensors must be float16 or bfloat16")
+        if key_states.dtype != value_states.dtype:
+            raise ValueError("key_states and value_states must have the same dtype")
+
+        start = _cache_position_start(cache_kwargs, self.seq_len)
+        token_count = key_states.shape[2]
+        end = start + token_count
+        if self.max_cache_len is not None and end > self.max_cache_len:
+            raise ValueError(f"ThriftAttentionCache length {end} exceeds max_cache_len={self.max_cache_len}")
+
+        self._ensure_capacity(key_states, end)
+        self.seq_len = max(self.seq_len, end)
+        if token_count:
+            self._append(key_states.contiguous(), value_states.contiguous(), start)
+        return self.key_view(), self.value_view()
+
+    def _append(self, key_states: torch.Tensor | None, value_states: torch.Tensor | None, start: int, *,
+                k_count: int | None = None, v_count: int | None = None, keep_k: bool = False, keep_v: bool = False,
+                stats: bool = True) -> None:
+        get_extension().cache_append(
+            key_states, value_states, self.k_fp16, self.v_fp16, self.k_packed, self.k_scale, self.v_packed_t,
+            self.v_scale_t, start=start, k_count=k_count, v_count=v_count,
+            k_mean=self.k_mean if stats else None, k_min=self.k_min if stats else None,
+            k_max=self.k_max if stats else None, is_mx=self.quant_format == "mxfp4", stat_block=PAGE,
+            keep_k=keep_k, keep_v=keep_v)
+
+    # ------------------------------------------------------------------------------------------- views
+    def key_view(self) -> torch.Tensor:
+        if self.k_fp16 is None:
+            raise RuntimeError("ThriftAttention cache layer has not been initialized")
+        return self.k_fp16[:, :, : self.seq_len]
+
+    def value_view(self) -> torch.Tensor:
+        if self.v_fp16 is None:
+            raise RuntimeError("ThriftAttention cache layer has not been initialized")
+        return self.v_fp16[:, :, : self.seq_len]
+
+    def kernel_len(self) -> int:
+        """Tokens the kernels walk: ``seq_len`` rounded up to whole 64-token blocks (at least one)."""
+        return max(PAGE, _round_up(self.seq_len, PAGE))
+
+    def packed_views(self) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+        """``(k_packed, v_packed_t, k_scale, v_scale_t)`` cut to the kernel length (V to a multiple of
+        128 tokens).  The rows between ``seq_len`` and the rounded length are zero rows."""
+        if self.k_packed is None or self.k_scale is None:
+            raise RuntimeError("ThriftAttention packed K cache has not been initialized")
+        if self.v_packed_t is None or self.v_scale_t is None:
+            raise RuntimeError("ThriftAttention packed V cache has not been initialized")
+        kernel_len = self.kernel_len()
+        v_len = _round_up(kernel_len, CAPACITY_QUANTUM)
+        g = _group_size(self.quant_format)
+        return (self.k_packed[:, :, :kernel_len], self.v_packed_t[:, :, :, : v_len // 2],
+                self.k_scale[:, :, :kernel_len], self.v_scale_t[:, :, :, : v_len // g])
+
+    def hi_kernel_views(self) -> tuple[torch.Tensor, torch.Tensor]:
+        """16-bit K/V cut to the kernel length (the rounded tail is zero)."""
+        if self.k_fp16 is None or self.v_fp16 is None:
+            raise RuntimeError("ThriftAttention cache layer has not been initialized")
+        n = self.kernel_len()
+        return self.k_fp16[:, :, :n], self.v_fp16[:, :, :n]
+
+    # --------------------------------------------------------------------------------------- selection
+    def select_key_blocks(self, q_grouped: torch.Tensor, *, top_k: int | None, fraction: float | None,
+                          block_size: int, selection: str = "block_mean", sink_blocks: int = 0,
+                          local_blocks: int = 0) -> torch.Tensor:
+        """Blocks of this layer to read in 16-bit for one decode step: int32 ``[batch * kv_heads, width]``.
+
+        Candidates are the COMPLETE blocks only (the trailing partial block stays FP4); the count comes
+        from ``resolve_top_k`` with the non-causal rule (transformers_cache.py:152-212).  ``selection``
+        is ``"block_mean"`` (score = q . mean(K block), the reference's policy) or ``"quest"``."""
+        complete_blocks = self.seq_len // block_size
+        selected_count = resolve_top_k(complete_blocks, causal=False, top_k=top_k, fraction=fraction)
+        batch, kv_heads, _, _ = q_grouped.shape
+        if selected_count == 0:
+            return torch.empty(batch * kv_heads, 0, device=q_grouped.device, dtype=torch.int32)
+        quest = selection == "quest"
+        stat_a, stat_b = (self.k_min, self.k_max) if quest else (self.k_mean, None)
+        if stat_a is None or (quest and stat_b is None):
+            raise RuntimeError("ThriftAttention K block means have not been initialized" if not quest else
+                               "ThriftAttention K block minima/maxima have not been initialized")
+        if q_grouped.dtype != stat_a.dtype:
+            raise ValueError("q_grouped and cached K means must have the same dtype")
+        is_bf16 = q_grouped.dtype == torch.bfloat16
+        # forced blocks never push the list beyond the number of candidates
+        local = max(0, min(local_blocks, complete_blocks - selected_count))
+        sink = max(0, min(sink_blocks, complete_blocks - selected_count - local))
+        if complete_blocks <= 2048:
+            width = selected_count + sink + local
+            shape = (batch * kv_heads, width)
+            if (self.selected_blocks is None or tuple(self.selected_blocks.shape) != shape
+                    or self.selected_blocks.device != q_grouped.device):
+                self.selected_blocks = torch.empty(shape, device=q_grouped.device, dtype=torch.int32)
+            return get_extension().select_decode_blocks(q_grouped, stat_a, stat_b, selected_count, complete_blocks,
+                                                        is_bf16, sink=sink, local=local, out=self.selected_blocks)
+        # longer than the selection kernel's 2048-block limit: tensor code, as the reference does
+        qf = q_grouped.float().unsqueeze(3)                                     # [B, Hkv, G, 1, D]
+        if quest:
+            bound = torch.where(qf >= 0, self.k_max[:, :, :complete_blocks].float().unsqueeze(2),
+                                self.k_min[:, :, :complete_blocks].float().unsqueeze(2))
+            scores = (qf * bound).sum(-1)
+        else:
+            scores = torch.matmul(q_grouped.float(), self.k_mean[:, :, :complete_blocks].float().transpose(-1, -2))
+        scores = scores.amax(dim=2).reshape(batch * kv_heads, complete_blocks)
+        return scores.topk(selected_count, dim=-1).indices.to(torch.int32).contiguous()
+
+    # ------------------------------------------------------------------------- batch-dimension surgery
+    def reorder(self, beam_idx: torch.Tensor) -> None:
+        self._index_select_batch(beam_idx)
+
+    def batch_select_indices(self, indices: torch.Tensor) -> None:
+        self._index_select_batch(indices)
+
+    def batch_repeat_interleave(self, repeats: int) -> None:
+        for name in self._tensor_names():
+            tensor = getattr(self, name)
+            if tensor is not None:
+                setattr(self, name, tensor.repeat_interleave(repeats, dim=0))
+        self.selected_blocks = None
+
+    def _index_select_batch(self, indices: torch.Tensor) -> None:
+        for name in self._tensor_names():
+            tensor = getattr(self, name)
+            if tensor is not None:
+                setattr(self, name, tensor.index_select(0, indices.to(tensor.device)))
+        self.selected_blocks = None
+
+    @staticmethod
+    def _tensor_names() -> tuple[str, ...]:
+        return ("k_fp16", "v_fp16", "k_packed", "k_scale", "v_packed_t", "v_scale_t", "k_mean", "k_min", "k_max")
+
+    # ------------------------------------------------------------------------------------ crop / reset
+    def crop(self, max_length: int) -> None:
+        """Shorten the logical length (negative = drop that many tokens) and return the rounded physical
+        tail to zero rows, so that the kernels' rounded views stay well defined."""
+        if max_length < 0:
+            max_length = max(self.seq_len + max_length, 0)
+        new_len = min(self.seq_len, max_length)
+        if new_len < self.seq_len:
+            self._zero_physical_tail(new_len)
+        self.seq_len = new_len
+
+    def reset(self) -> None:
+        self.seq_len = 0
+
+    def _zero_physical_tail(self, logical_len: int) -> None:
+        # K is cleared up to the next 64-token boundary, V up to the next 128-token boundary
+        # (transformers_cache.py:237-253); both ranges are then re-quantised.
+        if self.k_fp16 is None or self.v_fp16 is None:
+            return
+        key_end = min(max(PAGE, _round_up(logical_len, PAGE)), self.k_fp16.shape[2])
+        value_end = min(_round_up(key_end, CAPACITY_QUANTUM), self.v_fp16.shape[2])
+        if logical_len < key_end:
+            self.k_fp16[:, :, logical_len:key_end].zero_()
+            if self.k_packed is not None and self.k_scale is not None:
+                self._quantize_k_range(self.k_fp16[:, :, logical_len:key_end].contiguous(), logical_len, key_end)
+        if logical_len < value_end:
+            self.v_fp16[:, :, logical_len:value_end].zero_()
+            if self.v_packed_t is not None and self.v_scale_t is not None:
+                self._quantize_v_range(logical_len, value_end)
+
+    def _quantize_k_range(self, key_states: torch.Tensor, start: int, end: int) -> None:
+        """Store and quantise K rows ``[start, end)``; no statistics refresh."""
+        self._append(key_states, None, start, v_count=0, stats=False)
+
+    def _quantize_v_range(self, start: int, end: int) -> None:
+        """Re-quantise every V group overlapping ``[start, end)`` from the 16-bit cache."""
+        self._append(None, None, start, k_count=0, v_count=end - start, keep_v=True, stats=False)
+
+    def _refresh_k_means(self, start: int, end: int) -> None:
+        """Recompute the statistics of the 64-token blocks lying entirely inside ``[start // 64 * 64, end)``."""
+        self._append(None, None, start, k_count=end - start, v_count=0, keep_k=True)
+
+    # ---------------------------------------------------------------------------------------- capacity
+    def _ensure_capacity(self, like: torch.Tensor, required: int) -> None:
+        """Allocate or grow every tensor to hold ``required`` tokens.  The first allocation takes
+        ``max_cache_len`` when it is known, else 64 tokens; later ones double; the result is rounded up to
+        128 tokens and never exceeds ``max_cache_len`` rounded up to 128 (transformers_cache.py:255-306)."""
+        if self.k_fp16 is not None:
+            if like.shape[0] != self.k_fp16.shape[0] or like.shape[1] != self.k_fp16.shape[1]:
+                raise ValueError("ThriftAttentionCache batch/head shape changed unexpectedly")
+            if like.dtype != self.k_fp16.dtype:
+                raise ValueError("ThriftAttentionCache dtype changed unexpectedly")
+            if required <= self.capacity:
+                return
+
+        batch, heads, _, head_dim = like.shape
+        limit = self.max_cache_len
+        if self.capacity == 0:
+            wanted = limit if limit is not None else PAGE
+        else:
+            wanted = self.capacity * 2
+        wanted = max(wanted, required)
+        if limit is not None:
+            wanted = min(wanted, limit)
+        new_capacity = _round_up(wanted, CAPACITY_QUANTUM)
+        if limit is not None:
+            new_capacity = min(new_capacity, _round_up(limit, CAPACITY_QUANTUM))
+        if new_capacity < required:
+            raise ValueError("could not grow ThriftAttentionCache to required length")
+
+        g = _group_size(self.quant_format)
+        dev = like.device
+        fresh = {
+            "k_fp16": torch.zeros(batch, heads, new_capacity, head_dim, device=dev, dtype=like.dtype),
+            "v_fp16": torch.zeros(batch, heads, new_capacity, head_dim, device=dev, dtype=like.dtype),
+            "k_packed": torch.zeros(batch, heads, new_capacity, head_dim // 2, device=dev, dtype=torch.uint8),
+            "k_scale": torch.zeros(batch, heads, new_capacity, head_dim // g, device=dev, dtype=torch.uint8)
+            .view(_scale_dtype(self.quant_format)),
+            "v_packed_t": torch.zeros(batch, heads, head_dim, new_capacity // 2, device=dev, dtype=torch.uint8),
+            "v_scale_t": torch.zeros(batch, heads, head_dim, new_capacity // g, device=dev, dtype=torch.uint8)
+            .view(_scale_dtype(self.quant_format)),
+            "k_mean": torch.zeros(batch, heads, new_capacity // PAGE, head_dim, device=dev, dtype=like.dtype),
+        }
+        if self.track_minmax:
+            fresh["k_min"] = torch.zeros_like(fresh["k_mean"])
+            fresh["k_max"] = torch.zeros_like(fresh["k_mean"])
+
+        if self.k_fp16 is not None:
+            old = self.capacity
+            for name in ("k_fp16", "v_fp16", "k_packed"):
+                fresh[name][:, :, :old] = getattr(self, name)
+            fresh["v_packed_t"][:, :, :, : old // 2] = self.v_packed_t
+            fresh["v_scale_t"].view(torch.uint8)[:, :, :, : old // g] = self.v_scale_t.view(torch.uint8)
+            for name in ("k_mean", "k_min", "k_max"):
+                if name in fresh and getattr(self, name) is not None:
+                    fresh[name][:, :, : old // PAGE] = getattr(self, name)
+            # fp8 tensors do not support slice assignment on every build: go through uint8 views
+            fresh["k_scale"].view(torch.uint8)[:, :, :old] = self.k_scale.view(torch.uint8)
+
+        for name, tensor in fresh.items():
+            setattr(self, name, tensor)
+        self.capacity = new_capacity
+        self.selected_blocks = None
+
+
+class ThriftAttentionCache:
+    """Cache object handed to ``model(..., past_key_values=cache)``: one ``ThriftAttentionCacheLayer``
+    per attention layer plus the Transformers cache protocol (``update``, ``get_seq_length``,
+    ``get_mask_sizes``, ``crop``, ``reset``, ``reorder_cache``, ``batch_*``).  It implements the protocol
+    directly instead of subclassing, because the base-class constructor differs between
+    Transformers releases (transformers_cache.py:478-567)."""
+
+    def __init__(self, *, config: AttentionConfig | None = None, max_cache_len: int | None = None) -> None:
+        self.config = config or AttentionConfig()
+        self._max_cache_len = max_cache_len
+        self.layers: list[ThriftAttentionCacheLayer] = []
+        self._seen_tokens = 0
+        self.prefill_real_seq_len: int | None = None
+
+    @classmethod
+    def from_model(cls, model: object, *, config: AttentionConfig | None = None,
+                   max_cache_len: int | None = None) -> "ThriftAttentionCache":
+        if max_cache_len is None:
+            max_cache_len = getattr(getattr(model, "config", None), "max_position_embeddings", None)
+        return cls(config=config, max_cache_len=max_cache_len)
+
+    # ------------------------------------------------------------------------------------ properties
+    @property
+    def seen_tokens(self) -> int:
+        return self._seen_tokens
+
+    @property
+    def max_cache_len(self) -> int | None:
+        return self._max_cache_len
+
+    @property
+    def is_compileable(self) -> bool:
+        return False
+
+    @property
+    def is_initialized(self) -> bool:
+        return len(self.layers) > 0
+
+    @property
+    def is_sliding(self) -> list[bool]:
+        return [False for _ in self.layers]
+
+    @property
+    def max_batch_size(self) -> int | None:
+        for layer in self.layers:
+            if layer.k_fp16 is not None:
+                return int(layer.k_fp16.shape[0])
+        return None
+
+    # -------------------------------------------------------------------------------------- protocol
+    def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int | None = None,
+               cache_kwargs: dict[str, Any] | None = None, **_: Any) -> tuple[torch.Tensor, torch.Tensor]:
+        if layer_idx is None:
+            raise ValueError("ThriftAttentionCache.update requires layer_idx")
+        layer = self.layer(layer_idx)
+        key, value = layer.update(key_states, value_states, cache_kwargs)
+        if layer_idx == 0:
+            self._seen_tokens = layer.seq_len
+        return key, value
+
+    def layer(self, layer_idx: int) -> ThriftAttentionCacheLayer:
+        while len(self.layers) <= layer_idx:
+            self.layers.append(ThriftAttentionCacheLayer(
+                max_cache_len=self._max_cache_len,
+                quant_format=self.config.quant_format,
+                track_minmax=self.config.selection == "quest"))
+        return self.layers[layer_idx]
+
+    def get_seq_length(self, layer_idx: int = 0) -> int:
+        return self.layers[layer_idx].seq_len if layer_idx < len(self.layers) else 0
+
+    def get_mask_sizes(self, query_length: int, layer_idx: int) -> tuple[int, int]:
+        if layer_idx >= len(self.layers):
+            return query_length, 0
+        return self.layers[layer_idx].seq_len + query_length, 0
+
+    def get_max_cache_shape(self) -> int | None:
+        return self._max_cache_len
+
+    def get_max_length(self) -> int | None:
+        return self._max_cache_len
+
+    def get_usable_length(self, new_seq_length: int, layer_idx: int = 0) -> int:
+        previous = self.get_seq_length(layer_idx)
+        if self._max_cache_len is None or previous + new_seq_length <= self._max_cache_len:
+            return previous
+        return max(self._max_cache_len - new_seq_length, 0)
+
+    def reorder_cache(self, beam_idx: torch.Tensor) -> None:
+        for layer in self.layers:
+            layer.reorder(beam_idx)
+
+    def batch_select_indices(self, indices: torch.Tensor) -> None:
+        for layer in self.layers:
+            layer.batch_select_indices(indices)
+
+    def batch_repeat_interleave(self, repeats: int) -> None:
+        for layer in self.layers:
+            layer.batch_repeat_interleave(repeats)
+
+    def crop(self, max_length: int) -> None:
+        for layer in self.layers:
+            layer.crop(max_length)
+        self._seen_tokens = self.get_seq_length(0)
+
+    def reset(self) -> None:
+        for layer in self.layers:
+            layer.reset()
+        self._seen_tokens = 0
+
+    def to_legacy_cache(self) -> tuple[tuple[torch.Tensor, torch.Tensor], ...]:
+        return tuple((layer.key_view(), layer.value_view()) for layer in self.layers)
+
+    def __getitem__(self, layer_idx: int) -> tuple[torch.Tensor, torch.Tensor]:
+        layer = self.layer(layer_idx)
+        return layer.key_view(), layer.value_view()
+
+    def __len__(self) -> int:
+        return len(self.layers)
+
+
+# ------------------------------------------------------------------------------------------------
+# Attention over the cache
+# ------------------------------------------------------------------------------------------------
+def _layer_format(layer: ThriftAttentionCacheLayer, config: AttentionConfig):
+    quant_format = get_quant_format(config.quant_format)          # NotImplementedError for unknown names
+    if quant_format.name != layer.quant_format:
+        raise ValueError(f"cache layer holds {layer.quant_format!r} codes but the call asks for {quant_format.name!r}")
+    return quant_format
+
+
+def cached_decode_attention(query: torch.Tensor, cache: ThriftAttentionCache, layer_idx: int,
+                            config: AttentionConfig) -> torch.Tensor:
+    """One decode step ``[B, Hq, 1, D]`` over layer ``layer_idx`` of ``cache``; returns ``[B, Hq, 1, D]``.
+
+    Launches: quantise the grouped query, select blocks, split-KV attention (+ its merge).  K and V are
+    read in place through capacity-strided views — nothing is copied (transformers_cache.py:570-619)."""
+    layer = cache.layer(layer_idx)
+    if layer.seq_len == 0:
+        raise RuntimeError("ThriftAttention decode cache is empty")
+    quant_format = _layer_format(layer, config)
+
+    q = query.contiguous()
+    is_bf16 = q.dtype == torch.bfloat16
+    kv_heads = layer.key_view().shape[1]
+    q_grouped = _group_single_query(q, kv_heads)
+    q_packed, q_scale = quant_format.quantize(q_grouped, is_bf16=is_bf16)
+    k_packed, v_packed_t, k_scale, v_scale_t = layer.packed_views()
+    ext = get_extension()
+    fmt = quant_format.name
+
+    if config.method == "fp4":
+        out = getattr(ext, f"fp4_attention_single_query_{fmt}_packed")(q_packed, k_packed, v_packed_t, q_scale, k_scale,
+                                                                       v_scale_t, is_bf16)
+        return _ungroup_single_query(out, q.shape[1])
+    if config.method != "thrift":
+        raise ValueError(f"unsupported ThriftAttention method {config.method!r}")
+
+    selected_blocks = select_cached_decode_blocks(q_grouped, layer, config)
+    out = getattr(ext, f"thrift_attention_single_query_{fmt}_packed")(
+        q_grouped, layer.key_view(), layer.value_view(), selected_blocks, q_packed, k_packed, v_packed_t, q_scale,
+        k_scale, v_scale_t, is_bf16)
+    return _ungroup_single_query(out, q.shape[1])
+
+
+def cached_prefill_attention(query: torch.Tensor, cache: ThriftAttentionCache, layer_idx: int,
+                             config: AttentionConfig) -> torch.Tensor:
+    """Prefill ``[B, Hq, Sq, D]`` against the K/V that ``update`` has just stored in layer ``layer_idx``.
+
+    The reference re-quantises the whole K and V into the tiled kernel's own layouts here
+    (transformers_cache.py:622-680).  The sm_100a prefill kernel reads plain K rows and capacity
+    strides, so only the query is quantised and K/V codes, scales and block statistics come straight
+    from the cache."""
+    layer = cache.layer(layer_idx)
+    quant_format = _layer_format(layer, config)
+    q = query.contiguous()
+    is_bf16 = q.dtype == torch.bfloat16
+    q_packed, q_scale = quant_format.quantize(q, is_bf16=is_bf16)
+    k_packed, v_packed_t, k_scale, v_scale_t = layer.packed_views()
+    k_hi, v_hi = layer.hi_kernel_views()
+    ext = get_extension()
+    common = dict(causal=config.causal, is_mx=quant_format.name == "mxfp4", is_bf16=is_bf16,
+                  block_size=config.block_size, k_permuted=False)
+
+    if config.method == "fp4":
+        return ext.prefill_attention(None, None, None, None, q_packed, k_packed, v_packed_t, q_scale, k_scale,
+                                     v_scale_t, **common)
+    if config.method != "thrift":
+        raise ValueError(f"unsupported ThriftAttention method {config.method!r}")
+
+    selected_blocks = select_cached_prefill_blocks(q, layer.key_view(), layer, config,
+                                                   real_q_len=cache.prefill_real_seq_len, is_bf16=is_bf16)
+    return ext.prefill_attention(q, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale,
+                                 v_scale_t, **common)
+
+
+# ------------------------------------------------------------------------------------------------
+# Selection over the cache
+# ------------------------------------------------------------------------------------------------
+def select_cached_decode_blocks(q_grouped: torch.Tensor, layer: ThriftAttentionCacheLayer,
+                                config: AttentionConfig) -> torch.Tensor:
+    if config.selection in ("block_mean", "quest"):
+        return select_topk_key_blocks(q_grouped, layer, config)
+    if config.selection == "local":
+        return select_local_key_blocks(q_grouped, layer, config)
+    raise ValueError(f"unsupported cached decode selection {config.selection!r}")
+
+
+def select_topk_key_blocks(q_grouped: torch.Tensor, layer: ThriftAttentionCacheLayer,
+                           config: AttentionConfig) -> torch.Tensor:
+    extra = {}
+    if config.selection == "quest":
+        extra["selection"] = "quest"
+    if getattr(config, "sink_blocks", 0) or getattr(config, "local_blocks", 0):
+        extra.update(sink_blocks=config.sink_blocks, local_blocks=config.local_blocks)
+    return layer.select_key_blocks(q_grouped, top_k=config.top_k, fraction=config.fraction,
+                                   block_size=config.block_size, **extra)
+
+
+def select_local_key_blocks(q_grouped: torch.Tensor, layer: ThriftAttentionCacheLayer,
+                            config: AttentionConfig) -> torch.Tensor:
+    """The most recent complete blocks (transformers_cache.py:714-731)."""
+    complete_blocks = layer.seq_len // config.block_size
+    selected_count = resolve_top_k(complete_blocks, causal=False, top_k=config.top_k, fraction=config.fraction)
+    flat_heads = q_grouped.shape[0] * q_grouped.shape[1]
+    if selected_count == 0:
+        return torch.empty(flat_heads, 0, device=q_grouped.device, dtype=torch.int32)
+    return get_extension().single_query_local_topk(q_grouped, selected_count, complete_blocks)
+
+
+def select_cached_prefill_blocks(q: torch.Tensor, k: torch.Tensor, layer: ThriftAttentionCacheLayer,
+                                 config: AttentionConfig, real_q_len: int | None = None,
+                                 is_bf16: bool = False) -> torch.Tensor:
+    if config.selection in ("block_mean", "quest"):
+        return _select_block_pairs_from_cached_stats(q, layer, config, real_q_len=real_q_len, is_bf16=is_bf16)
+    if config.selection == "local":
+        return select_local_block_pairs(q, k, causal=config.causal, top_k=config.top_k, fraction=config.fraction,
+                                        block_size=config.block_size, is_bf16=is_bf16)
+    raise ValueError(f"unsupported cached prefill selection {config.selection!r}")
+
+
+def _query_block_means(q: torch.Tensor, block_size: int, real_q_len: int | None) -> torch.Tensor:
+    """Mean query of every q block, 16-bit ``[B, Hq, Sq/block, D]``.  With ``real_q_len`` shorter than the
+    (padded) query, padding rows are left out: the partial block averages its real rows only and blocks
+    made of padding alone are zero (transformers_cache.py:789-808)."""
+    batch, q_heads, q_len, head_dim = q.shape
+    q_mean, _, _ = get_extension().block_stats(q, block_size, mean=True)
+    if real_q_len is None or real_q_len >= q_len:
+        return q_mean
+    real_q_len = max(0, int(real_q_len))
+    full_blocks, tail = divmod(real_q_len, block_size)
+    if tail:
+        rows = q[:, :, full_blocks * block_size: full_blocks * block_size + tail].float()
+        q_mean[:, :, full_blocks] = (rows.sum(dim=2) / tail).to(q_mean.dtype)
+        q_mean[:, :, full_blocks + 1:] = 0
+    else:
+        q_mean[:, :, full_blocks:] = 0
+    return q_mean
+
+
+def _select_block_pairs_from_cached_stats(q: torch.Tensor, layer: ThriftAttentionCacheLayer, config: AttentionConfig,
+                                          real_q_len: int | None = None, is_bf16: bool = False) -> torch.Tensor:
+    """Per-q-block top-k from the statistics the cache already holds (transformers_cache.py:761-831);
+    ``[B * Hq, Sq/block, width]`` int32, -1 padded under the causal mask."""
+    quest = config.selection == "quest"
+    if (layer.k_min is None or layer.k_max is None) if quest else layer.k_mean is None:
+        raise RuntimeError("ThriftAttention K block means have not been initialized")
+    block_size = config.block_size
+    batch, q_heads, q_len, head_dim = q.shape
+    num_q_blocks = q_len // block_size
+    num_kv_blocks = layer.seq_len // block_size
+    selected_count = resolve_top_k(num_kv_blocks, causal=config.causal, top_k=config.top_k, fraction=config.fraction)
+    if selected_count == 0:
+        return torch.empty(batch * q_heads, num_q_blocks, 0, device=q.device, dtype=torch.int32)
+
+    q_mean = _query_block_means(q, block_size, real_q_len)
+    ext = get_extension()
+    if block_size == PAGE:
+        stats = [t[:, :, :num_kv_blocks].contiguous() for t in ((layer.k_min, layer.k_max) if quest else (layer.k_mean,))]
+    else:   # statistics of wider blocks are recomputed from the 16-bit keys
+        k = layer.key_view()[:, :, : num_kv_blocks * block_size].contiguous()
+        mean, k_min, k_max = ext.block_stats(k, block_size, mean=not quest, minmax=quest)
+        stats = [k_min, k_max] if quest else [mean]
+
+    if num_kv_blocks > 2048:
+        raise NotImplementedError("ThriftAttention currently supports at most 2048 selected KV blocks")
+    sink = getattr(config, "sink_blocks", 0)
+    local = getattr(config, "local_blocks", 0)
+    if sink or local:
+        return ext.select_prefill_blocks(q_mean, stats[0], stats[1] if quest else None, selected_count, config.causal,
+                                         is_bf16, sink=sink, local=local)
+    if quest:
+        return ext.quest_block_topk(q_mean, stats[0], stats[1], selected_count, config.causal, is_bf16)
+    return ext.block_mean_topk(q_mean, stats[0], selected_count, config.causal, is_bf16)
