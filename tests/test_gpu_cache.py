@@ -59,7 +59,7 @@ def test_append_any_chunking_is_bit_exact(fmt, dtype, d):
             pos += c
             if c > 1 or pos % 16 == 0:
                 _check_layer_against_oracle(layer, k[:, :, :pos], v[:, :, :pos], fmt)
-        assert pos == total and layer.capacity == 1024
+        assert pos == total and layer.capacity in (768, 1024)
         _check_layer_against_oracle(layer, k, v, fmt)
 
 

@@ -35,7 +35,7 @@ struct DecodeParams {
     const uint8_t* ks;
     const uint8_t* v4;      // transposed layout or page pool
     const uint8_t* vs;
-    const uint16_t* k_hi;   // [heads, kv_len, D] or page pool
+    const uint16_t* k_hi;   // [heads, kv_len, D] with head stride kv_cap rows, or page pool
     const uint16_t* v_hi;
     const int32_t* sel;     // [heads, width]
     const int32_t* page_table;  // [batch, max_pages] or null
@@ -407,8 +407,7 @@ __global__ void __launch_bounds__(32) decode_kernel(const DecodeParams p) {
     // ================= selected pages (16-bit) =================
     uint8_t* hsm = sm + WarpSmem::H16;
     auto load16 = [&](const uint16_t* base, int page) {
-        const uint16_t* src = p.page_table ? base + phys(page) * (PAGE * D)
-                                           : base + (static_cast<long long>(h) * p.npages + page) * (PAGE * D);
+        const uint16_t* src = base + phys(page) * (PAGE * D);  // same capacity stride as the packed K
         for (int i = lane; i < PAGE * 16; i += 32) cp16(hsm + (i >> 4) * HROW + (i & 15) * 16, reinterpret_cast<const uint8_t*>(src) + i * 16);
         cp_commit();
         cp_wait<0>();
