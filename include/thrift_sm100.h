@@ -216,6 +216,16 @@ int ta100_decode_attention_static(const void* q_hi, const void* k_hi, const void
                                   void* stream);
 
 /*
+ * Device status of the decode kernels on the current device.  Every wait inside the kernel is
+ * bounded; when one runs out the kernel drains, releases its tensor memory and raises a flag.
+ * This call synchronises with `stream`, returns TA100_ERR_DEVICE_TIMEOUT if the flag was raised
+ * since the previous call (and clears it), else TA100_OK.  The reference kernels have no
+ * counterpart: their launches are not checked at all
+ * (csrc/cuda/sm120/nvfp4/single_query_attention.cu launch sites).
+ */
+int ta100_decode_status(void* stream);
+
+/*
  * Log-sum-exp merge of decode partials from `shards` producers (e.g. GPUs that each hold a slice
  * of the KV sequence): part_o [shards, flat_kv_heads, splits, group, D], part_ml [.., 2] ->
  * out [flat_kv_heads, group, D].  Same formula as the reference's in-kernel merge

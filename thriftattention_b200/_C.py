@@ -519,6 +519,15 @@ def decode_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_pa
     return out
 
 
+def decode_status(device=None) -> None:
+    """Raises ``RuntimeError`` if a bounded wait inside a decode kernel ran out on ``device`` since the
+    last call (synchronises with the current stream)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        rc = _lib.load().ta100_decode_status(ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    _lib.check(rc, "decode_attention (device)")
+
+
 def merge_decode_partials(part_o: torch.Tensor, part_ml: torch.Tensor, *, is_mx: bool, is_bf16: bool = False):
     """LSE merge of decode partials gathered from several shards.
 

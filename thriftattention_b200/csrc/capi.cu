@@ -25,6 +25,7 @@ int decode_dispatch(const void*, const void*, const void*, const void*, int, con
                     const void*, const void*, const void*, const void*, int, void*, void*, void*, int, int, int, int, int,
                     int, int, int, int, int, cudaStream_t);
 int merge_dispatch(const void*, const void*, void*, int, long long, int, int, int, int, int, cudaStream_t);
+int decode_status(cudaStream_t);
 size_t decode_static_scratch_bytes();
 int decode_static_dispatch(const void*, const void*, const void*, const void*, int, const void*, const void*, const void*,
                            const void*, const void*, const void*, const void*, int, void*, int, int, int, int, int, int, int,
@@ -136,6 +137,8 @@ int ta100_decode_attention(const void* q_hi, const void* k_hi, const void* v_hi,
                            part_ml, batch, hkv, group, kv_len, kv_cap, head_dim, is_mxfp4, is_bf16, splits, write_out,
                            S(stream));
 }
+
+int ta100_decode_status(void* stream) { return decode_status(S(stream)); }
 
 int ta100_merge_partials(const void* part_o, const void* part_ml, void* out, int shards, long long flat_kv_heads,
                          int splits, int group, int head_dim, int is_mxfp4, int is_bf16, void* stream) {

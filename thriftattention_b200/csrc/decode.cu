@@ -1,522 +1,605 @@
 // Single-token (decode) selective mixed-precision attention, split over the KV
 // sequence, plus the log-sum-exp merge of the partial results.
 //
-// Work decomposition: one warp (= one CTA) per chain; chain s of a (sequence,
-// KV head) pair walks pages [s*n/S, (s+1)*n/S) of 64 tokens: first the pages that
-// are NOT selected (FP4 K/V, P re-quantised to e2m1 with a per-group dynamic
-// scale), ascending, then the selected pages (16-bit K/V), ascending.  Rows of
-// the problem are the G <= 8 query heads that share the KV head.
+// One CTA per chain: chain s of a (sequence, KV head) pair walks pages
+// [s*n/S, (s+1)*n/S) of 64 tokens — first the pages that are NOT selected (FP4 K/V),
+// ascending, then the selected pages (16-bit K/V), ascending.  The kernel is
+// HBM-bound, so the arithmetic is kept off the instruction pipes:
+//   * pages arrive by TMA (tiled tensor maps over the contiguous cache or the page
+//     pools) into a ring of shared-memory slots;
+//   * S = Q K^T and O += P V are tcgen05 MMAs — block-scaled FP4 (the tensor core
+//     applies the E4M3 / E8M0 scales) or f16/bf16 — with accumulators in tensor memory.
+// The query group is tiny (G <= 16 heads), the MMA tile has 128 rows: every head is
+// stored FOUR times, in rows 32*w + 4*i + c (head g = 4*i + w, c = 0..3), and the thread
+// that owns row (g, c) handles token columns [16c, 16c+16) of each page.  Its P row is
+// zero outside those columns, so the four O rows of a head are partial sums that are
+// added once, at the end of the chain.  All four use the running row maximum of the
+// whole 64-token page, as the reference does, because the quantisation of P
+// (dynamic scale per 16 / 32 tokens, codes computed with the un-rounded scale) depends
+// on it.
 //
-// The kernel is HBM-bound; pages are streamed with cp.async into per-warp
-// double buffers.  FP4 operands are dequantised exactly to f16 in registers
-// (e2m1 x E4M3 products fit f16; for MXFP4 the E8M0 scales are applied in fp32
-// per 32-wide group) and multiplied with mma.sync.m16n8k16, with the KV tokens
-// (or head channels) on the M side and the query heads on the N side.
+// Warp roles (192 threads): warp 0 = page list + TMA producer, warp 1 = MMA issuer and
+// tensor-memory owner, warps 2..5 = softmax (they also bring the K and V block scales of
+// every page into the 512-byte atom order the tensor core reads).  Two CTAs share an SM.
+// Every mbarrier wait is bounded; a timeout raises a CTA-wide abort flag, all roles
+// drain, tensor memory is released and a status word is set.
 #include <cfloat>
+#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace ta100 {
 
 namespace {
 
 constexpr int PAGE = 64;
-constexpr int KROW = 80;    // padded shared-memory row of a 64-byte FP4 K row
-constexpr int VROW = 48;    // padded row of a 32-byte FP4 V^T row
-constexpr int HROW = 272;   // padded row of a 256-byte 16-bit row (D = 128)
-constexpr int PROW = 72;    // f16 elements per row of the P staging tile (64 + 8)
+constexpr int DEC_THREADS = 192;
+constexpr int DEC_NSLOTS = 3;
+constexpr int DEC_SLOT_BYTES = 16384;   // one FP4 page (K4, V4, scale atoms) or one 16-bit K or V page
+constexpr int DEC_LIST_CAP = 1024;      // pages per chain
+constexpr int DEC_MAX_GROUP = 16;
+
+// tensor-memory columns (256 allocated per CTA)
+constexpr uint32_t DTM_O = 0;           // 128 columns
+constexpr uint32_t DTM_S = 128;         // 64 columns
+constexpr uint32_t DTM_SFA_Q = 192;     // up to 8 columns
+constexpr uint32_t DTM_SFB_K = 200;     // up to 8 columns
+constexpr uint32_t DTM_SFA_P = 208;     // two buffers of 4 columns
+constexpr uint32_t DTM_SFB_V = 216;     // two buffers of 4 columns
+constexpr uint32_t DTM_COLS = 256;
+
+constexpr uint32_t L_FP16 = 0x80000000u;  // page-list flag: 16-bit page
+
+__device__ int g_decode_status;           // set to 1 by a kernel whose bounded wait ran out
 
 struct DecodeParams {
     const uint16_t* q_hi;   // [heads, G, D]
     const uint8_t* q4;      // [heads, G, D/2]
     const uint8_t* qs;      // [heads, G, D/g]
-    const uint8_t* k4;      // rows layout or page pool
-    const uint8_t* ks;
-    const uint8_t* v4;      // transposed layout or page pool
-    const uint8_t* vs;
-    const uint16_t* k_hi;   // [heads, kv_len, D] with head stride kv_cap rows, or page pool
-    const uint16_t* v_hi;
+    const uint8_t* ks;      // K block scales: rows layout or page pool
+    const uint8_t* vs;      // V block scales: transposed layout or page pool
     const int32_t* sel;     // [heads, width]
     const int32_t* page_table;  // [batch, max_pages] or null
     float* part_o;          // [heads, splits, G, D]
     float* part_ml;         // [heads, splits, G, 2]
     int heads, hkv, G, npages, cap_pages, max_pages, width, splits;
-    long long v_head_stride;   // bytes between heads in v4 (contiguous layout)
-    long long vs_head_stride;
-    int v_row_stride, vs_row_stride;  // bytes between channel rows
-    float sm_scale;
+    int vs_row_stride;      // bytes between channel rows of vs (contiguous layout)
+    float c2;               // (1/sqrt(d)) * log2(e)
+    float sm_scale;         // 1/sqrt(d)
+    long long budget;
 };
 
-__device__ __forceinline__ void cp16(void* smem_dst, const void* gsrc) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
-                 "l"(gsrc));
-}
-__device__ __forceinline__ void cp4(void* smem_dst, const void* gsrc) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
-                 "l"(gsrc));
-}
-__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-// one byte of two e2m1 codes -> f16x2 (low nibble in the low half), exact
-__device__ __forceinline__ uint32_t e2m1x2_to_h2(uint32_t byte) {
-    uint32_t r;
-    asm("{\n\t.reg .b8 b;\n\tcvt.u8.u32 b, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, b;\n\t}\n" : "=r"(r) : "r"(byte));
-    return r;
-}
-__device__ __forceinline__ uint32_t h2mul(uint32_t a, uint32_t b) {
-    uint32_t r;
-    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-    return r;
-}
-__device__ __forceinline__ uint32_t f2h2(float lo, float hi) {
-    __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-__device__ __forceinline__ void mma_f16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-// A fragment for two consecutive k16 chunks from one 32-bit word of 8 e2m1 codes per row:
-// codes 0,1 / 2,3 feed chunk 0 (k slots 2t,2t+1 / 2t+8,2t+9), codes 4,5 / 6,7 chunk 1.
-__device__ __forceinline__ void word_to_frags(uint32_t w_lo_row, uint32_t w_hi_row, uint32_t scale_lo_h2,
-                                              uint32_t scale_hi_h2, bool apply_scale, uint32_t (&a0)[4],
-                                              uint32_t (&a1)[4]) {
-    uint32_t l0 = e2m1x2_to_h2(w_lo_row & 0xFF), l1 = e2m1x2_to_h2((w_lo_row >> 8) & 0xFF);
-    uint32_t l2 = e2m1x2_to_h2((w_lo_row >> 16) & 0xFF), l3 = e2m1x2_to_h2(w_lo_row >> 24);
-    uint32_t h0 = e2m1x2_to_h2(w_hi_row & 0xFF), h1 = e2m1x2_to_h2((w_hi_row >> 8) & 0xFF);
-    uint32_t h2 = e2m1x2_to_h2((w_hi_row >> 16) & 0xFF), h3 = e2m1x2_to_h2(w_hi_row >> 24);
-    if (apply_scale) {
-        l0 = h2mul(l0, scale_lo_h2); l1 = h2mul(l1, scale_lo_h2); l2 = h2mul(l2, scale_lo_h2); l3 = h2mul(l3, scale_lo_h2);
-        h0 = h2mul(h0, scale_hi_h2); h1 = h2mul(h1, scale_hi_h2); h2 = h2mul(h2, scale_hi_h2); h3 = h2mul(h3, scale_hi_h2);
-    }
-    a0[0] = l0; a0[1] = h0; a0[2] = l1; a0[3] = h1;
-    a1[0] = l2; a1[1] = h2; a1[2] = l3; a1[3] = h3;
-}
-
-template <bool MX>
-__device__ __forceinline__ uint32_t scale_to_h2(uint8_t b) {
-    const float f = decode_scale<MX>(b);
-    return f2h2(f, f);
-}
-
-// shared-memory carve-up of one warp
-struct WarpSmem {
-    // FP4 phase: two page buffers
-    static constexpr int K4 = 0;                         // [2][64][KROW]
-    static constexpr int KS = K4 + 2 * PAGE * KROW;      // [2][64][8]
-    static constexpr int V4 = KS + 2 * PAGE * 8;         // [2][128][VROW]
-    static constexpr int VS = V4 + 2 * 128 * VROW;       // [2][128][4]
-    static constexpr int FP4_END = VS + 2 * 128 * 4;
-    // 16-bit phase: one page of K or V (aliases the FP4 buffers)
-    static constexpr int H16 = 0;                        // [64][HROW]
-    static constexpr int H16_END = PAGE * HROW;
-    static constexpr int PT = (FP4_END > H16_END ? FP4_END : H16_END);  // P staging [8][PROW] f16
-    static constexpr int FLAGS = PT + 8 * PROW * 2;      // selected-page flags, 1 byte per page (<= 2048)
-    static constexpr int TOTAL = FLAGS + 2048;
+template <int D>
+struct DecSmem {
+    static constexpr int Q4 = 0;                          // 128 x D/2, 64-byte swizzle
+    static constexpr int QSF = Q4 + 128 * D / 2;          // up to 2 atoms
+    static constexpr int Q16 = QSF + 1024;                // 128 x D x 2, two 64-column halves, 128-byte swizzle
+    static constexpr int P = Q16 + 128 * D * 2;           // 16 KB: two 4 KB FP4 buffers or one 16-bit tile
+    static constexpr int SLOTS = P + 16384;
+    static constexpr int PSF = SLOTS + DEC_NSLOTS * DEC_SLOT_BYTES;   // two 512-byte atoms
+    static constexpr int LIST = PSF + 1024;               // DEC_LIST_CAP x u32
+    static constexpr int BITS = LIST + DEC_LIST_CAP * 4;  // 64 words: selected pages of the chain
+    static constexpr int BARS = BITS + 256;
+    static constexpr int TOTAL = BARS + 512;
+    // inside an FP4 slot
+    static constexpr int K4 = 0, V4 = 4096, KSF = 8192, VSF = 9216;
+    static_assert(Q16 % 1024 == 0 && P % 1024 == 0 && SLOTS % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+    static_assert(TOTAL <= 113 * 1024, "two CTAs must fit one SM");
 };
 
-template <bool MX, bool BF16>
-__global__ void __launch_bounds__(32) decode_kernel(const DecodeParams p) {
-    constexpr int D = 128;
-    constexpr int GRP = MX ? 32 : 16;
-    constexpr int SPR = D / GRP;           // K/Q scales per row
-    constexpr float C = MX ? 6.0f : 2688.0f;
-    extern __shared__ __align__(16) uint8_t sm[];
-    const int lane = threadIdx.x, gl = lane >> 2, t = lane & 3;
-    const int split = blockIdx.x, h = blockIdx.y;
-    const int G = p.G;
-    const int b = h / p.hkv, kvh = h - b * p.hkv;
-    const int p_begin = static_cast<int>(static_cast<long long>(split) * p.npages / p.splits);
-    const int p_end = static_cast<int>(static_cast<long long>(split + 1) * p.npages / p.splits);
+struct DecBars {
+    uint64_t q_ready, list_full;
+    uint64_t slot_full[DEC_NSLOTS], slot_empty[DEC_NSLOTS], sf_full[DEC_NSLOTS];
+    uint64_t s_full, s_free;
+    uint64_t p_full[2], p_free[2];
+    uint64_t epi_full;
+    int n_total, n_fp4;
+    uint32_t tmem_base;
+    int abort_flag;
+    float m_row[DEC_MAX_GROUP];
+    float l_part[4][DEC_MAX_GROUP];
+};
+static_assert(sizeof(DecBars) <= 512, "barrier block must fit its shared-memory slot");
 
-    // ---- selected-page flags for this chain ----
-    uint8_t* flags = sm + WarpSmem::FLAGS;
-    for (int i = lane; i < p_end - p_begin; i += 32) flags[i] = 0;
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Page list of one chain (whole warp): FP4 pages ascending, then the selected pages ascending.
+// An entry is the page's addressing key — the physical page times hkv plus the KV head for a page
+// pool, the logical page for a contiguous cache — with L_FP16 set on 16-bit pages.
+__device__ void build_page_list(const DecodeParams& p, int h, int b, int kvh, int p_begin, int p_end, uint32_t* bits,
+                                uint32_t* list, int& n_fp4, int& n_total, int lane) {
+    for (int i = lane; i < 64; i += 32) bits[i] = 0u;
     __syncwarp();
     for (int i = lane; i < p.width; i += 32) {
         const int id = p.sel[static_cast<long long>(h) * p.width + i];
-        if (id >= p_begin && id < p_end) flags[id - p_begin] = 1;
+        if (id >= p_begin && id < p_end) atomicOr(&bits[id >> 5], 1u << (id & 31));
     }
     __syncwarp();
-
-    auto phys = [&](int page) -> long long {
-        return p.page_table ? static_cast<long long>(p.page_table[static_cast<long long>(b) * p.max_pages + page]) * p.hkv + kvh
-                            : static_cast<long long>(h) * p.cap_pages + page;
-    };
-
-    // ---- query fragments (B operands) ----
-    // FP4: per span s (32 channels) and chunk c: b0b1 <- codes 8t+4c+{0,1}, b2b3 <- +{2,3} of head gl
-    uint32_t qb4[4][2][2];
-    float qscale[2][4];  // MX: scale of heads 2t, 2t+1 per span
-    uint32_t qb16[8][2];
-    {
-        const bool live = gl < G;
-        const uint8_t* qrow = p.q4 + (static_cast<long long>(h) * G + gl) * (D / 2);
-        const uint8_t* qsr = p.qs + (static_cast<long long>(h) * G + gl) * SPR;
-#pragma unroll
-        for (int s = 0; s < 4; ++s) {
-            uint32_t w = live ? *reinterpret_cast<const uint32_t*>(qrow + s * 16 + 4 * t) : 0u;
-            uint32_t a0[4], a1[4];
-            uint32_t sc = 0;
-            if (!MX && live) sc = scale_to_h2<false>(qsr[2 * s + (t >> 1)]);
-            word_to_frags(w, 0u, sc, sc, !MX, a0, a1);
-            qb4[s][0][0] = a0[0]; qb4[s][0][1] = a0[2];
-            qb4[s][1][0] = a1[0]; qb4[s][1][1] = a1[2];
-        }
-        if (MX) {
-#pragma unroll
-            for (int e = 0; e < 2; ++e)
-#pragma unroll
-                for (int s = 0; s < 4; ++s) {
-                    const int head = 2 * t + e;
-                    qscale[e][s] = head < G ? decode_scale<true>(p.qs[(static_cast<long long>(h) * G + head) * SPR + s]) : 0.0f;
-                }
-        }
-        const uint16_t* qh = p.q_hi ? p.q_hi + (static_cast<long long>(h) * G + gl) * D : nullptr;
-#pragma unroll
-        for (int kc = 0; kc < 8; ++kc) {
-            qb16[kc][0] = (live && qh) ? *reinterpret_cast<const uint32_t*>(qh + kc * 16 + 2 * t) : 0u;
-            qb16[kc][1] = (live && qh) ? *reinterpret_cast<const uint32_t*>(qh + kc * 16 + 8 + 2 * t) : 0u;
-        }
-    }
-
-    // ---- running state for heads 2t and 2t+1 ----
-    float m_run[2] = {-FLT_MAX, -FLT_MAX}, l_run[2] = {0.0f, 0.0f};
-    float o[8][4];
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
-
-    __half* ptile = reinterpret_cast<__half*>(sm + WarpSmem::PT);
-
-    // ================= FP4 pages =================
-    auto issue_fp4 = [&](int page, int buf) {
-        const long long pp = phys(page);
-        const uint8_t* ksrc = p.k4 + pp * (PAGE * D / 2);
-        uint8_t* kdst = sm + WarpSmem::K4 + buf * PAGE * KROW;
-        for (int i = lane; i < PAGE * 4; i += 32) cp16(kdst + (i >> 2) * KROW + (i & 3) * 16, ksrc + i * 16);
-        const uint8_t* kssrc = p.ks + pp * (PAGE * SPR);
-        uint8_t* ksdst = sm + WarpSmem::KS + buf * PAGE * 8;
-        for (int i = lane; i < PAGE * SPR / 16; i += 32) cp16(ksdst + i * 16, kssrc + i * 16);
-        const uint8_t* vsrc;
-        const uint8_t* vssrc;
-        if (p.page_table) {
-            vsrc = p.v4 + pp * (D * 32);
-            vssrc = p.vs + pp * (D * (PAGE / GRP));
-        } else {
-            vsrc = p.v4 + static_cast<long long>(h) * p.v_head_stride + static_cast<long long>(page) * 32;
-            vssrc = p.vs + static_cast<long long>(h) * p.vs_head_stride + static_cast<long long>(page) * (PAGE / GRP);
-        }
-        uint8_t* vdst = sm + WarpSmem::V4 + buf * 128 * VROW;
-        for (int i = lane; i < D * 2; i += 32)
-            cp16(vdst + (i >> 1) * VROW + (i & 1) * 16, vsrc + static_cast<long long>(i >> 1) * p.v_row_stride + (i & 1) * 16);
-        uint8_t* vsdst = sm + WarpSmem::VS + buf * 128 * 4;
-        if (p.page_table) {
-            // pooled pages keep the scale bytes of a page contiguous
-            for (int i = lane; i < D * (PAGE / GRP) / 16; i += 32) cp16(vsdst + i * 16, vssrc + i * 16);
-        } else if (MX) {
-            // two scale bytes per channel row: fetch the aligned 4-byte word that holds them
-            for (int i = lane; i < D; i += 32) {
-                const uint8_t* src = vssrc + static_cast<long long>(i) * p.vs_row_stride;
-                cp4(vsdst + i * 4, reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(src) & ~static_cast<uintptr_t>(3)));
+    int n = 0;
+    for (int pass = 0; pass < 2; ++pass) {
+        for (int base = p_begin; base < p_end; base += 32) {
+            const int pg = base + lane;
+            const bool valid = pg < p_end;
+            const bool is_sel = valid && ((bits[pg >> 5] >> (pg & 31)) & 1u);
+            const bool take = valid && (is_sel == (pass == 1));
+            const uint32_t mask = __ballot_sync(0xFFFFFFFFu, take);
+            if (take) {
+                uint32_t key = static_cast<uint32_t>(pg);
+                if (p.page_table)
+                    key = static_cast<uint32_t>(p.page_table[static_cast<long long>(b) * p.max_pages + pg]) *
+                              static_cast<uint32_t>(p.hkv) + static_cast<uint32_t>(kvh);
+                list[n + __popc(mask & ((1u << lane) - 1u))] = key | (pass ? L_FP16 : 0u);
             }
-        } else {
-            for (int i = lane; i < D; i += 32) cp4(vsdst + i * 4, vssrc + static_cast<long long>(i) * p.vs_row_stride);
+            n += __popc(mask);
         }
-        cp_commit();
-    };
+        if (pass == 0) n_fp4 = n;
+    }
+    n_total = n;
+}
 
-    // first non-selected page
-    int cur = p_begin;
-    while (cur < p_end && flags[cur - p_begin]) ++cur;
-    int buf = 0;
-    if (cur < p_end) issue_fp4(cur, 0);
-    while (cur < p_end) {
-        int nxt = cur + 1;
-        while (nxt < p_end && flags[nxt - p_begin]) ++nxt;
-        if (nxt < p_end) { issue_fp4(nxt, buf ^ 1); cp_wait<1>(); } else { cp_wait<0>(); }
+template <bool MX, bool BF16>
+__global__ void __launch_bounds__(DEC_THREADS, 2)
+decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, const __grid_constant__ CUtensorMap mapV4,
+              const __grid_constant__ CUtensorMap mapK16, const __grid_constant__ CUtensorMap mapV16) {
+    constexpr int D = 128;
+    using L = DecSmem<D>;
+    constexpr int GRP = MX ? 32 : 16;
+    constexpr int QK_ATOMS = MX ? 1 : D / 64;
+    constexpr int KBLK = D / 64;
+    constexpr float CSCALE = MX ? 6.0f : 2688.0f;
+    constexpr float LOG2_C = MX ? 2.5849625007211562f : 11.392317422778761f;
+
+    extern __shared__ __align__(1024) uint8_t smem[];
+    DecBars& bars = *reinterpret_cast<DecBars*>(smem + L::BARS);
+    uint32_t* list = reinterpret_cast<uint32_t*>(smem + L::LIST);
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const uint32_t sbase = smem_u32(smem);
+    volatile int* abortp = &bars.abort_flag;
+    const long long budget = p.budget;
+
+    const int split = blockIdx.x, h = blockIdx.y;
+    const int b = h / p.hkv, kvh = h - b * p.hkv;
+    const int G = p.G;
+    const int p_begin = static_cast<int>(static_cast<long long>(split) * p.npages / p.splits);
+    const int p_end = static_cast<int>(static_cast<long long>(split + 1) * p.npages / p.splits);
+    const bool paged = p.page_table != nullptr;
+
+    if (tid == 0) {
+        mbar_init(smem_u32(&bars.q_ready), 128);
+        mbar_init(smem_u32(&bars.list_full), 1);
+        mbar_init(smem_u32(&bars.s_full), 1);
+        mbar_init(smem_u32(&bars.s_free), 128);
+        mbar_init(smem_u32(&bars.epi_full), 128);
+        for (int i = 0; i < DEC_NSLOTS; ++i) {
+            mbar_init(smem_u32(&bars.slot_full[i]), 1);
+            mbar_init(smem_u32(&bars.slot_empty[i]), 1);
+            mbar_init(smem_u32(&bars.sf_full[i]), 128);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&bars.p_full[i]), 128);
+            mbar_init(smem_u32(&bars.p_free[i]), 1);
+        }
+        mbar_fence_init();
+        bars.abort_flag = (sbase & 1023u) ? 1 : 0;
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&bars.tmem_base), DTM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = bars.tmem_base;
+
+    if (warp == 0) {
+        // =========================== page list + TMA producer ===========================
+        if (lane == 0) {
+            tma_prefetch_desc(&mapK4); tma_prefetch_desc(&mapV4);
+            if (p.width > 0) { tma_prefetch_desc(&mapK16); tma_prefetch_desc(&mapV16); }
+        }
+        int n_fp4 = 0, n = 0;
+        build_page_list(p, h, b, kvh, p_begin, p_end, reinterpret_cast<uint32_t*>(smem + L::BITS), list, n_fp4, n, lane);
+        if (lane == 0) { bars.n_fp4 = n_fp4; bars.n_total = n; }
         __syncwarp();
-        const uint8_t* ksm = sm + WarpSmem::K4 + buf * PAGE * KROW;
-        const uint8_t* kss = sm + WarpSmem::KS + buf * PAGE * 8;
-        const uint8_t* vsm = sm + WarpSmem::V4 + buf * 128 * VROW;
-        const uint8_t* vss = sm + WarpSmem::VS + buf * 128 * 4;
-        // in the MX contiguous layout the two V scale bytes may sit in either half of the fetched word
-        const int vs_off = (MX && !p.page_table) ? ((cur * (PAGE / GRP)) & 3) : 0;
-        const int vs_srow = p.page_table ? (PAGE / GRP) : 4;  // bytes per channel row in the staged scales
+        __threadfence_block();
+        if (lane == 0) mbar_arrive(smem_u32(&bars.list_full));
+        uint32_t gslot = 0;
+        bool ok = true;
+        for (int i = 0; i < n && ok; ++i) {
+            const uint32_t e = list[i];
+            const int key = static_cast<int>(e & ~L_FP16);
+            // tensor coordinates: (x, row, slab).  Pool: slab = key.  Cache: slab = head, rows / columns by page.
+            const int slab = paged ? key : h;
+            const int row0 = paged ? 0 : key * PAGE;
+            if (!(e & L_FP16)) {
+                const uint32_t slot = gslot % DEC_NSLOTS;
+                ok = mbar_wait(smem_u32(&bars.slot_empty[slot]), ((gslot / DEC_NSLOTS) & 1) ^ 1, abortp, budget);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t bar = smem_u32(&bars.slot_full[slot]);
+                    const uint32_t sa = sbase + L::SLOTS + slot * DEC_SLOT_BYTES;
+                    mbar_expect_tx(bar, PAGE * (D / 2) + D * (PAGE / 2));
+                    tma_load_3d(sa + L::K4, &mapK4, bar, 0, row0, slab);
+                    tma_load_3d(sa + L::V4, &mapV4, bar, paged ? 0 : key * (PAGE / 2), 0, slab);
+                }
+                gslot += 1;
+            } else {
+                for (int which = 0; which < 2 && ok; ++which) {   // K page, then V page
+                    const uint32_t slot = gslot % DEC_NSLOTS;
+                    ok = mbar_wait(smem_u32(&bars.slot_empty[slot]), ((gslot / DEC_NSLOTS) & 1) ^ 1, abortp, budget);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        const uint32_t bar = smem_u32(&bars.slot_full[slot]);
+                        const uint32_t sa = sbase + L::SLOTS + slot * DEC_SLOT_BYTES;
+                        mbar_expect_tx(bar, PAGE * D * 2);
+                        for (int hf = 0; hf < D / 64; ++hf)
+                            tma_load_3d(sa + hf * PAGE * 128, which ? &mapV16 : &mapK16, bar, hf * 64, row0, slab);
+                    }
+                    gslot += 1;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // =========================== MMA issuer ===========================
+        const uint32_t idesc_qk4 = make_idesc_fp4(128, PAGE, MX ? 1 : 0, 0, 0);
+        const uint32_t idesc_pv4 = make_idesc_fp4(128, D, MX ? 1 : 0, 0, 0);
+        const uint32_t idesc_qk16 = make_idesc_f16(128, PAGE, BF16 ? 1 : 0, 0, 0);
+        const uint32_t idesc_pv16 = make_idesc_f16(128, D, BF16 ? 1 : 0, 0, 1);
+        bool ok = mbar_wait(smem_u32(&bars.q_ready), 0, abortp, budget) &&
+                  mbar_wait(smem_u32(&bars.list_full), 0, abortp, budget);
+        const int n = ok ? bars.n_total : 0;
+        tc_fence_after_sync();
+        if (ok && lane == 0)
+            for (int a = 0; a < QK_ATOMS; ++a)
+                tmem_cp_sf(tmem + DTM_SFA_Q + a * 4, make_smem_desc(sbase + L::QSF + a * 512, 0, 128, SWZ_NONE));
 
-        // ---- S^T = K Q^T : 4 tiles of 16 tokens ----
-        float s_acc[4][4];
-#pragma unroll
-        for (int mt = 0; mt < 4; ++mt) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) s_acc[mt][j] = 0.0f;
-            const int r_lo = mt * 16 + gl, r_hi = r_lo + 8;
-#pragma unroll
-            for (int s = 0; s < 4; ++s) {
-                const uint32_t w_lo = *reinterpret_cast<const uint32_t*>(ksm + r_lo * KROW + s * 16 + 4 * t);
-                const uint32_t w_hi = *reinterpret_cast<const uint32_t*>(ksm + r_hi * KROW + s * 16 + 4 * t);
-                uint32_t a0[4], a1[4];
-                if (!MX) {
-                    const uint32_t sc_lo = scale_to_h2<false>(kss[r_lo * 8 + 2 * s + (t >> 1)]);
-                    const uint32_t sc_hi = scale_to_h2<false>(kss[r_hi * 8 + 2 * s + (t >> 1)]);
-                    word_to_frags(w_lo, w_hi, sc_lo, sc_hi, true, a0, a1);
-                    mma_f16_16816(s_acc[mt], a0, qb4[s][0][0], qb4[s][0][1]);
-                    mma_f16_16816(s_acc[mt], a1, qb4[s][1][0], qb4[s][1][1]);
+        // S = Q K^T of list entry `e`, operands in ring slot `slot` (one thread issues)
+        auto issue_qk = [&](uint32_t e, uint32_t slot) {
+            const uint32_t sa = sbase + L::SLOTS + slot * DEC_SLOT_BYTES;
+            const uint32_t d_t = tmem + DTM_S;
+            if (!(e & L_FP16)) {
+                const uint32_t sfb = tmem + DTM_SFB_K;
+                for (int a = 0; a < QK_ATOMS; ++a)
+                    tmem_cp_sf(sfb + a * 4, make_smem_desc(sa + L::KSF + a * 512, 0, 128, SWZ_NONE));
+                for (int kb = 0; kb < KBLK; ++kb) {
+                    const uint64_t ad = make_smem_desc(sbase + L::Q4 + kb * 32, 16, 512, SWZ_64B);
+                    const uint64_t bd = make_smem_desc(sa + L::K4 + kb * 32, 16, 512, SWZ_64B);
+                    if constexpr (MX)
+                        mma_mxfp4(d_t, ad, bd, make_idesc_fp4(128, PAGE, 1, kb * 2, kb * 2), tmem + DTM_SFA_Q, sfb, kb > 0);
+                    else
+                        mma_nvfp4(d_t, ad, bd, idesc_qk4, tmem + DTM_SFA_Q + kb * 4, sfb + kb * 4, kb > 0);
+                }
+            } else {
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t hf = ks / 4, kk = ks % 4;
+                    const uint64_t ad = make_smem_desc(sbase + L::Q16 + hf * 128 * 128 + kk * 32, 16, 1024, SWZ_128B);
+                    const uint64_t bd = make_smem_desc(sa + hf * PAGE * 128 + kk * 32, 16, 1024, SWZ_128B);
+                    mma_f16(d_t, ad, bd, idesc_qk16, ks > 0);
+                }
+                tc_commit(smem_u32(&bars.slot_empty[slot]));   // the K page is free once S is computed
+            }
+            tc_commit(smem_u32(&bars.s_full));
+        };
+        auto wait_operands = [&](uint32_t e, uint32_t gs) -> bool {
+            const uint32_t slot = gs % DEC_NSLOTS, par = (gs / DEC_NSLOTS) & 1;
+            bool good = mbar_wait(smem_u32(&bars.slot_full[slot]), par, abortp, budget);
+            if (good && !(e & L_FP16)) good = mbar_wait(smem_u32(&bars.sf_full[slot]), par, abortp, budget);
+            return good;
+        };
+
+        uint32_t qk_slot = 0;   // ring position of the step whose QK is issued next
+        if (ok && n > 0) {
+            const uint32_t e0 = list[0];
+            ok = wait_operands(e0, qk_slot);
+            if (ok) {
+                tc_fence_after_sync();
+                if (lane == 0) issue_qk(e0, qk_slot % DEC_NSLOTS);
+                __syncwarp();
+            }
+        }
+        for (int i = 0; i < n && ok; ++i) {
+            const uint32_t e = list[i];
+            const bool fp16 = e & L_FP16;
+            const uint32_t my_slot = qk_slot;                   // FP4: the page's slot; 16-bit: its K slot
+            const uint32_t pv_slot = fp16 ? my_slot + 1 : my_slot;
+            qk_slot = pv_slot + 1;
+            if (i + 1 < n) {   // S of the next page as soon as the softmax warps have read this one
+                const uint32_t e1 = list[i + 1];
+                ok = wait_operands(e1, qk_slot) &&
+                     mbar_wait(smem_u32(&bars.s_free), i & 1, abortp, budget);
+                if (!ok) break;
+                tc_fence_after_sync();
+                if (lane == 0) issue_qk(e1, qk_slot % DEC_NSLOTS);
+                __syncwarp();
+            }
+            const uint32_t buf = i & 1;
+            ok = mbar_wait(smem_u32(&bars.p_full[buf]), (i >> 1) & 1, abortp, budget);
+            if (ok && fp16) ok = mbar_wait(smem_u32(&bars.slot_full[pv_slot % DEC_NSLOTS]), (pv_slot / DEC_NSLOTS) & 1, abortp, budget);
+            if (!ok) break;
+            tc_fence_after_sync();
+            if (lane == 0) {
+                const uint32_t sa = sbase + L::SLOTS + (pv_slot % DEC_NSLOTS) * DEC_SLOT_BYTES;
+                const uint32_t d_t = tmem + DTM_O;
+                const uint32_t acc = i > 0 ? 1u : 0u;
+                if (!fp16) {
+                    const uint32_t sfa = tmem + DTM_SFA_P + buf * 4, sfb = tmem + DTM_SFB_V + buf * 4;
+                    tmem_cp_sf(sfa, make_smem_desc(sbase + L::PSF + buf * 512, 0, 128, SWZ_NONE));
+                    tmem_cp_sf(sfb, make_smem_desc(sa + L::VSF, 0, 128, SWZ_NONE));
+                    const uint64_t ad = make_smem_desc(sbase + L::P + buf * 4096, 16, 256, SWZ_32B);
+                    const uint64_t bd = make_smem_desc(sa + L::V4, 16, 256, SWZ_32B);
+                    if constexpr (MX) mma_mxfp4(d_t, ad, bd, idesc_pv4, sfa, sfb, acc);
+                    else mma_nvfp4(d_t, ad, bd, idesc_pv4, sfa, sfb, acc);
                 } else {
-                    word_to_frags(w_lo, w_hi, 0u, 0u, false, a0, a1);
-                    float tmp[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    mma_f16_16816(tmp, a0, qb4[s][0][0], qb4[s][0][1]);
-                    mma_f16_16816(tmp, a1, qb4[s][1][0], qb4[s][1][1]);
-                    const float k_lo = decode_scale<true>(kss[r_lo * 4 + s]), k_hi = decode_scale<true>(kss[r_hi * 4 + s]);
-                    s_acc[mt][0] = fmaf(tmp[0], k_lo * qscale[0][s], s_acc[mt][0]);
-                    s_acc[mt][1] = fmaf(tmp[1], k_lo * qscale[1][s], s_acc[mt][1]);
-                    s_acc[mt][2] = fmaf(tmp[2], k_hi * qscale[0][s], s_acc[mt][2]);
-                    s_acc[mt][3] = fmaf(tmp[3], k_hi * qscale[1][s], s_acc[mt][3]);
+                    for (int ks = 0; ks < PAGE / 16; ++ks) {
+                        const uint64_t ad = make_smem_desc(sbase + L::P + ks * 32, 16, 1024, SWZ_128B);
+                        const uint64_t bd = make_smem_desc(sa + ks * 2048, PAGE * 128, 1024, SWZ_128B);
+                        mma_f16(d_t, ad, bd, idesc_pv16, (acc == 0 && ks == 0) ? 0 : 1);
+                    }
+                }
+                tc_commit(smem_u32(&bars.slot_empty[pv_slot % DEC_NSLOTS]));
+                tc_commit(smem_u32(&bars.p_free[buf]));
+            }
+            __syncwarp();
+        }
+    } else {
+        // =========================== softmax ===========================
+        const int sub = warp & 3;                   // tensor-memory sub-partition of this warp
+        const int row = sub * 32 + lane;            // tile row = tensor-memory lane = index among the 128 threads
+        const int cq = lane & 3;                    // column quarter handled by this thread
+        const int g = (lane >> 2) * 4 + sub;        // query head of this row
+        const bool active = g < G;
+        const uint32_t lane_addr = static_cast<uint32_t>(sub * 32) << 16;
+        const bool has_sel = p.width > 0;
+
+        // ---- operand tiles written by hand: zero them, then place the query rows ----
+        {
+            const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+            for (int i = row; i < (L::Q16 - L::Q4) / 16; i += 128) reinterpret_cast<uint4*>(smem + L::Q4)[i] = z;
+            if (has_sel)
+                for (int i = row; i < 128 * D * 2 / 16; i += 128) reinterpret_cast<uint4*>(smem + L::Q16)[i] = z;
+            for (int i = row; i < 16384 / 16; i += 128) reinterpret_cast<uint4*>(smem + L::P)[i] = z;
+            for (int i = row; i < 1024 / 16; i += 128) reinterpret_cast<uint4*>(smem + L::PSF)[i] = z;
+        }
+        named_barrier_sync(1, 128);
+        if (active) {
+            const long long qrow = static_cast<long long>(h) * G + g;
+            const uint4* q4row = reinterpret_cast<const uint4*>(p.q4 + qrow * (D / 2));
+#pragma unroll
+            for (int c = 0; c < 4; ++c)   // 64-byte row, 64-byte swizzle
+                *reinterpret_cast<uint4*>(smem + L::Q4 + row * 64 + ((c ^ ((row >> 1) & 3)) * 16)) = __ldg(q4row + c);
+            const uint32_t* qsr = reinterpret_cast<const uint32_t*>(p.qs + qrow * (D / GRP));
+#pragma unroll
+            for (int a = 0; a < QK_ATOMS; ++a)
+                reinterpret_cast<uint32_t*>(smem + L::QSF + a * 512)[lane * 4 + sub] = __ldg(qsr + a);
+            if (has_sel) {
+                const uint4* qh = reinterpret_cast<const uint4*>(p.q_hi + qrow * D);
+#pragma unroll
+                for (int hf = 0; hf < D / 64; ++hf)
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)   // 128-byte row, 128-byte swizzle
+                        *reinterpret_cast<uint4*>(smem + L::Q16 + hf * 128 * 128 + (row >> 3) * 1024 + (row & 7) * 128 +
+                                                  ((c ^ (row & 7)) * 16)) = __ldg(qh + hf * 8 + c);
+            }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(smem_u32(&bars.q_ready));
+
+        bool ok = mbar_wait(smem_u32(&bars.list_full), 0, abortp, budget);
+        const int n = ok ? bars.n_total : 0;
+        const int n4 = ok ? bars.n_fp4 : 0;
+
+        // Block scales of FP4 page i: one 32-bit K word and one V word per thread, fetched a page ahead and
+        // stored in atom order (word m0 * 4 + m1 holds the scales of row / channel 32 * m1 + m0).
+        constexpr int KS_PAGE = PAGE * (D / GRP), VS_PAGE = D * (PAGE / GRP);
+        auto load_sf = [&](int i, uint32_t& kw, uint32_t& vw) {
+            kw = 0u; vw = 0u;
+            if (i >= n4) return;
+            const uint32_t key = list[i];
+            const uint8_t* kp = paged ? p.ks + static_cast<long long>(key) * KS_PAGE
+                                      : p.ks + (static_cast<long long>(h) * p.cap_pages + key) * KS_PAGE;
+            if (!MX || row < 64) kw = __ldg(reinterpret_cast<const uint32_t*>(kp) + row);
+            if constexpr (MX) {
+                const uint8_t* vp = paged ? p.vs + static_cast<long long>(key) * VS_PAGE + row * 2
+                                          : p.vs + (static_cast<long long>(h) * D + row) * p.vs_row_stride + key * 2;
+                vw = __ldg(reinterpret_cast<const uint16_t*>(vp));
+            } else {
+                const uint8_t* vp = paged ? p.vs + static_cast<long long>(key) * VS_PAGE + row * 4
+                                          : p.vs + (static_cast<long long>(h) * D + row) * p.vs_row_stride + key * 4;
+                vw = __ldg(reinterpret_cast<const uint32_t*>(vp));
+            }
+        };
+        auto store_sf = [&](int i, uint32_t kw, uint32_t vw) -> bool {
+            const uint32_t slot = i % DEC_NSLOTS;
+            if (!mbar_wait(smem_u32(&bars.slot_empty[slot]), ((i / DEC_NSLOTS) & 1) ^ 1, abortp, budget)) return false;
+            uint8_t* sa = smem + L::SLOTS + slot * DEC_SLOT_BYTES;
+            if constexpr (MX) {
+                if (row < 64) reinterpret_cast<uint32_t*>(sa + L::KSF)[(row & 31) * 4 + (row >> 5)] = kw;
+            } else {
+                const int tok = row >> 1;
+                reinterpret_cast<uint32_t*>(sa + L::KSF + (row & 1) * 512)[(tok & 31) * 4 + (tok >> 5)] = kw;
+            }
+            reinterpret_cast<uint32_t*>(sa + L::VSF)[lane * 4 + sub] = vw;
+            fence_proxy_async_smem();
+            mbar_arrive(smem_u32(&bars.sf_full[slot]));
+            return true;
+        };
+
+        uint32_t kw, vw;
+        load_sf(0, kw, vw);
+        if (ok && n4 > 0) ok = store_sf(0, kw, vw);
+        load_sf(1, kw, vw);
+
+        float m_run = -FLT_MAX, l_run = 0.0f;
+        bool prev_fp16 = false;
+        for (int i = 0; i < n && ok; ++i) {
+            const bool fp16 = (list[i] & L_FP16) != 0u;
+            if (i + 1 < n4) {
+                ok = store_sf(i + 1, kw, vw);
+                if (!ok) break;
+                load_sf(i + 2, kw, vw);
+            }
+            ok = mbar_wait(smem_u32(&bars.s_full), i & 1, abortp, budget);
+            if (!ok) break;
+            tc_fence_after_sync();
+            float s[16];
+            {
+                uint32_t r0[16], r1[16], r2[16], r3[16];
+                tmem_ld16(tmem + lane_addr + DTM_S, r0);
+                tmem_ld16(tmem + lane_addr + DTM_S + 16, r1);
+                tmem_ld16(tmem + lane_addr + DTM_S + 32, r2);
+                tmem_ld16(tmem + lane_addr + DTM_S + 48, r3);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const uint32_t lo = (cq & 1) ? r1[j] : r0[j], hi = (cq & 1) ? r3[j] : r2[j];
+                    s[j] = __uint_as_float((cq & 2) ? hi : lo);
                 }
             }
-        }
-        // ---- online softmax over the 64 tokens, per head (columns 2t, 2t+1) ----
-        float mx[2] = {-FLT_MAX, -FLT_MAX};
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&bars.s_free));
+
+            // running maximum of the whole page row (the four quarters sit in neighbouring lanes)
+            float mx = s[0];
 #pragma unroll
-        for (int mt = 0; mt < 4; ++mt) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) s_acc[mt][j] *= p.sm_scale;
-            mx[0] = fmaxf(mx[0], fmaxf(s_acc[mt][0], s_acc[mt][2]));
-            mx[1] = fmaxf(mx[1], fmaxf(s_acc[mt][1], s_acc[mt][3]));
-        }
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xFFFFFFFFu, mx[e], 4));
-            mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xFFFFFFFFu, mx[e], 8));
-            mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xFFFFFFFFu, mx[e], 16));
-        }
-        float resc[2], sum[2] = {0.0f, 0.0f};
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            const float m_new = fmaxf(m_run[e], mx[e]);
-            resc[e] = __expf(m_run[e] - m_new);
-            m_run[e] = m_new;
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { o[i][0] *= resc[0]; o[i][1] *= resc[1]; o[i][2] *= resc[0]; o[i][3] *= resc[1]; }
-#pragma unroll
-        for (int mt = 0; mt < 4; ++mt) {
-            s_acc[mt][0] = __expf(s_acc[mt][0] - m_run[0]); s_acc[mt][2] = __expf(s_acc[mt][2] - m_run[0]);
-            s_acc[mt][1] = __expf(s_acc[mt][1] - m_run[1]); s_acc[mt][3] = __expf(s_acc[mt][3] - m_run[1]);
-            sum[0] += s_acc[mt][0] + s_acc[mt][2];
-            sum[1] += s_acc[mt][1] + s_acc[mt][3];
-        }
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            sum[e] += __shfl_xor_sync(0xFFFFFFFFu, sum[e], 4);
-            sum[e] += __shfl_xor_sync(0xFFFFFFFFu, sum[e], 8);
-            sum[e] += __shfl_xor_sync(0xFFFFFFFFu, sum[e], 16);
-            l_run[e] = l_run[e] * resc[e] + sum[e];
-        }
-        // ---- P quantisation: dynamic scale per head and GRP tokens ----
-        float p_scale_mx[2][2];  // MX: decoded scale per head and 32-token span
-        constexpr int TILES_PER_GRP = GRP / 16;
-#pragma unroll
-        for (int g0 = 0; g0 < 4; g0 += TILES_PER_GRP) {
-            float amax[2] = {0.0f, 0.0f};
-#pragma unroll
-            for (int mt = g0; mt < g0 + TILES_PER_GRP; ++mt) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) s_acc[mt][j] *= C;
-                amax[0] = fmaxf(amax[0], fmaxf(s_acc[mt][0], s_acc[mt][2]));
-                amax[1] = fmaxf(amax[1], fmaxf(s_acc[mt][1], s_acc[mt][3]));
+            for (int j = 1; j < 16; ++j) mx = fmaxf(mx, s[j]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+            const float m_new = fmaxf(m_run, mx);
+            const bool changed = active && i > 0 && m_new > m_run;
+            const float rescale = ex2((m_run - m_new) * p.c2);
+            m_run = m_new;
+
+            const uint32_t buf = i & 1;
+            ok = mbar_wait(smem_u32(&bars.p_free[buf]), ((i >> 1) & 1) ^ 1, abortp, budget);
+            if (!ok) break;
+            const bool need_rescale = __any_sync(0xFFFFFFFFu, changed);
+            if ((need_rescale || fp16 || prev_fp16) && i > 0) {
+                // O, or a P tile spanning both buffers, is about to be touched: the previous PV must be done
+                ok = mbar_wait(smem_u32(&bars.p_free[(i - 1) & 1]), ((i - 1) >> 1) & 1, abortp, budget);
+                if (!ok) break;
             }
+            tc_fence_after_sync();
+            if (need_rescale) {
+                const float f = changed ? rescale : 1.0f;
+#pragma unroll 1
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem + lane_addr + DTM_O + c, r);
+                    tmem_wait_ld();
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                amax[e] = fmaxf(amax[e], __shfl_xor_sync(0xFFFFFFFFu, amax[e], 4));
-                amax[e] = fmaxf(amax[e], __shfl_xor_sync(0xFFFFFFFFu, amax[e], 8));
-                amax[e] = fmaxf(amax[e], __shfl_xor_sync(0xFFFFFFFFu, amax[e], 16));
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * f);
+                    tmem_st32(tmem + lane_addr + DTM_O + c, r);
+                }
+                tmem_wait_st();
             }
-            float inv[2], deq[2];
+
+            if (!fp16) {
+                // t = C p; group scale sf = amax(t) / 6 rounded to the scale format; codes = e2m1(t / sf), with
+                // the un-rounded sf, as the reference computes them
+                float t[16];
+                float sum = 0.0f, amax = 0.0f;
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const float sfp = __fdiv_rn(amax[e], 6.0f);
-                inv[e] = __fdiv_rn(1.0f, sfp);
-                deq[e] = decode_scale<MX>(encode_scale<MX>(sfp));
-                if (MX) p_scale_mx[e][g0 / 2] = deq[e];
-            }
+                for (int j = 0; j < 16; ++j) {
+                    const float pj = ex2((s[j] - m_new) * p.c2);   // exactly 1 at the row maximum
+                    sum += pj;
+                    t[j] = __fmul_rn(pj, CSCALE);
+                    amax = fmaxf(amax, t[j]);
+                }
+                l_run = fmaf(l_run, rescale, sum);
+                if constexpr (MX) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+                const float sfp = __fdiv_rn(amax, 6.0f);
+                const uint32_t sb = encode_scale<MX>(sfp);
+                const float inv = sfp > 0.0f ? __fdiv_rn(1.0f, sfp) : 0.0f;
+                const uint32_t w0 = e2m1x8(__fmul_rn(t[0], inv), __fmul_rn(t[1], inv), __fmul_rn(t[2], inv), __fmul_rn(t[3], inv),
+                                           __fmul_rn(t[4], inv), __fmul_rn(t[5], inv), __fmul_rn(t[6], inv), __fmul_rn(t[7], inv));
+                const uint32_t w1 = e2m1x8(__fmul_rn(t[8], inv), __fmul_rn(t[9], inv), __fmul_rn(t[10], inv), __fmul_rn(t[11], inv),
+                                           __fmul_rn(t[12], inv), __fmul_rn(t[13], inv), __fmul_rn(t[14], inv), __fmul_rn(t[15], inv));
+                if (active) {
+                    // 128 rows x 32 bytes, 32-byte swizzle; this thread's 16 codes are bytes [8 cq, 8 cq + 8) of its row
+                    uint8_t* dst = smem + L::P + buf * 4096 + (row >> 3) * 256 + (row & 7) * 32 +
+                                   (((cq >> 1) ^ ((row >> 2) & 1)) * 16) + (cq & 1) * 8;
+                    *reinterpret_cast<uint2*>(dst) = make_uint2(w0, w1);
+                    const int sj = MX ? (cq >> 1) : cq;
+                    reinterpret_cast<uint32_t*>(smem + L::PSF + buf * 512)[lane * 4 + sub] = sb << (8 * sj);
+                }
+            } else {
+                float sum = 0.0f;
+                uint32_t w[8];
 #pragma unroll
-            for (int mt = g0; mt < g0 + TILES_PER_GRP; ++mt) {
-                // codes for (token gl / gl+8, heads 2t / 2t+1)
-                const uint32_t c_lo = e2m1x2(s_acc[mt][0] * inv[0], s_acc[mt][1] * inv[1]);
-                const uint32_t c_hi = e2m1x2(s_acc[mt][2] * inv[0], s_acc[mt][3] * inv[1]);
-                const float v00 = e2m1_to_f(c_lo & 15u), v01 = e2m1_to_f(c_lo >> 4);
-                const float v10 = e2m1_to_f(c_hi & 15u), v11 = e2m1_to_f(c_hi >> 4);
-                const float d0 = MX ? 1.0f : deq[0], d1 = MX ? 1.0f : deq[1];
-                const bool z0 = deq[0] == 0.0f, z1 = deq[1] == 0.0f;
-                // staging tile: P[head][token]
-                ptile[(2 * t) * PROW + mt * 16 + gl] = __float2half_rn(z0 ? 0.0f : v00 * d0);
-                ptile[(2 * t + 1) * PROW + mt * 16 + gl] = __float2half_rn(z1 ? 0.0f : v01 * d1);
-                ptile[(2 * t) * PROW + mt * 16 + gl + 8] = __float2half_rn(z0 ? 0.0f : v10 * d0);
-                ptile[(2 * t + 1) * PROW + mt * 16 + gl + 8] = __float2half_rn(z1 ? 0.0f : v11 * d1);
-            }
-        }
-        __syncwarp();
-        // ---- O^T += V^T P^T : 8 tiles of 16 channels, 2 spans of 32 tokens ----
+                for (int j = 0; j < 16; j += 2) {
+                    const float a = ex2(fmaf(s[j] - m_new, p.c2, LOG2_C)), c = ex2(fmaf(s[j + 1] - m_new, p.c2, LOG2_C));
+                    sum += a + c;
+                    w[j >> 1] = In16<BF16>::pack2(a, c);
+                }
+                l_run = fmaf(l_run, rescale, sum * (1.0f / CSCALE));
+                if (active) {
+                    // 128 rows x 128 bytes, 128-byte swizzle; columns [16 cq, 16 cq + 16) are chunks 2 cq, 2 cq + 1
+                    uint8_t* base = smem + L::P + (row >> 3) * 1024 + (row & 7) * 128;
+                    if (!prev_fp16 && i > 0) {   // first 16-bit page: the row still holds FP4 codes
 #pragma unroll
-        for (int s = 0; s < 2; ++s) {
-            // B: P[head gl][tokens 32s + 8t + 4c + {0..3}]
-            const uint2 pb0 = *reinterpret_cast<const uint2*>(ptile + gl * PROW + 32 * s + 8 * t);
-            const uint2 pb1 = *reinterpret_cast<const uint2*>(ptile + gl * PROW + 32 * s + 8 * t + 4);
-#pragma unroll
-            for (int dt = 0; dt < 8; ++dt) {
-                const int r_lo = dt * 16 + gl, r_hi = r_lo + 8;
-                const uint32_t w_lo = *reinterpret_cast<const uint32_t*>(vsm + r_lo * VROW + s * 16 + 4 * t);
-                const uint32_t w_hi = *reinterpret_cast<const uint32_t*>(vsm + r_hi * VROW + s * 16 + 4 * t);
-                uint32_t a0[4], a1[4];
-                if (!MX) {
-                    const uint32_t sc_lo = scale_to_h2<false>(vss[r_lo * vs_srow + 2 * s + (t >> 1)]);
-                    const uint32_t sc_hi = scale_to_h2<false>(vss[r_hi * vs_srow + 2 * s + (t >> 1)]);
-                    word_to_frags(w_lo, w_hi, sc_lo, sc_hi, true, a0, a1);
-                    mma_f16_16816(o[dt], a0, pb0.x, pb0.y);
-                    mma_f16_16816(o[dt], a1, pb1.x, pb1.y);
-                } else {
-                    word_to_frags(w_lo, w_hi, 0u, 0u, false, a0, a1);
-                    float tmp[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    mma_f16_16816(tmp, a0, pb0.x, pb0.y);
-                    mma_f16_16816(tmp, a1, pb1.x, pb1.y);
-                    const float v_lo = decode_scale<true>(vss[r_lo * vs_srow + vs_off + s]), v_hi = decode_scale<true>(vss[r_hi * vs_srow + vs_off + s]);
-                    o[dt][0] = fmaf(tmp[0], v_lo * p_scale_mx[0][s], o[dt][0]);
-                    o[dt][1] = fmaf(tmp[1], v_lo * p_scale_mx[1][s], o[dt][1]);
-                    o[dt][2] = fmaf(tmp[2], v_hi * p_scale_mx[0][s], o[dt][2]);
-                    o[dt][3] = fmaf(tmp[3], v_hi * p_scale_mx[1][s], o[dt][3]);
+                        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(base + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    *reinterpret_cast<uint4*>(base + (((2 * cq) ^ (row & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(base + (((2 * cq + 1) ^ (row & 7)) * 16)) = make_uint4(w[4], w[5], w[6], w[7]);
                 }
             }
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&bars.p_full[buf]));
+            prev_fp16 = fp16;
         }
-        __syncwarp();
-        cur = nxt;
-        buf ^= 1;
-    }
 
-    // ================= selected pages (16-bit) =================
-    uint8_t* hsm = sm + WarpSmem::H16;
-    auto load16 = [&](const uint16_t* base, int page) {
-        const uint16_t* src = base + phys(page) * (PAGE * D);  // same capacity stride as the packed K
-        for (int i = lane; i < PAGE * 16; i += 32) cp16(hsm + (i >> 4) * HROW + (i & 15) * 16, reinterpret_cast<const uint8_t*>(src) + i * 16);
-        cp_commit();
-        cp_wait<0>();
-        __syncwarp();
-    };
-    for (int page = p_begin; page < p_end; ++page) {
-        if (!flags[page - p_begin]) continue;
-        __syncwarp();
-        load16(p.k_hi, page);
-        float s_acc[4][4];
+        // ---- end of chain: the four quarter rows of every head are added and written as one partial ----
+        if (ok && n > 0) ok = mbar_wait(smem_u32(&bars.p_free[(n - 1) & 1]), ((n - 1) >> 1) & 1, abortp, budget);
+        if (ok) {
+            tc_fence_after_sync();
+            float* stage = reinterpret_cast<float*>(smem + L::SLOTS);   // [quarter][head][D]
+#pragma unroll 1
+            for (int c = 0; c < D; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem + lane_addr + DTM_O + c, r);
+                tmem_wait_ld();
+                if (active) {
+                    uint4* dst = reinterpret_cast<uint4*>(stage + (cq * DEC_MAX_GROUP + g) * D + c);
 #pragma unroll
-        for (int mt = 0; mt < 4; ++mt) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) s_acc[mt][j] = 0.0f;
-#pragma unroll
-            for (int kc = 0; kc < 8; ++kc) {
-                uint32_t a[4];
-                const uint8_t* r_lo = hsm + (mt * 16 + gl) * HROW + kc * 32 + 4 * t;
-                const uint8_t* r_hi = r_lo + 8 * HROW;
-                a[0] = *reinterpret_cast<const uint32_t*>(r_lo);
-                a[1] = *reinterpret_cast<const uint32_t*>(r_hi);
-                a[2] = *reinterpret_cast<const uint32_t*>(r_lo + 16);
-                a[3] = *reinterpret_cast<const uint32_t*>(r_hi + 16);
-                if (BF16) mma_bf16_16816(s_acc[mt], a, qb16[kc][0], qb16[kc][1]);
-                else mma_f16_16816(s_acc[mt], a, qb16[kc][0], qb16[kc][1]);
+                    for (int j = 0; j < 8; ++j) dst[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                }
             }
+            tc_fence_before_sync();
+            if (active) {
+                bars.l_part[cq][g] = l_run;
+                if (cq == 0) bars.m_row[g] = m_run * p.sm_scale;
+            }
+            mbar_arrive(smem_u32(&bars.epi_full));
+            ok = mbar_wait(smem_u32(&bars.epi_full), 0, abortp, budget);
         }
-        float mx[2] = {-FLT_MAX, -FLT_MAX};
-#pragma unroll
-        for (int mt = 0; mt < 4; ++mt) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) s_acc[mt][j] *= p.sm_scale;
-            mx[0] = fmaxf(mx[0], fmaxf(s_acc[mt][0], s_acc[mt][2]));
-            mx[1] = fmaxf(mx[1], fmaxf(s_acc[mt][1], s_acc[mt][3]));
-        }
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xFFFFFFFFu, mx[e], 4));
-            mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xFFFFFFFFu, mx[e], 8));
-            mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xFFFFFFFFu, mx[e], 16));
-        }
-        float resc[2], sum[2] = {0.0f, 0.0f};
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            const float m_new = fmaxf(m_run[e], mx[e]);
-            resc[e] = __expf(m_run[e] - m_new);
-            m_run[e] = m_new;
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { o[i][0] *= resc[0]; o[i][1] *= resc[1]; o[i][2] *= resc[0]; o[i][3] *= resc[1]; }
-        __syncwarp();
-#pragma unroll
-        for (int mt = 0; mt < 4; ++mt) {
-            s_acc[mt][0] = __expf(s_acc[mt][0] - m_run[0]); s_acc[mt][2] = __expf(s_acc[mt][2] - m_run[0]);
-            s_acc[mt][1] = __expf(s_acc[mt][1] - m_run[1]); s_acc[mt][3] = __expf(s_acc[mt][3] - m_run[1]);
-            sum[0] += s_acc[mt][0] + s_acc[mt][2];
-            sum[1] += s_acc[mt][1] + s_acc[mt][3];
-            // P16 = 16-bit(C p), staged as [head][token]
-            uint16_t* pt = reinterpret_cast<uint16_t*>(ptile);
-            pt[(2 * t) * PROW + mt * 16 + gl] = In16<BF16>::from_f(s_acc[mt][0] * C);
-            pt[(2 * t + 1) * PROW + mt * 16 + gl] = In16<BF16>::from_f(s_acc[mt][1] * C);
-            pt[(2 * t) * PROW + mt * 16 + gl + 8] = In16<BF16>::from_f(s_acc[mt][2] * C);
-            pt[(2 * t + 1) * PROW + mt * 16 + gl + 8] = In16<BF16>::from_f(s_acc[mt][3] * C);
-        }
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            sum[e] += __shfl_xor_sync(0xFFFFFFFFu, sum[e], 4);
-            sum[e] += __shfl_xor_sync(0xFFFFFFFFu, sum[e], 8);
-            sum[e] += __shfl_xor_sync(0xFFFFFFFFu, sum[e], 16);
-            l_run[e] = l_run[e] * resc[e] + sum[e];
-        }
-        __syncwarp();
-        load16(p.v_hi, page);
-        // O^T += V^T P^T: A = V^T (channel rows, token k) read transposed from [token][channel]
-#pragma unroll
-        for (int kc = 0; kc < 4; ++kc) {
-            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(ptile + gl * PROW + kc * 16 + 2 * t);
-            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(ptile + gl * PROW + kc * 16 + 8 + 2 * t);
-#pragma unroll
-            for (int dt = 0; dt < 8; ++dt) {
-                uint32_t a[4];
-                // ldmatrix.trans: four 8x8 blocks of [token][channel] -> A fragment of V^T
-                const int blk = lane >> 3, rr = lane & 7;
-                const int tok = kc * 16 + (blk >> 1) * 8 + rr;
-                const int ch = dt * 16 + (blk & 1) * 8;
-                const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(hsm + tok * HROW + ch * 2));
-                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(addr));
-                if (BF16) mma_bf16_16816(o[dt], a, b0, b1);
-                else mma_f16_16816(o[dt], a, b0, b1);
+        if (ok) {
+            const float* stage = reinterpret_cast<const float*>(smem + L::SLOTS);
+            const long long pbase = (static_cast<long long>(h) * p.splits + split) * G;
+            for (int gg = 0; gg < G; ++gg) {
+                float o = stage[(0 * DEC_MAX_GROUP + gg) * D + row];
+                o += stage[(1 * DEC_MAX_GROUP + gg) * D + row];
+                o += stage[(2 * DEC_MAX_GROUP + gg) * D + row];
+                o += stage[(3 * DEC_MAX_GROUP + gg) * D + row];
+                p.part_o[(pbase + gg) * D + row] = o;
+            }
+            if (row < G) {
+                p.part_ml[(pbase + row) * 2] = bars.m_row[row];
+                p.part_ml[(pbase + row) * 2 + 1] = (bars.l_part[0][row] + bars.l_part[1][row]) + (bars.l_part[2][row] + bars.l_part[3][row]);
             }
         }
     }
 
-    // ---- partial results: O (units of C), m, l ----
-    float* po = p.part_o + (static_cast<long long>(h) * p.splits + split) * G * D;
-    float* pml = p.part_ml + (static_cast<long long>(h) * p.splits + split) * G * 2;
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-        const int head = 2 * t + e;
-        if (head < G) {
-#pragma unroll
-            for (int dt = 0; dt < 8; ++dt) {
-                po[head * D + dt * 16 + gl] = o[dt][e];
-                po[head * D + dt * 16 + gl + 8] = o[dt][2 + e];
-            }
-            if (gl == 0) { pml[head * 2] = m_run[e]; pml[head * 2 + 1] = l_run[e]; }
-        }
-    }
+    // ---- common exit ----
+    if (bars.abort_flag != 0) __nanosleep(20000);   // let copies already in flight land
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, DTM_COLS);
+    if (tid == 0 && bars.abort_flag != 0) atomicExch(&g_decode_status, 1);
 }
 
 // out[row, :] = sum_s O_s e^{m_s - M} / (C sum_s l_s e^{m_s - M}); rows = heads * G
@@ -549,21 +632,49 @@ __global__ void __launch_bounds__(128) merge_kernel(const float* __restrict__ pa
 
 }  // namespace
 
+// Chains per (sequence, KV head): enough CTAs to fill the GPU (two per SM) in whole waves.
 int decode_pick_splits(int heads, int npages) {
-    // about two resident waves of single-warp chains (9 per SM) over the whole GPU
     int sms = NUM_SMS_HINT;
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    long long target = 2LL * 9 * sms;
-    int splits = static_cast<int>((target + heads - 1) / (heads > 0 ? heads : 1));
-    if (splits > npages) splits = npages;
-    if (splits > 64) splits = 64;
-    if (splits < 1) splits = 1;
-    return splits;
+    if (heads < 1) heads = 1;
+    const long long resident = 2LL * sms;
+    int lo = cdiv(npages, DEC_LIST_CAP);
+    if (lo < 1) lo = 1;
+    int hi = npages < 64 ? npages : 64;
+    if (hi < lo) hi = lo;
+    int best = lo;
+    double best_eff = -1.0;
+    for (int s = lo; s <= hi; ++s) {
+        const long long ctas = static_cast<long long>(heads) * s;
+        const long long waves = (ctas + resident - 1) / resident;
+        const double eff = static_cast<double>(ctas) / static_cast<double>(waves * resident);
+        if (eff > best_eff + 1e-9) { best_eff = eff; best = s; }
+        // the first split count that fills at least two waves to 95 % is good enough
+        if (eff >= 0.95 && ctas >= 2 * resident) { best = s; break; }
+        if (npages / s < 8) break;   // chains shorter than 8 pages are mostly set-up
+    }
+    return best;
 }
 
 size_t decode_workspace_bytes(int heads, int G, int d, int splits) {
     return static_cast<size_t>(heads) * splits * G * (d + 2) * sizeof(float);
+}
+
+// Reads and clears the device status word: TA100_ERR_DEVICE_TIMEOUT if a bounded wait inside a decode
+// kernel of the current device ran out since the last call.  Synchronises with `stream`.
+int decode_status(cudaStream_t stream) {
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    int flag = 0;
+    e = cudaMemcpyFromSymbol(&flag, g_decode_status, sizeof(int));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (flag != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int));
+        return TA100_ERR_DEVICE_TIMEOUT;
+    }
+    return TA100_OK;
 }
 
 // See include/thrift_sm100.h (ta100_decode_attention).
@@ -575,37 +686,77 @@ int decode_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const 
     if (write_out && !out) return TA100_ERR_NULL;
     if (width > 0 && (!q_hi || !k_hi || !v_hi || !sel)) return TA100_ERR_NULL;
     if (d != 128) return TA100_ERR_UNSUPPORTED;
-    if (G < 1 || G > 8) return TA100_ERR_UNSUPPORTED;
+    if (G < 1 || G > DEC_MAX_GROUP) return TA100_ERR_UNSUPPORTED;
     if (batch <= 0 || hkv <= 0 || kv_len <= 0 || kv_len % PAGE != 0 || kv_cap < kv_len) return TA100_ERR_SHAPE;
     if (!page_table && kv_cap % PAGE != 0) return TA100_ERR_SHAPE;
     const int heads = batch * hkv;
     const int npages = kv_len / PAGE;
-    if (npages > 2048) return TA100_ERR_LIMIT;
+    if (npages > 2048 || heads > 65535) return TA100_ERR_LIMIT;
     if (splits < 1 || splits > npages) return TA100_ERR_SHAPE;
+    if (cdiv(npages, splits) > DEC_LIST_CAP) return TA100_ERR_LIMIT;
+    const uintptr_t align = reinterpret_cast<uintptr_t>(k4) | reinterpret_cast<uintptr_t>(v4) |
+                            reinterpret_cast<uintptr_t>(k_hi) | reinterpret_cast<uintptr_t>(v_hi) |
+                            reinterpret_cast<uintptr_t>(q4) | reinterpret_cast<uintptr_t>(q_hi);
+    if (align & 15) return TA100_ERR_ALIGN;
+    if ((reinterpret_cast<uintptr_t>(ks) | reinterpret_cast<uintptr_t>(vs) | reinterpret_cast<uintptr_t>(qs)) & 3)
+        return TA100_ERR_ALIGN;
     const int GRP = is_mx ? 32 : 16;
     const int P = cdiv(kv_cap, 128) * 128;
+    const bool paged = page_table != nullptr;
+    // a page pool's size is not part of the interface: its tensor maps get the largest slab count, the page
+    // table is what keeps the accesses inside the pool
+    const uint64_t pool_slabs = 0x7FFFFFFFull;
+
+    CUtensorMap maps[4];
+    memset(maps, 0, sizeof(maps));
+    {
+        int rc = 0;
+        const uint64_t d2 = static_cast<uint64_t>(d / 2);
+        {   // K codes: rows of d/2 bytes
+            uint64_t dims[3] = {d2, paged ? uint64_t(PAGE) : uint64_t(kv_cap), paged ? pool_slabs : uint64_t(heads)};
+            uint64_t str[2] = {d2, (paged ? uint64_t(PAGE) : uint64_t(kv_cap)) * d2};
+            uint32_t box[3] = {static_cast<uint32_t>(d2), PAGE, 1};
+            rc |= make_tensor_map(&maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, k4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_64B);
+        }
+        {   // V codes, transposed: d rows of (tokens / 2) bytes
+            const uint64_t rowb = paged ? uint64_t(PAGE / 2) : uint64_t(P / 2);
+            uint64_t dims[3] = {rowb, uint64_t(d), paged ? pool_slabs : uint64_t(heads)};
+            uint64_t str[2] = {rowb, rowb * d};
+            uint32_t box[3] = {PAGE / 2, static_cast<uint32_t>(d), 1};
+            rc |= make_tensor_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, v4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_32B);
+        }
+        if (width > 0) {
+            const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+            const uint64_t rows = paged ? uint64_t(PAGE) : uint64_t(kv_cap);
+            uint64_t dims[3] = {uint64_t(d), rows, paged ? pool_slabs : uint64_t(heads)};
+            uint64_t str[2] = {uint64_t(d) * 2, rows * d * 2};
+            uint32_t box[3] = {64, PAGE, 1};
+            rc |= make_tensor_map(&maps[2], dt, 3, k_hi, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+            rc |= make_tensor_map(&maps[3], dt, 3, v_hi, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        } else {
+            maps[2] = maps[0]; maps[3] = maps[0];
+        }
+        if (rc != 0) return TA100_ERR_TENSOR_MAP;
+    }
+
     DecodeParams p;
     p.q_hi = static_cast<const uint16_t*>(q_hi); p.q4 = static_cast<const uint8_t*>(q4); p.qs = static_cast<const uint8_t*>(qs);
-    p.k4 = static_cast<const uint8_t*>(k4); p.ks = static_cast<const uint8_t*>(ks);
-    p.v4 = static_cast<const uint8_t*>(v4); p.vs = static_cast<const uint8_t*>(vs);
-    p.k_hi = static_cast<const uint16_t*>(k_hi); p.v_hi = static_cast<const uint16_t*>(v_hi);
+    p.ks = static_cast<const uint8_t*>(ks); p.vs = static_cast<const uint8_t*>(vs);
     p.sel = static_cast<const int32_t*>(sel); p.page_table = static_cast<const int32_t*>(page_table);
     p.part_o = static_cast<float*>(part_o); p.part_ml = static_cast<float*>(part_ml);
     p.heads = heads; p.hkv = hkv; p.G = G; p.npages = npages; p.cap_pages = kv_cap / PAGE; p.max_pages = max_pages;
     p.width = width; p.splits = splits;
-    if (page_table) {
-        p.v_head_stride = 0; p.vs_head_stride = 0; p.v_row_stride = 32; p.vs_row_stride = PAGE / GRP;
-    } else {
-        p.v_head_stride = static_cast<long long>(d) * (P / 2); p.vs_head_stride = static_cast<long long>(d) * (P / GRP);
-        p.v_row_stride = P / 2; p.vs_row_stride = P / GRP;
-    }
+    p.vs_row_stride = P / GRP;
     p.sm_scale = static_cast<float>(1.0 / sqrt(static_cast<double>(d)));
+    p.c2 = static_cast<float>((1.0 / sqrt(static_cast<double>(d))) * 1.4426950408889634);
+    p.budget = 1000000000LL;
     const dim3 grid(splits, heads);
-    const int smem = WarpSmem::TOTAL;
+    const int smem = DecSmem<128>::TOTAL;
 #define TA100_DEC(MXX, BFF)                                                                               \
     do {                                                                                                  \
         cudaFuncSetAttribute(decode_kernel<MXX, BFF>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
-        decode_kernel<MXX, BFF><<<grid, 32, smem, stream>>>(p);                                           \
+        cudaFuncSetAttribute(decode_kernel<MXX, BFF>, cudaFuncAttributePreferredSharedMemoryCarveout, 100); \
+        decode_kernel<MXX, BFF><<<grid, DEC_THREADS, smem, stream>>>(p, maps[0], maps[1], maps[2], maps[3]); \
     } while (0)
     if (is_mx) { if (is_bf16) TA100_DEC(true, true); else TA100_DEC(true, false); }
     else { if (is_bf16) TA100_DEC(false, true); else TA100_DEC(false, false); }

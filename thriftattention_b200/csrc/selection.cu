@@ -223,44 +223,229 @@ __global__ void __launch_bounds__(SEL_WARPS * 32) select_prefill_kernel(
     }
 }
 
-// Decode: one CTA per flat KV head.  All warps score pages (max over the query
-// group), warp 0 then runs the top-k rounds.  q [flat, group, D]; ka/kb
-// [flat, cap_blocks, D]; out [flat, sink + local + k].
+// Decode: one CTA (256 threads) per flat KV head.
+//  1. scoring — 64-page tiles of the statistics stream through shared memory (cp.async, two stages);
+//     four threads share a page and split the query group between them.  Each thread reproduces the
+//     warp arithmetic above on its own: 32 partial sums (channel c goes to partial c mod 32, fused
+//     multiply-adds in ascending channel order), then the xor-butterfly pairing 16, 8, 4, 2, 1 as plain
+//     additions — fp32 addition commutes, so the value equals the warp's bit for bit.  Packed f32x2
+//     instructions carry two partials each.
+//  2. top-k — every page becomes a 64-bit key (descending score, then the tie-break rank of its index)
+//     and the keys are sorted with a bitonic network in shared memory; the first k keys are the k
+//     arg-max rounds' picks in the same order.
+// q [flat, group, D]; ka/kb [flat, cap_blocks, D]; out [flat, sink + local + k].
+constexpr int SELD_THREADS = 256;
+constexpr int SELD_TILE = 64;       // pages per tile
+constexpr int SELD_MAX_GROUP = 16;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))),
+                 "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    unsigned long long ra, rb, rc, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    unsigned long long ra, rb, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+
+template <bool BF16>
+__device__ __forceinline__ float2 word_to_float2(uint32_t w) {
+    if constexpr (BF16) return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+    else return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+
+// Sort key: high word orders scores descending (-0 counts as +0), low word is the tie-break rank.
+__device__ __forceinline__ unsigned long long seld_key(float score, int page) {
+    if (score == 0.0f) score = 0.0f;
+    const uint32_t u = __float_as_uint(score);
+    const uint32_t asc = (u >> 31) ? ~u : (u | 0x80000000u);
+    const uint32_t tie = (__brev(static_cast<uint32_t>(page) & 31u) >> 27 << 16) | (static_cast<uint32_t>(page) >> 5);
+    return (static_cast<unsigned long long>(~asc) << 32) | tie;
+}
+__device__ __forceinline__ float seld_key_score(unsigned long long key) {
+    const uint32_t asc = ~static_cast<uint32_t>(key >> 32);
+    return __uint_as_float((asc >> 31) ? (asc ^ 0x80000000u) : ~asc);
+}
+__device__ __forceinline__ int seld_key_page(unsigned long long key) {
+    const uint32_t tie = static_cast<uint32_t>(key);
+    return static_cast<int>((__brev(tie >> 16) >> 27) | ((tie & 0xFFFFu) << 5));
+}
+
+template <int D>
+struct SeldSmem {
+    static constexpr int ROW = D * 2 + 16;                       // padded statistics row (bytes)
+    static constexpr int TILE_BYTES = SELD_TILE * ROW;
+    static constexpr int QROW = D + 4;                            // floats per query row
+    static constexpr int MROW = D / 2 + 4;                        // mask words per query row
+    static constexpr int KEYS = 0;                                // 2048 x 8 B
+    static constexpr int QF = KEYS + 2048 * 8;
+    static constexpr int QM = QF + SELD_MAX_GROUP * QROW * 4;
+    static constexpr int TILES = QM + SELD_MAX_GROUP * MROW * 4;  // [2 stages][A | B]
+    static constexpr int total(bool quest) { return TILES + 2 * (quest ? 2 : 1) * TILE_BYTES; }
+};
+
 template <int D, bool BF16, bool QUEST>
-__global__ void __launch_bounds__(256) select_decode_kernel(const uint16_t* __restrict__ q,
-                                                            const uint16_t* __restrict__ ka,
-                                                            const uint16_t* __restrict__ kb,
-                                                            int32_t* __restrict__ out, int group, int nk,
-                                                            int cap_blocks, int k, int sink, int local) {
+__global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const uint16_t* __restrict__ q,
+                                                                        const uint16_t* __restrict__ ka,
+                                                                        const uint16_t* __restrict__ kb,
+                                                                        int32_t* __restrict__ out, int group, int nk,
+                                                                        int cap_blocks, int k, int sink, int local) {
+    using L = SeldSmem<D>;
+    constexpr int VEC = D / 8;            // 16-byte chunks per statistics row
+    constexpr int NARR = QUEST ? 2 : 1;
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    float* scores = reinterpret_cast<float*>(smem_raw);
-    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, nwarps = blockDim.x / 32;
+    unsigned long long* keys = reinterpret_cast<unsigned long long*>(smem_raw + L::KEYS);
+    float* qf = reinterpret_cast<float*>(smem_raw + L::QF);
+    uint32_t* qm = reinterpret_cast<uint32_t*>(smem_raw + L::QM);
+    uint8_t* tiles = smem_raw + L::TILES;
+
+    const int tid = threadIdx.x;
     const int h = blockIdx.x;
     const int n_sink = min(sink, nk);
     const int local_lo = max(nk - local, n_sink);
     const int width = sink + local + k;
-    for (int b = warp; b < nk; b += nwarps) {
-        const uint16_t* ra = ka + (static_cast<long long>(h) * cap_blocks + b) * D;
-        const uint16_t* rb = QUEST ? kb + (static_cast<long long>(h) * cap_blocks + b) * D : nullptr;
-        float best = -FLT_MAX;
-        for (int g = 0; g < group; ++g) {
-            float qv[D / 32];
-#pragma unroll
-            for (int i = 0; i < D / 32; ++i)
-                qv[i] = In16<BF16>::to_f(q[(static_cast<long long>(h) * group + g) * D + lane + 32 * i]);
-            const float s = warp_score<D, BF16, QUEST>(qv, ra, rb, lane);
-            if (s > best) best = s;
+    int n_sort = 2;
+    while (n_sort < nk) n_sort <<= 1;
+
+    // query group: fp32 values and, for Quest, one 16-bit mask per channel (all ones where q >= 0)
+    for (int i = tid; i < group * D; i += SELD_THREADS) {
+        const int g = i / D, c = i - g * D;
+        qf[g * L::QROW + c] = In16<BF16>::to_f(q[(static_cast<long long>(h) * group + g) * D + c]);
+    }
+    for (int i = tid; i < n_sort; i += SELD_THREADS) keys[i] = ~0ull;
+    __syncthreads();
+    if constexpr (QUEST) {
+        for (int i = tid; i < group * (D / 2); i += SELD_THREADS) {
+            const int g = i / (D / 2), w = i - g * (D / 2);
+            const uint32_t lo = qf[g * L::QROW + 2 * w] >= 0.0f ? 0xFFFFu : 0u;
+            const uint32_t hi = qf[g * L::QROW + 2 * w + 1] >= 0.0f ? 0xFFFF0000u : 0u;
+            qm[g * L::MROW + w] = lo | hi;
         }
-        if (lane == 0) scores[b] = (b < n_sink || b >= local_lo) ? -FLT_MAX : best;
+    }
+
+    const int n_tiles = cdiv(nk, SELD_TILE);
+    auto issue = [&](int t) {
+        uint8_t* stage = tiles + (t & 1) * NARR * L::TILE_BYTES;
+        const int p0 = t * SELD_TILE;
+        const int rows = min(SELD_TILE, nk - p0);
+        for (int i = tid; i < rows * VEC; i += SELD_THREADS) {
+            const int r = i / VEC, c = i - r * VEC;
+            const long long src = (static_cast<long long>(h) * cap_blocks + p0 + r) * D + c * 8;
+            cp_async16(stage + r * L::ROW + c * 16, ka + src);
+            if constexpr (QUEST) cp_async16(stage + L::TILE_BYTES + r * L::ROW + c * 16, kb + src);
+        }
+        cp_async_commit();
+    };
+
+    const int pl = tid >> 2, sub = tid & 3;
+    if (n_tiles > 0) issue(0);
+    for (int t = 0; t < n_tiles; ++t) {
+        if (t + 1 < n_tiles) { issue(t + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+        __syncthreads();
+        const uint8_t* stage = tiles + (t & 1) * NARR * L::TILE_BYTES;
+        const int page = t * SELD_TILE + pl;
+        float best = -FLT_MAX;
+        if (page < nk) {
+            const uint4* ra = reinterpret_cast<const uint4*>(stage + pl * L::ROW);
+            const uint4* rb = reinterpret_cast<const uint4*>(stage + L::TILE_BYTES + pl * L::ROW);
+            for (int g = sub; g < group; g += 4) {
+                float2 acc[16];
+#pragma unroll
+                for (int w = 0; w < 16; ++w) acc[w] = make_float2(0.0f, 0.0f);
+                const float4* qrow = reinterpret_cast<const float4*>(qf + g * L::QROW);
+                const uint4* mrow = reinterpret_cast<const uint4*>(qm + g * L::MROW);
+#pragma unroll 1
+                for (int i = 0; i < D / 32; ++i) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {          // 8 channels per 16-byte chunk
+                        const uint4 a = ra[i * 4 + v];
+                        uint32_t kw[4] = {a.x, a.y, a.z, a.w};
+                        if constexpr (QUEST) {
+                            const uint4 b = rb[i * 4 + v];
+                            const uint4 m = mrow[i * 4 + v];
+                            kw[0] = (b.x & m.x) | (a.x & ~m.x);
+                            kw[1] = (b.y & m.y) | (a.y & ~m.y);
+                            kw[2] = (b.z & m.z) | (a.z & ~m.z);
+                            kw[3] = (b.w & m.w) | (a.w & ~m.w);
+                        }
+                        const float4 q0 = qrow[i * 8 + v * 2], q1 = qrow[i * 8 + v * 2 + 1];
+                        acc[v * 4 + 0] = fma2(make_float2(q0.x, q0.y), word_to_float2<BF16>(kw[0]), acc[v * 4 + 0]);
+                        acc[v * 4 + 1] = fma2(make_float2(q0.z, q0.w), word_to_float2<BF16>(kw[1]), acc[v * 4 + 1]);
+                        acc[v * 4 + 2] = fma2(make_float2(q1.x, q1.y), word_to_float2<BF16>(kw[2]), acc[v * 4 + 2]);
+                        acc[v * 4 + 3] = fma2(make_float2(q1.z, q1.w), word_to_float2<BF16>(kw[3]), acc[v * 4 + 3]);
+                    }
+                }
+                // butterfly pairing: partial j with j+16, then j+8, j+4, j+2, j+1
+#pragma unroll
+                for (int w = 0; w < 8; ++w) acc[w] = add2(acc[w], acc[w + 8]);
+#pragma unroll
+                for (int w = 0; w < 4; ++w) acc[w] = add2(acc[w], acc[w + 4]);
+                acc[0] = add2(acc[0], acc[2]);
+                acc[1] = add2(acc[1], acc[3]);
+                acc[0] = add2(acc[0], acc[1]);
+                const float s = __fadd_rn(acc[0].x, acc[0].y);
+                if (s > best) best = s;
+            }
+        }
+        // the four threads of a page hold the maxima of their shares of the group
+        {
+            float o = __shfl_xor_sync(0xFFFFFFFFu, best, 1);
+            if (o > best) best = o;
+            o = __shfl_xor_sync(0xFFFFFFFFu, best, 2);
+            if (o > best) best = o;
+        }
+        if (sub == 0 && page < nk) keys[page] = seld_key((page < n_sink || page >= local_lo) ? -FLT_MAX : best, page);
+        __syncthreads();
+    }
+
+    // ---- bitonic sort of the keys, ascending ----
+    for (int size = 2; size <= n_sort; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            __syncthreads();
+            for (int t = tid; t < n_sort / 2; t += SELD_THREADS) {
+                const int pos = 2 * t - (t & (stride - 1));
+                const unsigned long long a = keys[pos], b = keys[pos + stride];
+                const bool up = (pos & size) == 0;
+                if ((a > b) == up) { keys[pos] = b; keys[pos + stride] = a; }
+            }
+        }
     }
     __syncthreads();
-    if (warp == 0) {
-        int32_t* row = out + static_cast<long long>(h) * width;
-        const int forced = n_sink + (nk - local_lo);
-        for (int i = lane; i < forced; i += 32) row[i] = i < n_sink ? i : local_lo + (i - n_sink);
-        topk_dispatch(scores, nk, k, (sink + local) > 0, row + forced, lane);
-        for (int i = forced + k + lane; i < width; i += 32) row[i] = -1;
+
+    int32_t* row = out + static_cast<long long>(h) * width;
+    const int forced = n_sink + (nk - local_lo);
+    const bool pad = (sink + local) > 0;
+    for (int i = tid; i < forced; i += SELD_THREADS) row[i] = i < n_sink ? i : local_lo + (i - n_sink);
+    for (int r = tid; r < k; r += SELD_THREADS) {
+        int32_t id = -1;
+        if (r < n_sort) {
+            const unsigned long long key = keys[r];
+            const bool real = key != ~0ull;
+            const bool found = real && seld_key_score(key) > -FLT_MAX * 0.5f;
+            if (found || (!pad && real)) id = seld_key_page(key);
+        }
+        row[forced + r] = id;
     }
+    for (int i = forced + k + tid; i < width; i += SELD_THREADS) row[i] = -1;
 }
 
 int select_prefill_dispatch(const void* q_mean, const void* ka, const void* kb, void* out, int heads, int group, int nq,
@@ -302,11 +487,15 @@ int select_decode_dispatch(const void* q, const void* ka, const void* kb, void* 
     if (nk > 2048 || nk < 0 || k < 0 || nk > cap_blocks || group <= 0) return TA100_ERR_SHAPE;
     if ((sink + local) == 0 && k > nk) return TA100_ERR_SHAPE;
     if (sink + local + k == 0 || flat_heads == 0) return TA100_OK;
-    const size_t smem = sizeof(float) * ((nk + 31) & ~31);
-#define TA100_SELD(DD, BFF, QQ)                                                                               \
-    select_decode_kernel<DD, BFF, QQ><<<flat_heads, 256, smem, stream>>>(                                      \
-        static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(ka), static_cast<const uint16_t*>(kb),   \
-        static_cast<int32_t*>(out), group, nk, cap_blocks, k, sink, local)
+    if (group > SELD_MAX_GROUP) return TA100_ERR_LIMIT;
+#define TA100_SELD(DD, BFF, QQ)                                                                                \
+    do {                                                                                                       \
+        const int smem = SeldSmem<DD>::total(QQ);                                                              \
+        cudaFuncSetAttribute(select_decode_kernel<DD, BFF, QQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+        select_decode_kernel<DD, BFF, QQ><<<flat_heads, SELD_THREADS, smem, stream>>>(                         \
+            static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(ka), static_cast<const uint16_t*>(kb), \
+            static_cast<int32_t*>(out), group, nk, cap_blocks, k, sink, local);                                \
+    } while (0)
     if (d == 128) {
         if (is_bf16) { if (quest) TA100_SELD(128, true, true); else TA100_SELD(128, true, false); }
         else { if (quest) TA100_SELD(128, false, true); else TA100_SELD(128, false, false); }
