@@ -18,12 +18,18 @@
 // (dynamic scale per 16 / 32 tokens, codes computed with the un-rounded scale) depends
 // on it.
 //
-// Warp roles (192 threads): warp 0 = page list + TMA producer, warp 1 = MMA issuer and
-// tensor-memory owner, warps 2..5 = softmax (they also bring the K and V block scales of
-// every page into the 512-byte atom order the tensor core reads).  Two CTAs share an SM.
+// Warp roles (224 threads): warp 0 = page list + TMA producer (its 32 lanes also bring the K
+// and V block scales of every page into the 512-byte atom order the tensor core reads),
+// warp 1 = issuer of the S = Q K^T MMAs and tensor-memory owner, warp 2 = issuer of the
+// O += P V MMAs (one thread needs some hundred cycles to issue the scale copies, MMAs and
+// commits of a page, so the two streams are issued side by side), warps 3..6 = softmax.
+// Two CTAs share an SM.
+// The ring holds five FP4 pages in flight; when the chain turns to its 16-bit pages the same
+// memory is re-cut into three 16 KB tiles.
 // Every mbarrier wait is bounded; a timeout raises a CTA-wide abort flag, all roles
 // drain, tensor memory is released and a status word is set.
 #include <cfloat>
+#include <cstdio>
 #include <cstring>
 #include <mutex>
 
@@ -35,9 +41,14 @@ namespace ta100 {
 namespace {
 
 constexpr int PAGE = 64;
-constexpr int DEC_THREADS = 192;
-constexpr int DEC_NSLOTS = 3;
-constexpr int DEC_SLOT_BYTES = 16384;   // one FP4 page (K4, V4, scale atoms) or one 16-bit K or V page
+constexpr int DEC_THREADS = 224;
+constexpr int DEC_NS4 = 5;              // ring slots while the chain reads FP4 pages
+constexpr int DEC_SLOT4_BYTES = 9728;   //   K4 4096 + V4 4096 + K scale atoms 1024 + V scale atom 512
+constexpr int DEC_NS16 = 3;             // ring slots while it reads 16-bit pages (same memory, re-cut)
+constexpr int DEC_SLOT16_BYTES = 16384; //   one K or V page
+constexpr int DEC_RING_BYTES = 49152;
+static_assert(DEC_NS4 * DEC_SLOT4_BYTES <= DEC_RING_BYTES && DEC_NS16 * DEC_SLOT16_BYTES <= DEC_RING_BYTES, "ring size");
+static_assert(DEC_SLOT4_BYTES % 512 == 0, "FP4 slots keep the 64-byte-swizzle alignment");
 constexpr int DEC_LIST_CAP = 1024;      // pages per chain
 constexpr int DEC_MAX_GROUP = 16;
 
@@ -53,6 +64,18 @@ constexpr uint32_t DTM_COLS = 256;
 constexpr uint32_t L_FP16 = 0x80000000u;  // page-list flag: 16-bit page
 
 __device__ int g_decode_status;           // set to 1 by a kernel whose bounded wait ran out
+
+// Optional phase timers for the softmax warps (development aid; compiled out by default).
+#ifdef TA100_PROFILE_SOFTMAX
+__device__ long long g_dec_prof[16];
+#define DEC_PROF_DECL long long prof_t = clock64(), prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+#define DEC_PROF(i) { const long long now_ = clock64(); prof_acc[i] += now_ - prof_t; prof_t = now_; }
+#define DEC_PROF_DUMP if (blockIdx.x == 0 && blockIdx.y == 0 && warp == 3 && lane == 0) { for (int i_ = 0; i_ < 10; ++i_) g_dec_prof[i_] = prof_acc[i_]; g_dec_prof[10] = n; }
+#else
+#define DEC_PROF_DECL
+#define DEC_PROF(i)
+#define DEC_PROF_DUMP
+#endif
 
 struct DecodeParams {
     const uint16_t* q_hi;   // [heads, G, D]
@@ -78,11 +101,11 @@ struct DecSmem {
     static constexpr int Q16 = QSF + 1024;                // 128 x D x 2, two 64-column halves, 128-byte swizzle
     static constexpr int P = Q16 + 128 * D * 2;           // 16 KB: two 4 KB FP4 buffers or one 16-bit tile
     static constexpr int SLOTS = P + 16384;
-    static constexpr int PSF = SLOTS + DEC_NSLOTS * DEC_SLOT_BYTES;   // two 512-byte atoms
+    static constexpr int PSF = SLOTS + DEC_RING_BYTES;    // two 512-byte atoms
     static constexpr int LIST = PSF + 1024;               // DEC_LIST_CAP x u32
     static constexpr int BITS = LIST + DEC_LIST_CAP * 4;  // 64 words: selected pages of the chain
     static constexpr int BARS = BITS + 256;
-    static constexpr int TOTAL = BARS + 512;
+    static constexpr int TOTAL = BARS + 1024;
     // inside an FP4 slot
     static constexpr int K4 = 0, V4 = 4096, KSF = 8192, VSF = 9216;
     static_assert(Q16 % 1024 == 0 && P % 1024 == 0 && SLOTS % 1024 == 0, "swizzled tiles need 1024-byte alignment");
@@ -91,20 +114,50 @@ struct DecSmem {
 
 struct DecBars {
     uint64_t q_ready, list_full;
-    uint64_t slot_full[DEC_NSLOTS], slot_empty[DEC_NSLOTS], sf_full[DEC_NSLOTS];
+    uint64_t f_full[DEC_NS4], f_empty[DEC_NS4];   // FP4 ring: page landed (TMA bytes + 32 scale-atom arrivals), released
+    // 16-bit ring.  A slot alternates between K and V tiles and the two kinds are consumed by different warps; a
+    // parity wait only works for a waiter that sees every phase of its barrier, so K and V arrivals are kept on
+    // separate barriers (page j: K tile 2j and V tile 2j + 1, slot = tile mod 3, use index j / 3 on either kind).
+    uint64_t hk_full[DEC_NS16], hv_full[DEC_NS16], h_empty[DEC_NS16];
     uint64_t s_full, s_free;
     uint64_t p_full[2], p_free[2];
     uint64_t epi_full;
     int n_total, n_fp4;
     uint32_t tmem_base;
     int abort_flag;
+    int abort_code;     // which wait gave up first (development aid, reported through the status word)
     float m_row[DEC_MAX_GROUP];
     float l_part[4][DEC_MAX_GROUP];
 };
-static_assert(sizeof(DecBars) <= 512, "barrier block must fit its shared-memory slot");
+static_assert(sizeof(DecBars) <= 1024, "barrier block must fit its shared-memory slot");
 
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// packed fp32x2 arithmetic (two values per instruction) and a three-input maximum
+__device__ __forceinline__ uint64_t pack2f(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2f(uint64_t v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 // Page list of one chain (whole warp): FP4 pages ascending, then the selected pages ascending.
@@ -160,6 +213,12 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
     const uint32_t sbase = smem_u32(smem);
     volatile int* abortp = &bars.abort_flag;
     const long long budget = p.budget;
+    // bounded wait that remembers the first site that gave up
+    auto waitc = [&](int code, uint64_t* bar, uint32_t parity) -> bool {
+        if (mbar_wait(smem_u32(bar), parity, abortp, budget)) return true;
+        atomicCAS(&bars.abort_code, 0, code);
+        return false;
+    };
 
     const int split = blockIdx.x, h = blockIdx.y;
     const int b = h / p.hkv, kvh = h - b * p.hkv;
@@ -174,10 +233,14 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
         mbar_init(smem_u32(&bars.s_full), 1);
         mbar_init(smem_u32(&bars.s_free), 128);
         mbar_init(smem_u32(&bars.epi_full), 128);
-        for (int i = 0; i < DEC_NSLOTS; ++i) {
-            mbar_init(smem_u32(&bars.slot_full[i]), 1);
-            mbar_init(smem_u32(&bars.slot_empty[i]), 1);
-            mbar_init(smem_u32(&bars.sf_full[i]), 128);
+        for (int i = 0; i < DEC_NS4; ++i) {
+            mbar_init(smem_u32(&bars.f_full[i]), 33);   // lane 0's expect_tx arrival + one arrival per lane
+            mbar_init(smem_u32(&bars.f_empty[i]), 1);
+        }
+        for (int i = 0; i < DEC_NS16; ++i) {
+            mbar_init(smem_u32(&bars.hk_full[i]), 1);
+            mbar_init(smem_u32(&bars.hv_full[i]), 1);
+            mbar_init(smem_u32(&bars.h_empty[i]), 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&bars.p_full[i]), 128);
@@ -185,6 +248,7 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
         }
         mbar_fence_init();
         bars.abort_flag = (sbase & 1023u) ? 1 : 0;
+        bars.abort_code = 0;
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(&bars.tmem_base), DTM_COLS);
@@ -207,125 +271,172 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
         __syncwarp();
         __threadfence_block();
         if (lane == 0) mbar_arrive(smem_u32(&bars.list_full));
-        uint32_t gslot = 0;
+        // ---- FP4 pages: TMA for the codes; the lanes fetch the page's block scales two pages ahead and store
+        //      them in atom order (word m0 * 4 + m1 holds the scales of row / channel 32 * m1 + m0) ----
+        constexpr int KS_PAGE = PAGE * (D / GRP), VS_PAGE = D * (PAGE / GRP);
+        constexpr int KW = MX ? 2 : 4;   // K scale words per lane and page
+        auto load_sf = [&](int i, uint32_t (&kw)[4], uint32_t (&vw)[4]) {
+            if (i >= n_fp4) return;
+            const uint32_t key = list[i];
+            const uint32_t* kp = reinterpret_cast<const uint32_t*>(
+                paged ? p.ks + static_cast<long long>(key) * KS_PAGE
+                      : p.ks + (static_cast<long long>(h) * p.cap_pages + key) * KS_PAGE);
+#pragma unroll
+            for (int j = 0; j < KW; ++j) kw[j] = __ldg(kp + lane + 32 * j);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int ch = lane + 32 * j;
+                if constexpr (MX) {
+                    const uint8_t* vp = paged ? p.vs + static_cast<long long>(key) * VS_PAGE + ch * 2
+                                              : p.vs + (static_cast<long long>(h) * D + ch) * p.vs_row_stride + key * 2;
+                    vw[j] = __ldg(reinterpret_cast<const uint16_t*>(vp));
+                } else {
+                    const uint8_t* vp = paged ? p.vs + static_cast<long long>(key) * VS_PAGE + ch * 4
+                                              : p.vs + (static_cast<long long>(h) * D + ch) * p.vs_row_stride + key * 4;
+                    vw[j] = __ldg(reinterpret_cast<const uint32_t*>(vp));
+                }
+            }
+        };
+        auto fp4_step = [&](int i, const uint32_t (&kw)[4], const uint32_t (&vw)[4]) -> bool {
+            const uint32_t slot = i % DEC_NS4;
+            if (!waitc(1, &bars.f_empty[slot], ((i / DEC_NS4) & 1) ^ 1)) return false;
+            const uint32_t key = list[i];
+            const int slab = paged ? static_cast<int>(key) : h;
+            if (lane == 0) {
+                const uint32_t bar = smem_u32(&bars.f_full[slot]);
+                const uint32_t sa = sbase + L::SLOTS + slot * DEC_SLOT4_BYTES;
+                mbar_expect_tx(bar, PAGE * (D / 2) + D * (PAGE / 2));
+                tma_load_3d(sa + L::K4, &mapK4, bar, 0, paged ? 0 : static_cast<int>(key) * PAGE, slab);
+                tma_load_3d(sa + L::V4, &mapV4, bar, paged ? 0 : static_cast<int>(key) * (PAGE / 2), 0, slab);
+            }
+            uint8_t* sl = smem + L::SLOTS + slot * DEC_SLOT4_BYTES;
+#pragma unroll
+            for (int j = 0; j < KW; ++j) {
+                const int w = lane + 32 * j;
+                if constexpr (MX) reinterpret_cast<uint32_t*>(sl + L::KSF)[(w & 31) * 4 + (w >> 5)] = kw[j];
+                else reinterpret_cast<uint32_t*>(sl + L::KSF + (w & 1) * 512)[((w >> 1) & 31) * 4 + (w >> 6)] = kw[j];
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) reinterpret_cast<uint32_t*>(sl + L::VSF)[lane * 4 + j] = vw[j];
+            fence_proxy_async_smem();
+            mbar_arrive(smem_u32(&bars.f_full[slot]));
+            return true;
+        };
         bool ok = true;
-        for (int i = 0; i < n && ok; ++i) {
-            const uint32_t e = list[i];
-            const int key = static_cast<int>(e & ~L_FP16);
-            // tensor coordinates: (x, row, slab).  Pool: slab = key.  Cache: slab = head, rows / columns by page.
-            const int slab = paged ? key : h;
-            const int row0 = paged ? 0 : key * PAGE;
-            if (!(e & L_FP16)) {
-                const uint32_t slot = gslot % DEC_NSLOTS;
-                ok = mbar_wait(smem_u32(&bars.slot_empty[slot]), ((gslot / DEC_NSLOTS) & 1) ^ 1, abortp, budget);
+        {
+            uint32_t kwa[4] = {0, 0, 0, 0}, vwa[4] = {0, 0, 0, 0}, kwb[4] = {0, 0, 0, 0}, vwb[4] = {0, 0, 0, 0};
+            load_sf(0, kwa, vwa);
+            load_sf(1, kwb, vwb);
+            for (int i = 0; i < n_fp4 && ok; i += 2) {
+                ok = fp4_step(i, kwa, vwa);
+                if (!ok) break;
+                load_sf(i + 2, kwa, vwa);
+                if (i + 1 < n_fp4) {
+                    ok = fp4_step(i + 1, kwb, vwb);
+                    if (!ok) break;
+                    load_sf(i + 3, kwb, vwb);
+                }
+            }
+        }
+        // ---- 16-bit pages: the ring is re-cut into 16 KB tiles once every FP4 slot has drained ----
+        if (ok && n > n_fp4) {
+            for (int sl = 0; sl < DEC_NS4 && ok; ++sl) {
+                const int uses = (n_fp4 - sl + DEC_NS4 - 1) / DEC_NS4;   // FP4 pages that went through slot sl
+                if (uses > 0) ok = waitc(1, &bars.f_empty[sl], (uses - 1) & 1);
+            }
+        }
+        uint32_t t16 = 0;
+        for (int i = n_fp4; i < n && ok; ++i) {
+            const uint32_t key = list[i] & ~L_FP16;
+            const int slab = paged ? static_cast<int>(key) : h;
+            const int row0 = paged ? 0 : static_cast<int>(key) * PAGE;
+            for (int which = 0; which < 2 && ok; ++which, ++t16) {   // K page, then V page
+                const uint32_t slot = t16 % DEC_NS16;
+                ok = waitc(2, &bars.h_empty[slot], ((t16 / DEC_NS16) & 1) ^ 1);
                 if (!ok) break;
                 if (lane == 0) {
-                    const uint32_t bar = smem_u32(&bars.slot_full[slot]);
-                    const uint32_t sa = sbase + L::SLOTS + slot * DEC_SLOT_BYTES;
-                    mbar_expect_tx(bar, PAGE * (D / 2) + D * (PAGE / 2));
-                    tma_load_3d(sa + L::K4, &mapK4, bar, 0, row0, slab);
-                    tma_load_3d(sa + L::V4, &mapV4, bar, paged ? 0 : key * (PAGE / 2), 0, slab);
-                }
-                gslot += 1;
-            } else {
-                for (int which = 0; which < 2 && ok; ++which) {   // K page, then V page
-                    const uint32_t slot = gslot % DEC_NSLOTS;
-                    ok = mbar_wait(smem_u32(&bars.slot_empty[slot]), ((gslot / DEC_NSLOTS) & 1) ^ 1, abortp, budget);
-                    if (!ok) break;
-                    if (lane == 0) {
-                        const uint32_t bar = smem_u32(&bars.slot_full[slot]);
-                        const uint32_t sa = sbase + L::SLOTS + slot * DEC_SLOT_BYTES;
-                        mbar_expect_tx(bar, PAGE * D * 2);
-                        for (int hf = 0; hf < D / 64; ++hf)
-                            tma_load_3d(sa + hf * PAGE * 128, which ? &mapV16 : &mapK16, bar, hf * 64, row0, slab);
-                    }
-                    gslot += 1;
+                    const uint32_t bar = smem_u32(which ? &bars.hv_full[slot] : &bars.hk_full[slot]);
+                    const uint32_t sa = sbase + L::SLOTS + slot * DEC_SLOT16_BYTES;
+                    mbar_expect_tx(bar, PAGE * D * 2);
+                    for (int hf = 0; hf < D / 64; ++hf)
+                        tma_load_3d(sa + hf * PAGE * 128, which ? &mapV16 : &mapK16, bar, hf * 64, row0, slab);
                 }
             }
         }
     } else if (warp == 1) {
-        // =========================== MMA issuer ===========================
+        // =========================== issuer of S = Q K^T ===========================
         const uint32_t idesc_qk4 = make_idesc_fp4(128, PAGE, MX ? 1 : 0, 0, 0);
-        const uint32_t idesc_pv4 = make_idesc_fp4(128, D, MX ? 1 : 0, 0, 0);
         const uint32_t idesc_qk16 = make_idesc_f16(128, PAGE, BF16 ? 1 : 0, 0, 0);
-        const uint32_t idesc_pv16 = make_idesc_f16(128, D, BF16 ? 1 : 0, 0, 1);
-        bool ok = mbar_wait(smem_u32(&bars.q_ready), 0, abortp, budget) &&
-                  mbar_wait(smem_u32(&bars.list_full), 0, abortp, budget);
+        bool ok = waitc(3, &bars.q_ready, 0) &&
+                  waitc(4, &bars.list_full, 0);
         const int n = ok ? bars.n_total : 0;
+        const int n4 = ok ? bars.n_fp4 : 0;
         tc_fence_after_sync();
         if (ok && lane == 0)
             for (int a = 0; a < QK_ATOMS; ++a)
                 tmem_cp_sf(tmem + DTM_SFA_Q + a * 4, make_smem_desc(sbase + L::QSF + a * 512, 0, 128, SWZ_NONE));
-
-        // S = Q K^T of list entry `e`, operands in ring slot `slot` (one thread issues)
-        auto issue_qk = [&](uint32_t e, uint32_t slot) {
-            const uint32_t sa = sbase + L::SLOTS + slot * DEC_SLOT_BYTES;
-            const uint32_t d_t = tmem + DTM_S;
-            if (!(e & L_FP16)) {
-                const uint32_t sfb = tmem + DTM_SFB_K;
-                for (int a = 0; a < QK_ATOMS; ++a)
-                    tmem_cp_sf(sfb + a * 4, make_smem_desc(sa + L::KSF + a * 512, 0, 128, SWZ_NONE));
-                for (int kb = 0; kb < KBLK; ++kb) {
-                    const uint64_t ad = make_smem_desc(sbase + L::Q4 + kb * 32, 16, 512, SWZ_64B);
-                    const uint64_t bd = make_smem_desc(sa + L::K4 + kb * 32, 16, 512, SWZ_64B);
-                    if constexpr (MX)
-                        mma_mxfp4(d_t, ad, bd, make_idesc_fp4(128, PAGE, 1, kb * 2, kb * 2), tmem + DTM_SFA_Q, sfb, kb > 0);
-                    else
-                        mma_nvfp4(d_t, ad, bd, idesc_qk4, tmem + DTM_SFA_Q + kb * 4, sfb + kb * 4, kb > 0);
-                }
-            } else {
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t hf = ks / 4, kk = ks % 4;
-                    const uint64_t ad = make_smem_desc(sbase + L::Q16 + hf * 128 * 128 + kk * 32, 16, 1024, SWZ_128B);
-                    const uint64_t bd = make_smem_desc(sa + hf * PAGE * 128 + kk * 32, 16, 1024, SWZ_128B);
-                    mma_f16(d_t, ad, bd, idesc_qk16, ks > 0);
-                }
-                tc_commit(smem_u32(&bars.slot_empty[slot]));   // the K page is free once S is computed
-            }
-            tc_commit(smem_u32(&bars.s_full));
-        };
-        auto wait_operands = [&](uint32_t e, uint32_t gs) -> bool {
-            const uint32_t slot = gs % DEC_NSLOTS, par = (gs / DEC_NSLOTS) & 1;
-            bool good = mbar_wait(smem_u32(&bars.slot_full[slot]), par, abortp, budget);
-            if (good && !(e & L_FP16)) good = mbar_wait(smem_u32(&bars.sf_full[slot]), par, abortp, budget);
-            return good;
-        };
-
-        uint32_t qk_slot = 0;   // ring position of the step whose QK is issued next
-        if (ok && n > 0) {
-            const uint32_t e0 = list[0];
-            ok = wait_operands(e0, qk_slot);
-            if (ok) {
-                tc_fence_after_sync();
-                if (lane == 0) issue_qk(e0, qk_slot % DEC_NSLOTS);
-                __syncwarp();
-            }
-        }
+        // ring position of step i: FP4 page -> slot i mod 5; 16-bit page -> tiles 2 (i - n4) (K) and + 1 (V)
         for (int i = 0; i < n && ok; ++i) {
-            const uint32_t e = list[i];
-            const bool fp16 = e & L_FP16;
-            const uint32_t my_slot = qk_slot;                   // FP4: the page's slot; 16-bit: its K slot
-            const uint32_t pv_slot = fp16 ? my_slot + 1 : my_slot;
-            qk_slot = pv_slot + 1;
-            if (i + 1 < n) {   // S of the next page as soon as the softmax warps have read this one
-                const uint32_t e1 = list[i + 1];
-                ok = wait_operands(e1, qk_slot) &&
-                     mbar_wait(smem_u32(&bars.s_free), i & 1, abortp, budget);
-                if (!ok) break;
-                tc_fence_after_sync();
-                if (lane == 0) issue_qk(e1, qk_slot % DEC_NSLOTS);
-                __syncwarp();
+            // operands of page i, and S of page i - 1 read by the softmax warps
+            if (i < n4) {
+                ok = waitc(5, &bars.f_full[i % DEC_NS4], (i / DEC_NS4) & 1);
+            } else {
+                const uint32_t j = i - n4, kt = 2u * j;
+                ok = waitc(6, &bars.hk_full[kt % DEC_NS16], (j / DEC_NS16) & 1);
             }
-            const uint32_t buf = i & 1;
-            ok = mbar_wait(smem_u32(&bars.p_full[buf]), (i >> 1) & 1, abortp, budget);
-            if (ok && fp16) ok = mbar_wait(smem_u32(&bars.slot_full[pv_slot % DEC_NSLOTS]), (pv_slot / DEC_NSLOTS) & 1, abortp, budget);
+            if (ok && i > 0) ok = waitc(7, &bars.s_free, (i - 1) & 1);
             if (!ok) break;
             tc_fence_after_sync();
             if (lane == 0) {
-                const uint32_t sa = sbase + L::SLOTS + (pv_slot % DEC_NSLOTS) * DEC_SLOT_BYTES;
+                const uint32_t d_t = tmem + DTM_S;
+                if (i < n4) {
+                    const uint32_t sa = sbase + L::SLOTS + (i % DEC_NS4) * DEC_SLOT4_BYTES;
+                    const uint32_t sfb = tmem + DTM_SFB_K;
+                    for (int a = 0; a < QK_ATOMS; ++a)
+                        tmem_cp_sf(sfb + a * 4, make_smem_desc(sa + L::KSF + a * 512, 0, 128, SWZ_NONE));
+                    for (int kb = 0; kb < KBLK; ++kb) {
+                        const uint64_t ad = make_smem_desc(sbase + L::Q4 + kb * 32, 16, 512, SWZ_64B);
+                        const uint64_t bd = make_smem_desc(sa + L::K4 + kb * 32, 16, 512, SWZ_64B);
+                        if constexpr (MX)
+                            mma_mxfp4(d_t, ad, bd, make_idesc_fp4(128, PAGE, 1, kb * 2, kb * 2), tmem + DTM_SFA_Q, sfb, kb > 0);
+                        else
+                            mma_nvfp4(d_t, ad, bd, idesc_qk4, tmem + DTM_SFA_Q + kb * 4, sfb + kb * 4, kb > 0);
+                    }
+                } else {
+                    const uint32_t kt = 2u * (i - n4);
+                    const uint32_t sa = sbase + L::SLOTS + (kt % DEC_NS16) * DEC_SLOT16_BYTES;
+                    for (int ks = 0; ks < D / 16; ++ks) {
+                        const uint32_t hf = ks / 4, kk = ks % 4;
+                        const uint64_t ad = make_smem_desc(sbase + L::Q16 + hf * 128 * 128 + kk * 32, 16, 1024, SWZ_128B);
+                        const uint64_t bd = make_smem_desc(sa + hf * PAGE * 128 + kk * 32, 16, 1024, SWZ_128B);
+                        mma_f16(d_t, ad, bd, idesc_qk16, ks > 0);
+                    }
+                    tc_commit(smem_u32(&bars.h_empty[kt % DEC_NS16]));   // the K page is free once S is computed
+                }
+                tc_commit(smem_u32(&bars.s_full));
+            }
+            __syncwarp();
+        }
+    } else if (warp == 2) {
+        // =========================== issuer of O += P V ===========================
+        const uint32_t idesc_pv4 = make_idesc_fp4(128, D, MX ? 1 : 0, 0, 0);
+        const uint32_t idesc_pv16 = make_idesc_f16(128, D, BF16 ? 1 : 0, 0, 1);
+        bool ok = waitc(4, &bars.list_full, 0);
+        const int n = ok ? bars.n_total : 0;
+        const int n4 = ok ? bars.n_fp4 : 0;
+        for (int i = 0; i < n && ok; ++i) {
+            const bool fp16 = i >= n4;
+            const uint32_t buf = i & 1;
+            const uint32_t vt = 2u * (i - n4) + 1u;   // V tile of a 16-bit step
+            ok = waitc(8, &bars.p_full[buf], (i >> 1) & 1);
+            if (ok && fp16) ok = waitc(6, &bars.hv_full[vt % DEC_NS16], ((i - n4) / DEC_NS16) & 1);
+            if (!ok) break;
+            tc_fence_after_sync();
+            if (lane == 0) {
                 const uint32_t d_t = tmem + DTM_O;
                 const uint32_t acc = i > 0 ? 1u : 0u;
                 if (!fp16) {
+                    const uint32_t sa = sbase + L::SLOTS + (i % DEC_NS4) * DEC_SLOT4_BYTES;
                     const uint32_t sfa = tmem + DTM_SFA_P + buf * 4, sfb = tmem + DTM_SFB_V + buf * 4;
                     tmem_cp_sf(sfa, make_smem_desc(sbase + L::PSF + buf * 512, 0, 128, SWZ_NONE));
                     tmem_cp_sf(sfb, make_smem_desc(sa + L::VSF, 0, 128, SWZ_NONE));
@@ -333,14 +444,16 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
                     const uint64_t bd = make_smem_desc(sa + L::V4, 16, 256, SWZ_32B);
                     if constexpr (MX) mma_mxfp4(d_t, ad, bd, idesc_pv4, sfa, sfb, acc);
                     else mma_nvfp4(d_t, ad, bd, idesc_pv4, sfa, sfb, acc);
+                    tc_commit(smem_u32(&bars.f_empty[i % DEC_NS4]));
                 } else {
+                    const uint32_t sa = sbase + L::SLOTS + (vt % DEC_NS16) * DEC_SLOT16_BYTES;
                     for (int ks = 0; ks < PAGE / 16; ++ks) {
                         const uint64_t ad = make_smem_desc(sbase + L::P + ks * 32, 16, 1024, SWZ_128B);
                         const uint64_t bd = make_smem_desc(sa + ks * 2048, PAGE * 128, 1024, SWZ_128B);
                         mma_f16(d_t, ad, bd, idesc_pv16, (acc == 0 && ks == 0) ? 0 : 1);
                     }
+                    tc_commit(smem_u32(&bars.h_empty[vt % DEC_NS16]));
                 }
-                tc_commit(smem_u32(&bars.slot_empty[pv_slot % DEC_NSLOTS]));
                 tc_commit(smem_u32(&bars.p_free[buf]));
             }
             __syncwarp();
@@ -388,63 +501,21 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
         fence_proxy_async_smem();
         mbar_arrive(smem_u32(&bars.q_ready));
 
-        bool ok = mbar_wait(smem_u32(&bars.list_full), 0, abortp, budget);
+        bool ok = waitc(21, &bars.list_full, 0);
         const int n = ok ? bars.n_total : 0;
         const int n4 = ok ? bars.n_fp4 : 0;
 
-        // Block scales of FP4 page i: one 32-bit K word and one V word per thread, fetched a page ahead and
-        // stored in atom order (word m0 * 4 + m1 holds the scales of row / channel 32 * m1 + m0).
-        constexpr int KS_PAGE = PAGE * (D / GRP), VS_PAGE = D * (PAGE / GRP);
-        auto load_sf = [&](int i, uint32_t& kw, uint32_t& vw) {
-            kw = 0u; vw = 0u;
-            if (i >= n4) return;
-            const uint32_t key = list[i];
-            const uint8_t* kp = paged ? p.ks + static_cast<long long>(key) * KS_PAGE
-                                      : p.ks + (static_cast<long long>(h) * p.cap_pages + key) * KS_PAGE;
-            if (!MX || row < 64) kw = __ldg(reinterpret_cast<const uint32_t*>(kp) + row);
-            if constexpr (MX) {
-                const uint8_t* vp = paged ? p.vs + static_cast<long long>(key) * VS_PAGE + row * 2
-                                          : p.vs + (static_cast<long long>(h) * D + row) * p.vs_row_stride + key * 2;
-                vw = __ldg(reinterpret_cast<const uint16_t*>(vp));
-            } else {
-                const uint8_t* vp = paged ? p.vs + static_cast<long long>(key) * VS_PAGE + row * 4
-                                          : p.vs + (static_cast<long long>(h) * D + row) * p.vs_row_stride + key * 4;
-                vw = __ldg(reinterpret_cast<const uint32_t*>(vp));
-            }
-        };
-        auto store_sf = [&](int i, uint32_t kw, uint32_t vw) -> bool {
-            const uint32_t slot = i % DEC_NSLOTS;
-            if (!mbar_wait(smem_u32(&bars.slot_empty[slot]), ((i / DEC_NSLOTS) & 1) ^ 1, abortp, budget)) return false;
-            uint8_t* sa = smem + L::SLOTS + slot * DEC_SLOT_BYTES;
-            if constexpr (MX) {
-                if (row < 64) reinterpret_cast<uint32_t*>(sa + L::KSF)[(row & 31) * 4 + (row >> 5)] = kw;
-            } else {
-                const int tok = row >> 1;
-                reinterpret_cast<uint32_t*>(sa + L::KSF + (row & 1) * 512)[(tok & 31) * 4 + (tok >> 5)] = kw;
-            }
-            reinterpret_cast<uint32_t*>(sa + L::VSF)[lane * 4 + sub] = vw;
-            fence_proxy_async_smem();
-            mbar_arrive(smem_u32(&bars.sf_full[slot]));
-            return true;
-        };
-
-        uint32_t kw, vw;
-        load_sf(0, kw, vw);
-        if (ok && n4 > 0) ok = store_sf(0, kw, vw);
-        load_sf(1, kw, vw);
-
         float m_run = -FLT_MAX, l_run = 0.0f;
         bool prev_fp16 = false;
+        DEC_PROF_DECL
+        DEC_PROF(9)
         for (int i = 0; i < n && ok; ++i) {
-            const bool fp16 = (list[i] & L_FP16) != 0u;
-            if (i + 1 < n4) {
-                ok = store_sf(i + 1, kw, vw);
-                if (!ok) break;
-                load_sf(i + 2, kw, vw);
-            }
-            ok = mbar_wait(smem_u32(&bars.s_full), i & 1, abortp, budget);
+            const bool fp16 = i >= n4;
+            DEC_PROF(0)
+            ok = waitc(22, &bars.s_full, i & 1);
             if (!ok) break;
             tc_fence_after_sync();
+            DEC_PROF(1)
             float s[16];
             {
                 uint32_t r0[16], r1[16], r2[16], r3[16];
@@ -461,11 +532,11 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
             }
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&bars.s_free));
+            DEC_PROF(2)
 
             // running maximum of the whole page row (the four quarters sit in neighbouring lanes)
-            float mx = s[0];
-#pragma unroll
-            for (int j = 1; j < 16; ++j) mx = fmaxf(mx, s[j]);
+            float mx = fmaxf(max3(max3(s[0], s[1], s[2]), max3(s[3], s[4], s[5]), max3(s[6], s[7], s[8])),
+                             max3(max3(s[9], s[10], s[11]), max3(s[12], s[13], s[14]), s[15]));
             mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
             const float m_new = fmaxf(m_run, mx);
@@ -474,15 +545,17 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
             m_run = m_new;
 
             const uint32_t buf = i & 1;
-            ok = mbar_wait(smem_u32(&bars.p_free[buf]), ((i >> 1) & 1) ^ 1, abortp, budget);
+            DEC_PROF(3)
+            ok = waitc(23, &bars.p_free[buf], ((i >> 1) & 1) ^ 1);
             if (!ok) break;
             const bool need_rescale = __any_sync(0xFFFFFFFFu, changed);
             if ((need_rescale || fp16 || prev_fp16) && i > 0) {
                 // O, or a P tile spanning both buffers, is about to be touched: the previous PV must be done
-                ok = mbar_wait(smem_u32(&bars.p_free[(i - 1) & 1]), ((i - 1) >> 1) & 1, abortp, budget);
+                ok = waitc(23, &bars.p_free[(i - 1) & 1], ((i - 1) >> 1) & 1);
                 if (!ok) break;
             }
             tc_fence_after_sync();
+            DEC_PROF(4)
             if (need_rescale) {
                 const float f = changed ? rescale : 1.0f;
 #pragma unroll 1
@@ -496,28 +569,47 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
                 }
                 tmem_wait_st();
             }
+            DEC_PROF(5)
 
             if (!fp16) {
                 // t = C p; group scale sf = amax(t) / 6 rounded to the scale format; codes = e2m1(t / sf), with
                 // the un-rounded sf, as the reference computes them
                 float t[16];
-                float sum = 0.0f, amax = 0.0f;
+                {
+                    const uint64_t mneg = pack2f(-m_new, -m_new), c2p = pack2f(p.c2, p.c2), cs = pack2f(CSCALE, CSCALE);
+                    const uint64_t zero = pack2f(0.0f, 0.0f);
+                    uint64_t acc0 = zero, acc1 = zero;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float pj = ex2((s[j] - m_new) * p.c2);   // exactly 1 at the row maximum
-                    sum += pj;
-                    t[j] = __fmul_rn(pj, CSCALE);
-                    amax = fmaxf(amax, t[j]);
+                    for (int j = 0; j < 16; j += 4) {
+                        float a0, a1, b0, b1;
+                        // (s - m) * c2 is exactly 0 at the row maximum, so p is exactly 1 there
+                        unpack2f(mul2(add2(pack2f(s[j], s[j + 1]), mneg), c2p), a0, a1);
+                        unpack2f(mul2(add2(pack2f(s[j + 2], s[j + 3]), mneg), c2p), b0, b1);
+                        const uint64_t pa = pack2f(ex2(a0), ex2(a1)), pb = pack2f(ex2(b0), ex2(b1));
+                        acc0 = add2(acc0, pa);
+                        acc1 = add2(acc1, pb);
+                        unpack2f(mul2(pa, cs), t[j], t[j + 1]);
+                        unpack2f(mul2(pb, cs), t[j + 2], t[j + 3]);
+                    }
+                    float x, y;
+                    unpack2f(add2(acc0, acc1), x, y);
+                    l_run = fmaf(l_run, rescale, x + y);
                 }
-                l_run = fmaf(l_run, rescale, sum);
+                float amax = fmaxf(max3(max3(t[0], t[1], t[2]), max3(t[3], t[4], t[5]), max3(t[6], t[7], t[8])),
+                                   max3(max3(t[9], t[10], t[11]), max3(t[12], t[13], t[14]), t[15]));
                 if constexpr (MX) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
                 const float sfp = __fdiv_rn(amax, 6.0f);
                 const uint32_t sb = encode_scale<MX>(sfp);
-                const float inv = sfp > 0.0f ? __fdiv_rn(1.0f, sfp) : 0.0f;
-                const uint32_t w0 = e2m1x8(__fmul_rn(t[0], inv), __fmul_rn(t[1], inv), __fmul_rn(t[2], inv), __fmul_rn(t[3], inv),
-                                           __fmul_rn(t[4], inv), __fmul_rn(t[5], inv), __fmul_rn(t[6], inv), __fmul_rn(t[7], inv));
-                const uint32_t w1 = e2m1x8(__fmul_rn(t[8], inv), __fmul_rn(t[9], inv), __fmul_rn(t[10], inv), __fmul_rn(t[11], inv),
-                                           __fmul_rn(t[12], inv), __fmul_rn(t[13], inv), __fmul_rn(t[14], inv), __fmul_rn(t[15], inv));
+                const float inv = sfp > 0.0f ? __frcp_rn(sfp) : 0.0f;
+                uint32_t w0, w1;
+                {
+                    const uint64_t ip = pack2f(inv, inv);
+                    float c[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j += 2) unpack2f(mul2(pack2f(t[j], t[j + 1]), ip), c[j], c[j + 1]);
+                    w0 = e2m1x8(c[0], c[1], c[2], c[3], c[4], c[5], c[6], c[7]);
+                    w1 = e2m1x8(c[8], c[9], c[10], c[11], c[12], c[13], c[14], c[15]);
+                }
                 if (active) {
                     // 128 rows x 32 bytes, 32-byte swizzle; this thread's 16 codes are bytes [8 cq, 8 cq + 8) of its row
                     uint8_t* dst = smem + L::P + buf * 4096 + (row >> 3) * 256 + (row & 7) * 32 +
@@ -547,14 +639,16 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
                     *reinterpret_cast<uint4*>(base + (((2 * cq + 1) ^ (row & 7)) * 16)) = make_uint4(w[4], w[5], w[6], w[7]);
                 }
             }
+            DEC_PROF(6)
             fence_proxy_async_smem();
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&bars.p_full[buf]));
+            DEC_PROF(7)
             prev_fp16 = fp16;
         }
 
         // ---- end of chain: the four quarter rows of every head are added and written as one partial ----
-        if (ok && n > 0) ok = mbar_wait(smem_u32(&bars.p_free[(n - 1) & 1]), ((n - 1) >> 1) & 1, abortp, budget);
+        if (ok && n > 0) ok = waitc(23, &bars.p_free[(n - 1) & 1], ((n - 1) >> 1) & 1);
         if (ok) {
             tc_fence_after_sync();
             float* stage = reinterpret_cast<float*>(smem + L::SLOTS);   // [quarter][head][D]
@@ -575,7 +669,7 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
                 if (cq == 0) bars.m_row[g] = m_run * p.sm_scale;
             }
             mbar_arrive(smem_u32(&bars.epi_full));
-            ok = mbar_wait(smem_u32(&bars.epi_full), 0, abortp, budget);
+            ok = waitc(24, &bars.epi_full, 0);
         }
         if (ok) {
             const float* stage = reinterpret_cast<const float*>(smem + L::SLOTS);
@@ -592,14 +686,19 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
                 p.part_ml[(pbase + row) * 2 + 1] = (bars.l_part[0][row] + bars.l_part[1][row]) + (bars.l_part[2][row] + bars.l_part[3][row]);
             }
         }
+        DEC_PROF(8)
+        DEC_PROF_DUMP
     }
 
     // ---- common exit ----
-    if (bars.abort_flag != 0) __nanosleep(20000);   // let copies already in flight land
+    if (bars.abort_flag != 0) {
+        // copies and MMAs already issued must finish before shared and tensor memory are given back
+        for (int i = 0; i < 25; ++i) __nanosleep(20000);
+    }
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, DTM_COLS);
-    if (tid == 0 && bars.abort_flag != 0) atomicExch(&g_decode_status, 1);
+    if (tid == 0 && bars.abort_flag != 0) atomicCAS(&g_decode_status, 0, bars.abort_code != 0 ? bars.abort_code : 99);
 }
 
 // out[row, :] = sum_s O_s e^{m_s - M} / (C sum_s l_s e^{m_s - M}); rows = heads * G
@@ -657,6 +756,12 @@ int decode_pick_splits(int heads, int npages) {
     return best;
 }
 
+#ifdef TA100_PROFILE_SOFTMAX
+int decode_profile_read(long long* out16) {
+    return static_cast<int>(cudaMemcpyFromSymbol(out16, g_dec_prof, sizeof(long long) * 16));
+}
+#endif
+
 size_t decode_workspace_bytes(int heads, int G, int d, int splits) {
     return static_cast<size_t>(heads) * splits * G * (d + 2) * sizeof(float);
 }
@@ -670,6 +775,7 @@ int decode_status(cudaStream_t stream) {
     e = cudaMemcpyFromSymbol(&flag, g_decode_status, sizeof(int));
     if (e != cudaSuccess) return static_cast<int>(e);
     if (flag != 0) {
+        fprintf(stderr, "libthrift_sm100: a decode kernel gave up waiting (wait site %d)\n", flag);
         const int zero = 0;
         cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int));
         return TA100_ERR_DEVICE_TIMEOUT;
