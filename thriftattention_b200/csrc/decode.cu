@@ -56,9 +56,10 @@ constexpr int DEC_MAX_GROUP = 16;
 constexpr uint32_t DTM_O = 0;           // 128 columns
 constexpr uint32_t DTM_S = 128;         // 64 columns
 constexpr uint32_t DTM_SFA_Q = 192;     // up to 8 columns
-constexpr uint32_t DTM_SFB_K = 200;     // up to 8 columns
+constexpr uint32_t DTM_SFB_K = 200;     // up to 8 columns; second buffer at DTM_SFB_K2
 constexpr uint32_t DTM_SFA_P = 208;     // two buffers of 4 columns
 constexpr uint32_t DTM_SFB_V = 216;     // two buffers of 4 columns
+constexpr uint32_t DTM_SFB_K2 = 224;    // up to 8 columns
 constexpr uint32_t DTM_COLS = 256;
 
 constexpr uint32_t L_FP16 = 0x80000000u;  // page-list flag: 16-bit page
@@ -365,18 +366,27 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
         }
     } else if (warp == 1) {
         // =========================== issuer of S = Q K^T ===========================
+        // The whole warp runs this code with warp-uniform values; one elected lane issues each instruction.
         const uint32_t idesc_qk4 = make_idesc_fp4(128, PAGE, MX ? 1 : 0, 0, 0);
         const uint32_t idesc_qk16 = make_idesc_f16(128, PAGE, BF16 ? 1 : 0, 0, 0);
-        bool ok = waitc(3, &bars.q_ready, 0) &&
-                  waitc(4, &bars.list_full, 0);
-        const int n = ok ? bars.n_total : 0;
-        const int n4 = ok ? bars.n_fp4 : 0;
+        bool ok = waitc(3, &bars.q_ready, 0) && waitc(4, &bars.list_full, 0);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        const int n = __shfl_sync(0xFFFFFFFFu, ok ? bars.n_total : 0, 0);
+        const int n4 = __shfl_sync(0xFFFFFFFFu, ok ? bars.n_fp4 : 0, 0);
+        const uint32_t tm = __shfl_sync(0xFFFFFFFFu, tmem, 0);
         tc_fence_after_sync();
-        if (ok && lane == 0)
+        if (ok)
             for (int a = 0; a < QK_ATOMS; ++a)
-                tmem_cp_sf(tmem + DTM_SFA_Q + a * 4, make_smem_desc(sbase + L::QSF + a * 512, 0, 128, SWZ_NONE));
+                tmem_cp_sf_elect(tm + DTM_SFA_Q + a * 4, make_smem_desc(sbase + L::QSF + a * 512, 0, 128, SWZ_NONE));
         // ring position of step i: FP4 page -> slot i mod 5; 16-bit page -> tiles 2 (i - n4) (K) and + 1 (V)
+#ifdef TA100_PROFILE_SOFTMAX
+        long long qprof[5] = {0, 0, 0, 0, 0}, qt = clock64();
+#define DEC_QPROF(k) { const long long now_ = clock64(); qprof[k] += now_ - qt; qt = now_; }
+#else
+#define DEC_QPROF(k)
+#endif
         for (int i = 0; i < n && ok; ++i) {
+            DEC_QPROF(4)
             // operands of page i, and S of page i - 1 read by the softmax warps
             if (i < n4) {
                 ok = waitc(5, &bars.f_full[i % DEC_NS4], (i / DEC_NS4) & 1);
@@ -384,39 +394,51 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
                 const uint32_t j = i - n4, kt = 2u * j;
                 ok = waitc(6, &bars.hk_full[kt % DEC_NS16], (j / DEC_NS16) & 1);
             }
-            if (ok && i > 0) ok = waitc(7, &bars.s_free, (i - 1) & 1);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            DEC_QPROF(0)
+            // the K scale atoms go to tensor memory (two alternating buffers) before S of the previous page is free
+            const uint32_t sfb = tm + ((i & 1) ? DTM_SFB_K2 : DTM_SFB_K);
+            tc_fence_after_sync();
+            if (i < n4) {
+                const uint32_t sa = sbase + L::SLOTS + (i % DEC_NS4) * DEC_SLOT4_BYTES;
+                for (int a = 0; a < QK_ATOMS; ++a)
+                    tmem_cp_sf_elect(sfb + a * 4, make_smem_desc(sa + L::KSF + a * 512, 0, 128, SWZ_NONE));
+            }
+            DEC_QPROF(1)
+            if (i > 0) ok = waitc(7, &bars.s_free, (i - 1) & 1);
+            ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             tc_fence_after_sync();
-            if (lane == 0) {
-                const uint32_t d_t = tmem + DTM_S;
-                if (i < n4) {
-                    const uint32_t sa = sbase + L::SLOTS + (i % DEC_NS4) * DEC_SLOT4_BYTES;
-                    const uint32_t sfb = tmem + DTM_SFB_K;
-                    for (int a = 0; a < QK_ATOMS; ++a)
-                        tmem_cp_sf(sfb + a * 4, make_smem_desc(sa + L::KSF + a * 512, 0, 128, SWZ_NONE));
-                    for (int kb = 0; kb < KBLK; ++kb) {
-                        const uint64_t ad = make_smem_desc(sbase + L::Q4 + kb * 32, 16, 512, SWZ_64B);
-                        const uint64_t bd = make_smem_desc(sa + L::K4 + kb * 32, 16, 512, SWZ_64B);
-                        if constexpr (MX)
-                            mma_mxfp4(d_t, ad, bd, make_idesc_fp4(128, PAGE, 1, kb * 2, kb * 2), tmem + DTM_SFA_Q, sfb, kb > 0);
-                        else
-                            mma_nvfp4(d_t, ad, bd, idesc_qk4, tmem + DTM_SFA_Q + kb * 4, sfb + kb * 4, kb > 0);
-                    }
-                } else {
-                    const uint32_t kt = 2u * (i - n4);
-                    const uint32_t sa = sbase + L::SLOTS + (kt % DEC_NS16) * DEC_SLOT16_BYTES;
-                    for (int ks = 0; ks < D / 16; ++ks) {
-                        const uint32_t hf = ks / 4, kk = ks % 4;
-                        const uint64_t ad = make_smem_desc(sbase + L::Q16 + hf * 128 * 128 + kk * 32, 16, 1024, SWZ_128B);
-                        const uint64_t bd = make_smem_desc(sa + hf * PAGE * 128 + kk * 32, 16, 1024, SWZ_128B);
-                        mma_f16(d_t, ad, bd, idesc_qk16, ks > 0);
-                    }
-                    tc_commit(smem_u32(&bars.h_empty[kt % DEC_NS16]));   // the K page is free once S is computed
+            DEC_QPROF(2)
+            const uint32_t d_t = tm + DTM_S;
+            if (i < n4) {
+                const uint32_t sa = sbase + L::SLOTS + (i % DEC_NS4) * DEC_SLOT4_BYTES;
+                for (int kb = 0; kb < KBLK; ++kb) {
+                    const uint64_t ad = make_smem_desc(sbase + L::Q4 + kb * 32, 16, 512, SWZ_64B);
+                    const uint64_t bd = make_smem_desc(sa + L::K4 + kb * 32, 16, 512, SWZ_64B);
+                    if constexpr (MX)
+                        mma_mxfp4_elect(d_t, ad, bd, make_idesc_fp4(128, PAGE, 1, kb * 2, kb * 2), tm + DTM_SFA_Q, sfb, kb > 0);
+                    else
+                        mma_nvfp4_elect(d_t, ad, bd, idesc_qk4, tm + DTM_SFA_Q + kb * 4, sfb + kb * 4, kb > 0);
                 }
-                tc_commit(smem_u32(&bars.s_full));
+            } else {
+                const uint32_t kt = 2u * (i - n4);
+                const uint32_t sa = sbase + L::SLOTS + (kt % DEC_NS16) * DEC_SLOT16_BYTES;
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t hf = ks / 4, kk = ks % 4;
+                    const uint64_t ad = make_smem_desc(sbase + L::Q16 + hf * 128 * 128 + kk * 32, 16, 1024, SWZ_128B);
+                    const uint64_t bd = make_smem_desc(sa + hf * PAGE * 128 + kk * 32, 16, 1024, SWZ_128B);
+                    mma_f16_elect(d_t, ad, bd, idesc_qk16, ks > 0);
+                }
+                tc_commit_elect(smem_u32(&bars.h_empty[kt % DEC_NS16]));   // the K page is free once S is computed
             }
-            __syncwarp();
+            tc_commit_elect(smem_u32(&bars.s_full));
+            DEC_QPROF(3)
         }
+#ifdef TA100_PROFILE_SOFTMAX
+        if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) for (int k_ = 0; k_ < 5; ++k_) g_dec_prof[11 + k_] = qprof[k_];
+#endif
     } else if (warp == 2) {
         // =========================== issuer of O += P V ===========================
         const uint32_t idesc_pv4 = make_idesc_fp4(128, D, MX ? 1 : 0, 0, 0);
@@ -535,8 +557,15 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
             DEC_PROF(2)
 
             // running maximum of the whole page row (the four quarters sit in neighbouring lanes)
+            // the P buffer of this step was last read by the PV of step i - 2: poll once now, look at the answer
+            // only when the buffer is about to be written
+            const uint32_t buf = i & 1;
+            const uint32_t pf_parity = ((i >> 1) & 1) ^ 1;
+            bool pf_ready = mbar_try_wait(smem_u32(&bars.p_free[buf]), pf_parity);
             float mx = fmaxf(max3(max3(s[0], s[1], s[2]), max3(s[3], s[4], s[5]), max3(s[6], s[7], s[8])),
                              max3(max3(s[9], s[10], s[11]), max3(s[12], s[13], s[14]), s[15]));
+            float mx_grp = mx;   // maximum of this thread's scale group: its 16 columns, 32 for MXFP4
+            if constexpr (MX) mx_grp = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
             const float m_new = fmaxf(m_run, mx);
@@ -544,17 +573,16 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
             const float rescale = ex2((m_run - m_new) * p.c2);
             m_run = m_new;
 
-            const uint32_t buf = i & 1;
             DEC_PROF(3)
-            ok = waitc(23, &bars.p_free[buf], ((i >> 1) & 1) ^ 1);
-            if (!ok) break;
             const bool need_rescale = __any_sync(0xFFFFFFFFu, changed);
             if ((need_rescale || fp16 || prev_fp16) && i > 0) {
-                // O, or a P tile spanning both buffers, is about to be touched: the previous PV must be done
-                ok = waitc(23, &bars.p_free[(i - 1) & 1], ((i - 1) >> 1) & 1);
+                // O, or a P tile spanning both buffers, is about to be touched: both earlier PVs must be done
+                if (!pf_ready) ok = waitc(23, &bars.p_free[buf], pf_parity);
+                pf_ready = true;
+                if (ok) ok = waitc(23, &bars.p_free[(i - 1) & 1], ((i - 1) >> 1) & 1);
                 if (!ok) break;
+                tc_fence_after_sync();
             }
-            tc_fence_after_sync();
             DEC_PROF(4)
             if (need_rescale) {
                 const float f = changed ? rescale : 1.0f;
@@ -574,6 +602,12 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
             if (!fp16) {
                 // t = C p; group scale sf = amax(t) / 6 rounded to the scale format; codes = e2m1(t / sf), with
                 // the un-rounded sf, as the reference computes them
+                // amax(t) is t at the group's largest logit: the same operations on the same value
+                const float amax = __fmul_rn(ex2(__fmul_rn(mx_grp - m_new, p.c2)), CSCALE);
+                const float sfp = __fmul_rn(amax, 1.0f / 6.0f);
+                const uint32_t sb = encode_scale<MX>(sfp);
+                float inv = 0.0f;
+                if (sfp > 1e-30f) asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(sfp));
                 float t[16];
                 {
                     const uint64_t mneg = pack2f(-m_new, -m_new), c2p = pack2f(p.c2, p.c2), cs = pack2f(CSCALE, CSCALE);
@@ -595,12 +629,6 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
                     unpack2f(add2(acc0, acc1), x, y);
                     l_run = fmaf(l_run, rescale, x + y);
                 }
-                float amax = fmaxf(max3(max3(t[0], t[1], t[2]), max3(t[3], t[4], t[5]), max3(t[6], t[7], t[8])),
-                                   max3(max3(t[9], t[10], t[11]), max3(t[12], t[13], t[14]), t[15]));
-                if constexpr (MX) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-                const float sfp = __fdiv_rn(amax, 6.0f);
-                const uint32_t sb = encode_scale<MX>(sfp);
-                const float inv = sfp > 0.0f ? __frcp_rn(sfp) : 0.0f;
                 uint32_t w0, w1;
                 {
                     const uint64_t ip = pack2f(inv, inv);
@@ -609,6 +637,10 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
                     for (int j = 0; j < 16; j += 2) unpack2f(mul2(pack2f(t[j], t[j + 1]), ip), c[j], c[j + 1]);
                     w0 = e2m1x8(c[0], c[1], c[2], c[3], c[4], c[5], c[6], c[7]);
                     w1 = e2m1x8(c[8], c[9], c[10], c[11], c[12], c[13], c[14], c[15]);
+                }
+                if (!pf_ready) {
+                    ok = waitc(23, &bars.p_free[buf], pf_parity);
+                    if (!ok) break;
                 }
                 if (active) {
                     // 128 rows x 32 bytes, 32-byte swizzle; this thread's 16 codes are bytes [8 cq, 8 cq + 8) of its row
