@@ -160,6 +160,88 @@ def run_reference(args) -> dict:
     }
 
 
+
+# --------------------------------------------------------------------------------------------- decode leg
+DEC_BATCH, DEC_SEQ, DEC_GROUP = 32, 131072, HQ // HKV
+DEC_SINK, DEC_LOCAL, DEC_FRACTION = 4, 16, 0.10
+
+
+def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_gbs: float) -> dict:
+    """Second half of the headline metric: one paged decode step for 32 sequences of 131072 cached tokens
+    (64-token pages through a seeded random page table, NVFP4 + fp16 shadow, Quest top-10 % + 4 sink + 16
+    recent pages).  A step = page selection + split-KV attention + merge.  With N GPUs every sequence's pages
+    are split N ways (KV-sequence sharding): kernel-scored candidates and partial results are exchanged with
+    two all-gathers per step.  Returns microseconds per step and whole-job algorithmic GB/s."""
+    import torch.distributed as dist
+
+    from thriftattention_b200 import _C
+    from thriftattention_b200 import distributed as tad
+
+    pages = DEC_SEQ // 64
+    shard = tad.plan_page_shards(pages, world)[rank]
+    n_local = shard.num_pages
+    top_k = max(1, round(DEC_FRACTION * pages))
+    pool = DEC_BATCH * n_local
+    g = torch.Generator(device=device)
+    g.manual_seed(1234 + rank)
+    u8 = dict(dtype=torch.uint8, device=device)
+    k4 = torch.randint(0, 256, (pool, HKV, 64, D // 2), generator=g, **u8)
+    v4 = torch.randint(0, 256, (pool, HKV, D, 32), generator=g, **u8)
+    ks = torch.randint(40, 60, (pool, HKV, 64, D // 16), generator=g, **u8)      # E4M3 bytes of moderate size
+    vs = torch.randint(40, 60, (pool, HKV, D, 4), generator=g, **u8)
+    k_hi = torch.empty(pool, HKV, 64, D, dtype=torch.float16, device=device).normal_(generator=g)
+    v_hi = torch.empty(pool, HKV, 64, D, dtype=torch.float16, device=device).normal_(generator=g)
+    k_min = torch.empty(DEC_BATCH, HKV, n_local, D, dtype=torch.float16, device=device).normal_(generator=g)
+    k_max = k_min + 1
+    table = torch.randperm(pool, generator=g, device=device).to(torch.int32).reshape(DEC_BATCH, n_local)
+    gq = torch.Generator(device=device)
+    gq.manual_seed(99)                                                             # the query is replicated
+    q = torch.empty(DEC_BATCH, HKV, DEC_GROUP, D, dtype=torch.float16, device=device).normal_(generator=gq)
+
+    def step():
+        q4, qs = _C.nvfp4_quantize(q)
+        if world == 1:
+            sel = _C.select_decode_blocks(q, k_min, k_max, top_k, pages, False, sink=DEC_SINK, local=DEC_LOCAL)
+            return _C.decode_attention(q, k_hi, v_hi, sel, q4, k4, v4, qs, ks, vs, is_mx=False, is_bf16=False,
+                                       kv_len=n_local * 64, page_table=table, allow_padded_selection=True)
+        sel = tad.select_pages_sharded(q, k_min, k_max, shard=shard, total_pages=pages, top_k=top_k, sink=DEC_SINK,
+                                       local=DEC_LOCAL)
+        _, po, pml = _C.decode_attention(q, k_hi, v_hi, sel, q4, k4, v4, qs, ks, vs, is_mx=False, is_bf16=False,
+                                         kv_len=n_local * 64, page_table=table, allow_padded_selection=True,
+                                         return_partials=True)
+        all_o, all_ml = tad.exchange_partials(po, pml)
+        return _C.merge_decode_partials(all_o, all_ml, is_mx=False, is_bf16=False)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(warmup, 3)):
+        step()
+    barrier()
+    n_steps = max(steps, 5) * 4
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n_steps):
+        step()
+    e1.record()
+    barrier()
+    _C.decode_status()
+    ms = torch.tensor([e0.elapsed_time(e1) / n_steps], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    n16 = top_k + DEC_SINK + DEC_LOCAL
+    step_bytes = DEC_BATCH * HKV * ((pages - n16) * 9216 + n16 * 32768 + pages * 512)
+    gbs = step_bytes / (ms.item() * 1e-3) / 1e9
+    return {"us_per_step": ms.item() * 1e3, "value": gbs, "unit": "GB/s", "bytes_per_step": step_bytes,
+            "frac_of_hbm_peak": gbs / (hbm_gbs * world), "hbm_peak_gbs_per_gpu": hbm_gbs,
+            "workload": f"paged decode {DEC_BATCH} seq x {DEC_SEQ} tokens, {HQ}q/{HKV}kv x {D}, NVFP4 + fp16 shadow, Quest "
+                        f"{top_k} + {DEC_SINK} sink + {DEC_LOCAL} recent of {pages} pages in 16 bits; step = select + "
+                        f"attend + merge; KV sequence split over {world} GPU(s)",
+            "launches_per_step": 4 if world == 1 else 6}
+
+
 def run_ours(args) -> dict:
     import torch.distributed as dist
 
@@ -262,6 +344,17 @@ def run_ours(args) -> dict:
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     e2e_value = total_flops / (e2e_ms.item() * 1e-3) / 1e12
 
+    # ---- decode half of the metric (all ranks take part; prefill tensors are released first) ----
+    del q, k, v, out, hq_h, out_host, gathered
+    torch.cuda.empty_cache()
+    hbm_gbs = 6545.0
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            hbm_gbs = float(json.load(f)["hbm_gbs"])
+    except (OSError, KeyError, ValueError):
+        pass
+    decode = run_decode_leg(device, world, rank, args.steps, args.warmup, hbm_gbs)
+
     result = {}
     if rank == 0:
         peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -295,6 +388,7 @@ def run_ours(args) -> dict:
                          "peak_source": f"{peak_src} x blended FP4/f16 mix (FP4 peak taken as {FP4_TO_BF16_PEAK_RATIO:g}x bf16; "
                                         f"f16 FLOP share {share16:.3f})"},
         }
+        result["decode"] = decode
         if cpu is not None:
             result["cpu_baseline"] = cpu
     if world > 1:

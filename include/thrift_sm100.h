@@ -107,13 +107,15 @@ int ta100_select_prefill(const void* q_mean, const void* k_a, const void* k_b, v
 /*
  * Decode block selection.  q_grouped [flat_kv_heads, group, D]; k_a / k_b
  * [flat_kv_heads, cap_blocks, D]; score = max over the group; out
- * [flat_kv_heads, sink + local + k].  Replaces single_query_key_mean_topk,
- * single_query_key_mean_topk_chunked and single_query_quest_topk
+ * [flat_kv_heads, sink + local + k].  out_scores (NULL or fp32, same shape) receives the score
+ * of every pick (+FLT_MAX for forced blocks, -FLT_MAX for padding): a shard of a longer sequence
+ * sends them to its peers so that all derive the same global top-k.  Replaces
+ * single_query_key_mean_topk, single_query_key_mean_topk_chunked and single_query_quest_topk
  * (bindings.cpp:205-247, block_selection.cu:127,339,450).
  */
-int ta100_select_decode(const void* q_grouped, const void* k_a, const void* k_b, void* out, int flat_kv_heads, int group,
-                        int nk, int cap_blocks, int head_dim, int k, int quest, int is_bf16, int sink, int local,
-                        void* stream);
+int ta100_select_decode(const void* q_grouped, const void* k_a, const void* k_b, void* out, void* out_scores,
+                        int flat_kv_heads, int group, int nk, int cap_blocks, int head_dim, int k, int quest, int is_bf16,
+                        int sink, int local, void* stream);
 
 /* Local windows: out [flat_heads, nq, k] (block_selection.cu:629) and
  * [flat_heads, k] (block_selection.cu:662); replace local_block_topk and

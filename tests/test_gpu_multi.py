@@ -41,7 +41,7 @@ def _worker(rank, world, port, results):
         ref = oracle.prefill_attention(q, k, v, sel, fmt="nvfp4", block=64, causal=True)
         err = (out.float().cpu() - ref.float()).abs()
         res["prefill"] = (tuple(out.shape) == (1, 8, 1024, 128)) and err.max().item() <= 2e-3 and err.mean().item() <= 2e-4
-        # ---- decode: 4096 cached tokens = 64 pages, 32 per rank; global Quest top-6 ----
+        # ---- decode: 4096 cached tokens = 64 pages, 32 per rank; global Quest top-6 + 1 sink + 2 recent pages ----
         torch.manual_seed(1)
         qd = torch.randn(2, 8, 1, 128).half()
         kd = torch.randn(2, 2, 4096, 128).half()
@@ -50,10 +50,23 @@ def _worker(rank, world, port, results):
         lo, hi = shard.page_begin * 64, shard.page_end * 64
         splits = 2
         out_d = tad.decode_kv_sharded(qd.to(dev), kd[:, :, lo:hi].contiguous().to(dev), vd[:, :, lo:hi].contiguous().to(dev),
-                                      shard=shard, total_pages=64, top_k=6, num_splits=splits)
+                                      shard=shard, total_pages=64, top_k=6, num_splits=splits, sink_blocks=1,
+                                      local_blocks=2)
         qg = qd.reshape(2, 2, 4, 128)
         kmin, kmax = oracle.block_stats(kd, 64, ("min", "max"))
-        sel_d = oracle.select_decode(qg, kmin, kmax, k=6, num_kv_blocks=64)
+        sel_d = oracle.select_decode(qg, kmin, kmax, k=6, num_kv_blocks=64, sink=1, local=2)
+        # the sharded selection is the single-GPU selection, exactly: same set, same top-k order
+        ext = ta._extension.get_extension()
+        _, la, lb = ext.block_stats(kd[:, :, lo:hi].contiguous().to(dev), 64, minmax=True)
+        mine = tad.select_pages_sharded(qg.to(dev), la, lb, shard=shard, total_pages=64, top_k=6, sink=1, local=2)
+        both = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(both, mine)
+        topk_cols = torch.stack([torch.where(t[:, 3:] >= 0, t[:, 3:] + tad.plan_page_shards(64, world)[r].page_begin, t[:, 3:])
+                                 for r, t in enumerate(both)]).amax(0).cpu()
+        res["selection_exact"] = bool(torch.equal(topk_cols, sel_d[:, 3:]))
+        forced = sorted(int(x) + tad.plan_page_shards(64, world)[r].page_begin
+                        for r, t in enumerate(both) for x in t[0, :3].tolist() if x >= 0)
+        res["forced_exact"] = forced == sorted(sel_d[0, :3].tolist())
         ref_d = oracle.decode_attention(qg, kd, vd, sel_d, fmt="nvfp4", splits=world * splits).reshape(2, 8, 1, 128)
         err = (out_d.float().cpu() - ref_d.float()).abs()
         res["decode"] = err.max().item() <= 2e-3 and err.mean().item() <= 2e-4
@@ -82,4 +95,5 @@ def test_two_gpu_prefill_and_decode():
     for rank in (0, 1):
         assert isinstance(results[rank], dict), results[rank]
         assert results[rank]["prefill"], results[rank]
+        assert results[rank]["selection_exact"] and results[rank]["forced_exact"], results[rank]
         assert results[rank]["decode"], results[rank]

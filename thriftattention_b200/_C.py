@@ -202,7 +202,10 @@ def quest_block_topk(q_mean, k_min, k_max, topk_count, causal=True, is_bf16=Fals
     return select_prefill_blocks(q_mean, k_min, k_max, topk_count, causal, is_bf16)
 
 
-def select_decode_blocks(q_grouped, k_a, k_b, topk_count, num_kv_blocks, is_bf16=False, sink=0, local=0, out=None):
+def select_decode_blocks(q_grouped, k_a, k_b, topk_count, num_kv_blocks, is_bf16=False, sink=0, local=0, out=None,
+                         return_scores=False):
+    """Decode selection; with ``return_scores`` also the fp32 score of every pick (forced blocks +FLT_MAX,
+    padding -FLT_MAX), bit-identical to what the kernel ranked by."""
     ts = [q_grouped, k_a] + ([k_b] if k_b is not None else [])
     _check(all(t.is_cuda for t in ts), "selection inputs must be CUDA tensors")
     _check(all(t.is_contiguous() for t in ts), "selection inputs must be contiguous")
@@ -221,14 +224,15 @@ def select_decode_blocks(q_grouped, k_a, k_b, topk_count, num_kv_blocks, is_bf16
     width = sink + local + topk_count
     if out is None:
         out = torch.empty(b * hkv, width, dtype=torch.int32, device=q_grouped.device)
+    scores = torch.empty(b * hkv, width, dtype=torch.float32, device=q_grouped.device) if return_scores else None
     if width == 0:
-        return out
+        return (out, scores) if return_scores else out
     with torch.cuda.device(q_grouped.device):
-        rc = _lib.load().ta100_select_decode(_ptr(q_grouped), _ptr(k_a), _ptr(k_b), _ptr(out), b * hkv, groups,
+        rc = _lib.load().ta100_select_decode(_ptr(q_grouped), _ptr(k_a), _ptr(k_b), _ptr(out), _ptr(scores), b * hkv, groups,
                                              num_kv_blocks, cap, d, topk_count, int(k_b is not None), int(is_bf16),
                                              sink, local, _stream(q_grouped))
     _lib.check(rc, "select_decode")
-    return out
+    return (out, scores) if return_scores else out
 
 
 def single_query_key_mean_topk(q_grouped, k_mean, topk_count, num_kv_blocks, is_bf16=False):

@@ -22,7 +22,7 @@ SIGNATURES = {
     "ta100_block_stats": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_vp]),
     "ta100_cache_append": (_c_int, [_c_vp] * 11 + [_c_ll] + [_c_int] * 9 + [_c_vp]),
     "ta100_select_prefill": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp] + [_c_int] * 11 + [_c_vp]),
-    "ta100_select_decode": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp] + [_c_int] * 10 + [_c_vp]),
+    "ta100_select_decode": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp] + [_c_int] * 10 + [_c_vp]),
     "ta100_local_block_topk": (_c_int, [_c_vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_vp]),
     "ta100_single_query_local_topk": (_c_int, [_c_vp, _c_ll, _c_int, _c_int, _c_vp]),
     "ta100_pack_topk_mask": (_c_int, [_c_vp, _c_vp, _c_ll, _c_int, _c_int, _c_int, _c_vp]),

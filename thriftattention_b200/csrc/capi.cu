@@ -9,7 +9,7 @@ int quantize_dispatch(const void*, void*, void*, long long, int, int, int, int, 
 int block_stats_dispatch(const void*, void*, void*, void*, long long, int, int, int, int, cudaStream_t);
 int select_prefill_dispatch(const void*, const void*, const void*, void*, int, int, int, int, int, int, int, int, int, int,
                             int, cudaStream_t);
-int select_decode_dispatch(const void*, const void*, const void*, void*, int, int, int, int, int, int, int, int, int, int,
+int select_decode_dispatch(const void*, const void*, const void*, void*, void*, int, int, int, int, int, int, int, int, int, int,
                            cudaStream_t);
 int local_prefill_dispatch(void*, long long, int, int, int, int, cudaStream_t);
 int local_decode_dispatch(void*, long long, int, int, cudaStream_t);
@@ -84,11 +84,11 @@ int ta100_select_prefill(const void* q_mean, const void* k_a, const void* k_b, v
                                    local, S(stream));
 }
 
-int ta100_select_decode(const void* q_grouped, const void* k_a, const void* k_b, void* out, int flat_kv_heads, int group,
-                        int nk, int cap_blocks, int head_dim, int k, int quest, int is_bf16, int sink, int local,
-                        void* stream) {
-    return select_decode_dispatch(q_grouped, k_a, k_b, out, flat_kv_heads, group, nk, cap_blocks, head_dim, k, quest,
-                                  is_bf16, sink, local, S(stream));
+int ta100_select_decode(const void* q_grouped, const void* k_a, const void* k_b, void* out, void* out_scores,
+                        int flat_kv_heads, int group, int nk, int cap_blocks, int head_dim, int k, int quest, int is_bf16,
+                        int sink, int local, void* stream) {
+    return select_decode_dispatch(q_grouped, k_a, k_b, out, out_scores, flat_kv_heads, group, nk, cap_blocks, head_dim, k,
+                                  quest, is_bf16, sink, local, S(stream));
 }
 
 int ta100_local_block_topk(void* out, long long flat_heads, int nq, int nk, int k, int causal, void* stream) {

@@ -307,7 +307,8 @@ template <int D, bool BF16, bool QUEST>
 __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const uint16_t* __restrict__ q,
                                                                         const uint16_t* __restrict__ ka,
                                                                         const uint16_t* __restrict__ kb,
-                                                                        int32_t* __restrict__ out, int group, int nk,
+                                                                        int32_t* __restrict__ out,
+                                                                        float* __restrict__ out_scores, int group, int nk,
                                                                         int cap_blocks, int k, int sink, int local) {
     using L = SeldSmem<D>;
     constexpr int VEC = D / 8;            // 16-byte chunks per statistics row
@@ -434,18 +435,29 @@ __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const ui
     int32_t* row = out + static_cast<long long>(h) * width;
     const int forced = n_sink + (nk - local_lo);
     const bool pad = (sink + local) > 0;
-    for (int i = tid; i < forced; i += SELD_THREADS) row[i] = i < n_sink ? i : local_lo + (i - n_sink);
+    // optional scores of the picks (forced blocks +FLT_MAX, padding -FLT_MAX): what a shard of a longer
+    // sequence sends to its peers so that all of them derive the same global top-k
+    float* srow = out_scores ? out_scores + static_cast<long long>(h) * width : nullptr;
+    for (int i = tid; i < forced; i += SELD_THREADS) {
+        row[i] = i < n_sink ? i : local_lo + (i - n_sink);
+        if (srow) srow[i] = FLT_MAX;
+    }
     for (int r = tid; r < k; r += SELD_THREADS) {
         int32_t id = -1;
+        float sc = -FLT_MAX;
         if (r < n_sort) {
             const unsigned long long key = keys[r];
             const bool real = key != ~0ull;
             const bool found = real && seld_key_score(key) > -FLT_MAX * 0.5f;
-            if (found || (!pad && real)) id = seld_key_page(key);
+            if (found || (!pad && real)) { id = seld_key_page(key); sc = seld_key_score(key); }
         }
         row[forced + r] = id;
+        if (srow) srow[forced + r] = sc;
     }
-    for (int i = forced + k + tid; i < width; i += SELD_THREADS) row[i] = -1;
+    for (int i = forced + k + tid; i < width; i += SELD_THREADS) {
+        row[i] = -1;
+        if (srow) srow[i] = -FLT_MAX;
+    }
 }
 
 int select_prefill_dispatch(const void* q_mean, const void* ka, const void* kb, void* out, int heads, int group, int nq,
@@ -479,7 +491,7 @@ int select_prefill_dispatch(const void* q_mean, const void* ka, const void* kb, 
     return static_cast<int>(cudaGetLastError());
 }
 
-int select_decode_dispatch(const void* q, const void* ka, const void* kb, void* out, int flat_heads, int group, int nk,
+int select_decode_dispatch(const void* q, const void* ka, const void* kb, void* out, void* out_scores, int flat_heads, int group, int nk,
                            int cap_blocks, int d, int k, int quest, int is_bf16, int sink, int local,
                            cudaStream_t stream) {
     if (!q || !ka || !out || (quest && !kb)) return TA100_ERR_NULL;
@@ -494,7 +506,7 @@ int select_decode_dispatch(const void* q, const void* ka, const void* kb, void* 
         cudaFuncSetAttribute(select_decode_kernel<DD, BFF, QQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
         select_decode_kernel<DD, BFF, QQ><<<flat_heads, SELD_THREADS, smem, stream>>>(                         \
             static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(ka), static_cast<const uint16_t*>(kb), \
-            static_cast<int32_t*>(out), group, nk, cap_blocks, k, sink, local);                                \
+            static_cast<int32_t*>(out), static_cast<float*>(out_scores), group, nk, cap_blocks, k, sink, local); \
     } while (0)
     if (d == 128) {
         if (is_bf16) { if (quest) TA100_SELD(128, true, true); else TA100_SELD(128, true, false); }

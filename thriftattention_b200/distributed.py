@@ -6,8 +6,9 @@ The reference has no distributed code; these are the two decompositions the path
   one KV head and its query heads never look at another group), so ranks take whole groups and
   the only collective is an optional ``all_gather`` of the outputs;
 * decode — the KV sequence is split into contiguous page ranges, one per rank.  Each rank scores
-  its own pages, the ranks exchange their local top-k candidates (a global top-k element is always
-  inside its shard's top-k), every rank derives the same global selection, runs the split-KV kernel
+  its own pages with the selection kernel (which also returns its fp32 scores), the ranks exchange their
+  local top-k candidates (a global top-k element is always inside its shard's top-k), every rank derives
+  the same global selection — bit-identical to the single-GPU one —, runs the split-KV kernel
   over its pages and contributes un-normalised partials ``(o, m, l)``; after an ``all_gather`` the
   log-sum-exp merge kernel produces the output on every rank.
 
@@ -157,22 +158,59 @@ def exchange_partials(part_o: torch.Tensor, part_ml: torch.Tensor, group=None):
     return _all_gather_stack(part_o, group), _all_gather_stack(part_ml, group)
 
 
-def quest_page_scores(q_grouped: torch.Tensor, k_min: torch.Tensor, k_max: torch.Tensor) -> torch.Tensor:
-    """Quest upper-bound score of every local page, max over the grouped query heads:
-    ``[B*Hkv, pages]`` fp32 (tensor code; used only to rank this shard's candidates for the exchange)."""
-    qf = q_grouped.float().unsqueeze(3)                                   # [B,Hkv,G,1,D]
-    bound = torch.where(qf >= 0, k_max.float().unsqueeze(2), k_min.float().unsqueeze(2))
-    s = (qf * bound).sum(-1).amax(dim=2)                                  # [B,Hkv,pages]
-    return s.reshape(-1, s.shape[-1])
+def select_pages_sharded(q_grouped, k_a, k_b, *, shard: PageShard, total_pages: int, top_k: int, sink: int = 0,
+                         local: int = 0, group=None) -> torch.Tensor:
+    """Global page selection when every rank holds the statistics of its own pages only.
+
+    ``k_a`` / ``k_b`` ``[B, Hkv, shard.num_pages(+), D]``: block means (``k_b is None``) or Quest minima / maxima
+    of the LOCAL pages.  Each rank runs the selection kernel on its pages — forcing the sink pages that fall at
+    the start of its range and the recent pages that fall at its end — and receives the kernel's own fp32
+    scores; the ranks exchange their top-k candidates and merge them with the kernel's tie-break, so the result
+    equals the single-GPU selection bit for bit.  Returns int32 ``[B*Hkv, sink + local + top_k]`` LOCAL page ids
+    of this rank's share (forced pages first), -1 elsewhere.
+    """
+    from thriftattention_b200._extension import get_extension
+
+    ext = get_extension()
+    n_local = shard.num_pages
+    rows = q_grouped.shape[0] * q_grouped.shape[1]
+    dev = q_grouped.device
+    n_sink = min(sink, total_pages)
+    local_lo = max(total_pages - local, n_sink)
+    my_sink = max(0, min(n_sink, shard.page_end) - shard.page_begin)             # forced at the start of my range
+    my_local = max(0, shard.page_end - max(local_lo, shard.page_begin))          # forced at its end
+    k_glob = min(top_k, max(total_pages - n_sink - (total_pages - local_lo), 0))
+    cand = min(k_glob, max(n_local - my_sink - my_local, 0))
+    sel, scores = ext.select_decode_blocks(q_grouped, k_a, k_b, cand, n_local, q_grouped.dtype == torch.bfloat16,
+                                           sink=my_sink, local=my_local, return_scores=True)
+    forced = sel[:, : my_sink + my_local]
+    c_pages = sel[:, my_sink + my_local: my_sink + my_local + cand]
+    c_scores = scores[:, my_sink + my_local: my_sink + my_local + cand]
+    # fixed-width candidate lists (k_glob per rank) for the exchange
+    pad_p = torch.full((rows, k_glob), -1, dtype=torch.int32, device=dev)
+    pad_s = torch.full((rows, k_glob), float("-inf"), dtype=torch.float32, device=dev)
+    if cand:
+        pad_p[:, :cand] = torch.where(c_pages >= 0, c_pages + shard.page_begin, c_pages)
+        pad_s[:, :cand] = torch.where(c_pages >= 0, c_scores, torch.full_like(c_scores, float("-inf")))
+    all_s, all_p = exchange_candidates(pad_s, pad_p, group)
+    global_sel = merge_topk_candidates(all_s, all_p, k_glob) if k_glob else pad_p
+    mine = (global_sel >= shard.page_begin) & (global_sel < shard.page_end)
+    local_topk = torch.where(mine, global_sel - shard.page_begin, torch.full_like(global_sel, -1))
+    out = torch.full((rows, sink + local + top_k), -1, dtype=torch.int32, device=dev)
+    out[:, : my_sink + my_local] = forced
+    out[:, sink + local: sink + local + k_glob] = local_topk
+    return out.contiguous()
 
 
 def decode_kv_sharded(q, k_local, v_local, *, shard: PageShard, total_pages: int, top_k: int, quant_format="nvfp4",
-                      num_splits: int = 0, group=None):
+                      num_splits: int = 0, group=None, selection: str = "quest", sink_blocks: int = 0,
+                      local_blocks: int = 0):
     """One decode step with the KV sequence sharded over ranks.
 
     ``q`` ``[B, Hq, 1, D]`` replicated; ``k_local`` / ``v_local`` ``[B, Hkv, shard.num_pages*64, D]`` are this
-    rank's slice of the cache.  Quest selection of ``top_k`` pages over the WHOLE sequence, mixed attention
-    over the local pages, LSE merge across ranks.  Returns ``[B, Hq, 1, D]`` on every rank.
+    rank's slice of the cache.  Selection of ``top_k`` pages (+ forced sink / recent pages) over the WHOLE
+    sequence, mixed attention over the local pages, LSE merge across ranks.  Returns ``[B, Hq, 1, D]`` on
+    every rank, equal to the single-GPU result up to the split-dependent fp32 rounding of the merge.
     """
     from thriftattention_b200._extension import get_extension
 
@@ -182,25 +220,23 @@ def decode_kv_sharded(q, k_local, v_local, *, shard: PageShard, total_pages: int
     b, hq, _, d = q.shape
     hkv = k_local.shape[1]
     q_grouped = q.reshape(b, hkv, hq // hkv, d).contiguous()
-    n_local = shard.num_pages
-    # 1. local page statistics and scores, 2. candidate exchange, 3. identical global selection everywhere
-    _, k_min, k_max = ext.block_stats(k_local.contiguous(), 64, minmax=True)
-    scores = quest_page_scores(q_grouped, k_min, k_max)
-    c = min(top_k, n_local)
-    top = torch.topk(scores, c, dim=1)
-    cand_pages = (top.indices + shard.page_begin).to(torch.int32)
-    all_s, all_p = exchange_candidates(top.values.contiguous(), cand_pages.contiguous(), group)
-    global_sel = merge_topk_candidates(all_s, all_p, min(top_k, total_pages))
-    mine = (global_sel >= shard.page_begin) & (global_sel < shard.page_end)
-    local_sel = torch.where(mine, global_sel - shard.page_begin, torch.full_like(global_sel, -1)).contiguous()
+    k_local, v_local = k_local.contiguous(), v_local.contiguous()
+    # 1. local page statistics, 2. kernel-scored candidates + exchange, 3. identical global selection everywhere
+    if selection == "quest":
+        _, k_a, k_b = ext.block_stats(k_local, 64, minmax=True)
+    else:
+        k_a, _, _ = ext.block_stats(k_local, 64, mean=True)
+        k_b = None
+    local_sel = select_pages_sharded(q_grouped, k_a, k_b, shard=shard, total_pages=total_pages, top_k=top_k,
+                                     sink=sink_blocks, local=local_blocks, group=group)
     # 4. local split-KV attention -> partials, 5. exchange + merge
     quant = getattr(ext, f"{quant_format}_quantize")
     quant_t = getattr(ext, f"{quant_format}_quantize_transposed")
     q4, qs = quant(q_grouped, is_bf16)
-    k4, ks = quant(k_local.contiguous(), is_bf16)
-    v4, vs = quant_t(v_local.contiguous(), is_bf16)
-    _, part_o, part_ml = ext.decode_attention(q_grouped, k_local.contiguous(), v_local.contiguous(), local_sel, q4, k4,
-                                              v4, qs, ks, vs, is_mx=is_mx, is_bf16=is_bf16, num_splits=num_splits,
+    k4, ks = quant(k_local, is_bf16)
+    v4, vs = quant_t(v_local, is_bf16)
+    _, part_o, part_ml = ext.decode_attention(q_grouped, k_local, v_local, local_sel, q4, k4, v4, qs, ks, vs,
+                                              is_mx=is_mx, is_bf16=is_bf16, num_splits=num_splits,
                                               return_partials=True, allow_padded_selection=True)
     all_o, all_ml = exchange_partials(part_o, part_ml, group)
     out = ext.merge_decode_partials(all_o.contiguous(), all_ml.contiguous(), is_mx=is_mx, is_bf16=is_bf16)
