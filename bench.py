@@ -242,6 +242,60 @@ def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_g
             "launches_per_step": 4 if world == 1 else 6}
 
 
+# ------------------------------------------------------------------------- small cases for profiler captures
+def run_small_case(kind: str) -> None:
+    """Three back-to-back launches of one hot kernel on a case of a few hundred MB (larger than L2): what a
+    full-set ncu capture is taken on.  Prints the algorithmic work of one launch."""
+    from thriftattention_b200 import _C
+    from thriftattention_b200.selection import resolve_top_k
+
+    device = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    if kind == "prefill":
+        hq, hkv, seq = 16, 4, 8192
+        q, k, v = make_inputs(hq, hkv, seq, device, torch.float16)
+        top_k = resolve_top_k(seq // BLOCK, causal=True, fraction=FRACTION)
+        q_mean, _, _ = _C.block_stats(q, BLOCK, mean=True)
+        _, k_min, k_max = _C.block_stats(k, BLOCK, minmax=True)
+        sel = _C.quest_block_topk(q_mean, k_min, k_max, top_k, True, False)
+        q4, qs = _C.nvfp4_quantize(q)
+        k4, ks = _C.nvfp4_quantize_permuted(k)
+        v4, vs = _C.nvfp4_quantize_transposed(v)
+        for _ in range(3):
+            _C.prefill_attention(q, k, v, sel, q4, k4, v4, qs, ks, vs, causal=True, is_mx=False, is_bf16=False,
+                                 block_size=BLOCK, k_permuted=True, check_status=True)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": "prefill 1x16q/4kv x8192 x128 fp16 NVFP4 Quest top-10%", "flops_per_launch":
+                          algorithmic_flops(hq, seq, D, BLOCK)}))
+        return
+    batch, seq = 8, 32768
+    pages = seq // 64
+    pool = batch * pages
+    u8 = dict(dtype=torch.uint8, device=device)
+    k4 = torch.randint(0, 256, (pool, HKV, 64, D // 2), **u8)
+    v4 = torch.randint(0, 256, (pool, HKV, D, 32), **u8)
+    ks = torch.randint(40, 60, (pool, HKV, 64, D // 16), **u8)
+    vs = torch.randint(40, 60, (pool, HKV, D, 4), **u8)
+    k_hi = torch.empty(pool, HKV, 64, D, dtype=torch.float16, device=device).normal_()
+    v_hi = torch.empty(pool, HKV, 64, D, dtype=torch.float16, device=device).normal_()
+    k_min = torch.randn(batch, HKV, pages, D, device=device).half()
+    k_max = k_min + 1
+    table = torch.randperm(pool, device=device).to(torch.int32).reshape(batch, pages)
+    q = torch.randn(batch, HKV, DEC_GROUP, D, device=device).half()
+    top_k = max(1, round(DEC_FRACTION * pages))
+    for _ in range(3):
+        q4, qs = _C.nvfp4_quantize(q)
+        sel = _C.select_decode_blocks(q, k_min, k_max, top_k, pages, False, sink=DEC_SINK, local=DEC_LOCAL)
+        _C.decode_attention(q, k_hi, v_hi, sel, q4, k4, v4, qs, ks, vs, is_mx=False, is_bf16=False, kv_len=seq,
+                            page_table=table, allow_padded_selection=True)
+    torch.cuda.synchronize()
+    _C.decode_status()
+    n16 = top_k + DEC_SINK + DEC_LOCAL
+    print(json.dumps({"case": "paged decode 8 seq x 32768 tokens, 32q/8kv x128, NVFP4 + fp16 shadow, 71 of 512 pages in 16 bits",
+                      "attention_bytes_per_launch": batch * HKV * ((pages - n16) * 9216 + n16 * 32768),
+                      "selection_bytes_per_launch": batch * HKV * pages * 512}))
+
+
 def run_ours(args) -> dict:
     import torch.distributed as dist
 
@@ -402,7 +456,12 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--small", choices=["prefill", "decode"], default=None,
+                    help="run a small case of one kernel three times (for profiler captures) and exit")
     args = ap.parse_args()
+    if args.small:
+        run_small_case(args.small)
+        return
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     if result:
         print(json.dumps(result), flush=True)
