@@ -177,14 +177,14 @@ def test_local_windows_on_gpu(cuda_device):
 
 
 # ------------------------------------------------------------------------------------ prefill attention
-def _prefill_case(dev, dtype, fmt, block, S, hq, hkv, frac, causal, kperm, seed=0, outlier=False, sq=None):
+def _prefill_case(dev, dtype, fmt, block, S, hq, hkv, frac, causal, kperm, seed=0, outlier=False, sq=None, d=128):
     torch.manual_seed(seed)
     sq = S if sq is None else sq
-    q = torch.randn(1, hq, sq, 128)
-    k = torch.randn(1, hkv, S, 128)
-    v = torch.randn(1, hkv, S, 128)
+    q = torch.randn(1, hq, sq, d)
+    k = torch.randn(1, hkv, S, d)
+    v = torch.randn(1, hkv, S, d)
     if outlier:
-        k[:, :, :, torch.randperm(128)[:4]] *= 10
+        k[:, :, :, torch.randperm(d)[:4]] *= 10
     q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
     bf, mx = dtype == torch.bfloat16, fmt == "mxfp4"
     ext = _ext()
@@ -235,6 +235,19 @@ def test_prefill_attention_matches_oracle(cuda_device, dtype, fmt, block, S, hq,
                                                               v.float().repeat_interleave(g, 1), is_causal=causal)
         cos = torch.nn.functional.cosine_similarity(out.float().cpu().flatten(), sd.flatten(), dim=0)
         assert float(cos) > 0.95
+
+
+@pytest.mark.parametrize("dtype,fmt,block,S,hq,hkv,frac,causal,kperm", [
+    (torch.float16, "nvfp4", 64, 1024, 2, 1, 0.1, True, True),
+    (torch.float16, "nvfp4", 64, 1024, 2, 1, 0.0, True, False),
+    (torch.bfloat16, "nvfp4", 128, 1024, 4, 2, 0.25, True, False),
+    (torch.float16, "mxfp4", 64, 1024, 4, 2, 0.1, True, True),
+    (torch.bfloat16, "mxfp4", 64, 512, 2, 2, 0.5, False, False),
+    (torch.float16, "nvfp4", 64, 4096, 4, 1, 0.1, True, True),
+])
+def test_prefill_attention_head_dim_64(cuda_device, dtype, fmt, block, S, hq, hkv, frac, causal, kperm):
+    """The reference's own CUDA tests run at head_dim 64 (tests/test_cuda_bf16_correctness.py:42-122)."""
+    _prefill_case(cuda_device, dtype, fmt, block, S, hq, hkv, frac, causal, kperm, d=64)
 
 
 def test_prefill_noncausal_rectangular(cuda_device):
@@ -319,25 +332,31 @@ def test_prefill_long_context_slice_matches_oracle(cuda_device):
 
 # ------------------------------------------------------------------------------------ decode attention
 DECODE_CASES = [
-    (torch.float16, "nvfp4", 1, 1, 4, 256, 0, 1),
-    (torch.float16, "nvfp4", 1, 1, 4, 256, 1, 1),
-    (torch.float16, "nvfp4", 2, 2, 8, 4096, 6, 5),
-    (torch.float16, "nvfp4", 1, 2, 1, 1024, 2, 3),
-    (torch.bfloat16, "nvfp4", 2, 2, 4, 1024, 3, 2),
-    (torch.float16, "mxfp4", 2, 2, 4, 1024, 3, 2),
-    (torch.bfloat16, "mxfp4", 2, 2, 4, 2048, 5, 4),
-    (torch.float16, "nvfp4", 2, 8, 4, 8192, 13, 7),
+    (torch.float16, "nvfp4", 1, 1, 4, 256, 0, 1, 128),
+    (torch.float16, "nvfp4", 1, 1, 4, 256, 1, 1, 128),
+    (torch.float16, "nvfp4", 2, 2, 8, 4096, 6, 5, 128),
+    (torch.float16, "nvfp4", 1, 2, 1, 1024, 2, 3, 128),
+    (torch.bfloat16, "nvfp4", 2, 2, 4, 1024, 3, 2, 128),
+    (torch.float16, "mxfp4", 2, 2, 4, 1024, 3, 2, 128),
+    (torch.bfloat16, "mxfp4", 2, 2, 4, 2048, 5, 4, 128),
+    (torch.float16, "nvfp4", 2, 8, 4, 8192, 13, 7, 128),
+    (torch.float16, "nvfp4", 1, 2, 16, 2048, 4, 2, 128),       # the largest query group
+    (torch.bfloat16, "mxfp4", 1, 1, 12, 1024, 16, 1, 128),     # every page selected: 16-bit pages only
+    (torch.float16, "nvfp4", 2, 2, 4, 1024, 3, 2, 64),         # head_dim 64
+    (torch.bfloat16, "nvfp4", 1, 2, 8, 2048, 0, 3, 64),
+    (torch.float16, "mxfp4", 2, 1, 4, 1024, 2, 2, 64),
+    (torch.bfloat16, "mxfp4", 1, 2, 2, 512, 8, 1, 64),
 ]
 
 
-@pytest.mark.parametrize("dtype,fmt,B,hkv,G,S,top_k,splits", DECODE_CASES)
-def test_decode_attention_matches_oracle(cuda_device, dtype, fmt, B, hkv, G, S, top_k, splits):
+@pytest.mark.parametrize("dtype,fmt,B,hkv,G,S,top_k,splits,d", DECODE_CASES)
+def test_decode_attention_matches_oracle(cuda_device, dtype, fmt, B, hkv, G, S, top_k, splits, d):
     torch.manual_seed(6)
     ext = _ext()
     bf, mx = dtype == torch.bfloat16, fmt == "mxfp4"
-    q = torch.randn(B, hkv, G, 128).to(dtype)
-    k = torch.randn(B, hkv, S, 128).to(dtype)
-    v = torch.randn(B, hkv, S, 128).to(dtype)
+    q = torch.randn(B, hkv, G, d).to(dtype)
+    k = torch.randn(B, hkv, S, d).to(dtype)
+    v = torch.randn(B, hkv, S, d).to(dtype)
     sel = None
     if top_k:
         kmin, kmax = oracle.block_stats(k, 64, ("min", "max"))

@@ -195,12 +195,14 @@ __device__ void build_page_list(const DecodeParams& p, int h, int b, int kvh, in
     n_total = n;
 }
 
-template <bool MX, bool BF16>
+template <int D, bool MX, bool BF16>
 __global__ void __launch_bounds__(DEC_THREADS, 2)
 decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, const __grid_constant__ CUtensorMap mapV4,
               const __grid_constant__ CUtensorMap mapK16, const __grid_constant__ CUtensorMap mapV16) {
-    constexpr int D = 128;
     using L = DecSmem<D>;
+    constexpr uint32_t ROW4 = D / 2;                                   // bytes per FP4 row of Q / K
+    constexpr uint32_t SWZ_QK = (ROW4 == 64) ? SWZ_64B : SWZ_32B;
+    constexpr uint32_t SBO_QK = 8 * ROW4;
     constexpr int GRP = MX ? 32 : 16;
     constexpr int QK_ATOMS = MX ? 1 : D / 64;
     constexpr int KBLK = D / 64;
@@ -274,18 +276,25 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
         if (lane == 0) mbar_arrive(smem_u32(&bars.list_full));
         // ---- FP4 pages: TMA for the codes; the lanes fetch the page's block scales two pages ahead and store
         //      them in atom order (word m0 * 4 + m1 holds the scales of row / channel 32 * m1 + m0) ----
+        // K scales: D / GRP bytes per token row = KROW_WORDS 32-bit words (one 16-bit word for MXFP4 at D = 64);
+        // V scales: PAGE / GRP bytes per channel row and page (4 NVFP4, 2 MXFP4)
         constexpr int KS_PAGE = PAGE * (D / GRP), VS_PAGE = D * (PAGE / GRP);
-        constexpr int KW = MX ? 2 : 4;   // K scale words per lane and page
+        constexpr int KROW_BYTES = D / GRP;
+        constexpr int KROW_WORDS = KROW_BYTES >= 4 ? KROW_BYTES / 4 : 1;
+        constexpr int KW = PAGE * KROW_WORDS / 32;   // K scale words per lane and page (4 or 2)
+        constexpr int VW = D / 32;                   // V scale words per lane and page (4 or 2)
         auto load_sf = [&](int i, uint32_t (&kw)[4], uint32_t (&vw)[4]) {
             if (i >= n_fp4) return;
             const uint32_t key = list[i];
-            const uint32_t* kp = reinterpret_cast<const uint32_t*>(
-                paged ? p.ks + static_cast<long long>(key) * KS_PAGE
-                      : p.ks + (static_cast<long long>(h) * p.cap_pages + key) * KS_PAGE);
+            const uint8_t* kp = paged ? p.ks + static_cast<long long>(key) * KS_PAGE
+                                      : p.ks + (static_cast<long long>(h) * p.cap_pages + key) * KS_PAGE;
 #pragma unroll
-            for (int j = 0; j < KW; ++j) kw[j] = __ldg(kp + lane + 32 * j);
+            for (int j = 0; j < KW; ++j) {
+                if constexpr (KROW_BYTES >= 4) kw[j] = __ldg(reinterpret_cast<const uint32_t*>(kp) + lane + 32 * j);
+                else kw[j] = __ldg(reinterpret_cast<const uint16_t*>(kp) + lane + 32 * j);
+            }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < VW; ++j) {
                 const int ch = lane + 32 * j;
                 if constexpr (MX) {
                     const uint8_t* vp = paged ? p.vs + static_cast<long long>(key) * VS_PAGE + ch * 2
@@ -313,12 +322,12 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
             uint8_t* sl = smem + L::SLOTS + slot * DEC_SLOT4_BYTES;
 #pragma unroll
             for (int j = 0; j < KW; ++j) {
-                const int w = lane + 32 * j;
-                if constexpr (MX) reinterpret_cast<uint32_t*>(sl + L::KSF)[(w & 31) * 4 + (w >> 5)] = kw[j];
-                else reinterpret_cast<uint32_t*>(sl + L::KSF + (w & 1) * 512)[((w >> 1) & 31) * 4 + (w >> 6)] = kw[j];
+                const int w = lane + 32 * j;                     // word w: token w / KROW_WORDS, atom w % KROW_WORDS
+                const int tok = w / KROW_WORDS, atom = w % KROW_WORDS;
+                reinterpret_cast<uint32_t*>(sl + L::KSF + atom * 512)[(tok & 31) * 4 + (tok >> 5)] = kw[j];
             }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) reinterpret_cast<uint32_t*>(sl + L::VSF)[lane * 4 + j] = vw[j];
+            for (int j = 0; j < VW; ++j) reinterpret_cast<uint32_t*>(sl + L::VSF)[lane * 4 + j] = vw[j];
             fence_proxy_async_smem();
             mbar_arrive(smem_u32(&bars.f_full[slot]));
             return true;
@@ -415,8 +424,8 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
             if (i < n4) {
                 const uint32_t sa = sbase + L::SLOTS + (i % DEC_NS4) * DEC_SLOT4_BYTES;
                 for (int kb = 0; kb < KBLK; ++kb) {
-                    const uint64_t ad = make_smem_desc(sbase + L::Q4 + kb * 32, 16, 512, SWZ_64B);
-                    const uint64_t bd = make_smem_desc(sa + L::K4 + kb * 32, 16, 512, SWZ_64B);
+                    const uint64_t ad = make_smem_desc(sbase + L::Q4 + kb * 32, 16, SBO_QK, SWZ_QK);
+                    const uint64_t bd = make_smem_desc(sa + L::K4 + kb * 32, 16, SBO_QK, SWZ_QK);
                     if constexpr (MX)
                         mma_mxfp4_elect(d_t, ad, bd, make_idesc_fp4(128, PAGE, 1, kb * 2, kb * 2), tm + DTM_SFA_Q, sfb, kb > 0);
                     else
@@ -503,13 +512,23 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
         if (active) {
             const long long qrow = static_cast<long long>(h) * G + g;
             const uint4* q4row = reinterpret_cast<const uint4*>(p.q4 + qrow * (D / 2));
+            if constexpr (D == 128) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c)   // 64-byte row, 64-byte swizzle
-                *reinterpret_cast<uint4*>(smem + L::Q4 + row * 64 + ((c ^ ((row >> 1) & 3)) * 16)) = __ldg(q4row + c);
-            const uint32_t* qsr = reinterpret_cast<const uint32_t*>(p.qs + qrow * (D / GRP));
+                for (int c = 0; c < 4; ++c)   // 64-byte row, 64-byte swizzle
+                    *reinterpret_cast<uint4*>(smem + L::Q4 + row * 64 + ((c ^ ((row >> 1) & 3)) * 16)) = __ldg(q4row + c);
+            } else {
 #pragma unroll
-            for (int a = 0; a < QK_ATOMS; ++a)
-                reinterpret_cast<uint32_t*>(smem + L::QSF + a * 512)[lane * 4 + sub] = __ldg(qsr + a);
+                for (int c = 0; c < 2; ++c)   // 32-byte row, 32-byte swizzle
+                    *reinterpret_cast<uint4*>(smem + L::Q4 + row * 32 + ((c ^ ((row >> 2) & 1)) * 16)) = __ldg(q4row + c);
+            }
+            const uint8_t* qsr = p.qs + qrow * (D / GRP);
+#pragma unroll
+            for (int a = 0; a < QK_ATOMS; ++a) {
+                uint32_t word;
+                if constexpr (D / GRP >= 4) word = __ldg(reinterpret_cast<const uint32_t*>(qsr) + a);
+                else word = __ldg(reinterpret_cast<const uint16_t*>(qsr));
+                reinterpret_cast<uint32_t*>(smem + L::QSF + a * 512)[lane * 4 + sub] = word;
+            }
             if (has_sel) {
                 const uint4* qh = reinterpret_cast<const uint4*>(p.q_hi + qrow * D);
 #pragma unroll
@@ -706,7 +725,7 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
         if (ok) {
             const float* stage = reinterpret_cast<const float*>(smem + L::SLOTS);
             const long long pbase = (static_cast<long long>(h) * p.splits + split) * G;
-            for (int gg = 0; gg < G; ++gg) {
+            for (int gg = 0; gg < G && row < D; ++gg) {
                 float o = stage[(0 * DEC_MAX_GROUP + gg) * D + row];
                 o += stage[(1 * DEC_MAX_GROUP + gg) * D + row];
                 o += stage[(2 * DEC_MAX_GROUP + gg) * D + row];
@@ -823,7 +842,7 @@ int decode_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const 
     if (!q4 || !k4 || !v4 || !qs || !ks || !vs || !part_o || !part_ml) return TA100_ERR_NULL;
     if (write_out && !out) return TA100_ERR_NULL;
     if (width > 0 && (!q_hi || !k_hi || !v_hi || !sel)) return TA100_ERR_NULL;
-    if (d != 128) return TA100_ERR_UNSUPPORTED;
+    if (d != 128 && d != 64) return TA100_ERR_UNSUPPORTED;
     if (G < 1 || G > DEC_MAX_GROUP) return TA100_ERR_UNSUPPORTED;
     if (batch <= 0 || hkv <= 0 || kv_len <= 0 || kv_len % PAGE != 0 || kv_cap < kv_len) return TA100_ERR_SHAPE;
     if (!page_table && kv_cap % PAGE != 0) return TA100_ERR_SHAPE;
@@ -854,7 +873,8 @@ int decode_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const 
             uint64_t dims[3] = {d2, paged ? uint64_t(PAGE) : uint64_t(kv_cap), paged ? pool_slabs : uint64_t(heads)};
             uint64_t str[2] = {d2, (paged ? uint64_t(PAGE) : uint64_t(kv_cap)) * d2};
             uint32_t box[3] = {static_cast<uint32_t>(d2), PAGE, 1};
-            rc |= make_tensor_map(&maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, k4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_64B);
+            rc |= make_tensor_map(&maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, k4, dims, str, box,
+                                  d == 128 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
         }
         {   // V codes, transposed: d rows of (tokens / 2) bytes
             const uint64_t rowb = paged ? uint64_t(PAGE / 2) : uint64_t(P / 2);
@@ -889,15 +909,20 @@ int decode_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const 
     p.c2 = static_cast<float>((1.0 / sqrt(static_cast<double>(d))) * 1.4426950408889634);
     p.budget = 1000000000LL;
     const dim3 grid(splits, heads);
-    const int smem = DecSmem<128>::TOTAL;
-#define TA100_DEC(MXX, BFF)                                                                               \
-    do {                                                                                                  \
-        cudaFuncSetAttribute(decode_kernel<MXX, BFF>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
-        cudaFuncSetAttribute(decode_kernel<MXX, BFF>, cudaFuncAttributePreferredSharedMemoryCarveout, 100); \
-        decode_kernel<MXX, BFF><<<grid, DEC_THREADS, smem, stream>>>(p, maps[0], maps[1], maps[2], maps[3]); \
+#define TA100_DEC(DD, MXX, BFF)                                                                               \
+    do {                                                                                                      \
+        const int smem = DecSmem<DD>::TOTAL;                                                                  \
+        cudaFuncSetAttribute(decode_kernel<DD, MXX, BFF>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+        cudaFuncSetAttribute(decode_kernel<DD, MXX, BFF>, cudaFuncAttributePreferredSharedMemoryCarveout, 100); \
+        decode_kernel<DD, MXX, BFF><<<grid, DEC_THREADS, smem, stream>>>(p, maps[0], maps[1], maps[2], maps[3]); \
     } while (0)
-    if (is_mx) { if (is_bf16) TA100_DEC(true, true); else TA100_DEC(true, false); }
-    else { if (is_bf16) TA100_DEC(false, true); else TA100_DEC(false, false); }
+    if (d == 128) {
+        if (is_mx) { if (is_bf16) TA100_DEC(128, true, true); else TA100_DEC(128, true, false); }
+        else { if (is_bf16) TA100_DEC(128, false, true); else TA100_DEC(128, false, false); }
+    } else {
+        if (is_mx) { if (is_bf16) TA100_DEC(64, true, true); else TA100_DEC(64, true, false); }
+        else { if (is_bf16) TA100_DEC(64, false, true); else TA100_DEC(64, false, false); }
+    }
 #undef TA100_DEC
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return static_cast<int>(e);

@@ -821,7 +821,7 @@ int prefill_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const
                      int max_ctas, cudaStream_t stream) {
     if (!q4 || !k4 || !v4t || !qs || !ks || !vst || !out || !workspace) return TA100_ERR_NULL;
     if (width > 0 && (!q_hi || !k_hi || !v_hi || !sel)) return TA100_ERR_NULL;
-    if (d != 128) return TA100_ERR_UNSUPPORTED;
+    if (d != 128 && d != 64) return TA100_ERR_UNSUPPORTED;
     if (block != 64 && block != 128) return TA100_ERR_UNSUPPORTED;
     if (batch <= 0 || hq <= 0 || hkv <= 0 || hq % hkv != 0 || sq <= 0 || skv <= 0) return TA100_ERR_SHAPE;
     if (sq % 64 != 0 || skv % 64 != 0 || kv_cap < skv) return TA100_ERR_SHAPE;
@@ -917,13 +917,18 @@ int prefill_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const
     int grid = p.n_items < 2 * sms ? p.n_items : 2 * sms;
     if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
 
-#define TA100_PF(MXX, BFF, CC, KP) launch_prefill_t<128, MXX, BFF, CC, KP>(p, maps, grid, stream)
-#define TA100_PF2(MXX, BFF)                                                                    \
-    (causal ? (k_permuted ? TA100_PF(MXX, BFF, true, true) : TA100_PF(MXX, BFF, true, false))  \
-            : (k_permuted ? TA100_PF(MXX, BFF, false, true) : TA100_PF(MXX, BFF, false, false)))
+#define TA100_PF(DD, MXX, BFF, CC, KP) launch_prefill_t<DD, MXX, BFF, CC, KP>(p, maps, grid, stream)
+#define TA100_PF2(DD, MXX, BFF)                                                                        \
+    (causal ? (k_permuted ? TA100_PF(DD, MXX, BFF, true, true) : TA100_PF(DD, MXX, BFF, true, false))  \
+            : (k_permuted ? TA100_PF(DD, MXX, BFF, false, true) : TA100_PF(DD, MXX, BFF, false, false)))
     int rc;
-    if (is_mx) rc = is_bf16 ? TA100_PF2(true, true) : TA100_PF2(true, false);
-    else rc = is_bf16 ? TA100_PF2(false, true) : TA100_PF2(false, false);
+    if (d == 128) {
+        if (is_mx) rc = is_bf16 ? TA100_PF2(128, true, true) : TA100_PF2(128, true, false);
+        else rc = is_bf16 ? TA100_PF2(128, false, true) : TA100_PF2(128, false, false);
+    } else {
+        if (is_mx) rc = is_bf16 ? TA100_PF2(64, true, true) : TA100_PF2(64, true, false);
+        else rc = is_bf16 ? TA100_PF2(64, false, true) : TA100_PF2(64, false, false);
+    }
 #undef TA100_PF2
 #undef TA100_PF
     return rc;
