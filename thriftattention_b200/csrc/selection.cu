@@ -290,6 +290,14 @@ __device__ __forceinline__ int seld_key_page(unsigned long long key) {
     return static_cast<int>((__brev(tie >> 16) >> 27) | ((tie & 0xFFFFu) << 5));
 }
 
+#ifdef TA100_PROFILE_SOFTMAX
+__device__ long long g_sel_prof[16];
+#define SELD_PROF(i) if (blockIdx.x == 0 && threadIdx.x == 0) g_sel_prof[i] = clock64();
+#else
+#define SELD_PROF(i)
+#endif
+constexpr int SELD_CAND_CAP = 512;   // exact re-scoring handles at most this many candidates
+
 template <int D>
 struct SeldSmem {
     static constexpr int ROW = D * 2 + 16;                       // padded statistics row (bytes)
@@ -297,12 +305,42 @@ struct SeldSmem {
     static constexpr int QROW = D + 4;                            // floats per query row
     static constexpr int MROW = D / 2 + 4;                        // mask words per query row
     static constexpr int KEYS = 0;                                // 2048 x 8 B
-    static constexpr int QF = KEYS + 2048 * 8;
+    static constexpr int APPROX = KEYS + 2048 * 8;                // 2048 approximate scores
+    static constexpr int CAND = APPROX + 2048 * 4;                // candidate page ids
+    static constexpr int MISC = CAND + SELD_CAND_CAP * 4;         // counters
+    static constexpr int QF = MISC + 64;
     static constexpr int QM = QF + SELD_MAX_GROUP * QROW * 4;
     static constexpr int TILES = QM + SELD_MAX_GROUP * MROW * 4;  // [2 stages][A | B]
     static constexpr int total(bool quest) { return TILES + 2 * (quest ? 2 : 1) * TILE_BYTES; }
 };
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_row))));
+}
+template <bool BF16>
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if constexpr (BF16)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    else
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Decode selection.  The exact score (see above) costs ~400 instructions per (page, head), far more than the
+// 512 bytes of statistics it reads are worth, so the kernel ranks in two passes whenever it pays off:
+//   pass 1  approximate scores of ALL pages with mma.sync (q split into its non-negative and negative parts,
+//           so the Quest bound is a plain GEMM against [max | min]); every approximate score is within
+//           delta = 2^-16 * max_g |q_g|_1 * max|statistics| of the exact one (exact products, fp32 sums);
+//   pass 2  exact scores only for the pages that can still reach the top k: those whose approximate score
+//           plus delta is at least the k-th largest (approximate score minus delta).
+// Pages left out are provably below the exact k-th score, so the result is the one of scoring everything
+// exactly.  With more than SELD_CAND_CAP candidates, few pages or a large query group, every page is scored
+// exactly in one pass.
 template <int D, bool BF16, bool QUEST>
 __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const uint16_t* __restrict__ q,
                                                                         const uint16_t* __restrict__ ka,
@@ -315,24 +353,27 @@ __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const ui
     constexpr int NARR = QUEST ? 2 : 1;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     unsigned long long* keys = reinterpret_cast<unsigned long long*>(smem_raw + L::KEYS);
+    float* approx = reinterpret_cast<float*>(smem_raw + L::APPROX);
+    int* cand = reinterpret_cast<int*>(smem_raw + L::CAND);
+    int* misc = reinterpret_cast<int*>(smem_raw + L::MISC);   // [0] candidates, [1] max |statistic| bits, [2] max |q|_1 bits
     float* qf = reinterpret_cast<float*>(smem_raw + L::QF);
     uint32_t* qm = reinterpret_cast<uint32_t*>(smem_raw + L::QM);
     uint8_t* tiles = smem_raw + L::TILES;
 
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.x;
     const int n_sink = min(sink, nk);
     const int local_lo = max(nk - local, n_sink);
     const int width = sink + local + k;
-    int n_sort = 2;
-    while (n_sort < nk) n_sort <<= 1;
+    const int forced = n_sink + (nk - local_lo);
+    const bool two_pass = group <= 8 && nk >= 256 && k > 0 && k + forced < nk;
 
     // query group: fp32 values and, for Quest, one 16-bit mask per channel (all ones where q >= 0)
     for (int i = tid; i < group * D; i += SELD_THREADS) {
         const int g = i / D, c = i - g * D;
         qf[g * L::QROW + c] = In16<BF16>::to_f(q[(static_cast<long long>(h) * group + g) * D + c]);
     }
-    for (int i = tid; i < n_sort; i += SELD_THREADS) keys[i] = ~0ull;
+    if (tid < 4) misc[tid] = 0;
     __syncthreads();
     if constexpr (QUEST) {
         for (int i = tid; i < group * (D / 2); i += SELD_THREADS) {
@@ -342,98 +383,313 @@ __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const ui
             qm[g * L::MROW + w] = lo | hi;
         }
     }
+    if (two_pass && warp < group) {   // |q_g|_1, one warp per head
+        float a1 = 0.0f;
+        for (int c = lane; c < D; c += 32) a1 += fabsf(qf[warp * L::QROW + c]);
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) a1 += __shfl_xor_sync(0xFFFFFFFFu, a1, d);
+        if (lane == 0) atomicMax(&misc[2], __float_as_int(a1));
+    }
 
-    const int n_tiles = cdiv(nk, SELD_TILE);
-    auto issue = [&](int t) {
+    // Statistics rows of list entries [t*64, t*64+64) -> shared-memory stage t & 1.  identity: entry i is page i.
+    auto issue = [&](int t, int count, bool identity) {
         uint8_t* stage = tiles + (t & 1) * NARR * L::TILE_BYTES;
         const int p0 = t * SELD_TILE;
-        const int rows = min(SELD_TILE, nk - p0);
+        const int rows = min(SELD_TILE, count - p0);
         for (int i = tid; i < rows * VEC; i += SELD_THREADS) {
             const int r = i / VEC, c = i - r * VEC;
-            const long long src = (static_cast<long long>(h) * cap_blocks + p0 + r) * D + c * 8;
+            const int page = identity ? p0 + r : cand[p0 + r];
+            const long long src = (static_cast<long long>(h) * cap_blocks + page) * D + c * 8;
             cp_async16(stage + r * L::ROW + c * 16, ka + src);
             if constexpr (QUEST) cp_async16(stage + L::TILE_BYTES + r * L::ROW + c * 16, kb + src);
         }
         cp_async_commit();
     };
 
-    const int pl = tid >> 2, sub = tid & 3;
-    if (n_tiles > 0) issue(0);
-    for (int t = 0; t < n_tiles; ++t) {
-        if (t + 1 < n_tiles) { issue(t + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
-        __syncthreads();
-        const uint8_t* stage = tiles + (t & 1) * NARR * L::TILE_BYTES;
-        const int page = t * SELD_TILE + pl;
-        float best = -FLT_MAX;
-        if (page < nk) {
-            const uint4* ra = reinterpret_cast<const uint4*>(stage + pl * L::ROW);
-            const uint4* rb = reinterpret_cast<const uint4*>(stage + L::TILE_BYTES + pl * L::ROW);
-            for (int g = sub; g < group; g += 4) {
-                float2 acc[16];
-#pragma unroll
-                for (int w = 0; w < 16; ++w) acc[w] = make_float2(0.0f, 0.0f);
-                const float4* qrow = reinterpret_cast<const float4*>(qf + g * L::QROW);
-                const uint4* mrow = reinterpret_cast<const uint4*>(qm + g * L::MROW);
-#pragma unroll 1
-                for (int i = 0; i < D / 32; ++i) {
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {          // 8 channels per 16-byte chunk
-                        const uint4 a = ra[i * 4 + v];
-                        uint32_t kw[4] = {a.x, a.y, a.z, a.w};
-                        if constexpr (QUEST) {
-                            const uint4 b = rb[i * 4 + v];
-                            const uint4 m = mrow[i * 4 + v];
-                            kw[0] = (b.x & m.x) | (a.x & ~m.x);
-                            kw[1] = (b.y & m.y) | (a.y & ~m.y);
-                            kw[2] = (b.z & m.z) | (a.z & ~m.z);
-                            kw[3] = (b.w & m.w) | (a.w & ~m.w);
-                        }
-                        const float4 q0 = qrow[i * 8 + v * 2], q1 = qrow[i * 8 + v * 2 + 1];
-                        acc[v * 4 + 0] = fma2(make_float2(q0.x, q0.y), word_to_float2<BF16>(kw[0]), acc[v * 4 + 0]);
-                        acc[v * 4 + 1] = fma2(make_float2(q0.z, q0.w), word_to_float2<BF16>(kw[1]), acc[v * 4 + 1]);
-                        acc[v * 4 + 2] = fma2(make_float2(q1.x, q1.y), word_to_float2<BF16>(kw[2]), acc[v * 4 + 2]);
-                        acc[v * 4 + 3] = fma2(make_float2(q1.z, q1.w), word_to_float2<BF16>(kw[3]), acc[v * 4 + 3]);
-                    }
-                }
-                // butterfly pairing: partial j with j+16, then j+8, j+4, j+2, j+1
-#pragma unroll
-                for (int w = 0; w < 8; ++w) acc[w] = add2(acc[w], acc[w + 8]);
-#pragma unroll
-                for (int w = 0; w < 4; ++w) acc[w] = add2(acc[w], acc[w + 4]);
-                acc[0] = add2(acc[0], acc[2]);
-                acc[1] = add2(acc[1], acc[3]);
-                acc[0] = add2(acc[0], acc[1]);
-                const float s = __fadd_rn(acc[0].x, acc[0].y);
-                if (s > best) best = s;
-            }
-        }
-        // the four threads of a page hold the maxima of their shares of the group
-        {
-            float o = __shfl_xor_sync(0xFFFFFFFFu, best, 1);
-            if (o > best) best = o;
-            o = __shfl_xor_sync(0xFFFFFFFFu, best, 2);
-            if (o > best) best = o;
-        }
-        if (sub == 0 && page < nk) keys[page] = seld_key((page < n_sink || page >= local_lo) ? -FLT_MAX : best, page);
-        __syncthreads();
-    }
-
-    // ---- bitonic sort of the keys, ascending ----
-    for (int size = 2; size <= n_sort; size <<= 1) {
-        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+    // Exact scores of `count` list entries into keys[entry] (the arithmetic of the reference's warp, one thread
+    // per (page, head)).
+    auto exact_pass = [&](int count, bool identity) {
+        const int n_tiles = cdiv(count, SELD_TILE);
+        const int pl = tid >> 2, sub = tid & 3;
+        if (n_tiles > 0) issue(0, count, identity);
+        for (int t = 0; t < n_tiles; ++t) {
+            if (t + 1 < n_tiles) { issue(t + 1, count, identity); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
             __syncthreads();
-            for (int t = tid; t < n_sort / 2; t += SELD_THREADS) {
-                const int pos = 2 * t - (t & (stride - 1));
-                const unsigned long long a = keys[pos], b = keys[pos + stride];
-                const bool up = (pos & size) == 0;
-                if ((a > b) == up) { keys[pos] = b; keys[pos + stride] = a; }
+            const uint8_t* stage = tiles + (t & 1) * NARR * L::TILE_BYTES;
+            const int entry = t * SELD_TILE + pl;
+            float best = -FLT_MAX;
+            if (entry < count) {
+                const uint4* ra = reinterpret_cast<const uint4*>(stage + pl * L::ROW);
+                const uint4* rb = reinterpret_cast<const uint4*>(stage + L::TILE_BYTES + pl * L::ROW);
+                for (int g = sub; g < group; g += 4) {
+                    float2 acc[16];
+#pragma unroll
+                    for (int w = 0; w < 16; ++w) acc[w] = make_float2(0.0f, 0.0f);
+                    const float4* qrow = reinterpret_cast<const float4*>(qf + g * L::QROW);
+                    const uint4* mrow = reinterpret_cast<const uint4*>(qm + g * L::MROW);
+#pragma unroll 1
+                    for (int i = 0; i < D / 32; ++i) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {          // 8 channels per 16-byte chunk
+                            const uint4 a = ra[i * 4 + v];
+                            uint32_t kw[4] = {a.x, a.y, a.z, a.w};
+                            if constexpr (QUEST) {
+                                const uint4 b = rb[i * 4 + v];
+                                const uint4 m = mrow[i * 4 + v];
+                                kw[0] = (b.x & m.x) | (a.x & ~m.x);
+                                kw[1] = (b.y & m.y) | (a.y & ~m.y);
+                                kw[2] = (b.z & m.z) | (a.z & ~m.z);
+                                kw[3] = (b.w & m.w) | (a.w & ~m.w);
+                            }
+                            const float4 q0 = qrow[i * 8 + v * 2], q1 = qrow[i * 8 + v * 2 + 1];
+                            acc[v * 4 + 0] = fma2(make_float2(q0.x, q0.y), word_to_float2<BF16>(kw[0]), acc[v * 4 + 0]);
+                            acc[v * 4 + 1] = fma2(make_float2(q0.z, q0.w), word_to_float2<BF16>(kw[1]), acc[v * 4 + 1]);
+                            acc[v * 4 + 2] = fma2(make_float2(q1.x, q1.y), word_to_float2<BF16>(kw[2]), acc[v * 4 + 2]);
+                            acc[v * 4 + 3] = fma2(make_float2(q1.z, q1.w), word_to_float2<BF16>(kw[3]), acc[v * 4 + 3]);
+                        }
+                    }
+                    // butterfly pairing: partial j with j+16, then j+8, j+4, j+2, j+1
+#pragma unroll
+                    for (int w = 0; w < 8; ++w) acc[w] = add2(acc[w], acc[w + 8]);
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) acc[w] = add2(acc[w], acc[w + 4]);
+                    acc[0] = add2(acc[0], acc[2]);
+                    acc[1] = add2(acc[1], acc[3]);
+                    acc[0] = add2(acc[0], acc[1]);
+                    const float s = __fadd_rn(acc[0].x, acc[0].y);
+                    if (s > best) best = s;
+                }
+            }
+            // the four threads of a page hold the maxima of their shares of the group
+            {
+                float o = __shfl_xor_sync(0xFFFFFFFFu, best, 1);
+                if (o > best) best = o;
+                o = __shfl_xor_sync(0xFFFFFFFFu, best, 2);
+                if (o > best) best = o;
+            }
+            if (sub == 0 && entry < count) {
+                const int page = identity ? entry : cand[entry];
+                keys[entry] = seld_key((page < n_sink || page >= local_lo) ? -FLT_MAX : best, page);
+            }
+            __syncthreads();
+        }
+    };
+
+    // ascending bitonic sort of keys[0, n)
+    auto sort_keys = [&](int n) {
+        for (int size = 2; size <= n; size <<= 1) {
+            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                __syncthreads();
+                for (int t = tid; t < n / 2; t += SELD_THREADS) {
+                    const int pos = 2 * t - (t & (stride - 1));
+                    const unsigned long long a = keys[pos], b = keys[pos + stride];
+                    const bool up = (pos & size) == 0;
+                    if ((a > b) == up) { keys[pos] = b; keys[pos + stride] = a; }
+                }
             }
         }
+        __syncthreads();
+    };
+    auto pow2_at_least = [](int n) { int m = 2; while (m < n) m <<= 1; return m; };
+
+    int n_sorted = 0;   // number of keys sorted at the end
+    bool done = false;
+    SELD_PROF(0)
+    if (two_pass) {
+        // ---------------- pass 1: approximate scores with tensor cores ----------------
+        // Each warp takes 16 pages at a time straight from global memory: thread (r = lane/4, t = lane%4) reads
+        // 16 contiguous bytes — channels 32 s + 8 t .. + 7 — of rows r and r + 8 for every 32-channel chunk s.
+        // Those eight channels feed two m16n8k16 MMAs (slots k = 2t, 2t+1 and k = 2t+8, 2t+9 of each); the sum
+        // over k does not care about the order as long as the q fragments below use the same assignment.
+        constexpr int NSC = D / 32;
+        uint32_t bp[NSC][2][2], bm[NSC][2][2];
+        {
+            const int gid = lane >> 2, t4 = lane & 3;
+#pragma unroll
+            for (int sc = 0; sc < NSC; ++sc)
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        uint32_t w = 0u;
+                        if (gid < group)
+                            w = *reinterpret_cast<const uint32_t*>(q + (static_cast<long long>(h) * group + gid) * D +
+                                                                   sc * 32 + 8 * t4 + 4 * j + 2 * hh);
+                        const uint32_t neg = ((w & 0x8000u) ? 0xFFFFu : 0u) | ((w & 0x80000000u) ? 0xFFFF0000u : 0u);
+                        bp[sc][j][hh] = w & ~neg;     // non-negative part of q
+                        bm[sc][j][hh] = w & neg;      // negative part
+                    }
+        }
+        uint32_t kabs2 = 0u;
+        const int n_groups = cdiv(nk, 16);
+        for (int grp = warp; grp < n_groups; grp += SELD_THREADS / 32) {
+            const int pg0 = grp * 16 + (lane >> 2), pg1 = pg0 + 8;
+            const int t4 = lane & 3;
+            // rows past the end are read from the last page instead (in bounds) and ignored afterwards
+            const long long r0 = (static_cast<long long>(h) * cap_blocks + min(pg0, nk - 1)) * D + 8 * t4;
+            const long long r1 = (static_cast<long long>(h) * cap_blocks + min(pg1, nk - 1)) * D + 8 * t4;
+            uint4 a0[NSC], a1[NSC], b0[QUEST ? NSC : 1], b1[QUEST ? NSC : 1];
+#pragma unroll
+            for (int sc = 0; sc < NSC; ++sc) {
+                a0[sc] = __ldg(reinterpret_cast<const uint4*>(ka + r0 + sc * 32));
+                a1[sc] = __ldg(reinterpret_cast<const uint4*>(ka + r1 + sc * 32));
+                if constexpr (QUEST) {
+                    b0[sc] = __ldg(reinterpret_cast<const uint4*>(kb + r0 + sc * 32));
+                    b1[sc] = __ldg(reinterpret_cast<const uint4*>(kb + r1 + sc * 32));
+                }
+            }
+            const uint32_t keep0 = pg0 < nk ? 0x7FFF7FFFu : 0u, keep1 = pg1 < nk ? 0x7FFF7FFFu : 0u;
+            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int sc = 0; sc < NSC; ++sc) {
+                // MMA j uses words (2j, 2j+1) of the 16 bytes: fragment {row r: word 2j | row r+8: word 2j | row r: word 2j+1 | ...}
+                const uint32_t fa[2][4] = {{a0[sc].x, a1[sc].x, a0[sc].y, a1[sc].y}, {a0[sc].z, a1[sc].z, a0[sc].w, a1[sc].w}};
+                kabs2 = __vmaxu2(kabs2, __vmaxu2(__vmaxu2(a0[sc].x & keep0, a0[sc].y & keep0), __vmaxu2(a0[sc].z & keep0, a0[sc].w & keep0)));
+                kabs2 = __vmaxu2(kabs2, __vmaxu2(__vmaxu2(a1[sc].x & keep1, a1[sc].y & keep1), __vmaxu2(a1[sc].z & keep1, a1[sc].w & keep1)));
+                if constexpr (QUEST) {
+                    const uint32_t fb[2][4] = {{b0[sc].x, b1[sc].x, b0[sc].y, b1[sc].y}, {b0[sc].z, b1[sc].z, b0[sc].w, b1[sc].w}};
+                    kabs2 = __vmaxu2(kabs2, __vmaxu2(__vmaxu2(b0[sc].x & keep0, b0[sc].y & keep0), __vmaxu2(b0[sc].z & keep0, b0[sc].w & keep0)));
+                    kabs2 = __vmaxu2(kabs2, __vmaxu2(__vmaxu2(b1[sc].x & keep1, b1[sc].y & keep1), __vmaxu2(b1[sc].z & keep1, b1[sc].w & keep1)));
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        mma_16816<BF16>(c, fa[j], bm[sc][j][0], bm[sc][j][1]);   // minima meet the negative part of q
+                        mma_16816<BF16>(c, fb[j], bp[sc][j][0], bp[sc][j][1]);   // maxima meet the non-negative part
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        mma_16816<BF16>(c, fa[j], bp[sc][j][0] | bm[sc][j][0], bp[sc][j][1] | bm[sc][j][1]);
+                }
+            }
+            // c0,c1: page lane/4, heads 2t,2t+1; c2,c3: page lane/4 + 8
+            float lo = -FLT_MAX, hi = -FLT_MAX;
+            if (2 * t4 < group) { lo = c[0]; hi = c[2]; }
+            if (2 * t4 + 1 < group) { lo = fmaxf(lo, c[1]); hi = fmaxf(hi, c[3]); }
+#pragma unroll
+            for (int d = 1; d <= 2; d <<= 1) {
+                lo = fmaxf(lo, __shfl_xor_sync(0xFFFFFFFFu, lo, d));
+                hi = fmaxf(hi, __shfl_xor_sync(0xFFFFFFFFu, hi, d));
+            }
+            if (t4 == 0) {
+                if (pg0 < nk) approx[pg0] = lo;
+                if (pg1 < nk) approx[pg1] = hi;
+            }
+        }
+        SELD_PROF(1)
+        {   // largest |statistic| seen (16-bit patterns of non-negative values order like the values)
+            uint32_t m16 = max(kabs2 & 0xFFFFu, kabs2 >> 16);
+#pragma unroll
+            for (int d = 16; d >= 1; d >>= 1) m16 = max(m16, __shfl_xor_sync(0xFFFFFFFFu, m16, d));
+            if (lane == 0) atomicMax(&misc[1], static_cast<int>(m16));
+        }
+        __syncthreads();
+        const float kabs = In16<BF16>::to_f(static_cast<uint16_t>(misc[1]));
+        const float delta = __int_as_float(misc[2]) * kabs * (1.0f / 65536.0f);
+        // ---------------- threshold: k-th largest lower bound, by radix selection ----------------
+        // ascending 32-bit image of (approx - delta); forced pages rank lowest.  Four 8-bit digits, most
+        // significant first: histogram of the keys that share the prefix found so far, then the digit whose
+        // bucket holds the k-th largest.
+        auto lower_key = [&](int i) -> uint32_t {
+            if (i < n_sink || i >= local_lo) return 0u;
+            float v = approx[i] - delta;
+            if (v == 0.0f) v = 0.0f;
+            const uint32_t u = __float_as_uint(v);
+            return (u >> 31) ? ~u : (u | 0x80000000u);
+        };
+        int* hist = reinterpret_cast<int*>(keys);      // the key array is free until pass 2
+        uint32_t prefix = 0u;
+        int remaining = k;
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            hist[tid] = 0;
+            __syncthreads();
+            for (int i = tid; i < nk; i += SELD_THREADS) {
+                const uint32_t key = lower_key(i);
+                if (shift == 24 || (key >> (shift + 8)) == (prefix >> (shift + 8))) atomicAdd(&hist[(key >> shift) & 255u], 1);
+            }
+            __syncthreads();
+            if (warp == 0) {
+                // lane l owns digits 8l .. 8l+7; walk from the largest digit down
+                int cnt[8], mine = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { cnt[j] = hist[lane * 8 + j]; mine += cnt[j]; }
+                // inclusive suffix sums over the lanes
+                int incl = mine;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int v = __shfl_down_sync(0xFFFFFFFFu, incl, d);
+                    if (lane + d < 32) incl += v;
+                }
+                const int excl = incl - mine;                    // keys in digits above this lane's eight
+                if (excl < remaining && remaining <= incl) {     // the k-th largest lies in this lane's digits
+                    int seen = excl, digit = 0;
+#pragma unroll
+                    for (int j = 7; j >= 0; --j) {
+                        if (seen < remaining && remaining <= seen + cnt[j]) { digit = lane * 8 + j; break; }
+                        seen += cnt[j];
+                    }
+                    misc[3] = digit;
+                    misc[0] = remaining - seen;                  // rank inside the chosen bucket
+                }
+            }
+            __syncthreads();
+            prefix |= static_cast<uint32_t>(misc[3]) << shift;
+            remaining = misc[0];
+            __syncthreads();
+        }
+        if (tid == 0) misc[0] = 0;
+        float threshold;
+        {
+            // prefix 0 is the rank of a forced page: fewer than k free pages, so every one of them is a candidate
+            const uint32_t u = (prefix >> 31) ? (prefix ^ 0x80000000u) : ~prefix;
+            threshold = prefix == 0u ? -FLT_MAX : __uint_as_float(u);
+        }
+        __syncthreads();
+        for (int i = tid; i < nk; i += SELD_THREADS) {
+            if (i >= n_sink && i < local_lo && approx[i] + delta >= threshold) {
+                const int slot = atomicAdd(&misc[0], 1);
+                if (slot < SELD_CAND_CAP) cand[slot] = i;
+            }
+        }
+        __syncthreads();
+        const int n_cand = misc[0];
+        SELD_PROF(4)
+#ifdef TA100_PROFILE_SOFTMAX
+        if (blockIdx.x == 0 && threadIdx.x == 0) g_sel_prof[10] = n_cand;
+#endif
+        if (n_cand <= SELD_CAND_CAP && isfinite(delta)) {
+            // ---------------- pass 2: exact scores of the candidates ----------------
+            n_sorted = pow2_at_least(n_cand);
+            for (int i = tid; i < n_sorted; i += SELD_THREADS) keys[i] = ~0ull;
+            __syncthreads();
+            exact_pass(n_cand, false);
+            SELD_PROF(5)
+            // order the few candidates by counting: rank = number of smaller keys (keys are distinct)
+            unsigned long long* sorted = keys + SELD_CAND_CAP;
+            for (int i = tid; i < n_sorted; i += SELD_THREADS) sorted[i] = ~0ull;
+            __syncthreads();
+            for (int i = tid; i < n_cand; i += SELD_THREADS) {
+                const unsigned long long mine = keys[i];
+                int rank = 0;
+                for (int j = 0; j < n_cand; ++j) rank += keys[j] < mine ? 1 : 0;
+                sorted[rank] = mine;
+            }
+            __syncthreads();
+            for (int i = tid; i < n_sorted; i += SELD_THREADS) keys[i] = sorted[i];
+            __syncthreads();
+            SELD_PROF(6)
+            done = true;
+        }
     }
-    __syncthreads();
+    if (!done) {
+        n_sorted = pow2_at_least(nk);
+        __syncthreads();
+        for (int i = tid; i < n_sorted; i += SELD_THREADS) keys[i] = ~0ull;
+        __syncthreads();
+        exact_pass(nk, true);
+        sort_keys(n_sorted);
+    }
 
     int32_t* row = out + static_cast<long long>(h) * width;
-    const int forced = n_sink + (nk - local_lo);
     const bool pad = (sink + local) > 0;
     // optional scores of the picks (forced blocks +FLT_MAX, padding -FLT_MAX): what a shard of a longer
     // sequence sends to its peers so that all of them derive the same global top-k
@@ -445,7 +701,7 @@ __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const ui
     for (int r = tid; r < k; r += SELD_THREADS) {
         int32_t id = -1;
         float sc = -FLT_MAX;
-        if (r < n_sort) {
+        if (r < n_sorted) {
             const unsigned long long key = keys[r];
             const bool real = key != ~0ull;
             const bool found = real && seld_key_score(key) > -FLT_MAX * 0.5f;
@@ -458,7 +714,14 @@ __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const ui
         row[i] = -1;
         if (srow) srow[i] = -FLT_MAX;
     }
+    SELD_PROF(7)
 }
+
+#ifdef TA100_PROFILE_SOFTMAX
+int select_profile_read(long long* out16) {
+    return static_cast<int>(cudaMemcpyFromSymbol(out16, g_sel_prof, sizeof(long long) * 16));
+}
+#endif
 
 int select_prefill_dispatch(const void* q_mean, const void* ka, const void* kb, void* out, int heads, int group, int nq,
                             int nk, int d, int k, int causal, int quest, int is_bf16, int sink, int local,
