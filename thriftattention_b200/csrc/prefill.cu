@@ -405,7 +405,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
         }
     } else if (warp == 1) {
         // =========================== MMA issuer ===========================
-        if (lane == 0) tmem_cp_sf(tmem + TM_SFA_P, make_smem_desc(sbase + L::CSF, 0, 128, SWZ_NONE));
+        tmem_cp_sf_elect(tmem + TM_SFA_P, make_smem_desc(sbase + L::CSF, 0, 128, SWZ_NONE));
         uint32_t gstep = 0, gslot = 0;
         int n_item = 0;
         bool ok = true;
@@ -414,32 +414,32 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
         const uint32_t idesc_qk16 = make_idesc_f16(128, STEP, BF16 ? 1 : 0, 0, 0);
         const uint32_t idesc_pv16 = make_idesc_f16(128, D, BF16 ? 1 : 0, 0, 1);
 
-        // S = Q K^T for the step described by `e`, operands in ring slot `slot` (one thread)
+        // S = Q K^T for the step described by `e`, operands in ring slot `slot` (whole warp, one lane issues)
         auto issue_qk = [&](uint32_t e, uint32_t slot) {
             const uint32_t sa = sbase + L::SLOTS + slot * SLOT_BYTES;
             const uint32_t d_t = tmem + TM_S;
             if (!(e & E_FP16)) {
                 const uint32_t sfb = tmem + TM_SFB_K;
                 for (int a = 0; a < QK_ATOMS; ++a)
-                    tmem_cp_sf(sfb + a * 4, make_smem_desc(sa + L::KSF + a * 512, 0, 128, SWZ_NONE));
+                    tmem_cp_sf_elect(sfb + a * 4, make_smem_desc(sa + L::KSF + a * 512, 0, 128, SWZ_NONE));
                 for (int kb = 0; kb < KBLK; ++kb) {
                     const uint64_t ad = make_smem_desc(sbase + L::Q4 + kb * 32, 16, SBO_QK, SWZ_QK);
                     const uint64_t bd = make_smem_desc(sa + L::K4 + kb * 32, 16, SBO_QK, SWZ_QK);
                     if constexpr (MX)
-                        mma_mxfp4(d_t, ad, bd, make_idesc_fp4(128, STEP, 1, kb * 2, kb * 2), tmem + TM_SFA_Q, sfb, kb > 0);
+                        mma_mxfp4_elect(d_t, ad, bd, make_idesc_fp4(128, STEP, 1, kb * 2, kb * 2), tmem + TM_SFA_Q, sfb, kb > 0);
                     else
-                        mma_nvfp4(d_t, ad, bd, idesc_qk4, tmem + TM_SFA_Q + kb * 4, sfb + kb * 4, kb > 0);
+                        mma_nvfp4_elect(d_t, ad, bd, idesc_qk4, tmem + TM_SFA_Q + kb * 4, sfb + kb * 4, kb > 0);
                 }
             } else {
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t hf = ks / 4, kk = ks % 4;
                     const uint64_t ad = make_smem_desc(sbase + L::Q16 + hf * QTILE * 128 + kk * 32, 16, 1024, SWZ_128B);
                     const uint64_t bd = make_smem_desc(sa + hf * STEP * 128 + kk * 32, 16, 1024, SWZ_128B);
-                    mma_f16(d_t, ad, bd, idesc_qk16, ks > 0);
+                    mma_f16_elect(d_t, ad, bd, idesc_qk16, ks > 0);
                 }
-                tc_commit(smem_u32(&bars.slot_empty[slot]));  // the K tile is free once S is computed
+                tc_commit_elect(smem_u32(&bars.slot_empty[slot]));  // the K tile is free once S is computed
             }
-            tc_commit(smem_u32(&bars.s_full));
+            tc_commit_elect(smem_u32(&bars.s_full));
         };
 
         for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
@@ -449,9 +449,8 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
             ok = mbar_wait(smem_u32(&bars.q_full), n_item & 1, abortp, budget);
             if (!ok) break;
             tc_fence_after_sync();
-            if (lane == 0)
-                for (int a = 0; a < QK_ATOMS; ++a)
-                    tmem_cp_sf(tmem + TM_SFA_Q + a * 4, make_smem_desc(sbase + L::QSF + a * 512, 0, 128, SWZ_NONE));
+            for (int a = 0; a < QK_ATOMS; ++a)
+                    tmem_cp_sf_elect(tmem + TM_SFA_Q + a * 4, make_smem_desc(sbase + L::QSF + a * 512, 0, 128, SWZ_NONE));
             if (n == 0 && lane == 0) mbar_arrive(smem_u32(&bars.q_empty));
 
             // slot bookkeeping: an FP4 step owns one slot, a 16-bit step a K slot then a V slot
@@ -462,8 +461,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                      mbar_wait(smem_u32(&bars.s_free), (gstep & 1) ^ 1, abortp, budget);
                 if (ok) {
                     tc_fence_after_sync();
-                    if (lane == 0) issue_qk(e0, qk_slot % NSLOTS);
-                    __syncwarp();
+                    issue_qk(e0, qk_slot % NSLOTS);
                 }
             }
             for (int i = 0; i < n && ok; ++i) {
@@ -479,8 +477,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                          mbar_wait(smem_u32(&bars.s_free), ((gstep + 1) & 1) ^ 1, abortp, budget);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    if (lane == 0) issue_qk(e1, qk_slot % NSLOTS);
-                    __syncwarp();
+                    issue_qk(e1, qk_slot % NSLOTS);
                 }
                 // O += P V for the current step
                 const uint32_t buf = gstep & 1;
@@ -488,29 +485,28 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                 if (ok && fp16) ok = mbar_wait(smem_u32(&bars.slot_full[pv_slot % NSLOTS]), (pv_slot / NSLOTS) & 1, abortp, budget);
                 if (!ok) break;
                 tc_fence_after_sync();
-                if (lane == 0) {
+                {
                     const uint32_t sa = sbase + L::SLOTS + (pv_slot % NSLOTS) * SLOT_BYTES;
                     const uint32_t d_t = tmem + TM_O;
                     const uint32_t acc = i > 0 ? 1u : 0u;
                     if (!fp16) {
                         const uint32_t sfb = tmem + TM_SFB_V + buf * 4;
-                        tmem_cp_sf(sfb, make_smem_desc(sa + L::VSF, 0, 128, SWZ_NONE));
+                        tmem_cp_sf_elect(sfb, make_smem_desc(sa + L::VSF, 0, 128, SWZ_NONE));
                         const uint64_t ad = make_smem_desc(sbase + L::P + buf * 4096, 16, 256, SWZ_32B);
                         const uint64_t bd = make_smem_desc(sa + L::V4, 16, 256, SWZ_32B);
-                        if constexpr (MX) mma_mxfp4(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
-                        else mma_nvfp4(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
+                        if constexpr (MX) mma_mxfp4_elect(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
+                        else mma_nvfp4_elect(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
                     } else {
                         for (int ks = 0; ks < STEP / 16; ++ks) {
                             const uint64_t ad = make_smem_desc(sbase + L::P + ks * 32, 16, 1024, SWZ_128B);
                             const uint64_t bd = make_smem_desc(sa + ks * 2048, STEP * 128, 1024, SWZ_128B);
-                            mma_f16(d_t, ad, bd, idesc_pv16, (acc == 0 && ks == 0) ? 0 : 1);
+                            mma_f16_elect(d_t, ad, bd, idesc_pv16, (acc == 0 && ks == 0) ? 0 : 1);
                         }
                     }
-                    tc_commit(smem_u32(&bars.slot_empty[pv_slot % NSLOTS]));
-                    tc_commit(smem_u32(&bars.p_free[buf]));
-                    if (i + 1 == n) tc_commit(smem_u32(&bars.q_empty));
+                    tc_commit_elect(smem_u32(&bars.slot_empty[pv_slot % NSLOTS]));
+                    tc_commit_elect(smem_u32(&bars.p_free[buf]));
+                    if (i + 1 == n) tc_commit_elect(smem_u32(&bars.q_empty));
                 }
-                __syncwarp();
                 ++gstep;
             }
             gslot = qk_slot;
@@ -585,56 +581,19 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                 }
                 TA100_PROF(3)
                 const uint32_t buf = gstep & 1;
-                // the PV that last read this P buffer must be complete: two steps ago for the FP4
-                // double buffer; the previous step whenever a 16-bit P tile (which spans the
-                // whole P region) is involved
-                ok = mbar_wait(smem_u32(&bars.p_free[buf]), ((gstep >> 1) & 1) ^ 1, abortp, budget);
-                if (!ok) break;
                 const bool transition = fp16 && i > 0 && !prev_fp16 && p.round_partial;
                 const bool need_rescale = __any_sync(0xFFFFFFFFu, changed && i > 0);
-                if ((transition || need_rescale || fp16 || prev_fp16) && gstep > 0) {
+                // A 16-bit P tile spans the whole P region, so with one involved the previous PV must be complete
+                // before P is written; the FP4 tiles alternate between two buffers and only wait for the PV of
+                // two steps ago, and that only once the probabilities are ready to be stored.
+                const bool wide_p = fp16 || prev_fp16;
+                if (wide_p && gstep > 0) {
                     ok = mbar_wait(smem_u32(&bars.p_free[(gstep - 1) & 1]), ((gstep - 1) >> 1) & 1, abortp, budget);
                     if (!ok) break;
                 }
-                tc_fence_after_sync();
                 TA100_PROF(4)
-                if (transition) {
-                    // state rounding between the FP4 and the 16-bit phase
-                    const float norm = l_run > 0.0f ? __fdiv_rn(CSCALE_INV, l_run) : 0.0f;
-                    const float back = l_run * CSCALE;
-#pragma unroll 1
-                    for (int c = 0; c < D; c += 32) {
-                        uint32_t r[32];
-                        tmem_ld32(tmem + lane_addr + TM_O + c, r);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const float v = __uint_as_float(r[j]) * norm;
-                            r[j] = __float_as_uint(In16<BF16>::to_f(In16<BF16>::from_f(v)) * back);
-                        }
-                        tmem_st32(tmem + lane_addr + TM_O + c, r);
-                    }
-                    tmem_wait_st();
-                }
-                if (need_rescale) {
-#pragma unroll 1
-                    for (int c = 0; c < D; c += 64) {
-                        uint32_t ra[32], rb[32];
-                        tmem_ld32(tmem + lane_addr + TM_O + c, ra);
-                        tmem_ld32(tmem + lane_addr + TM_O + c + 32, rb);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            ra[j] = __float_as_uint(__uint_as_float(ra[j]) * rescale);
-                            rb[j] = __float_as_uint(__uint_as_float(rb[j]) * rescale);
-                        }
-                        tmem_st32(tmem + lane_addr + TM_O + c, ra);
-                        tmem_st32(tmem + lane_addr + TM_O + c + 32, rb);
-                    }
-                    tmem_wait_st();
-                }
-                TA100_PROF(5)
                 // probabilities, row sum, P tile
+                const float l_prev = l_run;
                 if (!fp16) {
                     uint32_t w[STEP / 8];
                     if (part) {
@@ -650,6 +609,8 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
 #pragma unroll
                         for (int g = 0; g < STEP / 8; ++g) w[g] = 0u;
                     }
+                    ok = mbar_wait(smem_u32(&bars.p_free[buf]), ((gstep >> 1) & 1) ^ 1, abortp, budget);
+                    if (!ok) break;
                     // 128 rows x 32 bytes, 32-byte swizzle; FP4 steps alternate between two 4 KB buffers
                     const uint32_t r8 = row & 7;
                     uint8_t* base = smem + L::P + buf * 4096 + (row >> 3) * 256 + r8 * 32;
@@ -669,6 +630,8 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
 #pragma unroll
                         for (int j = 0; j < STEP / 2; ++j) w[j] = 0u;
                     }
+                    ok = mbar_wait(smem_u32(&bars.p_free[buf]), ((gstep >> 1) & 1) ^ 1, abortp, budget);
+                    if (!ok) break;
                     // 128 rows x 128 bytes, 128-byte swizzle; one buffer for 16-bit steps
                     const uint32_t r8 = row & 7;
                     uint8_t* base = smem + L::P + (row >> 3) * 1024 + r8 * 128;
@@ -677,8 +640,50 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                         *reinterpret_cast<uint4*>(base + ((c ^ r8) * 16)) =
                             make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
                 }
-                TA100_PROF(6)
                 fence_proxy_async_smem();
+                TA100_PROF(5)
+                // O is touched only now, after the exponentials: the PV of the previous step has had their time
+                // to finish.  The issuer adds this step's P V only after the arrival below.
+                if ((transition || need_rescale) && !wide_p) {
+                    ok = mbar_wait(smem_u32(&bars.p_free[(gstep - 1) & 1]), ((gstep - 1) >> 1) & 1, abortp, budget);
+                    if (!ok) break;
+                }
+                if (transition || need_rescale) tc_fence_after_sync();
+                if (transition) {
+                    // state rounding between the FP4 and the 16-bit phase (state before this step's update)
+                    const float norm = l_prev > 0.0f ? __fdiv_rn(CSCALE_INV, l_prev) : 0.0f;
+                    const float back = l_prev * CSCALE * rescale;
+#pragma unroll 1
+                    for (int c = 0; c < D; c += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(tmem + lane_addr + TM_O + c, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float v = __uint_as_float(r[j]) * norm;
+                            r[j] = __float_as_uint(In16<BF16>::to_f(In16<BF16>::from_f(v)) * back);
+                        }
+                        tmem_st32(tmem + lane_addr + TM_O + c, r);
+                    }
+                    tmem_wait_st();
+                } else if (need_rescale) {
+#pragma unroll 1
+                    for (int c = 0; c < D; c += 64) {
+                        uint32_t ra[32], rb[32];
+                        tmem_ld32(tmem + lane_addr + TM_O + c, ra);
+                        tmem_ld32(tmem + lane_addr + TM_O + c + 32, rb);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            ra[j] = __float_as_uint(__uint_as_float(ra[j]) * rescale);
+                            rb[j] = __float_as_uint(__uint_as_float(rb[j]) * rescale);
+                        }
+                        tmem_st32(tmem + lane_addr + TM_O + c, ra);
+                        tmem_st32(tmem + lane_addr + TM_O + c + 32, rb);
+                    }
+                    tmem_wait_st();
+                }
+                TA100_PROF(6)
                 tc_fence_before_sync();
                 mbar_arrive(smem_u32(&bars.p_full[buf]));
                 TA100_PROF(7)
