@@ -206,11 +206,11 @@ def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_g
                                        kv_len=n_local * 64, page_table=table, allow_padded_selection=True)
         sel = tad.select_pages_sharded(q, k_min, k_max, shard=shard, total_pages=pages, top_k=top_k, sink=DEC_SINK,
                                        local=DEC_LOCAL)
-        _, po, pml = _C.decode_attention(q, k_hi, v_hi, sel, q4, k4, v4, qs, ks, vs, is_mx=False, is_bf16=False,
-                                         kv_len=n_local * 64, page_table=table, allow_padded_selection=True,
-                                         return_partials=True)
-        all_o, all_ml = tad.exchange_partials(po, pml)
-        return _C.merge_decode_partials(all_o, all_ml, is_mx=False, is_bf16=False)
+        return tad.decode_partials_exchange_merge(
+            lambda **kw: _C.decode_attention(q, k_hi, v_hi, sel, q4, k4, v4, qs, ks, vs, is_mx=False, is_bf16=False,
+                                             kv_len=n_local * 64, page_table=table, allow_padded_selection=True, **kw),
+            heads=DEC_BATCH * HKV, group_size=DEC_GROUP, head_dim=D, shard=shard, total_pages=pages, num_splits=0,
+            is_mx=False, is_bf16=False, device=device)
 
     def barrier():
         if world > 1:
@@ -239,7 +239,7 @@ def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_g
             "workload": f"paged decode {DEC_BATCH} seq x {DEC_SEQ} tokens, {HQ}q/{HKV}kv x {D}, NVFP4 + fp16 shadow, Quest "
                         f"{top_k} + {DEC_SINK} sink + {DEC_LOCAL} recent of {pages} pages in 16 bits; step = select + "
                         f"attend + merge; KV sequence split over {world} GPU(s)",
-            "launches_per_step": 4 if world == 1 else 6}
+            "launches_per_step": 4 if world == 1 else 5}
 
 
 # ------------------------------------------------------------------------- small cases for profiler captures

@@ -109,13 +109,28 @@ int ta100_select_prefill(const void* q_mean, const void* k_a, const void* k_b, v
  * [flat_kv_heads, cap_blocks, D]; score = max over the group; out
  * [flat_kv_heads, sink + local + k].  out_scores (NULL or fp32, same shape) receives the score
  * of every pick (+FLT_MAX for forced blocks, -FLT_MAX for padding): a shard of a longer sequence
- * sends them to its peers so that all derive the same global top-k.  Replaces
+ * sends them to its peers so that all derive the same global top-k.  out_stride (0 = sink + local + k) is the
+ * distance between rows of out / out_scores in entries; entries past sink + local + k are padding.  Replaces
  * single_query_key_mean_topk, single_query_key_mean_topk_chunked and single_query_quest_topk
  * (bindings.cpp:205-247, block_selection.cu:127,339,450).
  */
 int ta100_select_decode(const void* q_grouped, const void* k_a, const void* k_b, void* out, void* out_scores,
                         int flat_kv_heads, int group, int nk, int cap_blocks, int head_dim, int k, int quest, int is_bf16,
-                        int sink, int local, void* stream);
+                        int sink, int local, int out_stride, void* stream);
+
+/*
+ * Decode selection with the KV sequence sharded over `world` GPUs (shard r owns pages
+ * [r * total_pages / world, (r + 1) * total_pages / world)).  Every shard calls ta100_select_decode over its
+ * own pages with out / out_scores laid out as one buffer [2, rows, width] (plane 0 ids, plane 1 scores) and
+ * all-gathers it; `gathered` is the result [world, 2, rows, width].  The union of the shards' candidates is
+ * ranked with the single-GPU key (score, then the reference's tie-break on the global page id) and the first
+ * top_k are the global selection.  out [rows, sink + local + top_k] receives shard `rank`'s part as LOCAL page
+ * ids: its forced pages first, picks at position sink + local + j when pick j lies in this shard, -1 elsewhere.
+ * world * width <= 2048.  The reference has no multi-GPU path; the merge follows the same argument as its
+ * chunked single-GPU top-k (block_selection.cu:443-447).
+ */
+int ta100_merge_page_candidates(const void* gathered, void* out, int rows, int world, int width, int rank,
+                                int total_pages, int top_k, int sink, int local, void* stream);
 
 /* Local windows: out [flat_heads, nq, k] (block_selection.cu:629) and
  * [flat_heads, k] (block_selection.cu:662); replace local_block_topk and
@@ -137,13 +152,15 @@ int ta100_pack_topk_mask(const void* sel, void* mask, long long rows, int k, int
  *   q4/qs rows layout [B*hq, sq, ..]; k4/ks rows layout with head stride kv_cap rows
  *        (k_permuted = 1 when produced with layout 1); v4t/vst transposed layout with
  *        P = ceil(kv_cap/128)*128
- *   out  [B*hq, sq, D] 16-bit
+ *   out  [B*hq, sq, D] 16-bit, or [B, sq, hq, D] with out_seq_major = 1 (the layout a Transformers
+ *        attention function returns, integrations/transformers.py:168,184,200 of the reference, which
+ *        transposes and copies instead)
  *   workspace: ta100_prefill_workspace_bytes(...) bytes, 256-byte aligned; holds
  *        re-tiled scale factors and a device status word
  *   round_partial = 1 rounds the running state to the 16-bit type between the two
  *        passes as the reference's two-kernel pipeline does
  *   max_ctas: 0 = two persistent CTAs per SM
- * sq and skv multiples of 64, head_dim 128, skv <= 131072.  causal assumes query
+ * sq and skv multiples of 64, head_dim 64 or 128, skv <= 131072.  causal assumes query
  * row r sees keys <= r.
  * Replaces fp4_attention_{causal,noncausal}_{nvfp4,mxfp4} and
  * thrift_attention_{causal,noncausal}_{nvfp4,mxfp4} (bindings.cpp:56-147; kernels
@@ -154,7 +171,7 @@ int ta100_prefill_attention(const void* q_hi, const void* k_hi, const void* v_hi
                             const void* q4, const void* k4, const void* v4t, const void* qs, const void* ks,
                             const void* vst, void* out, void* workspace, size_t workspace_bytes, int batch, int hq,
                             int hkv, int sq, int skv, int kv_cap, int head_dim, int causal, int is_mxfp4, int is_bf16,
-                            int k_permuted, int round_partial, int max_ctas, void* stream);
+                            int k_permuted, int round_partial, int max_ctas, int out_seq_major, void* stream);
 /* Synchronises `stream` and reports TA100_ERR_DEVICE_TIMEOUT if a bounded wait
  * inside the last prefill launch on this workspace gave up. */
 int ta100_prefill_status(const void* workspace, int batch, int hq, int hkv, int sq, int skv, int head_dim, int is_mxfp4,
@@ -230,11 +247,13 @@ int ta100_decode_status(void* stream);
 /*
  * Log-sum-exp merge of decode partials from `shards` producers (e.g. GPUs that each hold a slice
  * of the KV sequence): part_o [shards, flat_kv_heads, splits, group, D], part_ml [.., 2] ->
- * out [flat_kv_heads, group, D].  Same formula as the reference's in-kernel merge
- * (csrc/cuda/sm120/nvfp4/single_query_attention.cu:1562-1593).
+ * out [flat_kv_heads, group, D].  shard_stride_o / shard_stride_ml: floats between consecutive shards (0 = densely
+ * packed), so that the two arrays may be the two parts of one all-gathered buffer per shard.  Same formula as
+ * the reference's in-kernel merge (csrc/cuda/sm120/nvfp4/single_query_attention.cu:1562-1593).
  */
-int ta100_merge_partials(const void* part_o, const void* part_ml, void* out, int shards, long long flat_kv_heads,
-                         int splits, int group, int head_dim, int is_mxfp4, int is_bf16, void* stream);
+int ta100_merge_partials(const void* part_o, const void* part_ml, void* out, int shards, long long shard_stride_o,
+                         long long shard_stride_ml, long long flat_kv_heads, int splits, int group, int head_dim,
+                         int is_mxfp4, int is_bf16, void* stream);
 
 #ifdef __cplusplus
 }

@@ -274,6 +274,38 @@ def test_prefill_is_deterministic_and_reference_named_ops_agree(cuda_device):
     assert torch.equal(c, d)  # topk_count == 0 falls back to pure FP4 (bindings.cpp:525-528 of the reference)
 
 
+def test_prefill_sequence_major_output(cuda_device):
+    """out_seq_major writes [B, Sq, Hq, D] from the kernel epilogue: bit-identical to the transposed default."""
+    import thriftattention_b200 as ta
+    from thriftattention_b200.functional import attention_seq_major
+
+    torch.manual_seed(8)
+    ext = _ext()
+    for d, b, hq, hkv, S in ((128, 2, 4, 2, 512), (64, 1, 6, 3, 320)):
+        q = torch.randn(b, hq, S, d, device=cuda_device).half()
+        k = torch.randn(b, hkv, S, d, device=cuda_device).half()
+        v = torch.randn(b, hkv, S, d, device=cuda_device).half()
+        qm, _, _ = ext.block_stats(q, 64, mean=True)
+        km, _, _ = ext.block_stats(k, 64, mean=True)
+        sel = ext.block_mean_topk(qm, km, 2, True, False)
+        q4, qs = ext.nvfp4_quantize(q)
+        k4, ks = ext.nvfp4_quantize_permuted(k)
+        v4, vs = ext.nvfp4_quantize_transposed(v)
+        for args in ((q, k, v, sel), (None, None, None, None)):
+            kw = dict(causal=True, is_mx=False, block_size=64, k_permuted=True)
+            plain = ext.prefill_attention(*args, q4, k4, v4, qs, ks, vs, **kw)
+            major = ext.prefill_attention(*args, q4, k4, v4, qs, ks, vs, seq_major_out=True, **kw)
+            assert major.shape == (b, S, hq, d) and major.is_contiguous()
+            assert torch.equal(major, plain.transpose(1, 2))
+        cfg = ta.AttentionConfig(fraction=0.25)
+        assert torch.equal(attention_seq_major(q, k, v, config=cfg), ta.attention(q, k, v, config=cfg).transpose(1, 2))
+    # one query token: the sequence-major result is a view of the grouped decode output
+    q1 = torch.randn(2, 4, 1, 128, device=cuda_device).half()
+    kk = torch.randn(2, 2, 256, 128, device=cuda_device).half()
+    cfg = ta.AttentionConfig(fraction=0.5, causal=False)
+    assert torch.equal(attention_seq_major(q1, kk, kk, config=cfg), ta.attention(q1, kk, kk, config=cfg).transpose(1, 2))
+
+
 def test_public_attention_api(cuda_device):
     import thriftattention_b200 as ta
 
@@ -347,6 +379,155 @@ DECODE_CASES = [
     (torch.float16, "mxfp4", 2, 1, 4, 1024, 2, 2, 64),
     (torch.bfloat16, "mxfp4", 1, 2, 2, 512, 8, 1, 64),
 ]
+
+
+def _to_page_pools(table, n_pool, k4, ks, v4, vs, k_hi, v_hi):
+    """Scatters contiguous cache tensors into page pools addressed by ``table`` [B, pages] (64-token pages)."""
+    B, hkv, S = k4.shape[0], k4.shape[1], k4.shape[2]
+    pages = S // 64
+    flat = table.reshape(-1).long()
+
+    def rows(t):       # [B, hkv, S, X] -> pool [n_pool, hkv, 64, X]
+        pool = torch.zeros(n_pool, hkv, 64, t.shape[-1], dtype=t.dtype, device=t.device)
+        pool[flat] = t.reshape(B, hkv, pages, 64, -1).permute(0, 2, 1, 3, 4).reshape(B * pages, hkv, 64, -1)
+        return pool
+
+    def cols(t, per_page):   # [B, hkv, D, >= pages * per_page] -> pool [n_pool, hkv, D, per_page]
+        D = t.shape[2]
+        pool = torch.zeros(n_pool, hkv, D, per_page, dtype=t.dtype, device=t.device)
+        pool[flat] = (t[..., :pages * per_page].reshape(B, hkv, D, pages, per_page).permute(0, 3, 1, 2, 4)
+                      .reshape(B * pages, hkv, D, per_page))
+        return pool
+
+    group = k4.shape[-1] * 2 // ks.shape[-1]                     # elements per scale: D / scales per row
+    return rows(k4), rows(ks), cols(v4, 32), cols(vs, 64 // group), rows(k_hi), rows(v_hi)
+
+
+@pytest.mark.parametrize("dtype,fmt,B,hkv,G,S,top_k,splits,d", [
+    (torch.float16, "nvfp4", 3, 2, 4, 2048, 5, 4, 128),
+    (torch.bfloat16, "mxfp4", 2, 2, 8, 1024, 3, 0, 128),
+    (torch.float16, "mxfp4", 2, 3, 2, 1024, 0, 2, 64),
+    (torch.bfloat16, "nvfp4", 1, 2, 4, 4096, 64, 8, 64),
+])
+def test_paged_decode_equals_contiguous(cuda_device, dtype, fmt, B, hkv, G, S, top_k, splits, d):
+    """Page pools behind a seeded random page table give bit-identical results to the contiguous cache (and so
+    inherit its parity with the oracle): the table only changes where a page is fetched from."""
+    torch.manual_seed(12)
+    ext = _ext()
+    bf, mx = dtype == torch.bfloat16, fmt == "mxfp4"
+    q = torch.randn(B, hkv, G, d, device=cuda_device).to(dtype)
+    k = torch.randn(B, hkv, S, d, device=cuda_device).to(dtype)
+    v = torch.randn(B, hkv, S, d, device=cuda_device).to(dtype)
+    pages = S // 64
+    sel = None
+    if top_k:
+        _, kmin, kmax = ext.block_stats(k, 64, minmax=True)
+        sel = ext.single_query_quest_topk(q, kmin, kmax, top_k, pages, bf)
+    q4, qs = getattr(ext, f"{fmt}_quantize")(q, bf)
+    k4, ks = getattr(ext, f"{fmt}_quantize")(k, bf)
+    v4, vs = getattr(ext, f"{fmt}_quantize_transposed")(v, bf)
+    want, wo, wml = ext.decode_attention(q, k, v, sel, q4, k4, v4, qs, ks, vs, is_mx=mx, is_bf16=bf, num_splits=splits,
+                                         return_partials=True)
+    n_pool = B * pages + 7                                    # a few unused pages in the pool
+    table = torch.randperm(n_pool, device=cuda_device)[:B * pages].to(torch.int32).reshape(B, pages)
+    pk4, pks, pv4, pvs, pk, pv = _to_page_pools(table, n_pool, _u8(k4), _u8(ks), _u8(v4), _u8(vs), k, v)
+    got, go, gml = ext.decode_attention(q, pk, pv, sel, q4, pk4, pv4, qs, pks, pvs, is_mx=mx, is_bf16=bf,
+                                        num_splits=splits, kv_len=S, page_table=table, return_partials=True)
+    assert torch.equal(got, want) and torch.equal(go, wo) and torch.equal(gml, wml)
+    ext.decode_status(cuda_device)
+
+
+@pytest.mark.parametrize("world,pages,top_k,sink,local,quest", [(2, 64, 6, 1, 2, True), (4, 256, 25, 4, 16, True),
+                                                               (8, 2048, 205, 4, 16, True), (3, 100, 10, 0, 0, False),
+                                                               (4, 64, 64, 2, 3, True)])
+def test_sharded_selection_merge_equals_single_gpu(cuda_device, world, pages, top_k, sink, local, quest):
+    """The shards of a KV sequence each rank their own pages; the merge kernel over the gathered candidate buffers
+    reproduces the single-GPU selection exactly (same picks in the same order, same forced pages).  All shards are
+    emulated in one process here; the NCCL exchange itself is covered by the two-GPU test."""
+    from thriftattention_b200 import distributed as tad
+
+    torch.manual_seed(21)
+    ext = _ext()
+    B, hkv, G, d = 2, 2, 4, 128
+    rows = B * hkv
+    q = torch.randn(B, hkv, G, d, device=cuda_device).half()
+    if quest:
+        lo = torch.randn(B, hkv, pages, d, device=cuda_device).half()
+        hi = lo + torch.rand(B, hkv, pages, d, device=cuda_device).half()
+    else:
+        lo, hi = torch.randn(B, hkv, pages, d, device=cuda_device).half(), None
+    k_eff = min(top_k, pages - min(sink, pages) - min(local, pages - min(sink, pages)))
+    want = ext.select_decode_blocks(q, lo, hi, k_eff, pages, False, sink=sink, local=local)
+    shards = tad.plan_page_shards(pages, world)
+    n_sink = min(sink, pages)
+    local_lo = max(pages - local, n_sink)
+    biggest = max(s.num_pages for s in shards)
+    send = min(n_sink, biggest) + min(pages - local_lo, biggest) + min(k_eff, biggest)
+    gathered = torch.empty(world, 2, rows, send, dtype=torch.int32, device=cuda_device)
+    for s in shards:
+        my_sink = max(0, min(n_sink, s.page_end) - s.page_begin)
+        my_local = max(0, s.page_end - max(local_lo, s.page_begin))
+        cand = min(k_eff, max(s.num_pages - my_sink - my_local, 0))
+        sl = slice(s.page_begin, s.page_end)
+        ext.select_decode_blocks(q, lo[:, :, sl].contiguous(), None if hi is None else hi[:, :, sl].contiguous(), cand,
+                                 s.num_pages, False, sink=my_sink, local=my_local, out=gathered[s.rank, 0],
+                                 return_scores=True, scores_out=gathered[s.rank, 1].view(torch.float32), row_width=send)
+    picks = torch.full((rows, top_k), -1, dtype=torch.int64, device=cuda_device)
+    forced = [[] for _ in range(rows)]
+    for s in shards:
+        mine = ext.merge_page_candidates(gathered, rank=s.rank, total_pages=pages, top_k=top_k, sink=sink, local=local)
+        assert mine.shape == (rows, sink + local + top_k)
+        t = mine[:, sink + local:].long()
+        assert not ((t >= 0) & (picks >= 0)).any()              # every pick belongs to exactly one shard
+        picks = torch.where(t >= 0, t + s.page_begin, picks)
+        assert ((t < s.num_pages)).all()
+        for r in range(rows):
+            forced[r] += [int(x) + s.page_begin for x in mine[r, : sink + local].tolist() if x >= 0]
+    n_forced = n_sink + (pages - local_lo)
+    assert torch.equal(picks[:, :k_eff].cpu(), want[:, n_forced:n_forced + k_eff].long().cpu())
+    assert (picks[:, k_eff:] == -1).all()
+    for r in range(rows):
+        assert sorted(forced[r]) == sorted(want[r, :n_forced].tolist())
+
+
+def test_decode_step_replays_from_a_cuda_graph(cuda_device):
+    """Quantise q + page selection + paged attention + merge allocate nothing behind torch's back and never
+    synchronise, so one decode step can be captured once and replayed on new queries."""
+    torch.manual_seed(13)
+    ext = _ext()
+    B, hkv, G, S, d, top_k = 2, 2, 4, 4096, 128, 6
+    pages = S // 64
+    k = torch.randn(B, hkv, S, d, device=cuda_device).half()
+    v = torch.randn(B, hkv, S, d, device=cuda_device).half()
+    _, kmin, kmax = ext.block_stats(k, 64, minmax=True)
+    k4, ks = ext.nvfp4_quantize(k)
+    v4, vs = ext.nvfp4_quantize_transposed(v)
+    table = torch.randperm(B * pages, device=cuda_device).to(torch.int32).reshape(B, pages)
+    pools = _to_page_pools(table, B * pages, _u8(k4), _u8(ks), _u8(v4), _u8(vs), k, v)
+    pk4, pks, pv4, pvs, pk, pv = pools
+    q_static = torch.randn(B, hkv, G, d, device=cuda_device).half()
+
+    def step():
+        q4, qs = ext.nvfp4_quantize(q_static)
+        sel = ext.select_decode_blocks(q_static, kmin, kmax, top_k, pages, False, sink=1, local=2)
+        return ext.decode_attention(q_static, pk, pv, sel, q4, pk4, pv4, qs, pks, pvs, is_mx=False, kv_len=S,
+                                    page_table=table, allow_padded_selection=True)
+
+    side = torch.cuda.Stream(device=cuda_device)
+    side.wait_stream(torch.cuda.current_stream(cuda_device))
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step()
+    torch.cuda.current_stream(cuda_device).wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out_static = step()
+    for seed in (1, 2):
+        q_static.copy_(torch.randn(B, hkv, G, d, device=cuda_device, generator=torch.Generator(cuda_device).manual_seed(seed)).half())
+        graph.replay()
+        replayed = out_static.clone()
+        assert torch.equal(replayed, step())
+    ext.decode_status(cuda_device)
 
 
 @pytest.mark.parametrize("dtype,fmt,B,hkv,G,S,top_k,splits,d", DECODE_CASES)

@@ -174,24 +174,50 @@ def test_trim_padding_crops_only_when_padded():
 
 
 # ------------------------------------------------------------------------------------ routing rules
-def test_fast_path_output_is_transposed(registry, monkeypatch):
+def test_fast_path_output_is_sequence_major(registry, monkeypatch):
+    """The hook returns [B, S, H, D] (integrations/transformers.py:200 of the reference transposes and copies;
+    here the kernel epilogue writes that layout, so the hook hands the kernel's tensor through)."""
     for causal in (True, False):
         name = f"t_fast_{causal}"
         hf.register_transformers_attention(hf.TransformersAttentionConfig(name=name, causal=causal))
         seen = {}
+        produced = torch.arange(1 * 64 * 2 * 64, dtype=torch.float32).reshape(1, 64, 2, 64)
 
         def fake_attention(q, k, v, **kwargs):
             seen["config"] = kwargs["config"]
-            return torch.arange(1 * 2 * 64 * 64, dtype=torch.float32).reshape(1, 2, 64, 64)
+            seen["shape"] = tuple(q.shape)
+            return produced
 
         monkeypatch.setattr(hf, "_fast_path_rejection_reason", lambda *a, **k: None)
-        monkeypatch.setattr(hf, "thrift_attention", fake_attention)
+        monkeypatch.setattr(hf, "thrift_attention_seq_major", fake_attention)
         module = _module(name)
         module.is_causal = causal
         out, weights = hf.thriftattention_forward(module, *_qkv(), None, scaling=64 ** -0.5)
-        assert weights is None and out.shape == (1, 64, 2, 64) and out.is_contiguous()
-        assert torch.equal(out[0, 5, 1], torch.arange(64, dtype=torch.float32) + (1 * 64 + 5) * 64)
+        assert weights is None and out is produced and seen["shape"] == (1, 2, 64, 64)
         assert seen["config"].causal is causal and seen["config"].selection == "block_mean"
+
+
+def test_sequence_major_entry_point_shares_the_public_one(monkeypatch):
+    """attention_seq_major runs the same selection + backend call as attention, with one extra flag."""
+    from thriftattention_b200 import functional
+
+    calls = []
+
+    class Backend:
+        def attention(self, q, k, v, **kwargs):
+            calls.append(kwargs)
+            return "out"
+
+    class Policy:
+        def select(self, q, k, **kwargs):
+            return "sel"
+
+    monkeypatch.setattr(functional, "select_backend", lambda *a, **k: Backend())
+    monkeypatch.setattr(functional, "get_selection_policy", lambda name: Policy())
+    q = torch.zeros(1, 2, 64, 64, dtype=torch.float16)
+    assert functional.attention(q, q, q) == "out" and functional.attention_seq_major(q, q, q) == "out"
+    assert "seq_major_out" not in calls[0] and calls[1]["seq_major_out"] is True
+    assert calls[0]["selection"] == calls[1]["selection"] == "sel"
 
 
 def test_cached_decode_output_is_a_view_in_bshd(registry, monkeypatch):

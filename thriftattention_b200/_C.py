@@ -203,9 +203,11 @@ def quest_block_topk(q_mean, k_min, k_max, topk_count, causal=True, is_bf16=Fals
 
 
 def select_decode_blocks(q_grouped, k_a, k_b, topk_count, num_kv_blocks, is_bf16=False, sink=0, local=0, out=None,
-                         return_scores=False):
+                         return_scores=False, scores_out=None, row_width=None):
     """Decode selection; with ``return_scores`` also the fp32 score of every pick (forced blocks +FLT_MAX,
-    padding -FLT_MAX), bit-identical to what the kernel ranked by."""
+    padding -FLT_MAX), bit-identical to what the kernel ranked by.  ``out`` / ``scores_out`` let the caller
+    supply the two result buffers (e.g. the two planes of one buffer that is all-gathered afterwards);
+    ``row_width`` >= sink + local + topk_count makes the rows that wide, the tail being padding."""
     ts = [q_grouped, k_a] + ([k_b] if k_b is not None else [])
     _check(all(t.is_cuda for t in ts), "selection inputs must be CUDA tensors")
     _check(all(t.is_contiguous() for t in ts), "selection inputs must be contiguous")
@@ -221,18 +223,49 @@ def select_decode_blocks(q_grouped, k_a, k_b, topk_count, num_kv_blocks, is_bf16
     _check(0 <= num_kv_blocks <= cap, "num_kv_blocks must be in [0, key stat capacity]")
     _check(num_kv_blocks <= 2048, f"single-query block selector supports <= 2048 KV blocks, got {num_kv_blocks}")
     _check(0 <= topk_count <= num_kv_blocks, "topk_count must be in [0, num_kv_blocks]")
-    width = sink + local + topk_count
+    used = sink + local + topk_count
+    width = used if row_width is None else row_width
+    _check(width >= used, "row_width must cover sink + local + topk_count")
     if out is None:
         out = torch.empty(b * hkv, width, dtype=torch.int32, device=q_grouped.device)
-    scores = torch.empty(b * hkv, width, dtype=torch.float32, device=q_grouped.device) if return_scores else None
-    if width == 0:
+    scores = None
+    if return_scores:
+        scores = scores_out if scores_out is not None else torch.empty(b * hkv, width, dtype=torch.float32,
+                                                                      device=q_grouped.device)
+        _check(scores.is_cuda and scores.dtype == torch.float32 and scores.is_contiguous()
+               and tuple(scores.shape) == (b * hkv, width), "scores_out must be contiguous fp32 [batch * kv_heads, width]")
+    _check(out.is_cuda and out.dtype == torch.int32 and out.is_contiguous() and tuple(out.shape) == (b * hkv, width),
+           "out must be contiguous int32 [batch * kv_heads, width]")
+    if used == 0:
+        if width:
+            out.fill_(-1)
+            if scores is not None:
+                scores.fill_(-3.4028234663852886e38)
         return (out, scores) if return_scores else out
     with torch.cuda.device(q_grouped.device):
         rc = _lib.load().ta100_select_decode(_ptr(q_grouped), _ptr(k_a), _ptr(k_b), _ptr(out), _ptr(scores), b * hkv, groups,
                                              num_kv_blocks, cap, d, topk_count, int(k_b is not None), int(is_bf16),
-                                             sink, local, _stream(q_grouped))
+                                             sink, local, width, _stream(q_grouped))
     _lib.check(rc, "select_decode")
     return (out, scores) if return_scores else out
+
+
+def merge_page_candidates(gathered, *, rank, total_pages, top_k, sink=0, local=0):
+    """Global decode selection from the all-gathered candidate buffers of every KV-sequence shard.
+
+    ``gathered`` int32 ``[world, 2, rows, width]``: per shard the page ids (local to the shard) and the bit
+    patterns of their fp32 scores as written by ``select_decode_blocks(..., return_scores=True)``.  Returns int32
+    ``[rows, sink + local + top_k]`` local page ids of shard ``rank``'s part of the global selection
+    (its forced pages first, -1 where a pick belongs to another shard)."""
+    _check(gathered.is_cuda and gathered.dtype == torch.int32 and gathered.is_contiguous() and gathered.dim() == 4
+           and gathered.size(1) == 2, "gathered must be contiguous int32 [world, 2, rows, width]")
+    world, _, rows, width = gathered.shape
+    out = torch.empty(rows, sink + local + top_k, dtype=torch.int32, device=gathered.device)
+    with torch.cuda.device(gathered.device):
+        rc = _lib.load().ta100_merge_page_candidates(_ptr(gathered), _ptr(out), rows, world, width, rank, total_pages,
+                                                     top_k, sink, local, _stream(gathered))
+    _lib.check(rc, "merge_page_candidates")
+    return out
 
 
 def single_query_key_mean_topk(q_grouped, k_mean, topk_count, num_kv_blocks, is_bf16=False):
@@ -338,11 +371,13 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
 
 def prefill_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, *,
                       causal, is_mx, is_bf16=False, block_size=64, k_permuted=True, round_partial=True, max_ctas=0,
-                      check_status=False):
+                      check_status=False, seq_major_out=False):
     """Fused mixed-precision prefill attention (one kernel for the FP4 pass and the 16-bit pass).
 
     ``selected_blocks`` is ``None`` (pure FP4) or int32 ``[B*Hq, Sq/block_size, W]`` with -1
     padding.  ``k_permuted`` says whether ``k_packed`` uses the reference's row-permuted layout.
+    ``seq_major_out`` makes the kernel epilogue write ``[B, Sq, Hq, D]`` (what a Transformers attention
+    function returns) instead of ``[B, Hq, Sq, D]``.
     """
     _check_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t)
     b, hq, sq, dh = q_packed.shape
@@ -368,7 +403,8 @@ def prefill_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_p
         for t in (k_hi, v_hi):
             _check((t.is_contiguous() and t.size(2) == kv_cap) or tuple(t.stride()) == want,
                    "16-bit K/V must be contiguous or views of a cache with the packed K's capacity")
-    out = torch.empty(b, hq, sq, d, dtype=torch.bfloat16 if is_bf16 else torch.float16, device=q_packed.device)
+    out = torch.empty((b, sq, hq, d) if seq_major_out else (b, hq, sq, d),
+                      dtype=torch.bfloat16 if is_bf16 else torch.float16, device=q_packed.device)
     lib = _lib.load()
     with torch.cuda.device(out.device):
         nbytes = lib.ta100_prefill_workspace_bytes(b, hq, hkv, sq, skv, d, int(is_mx))
@@ -379,7 +415,7 @@ def prefill_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_p
             _ptr(v_hi) if sel is not None else None, _ptr(sel), width, block_size, _ptr(q_packed), _ptr(k_packed),
             _ptr(v_packed_t), _ptr(q_scale), _ptr(k_scale), _ptr(v_scale_t), _ptr(out), _ptr(ws), ws.numel(), b, hq, hkv,
             sq, skv, kv_cap, d, int(causal), int(is_mx), int(is_bf16), int(k_permuted), int(round_partial), max_ctas,
-            _stream(out))
+            int(seq_major_out), _stream(out))
         _lib.check(rc, "prefill_attention")
         if check_status:
             _lib.check(lib.ta100_prefill_status(_ptr(ws), b, hq, hkv, sq, skv, d, int(is_mx), _stream(out)),
@@ -448,10 +484,10 @@ def decode_pick_splits(flat_kv_heads: int, num_pages: int) -> int:
 
 def decode_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, *,
                      is_mx, is_bf16=False, num_splits=0, kv_len=None, page_table=None, return_partials=False,
-                     allow_padded_selection=False):
+                     allow_padded_selection=False, partials_out=None):
     """Split-KV decode attention over 64-token pages.
 
-    q_* are grouped: [B, Hkv, G, ...] with G <= 8 query heads per KV head.  K/V are either the
+    q_* are grouped: [B, Hkv, G, ...] with G <= 16 query heads per KV head.  K/V are either the
     reference's contiguous, capacity-strided cache tensors (``page_table is None``) or page pools
     ``[n_pages, Hkv, 64, ...]`` (K rows, 16-bit K/V) and ``[n_pages, Hkv, D, 32]`` (V codes) addressed
     through ``page_table`` int32 [B, max_pages].  ``selected_blocks`` is ``None`` or int32 [B*Hkv, W].
@@ -508,8 +544,16 @@ def decode_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_pa
     splits = num_splits if num_splits > 0 else lib.ta100_decode_pick_splits(b * hkv, npages)
     splits = max(1, min(splits, npages))
     out = torch.empty(b, hkv, g, d, dtype=torch.bfloat16 if is_bf16 else torch.float16, device=dev)
-    part_o = torch.empty(b * hkv, splits, g, d, dtype=torch.float32, device=dev)
-    part_ml = torch.empty(b * hkv, splits, g, 2, dtype=torch.float32, device=dev)
+    if partials_out is not None:
+        # caller-owned partials (e.g. two views of the buffer a rank all-gathers afterwards)
+        part_o, part_ml = partials_out
+        _check(tuple(part_o.shape) == (b * hkv, splits, g, d) and tuple(part_ml.shape) == (b * hkv, splits, g, 2)
+               and part_o.dtype == part_ml.dtype == torch.float32 and part_o.is_contiguous() and part_ml.is_contiguous()
+               and part_o.device == dev and part_ml.device == dev,
+               f"partials_out must be contiguous fp32 [{b * hkv}, {splits}, {g}, {d}] and [.., 2] on the query's device")
+    else:
+        part_o = torch.empty(b * hkv, splits, g, d, dtype=torch.float32, device=dev)
+        part_ml = torch.empty(b * hkv, splits, g, 2, dtype=torch.float32, device=dev)
     sel = selected_blocks if width else None
     with torch.cuda.device(dev):
         rc = lib.ta100_decode_attention(
@@ -539,14 +583,19 @@ def merge_decode_partials(part_o: torch.Tensor, part_ml: torch.Tensor, *, is_mx:
     -> [heads, G, D] 16-bit.  Same formula as the in-kernel merge of the reference
     (csrc/cuda/sm120/nvfp4/single_query_attention.cu:1562-1593).
     """
-    _check(part_o.is_cuda and part_ml.is_cuda and part_o.is_contiguous() and part_ml.is_contiguous(),
-           "partials must be contiguous CUDA tensors")
+    _check(part_o.is_cuda and part_ml.is_cuda and part_o.dim() == 5 and part_ml.dim() == 5,
+           "partials must be 5-D CUDA tensors")
+    # each shard's block must be dense; the shards themselves may be any distance apart (two views of one
+    # all-gathered buffer per shard)
+    _check(part_o[0].is_contiguous() and part_ml[0].is_contiguous(), "each shard's partials must be contiguous")
     _check(part_o.dtype == torch.float32 and part_ml.dtype == torch.float32, "partials must be float32")
     shards, heads, splits, g, d = part_o.shape
     out = torch.empty(heads, g, d, dtype=torch.bfloat16 if is_bf16 else torch.float16, device=part_o.device)
+    so = part_o.stride(0) if shards > 1 else 0
+    sml = part_ml.stride(0) if shards > 1 else 0
     with torch.cuda.device(out.device):
-        rc = _lib.load().ta100_merge_partials(_ptr(part_o), _ptr(part_ml), _ptr(out), shards, heads, splits, g, d,
-                                              int(is_mx), int(is_bf16), _stream(out))
+        rc = _lib.load().ta100_merge_partials(_ptr(part_o), _ptr(part_ml), _ptr(out), shards, so, sml, heads, splits, g,
+                                              d, int(is_mx), int(is_bf16), _stream(out))
     _lib.check(rc, "merge_partials")
     return out
 

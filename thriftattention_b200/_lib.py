@@ -22,19 +22,20 @@ SIGNATURES = {
     "ta100_block_stats": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_vp]),
     "ta100_cache_append": (_c_int, [_c_vp] * 11 + [_c_ll] + [_c_int] * 9 + [_c_vp]),
     "ta100_select_prefill": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp] + [_c_int] * 11 + [_c_vp]),
-    "ta100_select_decode": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp] + [_c_int] * 10 + [_c_vp]),
+    "ta100_select_decode": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp] + [_c_int] * 11 + [_c_vp]),
     "ta100_local_block_topk": (_c_int, [_c_vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_vp]),
     "ta100_single_query_local_topk": (_c_int, [_c_vp, _c_ll, _c_int, _c_int, _c_vp]),
     "ta100_pack_topk_mask": (_c_int, [_c_vp, _c_vp, _c_ll, _c_int, _c_int, _c_int, _c_vp]),
+    "ta100_merge_page_candidates": (_c_int, [_c_vp, _c_vp] + [_c_int] * 8 + [_c_vp]),
     "ta100_prefill_workspace_bytes": (_c_sz, [_c_int] * 7),
-    "ta100_prefill_attention": (_c_int, [_c_vp] * 4 + [_c_int, _c_int] + [_c_vp] * 8 + [_c_sz] + [_c_int] * 13 + [_c_vp]),
+    "ta100_prefill_attention": (_c_int, [_c_vp] * 4 + [_c_int, _c_int] + [_c_vp] * 8 + [_c_sz] + [_c_int] * 14 + [_c_vp]),
     "ta100_prefill_status": (_c_int, [_c_vp] + [_c_int] * 7 + [_c_vp]),
     "ta100_decode_pick_splits": (_c_int, [_c_int, _c_int]),
     "ta100_decode_workspace_bytes": (_c_sz, [_c_int] * 4),
     "ta100_decode_attention": (_c_int, [_c_vp] * 4 + [_c_int] + [_c_vp] * 7 + [_c_int] + [_c_vp] * 3 + [_c_int] * 10
                                + [_c_vp]),
     "ta100_decode_status": (_c_int, [_c_vp]),
-    "ta100_merge_partials": (_c_int, [_c_vp, _c_vp, _c_vp, _c_int, _c_ll] + [_c_int] * 5 + [_c_vp]),
+    "ta100_merge_partials": (_c_int, [_c_vp, _c_vp, _c_vp, _c_int, _c_ll, _c_ll, _c_ll] + [_c_int] * 5 + [_c_vp]),
     "ta100_decode_static_scratch_bytes": (_c_sz, []),
     "ta100_decode_attention_static": (_c_int, [_c_vp] * 4 + [_c_int] + [_c_vp] * 7 + [_c_int] + [_c_vp] + [_c_int] * 9
                                       + [_c_vp]),

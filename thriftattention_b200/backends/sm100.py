@@ -23,7 +23,9 @@ class Sm100Backend:
     name = "sm100"
 
     def attention(self, q, k, v, *, selection, quant_format: QuantFormat, config: AttentionConfig,
-                  is_bf16: bool) -> torch.Tensor:
+                  is_bf16: bool, seq_major_out: bool = False) -> torch.Tensor:
+        """``seq_major_out`` returns ``[B, Sq, Hq, D]`` straight from the kernel epilogue (tiled path) or as a
+        view (single query) instead of ``[B, Hq, Sq, D]``."""
         check_qkv(q, k, v)
         if config.block_size not in SUPPORTED_BLOCK_SIZES:
             raise NotImplementedError("the sm100 attention kernels use 64- or 128-token KV blocks")
@@ -34,8 +36,9 @@ class Sm100Backend:
         if config.method == "thrift" and selection is None:
             raise ValueError("thrift attention requires a selection tensor")
         if _use_single_query(q, config.implementation):
-            return self._single_query_attention(q, k, v, selection, quant_format, config, is_bf16)
-        return self._tiled_attention(q, k, v, selection, quant_format, config, is_bf16)
+            out = self._single_query_attention(q, k, v, selection, quant_format, config, is_bf16)
+            return out.reshape(out.shape[0], 1, out.shape[1], out.shape[3]) if seq_major_out else out
+        return self._tiled_attention(q, k, v, selection, quant_format, config, is_bf16, seq_major_out)
 
     # ------------------------------------------------------------------ decode
     def _single_query_attention(self, q, k, v, selection, quant_format, config, is_bf16):
@@ -55,7 +58,7 @@ class Sm100Backend:
         return _ungroup_single_query(out, q.shape[1])
 
     # ------------------------------------------------------------------ prefill
-    def _tiled_attention(self, q, k, v, selection, quant_format, config, is_bf16):
+    def _tiled_attention(self, q, k, v, selection, quant_format, config, is_bf16, seq_major_out=False):
         require_block_aligned("q", q.shape[2], 64)
         require_block_aligned("k", k.shape[2], config.block_size)
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
@@ -63,6 +66,12 @@ class Sm100Backend:
         ext = get_extension()
         fmt = quant_format.name
         mode = "causal" if config.causal else "noncausal"
+        if seq_major_out:
+            sel = selection if config.method == "thrift" else None
+            hi = (q, k, v) if sel is not None else (None, None, None)
+            return ext.prefill_attention(*hi, sel, *packed, causal=config.causal, is_mx=(fmt == "mxfp4"),
+                                         is_bf16=is_bf16, block_size=config.block_size, k_permuted=True,
+                                         seq_major_out=True)
         if config.method == "fp4":
             return getattr(ext, f"fp4_attention_{mode}_{fmt}_packed")(*packed, is_bf16)
         if config.block_size == 64:

@@ -10,21 +10,23 @@ int block_stats_dispatch(const void*, void*, void*, void*, long long, int, int, 
 int select_prefill_dispatch(const void*, const void*, const void*, void*, int, int, int, int, int, int, int, int, int, int,
                             int, cudaStream_t);
 int select_decode_dispatch(const void*, const void*, const void*, void*, void*, int, int, int, int, int, int, int, int, int, int,
-                           cudaStream_t);
+                           int, cudaStream_t);
+int merge_page_candidates_dispatch(const void*, void*, int, int, int, int, int, int, int, int, cudaStream_t);
 int local_prefill_dispatch(void*, long long, int, int, int, int, cudaStream_t);
 int local_decode_dispatch(void*, long long, int, int, cudaStream_t);
 int pack_mask_dispatch(const void*, void*, long long, int, int, int, cudaStream_t);
 size_t prefill_workspace_bytes(int, int, int, int, int, int, int);
 int prefill_dispatch(const void*, const void*, const void*, const void*, int, int, const void*, const void*, const void*,
                      const void*, const void*, const void*, void*, void*, size_t, int, int, int, int, int, int, int, int,
-                     int, int, int, int, int, cudaStream_t);
+                     int, int, int, int, int, int, cudaStream_t);
 int prefill_status(const void*, int, int, int, int, int, int, int, cudaStream_t);
 int decode_pick_splits(int, int);
 size_t decode_workspace_bytes(int, int, int, int);
 int decode_dispatch(const void*, const void*, const void*, const void*, int, const void*, const void*, const void*,
                     const void*, const void*, const void*, const void*, int, void*, void*, void*, int, int, int, int, int,
                     int, int, int, int, int, cudaStream_t);
-int merge_dispatch(const void*, const void*, void*, int, long long, int, int, int, int, int, cudaStream_t);
+int merge_dispatch(const void*, const void*, void*, int, long long, long long, long long, int, int, int, int, int,
+                   cudaStream_t);
 int decode_status(cudaStream_t);
 size_t decode_static_scratch_bytes();
 int decode_static_dispatch(const void*, const void*, const void*, const void*, int, const void*, const void*, const void*,
@@ -86,9 +88,15 @@ int ta100_select_prefill(const void* q_mean, const void* k_a, const void* k_b, v
 
 int ta100_select_decode(const void* q_grouped, const void* k_a, const void* k_b, void* out, void* out_scores,
                         int flat_kv_heads, int group, int nk, int cap_blocks, int head_dim, int k, int quest, int is_bf16,
-                        int sink, int local, void* stream) {
+                        int sink, int local, int out_stride, void* stream) {
     return select_decode_dispatch(q_grouped, k_a, k_b, out, out_scores, flat_kv_heads, group, nk, cap_blocks, head_dim, k,
-                                  quest, is_bf16, sink, local, S(stream));
+                                  quest, is_bf16, sink, local, out_stride, S(stream));
+}
+
+int ta100_merge_page_candidates(const void* gathered, void* out, int rows, int world, int width, int rank,
+                                int total_pages, int top_k, int sink, int local, void* stream) {
+    return merge_page_candidates_dispatch(gathered, out, rows, world, width, rank, total_pages, top_k, sink, local,
+                                          S(stream));
 }
 
 int ta100_local_block_topk(void* out, long long flat_heads, int nq, int nk, int k, int causal, void* stream) {
@@ -111,10 +119,10 @@ int ta100_prefill_attention(const void* q_hi, const void* k_hi, const void* v_hi
                             const void* q4, const void* k4, const void* v4t, const void* qs, const void* ks,
                             const void* vst, void* out, void* workspace, size_t workspace_bytes, int batch, int hq,
                             int hkv, int sq, int skv, int kv_cap, int head_dim, int causal, int is_mxfp4, int is_bf16,
-                            int k_permuted, int round_partial, int max_ctas, void* stream) {
+                            int k_permuted, int round_partial, int max_ctas, int out_seq_major, void* stream) {
     return prefill_dispatch(q_hi, k_hi, v_hi, sel, width, block, q4, k4, v4t, qs, ks, vst, out, workspace, workspace_bytes,
                             batch, hq, hkv, sq, skv, kv_cap, head_dim, causal, is_mxfp4, is_bf16, k_permuted,
-                            round_partial, max_ctas, S(stream));
+                            round_partial, max_ctas, out_seq_major, S(stream));
 }
 
 int ta100_prefill_status(const void* workspace, int batch, int hq, int hkv, int sq, int skv, int head_dim, int is_mxfp4,
@@ -140,10 +148,11 @@ int ta100_decode_attention(const void* q_hi, const void* k_hi, const void* v_hi,
 
 int ta100_decode_status(void* stream) { return decode_status(S(stream)); }
 
-int ta100_merge_partials(const void* part_o, const void* part_ml, void* out, int shards, long long flat_kv_heads,
-                         int splits, int group, int head_dim, int is_mxfp4, int is_bf16, void* stream) {
-    return merge_dispatch(part_o, part_ml, out, shards, flat_kv_heads, splits, group, head_dim, is_mxfp4, is_bf16,
-                          S(stream));
+int ta100_merge_partials(const void* part_o, const void* part_ml, void* out, int shards, long long shard_stride_o,
+                         long long shard_stride_ml, long long flat_kv_heads, int splits, int group, int head_dim,
+                         int is_mxfp4, int is_bf16, void* stream) {
+    return merge_dispatch(part_o, part_ml, out, shards, shard_stride_o, shard_stride_ml, flat_kv_heads, splits, group,
+                          head_dim, is_mxfp4, is_bf16, S(stream));
 }
 
 size_t ta100_decode_static_scratch_bytes(void) { return decode_static_scratch_bytes(); }

@@ -940,13 +940,18 @@ int decode_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const 
 }
 
 // Merge partials of `shards` ranks laid out as [shard][heads][splits][G][d] / [..][2].
-int merge_dispatch(const void* part_o, const void* part_ml, void* out, int shards, long long heads, int splits, int G, int d,
-                   int is_mx, int is_bf16, cudaStream_t stream) {
+// shard_stride_* = elements between consecutive shards (0: densely packed).
+int merge_dispatch(const void* part_o, const void* part_ml, void* out, int shards, long long shard_stride_o,
+                   long long shard_stride_ml, long long heads, int splits, int G, int d, int is_mx, int is_bf16,
+                   cudaStream_t stream) {
     if (!part_o || !part_ml || !out) return TA100_ERR_NULL;
     if (d > 128 || shards < 1 || splits < 1) return TA100_ERR_SHAPE;
     const long long rows = heads * G;
     if (rows == 0) return TA100_OK;
-    const long long so = heads * splits * G * d, sml = heads * splits * G * 2;
+    const long long dense_o = heads * splits * G * d, dense_ml = heads * splits * G * 2;
+    if ((shard_stride_o != 0 && shard_stride_o < dense_o) || (shard_stride_ml != 0 && shard_stride_ml < dense_ml))
+        return TA100_ERR_SHAPE;
+    const long long so = shard_stride_o ? shard_stride_o : dense_o, sml = shard_stride_ml ? shard_stride_ml : dense_ml;
     const int mgrid = static_cast<int>(rows < NUM_SMS_HINT * 8LL ? rows : NUM_SMS_HINT * 8LL);
     const float c = is_mx ? 6.0f : 2688.0f;
     if (is_bf16)

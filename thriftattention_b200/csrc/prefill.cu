@@ -65,6 +65,7 @@ struct PrefillParams {
     int block;      // selection block size in tokens (64 or 128)
     int width;      // entries per selection row (0: pure FP4)
     int causal, round_partial;
+    int out_seq_major;   // 0: out [B, Hq, Sq, D]; 1: out [B, Sq, Hq, D]
     int n_qtiles, n_items, nsteps_total, nkb;
     const int32_t* sel;
     const uint8_t* q_sf;
@@ -693,7 +694,9 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
             }
             if (!ok) break;
             // ---- epilogue ----
-            uint16_t* orow = p.out + (static_cast<long long>(it.h) * p.sq + grow) * D;
+            uint16_t* orow = p.out + (p.out_seq_major
+                ? ((static_cast<long long>(it.h / p.hq_per_b) * p.sq + grow) * p.hq_per_b + it.h % p.hq_per_b) * D
+                : (static_cast<long long>(it.h) * p.sq + grow) * D);
             if (n > 0) {
                 ok = mbar_wait(smem_u32(&bars.p_free[(gstep - 1) & 1]), ((gstep - 1) >> 1) & 1, abortp, budget);
                 if (!ok) break;
@@ -823,7 +826,7 @@ int prefill_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const
                      const void* q4, const void* k4, const void* v4t, const void* qs, const void* ks, const void* vst,
                      void* out, void* workspace, size_t workspace_bytes, int batch, int hq, int hkv, int sq, int skv,
                      int kv_cap, int d, int causal, int is_mx, int is_bf16, int k_permuted, int round_partial,
-                     int max_ctas, cudaStream_t stream) {
+                     int max_ctas, int out_seq_major, cudaStream_t stream) {
     if (!q4 || !k4 || !v4t || !qs || !ks || !vst || !out || !workspace) return TA100_ERR_NULL;
     if (width > 0 && (!q_hi || !k_hi || !v_hi || !sel)) return TA100_ERR_NULL;
     if (d != 128 && d != 64) return TA100_ERR_UNSUPPORTED;
@@ -907,7 +910,7 @@ int prefill_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const
     PrefillParams p;
     p.batch = batch; p.hq_per_b = hq; p.hkv_per_b = hkv; p.group = hq / hkv;
     p.sq = sq; p.skv = skv; p.block = block; p.width = width;
-    p.causal = causal; p.round_partial = round_partial;
+    p.causal = causal; p.round_partial = round_partial; p.out_seq_major = out_seq_major ? 1 : 0;
     p.n_qtiles = n_qtiles; p.n_items = n_qtiles * hq_flat; p.nsteps_total = nsteps; p.nkb = skv / block;
     p.sel = static_cast<const int32_t*>(sel);
     p.q_sf = ws + w.q_sf; p.k_sf = ws + w.k_sf; p.v_sf = ws + w.v_sf;

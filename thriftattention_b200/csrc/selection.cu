@@ -347,7 +347,8 @@ __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const ui
                                                                         const uint16_t* __restrict__ kb,
                                                                         int32_t* __restrict__ out,
                                                                         float* __restrict__ out_scores, int group, int nk,
-                                                                        int cap_blocks, int k, int sink, int local) {
+                                                                        int cap_blocks, int k, int sink, int local,
+                                                                        int out_stride) {
     using L = SeldSmem<D>;
     constexpr int VEC = D / 8;            // 16-byte chunks per statistics row
     constexpr int NARR = QUEST ? 2 : 1;
@@ -689,11 +690,12 @@ __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const ui
         sort_keys(n_sorted);
     }
 
-    int32_t* row = out + static_cast<long long>(h) * width;
+    // rows are out_stride entries apart (>= width); the tail of a wider row is padding
+    int32_t* row = out + static_cast<long long>(h) * out_stride;
     const bool pad = (sink + local) > 0;
     // optional scores of the picks (forced blocks +FLT_MAX, padding -FLT_MAX): what a shard of a longer
     // sequence sends to its peers so that all of them derive the same global top-k
-    float* srow = out_scores ? out_scores + static_cast<long long>(h) * width : nullptr;
+    float* srow = out_scores ? out_scores + static_cast<long long>(h) * out_stride : nullptr;
     for (int i = tid; i < forced; i += SELD_THREADS) {
         row[i] = i < n_sink ? i : local_lo + (i - n_sink);
         if (srow) srow[i] = FLT_MAX;
@@ -710,7 +712,7 @@ __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const ui
         row[forced + r] = id;
         if (srow) srow[forced + r] = sc;
     }
-    for (int i = forced + k + tid; i < width; i += SELD_THREADS) {
+    for (int i = forced + k + tid; i < out_stride; i += SELD_THREADS) {
         row[i] = -1;
         if (srow) srow[i] = -FLT_MAX;
     }
@@ -755,9 +757,11 @@ int select_prefill_dispatch(const void* q_mean, const void* ka, const void* kb, 
 }
 
 int select_decode_dispatch(const void* q, const void* ka, const void* kb, void* out, void* out_scores, int flat_heads, int group, int nk,
-                           int cap_blocks, int d, int k, int quest, int is_bf16, int sink, int local,
+                           int cap_blocks, int d, int k, int quest, int is_bf16, int sink, int local, int out_stride,
                            cudaStream_t stream) {
     if (!q || !ka || !out || (quest && !kb)) return TA100_ERR_NULL;
+    if (out_stride == 0) out_stride = sink + local + k;
+    if (out_stride < sink + local + k) return TA100_ERR_SHAPE;
     if (d != 64 && d != 128) return TA100_ERR_UNSUPPORTED;
     if (nk > 2048 || nk < 0 || k < 0 || nk > cap_blocks || group <= 0) return TA100_ERR_SHAPE;
     if ((sink + local) == 0 && k > nk) return TA100_ERR_SHAPE;
@@ -769,7 +773,8 @@ int select_decode_dispatch(const void* q, const void* ka, const void* kb, void* 
         cudaFuncSetAttribute(select_decode_kernel<DD, BFF, QQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
         select_decode_kernel<DD, BFF, QQ><<<flat_heads, SELD_THREADS, smem, stream>>>(                         \
             static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(ka), static_cast<const uint16_t*>(kb), \
-            static_cast<int32_t*>(out), static_cast<float*>(out_scores), group, nk, cap_blocks, k, sink, local); \
+            static_cast<int32_t*>(out), static_cast<float*>(out_scores), group, nk, cap_blocks, k, sink, local, \
+            out_stride);                                                                                       \
     } while (0)
     if (d == 128) {
         if (is_bf16) { if (quest) TA100_SELD(128, true, true); else TA100_SELD(128, true, false); }
@@ -779,6 +784,83 @@ int select_decode_dispatch(const void* q, const void* ka, const void* kb, void* 
         else { if (quest) TA100_SELD(64, false, true); else TA100_SELD(64, false, false); }
     }
 #undef TA100_SELD
+    return static_cast<int>(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------
+// KV-sequence-sharded decode: global top-k from the shards' candidate lists
+// ---------------------------------------------------------------------------
+// Every shard runs select_decode_kernel over its own pages with out_scores and all-gathers its
+// [2, rows, width] buffer (plane 0 page ids local to the shard, plane 1 fp32 scores; forced pages carry
+// +FLT_MAX, padding -1 / -FLT_MAX).  Any page of the global top-k is in its shard's top-k, so sorting the
+// union with the single-GPU key (score descending, then the tie-break rank of the GLOBAL page id) gives the
+// single-GPU selection.  One CTA per row writes this shard's part of it as local page ids:
+//   out[row] = [ this shard's forced pages | -1 ... up to sink+local | pick j if it lies in this shard else -1 ]
+// Shard r owns pages [r * total / world, (r + 1) * total / world).
+constexpr int MERGE_CAP = 2048;
+__global__ void __launch_bounds__(256)
+merge_page_candidates_kernel(const int32_t* __restrict__ gathered, int32_t* __restrict__ out, int rows, int world,
+                             int width, int rank, int total_pages, int top_k, int sink, int local) {
+    __shared__ unsigned long long keys[MERGE_CAP];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const int n = world * width;
+    int n_sorted = 2;
+    while (n_sorted < n) n_sorted <<= 1;
+    const long long plane = static_cast<long long>(rows) * width;
+    for (int i = tid; i < n_sorted; i += blockDim.x) {
+        unsigned long long key = ~0ull;
+        if (i < n) {
+            const int r = i / width, j = i - r * width;
+            const int32_t* base = gathered + static_cast<long long>(r) * 2 * plane + static_cast<long long>(row) * width + j;
+            const int page = base[0];
+            const float score = __int_as_float(base[plane]);
+            if (page >= 0 && score < FLT_MAX && score > -FLT_MAX)
+                key = seld_key(score, page + static_cast<int>(static_cast<long long>(r) * total_pages / world));
+        }
+        keys[i] = key;
+    }
+    for (int size = 2; size <= n_sorted; size <<= 1)
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            __syncthreads();
+            for (int t = tid; t < n_sorted / 2; t += blockDim.x) {
+                const int pos = 2 * t - (t & (stride - 1));
+                const unsigned long long a = keys[pos], b = keys[pos + stride];
+                const bool up = (pos & size) == 0;
+                if ((a > b) == up) { keys[pos] = b; keys[pos + stride] = a; }
+            }
+        }
+    __syncthreads();
+    const int begin = static_cast<int>(static_cast<long long>(rank) * total_pages / world);
+    const int end = static_cast<int>(static_cast<long long>(rank + 1) * total_pages / world);
+    const int out_width = sink + local + top_k;
+    int32_t* orow = out + static_cast<long long>(row) * out_width;
+    const int32_t* mine = gathered + static_cast<long long>(rank) * 2 * plane + static_cast<long long>(row) * width;
+    for (int i = tid; i < sink + local; i += blockDim.x) {
+        // this shard's forced pages lead its own list
+        const bool forced = i < width && mine[i] >= 0 && __int_as_float(mine[plane + i]) >= FLT_MAX;
+        orow[i] = forced ? mine[i] : -1;
+    }
+    for (int j = tid; j < top_k; j += blockDim.x) {
+        int32_t id = -1;
+        if (j < n_sorted && keys[j] != ~0ull) {
+            const int page = seld_key_page(keys[j]);
+            if (page >= begin && page < end) id = page - begin;
+        }
+        orow[sink + local + j] = id;
+    }
+}
+
+int merge_page_candidates_dispatch(const void* gathered, void* out, int rows, int world, int width, int rank,
+                                   int total_pages, int top_k, int sink, int local, cudaStream_t stream) {
+    if (!gathered || !out) return TA100_ERR_NULL;
+    if (rows < 0 || world <= 0 || width < 0 || rank < 0 || rank >= world || total_pages < 0 || top_k < 0 || sink < 0 ||
+        local < 0)
+        return TA100_ERR_SHAPE;
+    if (static_cast<long long>(world) * width > MERGE_CAP) return TA100_ERR_LIMIT;
+    if (rows == 0 || sink + local + top_k == 0) return TA100_OK;
+    merge_page_candidates_kernel<<<rows, 256, 0, stream>>>(static_cast<const int32_t*>(gathered),
+                                                           static_cast<int32_t*>(out), rows, world, width, rank,
+                                                           total_pages, top_k, sink, local);
     return static_cast<int>(cudaGetLastError());
 }
 

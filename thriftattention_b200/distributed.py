@@ -110,6 +110,10 @@ def plan_page_shards(num_pages: int, world: int) -> list[PageShard]:
     return [PageShard(r, world, r * num_pages // world, (r + 1) * num_pages // world) for r in range(world)]
 
 
+def _max_shard_pages(total_pages: int, world: int) -> int:
+    return max((r + 1) * total_pages // world - r * total_pages // world for r in range(world))
+
+
 def _bitrev5(x: torch.Tensor) -> torch.Tensor:
     r = torch.zeros_like(x)
     for i in range(5):
@@ -181,6 +185,20 @@ def select_pages_sharded(q_grouped, k_a, k_b, *, shard: PageShard, total_pages: 
     my_local = max(0, shard.page_end - max(local_lo, shard.page_begin))          # forced at its end
     k_glob = min(top_k, max(total_pages - n_sink - (total_pages - local_lo), 0))
     cand = min(k_glob, max(n_local - my_sink - my_local, 0))
+    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    # every rank sends a list of the same width: forced pages + candidates, padded
+    send_width = min(n_sink, _max_shard_pages(total_pages, shard.world)) + \
+        min(total_pages - local_lo, _max_shard_pages(total_pages, shard.world)) + \
+        min(k_glob, _max_shard_pages(total_pages, shard.world))
+    if q_grouped.is_cuda and world * send_width <= 2048:
+        # one buffer, one all-gather, one merge kernel
+        buf = torch.empty(2, rows, send_width, dtype=torch.int32, device=dev)
+        ext.select_decode_blocks(q_grouped, k_a, k_b, cand, n_local, q_grouped.dtype == torch.bfloat16, sink=my_sink,
+                                 local=my_local, out=buf[0], return_scores=True, scores_out=buf[1].view(torch.float32),
+                                 row_width=send_width)
+        gathered = _all_gather_stack(buf, group) if world > 1 else buf.unsqueeze(0)
+        return ext.merge_page_candidates(gathered.contiguous(), rank=shard.rank, total_pages=total_pages, top_k=top_k,
+                                         sink=sink, local=local)
     sel, scores = ext.select_decode_blocks(q_grouped, k_a, k_b, cand, n_local, q_grouped.dtype == torch.bfloat16,
                                            sink=my_sink, local=my_local, return_scores=True)
     forced = sel[:, : my_sink + my_local]
@@ -235,9 +253,41 @@ def decode_kv_sharded(q, k_local, v_local, *, shard: PageShard, total_pages: int
     q4, qs = quant(q_grouped, is_bf16)
     k4, ks = quant(k_local, is_bf16)
     v4, vs = quant_t(v_local, is_bf16)
-    _, part_o, part_ml = ext.decode_attention(q_grouped, k_local, v_local, local_sel, q4, k4, v4, qs, ks, vs,
-                                              is_mx=is_mx, is_bf16=is_bf16, num_splits=num_splits,
-                                              return_partials=True, allow_padded_selection=True)
-    all_o, all_ml = exchange_partials(part_o, part_ml, group)
-    out = ext.merge_decode_partials(all_o.contiguous(), all_ml.contiguous(), is_mx=is_mx, is_bf16=is_bf16)
+    out = decode_partials_exchange_merge(
+        lambda **kw: ext.decode_attention(q_grouped, k_local, v_local, local_sel, q4, k4, v4, qs, ks, vs, is_mx=is_mx,
+                                          is_bf16=is_bf16, allow_padded_selection=True, **kw),
+        heads=b * hkv, group_size=hq // hkv, head_dim=d, shard=shard, total_pages=total_pages, num_splits=num_splits,
+        is_mx=is_mx, is_bf16=is_bf16, device=q.device, group=group)
     return out.reshape(b, hq, 1, d)
+
+
+def sharded_splits(heads: int, shard: PageShard, total_pages: int, num_splits: int = 0) -> int:
+    """Split count used by EVERY rank of a KV-sequence-sharded decode step (the merge needs one value): the
+    kernel's own choice for the largest shard, bounded by the smallest shard's page count."""
+    from thriftattention_b200._extension import get_extension
+
+    sizes = [s.num_pages for s in plan_page_shards(total_pages, shard.world)]
+    splits = num_splits if num_splits > 0 else get_extension().decode_pick_splits(heads, max(sizes))
+    return max(1, min(splits, min(sizes)))
+
+
+def decode_partials_exchange_merge(run_decode, *, heads: int, group_size: int, head_dim: int, shard: PageShard,
+                                   total_pages: int, num_splits: int, is_mx: bool, is_bf16: bool, device, group=None):
+    """Local split-KV attention into ONE buffer per rank, ONE ``all_gather`` of it, LSE merge on every rank.
+
+    ``run_decode(num_splits=, return_partials=True, partials_out=(o, ml))`` launches the local decode kernel.
+    Returns ``[heads, group_size, head_dim]``."""
+    from thriftattention_b200._extension import get_extension
+
+    ext = get_extension()
+    splits = sharded_splits(heads, shard, total_pages, num_splits)
+    n_o, n_ml = heads * splits * group_size * head_dim, heads * splits * group_size * 2
+    flat = torch.empty(n_o + n_ml, dtype=torch.float32, device=device)
+    part_o = flat[:n_o].view(heads, splits, group_size, head_dim)
+    part_ml = flat[n_o:].view(heads, splits, group_size, 2)
+    run_decode(num_splits=splits, return_partials=True, partials_out=(part_o, part_ml))
+    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    gathered = _all_gather_stack(flat, group) if world > 1 else flat.unsqueeze(0)        # [world, n_o + n_ml]
+    all_o = gathered[:, :n_o].view(world, heads, splits, group_size, head_dim)
+    all_ml = gathered[:, n_o:].view(world, heads, splits, group_size, 2)
+    return ext.merge_decode_partials(all_o, all_ml, is_mx=is_mx, is_bf16=is_bf16)

@@ -19,6 +19,17 @@ def attention(
     config: AttentionConfig | None = None,
 ) -> torch.Tensor:
     """q [B,Hq,Sq,D], k/v [B,Hkv,Skv,D] (fp16 or bf16, CUDA) -> [B,Hq,Sq,D]."""
+    return _attention(q, k, v, config, seq_major_out=False)
+
+
+def attention_seq_major(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
+                        config: AttentionConfig | None = None) -> torch.Tensor:
+    """``attention`` with the result laid out ``[B, Sq, Hq, D]`` by the kernel itself: what the Transformers
+    hook returns (the reference transposes and copies, integrations/transformers.py:200)."""
+    return _attention(q, k, v, config, seq_major_out=True)
+
+
+def _attention(q, k, v, config, *, seq_major_out: bool) -> torch.Tensor:
     cfg = AttentionConfig() if config is None else config
     is_bf16 = q.dtype == torch.bfloat16
     quant_format = get_quant_format(cfg.quant_format)
@@ -36,7 +47,9 @@ def attention(
         )
         selection = policy.select(q, k, config=sel_cfg, causal=cfg.causal, is_bf16=is_bf16)
 
-    return backend.attention(q, k, v, selection=selection, quant_format=quant_format, config=cfg, is_bf16=is_bf16)
+    extra = {"seq_major_out": True} if seq_major_out else {}
+    return backend.attention(q, k, v, selection=selection, quant_format=quant_format, config=cfg, is_bf16=is_bf16,
+                             **extra)
 
 
 def _selection_extras(cfg: AttentionConfig) -> dict:

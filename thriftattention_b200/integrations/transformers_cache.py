@@ -522,8 +522,9 @@ def cached_decode_attention(query: torch.Tensor, cache: ThriftAttentionCache, la
 
 
 def cached_prefill_attention(query: torch.Tensor, cache: ThriftAttentionCache, layer_idx: int,
-                             config: AttentionConfig) -> torch.Tensor:
-    """Prefill ``[B, Hq, Sq, D]`` against the K/V that ``update`` has just stored in layer ``layer_idx``.
+                             config: AttentionConfig, *, seq_major_out: bool = False) -> torch.Tensor:
+    """Prefill ``[B, Hq, Sq, D]`` against the K/V that ``update`` has just stored in layer ``layer_idx``;
+    the result is ``[B, Hq, Sq, D]``, or ``[B, Sq, Hq, D]`` with ``seq_major_out``.
 
     The reference re-quantises the whole K and V into the tiled kernel's own layouts here
     (transformers_cache.py:622-680).  The sm_100a prefill kernel reads plain K rows and capacity
@@ -539,6 +540,8 @@ def cached_prefill_attention(query: torch.Tensor, cache: ThriftAttentionCache, l
     ext = get_extension()
     common = dict(causal=config.causal, is_mx=quant_format.name == "mxfp4", is_bf16=is_bf16,
                   block_size=config.block_size, k_permuted=False)
+    if seq_major_out:
+        common["seq_major_out"] = True
 
     if config.method == "fp4":
         return ext.prefill_attention(None, None, None, None, q_packed, k_packed, v_packed_t, q_scale, k_scale,
