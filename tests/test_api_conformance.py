@@ -209,3 +209,17 @@ def test_selection_policies_route_by_query_length(monkeypatch):
     assert [c[0] for c in calls] == ["select_block_pairs", "select_key_blocks", "select_quest_block_pairs",
                                      "select_quest_key_blocks", "select_local_block_pairs", "select_local_key_blocks"]
     assert calls[0][1]["causal"] is True and "causal" not in calls[1][1]
+
+
+def test_attention_host_argument_errors():
+    """The host-side entry point validates shapes before it touches CUDA."""
+    import thriftattention_b200 as ta
+
+    q = torch.zeros(1, 4, 64, 128, dtype=torch.float16)
+    k = torch.zeros(1, 3, 64, 128, dtype=torch.float16)
+    with pytest.raises(ValueError, match="multiple of the number of KV heads"):
+        ta.attention_host(q, k, k)
+    with pytest.raises(ValueError, match="expects q"):
+        ta.attention_host(q, k, k[:, :2])
+    with pytest.raises(ValueError, match="kv_heads_per_chunk"):
+        ta.attention_host(q, k[:, :2], k[:, :2], kv_heads_per_chunk=0)

@@ -68,10 +68,10 @@ def _tiny_llama(name):
     return transformers.LlamaForCausalLM(cfg).half().eval().to(DEV)
 
 
-def test_llama_prefill_and_decode_through_the_hook():
+def _hook_against_oracle(model_factory, hook_name, fraction, vocab, prompt_len, new_tokens, padding, layers):
     from thriftattention_b200._extension import get_extension
 
-    name = register_transformers_attention(TransformersAttentionConfig(name="thrift_hf_test", fraction=0.25))
+    name = register_transformers_attention(TransformersAttentionConfig(name=hook_name, fraction=fraction))
     transformers.AttentionInterface.register("thrift_oracle_test", _oracle_forward)
     try:
         from transformers import AttentionMaskInterface
@@ -80,14 +80,13 @@ def test_llama_prefill_and_decode_through_the_hook():
         AttentionMaskInterface.register("thrift_oracle_test", sdpa_mask)
     except ImportError:
         pass
-    model = _tiny_llama(name)
-    prompt_len, new_tokens = 300, 3
-    ids = torch.randint(0, 512, (1, prompt_len), generator=torch.Generator().manual_seed(1)).to(DEV)
+    model = model_factory(name)
+    ids = torch.randint(0, vocab, (1, prompt_len), generator=torch.Generator().manual_seed(1)).to(DEV)
 
     # ---------------- run A: the registered sm_100a path over a ThriftAttentionCache
     prep = prepare_transformers_generation_cache(model, ids, max_new_tokens=new_tokens)
-    assert (prep.padding, prep.padded_length) == (20, 320)
-    count = resolve_top_k(300 // 64, causal=True, fraction=0.25)
+    assert (prep.padding, prep.padded_length) == (padding, prompt_len + padding)
+    count = resolve_top_k(prompt_len // 64, causal=True, fraction=fraction)
     assert prep.config.top_k == count
     logits_a, tokens = [], []
     with prep.activate(), torch.no_grad():
@@ -103,7 +102,7 @@ def test_llama_prefill_and_decode_through_the_hook():
                         cache_position=torch.tensor([pos], device=DEV), use_cache=True)
             logits_a.append(out.logits[:, -1].float().cpu())
         assert prep.past_key_values.get_seq_length() == prompt_len + new_tokens
-        assert len(prep.past_key_values) == 2
+        assert len(prep.past_key_values) == layers
 
     # ---------------- run B: same weights, attention computed by the CPU oracle over a plain dynamic cache
     _ORACLE_STATE.update(config=prep.config, real_q_len=prompt_len, pick_splits=get_extension().decode_pick_splits)
@@ -127,6 +126,28 @@ def test_llama_prefill_and_decode_through_the_hook():
         assert torch.nn.functional.cosine_similarity(a, b).item() > 0.9995
 
 
+def test_llama_prefill_and_decode_through_the_hook():
+    _hook_against_oracle(_tiny_llama, "thrift_hf_test", 0.25, 512, 300, 3, 20, 2)
+
+
+def _llama3_8b_shaped(name):
+    """Two decoder layers with the Llama-3-8B shape: d_model 4096, 32 q / 8 kv heads x 128, SwiGLU 14336,
+    RoPE theta 5e5, vocab 128256, fp16, random init."""
+    cfg = transformers.LlamaConfig(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=2,
+                                   num_attention_heads=32, num_key_value_heads=8, head_dim=128, rope_theta=500000.0,
+                                   max_position_embeddings=8192, tie_word_embeddings=False)
+    cfg._attn_implementation = name
+    torch.manual_seed(0)
+    with torch.device(DEV):
+        return transformers.LlamaForCausalLM(cfg).half().eval()
+
+
+def test_llama3_8b_shaped_layers_through_the_hook():
+    """The Llama-3-8B layer shape, a 4096-token prompt (no padding) and three decode steps, NVFP4 with the top 10 %
+    of the key blocks in fp16: logits against the same weights with the CPU oracle as the attention function."""
+    _hook_against_oracle(_llama3_8b_shaped, "thrift_hf_8b_shape", 0.10, 128256, 4096, 3, 0, 2)
+
+
 def test_hook_rejects_what_the_kernels_cannot_serve():
     name = register_transformers_attention(TransformersAttentionConfig(name="thrift_hf_reject"))
     module = type("M", (), {})()
@@ -144,54 +165,3 @@ def test_hook_rejects_what_the_kernels_cannot_serve():
     assert out.shape == (1, 128, 4, 128) and weights is None and torch.isfinite(out).all()
 
 
-def test_llama3_8b_shaped_layers_against_exact_attention():
-    """Two decoder layers with the Llama-3-8B shape (d_model 4096, 32 q / 8 kv heads x 128, SwiGLU 14336, RoPE theta
-    5e5, vocab 128256, fp16, random init) run a 4096-token prefill and four greedy decode steps through the
-    registered hook (NVFP4, Quest top-10 % + 1 sink + 2 recent blocks), and the same weights are run with
-    Transformers' own exact attention.  The mixed-precision logits stay within cosine 0.999 of the exact ones."""
-    name = register_transformers_attention(TransformersAttentionConfig(
-        name="thrift_hf_8b_shape", selection="quest", fraction=0.10, sink_blocks=1, local_blocks=2))
-    cfg = transformers.LlamaConfig(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=2,
-                                   num_attention_heads=32, num_key_value_heads=8, head_dim=128, rope_theta=500000.0,
-                                   max_position_embeddings=8192, tie_word_embeddings=False)
-    cfg._attn_implementation = name
-    torch.manual_seed(0)
-    with torch.device(DEV):
-        model = transformers.LlamaForCausalLM(cfg).half().eval()
-    prompt_len, new_tokens = 4096, 4
-    ids = torch.randint(0, 128256, (1, prompt_len), generator=torch.Generator().manual_seed(2)).to(DEV)
-
-    def run(use_hook):
-        logits, tokens = [], []
-        with torch.no_grad():
-            if use_hook:
-                model.config._attn_implementation = name
-                prep = prepare_transformers_generation_cache(model, ids, max_new_tokens=new_tokens)
-                assert prep.padding == 0
-                ctx, cache, inputs, pos0 = prep.activate(), prep.past_key_values, prep.input_ids, prep.cache_position
-            else:
-                import contextlib
-
-                model.config._attn_implementation = "sdpa"
-                ctx, cache, inputs = contextlib.nullcontext(), transformers.DynamicCache(config=model.config), ids
-                pos0 = torch.arange(prompt_len, device=DEV)
-            with ctx:
-                out = model(input_ids=inputs, past_key_values=cache, cache_position=pos0, use_cache=True, logits_to_keep=1)
-                logits.append(out.logits[:, -1].float())
-                for step in range(new_tokens):
-                    tok = _TOKENS[step] if not use_hook else int(logits[-1].argmax())
-                    tokens.append(tok)
-                    out = model(input_ids=torch.tensor([[tok]], device=DEV), past_key_values=cache,
-                                cache_position=torch.tensor([prompt_len + step], device=DEV), use_cache=True)
-                    logits.append(out.logits[:, -1].float())
-        return logits, tokens
-
-    mixed, toks = run(True)
-    _TOKENS[:] = toks
-    exact, _ = run(False)
-    for a, b in zip(mixed, exact):
-        assert torch.isfinite(a).all()
-        assert torch.nn.functional.cosine_similarity(a, b).item() > 0.999
-
-
-_TOKENS: list = []

@@ -306,6 +306,29 @@ def test_prefill_sequence_major_output(cuda_device):
     assert torch.equal(attention_seq_major(q1, kk, kk, config=cfg), ta.attention(q1, kk, kk, config=cfg).transpose(1, 2))
 
 
+def test_attention_host_pipelines_head_groups(cuda_device):
+    """Host tensors in, host tensor out, one KV-head group at a time on three streams: the result equals the
+    device-resident call bit for bit, for every chunking."""
+    import thriftattention_b200 as ta
+
+    torch.manual_seed(14)
+    q = torch.randn(2, 8, 512, 128).half().pin_memory()
+    k = torch.randn(2, 4, 512, 128).half().pin_memory()
+    v = torch.randn(2, 4, 512, 128).half().pin_memory()
+    cfg = ta.AttentionConfig(selection="quest", fraction=0.25)
+    want = ta.attention(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), config=cfg).cpu()
+    for per_chunk in (1, 3, 4):
+        got = ta.attention_host(q, k, v, config=cfg, device=cuda_device, kv_heads_per_chunk=per_chunk)
+        torch.cuda.synchronize(cuda_device)
+        assert got.is_pinned() and torch.equal(got, want)
+    out = torch.zeros_like(want).pin_memory()
+    assert ta.attention_host(q, k, v, config=cfg, device=cuda_device, out=out) is out
+    torch.cuda.synchronize(cuda_device)
+    assert torch.equal(out, want)
+    with pytest.raises(ValueError, match="host tensors"):
+        ta.attention_host(q.to(cuda_device), k, v, config=cfg)
+
+
 def test_public_attention_api(cuda_device):
     import thriftattention_b200 as ta
 

@@ -7,12 +7,14 @@ the first operator is called.
 """
 from .config import AttentionConfig
 from .functional import attention
+from .offload import attention_host
 from .quant import QuantFormat, get_quant_format
 from .selection import SelectionConfig, get_selection_policy, resolve_top_k
 
 __all__ = [
     "AttentionConfig",
     "attention",
+    "attention_host",
     "ThriftAttentionCache",
     "QuantFormat",
     "get_quant_format",
