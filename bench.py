@@ -220,11 +220,43 @@ def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_g
     for _ in range(max(warmup, 3)):
         step()
     barrier()
+    _C.decode_status()
+    # A decode step is a fixed sequence of kernels and (N > 1) two all-gathers with no host decision in between,
+    # so it is captured once and replayed: what is timed is the device work, not the Python that queues it.
+    # Falls back to queueing the step eagerly where the capture is refused.
+    run, mode = step, "eager"
+    if os.environ.get("TA100_BENCH_DECODE_GRAPH", "1") != "0":
+        try:
+            side = torch.cuda.Stream(device=device)
+            side.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(side):
+                step()
+            torch.cuda.current_stream(device).wait_stream(side)
+            barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            barrier()
+            graph.replay()
+            barrier()
+            run, mode = graph.replay, "cuda graph"
+        except Exception as exc:                                  # noqa: BLE001 - any refusal means eager
+            if rank == 0:
+                print(f"decode step not captured ({type(exc).__name__}: {exc}); timing eager launches", file=sys.stderr)
+            torch.cuda.synchronize()
+            run, mode = step, "eager"
+    if world > 1:
+        # every rank must time the same way, or the replays and the eager collectives would interleave
+        flag = torch.tensor([1 if mode == "cuda graph" else 0], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if flag.item() == 0:
+            run, mode = step, "eager"
+    barrier()
     n_steps = max(steps, 5) * 4
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(n_steps):
-        step()
+        run()
     e1.record()
     barrier()
     _C.decode_status()
@@ -239,7 +271,7 @@ def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_g
             "workload": f"paged decode {DEC_BATCH} seq x {DEC_SEQ} tokens, {HQ}q/{HKV}kv x {D}, NVFP4 + fp16 shadow, Quest "
                         f"{top_k} + {DEC_SINK} sink + {DEC_LOCAL} recent of {pages} pages in 16 bits; step = select + "
                         f"attend + merge; KV sequence split over {world} GPU(s)",
-            "launches_per_step": 4 if world == 1 else 5}
+            "launches_per_step": 4 if world == 1 else 5, "queued_as": mode}
 
 
 # ------------------------------------------------------------------------- small cases for profiler captures
