@@ -271,7 +271,7 @@ def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_g
             "workload": f"paged decode {DEC_BATCH} seq x {DEC_SEQ} tokens, {HQ}q/{HKV}kv x {D}, NVFP4 + fp16 shadow, Quest "
                         f"{top_k} + {DEC_SINK} sink + {DEC_LOCAL} recent of {pages} pages in 16 bits; step = select + "
                         f"attend + merge; KV sequence split over {world} GPU(s)",
-            "launches_per_step": 4 if world == 1 else 5, "queued_as": mode}
+            "launches_per_step": 4 if world == 1 else 6, "queued_as": mode}
 
 
 # ------------------------------------------------------------------------- small cases for profiler captures

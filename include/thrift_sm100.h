@@ -255,6 +255,16 @@ int ta100_merge_partials(const void* part_o, const void* part_ml, void* out, int
                          long long shard_stride_ml, long long flat_kv_heads, int splits, int group, int head_dim,
                          int is_mxfp4, int is_bf16, void* stream);
 
+/*
+ * The merge of one producer's chains that stays a partial: part_o [flat_kv_heads, splits, group, D],
+ * part_ml [.., 2] -> out_o [flat_kv_heads, 1, group, D] (fp32, units of C), out_ml [flat_kv_heads, 1, group, 2]
+ * (row maximum, row sum), i.e. the same arrays with splits = 1.  A GPU that holds a slice of the KV sequence
+ * reduces its own chains with this before the exchange, so that the bytes it sends do not grow with its chain
+ * count; ta100_merge_partials(shards = N, splits = 1) finishes.  No counterpart in the reference (single GPU).
+ */
+int ta100_reduce_partials(const void* part_o, const void* part_ml, void* out_o, void* out_ml, long long flat_kv_heads,
+                          int splits, int group, int head_dim, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

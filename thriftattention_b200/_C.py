@@ -576,6 +576,28 @@ def decode_status(device=None) -> None:
     _lib.check(rc, "decode_attention (device)")
 
 
+def reduce_decode_partials(part_o: torch.Tensor, part_ml: torch.Tensor, out=None):
+    """One producer's chains reduced to a single partial per head: ``[heads, splits, G, D]`` / ``[.., 2]`` ->
+    ``[heads, 1, G, D]`` / ``[heads, 1, G, 2]`` (fp32; same meaning as the inputs).  ``out`` = the two result
+    tensors, e.g. two views of the buffer that is all-gathered next."""
+    _check(part_o.is_cuda and part_ml.is_cuda and part_o.is_contiguous() and part_ml.is_contiguous()
+           and part_o.dim() == 4 and part_ml.dim() == 4, "partials must be contiguous 4-D CUDA tensors")
+    _check(part_o.dtype == torch.float32 and part_ml.dtype == torch.float32, "partials must be float32")
+    heads, splits, g, d = part_o.shape
+    if out is None:
+        out = (torch.empty(heads, 1, g, d, dtype=torch.float32, device=part_o.device),
+               torch.empty(heads, 1, g, 2, dtype=torch.float32, device=part_o.device))
+    out_o, out_ml = out
+    _check(tuple(out_o.shape) == (heads, 1, g, d) and tuple(out_ml.shape) == (heads, 1, g, 2) and out_o.is_contiguous()
+           and out_ml.is_contiguous() and out_o.dtype == out_ml.dtype == torch.float32,
+           "out must be contiguous fp32 [heads, 1, G, D] and [heads, 1, G, 2]")
+    with torch.cuda.device(part_o.device):
+        rc = _lib.load().ta100_reduce_partials(_ptr(part_o), _ptr(part_ml), _ptr(out_o), _ptr(out_ml), heads, splits, g, d,
+                                               _stream(part_o))
+    _lib.check(rc, "reduce_partials")
+    return out_o, out_ml
+
+
 def merge_decode_partials(part_o: torch.Tensor, part_ml: torch.Tensor, *, is_mx: bool, is_bf16: bool = False):
     """LSE merge of decode partials gathered from several shards.
 

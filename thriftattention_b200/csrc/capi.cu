@@ -27,6 +27,7 @@ int decode_dispatch(const void*, const void*, const void*, const void*, int, con
                     int, int, int, int, int, cudaStream_t);
 int merge_dispatch(const void*, const void*, void*, int, long long, long long, long long, int, int, int, int, int,
                    cudaStream_t);
+int reduce_partials_dispatch(const void*, const void*, void*, void*, long long, int, int, int, cudaStream_t);
 int decode_status(cudaStream_t);
 size_t decode_static_scratch_bytes();
 int decode_static_dispatch(const void*, const void*, const void*, const void*, int, const void*, const void*, const void*,
@@ -153,6 +154,11 @@ int ta100_merge_partials(const void* part_o, const void* part_ml, void* out, int
                          int is_mxfp4, int is_bf16, void* stream) {
     return merge_dispatch(part_o, part_ml, out, shards, shard_stride_o, shard_stride_ml, flat_kv_heads, splits, group,
                           head_dim, is_mxfp4, is_bf16, S(stream));
+}
+
+int ta100_reduce_partials(const void* part_o, const void* part_ml, void* out_o, void* out_ml, long long flat_kv_heads,
+                          int splits, int group, int head_dim, void* stream) {
+    return reduce_partials_dispatch(part_o, part_ml, out_o, out_ml, flat_kv_heads, splits, group, head_dim, S(stream));
 }
 
 size_t ta100_decode_static_scratch_bytes(void) { return decode_static_scratch_bytes(); }

@@ -780,6 +780,30 @@ __global__ void __launch_bounds__(128) merge_kernel(const float* __restrict__ pa
     }
 }
 
+// The same merge, but the result stays a partial: (sum_s O_s e^{m_s - M}, M, sum_s l_s e^{m_s - M}) as one split
+// per head.  A rank of a KV-sequence-sharded step reduces its own chains with this before the exchange, so that
+// what crosses NVLink does not grow with the number of chains.
+__global__ void __launch_bounds__(128) reduce_partials_kernel(const float* __restrict__ part_o,
+                                                              const float* __restrict__ part_ml,
+                                                              float* __restrict__ out_o, float* __restrict__ out_ml,
+                                                              int splits, int G, int d, long long rows) {
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        const long long head = row / G;
+        const int g = static_cast<int>(row - head * G);
+        float M = -FLT_MAX;
+        for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[((head * splits + s) * G + g) * 2]);
+        float den = 0.0f, acc = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const long long i = (head * splits + s) * G + g;
+            const float w = __expf(part_ml[i * 2] - M);
+            den = fmaf(part_ml[i * 2 + 1], w, den);
+            if (threadIdx.x < d) acc = fmaf(part_o[i * d + threadIdx.x], w, acc);
+        }
+        if (threadIdx.x < d) out_o[row * d + threadIdx.x] = acc;
+        if (threadIdx.x == 0) { out_ml[row * 2] = M; out_ml[row * 2 + 1] = den; }
+    }
+}
+
 }  // namespace
 
 // Chains per (sequence, KV head): enough CTAs to fill the GPU (two per SM) in whole waves.
@@ -960,6 +984,20 @@ int merge_dispatch(const void* part_o, const void* part_ml, void* out, int shard
     else
         merge_kernel<false><<<mgrid, 128, 0, stream>>>(static_cast<const float*>(part_o), static_cast<const float*>(part_ml),
                                                        static_cast<uint16_t*>(out), shards, so, sml, splits, G, d, rows, c);
+    return static_cast<int>(cudaGetLastError());
+}
+
+// Reduce the chains of every head to one partial per head: part_o [heads][splits][G][d] -> out_o [heads][1][G][d].
+int reduce_partials_dispatch(const void* part_o, const void* part_ml, void* out_o, void* out_ml, long long heads,
+                             int splits, int G, int d, cudaStream_t stream) {
+    if (!part_o || !part_ml || !out_o || !out_ml) return TA100_ERR_NULL;
+    if (d > 128 || d < 1 || splits < 1 || G < 1 || heads < 0) return TA100_ERR_SHAPE;
+    const long long rows = heads * G;
+    if (rows == 0) return TA100_OK;
+    const int grid = static_cast<int>(rows < NUM_SMS_HINT * 8LL ? rows : NUM_SMS_HINT * 8LL);
+    reduce_partials_kernel<<<grid, 128, 0, stream>>>(static_cast<const float*>(part_o), static_cast<const float*>(part_ml),
+                                                     static_cast<float*>(out_o), static_cast<float*>(out_ml), splits, G, d,
+                                                     rows);
     return static_cast<int>(cudaGetLastError());
 }
 

@@ -261,33 +261,26 @@ def decode_kv_sharded(q, k_local, v_local, *, shard: PageShard, total_pages: int
     return out.reshape(b, hq, 1, d)
 
 
-def sharded_splits(heads: int, shard: PageShard, total_pages: int, num_splits: int = 0) -> int:
-    """Split count used by EVERY rank of a KV-sequence-sharded decode step (the merge needs one value): the
-    kernel's own choice for the largest shard, bounded by the smallest shard's page count."""
-    from thriftattention_b200._extension import get_extension
-
-    sizes = [s.num_pages for s in plan_page_shards(total_pages, shard.world)]
-    splits = num_splits if num_splits > 0 else get_extension().decode_pick_splits(heads, max(sizes))
-    return max(1, min(splits, min(sizes)))
-
-
 def decode_partials_exchange_merge(run_decode, *, heads: int, group_size: int, head_dim: int, shard: PageShard,
                                    total_pages: int, num_splits: int, is_mx: bool, is_bf16: bool, device, group=None):
-    """Local split-KV attention into ONE buffer per rank, ONE ``all_gather`` of it, LSE merge on every rank.
+    """Local split-KV attention, the rank's chains reduced to one partial per head, ONE ``all_gather`` of that
+    buffer, LSE merge on every rank.
 
-    ``run_decode(num_splits=, return_partials=True, partials_out=(o, ml))`` launches the local decode kernel.
-    Returns ``[heads, group_size, head_dim]``."""
+    ``run_decode(num_splits=, return_partials=True)`` launches the local decode kernel and returns
+    ``(out, part_o, part_ml)``; every rank may use its own chain count.  Returns ``[heads, group_size, head_dim]``."""
     from thriftattention_b200._extension import get_extension
 
     ext = get_extension()
-    splits = sharded_splits(heads, shard, total_pages, num_splits)
-    n_o, n_ml = heads * splits * group_size * head_dim, heads * splits * group_size * 2
-    flat = torch.empty(n_o + n_ml, dtype=torch.float32, device=device)
-    part_o = flat[:n_o].view(heads, splits, group_size, head_dim)
-    part_ml = flat[n_o:].view(heads, splits, group_size, 2)
-    run_decode(num_splits=splits, return_partials=True, partials_out=(part_o, part_ml))
     world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    # this rank's chains are reduced to one partial per head first: the exchange then carries
+    # heads x G x (D + 2) floats per rank whatever the chain count
+    n_o, n_ml = heads * group_size * head_dim, heads * group_size * 2
+    flat = torch.empty(n_o + n_ml, dtype=torch.float32, device=device)
+    mine_o = flat[:n_o].view(heads, 1, group_size, head_dim)
+    mine_ml = flat[n_o:].view(heads, 1, group_size, 2)
+    _, part_o, part_ml = run_decode(num_splits=num_splits, return_partials=True)
+    ext.reduce_decode_partials(part_o, part_ml, out=(mine_o, mine_ml))
     gathered = _all_gather_stack(flat, group) if world > 1 else flat.unsqueeze(0)        # [world, n_o + n_ml]
-    all_o = gathered[:, :n_o].view(world, heads, splits, group_size, head_dim)
-    all_ml = gathered[:, n_o:].view(world, heads, splits, group_size, 2)
+    all_o = gathered[:, :n_o].view(world, heads, 1, group_size, head_dim)
+    all_ml = gathered[:, n_o:].view(world, heads, 1, group_size, 2)
     return ext.merge_decode_partials(all_o, all_ml, is_mx=is_mx, is_bf16=is_bf16)
