@@ -328,6 +328,64 @@ def run_small_case(kind: str) -> None:
                       "selection_bytes_per_launch": batch * HKV * pages * 512}))
 
 
+def run_sweep() -> None:
+    """Secondary measurements on one GPU, one JSON line each (not the headline; `python bench.py --sweep`):
+    the long-context MXFP4 / bf16 prefill with 5, 10 and 25 % of the 128-token blocks in 16 bits, the 32k NVFP4
+    prefill, and the HBM-bound helper kernels (quantisers, block statistics) as GB/s of algorithmic bytes."""
+    from thriftattention_b200 import _C
+    from thriftattention_b200.selection import resolve_top_k
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    hbm = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else 6650.0
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    for fmt, dtype, seq, fractions in (("mxfp4", torch.bfloat16, SEQ, (0.05, 0.10, 0.25)),
+                                       ("nvfp4", torch.float16, 32768, (0.10,))):
+        bf16, mx = dtype == torch.bfloat16, fmt == "mxfp4"
+        q, k, v = make_inputs(HQ, HKV, seq, device, dtype)
+        q_mean, _, _ = _C.block_stats(q, BLOCK, mean=True)
+        _, k_min, k_max = _C.block_stats(k, BLOCK, minmax=True)
+        q4, qs = getattr(_C, f"{fmt}_quantize")(q, bf16)
+        k4, ks = getattr(_C, f"{fmt}_quantize_permuted")(k, bf16)
+        v4, vs = getattr(_C, f"{fmt}_quantize_transposed")(v, bf16)
+        flops = algorithmic_flops(HQ, seq, D, BLOCK)
+        for fraction in fractions:
+            top_k = resolve_top_k(seq // BLOCK, causal=True, fraction=fraction)
+            sel = _C.quest_block_topk(q_mean, k_min, k_max, top_k, True, bf16)
+            ms = timed(lambda: _C.prefill_attention(q, k, v, sel, q4, k4, v4, qs, ks, vs, causal=True, is_mx=mx,
+                                                    is_bf16=bf16, block_size=BLOCK, k_permuted=True), 2 if seq > 65536 else 5)
+            print(json.dumps({"case": f"prefill_kernel 1x{HQ}q/{HKV}kv x{seq} x{D} {'bf16' if bf16 else 'fp16'} {fmt}, "
+                                      f"Quest top-{fraction:.0%} ({top_k} blocks of {BLOCK})", "ms": ms,
+                              "tflops": flops / ms / 1e9}), flush=True)
+        # helper kernels on this K / V: algorithmic bytes = 16-bit input + codes + scale bytes
+        elems = k.numel()
+        group = 32 if mx else 16
+        qbytes = elems * (2 + 0.5 + 1.0 / group)
+        for name, fn, nbytes in (
+                (f"{fmt}_quantize (rows)", lambda: getattr(_C, f"{fmt}_quantize")(k, bf16), qbytes),
+                (f"{fmt}_quantize_permuted", lambda: getattr(_C, f"{fmt}_quantize_permuted")(k, bf16), qbytes),
+                (f"{fmt}_quantize_transposed", lambda: getattr(_C, f"{fmt}_quantize_transposed")(v, bf16), qbytes),
+                ("block_stats min/max", lambda: _C.block_stats(k, BLOCK, minmax=True), elems * 2.0)):
+            ms = timed(fn, 10)
+            print(json.dumps({"case": f"{name} of [1,{HKV},{seq},{D}]", "us": ms * 1e3, "gbs": nbytes / ms / 1e6,
+                              "frac_of_hbm_peak": nbytes / ms / 1e6 / hbm}), flush=True)
+        del q, k, v, q4, k4, v4, qs, ks, vs
+        torch.cuda.empty_cache()
+
+
 def run_ours(args) -> dict:
     import torch.distributed as dist
 
@@ -489,7 +547,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--small", choices=["prefill", "decode"], default=None,
                     help="run a small case of one kernel three times (for profiler captures) and exit")
+    ap.add_argument("--sweep", action="store_true",
+                    help="secondary single-GPU measurements (MXFP4 top-k sweep, 32k prefill, quantiser bandwidth)")
     args = ap.parse_args()
+    if args.sweep:
+        run_sweep()
+        return
     if args.small:
         run_small_case(args.small)
         return
