@@ -250,6 +250,26 @@ def test_prefill_attention_head_dim_64(cuda_device, dtype, fmt, block, S, hq, hk
     _prefill_case(cuda_device, dtype, fmt, block, S, hq, hkv, frac, causal, kperm, d=64)
 
 
+def _seeded_prefill_configs(n):
+    rng = torch.Generator().manual_seed(2024)
+    pick = lambda seq: seq[int(torch.randint(0, len(seq), (1,), generator=rng))]
+    out = []
+    for _ in range(n):
+        hkv = pick((1, 2, 3))
+        out.append((pick((torch.float16, torch.bfloat16)), pick(("nvfp4", "mxfp4")), pick((64, 128)),
+                    128 * int(torch.randint(1, 11, (1,), generator=rng)), hkv * pick((1, 2, 4)), hkv,
+                    pick((0.0, 0.1, 0.3, 1.0)), pick((True, False)), pick((True, False)), pick((64, 128))))
+    return out
+
+
+@pytest.mark.parametrize("idx,cfg", list(enumerate(_seeded_prefill_configs(16))))
+def test_prefill_seeded_random_shapes(cuda_device, idx, cfg):
+    """Sixteen configurations drawn from a fixed seed (dtype, format, block size, 128..1280 tokens, head counts,
+    selected fraction, causal, K layout, head_dim), each against the oracle."""
+    dtype, fmt, block, S, hq, hkv, frac, causal, kperm, d = cfg
+    _prefill_case(cuda_device, dtype, fmt, block, S, hq, hkv, frac, causal, kperm, seed=100 + idx, outlier=idx % 2 == 0, d=d)
+
+
 def test_prefill_noncausal_rectangular(cuda_device):
     _prefill_case(cuda_device, torch.float16, "nvfp4", 64, 1024, 2, 1, 0.1, False, True, sq=256)
 
@@ -402,6 +422,25 @@ DECODE_CASES = [
     (torch.float16, "mxfp4", 2, 1, 4, 1024, 2, 2, 64),
     (torch.bfloat16, "mxfp4", 1, 2, 2, 512, 8, 1, 64),
 ]
+
+
+def _seeded_decode_configs(n):
+    rng = torch.Generator().manual_seed(4048)
+    pick = lambda seq: seq[int(torch.randint(0, len(seq), (1,), generator=rng))]
+    out = []
+    for _ in range(n):
+        pages = int(torch.randint(1, 40, (1,), generator=rng))
+        out.append((pick((torch.float16, torch.bfloat16)), pick(("nvfp4", "mxfp4")), pick((1, 2, 3)), pick((1, 2)),
+                    pick((1, 2, 3, 4, 5, 8, 12, 16)), pages * 64, min(pages, pick((0, 1, 3, 7, 40))),
+                    min(pages, pick((1, 2, 3, 5))), pick((64, 128))))
+    return out
+
+
+@pytest.mark.parametrize("idx,cfg", list(enumerate(_seeded_decode_configs(16))))
+def test_decode_seeded_random_shapes(cuda_device, idx, cfg):
+    """Sixteen configurations drawn from a fixed seed (1..39 pages, any group size up to 16, ragged split counts,
+    none / some / all pages selected), each against the oracle through the same check as the listed cases."""
+    test_decode_attention_matches_oracle(cuda_device, *cfg)
 
 
 def _to_page_pools(table, n_pool, k4, ks, v4, vs, k_hi, v_hi):
