@@ -163,15 +163,94 @@ __device__ __forceinline__ void topk_dispatch(const float* scores, int n, int k,
 constexpr int SEL_WARPS = 8;
 constexpr int SEL_KTILE = 32;
 
+template <int D>
+struct SelpSmem {
+    static constexpr int ROW = D * 2 + 16;                    // padded statistics row: 16-byte reads by 32 lanes do not collide
+    static constexpr int TILE = SEL_KTILE * ROW;
+    static constexpr int QF = SEL_WARPS * D * 4;              // q rows as fp32
+    static constexpr int QM = SEL_WARPS * (D / 2) * 4;        // Quest masks, one 16-bit mask per channel
+    static int total(int nk_pad) { return SEL_WARPS * nk_pad * 4 + 2 * TILE + QF + QM; }
+};
+
+// packed fp32x2 arithmetic (two partial sums per instruction) and 16-bit pair -> fp32 pair
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    unsigned long long ra, rb, rc, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    unsigned long long ra, rb, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+
+template <bool BF16>
+__device__ __forceinline__ float2 word_to_float2(uint32_t w) {
+    if constexpr (BF16) return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+    else return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+
+// Score of one (q row, key block) pair computed by ONE thread with the arithmetic of warp_score: 32 partial sums
+// (channel c goes to partial c mod 32, fused multiply-adds in ascending channel order), then the xor-butterfly
+// pairing 16, 8, 4, 2, 1 as plain additions — fp32 addition commutes, so the value is the warp's bit for bit.
+template <int D, bool BF16, bool QUEST>
+__device__ __forceinline__ float thread_score(const float4* __restrict__ qrow, const uint4* __restrict__ mrow,
+                                              const uint4* __restrict__ ra, const uint4* __restrict__ rb) {
+    float2 acc[16];
+#pragma unroll
+    for (int w = 0; w < 16; ++w) acc[w] = make_float2(0.0f, 0.0f);
+#pragma unroll 1
+    for (int i = 0; i < D / 32; ++i) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {          // 8 channels per 16-byte chunk
+            const uint4 a = ra[i * 4 + v];
+            uint32_t kw[4] = {a.x, a.y, a.z, a.w};
+            if constexpr (QUEST) {
+                const uint4 b = rb[i * 4 + v];
+                const uint4 m = mrow[i * 4 + v];
+                kw[0] = (b.x & m.x) | (a.x & ~m.x);
+                kw[1] = (b.y & m.y) | (a.y & ~m.y);
+                kw[2] = (b.z & m.z) | (a.z & ~m.z);
+                kw[3] = (b.w & m.w) | (a.w & ~m.w);
+            }
+            const float4 q0 = qrow[i * 8 + v * 2], q1 = qrow[i * 8 + v * 2 + 1];
+            acc[v * 4 + 0] = fma2(make_float2(q0.x, q0.y), word_to_float2<BF16>(kw[0]), acc[v * 4 + 0]);
+            acc[v * 4 + 1] = fma2(make_float2(q0.z, q0.w), word_to_float2<BF16>(kw[1]), acc[v * 4 + 1]);
+            acc[v * 4 + 2] = fma2(make_float2(q1.x, q1.y), word_to_float2<BF16>(kw[2]), acc[v * 4 + 2]);
+            acc[v * 4 + 3] = fma2(make_float2(q1.z, q1.w), word_to_float2<BF16>(kw[3]), acc[v * 4 + 3]);
+        }
+    }
+#pragma unroll
+    for (int w = 0; w < 8; ++w) acc[w] = add2(acc[w], acc[w + 8]);
+#pragma unroll
+    for (int w = 0; w < 4; ++w) acc[w] = add2(acc[w], acc[w + 4]);
+    acc[0] = add2(acc[0], acc[2]);
+    acc[1] = add2(acc[1], acc[3]);
+    acc[0] = add2(acc[0], acc[1]);
+    return __fadd_rn(acc[0].x, acc[0].y);
+}
+
 template <int D, bool BF16, bool QUEST>
 __global__ void __launch_bounds__(SEL_WARPS * 32) select_prefill_kernel(
     const uint16_t* __restrict__ q_mean, const uint16_t* __restrict__ ka, const uint16_t* __restrict__ kb,
     int32_t* __restrict__ out, int heads, int group, int nq, int nk, int k, int causal, int sink, int local) {
+    using L = SelpSmem<D>;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     float* scores = reinterpret_cast<float*>(smem_raw);                              // [SEL_WARPS][nk_pad]
     const int nk_pad = (nk + 31) & ~31;
-    uint16_t* s_ka = reinterpret_cast<uint16_t*>(scores + SEL_WARPS * nk_pad);        // [SEL_KTILE][D]
-    uint16_t* s_kb = s_ka + SEL_KTILE * D;
+    uint8_t* s_ka = smem_raw + SEL_WARPS * nk_pad * 4;                                // [SEL_KTILE] padded rows
+    uint8_t* s_kb = s_ka + L::TILE;
+    float* qf = reinterpret_cast<float*>(s_kb + L::TILE);                             // [SEL_WARPS][D]
+    uint32_t* qm = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(qf) + L::QF);   // [SEL_WARPS][D/2]
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int q_tiles = cdiv(nq, SEL_WARPS);
     const int width = sink + local + k;
@@ -181,11 +260,16 @@ __global__ void __launch_bounds__(SEL_WARPS * 32) select_prefill_kernel(
         const int qb = (work - h * q_tiles) * SEL_WARPS + warp;
         const int kvh = h / group;
         const bool active = qb < nq;
-        float q[D / 32];
+        // this warp's q row as fp32, and for Quest an all-ones 16-bit mask per channel where q >= 0
         if (active) {
-#pragma unroll
-            for (int i = 0; i < D / 32; ++i)
-                q[i] = In16<BF16>::to_f(q_mean[(static_cast<long long>(h) * nq + qb) * D + lane + 32 * i]);
+            for (int c = lane; c < D; c += 32)
+                qf[warp * D + c] = In16<BF16>::to_f(q_mean[(static_cast<long long>(h) * nq + qb) * D + c]);
+            __syncwarp();
+            if constexpr (QUEST)
+                for (int w = lane; w < D / 2; w += 32)
+                    qm[warp * (D / 2) + w] = (qf[warp * D + 2 * w] >= 0.0f ? 0xFFFFu : 0u) |
+                                             (qf[warp * D + 2 * w + 1] >= 0.0f ? 0xFFFF0000u : 0u);
+            __syncwarp();
         }
         const int qb_hi = min((work - h * q_tiles) * SEL_WARPS + SEL_WARPS - 1, nq - 1);
         const int nk_need = causal ? min(nk, qb_hi + 1) : nk;
@@ -193,22 +277,25 @@ __global__ void __launch_bounds__(SEL_WARPS * 32) select_prefill_kernel(
         const int n_sink = min(sink, nvalid);
         const int local_lo = max(nvalid - local, n_sink);
         float* my = scores + warp * nk_pad;
+        const float4* qrow = reinterpret_cast<const float4*>(qf + warp * D);
+        const uint4* mrow = reinterpret_cast<const uint4*>(qm + warp * (D / 2));
         for (int b0 = 0; b0 < nk_need; b0 += SEL_KTILE) {
             const int nb = min(SEL_KTILE, nk_need - b0);
             __syncthreads();
             for (int i = threadIdx.x; i < nb * (D / 8); i += blockDim.x) {
-                const long long g = (static_cast<long long>(kvh) * nk + b0) * D + static_cast<long long>(i) * 8;
-                reinterpret_cast<uint4*>(s_ka)[i] = __ldg(reinterpret_cast<const uint4*>(ka + g));
-                if constexpr (QUEST) reinterpret_cast<uint4*>(s_kb)[i] = __ldg(reinterpret_cast<const uint4*>(kb + g));
+                const int r = i / (D / 8), c = i - r * (D / 8);
+                const long long g = (static_cast<long long>(kvh) * nk + b0 + r) * D + c * 8;
+                *reinterpret_cast<uint4*>(s_ka + r * L::ROW + c * 16) = __ldg(reinterpret_cast<const uint4*>(ka + g));
+                if constexpr (QUEST)
+                    *reinterpret_cast<uint4*>(s_kb + r * L::ROW + c * 16) = __ldg(reinterpret_cast<const uint4*>(kb + g));
             }
             __syncthreads();
-            if (active) {
-                for (int j = 0; j < nb; ++j) {
-                    const int b = b0 + j;
-                    if (b >= nvalid) break;
-                    const float s = warp_score<D, BF16, QUEST>(q, s_ka + j * D, s_kb + j * D, lane);
-                    if (lane == 0) my[b] = (b < n_sink || b >= local_lo) ? -FLT_MAX : s;
-                }
+            // one key block per lane
+            const int b = b0 + lane;
+            if (lane < nb && b < nvalid) {
+                const float s = thread_score<D, BF16, QUEST>(qrow, mrow, reinterpret_cast<const uint4*>(s_ka + lane * L::ROW),
+                                                             reinterpret_cast<const uint4*>(s_kb + lane * L::ROW));
+                my[b] = (b < n_sink || b >= local_lo) ? -FLT_MAX : s;
             }
         }
         __syncwarp();
@@ -246,32 +333,6 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
-    unsigned long long ra, rb, rc, rd;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
-    float2 d;
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
-    return d;
-}
-__device__ __forceinline__ float2 add2(float2 a, float2 b) {
-    unsigned long long ra, rb, rd;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
-    float2 d;
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
-    return d;
-}
-
-template <bool BF16>
-__device__ __forceinline__ float2 word_to_float2(uint32_t w) {
-    if constexpr (BF16) return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
-    else return __half22float2(*reinterpret_cast<const __half2*>(&w));
-}
 
 // Sort key: high word orders scores descending (-0 counts as +0), low word is the tie-break rank.
 __device__ __forceinline__ unsigned long long seld_key(float score, int page) {
@@ -733,7 +794,7 @@ int select_prefill_dispatch(const void* q_mean, const void* ka, const void* kb, 
     if (nk > 2048 || nk < 0 || k < 0 || group <= 0 || heads % group != 0) return TA100_ERR_SHAPE;
     if (sink + local + k == 0 || heads == 0 || nq == 0) return TA100_OK;
     const int nk_pad = (nk + 31) & ~31;
-    const size_t smem = sizeof(float) * SEL_WARPS * nk_pad + 2ull * SEL_KTILE * d * 2;
+    const size_t smem = d == 128 ? SelpSmem<128>::total(nk_pad) : SelpSmem<64>::total(nk_pad);
     const long long work = static_cast<long long>(heads) * cdiv(nq, SEL_WARPS);
     const int grid = static_cast<int>(work < NUM_SMS_HINT * 8LL ? work : NUM_SMS_HINT * 8LL);
 #define TA100_SEL(DD, BFF, QQ)                                                                                   \
