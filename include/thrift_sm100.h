@@ -256,6 +256,23 @@ int ta100_merge_partials(const void* part_o, const void* part_ml, void* out, int
                          int is_mxfp4, int is_bf16, void* stream);
 
 /*
+ * One decode step over a contiguous (capacity-strided) cache in a single call: quantise the grouped query
+ * q [B*hkv, group, D] into the caller's q4 / qs, select top_k (+ sink + local) of the first n_select_blocks
+ * 64-token blocks by block mean (stat_b = NULL, stat_a = means) or Quest (stat_a = minima, stat_b = maxima;
+ * both [B*hkv, stat_cap_blocks, D]) into sel [B*hkv, top_k + sink + local], then split-KV attention and merge
+ * into out [B*hkv, group, D].  The three launches are those of ta100_quantize, ta100_select_decode and
+ * ta100_decode_attention with the same arguments; one call saves the host the per-call overhead, which at batch 1
+ * exceeds the device time.  Replaces the body of cached_decode_attention
+ * (integrations/transformers_cache.py:570-619 of the reference: quantize_single_query_qkv, select_key_blocks and
+ * the single-query operator).
+ */
+int ta100_cached_decode_step(const void* q, void* q4, void* qs, const void* k_hi, const void* v_hi, const void* k4,
+                             const void* ks, const void* v4t, const void* vst, const void* stat_a, const void* stat_b,
+                             void* sel, void* out, void* part_o, void* part_ml, int batch, int hkv, int group, int kv_len,
+                             int kv_cap, int stat_cap_blocks, int n_select_blocks, int top_k, int sink, int local,
+                             int head_dim, int is_mxfp4, int is_bf16, int splits, void* stream);
+
+/*
  * The merge of one producer's chains that stays a partial: part_o [flat_kv_heads, splits, group, D],
  * part_ml [.., 2] -> out_o [flat_kv_heads, 1, group, D] (fp32, units of C), out_ml [flat_kv_heads, 1, group, 2]
  * (row maximum, row sum), i.e. the same arrays with splits = 1.  A GPU that holds a slice of the KV sequence

@@ -221,3 +221,35 @@ def test_cached_prefill_ignores_prompt_padding_in_selection():
     ref = oracle.select_prefill(qm, mean, k=1, causal=True)
     assert torch.equal(sel[:, :2], ref[:, :2])          # blocks made only of real rows: identical arithmetic
     assert sel.shape == ref.shape
+
+
+@pytest.mark.parametrize("fmt,selection,dtype,sink,local", [("nvfp4", "block_mean", torch.float16, 0, 0),
+                                                          ("mxfp4", "quest", torch.bfloat16, 1, 2),
+                                                          ("nvfp4", "quest", torch.float16, 2, 0)])
+def test_fused_decode_step_equals_the_operator_path(monkeypatch, fmt, selection, dtype, sink, local):
+    """cached_decode_attention queues quantise q + selection + attention through one library call; with that entry
+    hidden it goes operator by operator.  Both give the same bytes, over several appended tokens and a ragged
+    last block."""
+    from thriftattention_b200 import _C
+    from thriftattention_b200.integrations import transformers_cache as tc
+
+    torch.manual_seed(31)
+    cfg = ta.AttentionConfig(selection=selection, top_k=3, quant_format=fmt, sink_blocks=sink, local_blocks=local)
+    caches = [tc.ThriftAttentionCache(config=cfg, max_cache_len=1024) for _ in range(2)]
+    k = torch.randn(2, 2, 700, 128, device=DEV).to(dtype)
+    v = torch.randn(2, 2, 700, 128, device=DEV).to(dtype)
+    for c in caches:
+        c.update(k, v, 0, {"cache_position": torch.arange(700, device=DEV)})
+    for step in range(3):
+        q = torch.randn(2, 8, 1, 128, device=DEV).to(dtype)
+        k1 = torch.randn(2, 2, 1, 128, device=DEV).to(dtype)
+        v1 = torch.randn(2, 2, 1, 128, device=DEV).to(dtype)
+        for c in caches:
+            c.update(k1, v1, 0, {"cache_position": torch.tensor([700 + step], device=DEV)})
+        fused = tc.cached_decode_attention(q, caches[0], 0, cfg)
+        with monkeypatch.context() as m:
+            m.delattr(_C, "cached_decode_step")
+            plain = tc.cached_decode_attention(q, caches[1], 0, cfg)
+        assert torch.equal(fused, plain)
+        assert torch.equal(caches[0].layer(0).selected_blocks, caches[1].layer(0).selected_blocks)
+    _C.decode_status(DEV)

@@ -568,3 +568,24 @@ def test_query_block_means_skip_padding(monkeypatch):
     assert part[:, :, 2:].abs().sum() == 0
     edge = cache_mod._query_block_means(q, 64, 128)
     assert torch.equal(edge[:, :, :2], full[:, :, :2]) and edge[:, :, 2:].abs().sum() == 0
+
+
+def test_cache_position_is_read_once_per_forward():
+    """Every layer of a forward pass receives the same cache_position tensor object; its value is read (a device
+    synchronisation on a GPU) for the first layer only.  A new tensor, or the same one changed in place, is read
+    again."""
+    from thriftattention_b200.integrations import transformers_cache as cache_mod
+
+    first = torch.tensor([5])
+    assert cache_mod._cache_position_start({"cache_position": first}, 0) == 5
+    memo = cache_mod._POSITION_MEMO
+    assert memo[0]() is first and memo[2] == 5
+    second = torch.tensor([9])
+    assert cache_mod._cache_position_start({"cache_position": second}, 0) == 9
+    assert cache_mod._cache_position_start({"cache_position": first}, 0) == 5     # other object: read again
+    first.add_(1)
+    assert cache_mod._cache_position_start({"cache_position": first}, 0) == 6     # changed in place: read again
+    assert cache_mod._cache_position_start({"cache_position": torch.arange(3, 7)}, 0) == 3
+    with pytest.raises(ValueError, match="contiguous cache_position"):
+        cache_mod._cache_position_start({"cache_position": torch.tensor([3, 5])}, 0)
+    assert cache_mod._cache_position_start(None, 7) == 7 and cache_mod._cache_position_start({"cache_position": 4}, 7) == 4

@@ -123,7 +123,8 @@ def block_stats(x: torch.Tensor, block_size: int, *, mean=False, minmax=False):
 
 
 def cache_append(k_new, v_new, k_hi, v_hi, k_codes, k_scales, v_codes_t, v_scales_t, *, start, k_count=None, v_count=None,
-                 k_mean=None, k_min=None, k_max=None, is_mx=False, stat_block=64, keep_k=False, keep_v=False):
+                 k_mean=None, k_min=None, k_max=None, is_mx=False, stat_block=64, keep_k=False, keep_v=False,
+                 trusted=False):
     """Fused KV-cache append (one launch): stores ``k_new`` / ``v_new`` [B, H, T, D] at token positions
     ``[start, start + T)`` of the capacity-strided caches ``k_hi`` / ``v_hi`` [B, H, cap, D], quantises the
     new K rows, re-quantises the V groups they touch and refreshes the statistics of completed blocks.
@@ -131,11 +132,26 @@ def cache_append(k_new, v_new, k_hi, v_hi, k_codes, k_scales, v_codes_t, v_scale
     ``k_new`` / ``v_new`` may be ``None`` with an explicit count: zero rows are stored, or with
     ``keep_k`` / ``keep_v`` the cached rows are kept and only re-quantised.  Stands in for
     ``ThriftAttentionCacheLayer.update`` and its three helpers
-    (integrations/transformers_cache.py:87-123, 308-351).
+    (integrations/transformers_cache.py:87-123, 308-351).  ``trusted`` skips the shape checks: the cache layer
+    that owns all of these buffers calls it once per layer and token, where the checks cost more than the launch.
     """
-    _check(k_hi.is_cuda and k_hi.dim() == 4 and k_hi.is_contiguous(), "k cache must be a contiguous 4D CUDA tensor")
     b, h, cap, d = k_hi.shape
     is_bf16 = k_hi.dtype == torch.bfloat16
+    if trusted:
+        vp = ctypes.c_void_p
+        ptr = lambda t: None if t is None else vp(t.data_ptr())
+        k_count = k_new.shape[2] if k_new is not None else int(k_count or 0)
+        v_count = v_new.shape[2] if v_new is not None else int(v_count or 0)
+        with torch.cuda.device(k_hi.device):
+            rc = _lib.load().ta100_cache_append(ptr(k_new), ptr(v_new), ptr(k_hi), ptr(v_hi), ptr(k_codes), ptr(k_scales),
+                                                ptr(v_codes_t), ptr(v_scales_t), ptr(k_mean), ptr(k_min), ptr(k_max),
+                                                b * h, int(start), k_count, v_count, cap, d, stat_block, int(is_mx),
+                                                int(is_bf16), (1 if keep_k else 0) | (2 if keep_v else 0),
+                                                vp(torch.cuda.current_stream(k_hi.device).cuda_stream))
+        if rc:
+            _lib.check(rc, "cache_append")
+        return
+    _check(k_hi.is_cuda and k_hi.dim() == 4 and k_hi.is_contiguous(), "k cache must be a contiguous 4D CUDA tensor")
     _check(k_hi.dtype in (torch.float16, torch.bfloat16), "KV cache tensors must be float16 or bfloat16")
     g = 32 if is_mx else 16
     for name, new, count in (("key_states", k_new, k_count), ("value_states", v_new, v_count)):
@@ -565,6 +581,60 @@ def decode_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_pa
     if return_partials:
         return out, part_o, part_ml
     return out
+
+
+_decode_step_scratch: dict = {}
+_decode_step_splits: dict = {}
+
+
+def cached_decode_step(q_grouped, k_hi, v_hi, k_packed, k_scale, v_packed_t, v_scale_t, stat_a, stat_b, *, kv_len, n_select_blocks,
+                       top_k, sink=0, local=0, is_mx=False, sel_out=None):
+    """One decode step over a contiguous cache in ONE library call (quantise q, select, attend, merge).
+
+    ``q_grouped`` [B, Hkv, G, D]; the cache tensors are the capacity-sized buffers themselves (not views):
+    ``k_hi`` / ``v_hi`` [B, Hkv, cap, D], ``k_packed`` [B, Hkv, cap, D/2], ``v_packed_t`` [B, Hkv, D, cap/2] and their
+    scales, ``stat_a`` / ``stat_b`` [B, Hkv, cap/64, D] block means or (Quest) minima / maxima.  ``kv_len`` is the
+    kernel length (a multiple of 64).  The caller owns the shapes: this entry validates only what the library
+    cannot (it is the hot path of a batch-1 generation loop, where the host time per call exceeds the device
+    time).  Returns ``(out [B, Hkv, G, D], selected [B*Hkv, top_k + sink + local])``."""
+    b, hkv, g, d = q_grouped.shape
+    dev = q_grouped.device
+    is_bf16 = q_grouped.dtype == torch.bfloat16
+    _check(q_grouped.is_cuda and q_grouped.is_contiguous() and kv_len % 64 == 0 and 1 <= g <= 16,
+           "cached_decode_step expects a contiguous CUDA query [B, Hkv, G <= 16, D] and a kernel length in whole pages")
+    cap = k_packed.shape[2]
+    width = top_k + sink + local
+    lib = _lib.load()
+    key = (b * hkv, kv_len // 64)
+    splits = _decode_step_splits.get(key)
+    if splits is None:
+        splits = max(1, min(lib.ta100_decode_pick_splits(b * hkv, kv_len // 64), kv_len // 64))
+        _decode_step_splits[key] = splits
+    skey = (dev.index, b, hkv, g, d, splits, is_mx)
+    scratch = _decode_step_scratch.get(skey)
+    if scratch is None:
+        grp = 32 if is_mx else 16
+        scratch = (torch.empty(b, hkv, g, d // 2, dtype=torch.uint8, device=dev),
+                   torch.empty(b, hkv, g, d // grp, dtype=torch.uint8, device=dev),
+                   torch.empty(b * hkv, splits, g, d, dtype=torch.float32, device=dev),
+                   torch.empty(b * hkv, splits, g, 2, dtype=torch.float32, device=dev))
+        _decode_step_scratch[skey] = scratch
+    q4, qs, part_o, part_ml = scratch
+    if sel_out is None or tuple(sel_out.shape) != (b * hkv, width):
+        sel_out = torch.empty(b * hkv, width, dtype=torch.int32, device=dev)
+    out = torch.empty(b, hkv, g, d, dtype=q_grouped.dtype, device=dev)
+    vp = ctypes.c_void_p
+    with torch.cuda.device(dev):
+        rc = lib.ta100_cached_decode_step(
+            vp(q_grouped.data_ptr()), vp(q4.data_ptr()), vp(qs.data_ptr()), vp(k_hi.data_ptr()), vp(v_hi.data_ptr()),
+            vp(k_packed.data_ptr()), vp(k_scale.data_ptr()), vp(v_packed_t.data_ptr()), vp(v_scale_t.data_ptr()),
+            vp(stat_a.data_ptr()) if width else None, vp(stat_b.data_ptr()) if (width and stat_b is not None) else None,
+            vp(sel_out.data_ptr()), vp(out.data_ptr()), vp(part_o.data_ptr()), vp(part_ml.data_ptr()), b, hkv, g, kv_len,
+            cap, stat_a.shape[2] if stat_a is not None else 0, n_select_blocks, top_k, sink, local, d, int(is_mx),
+            int(is_bf16), splits, vp(torch.cuda.current_stream(dev).cuda_stream))
+    if rc:
+        _lib.check(rc, "cached_decode_step")
+    return out, sel_out
 
 
 def decode_status(device=None) -> None:

@@ -23,6 +23,8 @@ from contextvars import ContextVar
 from dataclasses import dataclass
 from typing import Any, Iterator
 
+import weakref
+
 import torch
 
 from .._extension import get_extension
@@ -70,12 +72,25 @@ def _cache_position_start(cache_kwargs: dict[str, Any] | None, fallback: int) ->
     flat = position.reshape(-1)
     if flat.numel() == 0:
         return fallback
+    # Reading a device tensor synchronises with the GPU.  A model passes the SAME tensor object to every layer
+    # of a forward pass, so the value read for the first layer serves the others (checked by object identity
+    # and version counter, not by address: the allocator reuses addresses from step to step).
+    memo = _POSITION_MEMO
+    if memo[0] is not None and memo[0]() is position and memo[1] == position._version:
+        return memo[2]
     first = int(flat[0].item())
     if flat.numel() > 1:
         expected = torch.arange(first, first + flat.numel(), device=flat.device, dtype=flat.dtype)
         if not torch.equal(flat, expected):
             raise ValueError("ThriftAttentionCache requires contiguous cache_position values")
+    try:
+        memo[0], memo[1], memo[2] = weakref.ref(position), position._version, first
+    except TypeError:
+        memo[0] = None
     return first
+
+
+_POSITION_MEMO: list = [None, 0, 0]
 
 
 def _scale_dtype(quant_format: str) -> torch.dtype:
@@ -145,7 +160,20 @@ class ThriftAttentionCacheLayer:
             self.v_scale_t, start=start, k_count=k_count, v_count=v_count,
             k_mean=self.k_mean if stats else None, k_min=self.k_min if stats else None,
             k_max=self.k_max if stats else None, is_mx=self.quant_format == "mxfp4", stat_block=PAGE,
-            keep_k=keep_k, keep_v=keep_v)
+            keep_k=keep_k, keep_v=keep_v, **({"trusted": True} if self._trusted_append(key_states, value_states) else {}))
+
+    def _trusted_append(self, key_states, value_states) -> bool:
+        """The layer allocated every cache buffer itself (``_ensure_capacity``), so only the new rows need a
+        look before the unchecked entry point is used."""
+        like = self.k_fp16
+        if like is None or not like.is_cuda:
+            return False
+        for t in (key_states, value_states):
+            if t is not None and not (t.is_cuda and t.is_contiguous() and t.dtype == like.dtype and t.dim() == 4
+                                      and t.shape[0] == like.shape[0] and t.shape[1] == like.shape[1]
+                                      and t.shape[3] == like.shape[3]):
+                return False
+        return True
 
     # ------------------------------------------------------------------------------------------- views
     def key_view(self) -> torch.Tensor:
@@ -491,8 +519,9 @@ def cached_decode_attention(query: torch.Tensor, cache: ThriftAttentionCache, la
                             config: AttentionConfig) -> torch.Tensor:
     """One decode step ``[B, Hq, 1, D]`` over layer ``layer_idx`` of ``cache``; returns ``[B, Hq, 1, D]``.
 
-    Launches: quantise the grouped query, select blocks, split-KV attention (+ its merge).  K and V are
-    read in place through capacity-strided views — nothing is copied (transformers_cache.py:570-619)."""
+    Launches: quantise the grouped query, select blocks, split-KV attention (+ its merge) — queued by one
+    library call on the common path, operator by operator otherwise.  K and V are read in place through
+    capacity strides — nothing is copied (transformers_cache.py:570-619)."""
     layer = cache.layer(layer_idx)
     if layer.seq_len == 0:
         raise RuntimeError("ThriftAttention decode cache is empty")
@@ -502,10 +531,14 @@ def cached_decode_attention(query: torch.Tensor, cache: ThriftAttentionCache, la
     is_bf16 = q.dtype == torch.bfloat16
     kv_heads = layer.key_view().shape[1]
     q_grouped = _group_single_query(q, kv_heads)
+    fmt = quant_format.name
+    if config.method == "thrift":
+        fused = _fused_decode_step(q_grouped, layer, config, fmt)
+        if fused is not None:
+            return _ungroup_single_query(fused, q.shape[1])
     q_packed, q_scale = quant_format.quantize(q_grouped, is_bf16=is_bf16)
     k_packed, v_packed_t, k_scale, v_scale_t = layer.packed_views()
     ext = get_extension()
-    fmt = quant_format.name
 
     if config.method == "fp4":
         out = getattr(ext, f"fp4_attention_single_query_{fmt}_packed")(q_packed, k_packed, v_packed_t, q_scale, k_scale,
@@ -519,6 +552,32 @@ def cached_decode_attention(query: torch.Tensor, cache: ThriftAttentionCache, la
         q_grouped, layer.key_view(), layer.value_view(), selected_blocks, q_packed, k_packed, v_packed_t, q_scale,
         k_scale, v_scale_t, is_bf16)
     return _ungroup_single_query(out, q.shape[1])
+
+
+def _fused_decode_step(q_grouped: torch.Tensor, layer: ThriftAttentionCacheLayer, config: AttentionConfig,
+                       fmt: str) -> torch.Tensor | None:
+    """Quantise q + select + attend + merge through one library call when the step is the common one (score-based
+    selection over at most 2048 complete blocks of a 64-token-block cache); ``None`` sends the caller down the
+    operator-by-operator path, which computes the same thing."""
+    ext = get_extension()
+    step = getattr(ext, "cached_decode_step", None)
+    if step is None or config.selection not in ("block_mean", "quest") or config.block_size != PAGE:
+        return None
+    quest = config.selection == "quest"
+    stat_a, stat_b = (layer.k_min, layer.k_max) if quest else (layer.k_mean, None)
+    complete_blocks = layer.seq_len // PAGE
+    if stat_a is None or (quest and stat_b is None) or complete_blocks > 2048 or q_grouped.dtype != stat_a.dtype:
+        return None
+    selected_count = resolve_top_k(complete_blocks, causal=False, top_k=config.top_k, fraction=config.fraction)
+    local = max(0, min(getattr(config, "local_blocks", 0), complete_blocks - selected_count))
+    sink = max(0, min(getattr(config, "sink_blocks", 0), complete_blocks - selected_count - local))
+    if selected_count == 0:
+        sink = local = 0
+    out, layer.selected_blocks = step(q_grouped, layer.k_fp16, layer.v_fp16, layer.k_packed, layer.k_scale,
+                                      layer.v_packed_t, layer.v_scale_t, stat_a, stat_b, kv_len=layer.kernel_len(),
+                                      n_select_blocks=complete_blocks, top_k=selected_count, sink=sink, local=local,
+                                      is_mx=fmt == "mxfp4", sel_out=layer.selected_blocks)
+    return out
 
 
 def cached_prefill_attention(query: torch.Tensor, cache: ThriftAttentionCache, layer_idx: int,
