@@ -126,7 +126,9 @@ int ta100_select_decode(const void* q_grouped, const void* k_a, const void* k_b,
  * ranked with the single-GPU key (score, then the reference's tie-break on the global page id) and the first
  * top_k are the global selection.  out [rows, sink + local + top_k] receives shard `rank`'s part as LOCAL page
  * ids: its forced pages first, picks at position sink + local + j when pick j lies in this shard, -1 elsewhere.
- * world * width <= 2048.  The reference has no multi-GPU path; the merge follows the same argument as its
+ * world * width <= 2048.  Exact ties in score are ranked by the global page id here and by the shard-local id
+ * inside a shard's own pre-selection; the two orders agree when every shard begins at a multiple of 32 pages.
+ * The reference has no multi-GPU path; the merge follows the same argument as its
  * chunked single-GPU top-k (block_selection.cu:443-447).
  */
 int ta100_merge_page_candidates(const void* gathered, void* out, int rows, int world, int width, int rank,
