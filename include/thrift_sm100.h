@@ -181,7 +181,7 @@ int ta100_prefill_status(const void* workspace, int batch, int hq, int hkv, int 
 
 /*
  * Decode (single query token) attention over 64-token pages, split over the KV sequence.
- * Rows are the `group` (<= 8) query heads that share a KV head:
+ * Rows are the `group` (<= 16) query heads that share a KV head; head_dim 64 or 128:
  *   q_hi [B*hkv, group, D] 16-bit and its rows-layout quantisation q4 / qs
  *   K/V, contiguous cache (page_table = NULL): k4 / ks rows layout with head stride kv_cap rows
  *        (plain, not permuted), v4 / vs transposed layout with P = ceil(kv_cap/128)*128,
