@@ -194,7 +194,7 @@ int ta100_prefill_status(const void* workspace, int batch, int hq, int hkv, int 
  * selected pages ascending.  Partial results go to part_o [B*hkv, splits, group, D] (fp32,
  * un-normalised, in units of C = 2688 NVFP4 / 6 MXFP4) and part_ml [B*hkv, splits, group, 2]
  * (row max, row sum); with write_out = 1 they are merged into out [B*hkv, group, D] on the same
- * stream.  kv_len a multiple of 64, head_dim 128.
+ * stream.  kv_len a multiple of 64, head_dim 64 or 128.
  * Replaces fp4_attention_single_query_{nvfp4,mxfp4} and thrift_attention_single_query_{nvfp4,mxfp4}
  * (bindings.cpp:79-92, 132-147; kernels csrc/cuda/sm120/nvfp4/single_query_attention.cu:795,1196,
  * single_query_fp4_attention.cu:718,1116 and twins).  The scratch the reference's binding allocates
