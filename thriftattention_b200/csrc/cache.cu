@@ -33,6 +33,7 @@ struct AppendParams {
     int start, k_count, v_count, cap;
     int k_keep, v_keep;           // with a null input: 1 = re-quantise the cached rows, 0 = store zero rows
     int n_k_items, n_v_items, n_s_items;
+    int k_loop;                   // K row bundles per K item (more than one for bulk appends)
     int v_begin, v_end;           // group-aligned token range whose V groups are re-quantised
     int s_first, stat_block;
 };
@@ -67,26 +68,28 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p)
 
     if (it < p.n_k_items) {
         // ---------------------------------------------------------------- K rows: one thread per group
-        const int row = it * ROWS + tid / GPR;
         const int c = tid % GPR;
-        if (row >= p.k_count) return;
-        const int tok = p.start + row;
-        uint32_t raw[G / 2];
-        bool is_new = false;
+        for (int b = 0; b < p.k_loop; ++b) {
+            const int row = (it * p.k_loop + b) * ROWS + tid / GPR;
+            if (row >= p.k_count) return;
+            const int tok = p.start + row;
+            uint32_t raw[G / 2];
+            bool is_new = false;
 #pragma unroll
-        for (int i = 0; i < G / 8; ++i) {
-            const uint4 t = row_chunk<D>(p.k_new, p.k_hi, p.k_keep, p.start, p.k_count, p.cap, head, tok,
-                                         c * (G / 8) + i, is_new);
-            raw[4 * i + 0] = t.x; raw[4 * i + 1] = t.y; raw[4 * i + 2] = t.z; raw[4 * i + 3] = t.w;
-            if (is_new) *(reinterpret_cast<uint4*>(p.k_hi + (head * p.cap + tok) * D) + c * (G / 8) + i) = t;
+            for (int i = 0; i < G / 8; ++i) {
+                const uint4 t = row_chunk<D>(p.k_new, p.k_hi, p.k_keep, p.start, p.k_count, p.cap, head, tok,
+                                             c * (G / 8) + i, is_new);
+                raw[4 * i + 0] = t.x; raw[4 * i + 1] = t.y; raw[4 * i + 2] = t.z; raw[4 * i + 3] = t.w;
+                if (is_new) *(reinterpret_cast<uint4*>(p.k_hi + (head * p.cap + tok) * D) + c * (G / 8) + i) = t;
+            }
+            uint32_t out[G / 8];
+            uint8_t sb;
+            quantise_group_regs<MX, BF16>(raw, out, sb);
+            const long long gid = (head * p.cap + tok) * GPR + c;
+            if constexpr (MX) *reinterpret_cast<uint4*>(p.k_codes + gid * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+            else *reinterpret_cast<uint2*>(p.k_codes + gid * 8) = make_uint2(out[0], out[1]);
+            p.k_scales[gid] = sb;
         }
-        uint32_t out[G / 8];
-        uint8_t sb;
-        quantise_group_regs<MX, BF16>(raw, out, sb);
-        const long long gid = (head * p.cap + tok) * GPR + c;
-        if constexpr (MX) *reinterpret_cast<uint4*>(p.k_codes + gid * 16) = make_uint4(out[0], out[1], out[2], out[3]);
-        else *reinterpret_cast<uint2*>(p.k_codes + gid * 8) = make_uint2(out[0], out[1]);
-        p.k_scales[gid] = sb;
         return;
     }
     it -= p.n_k_items;
@@ -230,7 +233,8 @@ int cache_append_dispatch(const void* k_new, const void* v_new, void* k_hi, void
     p.v_keep = (flags & 2) ? 1 : 0;
     p.stat_block = stat_block;
     const int rows_per_item = 128 / (head_dim / G);
-    p.n_k_items = cdiv(k_count, rows_per_item);
+    p.k_loop = k_count >= 2048 ? 8 : 1;
+    p.n_k_items = cdiv(k_count, rows_per_item * p.k_loop);
     if (v_count > 0) {
         p.v_begin = start / G * G;
         p.v_end = cdiv(start + v_count, G) * G;
