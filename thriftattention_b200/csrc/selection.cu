@@ -148,6 +148,103 @@ __device__ __forceinline__ void warp_topk_rounds(const float* scores, int n, int
     }
 }
 
+// Sort key: high word orders scores descending (-0 counts as +0), low word is the tie-break rank.
+__device__ __forceinline__ unsigned long long seld_key(float score, int page) {
+    if (score == 0.0f) score = 0.0f;
+    const uint32_t u = __float_as_uint(score);
+    const uint32_t asc = (u >> 31) ? ~u : (u | 0x80000000u);
+    const uint32_t tie = (__brev(static_cast<uint32_t>(page) & 31u) >> 27 << 16) | (static_cast<uint32_t>(page) >> 5);
+    return (static_cast<unsigned long long>(~asc) << 32) | tie;
+}
+__device__ __forceinline__ float seld_key_score(unsigned long long key) {
+    const uint32_t asc = ~static_cast<uint32_t>(key >> 32);
+    return __uint_as_float((asc >> 31) ? (asc ^ 0x80000000u) : ~asc);
+}
+__device__ __forceinline__ int seld_key_page(unsigned long long key) {
+    const uint32_t tie = static_cast<uint32_t>(key);
+    return static_cast<int>((__brev(tie >> 16) >> 27) | ((tie & 0xFFFFu) << 5));
+}
+
+// The same k picks as warp_topk_rounds(pad = true) without k serial rounds (one warp, scores in shared memory):
+// a four-digit radix selection finds the k-th largest score, the entries at or above it are gathered (at most
+// SELP_CAND of them) and ranked by counting smaller 64-bit keys (descending score, then the arg-max rounds'
+// tie-break: smallest 5-bit bit-reversal of idx mod 32, then smallest idx div 32).  Returns false without
+// writing anything when more than SELP_CAND entries tie into the candidate set; the caller then runs the rounds.
+// hist: 256 ints (reused for the candidate indices), keys: SELP_CAND 64-bit words, both private to the warp.
+constexpr int SELP_CAND = 256;
+__device__ __forceinline__ bool warp_topk_select(const float* scores, int n, int k, int32_t* out, int lane, int* hist,
+                                                 unsigned long long* keys) {
+    if (k <= 0) return true;
+    auto image = [&](int i) -> uint32_t {       // ascending 32-bit image of the score
+        float v = scores[i];
+        if (v == 0.0f) v = 0.0f;
+        const uint32_t u = __float_as_uint(v);
+        return (u >> 31) ? ~u : (u | 0x80000000u);
+    };
+    uint32_t prefix = 0u;
+    if (n > k) {
+        int remaining = k;
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            for (int j = lane; j < 256; j += 32) hist[j] = 0;
+            __syncwarp();
+            for (int i = lane; i < n; i += 32) {
+                const uint32_t key = image(i);
+                if (shift == 24 || (key >> (shift + 8)) == (prefix >> (shift + 8))) atomicAdd(&hist[(key >> shift) & 255u], 1);
+            }
+            __syncwarp();
+            int cnt[8], mine = 0;            // lane l owns digits 8l .. 8l+7; suffix sums over the lanes
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { cnt[j] = hist[lane * 8 + j]; mine += cnt[j]; }
+            int incl = mine;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int v = __shfl_down_sync(0xFFFFFFFFu, incl, d);
+                if (lane + d < 32) incl += v;
+            }
+            const int excl = incl - mine;
+            const bool owner = excl < remaining && remaining <= incl;
+            int digit = 0, rest = 0;
+            if (owner) {
+                int seen = excl;
+#pragma unroll
+                for (int j = 7; j >= 0; --j) {
+                    if (seen < remaining && remaining <= seen + cnt[j]) { digit = lane * 8 + j; rest = remaining - seen; break; }
+                    seen += cnt[j];
+                }
+            }
+            const int src = __ffs(__ballot_sync(0xFFFFFFFFu, owner)) - 1;
+            digit = __shfl_sync(0xFFFFFFFFu, digit, src);
+            remaining = __shfl_sync(0xFFFFFFFFu, rest, src);
+            prefix |= static_cast<uint32_t>(digit) << shift;
+            __syncwarp();
+        }
+    }
+    // gather the entries at or above the threshold (all of them when n <= k)
+    int* cand = hist;
+    const uint32_t lt = (1u << lane) - 1u;
+    int n_c = 0;
+    for (int base = 0; base < n; base += 32) {
+        const int i = base + lane;
+        const bool take = i < n && image(i) >= prefix;
+        const uint32_t m = __ballot_sync(0xFFFFFFFFu, take);
+        const int pos = n_c + __popc(m & lt);
+        if (take && pos < SELP_CAND) cand[pos] = i;
+        n_c += __popc(m);
+    }
+    if (n_c > SELP_CAND) return false;
+    __syncwarp();
+    for (int c = lane; c < n_c; c += 32) keys[c] = seld_key(scores[cand[c]], cand[c]);
+    __syncwarp();
+    for (int c = lane; c < n_c; c += 32) {
+        const unsigned long long mine = keys[c];
+        int rank = 0;
+        for (int j = 0; j < n_c; ++j) rank += keys[j] < mine ? 1 : 0;
+        if (rank < k) out[rank] = seld_key_score(mine) > -FLT_MAX * 0.5f ? seld_key_page(mine) : -1;
+    }
+    for (int r = n_c + lane; r < k; r += 32) out[r] = -1;
+    return true;
+}
+
 __device__ __forceinline__ void topk_dispatch(const float* scores, int n, int k, bool pad, int32_t* out, int lane) {
     if (n <= 128) warp_topk_rounds<4>(scores, n, k, pad, out, lane);
     else if (n <= 512) warp_topk_rounds<16>(scores, n, k, pad, out, lane);
@@ -169,7 +266,8 @@ struct SelpSmem {
     static constexpr int TILE = SEL_KTILE * ROW;
     static constexpr int QF = SEL_WARPS * D * 4;              // q rows as fp32
     static constexpr int QM = SEL_WARPS * (D / 2) * 4;        // Quest masks, one 16-bit mask per channel
-    static int total(int nk_pad) { return SEL_WARPS * nk_pad * 4 + 2 * TILE + QF + QM; }
+    static constexpr int TOPK = SEL_WARPS * (256 * 4 + SELP_CAND * 8);   // per warp: histogram / candidates, keys
+    static int total(int nk_pad) { return SEL_WARPS * nk_pad * 4 + 2 * TILE + QF + QM + TOPK; }
 };
 
 // packed fp32x2 arithmetic (two partial sums per instruction) and 16-bit pair -> fp32 pair
@@ -251,6 +349,10 @@ __global__ void __launch_bounds__(SEL_WARPS * 32) select_prefill_kernel(
     uint8_t* s_kb = s_ka + L::TILE;
     float* qf = reinterpret_cast<float*>(s_kb + L::TILE);                             // [SEL_WARPS][D]
     uint32_t* qm = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(qf) + L::QF);   // [SEL_WARPS][D/2]
+    unsigned long long* tk_keys = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(qm) + L::QM) +
+                                  (threadIdx.x / 32) * SELP_CAND;
+    int* tk_hist = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(qm) + L::QM + SEL_WARPS * SELP_CAND * 8) +
+                   (threadIdx.x / 32) * 256;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int q_tiles = cdiv(nq, SEL_WARPS);
     const int width = sink + local + k;
@@ -303,7 +405,8 @@ __global__ void __launch_bounds__(SEL_WARPS * 32) select_prefill_kernel(
             int32_t* row = out + (static_cast<long long>(h) * nq + qb) * width;
             const int forced = n_sink + (nvalid - local_lo);
             for (int i = lane; i < forced; i += 32) row[i] = i < n_sink ? i : local_lo + (i - n_sink);
-            topk_dispatch(my, nvalid, k, true, row + forced, lane);
+            if (!warp_topk_select(my, nvalid, k, row + forced, lane, tk_hist, tk_keys))
+                topk_dispatch(my, nvalid, k, true, row + forced, lane);
             for (int i = forced + k + lane; i < width; i += 32) row[i] = -1;
         }
         __syncthreads();
@@ -333,23 +436,6 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-// Sort key: high word orders scores descending (-0 counts as +0), low word is the tie-break rank.
-__device__ __forceinline__ unsigned long long seld_key(float score, int page) {
-    if (score == 0.0f) score = 0.0f;
-    const uint32_t u = __float_as_uint(score);
-    const uint32_t asc = (u >> 31) ? ~u : (u | 0x80000000u);
-    const uint32_t tie = (__brev(static_cast<uint32_t>(page) & 31u) >> 27 << 16) | (static_cast<uint32_t>(page) >> 5);
-    return (static_cast<unsigned long long>(~asc) << 32) | tie;
-}
-__device__ __forceinline__ float seld_key_score(unsigned long long key) {
-    const uint32_t asc = ~static_cast<uint32_t>(key >> 32);
-    return __uint_as_float((asc >> 31) ? (asc ^ 0x80000000u) : ~asc);
-}
-__device__ __forceinline__ int seld_key_page(unsigned long long key) {
-    const uint32_t tie = static_cast<uint32_t>(key);
-    return static_cast<int>((__brev(tie >> 16) >> 27) | ((tie & 0xFFFFu) << 5));
-}
 
 #ifdef TA100_PROFILE_SOFTMAX
 __device__ long long g_sel_prof[16];
