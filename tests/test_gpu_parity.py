@@ -113,6 +113,29 @@ def test_block_stats_and_prefill_selection_bit_exact(cuda_device, dtype, block):
     assert torch.equal(ext.pack_topk_mask(sel.to(cuda_device), nk).cpu(), oracle.pack_mask(sel, nk))
 
 
+def test_prefill_selection_with_ties(cuda_device):
+    """Exact score ties take the reference's tie-break (smallest bit-reversal of idx mod 32, then idx div 32):
+    a few ties inside the candidate set (duplicated key blocks), and everything tied (zero queries, as the
+    padded rows of a prompt are), which exceeds the candidate cap and takes the arg-max rounds."""
+    torch.manual_seed(23)
+    ext = _ext()
+    nq = nk = 640
+    qm = torch.randn(1, 2, nq, 128).half()
+    km = torch.randn(1, 1, nk, 128).half()
+    km[:, :, 100:140] = km[:, :, 300:340]                    # 40 exact duplicates
+    km[:, :, 500:520] = km[:, :, 20:21]                      # a block repeated 20 times
+    qm[:, :, 600:] = 0                                       # rows whose scores are all zero
+    qm[:, 1, 10] = 0
+    for k, causal in ((20, True), (64, False), (300, True)):
+        ref = oracle.select_prefill(qm, km, None, k=k, causal=causal)
+        got = ext.select_prefill_blocks(qm.to(cuda_device), km.to(cuda_device), None, k, causal, False)
+        assert torch.equal(got.cpu(), ref)
+        lo, hi = km - 0.5, km + 0.5
+        ref = oracle.select_prefill(qm, lo, hi, k=k, causal=causal, sink=1, local=1)
+        got = ext.select_prefill_blocks(qm.to(cuda_device), lo.to(cuda_device), hi.to(cuda_device), k, causal, False, 1, 1)
+        assert torch.equal(got.cpu(), ref)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_decode_selection_bit_exact(cuda_device, dtype):
     torch.manual_seed(3)
