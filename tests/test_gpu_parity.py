@@ -164,6 +164,96 @@ def test_decode_selection_bit_exact(cuda_device, dtype):
     assert torch.equal(topk.cpu(), oracle.select_decode(qg, km, None, k=5, num_kv_blocks=100))
 
 
+def _stats(nk, dtype, seed, hkv=2):
+    g = torch.Generator().manual_seed(seed)
+    km = torch.randn(1, hkv, nk, 128, generator=g)
+    ch = torch.randperm(128, generator=g)[:4]
+    km[..., ch] *= 10.0                                       # key outlier channels
+    half = torch.rand(1, hkv, nk, 128, generator=g) * 0.5
+    return km.to(dtype), (km - half).to(dtype), (km + half).to(dtype), g
+
+
+def _check_decode_selection(ext, dev, qg, km, kmin, kmax, k, nk, sink, local, bf):
+    """Two-pass kernel path == oracle == the kernel's exact path.  A query group above 8 heads always takes the
+    exact path; repeating heads does not change the maximum over the group, so the same selection must come out."""
+    reps = {1: 9, 2: 5, 4: 3, 8: 2}[qg.size(2)]
+    q_wide = qg.repeat(1, 1, reps, 1)
+    dq, dq_wide = qg.to(dev), q_wide.to(dev)
+    for a, b in ((kmin, kmax), (km, None)):
+        ref = oracle.select_decode(qg, a, b, k=k, num_kv_blocks=nk, sink=sink, local=local)
+        da, db = a.to(dev), None if b is None else b.to(dev)
+        got = ext.select_decode_blocks(dq, da, db, k, nk, bf, sink, local)
+        assert torch.equal(got.cpu(), ref), f"two-pass selection differs from the oracle (quest={b is not None})"
+        exact = ext.select_decode_blocks(dq_wide, da, db, k, nk, bf, sink, local)
+        assert torch.equal(exact.cpu(), ref), f"exact selection differs from the oracle (quest={b is not None})"
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("group", [1, 4, 8])
+@pytest.mark.parametrize("nk", [256, 1024, 2048])
+def test_decode_selection_two_pass_bit_exact(cuda_device, dtype, group, nk):
+    """The long-context selection path (approximate tensor-core pass, exact re-scoring of the candidates) that the
+    2048-page decode configurations run: index- and order-equal to the oracle (shared/block_selection.cu:339-441)
+    on eight seeds, with the 10 % + 4 sink + 16 local and the fixed-53 configurations."""
+    ext = _ext()
+    bf = dtype == torch.bfloat16
+    for seed in range(8):
+        km, kmin, kmax, g = _stats(nk, dtype, 100 + seed)
+        qg = torch.randn(1, 2, group, 128, generator=g).to(dtype)
+        k10 = oracle.resolve_top_k(nk, causal=False, fraction=0.1)
+        _check_decode_selection(ext, cuda_device, qg, km, kmin, kmax, k10, nk, 4, 16, bf)
+        _check_decode_selection(ext, cuda_device, qg, km, kmin, kmax, min(53, nk // 4), nk, 0, 0, bf)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_decode_selection_two_pass_adversarial(cuda_device, dtype):
+    """Rows built to sit on the pruning bound of the two-pass path: exact ties that straddle the k-th place,
+    all-zero queries (every page ties), one huge outlier channel (a wide error bound) and more tied candidates
+    than the exact re-scoring holds (falls back to scoring every page)."""
+    ext = _ext()
+    bf = dtype == torch.bfloat16
+    nk, k = 2048, 205
+    km, kmin, kmax, g = _stats(nk, dtype, 7)
+    qg = torch.randn(1, 2, 4, 128, generator=g).to(dtype)
+
+    def run(qq, a_mean, a_min, a_max, kk=k, sink=4, local=16):
+        _check_decode_selection(ext, cuda_device, qq, a_mean, a_min, a_max, kk, nk, sink, local, bf)
+
+    # (1) duplicated pages around the k-th place: find the oracle's ranking, then copy the page at rank k-1 over
+    #     40 pages spread over the sequence, so that exact ties straddle the cut
+    for a_min, a_max in ((kmin, kmax), (km, km)):
+        ref = oracle.select_decode(qg, a_min, a_max, k=k, num_kv_blocks=nk)
+        for h in range(2):
+            pivot = int(ref[h, k - 1])
+            idx = torch.arange(37, nk - 20, 50)
+            for t in (km, kmin, kmax):
+                t[0, h, idx] = t[0, h, pivot]
+    run(qg, km, kmin, kmax)
+    run(qg, km, kmin, kmax, kk=53, sink=0, local=0)
+    # (2) all-zero query: every score is +0, every page ties, the candidate set overflows
+    run(torch.zeros_like(qg), km, kmin, kmax)
+    # (3) one huge channel in q and in the statistics
+    q_big = qg.clone()
+    q_big[..., 5] = 200.0
+    k_big, kmin_big, kmax_big = km.clone(), kmin.clone(), kmax.clone()
+    for t in (k_big, kmin_big, kmax_big):
+        t[..., 5] *= 100.0
+    run(q_big, k_big, kmin_big, kmax_big)
+    # (4) 700 identical pages that all rank first: more candidates than the exact pass holds
+    k_dup, kmin_dup, kmax_dup = km.clone(), kmin.clone(), kmax.clone()
+    ref = oracle.select_decode(qg, kmin, kmax, k=1, num_kv_blocks=nk)
+    for h in range(2):
+        top = int(ref[h, 0])
+        idx = torch.randperm(nk, generator=g)[:700]
+        for t in (k_dup, kmin_dup, kmax_dup):
+            t[0, h, idx] = t[0, h, top]
+    run(qg, k_dup, kmin_dup, kmax_dup)
+    # (5) negative zero and sign mixtures in q
+    q_sign = qg.clone()
+    q_sign[..., ::3] = -0.0
+    run(q_sign, km, kmin, kmax)
+
+
 def test_reference_known_answers_on_gpu(cuda_device):
     """The reference tests' small known answers (tests/test_selection.py:37-129,
     tests/test_cuda_bf16_correctness.py:125-139), embedded in head_dim 64."""
@@ -520,6 +610,50 @@ def test_paged_decode_equals_contiguous(cuda_device, dtype, fmt, B, hkv, G, S, t
                                         num_splits=splits, kv_len=S, page_table=table, return_partials=True)
     assert torch.equal(got, want) and torch.equal(go, wo) and torch.equal(gml, wml)
     ext.decode_status(cuda_device)
+
+
+def test_paged_decode_at_the_128k_shape_matches_oracle(cuda_device):
+    """The long-context decode configuration at its stated size per sequence: 131072 cached tokens behind a seeded
+    random page table, 8 KV heads x 4 query heads, Quest top-10 % (205 of 2048 pages) + 4 sink + 16 local pages in
+    16 bits, the rest NVFP4, the chain count the library picks.  Two sequences run on the GPU; four (sequence, KV
+    head) rows are compared with the oracle, selection index-equal and attention within the fp16 tolerance."""
+    torch.manual_seed(31)
+    ext = _ext()
+    B, hkv, G, S, d = 2, 8, 4, 131072, 128
+    pages = S // 64
+    gen = torch.Generator(device=cuda_device).manual_seed(31)
+    q = torch.randn(B, hkv, G, d, device=cuda_device, generator=gen).half()
+    k = torch.randn(B, hkv, S, d, device=cuda_device, generator=gen).half()
+    v = torch.randn(B, hkv, S, d, device=cuda_device, generator=gen).half()
+    k[..., torch.randperm(d, device=cuda_device, generator=gen)[:4]] *= 10.0
+    top_k = oracle.resolve_top_k(pages, causal=False, fraction=0.1)
+    assert top_k == 205
+    _, kmin, kmax = ext.block_stats(k, 64, minmax=True)
+    sel = ext.select_decode_blocks(q, kmin, kmax, top_k, pages, False, sink=4, local=16)
+    q4, qs = ext.nvfp4_quantize(q)
+    k4, ks = ext.nvfp4_quantize(k)
+    v4, vs = ext.nvfp4_quantize_transposed(v)
+    n_pool = B * pages + 5
+    table = torch.randperm(n_pool, device=cuda_device, generator=gen)[:B * pages].to(torch.int32).reshape(B, pages)
+    pk4, pks, pv4, pvs, pk, pv = _to_page_pools(table, n_pool, _u8(k4), _u8(ks), _u8(v4), _u8(vs), k, v)
+    splits = ext.decode_pick_splits(B * hkv, pages)
+    out = ext.decode_attention(q, pk, pv, sel, q4, pk4, pv4, qs, pks, pvs, is_mx=False, num_splits=splits, kv_len=S,
+                               page_table=table)
+    ext.decode_status(cuda_device)
+    rows = [(0, 0), (0, 5), (1, 2), (1, 7)]
+    bi = torch.tensor([r[0] for r in rows])
+    hi = torch.tensor([r[1] for r in rows])
+    qo = q.cpu()[bi, hi].unsqueeze(0)                     # [1, 4, G, d]: the four rows as four KV heads of one sequence
+    ko = k.cpu()[bi, hi].unsqueeze(0)
+    vo = v.cpu()[bi, hi].unsqueeze(0)
+    lo, hi_ = oracle.block_stats(ko, 64, ("min", "max"))
+    sel_ref = oracle.select_decode(qo, lo, hi_, k=top_k, num_kv_blocks=pages, sink=4, local=16)
+    flat = [b * hkv + h for b, h in rows]
+    assert torch.equal(sel.cpu()[flat], sel_ref)
+    ref = oracle.decode_attention(qo, ko, vo, sel_ref, fmt="nvfp4", splits=splits)
+    got = out.cpu()[bi, hi].unsqueeze(0)
+    err = (got.float() - ref.float()).abs()
+    assert err.max().item() <= FP16_MAX_ABS and err.mean().item() <= MEAN_ABS
 
 
 @pytest.mark.parametrize("world,pages,top_k,sink,local,quest", [(2, 64, 6, 1, 2, True), (4, 256, 25, 4, 16, True),

@@ -482,7 +482,12 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
 // 512 bytes of statistics it reads are worth, so the kernel ranks in two passes whenever it pays off:
 //   pass 1  approximate scores of ALL pages with mma.sync (q split into its non-negative and negative parts,
 //           so the Quest bound is a plain GEMM against [max | min]); every approximate score is within
-//           delta = 2^-16 * max_g |q_g|_1 * max|statistics| of the exact one (exact products, fp32 sums);
+//           delta = 2^-13 * max_g |q_g|_1 * max|statistics| of the exact one.  The products of two 16-bit
+//           values are exact in fp32; what differs is the summation: the exact score rounds to nearest at
+//           each of its <= 9 additions per value (<= 9 * 2^-24 relative to sum |q k|), the tensor core adds
+//           up to 17 addends per MMA over 16 chained MMAs and its accumulation mode is not documented - a
+//           truncating adder that aligns to the largest addend loses at most 2^-23 * sum |q k| per addend,
+//           i.e. 16 * 17 * 2^-23 < 2^-14.9.  2^-13 covers both with a factor of three to spare;
 //   pass 2  exact scores only for the pages that can still reach the top k: those whose approximate score
 //           plus delta is at least the k-th largest (approximate score minus delta).
 // Pages left out are provably below the exact k-th score, so the result is the one of scoring everything
@@ -732,7 +737,7 @@ __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const ui
         }
         __syncthreads();
         const float kabs = In16<BF16>::to_f(static_cast<uint16_t>(misc[1]));
-        const float delta = __int_as_float(misc[2]) * kabs * (1.0f / 65536.0f);
+        const float delta = __int_as_float(misc[2]) * kabs * (1.0f / 8192.0f);
         // ---------------- threshold: k-th largest lower bound, by radix selection ----------------
         // ascending 32-bit image of (approx - delta); forced pages rank lowest.  Four 8-bit digits, most
         // significant first: histogram of the keys that share the prefix found so far, then the digit whose
