@@ -6,8 +6,12 @@
  * plain-C++ kernel launchers that its csrc/bindings.cpp declares (lines 56-247)
  * and calls from the 27 pybind11 functions (lines 1454-1671).  Every entry point
  * takes raw device pointers, sizes and a CUDA stream (as void*), allocates
- * nothing unless stated, holds no global mutable state and returns an int:
+ * nothing and returns an int:
  *   0 = ok, < 0 = argument error (TA100_ERR_*), > 0 = a cudaError_t value.
+ * State the library keeps per device: a status word that the decode kernels raise
+ * when a bounded wait runs out (ta100_decode_status reads and clears it) and the
+ * fixed scratch array of ta100_decode_attention_static; host side, a cache of that
+ * array's device address behind a mutex.  Everything else is re-entrant.
  * Calls are asynchronous with respect to the host unless stated otherwise.
  *
  * Conventions
@@ -40,6 +44,7 @@ extern "C" {
 #define TA100_ERR_DEVICE_TIMEOUT (-7)
 #define TA100_ERR_LIMIT (-8)
 #define TA100_ERR_STATIC_SCRATCH (-9)
+#define TA100_ERR_PAGE_TABLE (-10)
 
 int ta100_version(void);
 const char* ta100_status_string(int status);
@@ -161,7 +166,7 @@ int ta100_pack_topk_mask(const void* sel, void* mask, long long rows, int k, int
  *        re-tiled scale factors and a device status word
  *   round_partial = 1 rounds the running state to the 16-bit type between the two
  *        passes as the reference's two-kernel pipeline does
- *   max_ctas: 0 = two persistent CTAs per SM
+ *   max_ctas: 0 = one persistent CTA per SM
  * sq and skv multiples of 64, head_dim 64 or 128, skv <= 131072.  causal assumes query
  * row r sees keys <= r.
  * Replaces fp4_attention_{causal,noncausal}_{nvfp4,mxfp4} and
@@ -186,9 +191,11 @@ int ta100_prefill_status(const void* workspace, int batch, int hq, int hkv, int 
  *   K/V, contiguous cache (page_table = NULL): k4 / ks rows layout with head stride kv_cap rows
  *        (plain, not permuted), v4 / vs transposed layout with P = ceil(kv_cap/128)*128,
  *        k_hi / v_hi [B*hkv, kv_len, D] with head stride kv_cap rows
- *   K/V, paged pools (page_table int32 [B, max_pages] -> physical page): k4 [pages, hkv, 64, D/2],
- *        ks [pages, hkv, 64, D/G], v4 [pages, hkv, D, 32], vs [pages, hkv, D, 64/G],
- *        k_hi / v_hi [pages, hkv, 64, D]
+ *   K/V, paged pools (page_table int32 [B, max_pages] -> physical page in [0, pool_pages)):
+ *        k4 [pool_pages, hkv, 64, D/2], ks [pool_pages, hkv, 64, D/G], v4 [pool_pages, hkv, D, 32],
+ *        vs [pool_pages, hkv, D, 64/G], k_hi / v_hi [pool_pages, hkv, 64, D].  An entry outside the pool is
+ *        never dereferenced: the kernel leaves that page out and ta100_decode_status reports
+ *        TA100_ERR_PAGE_TABLE.  pool_pages is ignored for a contiguous cache.
  *   sel  [B*hkv, width] page ids kept in 16-bit (-1 entries ignored); width = 0 -> pure FP4
  * Chain s of `splits` walks pages [s*n/splits, (s+1)*n/splits): FP4 pages ascending, then the
  * selected pages ascending.  Partial results go to part_o [B*hkv, splits, group, D] (fp32,
@@ -204,7 +211,7 @@ int ta100_decode_pick_splits(int flat_kv_heads, int npages);
 size_t ta100_decode_workspace_bytes(int flat_kv_heads, int group, int head_dim, int splits);
 int ta100_decode_attention(const void* q_hi, const void* k_hi, const void* v_hi, const void* sel, int width,
                            const void* q4, const void* k4, const void* v4, const void* qs, const void* ks, const void* vs,
-                           const void* page_table, int max_pages, void* out, void* part_o, void* part_ml, int batch,
+                           const void* page_table, int max_pages, int pool_pages, void* out, void* part_o, void* part_ml, int batch,
                            int hkv, int group, int kv_len, int kv_cap, int head_dim, int is_mxfp4, int is_bf16, int splits,
                            int write_out, void* stream);
 
@@ -232,7 +239,7 @@ int ta100_decode_attention(const void* q_hi, const void* k_hi, const void* v_hi,
 size_t ta100_decode_static_scratch_bytes(void);
 int ta100_decode_attention_static(const void* q_hi, const void* k_hi, const void* v_hi, const void* sel, int width,
                                   const void* q4, const void* k4, const void* v4, const void* qs, const void* ks,
-                                  const void* vs, const void* page_table, int max_pages, void* out, int batch, int hkv,
+                                  const void* vs, const void* page_table, int max_pages, int pool_pages, void* out, int batch, int hkv,
                                   int group, int kv_len, int kv_cap, int head_dim, int is_mxfp4, int is_bf16, int splits,
                                   void* stream);
 
@@ -240,7 +247,8 @@ int ta100_decode_attention_static(const void* q_hi, const void* k_hi, const void
  * Device status of the decode kernels on the current device.  Every wait inside the kernel is
  * bounded; when one runs out the kernel drains, releases its tensor memory and raises a flag.
  * This call synchronises with `stream`, returns TA100_ERR_DEVICE_TIMEOUT if the flag was raised
- * since the previous call (and clears it), else TA100_OK.  The reference kernels have no
+ * since the previous call (and clears it), TA100_ERR_PAGE_TABLE if a kernel skipped a page-table
+ * entry that pointed outside the pool, else TA100_OK.  The reference kernels have no
  * counterpart: their launches are not checked at all
  * (csrc/cuda/sm120/nvfp4/single_query_attention.cu launch sites).
  */

@@ -364,9 +364,219 @@ def _check_hi(q, k, v):
 
 
 def _check_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t):
+    _check(q_packed.is_cuda and k_packed.is_cuda and v_packed_t.is_cuda, "packed Q/K/V must be CUDA tensors")
+    _check(q_scale.is_cuda and k_scale.is_cuda and v_scale_t.is_cuda, "Q/K/V scales must be CUDA tensors")
+    _check(q_packed.dim() == 4 and k_packed.dim() == 4 and v_packed_t.dim() == 4, "packed Q/K/V must be 4D tensors")
+    _check(q_packed.size(0) == k_packed.size(0), "packed Q/K batch dimensions must match")
+    _check(q_packed.size(1) % k_packed.size(1) == 0, "Q heads must be divisible by KV heads")
+    _check(q_packed.size(3) == k_packed.size(3), "packed Q/K head dimensions must match")
+
+
+_workspaces: dict = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    """Per-(device, stream) scratch buffer, grown on demand and reused across calls."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def prefill_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, *,
+                      causal, is_mx, is_bf16=False, block_size=64, k_permuted=True, round_partial=True, max_ctas=0,
+                      check_status=False, seq_major_out=False):
+    """Fused mixed-precision prefill attention (one kernel for the FP4 pass and the 16-bit pass).
+
+    ``selected_blocks`` is ``None`` (pure FP4) or int32 ``[B*Hq, Sq/block_size, W]`` with -1
+    padding.  ``k_permuted`` says whether ``k_packed`` uses the reference's row-permuted layout.
+    ``seq_major_out`` makes the kernel epilogue write ``[B, Sq, Hq, D]`` (what a Transformers attention
+    function returns) instead of ``[B, Hq, Sq, D]``.
+    """
+    _check_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t)
+    b, hq, sq, dh = q_packed.shape
+    hkv, skv = k_packed.size(1), k_packed.size(2)
+    d = dh * 2
+    _check(q_packed.is_contiguous() and q_scale.is_contiguous(), "packed Q and its scales must be contiguous")
+    _check(k_packed.stride(3) == 1 and k_packed.stride(2) == dh, "packed K rows must be dense")
+    kv_cap = k_packed.stride(1) // dh if hkv > 1 or b > 1 else max(skv, k_packed.stride(1) // dh)
+    width = 0
+    if selected_blocks is not None:
+        _check_hi(q_hi, k_hi, v_hi)
+        _check(selected_blocks.is_cuda, "selected_blocks must be a CUDA tensor")
+        _check(selected_blocks.dtype == torch.int32, "selected_blocks must be int32")
+        _check(selected_blocks.is_contiguous(), "selected_blocks must be contiguous")
+        _check(selected_blocks.dim() == 3, "selected_blocks must be [batch * heads, q_blocks, top_k]")
+        _check(selected_blocks.size(0) == b * hq, "selected_blocks first dimension must equal batch * Q heads")
+        _check(selected_blocks.size(1) == (sq + block_size - 1) // block_size,
+               "selected_blocks second dimension must equal number of Q blocks")
+        _check((skv + 63) // 64 <= 2048, f"ThriftAttention supports at most 2048 64-token KV blocks, got {(skv + 63) // 64}")
+        width = selected_blocks.size(2)
+        _check(q_hi.is_contiguous(), "Q must be contiguous")
+        want = (hkv * kv_cap * d, kv_cap * d, d, 1)
+        for t in (k_hi, v_hi):
+            _check((t.is_contiguous() and t.size(2) == kv_cap) or tuple(t.stride()) == want,
+                   "16-bit K/V must be contiguous or views of a cache with the packed K's capacity")
+    out = torch.empty((b, sq, hq, d) if seq_major_out else (b, hq, sq, d),
+                      dtype=torch.bfloat16 if is_bf16 else torch.float16, device=q_packed.device)
+    lib = _lib.load()
+    with torch.cuda.device(out.device):
+        nbytes = lib.ta100_prefill_workspace_bytes(b, hq, hkv, sq, skv, d, int(is_mx))
+        ws = _workspace(out.device, nbytes)
+        sel = selected_blocks if width > 0 else None
+        rc = lib.ta100_prefill_attention(
+            _ptr(q_hi) if sel is not None else None, _ptr(k_hi) if sel is not None else None,
+            _ptr(v_hi) if sel is not None else None, _ptr(sel), width, block_size, _ptr(q_packed), _ptr(k_packed),
+            _ptr(v_packed_t), _ptr(q_scale), _ptr(k_scale), _ptr(v_scale_t), _ptr(out), _ptr(ws), ws.numel(), b, hq, hkv,
+            sq, skv, kv_cap, d, int(causal), int(is_mx), int(is_bf16), int(k_permuted), int(round_partial), max_ctas,
+            int(seq_major_out), _stream(out))
+        _lib.check(rc, "prefill_attention")
+        if check_status:
+            _lib.check(lib.ta100_prefill_status(_ptr(ws), b, hq, hkv, sq, skv, d, int(is_mx), _stream(out)),
+                       "prefill_attention (device)")
+    return out
+
+
+def _fp4_tiled(packed, causal, is_mx, is_bf16):
+    q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t = packed
+    return prefill_attention(None, None, None, None, q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t,
+                             causal=causal, is_mx=is_mx, is_bf16=is_bf16)
+
+
+def fp4_attention_causal_nvfp4_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, is_bf16=False):
+    return _fp4_tiled((q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t), True, False, is_bf16)
+
+
+def fp4_attention_noncausal_nvfp4_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, is_bf16=False):
+    return _fp4_tiled((q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t), False, False, is_bf16)
+
+
+def fp4_attention_causal_mxfp4_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, is_bf16=False):
+    return _fp4_tiled((q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t), True, True, is_bf16)
+
+
+def fp4_attention_noncausal_mxfp4_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, is_bf16=False):
+    return _fp4_tiled((q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t), False, True, is_bf16)
+
+
+def _thrift_tiled(args, causal, is_mx, is_bf16):
+    q_hi, k_hi, v_hi, selected_blocks = args[:4]
+    return prefill_attention(q_hi, k_hi, v_hi, selected_blocks, *args[4:], causal=causal, is_mx=is_mx, is_bf16=is_bf16)
+
+
+def thrift_attention_causal_nvfp4_packed(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale,
+                                         k_scale, v_scale_t, is_bf16=False):
+    return _thrift_tiled((q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale,
+                          v_scale_t), True, False, is_bf16)
+
+
+def thrift_attention_noncausal_nvfp4_packed(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale,
+                                            k_scale, v_scale_t, is_bf16=False):
+    return _thrift_tiled((q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale,
+                          v_scale_t), False, False, is_bf16)
+
+
+def thrift_attention_causal_mxfp4_packed(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale,
+                                         k_scale, v_scale_t, is_bf16=False):
+    return _thrift_tiled((q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale,
+                          v_scale_t), True, True, is_bf16)
+
+
+def thrift_attention_noncausal_mxfp4_packed(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale,
+                                            k_scale, v_scale_t, is_bf16=False):
+    return _thrift_tiled((q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale,
+                          v_scale_t), False, True, is_bf16)
+
+
+# ---------------------------------------------------------------------------------------------
+# Decode (single query) attention  (bindings.cpp:420-486, 731-891)
+# ---------------------------------------------------------------------------------------------
+def _check_decode_args(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t,
+                       kv_len, page_table, allow_padded_selection):
+    """Argument checks shared by every decode entry (the conditions of bindings.cpp:731-810 plus the paged
+    extension).  Returns (b, hkv, g, d, skv, kv_cap, max_pages, npages, width)."""
+    _check(q_packed.is_cuda and k_packed.is_cuda and v_packed_t.is_cuda, "packed Q/K/V must be CUDA tensors")
+    _check(q_scale.is_cuda and k_scale.is_cuda and v_scale_t.is_cuda, "Q/K/V scales must be CUDA tensors")
+    _check(q_packed.dim() == 4, "packed Q must be 4D [batch, kv_heads, groups, head_dim / 2]")
+    b, hkv, g, dh = q_packed.shape
+    d = dh * 2
+    _check(1 <= g <= 16, f"single-query ThriftAttention expects grouped query length in [1, 16], got {g}")
+    _check(q_packed.is_contiguous() and q_scale.is_contiguous(), "packed Q and its scales must be contiguous")
+    if page_table is None:
+        _check(k_packed.dim() == 4 and k_packed.size(0) == b and k_packed.size(1) == hkv, "packed K shape mismatch")
+        skv = k_packed.size(2) if kv_len is None else kv_len
+        _check(k_packed.stride(3) == 1 and k_packed.stride(2) == dh, "packed K rows must be dense")
+        kv_cap = max(skv, k_packed.stride(1) // dh)
+        _check((kv_cap + 127) // 128 * 128 // 2 == v_packed_t.stride(2) or v_packed_t.size(3) * 1 == v_packed_t.stride(2),
+               "packed V row stride must equal the padded cache capacity / 2")
+        max_pages = 0
+    else:
+        _check(kv_len is not None, "kv_len is required with a page table")
+        _check(page_table.is_cuda and page_table.dtype == torch.int32 and page_table.is_contiguous()
+               and page_table.dim() == 2 and page_table.size(0) == b, "page_table must be int32 [batch, max_pages]")
+        skv, kv_cap, max_pages = kv_len, kv_len, page_table.size(1)
+        pool = k_packed.size(0)
+        _check(k_packed.dim() == 4 and k_packed.size(1) == hkv and k_packed.size(2) == 64 and k_packed.is_contiguous(),
+               "paged K codes must be a contiguous pool [pages, kv_heads, 64, head_dim / 2]")
+        _check(v_packed_t.dim() == 4 and v_packed_t.size(0) == pool and v_packed_t.is_contiguous()
+               and k_scale.size(0) == pool and v_scale_t.size(0) == pool and k_scale.is_contiguous()
+               and v_scale_t.is_contiguous(), "the K/V code and scale pools must be contiguous and hold the same number of pages")
+        _check(kv_len // 64 <= max_pages, "page_table has fewer columns than the sequence has pages")
+    _check(skv % 64 == 0, "k sequence length must be divisible by 64")
+    npages = skv // 64
+    width = 0
+    if selected_blocks is not None:
+        _check(selected_blocks.is_cuda, "selected_blocks must be a CUDA tensor")
+        _check(selected_blocks.dtype == torch.int32, "selected_blocks must be int32")
+        _check(selected_blocks.is_contiguous(), "selected_blocks must be contiguous")
+        _check(selected_blocks.dim() == 2, "selected_blocks must be [batch * grouped_heads, top_k]")
+        _check(selected_blocks.size(0) == b * hkv, "selected_blocks first dimension must equal batch * grouped_heads")
+        width = selected_blocks.size(1)
+        # a shard of a longer sequence may receive a list wider than its own page count (entries of other
+        # shards are -1)
+        _check(allow_padded_selection or 0 <= width <= npages,
+               "selected block count must be in [0, number of KV blocks]")
+        if width:
+            _check(q_hi is not None and q_hi.shape == (b, hkv, g, d), "q_hi shape must match packed Q")
+            _check(q_hi.is_contiguous(), "Q must be contiguous")
+            if page_table is None:
+                # 16-bit K/V may be views of a longer cache, as long as they share the packed K's capacity
+                want = (hkv * kv_cap * d, kv_cap * d, d, 1)
+                for t in (k_hi, v_hi):
+                    _check(t.dim() == 4 and (t.is_contiguous() and t.size(2) == kv_cap or tuple(t.stride()) == want),
+                           "16-bit K/V must be contiguous or views of a cache with the packed K's capacity")
+            else:
+                _check(k_hi.is_contiguous() and v_hi.is_contiguous() and k_hi.size(0) == k_packed.size(0)
+                       and v_hi.size(0) == k_packed.size(0),
+                       "the 16-bit K/V pools must be contiguous and hold as many pages as the code pools")
+    return b, hkv, g, d, skv, kv_cap, max_pages, npages, width
+
+
+def decode_pick_splits(flat_kv_heads: int, num_pages: int) -> int:
+    """Number of sequential KV chains per (sequence, KV head) the decode kernel uses by default."""
+    return _lib.load().ta100_decode_pick_splits(flat_kv_heads, num_pages)
+
+
+def decode_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, *,
+                     is_mx, is_bf16=False, num_splits=0, kv_len=None, page_table=None, return_partials=False,
+                     allow_padded_selection=False, partials_out=None, check_status=False):
+    """Split-KV decode attention over 64-token pages.
+
+    q_* are grouped: [B, Hkv, G, ...] with G <= 16 query heads per KV head.  K/V are either the
+    reference's contiguous, capacity-strided cache tensors (``page_table is None``) or page pools
+    ``[n_pages, Hkv, 64, ...]`` (K rows, 16-bit K/V) and ``[n_pages, Hkv, D, 32]`` (V codes) addressed
+    through ``page_table`` int32 [B, max_pages].  ``selected_blocks`` is ``None`` or int32 [B*Hkv, W].
+    Returns [B, Hkv, G, D]; with ``return_partials`` also the un-merged ``(o, ml)`` partials
+    ([B*Hkv, splits, G, D] in units of C and [B*Hkv, splits, G, 2] = (row max, row sum)).
+    ``check_status`` synchronises and raises if the kernel skipped a page-table entry outside the pool or gave up
+    a bounded wait (``decode_status``).
+    """
     b, hkv, g, d, skv, kv_cap, max_pages, npages, width = _check_decode_args(
         q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, kv_len, page_table,
         allow_padded_selection)
+    pool_pages = k_packed.size(0) if page_table is not None else 0
     lib = _lib.load()
     dev = q_packed.device
     splits = num_splits if num_splits > 0 else lib.ta100_decode_pick_splits(b * hkv, npages)
@@ -387,9 +597,11 @@ def _check_packed(q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t):
         rc = lib.ta100_decode_attention(
             _ptr(q_hi) if sel is not None else None, _ptr(k_hi) if sel is not None else None,
             _ptr(v_hi) if sel is not None else None, _ptr(sel), width, _ptr(q_packed), _ptr(k_packed), _ptr(v_packed_t),
-            _ptr(q_scale), _ptr(k_scale), _ptr(v_scale_t), _ptr(page_table), max_pages, _ptr(out), _ptr(part_o),
+            _ptr(q_scale), _ptr(k_scale), _ptr(v_scale_t), _ptr(page_table), max_pages, pool_pages, _ptr(out), _ptr(part_o),
             _ptr(part_ml), b, hkv, g, skv, kv_cap, d, int(is_mx), int(is_bf16), splits, 1, _stream(out))
     _lib.check(rc, "decode_attention")
+    if check_status:
+        decode_status(dev)
     if return_partials:
         return out, part_o, part_ml
     return out
@@ -562,7 +774,7 @@ def decode_attention_noalloc(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_pack
         rc = lib.ta100_decode_attention_static(
             _ptr(q_hi) if sel is not None else None, _ptr(k_hi) if sel is not None else None,
             _ptr(v_hi) if sel is not None else None, _ptr(sel), width, _ptr(q_packed), _ptr(k_packed), _ptr(v_packed_t),
-            _ptr(q_scale), _ptr(k_scale), _ptr(v_scale_t), None, 0, _ptr(out), b, hkv, g, skv, kv_cap, d, int(is_mx),
+            _ptr(q_scale), _ptr(k_scale), _ptr(v_scale_t), None, 0, 0, _ptr(out), b, hkv, g, skv, kv_cap, d, int(is_mx),
             int(is_bf16), splits, _stream(out))
     _lib.check(rc, "decode_attention_noalloc")
     return out

@@ -23,7 +23,7 @@ int prefill_status(const void*, int, int, int, int, int, int, int, cudaStream_t)
 int decode_pick_splits(int, int);
 size_t decode_workspace_bytes(int, int, int, int);
 int decode_dispatch(const void*, const void*, const void*, const void*, int, const void*, const void*, const void*,
-                    const void*, const void*, const void*, const void*, int, void*, void*, void*, int, int, int, int, int,
+                    const void*, const void*, const void*, const void*, int, int, void*, void*, void*, int, int, int, int, int,
                     int, int, int, int, int, cudaStream_t);
 int merge_dispatch(const void*, const void*, void*, int, long long, long long, long long, int, int, int, int, int,
                    cudaStream_t);
@@ -31,7 +31,7 @@ int reduce_partials_dispatch(const void*, const void*, void*, void*, long long, 
 int decode_status(cudaStream_t);
 size_t decode_static_scratch_bytes();
 int decode_static_dispatch(const void*, const void*, const void*, const void*, int, const void*, const void*, const void*,
-                           const void*, const void*, const void*, const void*, int, void*, int, int, int, int, int, int, int,
+                           const void*, const void*, const void*, const void*, int, int, void*, int, int, int, int, int, int, int,
                            int, int, cudaStream_t);
 int cache_append_dispatch(const void*, const void*, void*, void*, void*, void*, void*, void*, void*, void*, void*, long long,
                           int, int, int, int, int, int, int, int, int, cudaStream_t);
@@ -55,6 +55,8 @@ const char* ta100_status_string(int status) {
         case TA100_ERR_TENSOR_MAP: return "tensor map creation failed";
         case TA100_ERR_DEVICE_TIMEOUT: return "a device-side wait timed out";
         case TA100_ERR_LIMIT: return "size beyond a compiled-in limit";
+        case TA100_ERR_PAGE_TABLE:
+            return "a page-table entry pointed outside the page pool; that page was left out of the attention";
         case TA100_ERR_STATIC_SCRATCH:
             return "problem needs more split-KV scratch than the library's fixed 16 MiB array; use ta100_decode_attention";
         default: return status > 0 ? cudaGetErrorString(static_cast<cudaError_t>(status)) : "unknown status";
@@ -139,10 +141,10 @@ size_t ta100_decode_workspace_bytes(int flat_kv_heads, int group, int head_dim, 
 
 int ta100_decode_attention(const void* q_hi, const void* k_hi, const void* v_hi, const void* sel, int width,
                            const void* q4, const void* k4, const void* v4, const void* qs, const void* ks, const void* vs,
-                           const void* page_table, int max_pages, void* out, void* part_o, void* part_ml, int batch,
+                           const void* page_table, int max_pages, int pool_pages, void* out, void* part_o, void* part_ml, int batch,
                            int hkv, int group, int kv_len, int kv_cap, int head_dim, int is_mxfp4, int is_bf16, int splits,
                            int write_out, void* stream) {
-    return decode_dispatch(q_hi, k_hi, v_hi, sel, width, q4, k4, v4, qs, ks, vs, page_table, max_pages, out, part_o,
+    return decode_dispatch(q_hi, k_hi, v_hi, sel, width, q4, k4, v4, qs, ks, vs, page_table, max_pages, pool_pages, out, part_o,
                            part_ml, batch, hkv, group, kv_len, kv_cap, head_dim, is_mxfp4, is_bf16, splits, write_out,
                            S(stream));
 }
@@ -161,7 +163,7 @@ int ta100_cached_decode_step(const void* q, void* q4, void* qs, const void* k_hi
                                     stat_cap_blocks, head_dim, top_k, stat_b != nullptr, is_bf16, sink, local, 0, S(stream));
         if (rc != TA100_OK) return rc;
     }
-    return decode_dispatch(q, k_hi, v_hi, width > 0 ? sel : nullptr, width, q4, k4, v4t, qs, ks, vst, nullptr, 0, out, part_o,
+    return decode_dispatch(q, k_hi, v_hi, width > 0 ? sel : nullptr, width, q4, k4, v4t, qs, ks, vst, nullptr, 0, 0, out, part_o,
                            part_ml, batch, hkv, group, kv_len, kv_cap, head_dim, is_mxfp4, is_bf16, splits, 1, S(stream));
 }
 
@@ -183,10 +185,10 @@ size_t ta100_decode_static_scratch_bytes(void) { return decode_static_scratch_by
 
 int ta100_decode_attention_static(const void* q_hi, const void* k_hi, const void* v_hi, const void* sel, int width,
                                   const void* q4, const void* k4, const void* v4, const void* qs, const void* ks,
-                                  const void* vs, const void* page_table, int max_pages, void* out, int batch, int hkv,
+                                  const void* vs, const void* page_table, int max_pages, int pool_pages, void* out, int batch, int hkv,
                                   int group, int kv_len, int kv_cap, int head_dim, int is_mxfp4, int is_bf16, int splits,
                                   void* stream) {
-    return decode_static_dispatch(q_hi, k_hi, v_hi, sel, width, q4, k4, v4, qs, ks, vs, page_table, max_pages, out, batch,
+    return decode_static_dispatch(q_hi, k_hi, v_hi, sel, width, q4, k4, v4, qs, ks, vs, page_table, max_pages, pool_pages, out, batch,
                                   hkv, group, kv_len, kv_cap, head_dim, is_mxfp4, is_bf16, splits, S(stream));
 }
 

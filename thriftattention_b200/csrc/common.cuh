@@ -22,6 +22,7 @@ enum Status : int {
     TA100_ERR_DEVICE_TIMEOUT = -7,
     TA100_ERR_LIMIT = -8,
     TA100_ERR_STATIC_SCRATCH = -9,
+    TA100_ERR_PAGE_TABLE = -10,
 };
 
 constexpr int NUM_SMS_HINT = 148;

@@ -64,7 +64,8 @@ constexpr uint32_t DTM_COLS = 256;
 
 constexpr uint32_t L_FP16 = 0x80000000u;  // page-list flag: 16-bit page
 
-__device__ int g_decode_status;           // set to 1 by a kernel whose bounded wait ran out
+__device__ int g_decode_status;           // wait site of a kernel whose bounded wait ran out, or STATUS_BAD_PAGE
+constexpr int STATUS_BAD_PAGE = 1000;    // a page-table entry outside the pool was skipped
 
 // Optional phase timers for the softmax warps (development aid; compiled out by default).
 #ifdef TA100_PROFILE_SOFTMAX
@@ -88,7 +89,7 @@ struct DecodeParams {
     const int32_t* page_table;  // [batch, max_pages] or null
     float* part_o;          // [heads, splits, G, D]
     float* part_ml;         // [heads, splits, G, 2]
-    int heads, hkv, G, npages, cap_pages, max_pages, width, splits;
+    int heads, hkv, G, npages, cap_pages, max_pages, pool_pages, width, splits;
     int vs_row_stride;      // bytes between channel rows of vs (contiguous layout)
     float c2;               // (1/sqrt(d)) * log2(e)
     float sm_scale;         // 1/sqrt(d)
@@ -127,6 +128,7 @@ struct DecBars {
     uint32_t tmem_base;
     int abort_flag;
     int abort_code;     // which wait gave up first (development aid, reported through the status word)
+    int bad_entry;      // a page-table entry pointed outside the pool
     float m_row[DEC_MAX_GROUP];
     float l_part[4][DEC_MAX_GROUP];
 };
@@ -164,8 +166,10 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 // Page list of one chain (whole warp): FP4 pages ascending, then the selected pages ascending.
 // An entry is the page's addressing key — the physical page times hkv plus the KV head for a page
 // pool, the logical page for a contiguous cache — with L_FP16 set on 16-bit pages.
+// A page-table entry outside [0, pool_pages) never becomes a key: the page is left out of the chain
+// (nothing is read for it) and *bad_entry is raised so that the host learns of it.
 __device__ void build_page_list(const DecodeParams& p, int h, int b, int kvh, int p_begin, int p_end, uint32_t* bits,
-                                uint32_t* list, int& n_fp4, int& n_total, int lane) {
+                                uint32_t* list, int& n_fp4, int& n_total, int lane, int* bad_entry) {
     for (int i = lane; i < 64; i += 32) bits[i] = 0u;
     __syncwarp();
     for (int i = lane; i < p.width; i += 32) {
@@ -179,15 +183,19 @@ __device__ void build_page_list(const DecodeParams& p, int h, int b, int kvh, in
             const int pg = base + lane;
             const bool valid = pg < p_end;
             const bool is_sel = valid && ((bits[pg >> 5] >> (pg & 31)) & 1u);
-            const bool take = valid && (is_sel == (pass == 1));
-            const uint32_t mask = __ballot_sync(0xFFFFFFFFu, take);
-            if (take) {
-                uint32_t key = static_cast<uint32_t>(pg);
-                if (p.page_table)
-                    key = static_cast<uint32_t>(p.page_table[static_cast<long long>(b) * p.max_pages + pg]) *
-                              static_cast<uint32_t>(p.hkv) + static_cast<uint32_t>(kvh);
-                list[n + __popc(mask & ((1u << lane) - 1u))] = key | (pass ? L_FP16 : 0u);
+            bool take = valid && (is_sel == (pass == 1));
+            uint32_t key = static_cast<uint32_t>(pg);
+            if (take && p.page_table) {
+                const int entry = p.page_table[static_cast<long long>(b) * p.max_pages + pg];
+                if (entry < 0 || entry >= p.pool_pages) {
+                    take = false;
+                    *bad_entry = 1;
+                } else {
+                    key = static_cast<uint32_t>(entry) * static_cast<uint32_t>(p.hkv) + static_cast<uint32_t>(kvh);
+                }
             }
+            const uint32_t mask = __ballot_sync(0xFFFFFFFFu, take);
+            if (take) list[n + __popc(mask & ((1u << lane) - 1u))] = key | (pass ? L_FP16 : 0u);
             n += __popc(mask);
         }
         if (pass == 0) n_fp4 = n;
@@ -252,6 +260,7 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
         mbar_fence_init();
         bars.abort_flag = (sbase & 1023u) ? 1 : 0;
         bars.abort_code = 0;
+        bars.bad_entry = 0;
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(&bars.tmem_base), DTM_COLS);
@@ -269,7 +278,7 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
             if (p.width > 0) { tma_prefetch_desc(&mapK16); tma_prefetch_desc(&mapV16); }
         }
         int n_fp4 = 0, n = 0;
-        build_page_list(p, h, b, kvh, p_begin, p_end, reinterpret_cast<uint32_t*>(smem + L::BITS), list, n_fp4, n, lane);
+        build_page_list(p, h, b, kvh, p_begin, p_end, reinterpret_cast<uint32_t*>(smem + L::BITS), list, n_fp4, n, lane, &bars.bad_entry);
         if (lane == 0) { bars.n_fp4 = n_fp4; bars.n_total = n; }
         __syncwarp();
         __threadfence_block();
@@ -750,6 +759,7 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, DTM_COLS);
     if (tid == 0 && bars.abort_flag != 0) atomicCAS(&g_decode_status, 0, bars.abort_code != 0 ? bars.abort_code : 99);
+    if (tid == 0 && bars.bad_entry != 0) atomicCAS(&g_decode_status, 0, STATUS_BAD_PAGE);
 }
 
 // out[row, :] = sum_s O_s e^{m_s - M} / (C sum_s l_s e^{m_s - M}); rows = heads * G
@@ -850,9 +860,10 @@ int decode_status(cudaStream_t stream) {
     e = cudaMemcpyFromSymbol(&flag, g_decode_status, sizeof(int));
     if (e != cudaSuccess) return static_cast<int>(e);
     if (flag != 0) {
-        fprintf(stderr, "libthrift_sm100: a decode kernel gave up waiting (wait site %d)\n", flag);
         const int zero = 0;
         cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int));
+        if (flag == STATUS_BAD_PAGE) return TA100_ERR_PAGE_TABLE;
+        fprintf(stderr, "libthrift_sm100: a decode kernel gave up waiting (wait site %d)\n", flag);
         return TA100_ERR_DEVICE_TIMEOUT;
     }
     return TA100_OK;
@@ -861,8 +872,8 @@ int decode_status(cudaStream_t stream) {
 // See include/thrift_sm100.h (ta100_decode_attention).
 int decode_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const void* sel, int width, const void* q4,
                     const void* k4, const void* v4, const void* qs, const void* ks, const void* vs, const void* page_table,
-                    int max_pages, void* out, void* part_o, void* part_ml, int batch, int hkv, int G, int kv_len, int kv_cap,
-                    int d, int is_mx, int is_bf16, int splits, int write_out, cudaStream_t stream) {
+                    int max_pages, int pool_pages, void* out, void* part_o, void* part_ml, int batch, int hkv, int G, int kv_len,
+                    int kv_cap, int d, int is_mx, int is_bf16, int splits, int write_out, cudaStream_t stream) {
     if (!q4 || !k4 || !v4 || !qs || !ks || !vs || !part_o || !part_ml) return TA100_ERR_NULL;
     if (write_out && !out) return TA100_ERR_NULL;
     if (width > 0 && (!q_hi || !k_hi || !v_hi || !sel)) return TA100_ERR_NULL;
@@ -884,9 +895,11 @@ int decode_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const 
     const int GRP = is_mx ? 32 : 16;
     const int P = cdiv(kv_cap, 128) * 128;
     const bool paged = page_table != nullptr;
-    // a page pool's size is not part of the interface: its tensor maps get the largest slab count, the page
-    // table is what keeps the accesses inside the pool
-    const uint64_t pool_slabs = 0x7FFFFFFFull;
+    // a pool holds pool_pages x hkv slabs of one page each; the tensor maps end there and the kernel skips
+    // page-table entries that point beyond it
+    if (paged && (pool_pages <= 0 || max_pages < npages || static_cast<long long>(pool_pages) * hkv >= 0x7FFFFFFFll))
+        return TA100_ERR_SHAPE;
+    const uint64_t pool_slabs = paged ? static_cast<uint64_t>(pool_pages) * hkv : 1;
 
     CUtensorMap maps[4];
     memset(maps, 0, sizeof(maps));
@@ -926,7 +939,7 @@ int decode_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const 
     p.ks = static_cast<const uint8_t*>(ks); p.vs = static_cast<const uint8_t*>(vs);
     p.sel = static_cast<const int32_t*>(sel); p.page_table = static_cast<const int32_t*>(page_table);
     p.part_o = static_cast<float*>(part_o); p.part_ml = static_cast<float*>(part_ml);
-    p.heads = heads; p.hkv = hkv; p.G = G; p.npages = npages; p.cap_pages = kv_cap / PAGE; p.max_pages = max_pages;
+    p.heads = heads; p.hkv = hkv; p.G = G; p.npages = npages; p.cap_pages = kv_cap / PAGE; p.max_pages = max_pages; p.pool_pages = pool_pages;
     p.width = width; p.splits = splits;
     p.vs_row_stride = P / GRP;
     p.sm_scale = static_cast<float>(1.0 / sqrt(static_cast<double>(d)));
@@ -1047,9 +1060,11 @@ size_t decode_static_scratch_bytes() { return STATIC_SCRATCH_BYTES; }
 // (different streams) would race on it.
 int decode_static_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const void* sel, int width, const void* q4,
                            const void* k4, const void* v4, const void* qs, const void* ks, const void* vs,
-                           const void* page_table, int max_pages, void* out, int batch, int hkv, int G, int kv_len,
-                           int kv_cap, int d, int is_mx, int is_bf16, int splits, cudaStream_t stream) {
+                           const void* page_table, int max_pages, int pool_pages, void* out, int batch, int hkv, int G,
+                           int kv_len, int kv_cap, int d, int is_mx, int is_bf16, int splits, cudaStream_t stream) {
     if (batch <= 0 || hkv <= 0 || G <= 0 || splits <= 0 || d <= 0) return TA100_ERR_SHAPE;
+    // bound every factor before multiplying them
+    if (G > DEC_MAX_GROUP || d > 128 || splits > 4096 || static_cast<long long>(batch) * hkv > 65535) return TA100_ERR_STATIC_SCRATCH;
     const size_t n_o = static_cast<size_t>(batch) * hkv * splits * G * d * sizeof(float);
     const size_t n_ml = static_cast<size_t>(batch) * hkv * splits * G * 2 * sizeof(float);
     const size_t off_ml = (n_o + 255) & ~static_cast<size_t>(255);
@@ -1058,7 +1073,7 @@ int decode_static_dispatch(const void* q_hi, const void* k_hi, const void* v_hi,
     const int rc = static_scratch_address(&base);
     if (rc != TA100_OK) return rc;
     unsigned char* b = static_cast<unsigned char*>(base);
-    return decode_dispatch(q_hi, k_hi, v_hi, sel, width, q4, k4, v4, qs, ks, vs, page_table, max_pages, out, b, b + off_ml,
+    return decode_dispatch(q_hi, k_hi, v_hi, sel, width, q4, k4, v4, qs, ks, vs, page_table, max_pages, pool_pages, out, b, b + off_ml,
                            batch, hkv, G, kv_len, kv_cap, d, is_mx, is_bf16, splits, 1, stream);
 }
 

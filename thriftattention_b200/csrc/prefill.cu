@@ -1,23 +1,43 @@
 // Fused selective mixed-precision prefill attention for sm_100a.
 //
-// Persistent CTAs (two per SM) walk (q head, 128-row q tile) work items, longest
-// first.  Per item the KV sequence is consumed in 64-column steps:
-//   phase A  every step whose KV block is NOT selected: block-scaled FP4
+// One persistent CTA per SM walks (q head, 128-row q tile) work items, longest
+// first.  Per item the KV sequence is consumed in 64-column sub-steps:
+//   phase A  every sub-step whose KV block is NOT selected: block-scaled FP4
 //            tcgen05 MMAs (S = Q4 K4^T, O += P4 V4) with P quantised to e2m1;
 //   phase B  the selected blocks in list order: f16/bf16 tcgen05 MMAs.
-// Both phases share one online softmax whose state (row max, row sum) lives in
-// registers and whose accumulator O lives in tensor memory for the whole item.
+// Both phases share one online softmax whose accumulator O lives in tensor memory
+// for the whole item.
 //
-// Warp roles (192 threads): warp 0 = TMA producer (it also builds the item's
-// step list in shared memory), warp 1 = MMA issuer and tensor-memory owner,
-// warps 2..5 = softmax (one thread per q row; warp w owns tensor-memory lanes
-// 32*(w%4)..+31).  Two CTAs share an SM so that the softmax warps of one hide
-// the tensor-memory and barrier latencies of the other.
+// The softmax is what bounds this kernel (one ex2 per score on a unit that retires
+// 16 per cycle and SM), and a warp that runs a sub-step spends more time waiting -
+// for S to land in tensor memory, for the previous P V to finish, for its own
+// dependent instructions - than it spends in that unit.  So the sub-steps of an
+// item are dealt round robin to FOUR sets of softmax warps: sub-step n of the CTA
+// belongs to set n mod 4, has its own S buffer in tensor memory (4 x 64 columns)
+// and its own P tile in shared memory, and each scheduler of the SM holds four
+// softmax warps that are in four different sub-steps.  What ties consecutive
+// sub-steps together is small and is handed from set to set through shared memory:
+//   * the running row maximum (a chain of 32-arrival mbarriers per 32-row group);
+//   * the rescale of O when a maximum moved: set n does it after P V of sub-step
+//     n-1 completed and before it releases its own P tile, so the order in which
+//     the reference updates its state is kept exactly;
+//   * the row sum, which every set keeps for its own sub-steps (relative to the
+//     maximum it saw last) and which is added up once per item.
+//
+// Warp roles (640 threads): warp 0 = TMA producer (it also builds the item's
+// sub-step list in shared memory), warp 1 = issuer of the S = Q K^T MMAs and
+// tensor-memory owner, warp 2 = issuer of the O += P V MMAs, warps 3..18 =
+// softmax (one thread per q row; warp w owns tensor-memory lanes 32*(w%4)..+31
+// and belongs to set (w-3)/4).
 //
 // Every mbarrier wait is bounded; a timeout raises a CTA-wide abort flag, all
-// roles drain, tensor memory is released and a status word is set.
+// roles drain, tensor memory is released and a status word is set.  A parity
+// wait is only sound for a waiter that sees every phase of its barrier, so every
+// waiter here waits on each phase of the barriers it uses, also where the value
+// behind the barrier is not needed.
 #include <cfloat>
 #include <climits>
+#include <type_traits>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -26,37 +46,26 @@ namespace ta100 {
 
 namespace {
 
-// Optional phase timers for the softmax warps (development aid; compiled out by default).
-#ifdef TA100_PROFILE_SOFTMAX
-__device__ long long g_prof[16];
-#define TA100_PROF_DECL long long prof_t = clock64(), prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long prof_steps = 0;
-#define TA100_PROF(i) { const long long now_ = clock64(); prof_acc[i] += now_ - prof_t; prof_t = now_; }
-#define TA100_PROF_STEP ++prof_steps;
-#define TA100_PROF_DUMP if (blockIdx.x == 0 && warp == 2 && lane == 0) { for (int i_ = 0; i_ < 10; ++i_) g_prof[i_] = prof_acc[i_]; g_prof[10] = prof_steps; }
-#else
-#define TA100_PROF_DECL
-#define TA100_PROF(i)
-#define TA100_PROF_STEP
-#define TA100_PROF_DUMP
-#endif
 
 constexpr int QTILE = 128;
 constexpr int STEP = 64;
-constexpr int NSLOTS = 3;            // K/V ring slots
-constexpr int SLOT_BYTES = 16384;    // one FP4 step (K4, V4, scale atoms) or one 16-bit K or V tile
-constexpr int NUM_THREADS = 192;
-constexpr int SCHED_CAP = 2944;      // step-list entries per work item
+constexpr int NSETS = 4;             // softmax warp sets = S buffers = P tiles
+constexpr int NSLOTS = 6;            // K/V ring slots
+constexpr int SLOT_BYTES = 16384;    // one FP4 sub-step (K4, V4, scale atoms) or one 16-bit K or V tile
+constexpr int PSET_BYTES = 16384;    // P tile of a set: 4 KB of e2m1 or 16 KB of 16-bit values
+constexpr int NUM_THREADS = 32 * (3 + 4 * NSETS);   // 608: 104 registers per thread fit the SM's register file
+constexpr int SCHED_CAP = 2944;      // sub-step list entries per work item
 
-// tensor-memory columns (256 allocated per CTA)
-constexpr uint32_t TM_O = 0;
-constexpr uint32_t TM_S = 128;       // 64 columns
-constexpr uint32_t TM_SFA_Q = 192;   // up to 8 columns
-constexpr uint32_t TM_SFB_K = 200;   // 8 columns
-constexpr uint32_t TM_SFA_P = 208;   // 4 columns, constant
-constexpr uint32_t TM_SFB_V = 212;   // two slots of 4 columns
-constexpr uint32_t TM_COLS = 256;
+// tensor-memory columns (all 512 of the SM)
+constexpr uint32_t TM_O = 0;         // 128 columns
+constexpr uint32_t TM_S = 128;       // NSETS buffers of 64 columns
+constexpr uint32_t TM_SFA_Q = 384;   // up to 8 columns
+constexpr uint32_t TM_SFA_P = 392;   // 4 columns, constant
+constexpr uint32_t TM_SFB_K = 400;   // NSETS buffers of 8 columns
+constexpr uint32_t TM_SFB_V = 432;   // NSETS buffers of 4 columns
+constexpr uint32_t TM_COLS = 512;
 
-// step-list entry: bits 0..11 step index, 12 = 16-bit step, 13 / 14 = rows 0..63 / 64..127 take part
+// sub-step list entry: bits 0..11 sub-step index, 12 = 16-bit, 13 / 14 = rows 0..63 / 64..127 take part
 constexpr uint32_t E_FP16 = 1u << 12, E_P0 = 1u << 13, E_P1 = 1u << 14;
 
 struct PrefillParams {
@@ -83,28 +92,44 @@ struct Smem {
     static constexpr int Q4 = 0;                       // 128 x D/2
     static constexpr int QSF = Q4 + QTILE * D / 2;     // up to 2 atoms
     static constexpr int Q16 = QSF + 1024;             // 128 x D x 2
-    static constexpr int P = Q16 + QTILE * D * 2;      // 16 KB: two 4 KB FP4 buffers or one 16-bit tile
-    static constexpr int SLOTS = P + 16384;
+    static constexpr int P = Q16 + QTILE * D * 2;      // NSETS tiles
+    static constexpr int SLOTS = P + NSETS * PSET_BYTES;
     static constexpr int CSF = SLOTS + NSLOTS * SLOT_BYTES;    // constant scale atom (512 B)
     static constexpr int BITS = CSF + 512;                     // 2 halves x 64 words
-    static constexpr int BARS = BITS + 2 * 64 * 4;             // mbarriers and CTA-wide flags (256 B)
-    static constexpr int SCHED = BARS + 256;                   // SCHED_CAP x u16
-    static constexpr int TOTAL = SCHED + SCHED_CAP * 2;        // 112 KB: two CTAs fit one SM
+    static constexpr int BARS = BITS + 2 * 64 * 4;             // mbarriers and CTA-wide flags (1 KB)
+    static constexpr int XCH = BARS + 1024;                    // row maxima and row sums handed between sets
+    static constexpr int SCHED = XCH + sizeof(float) * 4 * NSETS * 32 * 5;   // SCHED_CAP x u16
+    static constexpr int TOTAL = SCHED + SCHED_CAP * 2;
     // inside an FP4 slot
     static constexpr int K4 = 0, V4 = 4096, KSF = 8192, VSF = 9216;
+    static_assert(Q16 % 1024 == 0 && P % 1024 == 0 && SLOTS % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+    static_assert(TOTAL <= 227 * 1024, "one CTA must fit the SM's shared memory");
 };
 
 struct Bars {
     uint64_t q_full, q_empty;
     uint64_t sched_full, sched_empty;
+    uint64_t o_full;                                   // last P V of the item complete
     uint64_t slot_full[NSLOTS], slot_empty[NSLOTS];
-    uint64_t s_full, s_free;
-    uint64_t p_full[2], p_free[2];
-    int sched_n;
+    uint64_t s_full[NSETS], s_free[NSETS];
+    uint64_t p_full[NSETS], p_free[NSETS];
+    uint64_t mch[4][NSETS];                            // row maxima of (row group, set) published
+    uint64_t trans[4];                                 // row sums of a row group published for the state rounding
+    uint64_t lend[4];                                  // ... and for the end of the item
+    int sched_n, sched_na;                             // entries; entries before the first 16-bit one
     uint32_t tmem_base;
     int abort_flag;
 };
-static_assert(sizeof(Bars) <= 256, "barrier block must fit its shared-memory slot");
+static_assert(sizeof(Bars) <= 1024, "barrier block must fit its shared-memory slot");
+
+// what the sets of one 32-row group hand to each other: [row group][set][lane]
+struct Xch {
+    float mrun[4][NSETS][32];       // running maximum after the set's latest sub-step
+    float l_end[4][NSETS][32];      // row sum and its reference maximum at the end of the item
+    float m_end[4][NSETS][32];
+    float l_tr[4][NSETS][32];       // the same at the hand-over from the FP4 to the 16-bit phase
+    float m_tr[4][NSETS][32];
+};
 
 struct ItemInfo {
     int h, t, kvh;
@@ -122,11 +147,13 @@ __device__ __forceinline__ ItemInfo decode_item(const PrefillParams& p, int item
 
 __device__ __forceinline__ bool bit_of(const uint32_t* b, int i) { return (b[i >> 5] >> (i & 31)) & 1u; }
 
-// Builds the step list of one work item (whole warp).  Order: every step whose
+// Builds the sub-step list of one work item (whole warp).  Order: every sub-step whose
 // block is not selected, ascending; then the selected blocks of the first
 // 64-row half in list order; then those of the second half that were not
-// already visited.  Returns the number of entries, or -1 if the list overflows.
-__device__ int build_schedule(const PrefillParams& p, const ItemInfo& it, uint32_t* bits, uint16_t* sched, int lane) {
+// already visited.  Returns the number of entries, or -1 if the list overflows;
+// n_fp4 receives the number of entries of the first kind.
+__device__ int build_schedule(const PrefillParams& p, const ItemInfo& it, uint32_t* bits, uint16_t* sched, int lane,
+                              int& n_fp4) {
     const int nqb = p.sq / p.block;
     const int row0 = it.t * QTILE;
     const int qb0 = row0 / p.block;
@@ -176,6 +203,7 @@ __device__ int build_schedule(const PrefillParams& p, const ItemInfo& it, uint32
         if (keep && pos < SCHED_CAP) sched[pos] = static_cast<uint16_t>(st | (p0 ? E_P0 : 0) | (p1 ? E_P1 : 0));
         n += __popc(m);
     }
+    n_fp4 = n;
     // ---- phase B ----
     if (has_sel) {
         for (int pass = 0; pass < (two ? 2 : 1); ++pass) {
@@ -275,7 +303,7 @@ __device__ __forceinline__ float exp_scaled_64(float (&s)[STEP], float c2, float
 }
 
 template <int D, bool MX, bool BF16, bool CAUSAL, bool KPERM>
-__global__ void __launch_bounds__(NUM_THREADS, 2)
+__global__ void __maxnreg__(104)   // 19 warps x 104 registers fill the SM's register file
 prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4, const __grid_constant__ CUtensorMap mapK4,
                const __grid_constant__ CUtensorMap mapV4, const __grid_constant__ CUtensorMap mapQ16,
                const __grid_constant__ CUtensorMap mapK16, const __grid_constant__ CUtensorMap mapV16) {
@@ -294,6 +322,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
     // 128-byte swizzled tiles need (checked below).
     extern __shared__ __align__(1024) uint8_t smem[];
     Bars& bars = *reinterpret_cast<Bars*>(smem + L::BARS);
+    Xch& xch = *reinterpret_cast<Xch*>(smem + L::XCH);
     int& abort_flag = bars.abort_flag;
     uint32_t& tmem_base_s = bars.tmem_base;
 
@@ -307,16 +336,22 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
         mbar_init(smem_u32(&bars.q_full), 1);
         mbar_init(smem_u32(&bars.q_empty), 1);
         mbar_init(smem_u32(&bars.sched_full), 1);
-        mbar_init(smem_u32(&bars.sched_empty), 5);
-        mbar_init(smem_u32(&bars.s_full), 1);
-        mbar_init(smem_u32(&bars.s_free), 128);
+        mbar_init(smem_u32(&bars.sched_empty), 2 + 4 * NSETS);
+        mbar_init(smem_u32(&bars.o_full), 1);
         for (int i = 0; i < NSLOTS; ++i) {
             mbar_init(smem_u32(&bars.slot_full[i]), 1);
             mbar_init(smem_u32(&bars.slot_empty[i]), 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < NSETS; ++i) {
+            mbar_init(smem_u32(&bars.s_full[i]), 1);
+            mbar_init(smem_u32(&bars.s_free[i]), 128);
             mbar_init(smem_u32(&bars.p_full[i]), 128);
             mbar_init(smem_u32(&bars.p_free[i]), 1);
+        }
+        for (int g = 0; g < 4; ++g) {
+            for (int i = 0; i < NSETS; ++i) mbar_init(smem_u32(&bars.mch[g][i]), 32);
+            mbar_init(smem_u32(&bars.trans[g]), 32 * NSETS);
+            mbar_init(smem_u32(&bars.lend[g]), 32 * NSETS);
         }
         mbar_fence_init();
         abort_flag = (sbase & 1023u) ? 1 : 0;
@@ -345,12 +380,13 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
         bool ok = true;
         for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
             const ItemInfo it = decode_item(p, item);
-            // ---- step list (consumers must be done with the previous one) ----
+            // ---- sub-step list (consumers must be done with the previous one) ----
             ok = mbar_wait(smem_u32(&bars.sched_empty), (n_item & 1) ^ 1, abortp, budget);
             if (!ok) break;
-            const int n = build_schedule(p, it, reinterpret_cast<uint32_t*>(smem + L::BITS), sched, lane);
+            int n_fp4 = 0;
+            const int n = build_schedule(p, it, reinterpret_cast<uint32_t*>(smem + L::BITS), sched, lane, n_fp4);
             if (n < 0) { abort_flag = 1; ok = false; break; }
-            if (lane == 0) bars.sched_n = n;
+            if (lane == 0) { bars.sched_n = n; bars.sched_na = n_fp4; }
             __syncwarp();
             __threadfence_block();
             if (lane == 0) mbar_arrive(smem_u32(&bars.sched_full));
@@ -368,7 +404,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                     for (int hf = 0; hf < HALVES; ++hf)
                         tma_load_3d(sbase + L::Q16 + hf * QTILE * 128, &mapQ16, bar, hf * 64, it.t * QTILE, it.h);
             }
-            // ---- K/V steps ----
+            // ---- K/V sub-steps ----
             for (int i = 0; i < n && ok; ++i) {
                 const uint32_t e = sched[i];
                 const int st = e & 0xFFF;
@@ -405,44 +441,12 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
             }
         }
     } else if (warp == 1) {
-        // =========================== MMA issuer ===========================
-        tmem_cp_sf_elect(tmem + TM_SFA_P, make_smem_desc(sbase + L::CSF, 0, 128, SWZ_NONE));
-        uint32_t gstep = 0, gslot = 0;
+        // =========================== S = Q K^T issuer ===========================
+        uint32_t gsub = 0, gslot = 0;     // sub-steps and ring slots consumed so far by this CTA
         int n_item = 0;
         bool ok = true;
         const uint32_t idesc_qk4 = make_idesc_fp4(128, STEP, MX ? 1 : 0, 0, 0);
-        const uint32_t idesc_pv4 = make_idesc_fp4(128, D, MX ? 1 : 0, 0, 0);
         const uint32_t idesc_qk16 = make_idesc_f16(128, STEP, BF16 ? 1 : 0, 0, 0);
-        const uint32_t idesc_pv16 = make_idesc_f16(128, D, BF16 ? 1 : 0, 0, 1);
-
-        // S = Q K^T for the step described by `e`, operands in ring slot `slot` (whole warp, one lane issues)
-        auto issue_qk = [&](uint32_t e, uint32_t slot) {
-            const uint32_t sa = sbase + L::SLOTS + slot * SLOT_BYTES;
-            const uint32_t d_t = tmem + TM_S;
-            if (!(e & E_FP16)) {
-                const uint32_t sfb = tmem + TM_SFB_K;
-                for (int a = 0; a < QK_ATOMS; ++a)
-                    tmem_cp_sf_elect(sfb + a * 4, make_smem_desc(sa + L::KSF + a * 512, 0, 128, SWZ_NONE));
-                for (int kb = 0; kb < KBLK; ++kb) {
-                    const uint64_t ad = make_smem_desc(sbase + L::Q4 + kb * 32, 16, SBO_QK, SWZ_QK);
-                    const uint64_t bd = make_smem_desc(sa + L::K4 + kb * 32, 16, SBO_QK, SWZ_QK);
-                    if constexpr (MX)
-                        mma_mxfp4_elect(d_t, ad, bd, make_idesc_fp4(128, STEP, 1, kb * 2, kb * 2), tmem + TM_SFA_Q, sfb, kb > 0);
-                    else
-                        mma_nvfp4_elect(d_t, ad, bd, idesc_qk4, tmem + TM_SFA_Q + kb * 4, sfb + kb * 4, kb > 0);
-                }
-            } else {
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t hf = ks / 4, kk = ks % 4;
-                    const uint64_t ad = make_smem_desc(sbase + L::Q16 + hf * QTILE * 128 + kk * 32, 16, 1024, SWZ_128B);
-                    const uint64_t bd = make_smem_desc(sa + hf * STEP * 128 + kk * 32, 16, 1024, SWZ_128B);
-                    mma_f16_elect(d_t, ad, bd, idesc_qk16, ks > 0);
-                }
-                tc_commit_elect(smem_u32(&bars.slot_empty[slot]));  // the K tile is free once S is computed
-            }
-            tc_commit_elect(smem_u32(&bars.s_full));
-        };
-
         for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
             ok = mbar_wait(smem_u32(&bars.sched_full), n_item & 1, abortp, budget);
             if (!ok) break;
@@ -451,113 +455,146 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
             if (!ok) break;
             tc_fence_after_sync();
             for (int a = 0; a < QK_ATOMS; ++a)
-                    tmem_cp_sf_elect(tmem + TM_SFA_Q + a * 4, make_smem_desc(sbase + L::QSF + a * 512, 0, 128, SWZ_NONE));
+                tmem_cp_sf_elect(tmem + TM_SFA_Q + a * 4, make_smem_desc(sbase + L::QSF + a * 512, 0, 128, SWZ_NONE));
             if (n == 0 && lane == 0) mbar_arrive(smem_u32(&bars.q_empty));
-
-            // slot bookkeeping: an FP4 step owns one slot, a 16-bit step a K slot then a V slot
-            uint32_t qk_slot = gslot;        // slot of the step whose QK is issued next
-            if (n > 0) {
-                const uint32_t e0 = sched[0];
-                ok = mbar_wait(smem_u32(&bars.slot_full[qk_slot % NSLOTS]), (qk_slot / NSLOTS) & 1, abortp, budget) &&
-                     mbar_wait(smem_u32(&bars.s_free), (gstep & 1) ^ 1, abortp, budget);
-                if (ok) {
-                    tc_fence_after_sync();
-                    issue_qk(e0, qk_slot % NSLOTS);
-                }
-            }
             for (int i = 0; i < n && ok; ++i) {
                 const uint32_t e = sched[i];
                 const bool fp16 = e & E_FP16;
-                const uint32_t my_slot = qk_slot;                 // FP4: the step's slot; 16-bit: its K slot
-                const uint32_t pv_slot = fp16 ? my_slot + 1 : my_slot;
-                qk_slot = pv_slot + 1;
-                // look ahead: S of the next step as soon as the softmax warps have read this one
-                if (i + 1 < n) {
-                    const uint32_t e1 = sched[i + 1];
-                    ok = mbar_wait(smem_u32(&bars.slot_full[qk_slot % NSLOTS]), (qk_slot / NSLOTS) & 1, abortp, budget) &&
-                         mbar_wait(smem_u32(&bars.s_free), ((gstep + 1) & 1) ^ 1, abortp, budget);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_qk(e1, qk_slot % NSLOTS);
-                }
-                // O += P V for the current step
-                const uint32_t buf = gstep & 1;
-                ok = mbar_wait(smem_u32(&bars.p_full[buf]), (gstep >> 1) & 1, abortp, budget);
-                if (ok && fp16) ok = mbar_wait(smem_u32(&bars.slot_full[pv_slot % NSLOTS]), (pv_slot / NSLOTS) & 1, abortp, budget);
+                const uint32_t set = gsub & (NSETS - 1), use = gsub / NSETS;
+                const uint32_t slot = gslot % NSLOTS;
+                ok = mbar_wait(smem_u32(&bars.slot_full[slot]), (gslot / NSLOTS) & 1, abortp, budget) &&
+                     mbar_wait(smem_u32(&bars.s_free[set]), (use & 1) ^ 1, abortp, budget);
                 if (!ok) break;
                 tc_fence_after_sync();
-                {
-                    const uint32_t sa = sbase + L::SLOTS + (pv_slot % NSLOTS) * SLOT_BYTES;
-                    const uint32_t d_t = tmem + TM_O;
-                    const uint32_t acc = i > 0 ? 1u : 0u;
-                    if (!fp16) {
-                        const uint32_t sfb = tmem + TM_SFB_V + buf * 4;
-                        tmem_cp_sf_elect(sfb, make_smem_desc(sa + L::VSF, 0, 128, SWZ_NONE));
-                        const uint64_t ad = make_smem_desc(sbase + L::P + buf * 4096, 16, 256, SWZ_32B);
-                        const uint64_t bd = make_smem_desc(sa + L::V4, 16, 256, SWZ_32B);
-                        if constexpr (MX) mma_mxfp4_elect(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
-                        else mma_nvfp4_elect(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
-                    } else {
-                        for (int ks = 0; ks < STEP / 16; ++ks) {
-                            const uint64_t ad = make_smem_desc(sbase + L::P + ks * 32, 16, 1024, SWZ_128B);
-                            const uint64_t bd = make_smem_desc(sa + ks * 2048, STEP * 128, 1024, SWZ_128B);
-                            mma_f16_elect(d_t, ad, bd, idesc_pv16, (acc == 0 && ks == 0) ? 0 : 1);
-                        }
+                const uint32_t sa = sbase + L::SLOTS + slot * SLOT_BYTES;
+                const uint32_t d_t = tmem + TM_S + set * STEP;
+                if (!fp16) {
+                    const uint32_t sfb = tmem + TM_SFB_K + set * 8;
+                    for (int a = 0; a < QK_ATOMS; ++a)
+                        tmem_cp_sf_elect(sfb + a * 4, make_smem_desc(sa + L::KSF + a * 512, 0, 128, SWZ_NONE));
+                    for (int kb = 0; kb < KBLK; ++kb) {
+                        const uint64_t ad = make_smem_desc(sbase + L::Q4 + kb * 32, 16, SBO_QK, SWZ_QK);
+                        const uint64_t bd = make_smem_desc(sa + L::K4 + kb * 32, 16, SBO_QK, SWZ_QK);
+                        if constexpr (MX)
+                            mma_mxfp4_elect(d_t, ad, bd, make_idesc_fp4(128, STEP, 1, kb * 2, kb * 2), tmem + TM_SFA_Q, sfb, kb > 0);
+                        else
+                            mma_nvfp4_elect(d_t, ad, bd, idesc_qk4, tmem + TM_SFA_Q + kb * 4, sfb + kb * 4, kb > 0);
                     }
-                    tc_commit_elect(smem_u32(&bars.slot_empty[pv_slot % NSLOTS]));
-                    tc_commit_elect(smem_u32(&bars.p_free[buf]));
-                    if (i + 1 == n) tc_commit_elect(smem_u32(&bars.q_empty));
+                } else {
+                    for (int ks = 0; ks < D / 16; ++ks) {
+                        const uint32_t hf = ks / 4, kk = ks % 4;
+                        const uint64_t ad = make_smem_desc(sbase + L::Q16 + hf * QTILE * 128 + kk * 32, 16, 1024, SWZ_128B);
+                        const uint64_t bd = make_smem_desc(sa + hf * STEP * 128 + kk * 32, 16, 1024, SWZ_128B);
+                        mma_f16_elect(d_t, ad, bd, idesc_qk16, ks > 0);
+                    }
+                    tc_commit_elect(smem_u32(&bars.slot_empty[slot]));  // the K tile is free once S is computed
                 }
-                ++gstep;
+                tc_commit_elect(smem_u32(&bars.s_full[set]));
+                if (i + 1 == n) tc_commit_elect(smem_u32(&bars.q_empty));
+                gslot += fp16 ? 2 : 1;
+                ++gsub;
             }
-            gslot = qk_slot;
+            if (lane == 0) mbar_arrive(smem_u32(&bars.sched_empty));
+        }
+    } else if (warp == 2) {
+        // =========================== O += P V issuer ===========================
+        tmem_cp_sf_elect(tmem + TM_SFA_P, make_smem_desc(sbase + L::CSF, 0, 128, SWZ_NONE));
+        uint32_t gsub = 0, gslot = 0;
+        int n_item = 0;
+        bool ok = true;
+        const uint32_t idesc_pv4 = make_idesc_fp4(128, D, MX ? 1 : 0, 0, 0);
+        const uint32_t idesc_pv16 = make_idesc_f16(128, D, BF16 ? 1 : 0, 0, 1);
+        for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
+            ok = mbar_wait(smem_u32(&bars.sched_full), n_item & 1, abortp, budget);
+            if (!ok) break;
+            const int n = bars.sched_n;
+            for (int i = 0; i < n && ok; ++i) {
+                const uint32_t e = sched[i];
+                const bool fp16 = e & E_FP16;
+                const uint32_t set = gsub & (NSETS - 1), use = gsub / NSETS;
+                // this warp looks at every phase of every slot barrier, also the K tile's of a 16-bit sub-step
+                ok = mbar_wait(smem_u32(&bars.slot_full[gslot % NSLOTS]), (gslot / NSLOTS) & 1, abortp, budget);
+                const uint32_t pv_slot = fp16 ? gslot + 1 : gslot;
+                if (ok && fp16) ok = mbar_wait(smem_u32(&bars.slot_full[pv_slot % NSLOTS]), (pv_slot / NSLOTS) & 1, abortp, budget);
+                if (ok) ok = mbar_wait(smem_u32(&bars.p_full[set]), use & 1, abortp, budget);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t sa = sbase + L::SLOTS + (pv_slot % NSLOTS) * SLOT_BYTES;
+                const uint32_t pa = sbase + L::P + set * PSET_BYTES;
+                const uint32_t d_t = tmem + TM_O;
+                const uint32_t acc = i > 0 ? 1u : 0u;
+                if (!fp16) {
+                    const uint32_t sfb = tmem + TM_SFB_V + set * 4;
+                    tmem_cp_sf_elect(sfb, make_smem_desc(sa + L::VSF, 0, 128, SWZ_NONE));
+                    const uint64_t ad = make_smem_desc(pa, 16, 256, SWZ_32B);
+                    const uint64_t bd = make_smem_desc(sa + L::V4, 16, 256, SWZ_32B);
+                    if constexpr (MX) mma_mxfp4_elect(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
+                    else mma_nvfp4_elect(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
+                } else {
+                    for (int ks = 0; ks < STEP / 16; ++ks) {
+                        const uint64_t ad = make_smem_desc(pa + ks * 32, 16, 1024, SWZ_128B);
+                        const uint64_t bd = make_smem_desc(sa + ks * 2048, STEP * 128, 1024, SWZ_128B);
+                        mma_f16_elect(d_t, ad, bd, idesc_pv16, (acc == 0 && ks == 0) ? 0 : 1);
+                    }
+                }
+                tc_commit_elect(smem_u32(&bars.slot_empty[pv_slot % NSLOTS]));
+                tc_commit_elect(smem_u32(&bars.p_free[set]));
+                if (i + 1 == n) tc_commit_elect(smem_u32(&bars.o_full));
+                gslot += fp16 ? 2 : 1;
+                ++gsub;
+            }
             if (lane == 0) mbar_arrive(smem_u32(&bars.sched_empty));
         }
     } else {
         // =========================== softmax ===========================
-        const int sub = warp & 3;                 // tensor-memory sub-partition
-        const int row = sub * 32 + lane;          // row inside the q tile
-        const int half = sub >> 1;                // 0: rows 0..63, 1: rows 64..127
-        const uint32_t lane_addr = static_cast<uint32_t>(sub * 32) << 16;
-        uint32_t gstep = 0;
-        int n_item = 0;
+        const int g = warp & 3;                   // 32-row group = tensor-memory sub-partition
+        const uint32_t set = (warp - 3) >> 2;     // this warp runs the sub-steps with (CTA-wide index) mod 4 == set
+        const uint32_t prev_set = (set + NSETS - 1) & (NSETS - 1);
+        const int row = g * 32 + lane;            // row inside the q tile
+        const int half = g >> 1;                  // 0: rows 0..63, 1: rows 64..127
+        const uint32_t lane_addr = static_cast<uint32_t>(g * 32) << 16;
+        const uint32_t tm_s = tmem + lane_addr + TM_S + set * STEP;
+        uint8_t* const ptile = smem + L::P + set * PSET_BYTES;
+        uint32_t gsub0 = 0;                       // CTA-wide index of the item's first sub-step
+        int n_item = 0, n_nonempty = 0, n_trans = 0;
         bool ok = true;
-        bool prev_fp16 = false;                   // kind of the previous step (across items)
-        TA100_PROF_DECL
         for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
             const ItemInfo it = decode_item(p, item);
             ok = mbar_wait(smem_u32(&bars.sched_full), n_item & 1, abortp, budget);
             if (!ok) break;
-            const int n = bars.sched_n;
+            const int n = bars.sched_n, n_fp4 = bars.sched_na;
+            const bool has_trans = p.round_partial && n_fp4 > 0 && n_fp4 < n;
+            bool trans_sent = false;
             const int grow = it.t * QTILE + row;  // absolute query row
-            float m_run = -FLT_MAX, l_run = 0.0f;
-            TA100_PROF(9)
-            for (int i = 0; i < n; ++i) {
+            float m_ref = -FLT_MAX, l_run = 0.0f; // this set's share of the row sum, relative to m_ref
+            // one sub-step; the FP4 and the 16-bit kind are compiled separately (they are separate runs of the list)
+            auto substep = [&](auto kind, const int i) -> bool {
+                constexpr bool fp16 = decltype(kind)::value;
+                const uint32_t gsub = gsub0 + i, use = gsub / NSETS;
                 const uint32_t e = sched[i];
-                const bool fp16 = e & E_FP16;
                 const int col0 = (e & 0xFFF) * STEP;
                 const bool part = e & (half ? E_P1 : E_P0);
-                TA100_PROF(0)
-                ok = mbar_wait(smem_u32(&bars.s_full), gstep & 1, abortp, budget);
-                if (!ok) break;
+                if (has_trans && !trans_sent && i >= n_fp4) {
+                    xch.l_tr[g][set][lane] = l_run; xch.m_tr[g][set][lane] = m_ref;
+                    mbar_arrive(smem_u32(&bars.trans[g]));
+                    trans_sent = true;
+                }
+                ok = mbar_wait(smem_u32(&bars.s_full[set]), use & 1, abortp, budget);
+                if (!ok) return false;
                 tc_fence_after_sync();
-                TA100_PROF(1)
                 float s[STEP];
                 {
                     uint32_t r0[32], r1[32];
-                    tmem_ld32(tmem + lane_addr + TM_S, r0);
-                    tmem_ld32(tmem + lane_addr + TM_S + 32, r1);
+                    tmem_ld32(tm_s, r0);
+                    tmem_ld32(tm_s + 32, r1);
                     tmem_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) { s[j] = __uint_as_float(r0[j]); s[32 + j] = __uint_as_float(r1[j]); }
                 }
                 tc_fence_before_sync();
-                mbar_arrive(smem_u32(&bars.s_free));
-                TA100_PROF(2)
+                mbar_arrive(smem_u32(&bars.s_free[set]));
 
-                float rescale = 1.0f;
-                bool changed = false;
-                float mneg = 0.0f;
+                float m_loc = -FLT_MAX;
                 if (part) {
                     if (CAUSAL && (col0 + STEP - 1 > grow)) {
 #pragma unroll
@@ -574,86 +611,102 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                         mx2 = max3(mx2, s[j + 4], s[j + 5]);
                         mx3 = max3(mx3, s[j + 6], s[j + 7]);
                     }
-                    const float m_new = max3(m_run, fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-                    changed = m_new > m_run;
-                    rescale = ex2((m_run - m_new) * p.c2);
-                    m_run = m_new;
-                    mneg = -m_new * p.c2;
+                    m_loc = max3(fmaxf(mx0, mx1), mx2, mx3);
                 }
-                TA100_PROF(3)
-                const uint32_t buf = gstep & 1;
-                const bool transition = fp16 && i > 0 && !prev_fp16 && p.round_partial;
+                // running maximum: from the set that ran the previous sub-step, to the one that runs the next
+                float m_prev = -FLT_MAX;
+                if (gsub > 0) {
+                    ok = mbar_wait(smem_u32(&bars.mch[g][prev_set]), ((gsub - 1) / NSETS) & 1, abortp, budget);
+                    if (!ok) return false;
+                    if (i > 0) m_prev = xch.mrun[g][prev_set][lane];
+                }
+                const float m_new = fmaxf(m_prev, m_loc);
+                xch.mrun[g][set][lane] = m_new;
+                mbar_arrive(smem_u32(&bars.mch[g][set]));
+                const bool changed = m_new > m_prev;
+                const float rescale_o = ex2((m_prev - m_new) * p.c2);
+                const float rescale_l = ex2((m_ref - m_new) * p.c2);
+                m_ref = m_new;
+                const float mneg = -m_new * p.c2;
+                l_run *= rescale_l;
+                const bool transition = fp16 && has_trans && i == n_fp4;
                 const bool need_rescale = __any_sync(0xFFFFFFFFu, changed && i > 0);
-                // A 16-bit P tile spans the whole P region, so with one involved the previous PV must be complete
-                // before P is written; the FP4 tiles alternate between two buffers and only wait for the PV of
-                // two steps ago, and that only once the probabilities are ready to be stored.
-                const bool wide_p = fp16 || prev_fp16;
-                if (wide_p && gstep > 0) {
-                    ok = mbar_wait(smem_u32(&bars.p_free[(gstep - 1) & 1]), ((gstep - 1) >> 1) & 1, abortp, budget);
-                    if (!ok) break;
-                }
-                TA100_PROF(4)
-                // probabilities, row sum, P tile
-                const float l_prev = l_run;
-                if (!fp16) {
+
+                // the P tile of this set is free once the P V of its previous sub-step completed
+                ok = mbar_wait(smem_u32(&bars.p_free[set]), (use & 1) ^ 1, abortp, budget);
+                if (!ok) return false;
+                if constexpr (!fp16) {
                     uint32_t w[STEP / 8];
                     if (part) {
                         // 6 p = 2^(s c2 - m c2 + log2 6): the e2m1 input directly
                         const float sum6 = exp_scaled_64(s, p.c2, mneg + 2.5849625007211562f);
-                        l_run = fmaf(sum6, 1.0f / 6.0f, l_run * rescale);
+                        l_run = fmaf(sum6, 1.0f / 6.0f, l_run);
 #pragma unroll
-                        for (int g = 0; g < STEP / 8; ++g)
-                            w[g] = e2m1x8(s[cmap.phys[g * 8 + 0]], s[cmap.phys[g * 8 + 1]], s[cmap.phys[g * 8 + 2]],
-                                          s[cmap.phys[g * 8 + 3]], s[cmap.phys[g * 8 + 4]], s[cmap.phys[g * 8 + 5]],
-                                          s[cmap.phys[g * 8 + 6]], s[cmap.phys[g * 8 + 7]]);
+                        for (int q8 = 0; q8 < STEP / 8; ++q8)
+                            w[q8] = e2m1x8(s[cmap.phys[q8 * 8 + 0]], s[cmap.phys[q8 * 8 + 1]], s[cmap.phys[q8 * 8 + 2]],
+                                           s[cmap.phys[q8 * 8 + 3]], s[cmap.phys[q8 * 8 + 4]], s[cmap.phys[q8 * 8 + 5]],
+                                           s[cmap.phys[q8 * 8 + 6]], s[cmap.phys[q8 * 8 + 7]]);
                     } else {
 #pragma unroll
-                        for (int g = 0; g < STEP / 8; ++g) w[g] = 0u;
+                        for (int q8 = 0; q8 < STEP / 8; ++q8) w[q8] = 0u;
                     }
-                    ok = mbar_wait(smem_u32(&bars.p_free[buf]), ((gstep >> 1) & 1) ^ 1, abortp, budget);
-                    if (!ok) break;
-                    // 128 rows x 32 bytes, 32-byte swizzle; FP4 steps alternate between two 4 KB buffers
+                    // 128 rows x 32 bytes, 32-byte swizzle
                     const uint32_t r8 = row & 7;
-                    uint8_t* base = smem + L::P + buf * 4096 + (row >> 3) * 256 + r8 * 32;
+                    uint8_t* base = ptile + (row >> 3) * 256 + r8 * 32;
                     const uint32_t x = (r8 >> 2) & 1;
                     *reinterpret_cast<uint4*>(base + ((0 ^ x) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
                     *reinterpret_cast<uint4*>(base + ((1 ^ x) * 16)) = make_uint4(w[4], w[5], w[6], w[7]);
                 } else {
-                    uint32_t w[STEP / 2];
+                    // C p = 2^(s c2 - m c2 + log2 C): the 16-bit P operand directly.  128 rows x 128 bytes,
+                    // 128-byte swizzle; eight values are exponentiated, packed and stored at a time.
+                    constexpr float LOG2_C = MX ? 2.5849625007211562f : 11.392317422778761f;
+                    const uint32_t r8 = row & 7;
+                    uint8_t* base = ptile + (row >> 3) * 1024 + r8 * 128;
                     if (part) {
-                        // C p = 2^(s c2 - m c2 + log2 C): the 16-bit P operand directly
-                        constexpr float LOG2_C = MX ? 2.5849625007211562f : 11.392317422778761f;
-                        const float sum_c = exp_scaled_64(s, p.c2, mneg + LOG2_C);
-                        l_run = fmaf(sum_c, CSCALE_INV, l_run * rescale);
+                        const uint64_t c2p = pack2f(p.c2, p.c2), bp = pack2f(mneg + LOG2_C, mneg + LOG2_C);
+                        uint64_t acc0 = pack2f(0.0f, 0.0f), acc1 = acc0;
 #pragma unroll
-                        for (int j = 0; j < STEP / 2; ++j) w[j] = In16<BF16>::pack2(s[2 * j], s[2 * j + 1]);
+                        for (int c = 0; c < 8; ++c) {
+                            float v[8];
+#pragma unroll
+                            for (int j = 0; j < 8; j += 2) {
+                                float a0, a1;
+                                unpack2f(fma2(pack2f(s[8 * c + j], s[8 * c + j + 1]), c2p, bp), a0, a1);
+                                v[j] = ex2(a0); v[j + 1] = ex2(a1);
+                            }
+                            acc0 = add2(acc0, add2(pack2f(v[0], v[1]), pack2f(v[2], v[3])));
+                            acc1 = add2(acc1, add2(pack2f(v[4], v[5]), pack2f(v[6], v[7])));
+                            *reinterpret_cast<uint4*>(base + ((c ^ r8) * 16)) =
+                                make_uint4(In16<BF16>::pack2(v[0], v[1]), In16<BF16>::pack2(v[2], v[3]),
+                                           In16<BF16>::pack2(v[4], v[5]), In16<BF16>::pack2(v[6], v[7]));
+                        }
+                        float x, y;
+                        unpack2f(add2(acc0, acc1), x, y);
+                        l_run = fmaf(x + y, CSCALE_INV, l_run);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < STEP / 2; ++j) w[j] = 0u;
+                        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(base + c * 16) = make_uint4(0u, 0u, 0u, 0u);
                     }
-                    ok = mbar_wait(smem_u32(&bars.p_free[buf]), ((gstep >> 1) & 1) ^ 1, abortp, budget);
-                    if (!ok) break;
-                    // 128 rows x 128 bytes, 128-byte swizzle; one buffer for 16-bit steps
-                    const uint32_t r8 = row & 7;
-                    uint8_t* base = smem + L::P + (row >> 3) * 1024 + r8 * 128;
-#pragma unroll
-                    for (int c = 0; c < 8; ++c)
-                        *reinterpret_cast<uint4*>(base + ((c ^ r8) * 16)) =
-                            make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
                 }
                 fence_proxy_async_smem();
-                TA100_PROF(5)
-                // O is touched only now, after the exponentials: the PV of the previous step has had their time
-                // to finish.  The issuer adds this step's P V only after the arrival below.
-                if ((transition || need_rescale) && !wide_p) {
-                    ok = mbar_wait(smem_u32(&bars.p_free[(gstep - 1) & 1]), ((gstep - 1) >> 1) & 1, abortp, budget);
-                    if (!ok) break;
+                // O may be touched once the P V of the previous sub-step (another set's) has completed; the
+                // issuer adds this sub-step's P V only after the arrival below.
+                if (gsub > 0) {
+                    ok = mbar_wait(smem_u32(&bars.p_free[prev_set]), ((gsub - 1) / NSETS) & 1, abortp, budget);
+                    if (!ok) return false;
                 }
-                if (transition || need_rescale) tc_fence_after_sync();
                 if (transition) {
-                    // state rounding between the FP4 and the 16-bit phase (state before this step's update)
+                    // state rounding between the FP4 and the 16-bit phase (state before this sub-step's update):
+                    // the row sum is the sum of the four sets' shares at their last FP4 sub-step
+                    ok = mbar_wait(smem_u32(&bars.trans[g]), n_trans & 1, abortp, budget);
+                    if (!ok) return false;
+                    float l_prev = 0.0f;
+#pragma unroll
+                    for (int c = 0; c < NSETS; ++c)
+                        l_prev = fmaf(xch.l_tr[g][c][lane], ex2((xch.m_tr[g][c][lane] - m_prev) * p.c2), l_prev);
+                    tc_fence_after_sync();
                     const float norm = l_prev > 0.0f ? __fdiv_rn(CSCALE_INV, l_prev) : 0.0f;
-                    const float back = l_prev * CSCALE * rescale;
+                    const float back = l_prev * CSCALE * rescale_o;
 #pragma unroll 1
                     for (int c = 0; c < D; c += 32) {
                         uint32_t r[32];
@@ -668,66 +721,81 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                     }
                     tmem_wait_st();
                 } else if (need_rescale) {
+                    tc_fence_after_sync();
 #pragma unroll 1
-                    for (int c = 0; c < D; c += 64) {
-                        uint32_t ra[32], rb[32];
+                    for (int c = 0; c < D; c += 32) {
+                        uint32_t ra[32];
                         tmem_ld32(tmem + lane_addr + TM_O + c, ra);
-                        tmem_ld32(tmem + lane_addr + TM_O + c + 32, rb);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            ra[j] = __float_as_uint(__uint_as_float(ra[j]) * rescale);
-                            rb[j] = __float_as_uint(__uint_as_float(rb[j]) * rescale);
-                        }
+                        for (int j = 0; j < 32; ++j) ra[j] = __float_as_uint(__uint_as_float(ra[j]) * rescale_o);
                         tmem_st32(tmem + lane_addr + TM_O + c, ra);
-                        tmem_st32(tmem + lane_addr + TM_O + c + 32, rb);
                     }
                     tmem_wait_st();
                 }
-                TA100_PROF(6)
                 tc_fence_before_sync();
-                mbar_arrive(smem_u32(&bars.p_full[buf]));
-                TA100_PROF(7)
-                TA100_PROF_STEP
-                prev_fp16 = fp16;
-                ++gstep;
+                mbar_arrive(smem_u32(&bars.p_full[set]));
+                return true;
+            };
+            {
+                int i = (set - gsub0) & (NSETS - 1);
+                for (; i < n_fp4 && ok; i += NSETS) ok = substep(std::false_type{}, i);
+                for (; i < n && ok; i += NSETS) ok = substep(std::true_type{}, i);
             }
             if (!ok) break;
-            // ---- epilogue ----
+            if (has_trans) {
+                if (!trans_sent) {
+                    xch.l_tr[g][set][lane] = l_run; xch.m_tr[g][set][lane] = m_ref;
+                    mbar_arrive(smem_u32(&bars.trans[g]));
+                }
+                ++n_trans;
+            }
+            // ---- epilogue: the four sets of a row group add up their row sums and each normalises and
+            //      stores a quarter of the output channels ----
+            constexpr int DQ = D / NSETS;          // channels per set
             uint16_t* orow = p.out + (p.out_seq_major
                 ? ((static_cast<long long>(it.h / p.hq_per_b) * p.sq + grow) * p.hq_per_b + it.h % p.hq_per_b) * D
-                : (static_cast<long long>(it.h) * p.sq + grow) * D);
+                : (static_cast<long long>(it.h) * p.sq + grow) * D) + set * DQ;
             if (n > 0) {
-                ok = mbar_wait(smem_u32(&bars.p_free[(gstep - 1) & 1]), ((gstep - 1) >> 1) & 1, abortp, budget);
+                xch.l_end[g][set][lane] = l_run; xch.m_end[g][set][lane] = m_ref;
+                mbar_arrive(smem_u32(&bars.lend[g]));
+                ok = mbar_wait(smem_u32(&bars.lend[g]), n_nonempty & 1, abortp, budget);
                 if (!ok) break;
+                float m_fin = -FLT_MAX;
+#pragma unroll
+                for (int c = 0; c < NSETS; ++c) m_fin = fmaxf(m_fin, xch.m_end[g][c][lane]);
+                float l_tot = 0.0f;
+#pragma unroll
+                for (int c = 0; c < NSETS; ++c)
+                    l_tot = fmaf(xch.l_end[g][c][lane], ex2((xch.m_end[g][c][lane] - m_fin) * p.c2), l_tot);
+                ok = mbar_wait(smem_u32(&bars.o_full), n_nonempty & 1, abortp, budget);
+                if (!ok) break;
+                ++n_nonempty;
                 tc_fence_after_sync();
-                const float norm = l_run > 0.0f ? __fdiv_rn(CSCALE_INV, l_run) : 0.0f;
-#pragma unroll 1
-                for (int c = 0; c < D; c += 32) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem + lane_addr + TM_O + c, r);
-                    tmem_wait_ld();
-                    if (grow < p.sq) {
+                const float norm = l_tot > 0.0f ? __fdiv_rn(CSCALE_INV, l_tot) : 0.0f;
+                uint32_t r[DQ];
+                if constexpr (DQ == 32) tmem_ld32(tmem + lane_addr + TM_O + set * DQ, r);
+                else tmem_ld16(tmem + lane_addr + TM_O + set * DQ, r);
+                tmem_wait_ld();
+                if (grow < p.sq) {
 #pragma unroll
-                        for (int v4 = 0; v4 < 4; ++v4) {
-                            uint32_t o[4];
+                    for (int v4 = 0; v4 < DQ / 8; ++v4) {
+                        uint32_t o[4];
 #pragma unroll
-                            for (int e2 = 0; e2 < 4; ++e2)
-                                o[e2] = In16<BF16>::pack2(__uint_as_float(r[v4 * 8 + 2 * e2]) * norm,
-                                                          __uint_as_float(r[v4 * 8 + 2 * e2 + 1]) * norm);
-                            *reinterpret_cast<uint4*>(orow + c + v4 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
-                        }
+                        for (int e2 = 0; e2 < 4; ++e2)
+                            o[e2] = In16<BF16>::pack2(__uint_as_float(r[v4 * 8 + 2 * e2]) * norm,
+                                                      __uint_as_float(r[v4 * 8 + 2 * e2 + 1]) * norm);
+                        *reinterpret_cast<uint4*>(orow + v4 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
                     }
                 }
                 tc_fence_before_sync();
             } else if (grow < p.sq) {
-                for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
+                for (int c = 0; c < DQ; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars.sched_empty));
-            TA100_PROF(8)
+            gsub0 += n;
         }
-        TA100_PROF_DUMP
     }
 
     // ---- common exit ----
@@ -922,7 +990,7 @@ int prefill_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const
     int dev = 0, sms = NUM_SMS_HINT;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int grid = p.n_items < 2 * sms ? p.n_items : 2 * sms;
+    int grid = p.n_items < sms ? p.n_items : sms;
     if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
 
 #define TA100_PF(DD, MXX, BFF, CC, KP) launch_prefill_t<DD, MXX, BFF, CC, KP>(p, maps, grid, stream)
@@ -942,11 +1010,6 @@ int prefill_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const
     return rc;
 }
 
-#ifdef TA100_PROFILE_SOFTMAX
-int prefill_profile_read(long long* out16) {
-    return static_cast<int>(cudaMemcpyFromSymbol(out16, g_prof, sizeof(long long) * 16));
-}
-#endif
 
 // Reads back the device status word written by the last prefill launch that
 // used `workspace` (synchronises the stream).
