@@ -1,19 +1,20 @@
 #!/usr/bin/env python
-"""Headline benchmark: long-context selective mixed-precision prefill attention.
+"""Headline benchmark: long-context selective mixed-precision prefill attention, and the paged decode step.
 
-Workload (BASELINE.json metric "prefill attn TFLOP/s @128k top-10% NVFP4"): batch 1,
-32 query heads / 8 KV heads, q_len = kv_len = 131072, head_dim 128, fp16, causal, Quest
-selection with 128-token blocks keeping top-10% (53 of 1024 blocks) in 16-bit and the rest
-in NVFP4; q, v ~ N(0,1), k ~ N(0,1) with 4 fixed channels per KV head scaled x10 (seeded,
-synthetic).  One step = block statistics + selection + quantisation of Q/K/V + the fused
-attention kernel over the whole problem.
+Workload of the headline metric ("prefill attn TFLOP/s @128k top-10% NVFP4; decode us/step & HBM GB/s @128k"):
+batch 1, 32 query heads / 8 KV heads, q_len = kv_len = 131072, head_dim 128, fp16, causal, Quest selection with
+128-token blocks keeping top-10% (53 of 1024 blocks) in 16-bit and the rest in NVFP4; q, v ~ N(0,1), k ~ N(0,1)
+with 4 fixed channels per KV head scaled x10 (seeded, synthetic).  One step = ``ta.attention(q, k, v, config=...)``:
+block statistics + selection + quantisation of Q/K/V + the fused attention kernel over the whole problem.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload headline|mxfp4-bf16]
 
-N > 1 (launched under torch.distributed.run): the 8 KV-head groups are split across the
-ranks (strong scaling, no communication during compute, one all_gather of the outputs per
-step).  ``--impl reference`` times the CPU oracle (the restatement of the reference's
-arithmetic) on the host cores on a bounded sample of the same workload.
+N > 1 (launched under torch.distributed.run): the 8 KV-head groups are split across the ranks (strong scaling, no
+communication during compute; the outputs are all-gathered on a side stream, two q-row ranges per step, so that the
+gather of the first range runs under the kernel of the second).  ``--workload mxfp4-bf16 --fraction F`` runs the
+long-context bf16 / MXFP4 configuration with F of the blocks in bf16 instead (prefill only).
+``--impl reference`` times the CPU oracle (the restatement of the reference's arithmetic) on the host cores on a
+bounded sample of the same workload, and runs the small CPU configuration (8 heads x 2048 tokens) in full.
 
 Rank 0 prints one JSON line.
 """
@@ -35,10 +36,12 @@ sys.path.insert(0, ROOT)
 
 HQ, HKV, SEQ, D = 32, 8, 131072, 128
 BLOCK = 128
-FRACTION = 0.10
-FMT = "nvfp4"
 METRIC = "prefill_attention_tflops_128k_top10pct_nvfp4"
 FP4_TO_BF16_PEAK_RATIO = 4.0  # dense FP4 : dense bf16 tensor peak on B200 (9 : 2.25 PFLOP/s nominal)
+# DRAM bytes of one prefill_kernel launch on the small profiler case (1 x 16q/4kv x 8192 x 128, 2.79e11 algorithmic
+# FLOP; dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture summarised under profiles/); scaled to a
+# launch of the timed workload by the FLOPs it processes (K/V re-reads grow with the q-tile count like the FLOPs).
+SMALL_CASE_DRAM_BYTES, SMALL_CASE_FLOPS = 65.0e6, 2.79e11
 
 
 def algorithmic_flops(hq: int, seq: int, d: int, block: int) -> float:
@@ -50,6 +53,24 @@ def algorithmic_flops(hq: int, seq: int, d: int, block: int) -> float:
 def fp16_flop_share(seq: int, block: int, k: int) -> float:
     nb = seq // block
     return sum(min(i + 1, k) for i in range(nb)) / (nb * (nb + 1) / 2)
+
+
+def call_stats(times_ms) -> dict:
+    """mean / median / p90 / min of per-call CUDA-event times (the reference harness's columns,
+    benchmarks/run_kernel_benchmarks.py:282-303)."""
+    t = sorted(times_ms)
+    pos = (len(t) - 1) * 0.9
+    lo = int(pos)
+    p90 = t[lo] + (t[min(lo + 1, len(t) - 1)] - t[lo]) * (pos - lo)
+    return {"mean": statistics.fmean(t), "median": statistics.median(t), "p90": p90, "min": t[0], "n": len(t)}
+
+
+def measured_peaks() -> dict:
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f)
+    except (OSError, ValueError):
+        return {}
 
 
 class ClockSampler:
@@ -116,8 +137,33 @@ def make_inputs(hq: int, hkv: int, seq: int, device, dtype, seed: int = 0, kv_he
     return q, k, v
 
 
+def run_small_cpu_config(cores: int) -> dict:
+    """The CPU-runnable configuration in full: batch 1, 8 query = 8 KV heads, 2048 tokens, head_dim 128, q, k, v ~
+    N(0,1) from seed 0, causal, 64-token blocks, top-10 % (2 of 32 blocks) + the first block (sink) + the newest block
+    (local) in 16 bits, the rest NVFP4 - oracle output against fp32 softmax attention, with the oracle's wall time."""
+    import oracle
+
+    torch.manual_seed(0)
+    q32, k32, v32 = (torch.randn(1, 8, 2048, D) for _ in range(3))
+    q, k, v = q32.half(), k32.half(), v32.half()
+    top_k = oracle.resolve_top_k(2048 // 64, causal=True, fraction=0.10)
+    t0 = time.perf_counter()
+    qm, = oracle.block_stats(q, 64, ("mean",))
+    km, = oracle.block_stats(k, 64, ("mean",))
+    sel = oracle.select_prefill(qm, km, None, k=top_k, causal=True, sink=1, local=1)
+    out = oracle.prefill_attention(q, k, v, sel, fmt="nvfp4", block=64, causal=True)
+    dt = time.perf_counter() - t0
+    exact = torch.nn.functional.scaled_dot_product_attention(q32, k32, v32, is_causal=True)
+    err = (out.float() - exact).abs()
+    cos = torch.nn.functional.cosine_similarity(out.float().flatten(), exact.flatten(), dim=0).item()
+    return {"workload": "1x8q/8kv x2048 x128, causal, block-mean top-10% (2 of 32 64-token blocks) + sink 1 + local 1 in "
+                        "f16, rest NVFP4; CPU oracle vs fp32 softmax attention",
+            "top_k": top_k, "wall_s": dt, "cores": cores, "max_abs_err": err.max().item(), "mean_abs_err": err.mean().item(),
+            "cosine": cos}
+
+
 def run_reference(args) -> dict:
-    """CPU arm: the oracle (a port of the reference's arithmetic) on a bounded sample."""
+    """CPU arm: the oracle (a port of the reference's arithmetic) on a bounded sample of the headline workload."""
     import oracle
 
     rank = int(os.environ.get("RANK", "0"))
@@ -128,13 +174,13 @@ def run_reference(args) -> dict:
     torch.set_num_threads(cores)
     rows = 4096  # the last 4096 query rows of one q head against all 131072 keys of its KV head
     q, k, v = make_inputs(1, 1, SEQ, "cpu", torch.float16)
-    top_k = oracle.resolve_top_k(SEQ // BLOCK, causal=True, fraction=FRACTION)
+    top_k = oracle.resolve_top_k(SEQ // BLOCK, causal=True, fraction=0.10)
 
     def step():
         qm, = oracle.block_stats(q, BLOCK, ("mean",))
         kmin, kmax = oracle.block_stats(k, BLOCK, ("min", "max"))
         sel = oracle.select_prefill(qm, kmin, kmax, k=top_k, causal=True)
-        return oracle.prefill_attention(q, k, v, sel, fmt=FMT, block=BLOCK, causal=True, rows=(SEQ - rows, SEQ))
+        return oracle.prefill_attention(q, k, v, sel, fmt="nvfp4", block=BLOCK, causal=True, rows=(SEQ - rows, SEQ))
 
     nb, r0 = SEQ // BLOCK, (SEQ - rows) // BLOCK
     pairs = sum(i + 1 for i in range(r0, nb))
@@ -149,7 +195,7 @@ def run_reference(args) -> dict:
     value = sample_flops / dt / 1e12
     sample = (f"last {rows} query rows of 1 of {HQ} q heads vs all {SEQ} keys of its KV head (statistics, selection, "
               f"quantisation of that head and mixed attention), {sample_flops:.3e} of {algorithmic_flops(HQ, SEQ, D, BLOCK):.3e} FLOP")
-    return {
+    result = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": steps,
         "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "fp4+f16 (emulated in fp32 on CPU)", "data": "synthetic",
@@ -158,20 +204,62 @@ def run_reference(args) -> dict:
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-
+    if getattr(args, "with_small_cpu_config", True):
+        result["cpu_config"] = run_small_cpu_config(cores)
+    return result
 
 
 # --------------------------------------------------------------------------------------------- decode leg
 DEC_BATCH, DEC_SEQ, DEC_GROUP = 32, 131072, HQ // HKV
 DEC_SINK, DEC_LOCAL, DEC_FRACTION = 4, 16, 0.10
+DEC_CHECK_ROWS = ((0, 0), (DEC_BATCH - 1, HKV - 1))       # (sequence, KV head) pairs compared with the oracle
+CHECK_MAX_ABS, CHECK_MEAN_ABS = 2e-3, 2e-4               # the fp16 attention tolerance of the parity tests
+
+
+def check_decode_rows(out, q, k_hi, v_hi, table, *, world: int, rank: int, pages: int, top_k: int, splits_local: int) -> str:
+    """Rank 0 compares DEC_CHECK_ROWS of the step's result with the CPU oracle run on the same cached K/V (the
+    16-bit shadow in logical page order, gathered from all ranks; the oracle quantises it exactly as the cache was
+    filled).  A shard's chains are the single-GPU chains of the same page ranges, so the oracle runs with
+    world x splits_local chains.  Raises on a mismatch."""
+    import torch.distributed as dist
+
+    import oracle
+
+    worst = 0.0
+    for b, h in DEC_CHECK_ROWS:
+        idx = table[b].long()
+        mine = [k_hi[idx, h].contiguous(), v_hi[idx, h].contiguous()]            # [n_local, 64, D] each
+        if world > 1:
+            parts = []
+            for t in mine:
+                bufs = [torch.empty_like(t) for _ in range(world)]
+                dist.all_gather(bufs, t)
+                parts.append(torch.cat(bufs, 0))
+        else:
+            parts = mine
+        if rank != 0:
+            continue
+        k_row = parts[0].reshape(1, 1, pages * 64, D).cpu()
+        v_row = parts[1].reshape(1, 1, pages * 64, D).cpu()
+        q_row = q[b, h].reshape(1, 1, DEC_GROUP, D).cpu()
+        lo, hi = oracle.block_stats(k_row, 64, ("min", "max"))
+        sel = oracle.select_decode(q_row, lo, hi, k=top_k, num_kv_blocks=pages, sink=DEC_SINK, local=DEC_LOCAL)
+        ref = oracle.decode_attention(q_row, k_row, v_row, sel, fmt="nvfp4", splits=world * splits_local)
+        err = (out[b, h].float().cpu() - ref[0, 0].float()).abs()
+        if not (err.max().item() <= CHECK_MAX_ABS and err.mean().item() <= CHECK_MEAN_ABS):
+            raise RuntimeError(f"decode check failed for (sequence {b}, KV head {h}): max-abs {err.max().item():.3e}, "
+                               f"mean-abs {err.mean().item():.3e} against the CPU oracle")
+        worst = max(worst, err.max().item())
+    return f"ok ({len(DEC_CHECK_ROWS)} (sequence, KV head) rows vs CPU oracle, max-abs {worst:.1e} <= {CHECK_MAX_ABS:g})"
 
 
 def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_gbs: float) -> dict:
     """Second half of the headline metric: one paged decode step for 32 sequences of 131072 cached tokens
-    (64-token pages through a seeded random page table, NVFP4 + fp16 shadow, Quest top-10 % + 4 sink + 16
-    recent pages).  A step = page selection + split-KV attention + merge.  With N GPUs every sequence's pages
-    are split N ways (KV-sequence sharding): kernel-scored candidates and partial results are exchanged with
-    two all-gathers per step.  Returns microseconds per step and whole-job algorithmic GB/s."""
+    (64-token pages through a seeded random page table, NVFP4 codes quantised from the fp16 shadow that holds the
+    selected pages, Quest top-10 % + 4 sink + 16 recent pages).  A step = quantise q + page selection + split-KV
+    attention + merge.  With N GPUs every sequence's pages are split N ways (KV-sequence sharding):
+    kernel-scored candidates and partial results are exchanged with two all-gathers per step.  Returns
+    microseconds per step, whole-job algorithmic GB/s and the outcome of the oracle check."""
     import torch.distributed as dist
 
     from thriftattention_b200 import _C
@@ -184,19 +272,22 @@ def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_g
     pool = DEC_BATCH * n_local
     g = torch.Generator(device=device)
     g.manual_seed(1234 + rank)
-    u8 = dict(dtype=torch.uint8, device=device)
-    k4 = torch.randint(0, 256, (pool, HKV, 64, D // 2), generator=g, **u8)
-    v4 = torch.randint(0, 256, (pool, HKV, D, 32), generator=g, **u8)
-    ks = torch.randint(40, 60, (pool, HKV, 64, D // 16), generator=g, **u8)      # E4M3 bytes of moderate size
-    vs = torch.randint(40, 60, (pool, HKV, D, 4), generator=g, **u8)
+    # the cache: fp16 shadow pools, their NVFP4 quantisation in the pool layouts, per-page key minima / maxima
     k_hi = torch.empty(pool, HKV, 64, D, dtype=torch.float16, device=device).normal_(generator=g)
     v_hi = torch.empty(pool, HKV, 64, D, dtype=torch.float16, device=device).normal_(generator=g)
-    k_min = torch.empty(DEC_BATCH, HKV, n_local, D, dtype=torch.float16, device=device).normal_(generator=g)
-    k_max = k_min + 1
+    k4, ks = _C.nvfp4_quantize(k_hi)                                   # [pool, HKV, 64, D/2], [.., D/16]
+    v4p, vsp = _C.nvfp4_quantize_transposed(v_hi)                      # padded to 128 tokens per page
+    v4, vs = v4p[..., :32].contiguous(), vsp[..., :4].contiguous()     # [pool, HKV, D, 32], [pool, HKV, D, 4]
+    del v4p, vsp
+    _, pmin, pmax = _C.block_stats(k_hi, 64, minmax=True)              # [pool, HKV, 1, D]
     table = torch.randperm(pool, generator=g, device=device).to(torch.int32).reshape(DEC_BATCH, n_local)
+    k_min = pmin[table.long(), :, 0].permute(0, 2, 1, 3).contiguous()  # [B, HKV, n_local, D] in logical page order
+    k_max = pmax[table.long(), :, 0].permute(0, 2, 1, 3).contiguous()
+    del pmin, pmax
     gq = torch.Generator(device=device)
     gq.manual_seed(99)                                                             # the query is replicated
     q = torch.empty(DEC_BATCH, HKV, DEC_GROUP, D, dtype=torch.float16, device=device).normal_(generator=gq)
+    splits_local = max(1, min(_C.decode_pick_splits(DEC_BATCH * HKV, n_local), n_local))
 
     def step():
         q4, qs = _C.nvfp4_quantize(q)
@@ -251,210 +342,38 @@ def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_g
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if flag.item() == 0:
             run, mode = step, "eager"
+    for _ in range(3):
+        run()
     barrier()
     n_steps = max(steps, 5) * 4
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(n_steps):
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(n_steps + 1)]
+    marks[0].record()
+    for i in range(n_steps):
         run()
-    e1.record()
+        marks[i + 1].record()
     barrier()
     _C.decode_status()
-    ms = torch.tensor([e0.elapsed_time(e1) / n_steps], device=device, dtype=torch.float64)
+    per_step = [marks[i].elapsed_time(marks[i + 1]) for i in range(n_steps)]
+    ms = torch.tensor([marks[0].elapsed_time(marks[-1]) / n_steps], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    # correctness of what was timed: an eager step with the same inputs, rows compared with the CPU oracle
+    out = step().reshape(DEC_BATCH, HKV, DEC_GROUP, D)
+    barrier()
+    check = check_decode_rows(out, q, k_hi, v_hi, table, world=world, rank=rank, pages=pages, top_k=top_k,
+                              splits_local=splits_local)
     n16 = top_k + DEC_SINK + DEC_LOCAL
     step_bytes = DEC_BATCH * HKV * ((pages - n16) * 9216 + n16 * 32768 + pages * 512)
     gbs = step_bytes / (ms.item() * 1e-3) / 1e9
+    stats = call_stats(per_step)
     return {"us_per_step": ms.item() * 1e3, "value": gbs, "unit": "GB/s", "bytes_per_step": step_bytes,
             "frac_of_hbm_peak": gbs / (hbm_gbs * world), "hbm_peak_gbs_per_gpu": hbm_gbs,
+            "us_per_step_rank0": {k: (v * 1e3 if k != "n" else v) for k, v in stats.items()},
+            "check": check,
             "workload": f"paged decode {DEC_BATCH} seq x {DEC_SEQ} tokens, {HQ}q/{HKV}kv x {D}, NVFP4 + fp16 shadow, Quest "
-                        f"{top_k} + {DEC_SINK} sink + {DEC_LOCAL} recent of {pages} pages in 16 bits; step = select + "
-                        f"attend + merge; KV sequence split over {world} GPU(s)",
+                        f"{top_k} + {DEC_SINK} sink + {DEC_LOCAL} recent of {pages} pages in 16 bits; step = quantise q + "
+                        f"select + attend + merge; KV sequence split over {world} GPU(s)",
             "launches_per_step": 4 if world == 1 else 6, "queued_as": mode}
-
-
-# ------------------------------------------------------------------------- small cases for profiler captures
-def run_small_case(kind: str) -> None:
-    """Three back-to-back launches of one hot kernel on a case of a few hundred MB (larger than L2): what a
-    full-set ncu capture is taken on.  Prints the algorithmic work of one launch."""
-    from thriftattention_b200 import _C
-    from thriftattention_b200.selection import resolve_top_k
-
-    device = torch.device("cuda", 0)
-    torch.manual_seed(0)
-    if kind == "prefill":
-        hq, hkv, seq = 16, 4, 8192
-        q, k, v = make_inputs(hq, hkv, seq, device, torch.float16)
-        top_k = resolve_top_k(seq // BLOCK, causal=True, fraction=FRACTION)
-        q_mean, _, _ = _C.block_stats(q, BLOCK, mean=True)
-        _, k_min, k_max = _C.block_stats(k, BLOCK, minmax=True)
-        sel = _C.quest_block_topk(q_mean, k_min, k_max, top_k, True, False)
-        q4, qs = _C.nvfp4_quantize(q)
-        k4, ks = _C.nvfp4_quantize_permuted(k)
-        v4, vs = _C.nvfp4_quantize_transposed(v)
-        for _ in range(3):
-            _C.prefill_attention(q, k, v, sel, q4, k4, v4, qs, ks, vs, causal=True, is_mx=False, is_bf16=False,
-                                 block_size=BLOCK, k_permuted=True, check_status=True)
-        torch.cuda.synchronize()
-        print(json.dumps({"case": "prefill 1x16q/4kv x8192 x128 fp16 NVFP4 Quest top-10%", "flops_per_launch":
-                          algorithmic_flops(hq, seq, D, BLOCK)}))
-        return
-    batch, seq = 8, 32768
-    pages = seq // 64
-    pool = batch * pages
-    u8 = dict(dtype=torch.uint8, device=device)
-    k4 = torch.randint(0, 256, (pool, HKV, 64, D // 2), **u8)
-    v4 = torch.randint(0, 256, (pool, HKV, D, 32), **u8)
-    ks = torch.randint(40, 60, (pool, HKV, 64, D // 16), **u8)
-    vs = torch.randint(40, 60, (pool, HKV, D, 4), **u8)
-    k_hi = torch.empty(pool, HKV, 64, D, dtype=torch.float16, device=device).normal_()
-    v_hi = torch.empty(pool, HKV, 64, D, dtype=torch.float16, device=device).normal_()
-    k_min = torch.randn(batch, HKV, pages, D, device=device).half()
-    k_max = k_min + 1
-    table = torch.randperm(pool, device=device).to(torch.int32).reshape(batch, pages)
-    q = torch.randn(batch, HKV, DEC_GROUP, D, device=device).half()
-    top_k = max(1, round(DEC_FRACTION * pages))
-    for _ in range(3):
-        q4, qs = _C.nvfp4_quantize(q)
-        sel = _C.select_decode_blocks(q, k_min, k_max, top_k, pages, False, sink=DEC_SINK, local=DEC_LOCAL)
-        _C.decode_attention(q, k_hi, v_hi, sel, q4, k4, v4, qs, ks, vs, is_mx=False, is_bf16=False, kv_len=seq,
-                            page_table=table, allow_padded_selection=True)
-    torch.cuda.synchronize()
-    _C.decode_status()
-    n16 = top_k + DEC_SINK + DEC_LOCAL
-    print(json.dumps({"case": "paged decode 8 seq x 32768 tokens, 32q/8kv x128, NVFP4 + fp16 shadow, 71 of 512 pages in 16 bits",
-                      "attention_bytes_per_launch": batch * HKV * ((pages - n16) * 9216 + n16 * 32768),
-                      "selection_bytes_per_launch": batch * HKV * pages * 512}))
-
-
-def run_sweep() -> None:
-    """Secondary measurements on one GPU, one JSON line each (not the headline; `python bench.py --sweep`):
-    the long-context MXFP4 / bf16 prefill with 5, 10 and 25 % of the 128-token blocks in 16 bits, the 32k NVFP4
-    prefill, and the HBM-bound helper kernels (quantisers, block statistics) as GB/s of algorithmic bytes."""
-    from thriftattention_b200 import _C
-    from thriftattention_b200.selection import resolve_top_k
-
-    device = torch.device("cuda", 0)
-    torch.cuda.set_device(device)
-    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    hbm = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else 6650.0
-
-    def timed(fn, reps):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / reps
-
-    for fmt, dtype, seq, fractions in (("mxfp4", torch.bfloat16, SEQ, (0.05, 0.10, 0.25)),
-                                       ("nvfp4", torch.float16, 32768, (0.10,))):
-        bf16, mx = dtype == torch.bfloat16, fmt == "mxfp4"
-        q, k, v = make_inputs(HQ, HKV, seq, device, dtype)
-        q_mean, _, _ = _C.block_stats(q, BLOCK, mean=True)
-        _, k_min, k_max = _C.block_stats(k, BLOCK, minmax=True)
-        q4, qs = getattr(_C, f"{fmt}_quantize")(q, bf16)
-        k4, ks = getattr(_C, f"{fmt}_quantize_permuted")(k, bf16)
-        v4, vs = getattr(_C, f"{fmt}_quantize_transposed")(v, bf16)
-        flops = algorithmic_flops(HQ, seq, D, BLOCK)
-        for fraction in fractions:
-            top_k = resolve_top_k(seq // BLOCK, causal=True, fraction=fraction)
-            sel = _C.quest_block_topk(q_mean, k_min, k_max, top_k, True, bf16)
-            ms = timed(lambda: _C.prefill_attention(q, k, v, sel, q4, k4, v4, qs, ks, vs, causal=True, is_mx=mx,
-                                                    is_bf16=bf16, block_size=BLOCK, k_permuted=True), 2 if seq > 65536 else 5)
-            print(json.dumps({"case": f"prefill_kernel 1x{HQ}q/{HKV}kv x{seq} x{D} {'bf16' if bf16 else 'fp16'} {fmt}, "
-                                      f"Quest top-{fraction:.0%} ({top_k} blocks of {BLOCK})", "ms": ms,
-                              "tflops": flops / ms / 1e9}), flush=True)
-        # helper kernels on this K / V: algorithmic bytes = 16-bit input + codes + scale bytes
-        elems = k.numel()
-        group = 32 if mx else 16
-        qbytes = elems * (2 + 0.5 + 1.0 / group)
-        for name, fn, nbytes in (
-                (f"{fmt}_quantize (rows)", lambda: getattr(_C, f"{fmt}_quantize")(k, bf16), qbytes),
-                (f"{fmt}_quantize_permuted", lambda: getattr(_C, f"{fmt}_quantize_permuted")(k, bf16), qbytes),
-                (f"{fmt}_quantize_transposed", lambda: getattr(_C, f"{fmt}_quantize_transposed")(v, bf16), qbytes),
-                ("block_stats min/max", lambda: _C.block_stats(k, BLOCK, minmax=True), elems * 2.0)):
-            ms = timed(fn, 10)
-            print(json.dumps({"case": f"{name} of [1,{HKV},{seq},{D}]", "us": ms * 1e3, "gbs": nbytes / ms / 1e6,
-                              "frac_of_hbm_peak": nbytes / ms / 1e6 / hbm}), flush=True)
-        del q, k, v, q4, k4, v4, qs, ks, vs
-        torch.cuda.empty_cache()
-
-
-def run_hf(prompt_len: int, new_tokens: int, layers: int) -> None:
-    """End to end through the Transformers hook on a random-init decoder of the Llama-3-8B shape (d_model 4096,
-    32 q / 8 kv heads x 128, SwiGLU 14336, RoPE theta 5e5, vocab 128256, fp16): prefill of `prompt_len` uniform
-    random token ids, then `new_tokens` greedy decode steps over a ThriftAttentionCache, NVFP4 with the top 10 %
-    of the key blocks in fp16.  One JSON line: prefill and decode token rates and the same model's exact-attention
-    (sdpa) rates for scale.  `python bench.py --hf`; logits parity against the oracle is covered at reduced sizes by
-    tests/test_gpu_hf_model.py."""
-    import contextlib
-
-    import transformers
-
-    from thriftattention_b200.integrations import (TransformersAttentionConfig, prepare_transformers_generation_cache,
-                                                   register_transformers_attention)
-
-    device = torch.device("cuda", 0)
-    torch.cuda.set_device(device)
-    name = register_transformers_attention(TransformersAttentionConfig(name="thrift_bench_hf", fraction=FRACTION))
-    cfg = transformers.LlamaConfig(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=layers,
-                                   num_attention_heads=32, num_key_value_heads=8, head_dim=128, rope_theta=500000.0,
-                                   max_position_embeddings=max(131072, prompt_len + new_tokens), tie_word_embeddings=False)
-    cfg._attn_implementation = name
-    torch.manual_seed(0)
-    with torch.device(device):
-        model = transformers.LlamaForCausalLM(cfg).half().eval()
-    ids = torch.randint(0, 128256, (1, prompt_len), generator=torch.Generator().manual_seed(1)).to(device)
-
-    def generate(use_hook: bool):
-        with torch.no_grad():
-            if use_hook:
-                model.config._attn_implementation = name
-                prep = prepare_transformers_generation_cache(model, ids, max_new_tokens=new_tokens)
-                ctx, cache, inputs, pos0 = prep.activate(), prep.past_key_values, prep.input_ids, prep.cache_position
-            else:
-                model.config._attn_implementation = "sdpa"
-                prep, ctx = None, contextlib.nullcontext()
-                cache, inputs = transformers.DynamicCache(config=model.config), ids
-                pos0 = torch.arange(prompt_len, device=device)
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-            with ctx:
-                ev[0].record()
-                out = model(input_ids=inputs, past_key_values=cache, cache_position=pos0, use_cache=True, logits_to_keep=1)
-                if prep is not None:
-                    prep.trim_padding()
-                tok = out.logits[:, -1].argmax(-1, keepdim=True)
-                ev[1].record()
-                for step in range(new_tokens):
-                    out = model(input_ids=tok, past_key_values=cache,
-                                cache_position=torch.tensor([prompt_len + step], device=device), use_cache=True)
-                    tok = out.logits[:, -1].argmax(-1, keepdim=True)
-                ev[2].record()
-            torch.cuda.synchronize()
-            assert torch.isfinite(out.logits).all()
-            return ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])
-
-    generate(True)                                           # warm-up (library handles, allocator, workspaces)
-    pre, dec = generate(True)
-    torch.cuda.empty_cache()
-    try:
-        generate(False)
-        pre_x, dec_x = generate(False)
-    except torch.OutOfMemoryError:
-        pre_x = dec_x = float("nan")
-    print(json.dumps({
-        "case": f"Transformers hook, Llama-3-8B-shaped decoder ({layers} layers, random init, fp16): prefill {prompt_len} "
-                f"tokens + {new_tokens} greedy decode steps, NVFP4 + block-mean top-{FRACTION:.0%}",
-        "prefill_ms": pre, "prefill_tokens_per_s": prompt_len / pre * 1e3,
-        "decode_ms_per_token": dec / new_tokens, "decode_tokens_per_s": new_tokens / dec * 1e3,
-        "sdpa_prefill_ms": pre_x, "sdpa_decode_ms_per_token": dec_x / new_tokens,
-        "peak_memory_gib": torch.cuda.max_memory_allocated(device) / 2 ** 30}), flush=True)
 
 
 def run_ours(args) -> dict:
@@ -476,34 +395,37 @@ def run_ours(args) -> dict:
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
+    headline = args.workload == "headline"
+    fmt, dtype, fraction = ("nvfp4", torch.float16, 0.10) if headline else ("mxfp4", torch.bfloat16, args.fraction)
     hkv_local, hq_local = HKV // world, HQ // world
-    dtype = torch.float16
     q, k, v = make_inputs(hq_local, hkv_local, SEQ, device, dtype, kv_head_offset=rank * hkv_local)
-    top_k = resolve_top_k(SEQ // BLOCK, causal=True, fraction=FRACTION)
-    cfg = ta.AttentionConfig(method="thrift", causal=True, selection="quest", fraction=FRACTION, block_size=BLOCK,
-                             quant_format=FMT)
-    gathered = torch.empty(world, 1, hq_local, SEQ, D, device=device, dtype=dtype) if world > 1 else None
-    attn_events = []
+    top_k = resolve_top_k(SEQ // BLOCK, causal=True, fraction=fraction)
+    cfg = ta.AttentionConfig(method="thrift", causal=True, selection="quest", fraction=fraction, block_size=BLOCK,
+                             quant_format=fmt)
+    # A rank's heads go through the public API in two calls so that (N > 1) the all-gather of the first half's output
+    # runs under the second half's kernel.  Halves are whole KV-head groups, or halves of the single group's q heads.
+    group = HQ // HKV
+    if hkv_local >= 2:
+        halves = [(0, hkv_local // 2), (hkv_local // 2, hkv_local)]
+        chunks = [(slice(a * group, b * group), slice(a, b)) for a, b in halves]
+    else:
+        chunks = [(slice(0, group // 2), slice(0, 1)), (slice(group // 2, group), slice(0, 1))]
+    if world == 1:
+        chunks = [(slice(0, hq_local), slice(0, hkv_local))]
+    gathered = [torch.empty(world, 1, c[0].stop - c[0].start, SEQ, D, device=device, dtype=dtype) for c in chunks] \
+        if world > 1 else None
+    kernel_events: list = []
 
-    def step(record_attn: bool):
-        # same call sequence as ta.attention(): statistics + selection, quantisation, fused kernel
-        q_mean, _, _ = _C.block_stats(q, BLOCK, mean=True)
-        _, k_min, k_max = _C.block_stats(k, BLOCK, minmax=True)
-        sel = _C.quest_block_topk(q_mean, k_min, k_max, top_k, True, False)
-        q4, qs = _C.nvfp4_quantize(q)
-        k4, ks = _C.nvfp4_quantize_permuted(k)
-        v4, vs = _C.nvfp4_quantize_transposed(v)
-        if record_attn:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-        out = _C.prefill_attention(q, k, v, sel, q4, k4, v4, qs, ks, vs, causal=True, is_mx=False, is_bf16=False,
-                                   block_size=BLOCK, k_permuted=True)
-        if record_attn:
-            e1.record()
-            attn_events.append((e0, e1))
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, out.unsqueeze(0))
-        return out
+    def step():
+        outs, works = [], []
+        for i, (qs_, kvs) in enumerate(chunks):
+            out = ta.attention(q[:, qs_], k[:, kvs], v[:, kvs], config=cfg)
+            outs.append(out)
+            if world > 1:
+                works.append(dist.all_gather_into_tensor(gathered[i], out.unsqueeze(0), async_op=True))
+        for w in works:
+            w.wait()
+        return outs
 
     def barrier():
         if world > 1:
@@ -511,22 +433,26 @@ def run_ours(args) -> dict:
         torch.cuda.synchronize()
 
     for _ in range(args.warmup):
-        step(False)
+        step()
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    _C.set_prefill_event_sink(kernel_events)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     barrier()
-    start.record()
-    for _ in range(args.steps):
-        out = step(True)
-    stop.record()
+    marks[0].record()
+    for i in range(args.steps):
+        step()
+        marks[i + 1].record()
     barrier()
+    _C.set_prefill_event_sink(None)
     clocks = sampler.stop() if rank == 0 else {}
-    ms = torch.tensor([start.elapsed_time(stop)], device=device, dtype=torch.float64)
-    attn_ms = torch.tensor([sum(a.elapsed_time(b) for a, b in attn_events) / len(attn_events)], device=device,
-                           dtype=torch.float64)
+    step_times = [marks[i].elapsed_time(marks[i + 1]) for i in range(args.steps)]
+    ms = torch.tensor([marks[0].elapsed_time(marks[-1])], device=device, dtype=torch.float64)
+    # the kernel time of a step = the sum over the step's launches (one per half), averaged over the steps
+    kernel_ms = sum(a.elapsed_time(b) for a, b in kernel_events) / args.steps
+    attn_ms = torch.tensor([kernel_ms], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         dist.all_reduce(attn_ms, op=dist.ReduceOp.MAX)
@@ -541,8 +467,8 @@ def run_ours(args) -> dict:
     d2h = out_host.numel() * out_host.element_size()
 
     def e2e_step():
-        # host in, host out: one KV-head group at a time, its copies overlapped with the neighbours' kernels
-        ta.attention_host(*hq_h, config=cfg, device=device, out=out_host)
+        # host in, host out: chunks of query heads, their copies overlapped with the neighbouring chunks' kernels
+        ta.attention_host(*hq_h, config=cfg, device=device, out=out_host, q_heads_per_chunk=2 if hkv_local == 1 else 0)
 
     e2e_steps = max(1, min(args.steps, 3))
     e2e_step()
@@ -559,22 +485,15 @@ def run_ours(args) -> dict:
     e2e_value = total_flops / (e2e_ms.item() * 1e-3) / 1e12
 
     # ---- decode half of the metric (all ranks take part; prefill tensors are released first) ----
-    del q, k, v, out, hq_h, out_host, gathered
+    del q, k, v, hq_h, out_host, gathered
     torch.cuda.empty_cache()
-    hbm_gbs = 6545.0
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            hbm_gbs = float(json.load(f)["hbm_gbs"])
-    except (OSError, KeyError, ValueError):
-        pass
-    decode = run_decode_leg(device, world, rank, args.steps, args.warmup, hbm_gbs)
+    peaks = measured_peaks()
+    hbm_gbs = float(peaks.get("hbm_gbs", 6650.0))
+    decode = run_decode_leg(device, world, rank, args.steps, args.warmup, hbm_gbs) if headline else None
 
     result = {}
     if rank == 0:
-        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-        if os.path.exists(peaks_path):
-            with open(peaks_path) as f:
-                peaks = json.load(f)
+        if "bf16_tflops_sustained" in peaks:
             bf16_peak, peak_src = float(peaks["bf16_tflops_sustained"]), "measured (bf16_tflops_sustained)"
         else:
             bf16_peak, peak_src = 1400.0, "fallback (1.4 PFLOP/s sustained)"
@@ -583,28 +502,40 @@ def run_ours(args) -> dict:
         blended_peak = 1.0 / ((1.0 - share16) / (FP4_TO_BF16_PEAK_RATIO * bf16_peak) + share16 / bf16_peak)
         per_rank_flops = total_flops / world
         achieved = per_rank_flops / (attn_ms.item() * 1e-3) / 1e12
-        cpu = run_reference(argparse.Namespace(gpus=args.gpus, steps=1, warmup=0))["cpu_baseline"] if world == 1 else None
+        launches_per_kernel = len(chunks)
+        traffic = SMALL_CASE_DRAM_BYTES * (per_rank_flops / launches_per_kernel) / SMALL_CASE_FLOPS
+        metric = METRIC if headline else f"prefill_attention_tflops_128k_top{fraction * 100:g}pct_mxfp4_bf16"
         result = {
-            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "metric": metric, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp4(e2m1, block-scaled)+f16, fp32 accumulate", "data": "synthetic",
-            "config": {"workload": "prefill 1x32q/8kv x131072 x128 fp16 causal, Quest top-10% (53 of 1024 128-token "
-                                   "blocks) in f16, rest NVFP4; step = stats+select+quantise+attend",
+            "config": {"workload": f"prefill 1x32q/8kv x131072 x128 {'fp16' if headline else 'bf16'} causal, Quest "
+                                   f"top-{fraction:.0%} ({top_k} of 1024 128-token blocks) in 16 bits, rest "
+                                   f"{fmt.upper()}; step = ta.attention(): stats+select+quantise+attend",
                        "partition": f"kv-head groups over {world} GPU(s)",
                        "l2": "inputs (1.5 GiB/GPU at N=1) exceed the 126 MB L2; no explicit flush"},
             "clocks": clocks,
+            "ms_per_step_rank0": call_stats(step_times),
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d * world,
                     "d2h_bytes_per_step": d2h * world, "ms_per_step": e2e_ms.item()},
-            "gpu_launches": 10 * args.steps,
+            "gpu_launches": 10 * len(chunks) * args.steps,
             "roofline": {"bound": "tensor", "kernel": "prefill_kernel (fused FP4 + f16 tcgen05 attention)",
                          "achieved": achieved, "peak": blended_peak, "unit": "TFLOP/s", "frac": achieved / blended_peak,
-                         "traffic": None, "kernel_ms": attn_ms.item(),
+                         "traffic": traffic, "traffic_note": "bytes per launch, scaled from the small-case ncu capture by FLOPs",
+                         "kernel_ms": attn_ms.item(), "launches_per_step": launches_per_kernel,
                          "peak_source": f"{peak_src} x blended FP4/f16 mix (FP4 peak taken as {FP4_TO_BF16_PEAK_RATIO:g}x bf16; "
-                                        f"f16 FLOP share {share16:.3f})"},
+                                        f"16-bit FLOP share {share16:.3f})"},
         }
-        result["decode"] = decode
-        if cpu is not None:
-            result["cpu_baseline"] = cpu
+        if decode is not None:
+            result["decode"] = decode
+            # the decode half of the metric, also as top-level keys
+            result["decode_us_per_step"] = decode["us_per_step"]
+            result["decode_gbs"] = decode["value"]
+            result["decode_frac_of_hbm_peak"] = decode["frac_of_hbm_peak"]
+            result["decode_check"] = decode["check"]
+        if world == 1 and headline:
+            result["cpu_baseline"] = run_reference(argparse.Namespace(gpus=args.gpus, steps=1, warmup=0,
+                                                                      with_small_cpu_config=False))["cpu_baseline"]
     if world > 1:
         dist.destroy_process_group()
     return result
@@ -616,25 +547,10 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--small", choices=["prefill", "decode"], default=None,
-                    help="run a small case of one kernel three times (for profiler captures) and exit")
-    ap.add_argument("--sweep", action="store_true",
-                    help="secondary single-GPU measurements (MXFP4 top-k sweep, 32k prefill, quantiser bandwidth)")
-    ap.add_argument("--hf", action="store_true",
-                    help="end-to-end run through the Transformers hook on a Llama-3-8B-shaped random-init decoder")
-    ap.add_argument("--hf-prompt", type=int, default=65536)
-    ap.add_argument("--hf-new-tokens", type=int, default=256)
-    ap.add_argument("--hf-layers", type=int, default=32)
+    ap.add_argument("--workload", default="headline", choices=["headline", "mxfp4-bf16"],
+                    help="headline = fp16 / NVFP4 top-10 %% prefill + the decode step; mxfp4-bf16 = the bf16 / MXFP4 prefill")
+    ap.add_argument("--fraction", type=float, default=0.10, help="share of 128-token blocks kept in bf16 (mxfp4-bf16 workload)")
     args = ap.parse_args()
-    if args.hf:
-        run_hf(args.hf_prompt, args.hf_new_tokens, args.hf_layers)
-        return
-    if args.sweep:
-        run_sweep()
-        return
-    if args.small:
-        run_small_case(args.small)
-        return
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     if result:
         print(json.dumps(result), flush=True)

@@ -454,6 +454,11 @@ def test_attention_host_pipelines_head_groups(cuda_device):
         got = ta.attention_host(q, k, v, config=cfg, device=cuda_device, kv_heads_per_chunk=per_chunk)
         torch.cuda.synchronize(cuda_device)
         assert got.is_pinned() and torch.equal(got, want)
+    got = ta.attention_host(q, k, v, config=cfg, device=cuda_device, q_heads_per_chunk=1)   # one query head at a time
+    torch.cuda.synchronize(cuda_device)
+    assert torch.equal(got, want)
+    with pytest.raises(ValueError, match="q_heads_per_chunk"):
+        ta.attention_host(q, k, v, config=cfg, device=cuda_device, kv_heads_per_chunk=2, q_heads_per_chunk=1)
     out = torch.zeros_like(want).pin_memory()
     assert ta.attention_host(q, k, v, config=cfg, device=cuda_device, out=out) is out
     torch.cuda.synchronize(cuda_device)
@@ -610,6 +615,37 @@ def test_paged_decode_equals_contiguous(cuda_device, dtype, fmt, B, hkv, G, S, t
                                         num_splits=splits, kv_len=S, page_table=table, return_partials=True)
     assert torch.equal(got, want) and torch.equal(go, wo) and torch.equal(gml, wml)
     ext.decode_status(cuda_device)
+
+
+def test_paged_decode_skips_page_table_entries_outside_the_pool(cuda_device):
+    """A negative or too-large page-table entry is never turned into an address: the kernel leaves the page out,
+    the call reports it through the status word, and the next call with a sound table is unaffected."""
+    torch.manual_seed(14)
+    ext = _ext()
+    B, hkv, G, S, d = 2, 2, 4, 2048, 128
+    pages = S // 64
+    q = torch.randn(B, hkv, G, d, device=cuda_device).half()
+    k = torch.randn(B, hkv, S, d, device=cuda_device).half()
+    v = torch.randn(B, hkv, S, d, device=cuda_device).half()
+    _, kmin, kmax = ext.block_stats(k, 64, minmax=True)
+    sel = ext.single_query_quest_topk(q, kmin, kmax, 4, pages, False)
+    q4, qs = ext.nvfp4_quantize(q)
+    k4, ks = ext.nvfp4_quantize(k)
+    v4, vs = ext.nvfp4_quantize_transposed(v)
+    want = ext.decode_attention(q, k, v, sel, q4, k4, v4, qs, ks, vs, is_mx=False, num_splits=4)
+    n_pool = B * pages
+    table = torch.randperm(n_pool, device=cuda_device).to(torch.int32).reshape(B, pages)
+    pk4, pks, pv4, pvs, pk, pv = _to_page_pools(table, n_pool, _u8(k4), _u8(ks), _u8(v4), _u8(vs), k, v)
+    bad = table.clone()
+    bad[0, 3] = -7
+    bad[1, 20] = n_pool
+    bad[1, int(sel[2, 0])] = 1 << 30                          # a selected (16-bit) page as well
+    with pytest.raises(RuntimeError, match="page-table"):
+        ext.decode_attention(q, pk, pv, sel, q4, pk4, pv4, qs, pks, pvs, is_mx=False, num_splits=4, kv_len=S,
+                             page_table=bad, check_status=True)
+    got = ext.decode_attention(q, pk, pv, sel, q4, pk4, pv4, qs, pks, pvs, is_mx=False, num_splits=4, kv_len=S,
+                               page_table=table, check_status=True)
+    assert torch.equal(got, want)
 
 
 def test_paged_decode_at_the_128k_shape_matches_oracle(cuda_device):

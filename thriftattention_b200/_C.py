@@ -385,6 +385,17 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
     return buf
 
 
+_prefill_event_sink = None
+
+
+def set_prefill_event_sink(sink) -> None:
+    """``sink`` = a list: every later ``prefill_attention`` call appends a (start, end) pair of CUDA events recorded
+    on the launching stream around the library call (scale re-tiling + the attention kernel), so that a caller of
+    the public API can time the kernel itself.  ``None`` switches the recording off."""
+    global _prefill_event_sink
+    _prefill_event_sink = sink
+
+
 def prefill_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale, v_scale_t, *,
                       causal, is_mx, is_bf16=False, block_size=64, k_permuted=True, round_partial=True, max_ctas=0,
                       check_status=False, seq_major_out=False):
@@ -426,6 +437,10 @@ def prefill_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_p
         nbytes = lib.ta100_prefill_workspace_bytes(b, hq, hkv, sq, skv, d, int(is_mx))
         ws = _workspace(out.device, nbytes)
         sel = selected_blocks if width > 0 else None
+        events = None
+        if _prefill_event_sink is not None:
+            events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            events[0].record()
         rc = lib.ta100_prefill_attention(
             _ptr(q_hi) if sel is not None else None, _ptr(k_hi) if sel is not None else None,
             _ptr(v_hi) if sel is not None else None, _ptr(sel), width, block_size, _ptr(q_packed), _ptr(k_packed),
@@ -433,6 +448,9 @@ def prefill_attention(q_hi, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_p
             sq, skv, kv_cap, d, int(causal), int(is_mx), int(is_bf16), int(k_permuted), int(round_partial), max_ctas,
             int(seq_major_out), _stream(out))
         _lib.check(rc, "prefill_attention")
+        if events is not None:
+            events[1].record()
+            _prefill_event_sink.append(events)
         if check_status:
             _lib.check(lib.ta100_prefill_status(_ptr(ws), b, hq, hkv, sq, skv, d, int(is_mx), _stream(out)),
                        "prefill_attention (device)")

@@ -67,17 +67,6 @@ constexpr uint32_t L_FP16 = 0x80000000u;  // page-list flag: 16-bit page
 __device__ int g_decode_status;           // wait site of a kernel whose bounded wait ran out, or STATUS_BAD_PAGE
 constexpr int STATUS_BAD_PAGE = 1000;    // a page-table entry outside the pool was skipped
 
-// Optional phase timers for the softmax warps (development aid; compiled out by default).
-#ifdef TA100_PROFILE_SOFTMAX
-__device__ long long g_dec_prof[16];
-#define DEC_PROF_DECL long long prof_t = clock64(), prof_acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-#define DEC_PROF(i) { const long long now_ = clock64(); prof_acc[i] += now_ - prof_t; prof_t = now_; }
-#define DEC_PROF_DUMP if (blockIdx.x == 0 && blockIdx.y == 0 && warp == 3 && lane == 0) { for (int i_ = 0; i_ < 10; ++i_) g_dec_prof[i_] = prof_acc[i_]; g_dec_prof[10] = n; }
-#else
-#define DEC_PROF_DECL
-#define DEC_PROF(i)
-#define DEC_PROF_DUMP
-#endif
 
 struct DecodeParams {
     const uint16_t* q_hi;   // [heads, G, D]
@@ -397,14 +386,7 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
             for (int a = 0; a < QK_ATOMS; ++a)
                 tmem_cp_sf_elect(tm + DTM_SFA_Q + a * 4, make_smem_desc(sbase + L::QSF + a * 512, 0, 128, SWZ_NONE));
         // ring position of step i: FP4 page -> slot i mod 5; 16-bit page -> tiles 2 (i - n4) (K) and + 1 (V)
-#ifdef TA100_PROFILE_SOFTMAX
-        long long qprof[5] = {0, 0, 0, 0, 0}, qt = clock64();
-#define DEC_QPROF(k) { const long long now_ = clock64(); qprof[k] += now_ - qt; qt = now_; }
-#else
-#define DEC_QPROF(k)
-#endif
         for (int i = 0; i < n && ok; ++i) {
-            DEC_QPROF(4)
             // operands of page i, and S of page i - 1 read by the softmax warps
             if (i < n4) {
                 ok = waitc(5, &bars.f_full[i % DEC_NS4], (i / DEC_NS4) & 1);
@@ -414,7 +396,6 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
             }
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
-            DEC_QPROF(0)
             // the K scale atoms go to tensor memory (two alternating buffers) before S of the previous page is free
             const uint32_t sfb = tm + ((i & 1) ? DTM_SFB_K2 : DTM_SFB_K);
             tc_fence_after_sync();
@@ -423,12 +404,10 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
                 for (int a = 0; a < QK_ATOMS; ++a)
                     tmem_cp_sf_elect(sfb + a * 4, make_smem_desc(sa + L::KSF + a * 512, 0, 128, SWZ_NONE));
             }
-            DEC_QPROF(1)
             if (i > 0) ok = waitc(7, &bars.s_free, (i - 1) & 1);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             tc_fence_after_sync();
-            DEC_QPROF(2)
             const uint32_t d_t = tm + DTM_S;
             if (i < n4) {
                 const uint32_t sa = sbase + L::SLOTS + (i % DEC_NS4) * DEC_SLOT4_BYTES;
@@ -452,11 +431,7 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
                 tc_commit_elect(smem_u32(&bars.h_empty[kt % DEC_NS16]));   // the K page is free once S is computed
             }
             tc_commit_elect(smem_u32(&bars.s_full));
-            DEC_QPROF(3)
         }
-#ifdef TA100_PROFILE_SOFTMAX
-        if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) for (int k_ = 0; k_ < 5; ++k_) g_dec_prof[11 + k_] = qprof[k_];
-#endif
     } else if (warp == 2) {
         // =========================== issuer of O += P V ===========================
         const uint32_t idesc_pv4 = make_idesc_fp4(128, D, MX ? 1 : 0, 0, 0);
@@ -557,15 +532,11 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
 
         float m_run = -FLT_MAX, l_run = 0.0f;
         bool prev_fp16 = false;
-        DEC_PROF_DECL
-        DEC_PROF(9)
         for (int i = 0; i < n && ok; ++i) {
             const bool fp16 = i >= n4;
-            DEC_PROF(0)
             ok = waitc(22, &bars.s_full, i & 1);
             if (!ok) break;
             tc_fence_after_sync();
-            DEC_PROF(1)
             float s[16];
             {
                 uint32_t r0[16], r1[16], r2[16], r3[16];
@@ -582,8 +553,6 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
             }
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&bars.s_free));
-            DEC_PROF(2)
-
             // running maximum of the whole page row (the four quarters sit in neighbouring lanes)
             // the P buffer of this step was last read by the PV of step i - 2: poll once now, look at the answer
             // only when the buffer is about to be written
@@ -600,8 +569,6 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
             const bool changed = active && i > 0 && m_new > m_run;
             const float rescale = ex2((m_run - m_new) * p.c2);
             m_run = m_new;
-
-            DEC_PROF(3)
             const bool need_rescale = __any_sync(0xFFFFFFFFu, changed);
             if ((need_rescale || fp16 || prev_fp16) && i > 0) {
                 // O, or a P tile spanning both buffers, is about to be touched: both earlier PVs must be done
@@ -611,7 +578,6 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
                 if (!ok) break;
                 tc_fence_after_sync();
             }
-            DEC_PROF(4)
             if (need_rescale) {
                 const float f = changed ? rescale : 1.0f;
 #pragma unroll 1
@@ -625,8 +591,6 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
                 }
                 tmem_wait_st();
             }
-            DEC_PROF(5)
-
             if (!fp16) {
                 // t = C p; group scale sf = amax(t) / 6 rounded to the scale format; codes = e2m1(t / sf), with
                 // the un-rounded sf, as the reference computes them
@@ -699,11 +663,9 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
                     *reinterpret_cast<uint4*>(base + (((2 * cq + 1) ^ (row & 7)) * 16)) = make_uint4(w[4], w[5], w[6], w[7]);
                 }
             }
-            DEC_PROF(6)
             fence_proxy_async_smem();
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&bars.p_full[buf]));
-            DEC_PROF(7)
             prev_fp16 = fp16;
         }
 
@@ -746,8 +708,6 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
                 p.part_ml[(pbase + row) * 2 + 1] = (bars.l_part[0][row] + bars.l_part[1][row]) + (bars.l_part[2][row] + bars.l_part[3][row]);
             }
         }
-        DEC_PROF(8)
-        DEC_PROF_DUMP
     }
 
     // ---- common exit ----
@@ -841,11 +801,6 @@ int decode_pick_splits(int heads, int npages) {
     return best;
 }
 
-#ifdef TA100_PROFILE_SOFTMAX
-int decode_profile_read(long long* out16) {
-    return static_cast<int>(cudaMemcpyFromSymbol(out16, g_dec_prof, sizeof(long long) * 16));
-}
-#endif
 
 size_t decode_workspace_bytes(int heads, int G, int d, int splits) {
     return static_cast<size_t>(heads) * splits * G * (d + 2) * sizeof(float);

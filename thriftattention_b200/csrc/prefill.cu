@@ -53,7 +53,7 @@ constexpr int NSETS = 4;             // softmax warp sets = S buffers = P tiles
 constexpr int NSLOTS = 6;            // K/V ring slots
 constexpr int SLOT_BYTES = 16384;    // one FP4 sub-step (K4, V4, scale atoms) or one 16-bit K or V tile
 constexpr int PSET_BYTES = 16384;    // P tile of a set: 4 KB of e2m1 or 16 KB of 16-bit values
-constexpr int NUM_THREADS = 32 * (3 + 4 * NSETS);   // 608: 104 registers per thread fit the SM's register file
+constexpr int NUM_THREADS = 32 * (3 + 4 * NSETS);   // 608; registers are handed out to 20 warps' worth: 96 per thread
 constexpr int SCHED_CAP = 2944;      // sub-step list entries per work item
 
 // tensor-memory columns (all 512 of the SM)
@@ -152,7 +152,7 @@ __device__ __forceinline__ bool bit_of(const uint32_t* b, int i) { return (b[i >
 // 64-row half in list order; then those of the second half that were not
 // already visited.  Returns the number of entries, or -1 if the list overflows;
 // n_fp4 receives the number of entries of the first kind.
-__device__ int build_schedule(const PrefillParams& p, const ItemInfo& it, uint32_t* bits, uint16_t* sched, int lane,
+__device__ __noinline__ int build_schedule(const PrefillParams& p, const ItemInfo& it, uint32_t* bits, uint16_t* sched, int lane,
                               int& n_fp4) {
     const int nqb = p.sq / p.block;
     const int row0 = it.t * QTILE;
@@ -303,7 +303,7 @@ __device__ __forceinline__ float exp_scaled_64(float (&s)[STEP], float c2, float
 }
 
 template <int D, bool MX, bool BF16, bool CAUSAL, bool KPERM>
-__global__ void __maxnreg__(104)   // 19 warps x 104 registers fill the SM's register file
+__global__ void __launch_bounds__(NUM_THREADS, 1)
 prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4, const __grid_constant__ CUtensorMap mapK4,
                const __grid_constant__ CUtensorMap mapV4, const __grid_constant__ CUtensorMap mapQ16,
                const __grid_constant__ CUtensorMap mapK16, const __grid_constant__ CUtensorMap mapV16) {
@@ -481,6 +481,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                             mma_nvfp4_elect(d_t, ad, bd, idesc_qk4, tmem + TM_SFA_Q + kb * 4, sfb + kb * 4, kb > 0);
                     }
                 } else {
+#pragma unroll 1
                     for (int ks = 0; ks < D / 16; ++ks) {
                         const uint32_t hf = ks / 4, kk = ks % 4;
                         const uint64_t ad = make_smem_desc(sbase + L::Q16 + hf * QTILE * 128 + kk * 32, 16, 1024, SWZ_128B);
@@ -531,6 +532,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                     if constexpr (MX) mma_mxfp4_elect(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
                     else mma_nvfp4_elect(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
                 } else {
+#pragma unroll 1
                     for (int ks = 0; ks < STEP / 16; ++ks) {
                         const uint64_t ad = make_smem_desc(pa + ks * 32, 16, 1024, SWZ_128B);
                         const uint64_t bd = make_smem_desc(sa + ks * 2048, STEP * 128, 1024, SWZ_128B);
@@ -690,8 +692,12 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                 }
                 fence_proxy_async_smem();
                 // O may be touched once the P V of the previous sub-step (another set's) has completed; the
-                // issuer adds this sub-step's P V only after the arrival below.
-                if (gsub > 0) {
+                // issuer adds this sub-step's P V only after the arrival below.  Only a moved maximum (or the state
+                // rounding) needs that wait: waiting every time would chain every sub-step behind the completion of
+                // the one before it.  This warp does not see every phase of that barrier, but it has seen (above,
+                // on its own p_free) the P V of sub-step gsub-4 complete, so the P V of gsub-5, committed earlier by
+                // the same thread, has completed as well and the barrier is in the phase asked for or past it.
+                if (gsub > 0 && (need_rescale || transition)) {
                     ok = mbar_wait(smem_u32(&bars.p_free[prev_set]), ((gsub - 1) / NSETS) & 1, abortp, budget);
                     if (!ok) return false;
                 }

@@ -437,12 +437,6 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-#ifdef TA100_PROFILE_SOFTMAX
-__device__ long long g_sel_prof[16];
-#define SELD_PROF(i) if (blockIdx.x == 0 && threadIdx.x == 0) g_sel_prof[i] = clock64();
-#else
-#define SELD_PROF(i)
-#endif
 constexpr int SELD_CAND_CAP = 512;   // exact re-scoring handles at most this many candidates
 
 template <int D>
@@ -647,7 +641,6 @@ __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const ui
 
     int n_sorted = 0;   // number of keys sorted at the end
     bool done = false;
-    SELD_PROF(0)
     if (two_pass) {
         // ---------------- pass 1: approximate scores with tensor cores ----------------
         // Each warp takes 16 pages at a time straight from global memory: thread (r = lane/4, t = lane%4) reads
@@ -728,7 +721,6 @@ __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const ui
                 if (pg1 < nk) approx[pg1] = hi;
             }
         }
-        SELD_PROF(1)
         {   // largest |statistic| seen (16-bit patterns of non-negative values order like the values)
             uint32_t m16 = max(kabs2 & 0xFFFFu, kabs2 >> 16);
 #pragma unroll
@@ -805,17 +797,12 @@ __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const ui
         }
         __syncthreads();
         const int n_cand = misc[0];
-        SELD_PROF(4)
-#ifdef TA100_PROFILE_SOFTMAX
-        if (blockIdx.x == 0 && threadIdx.x == 0) g_sel_prof[10] = n_cand;
-#endif
         if (n_cand <= SELD_CAND_CAP && isfinite(delta)) {
             // ---------------- pass 2: exact scores of the candidates ----------------
             n_sorted = pow2_at_least(n_cand);
             for (int i = tid; i < n_sorted; i += SELD_THREADS) keys[i] = ~0ull;
             __syncthreads();
             exact_pass(n_cand, false);
-            SELD_PROF(5)
             // order the few candidates by counting: rank = number of smaller keys (keys are distinct)
             unsigned long long* sorted = keys + SELD_CAND_CAP;
             for (int i = tid; i < n_sorted; i += SELD_THREADS) sorted[i] = ~0ull;
@@ -829,7 +816,6 @@ __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const ui
             __syncthreads();
             for (int i = tid; i < n_sorted; i += SELD_THREADS) keys[i] = sorted[i];
             __syncthreads();
-            SELD_PROF(6)
             done = true;
         }
     }
@@ -868,14 +854,8 @@ __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const ui
         row[i] = -1;
         if (srow) srow[i] = -FLT_MAX;
     }
-    SELD_PROF(7)
 }
 
-#ifdef TA100_PROFILE_SOFTMAX
-int select_profile_read(long long* out16) {
-    return static_cast<int>(cudaMemcpyFromSymbol(out16, g_sel_prof, sizeof(long long) * 16));
-}
-#endif
 
 int select_prefill_dispatch(const void* q_mean, const void* ka, const void* kb, void* out, int heads, int group, int nq,
                             int nk, int d, int k, int causal, int quest, int is_bf16, int sink, int local,
