@@ -227,7 +227,7 @@ def test_decode_selection_two_pass_adversarial(cuda_device, dtype):
             pivot = int(ref[h, k - 1])
             idx = torch.arange(37, nk - 20, 50)
             for t in (km, kmin, kmax):
-                t[0, h, idx] = t[0, h, pivot]
+                t[0, h, idx] = t[0, h, pivot].clone()
     run(qg, km, kmin, kmax)
     run(qg, km, kmin, kmax, kk=53, sink=0, local=0)
     # (2) all-zero query: every score is +0, every page ties, the candidate set overflows
@@ -246,7 +246,7 @@ def test_decode_selection_two_pass_adversarial(cuda_device, dtype):
         top = int(ref[h, 0])
         idx = torch.randperm(nk, generator=g)[:700]
         for t in (k_dup, kmin_dup, kmax_dup):
-            t[0, h, idx] = t[0, h, top]
+            t[0, h, idx] = t[0, h, top].clone()
     run(qg, k_dup, kmin_dup, kmax_dup)
     # (5) negative zero and sign mixtures in q
     q_sign = qg.clone()

@@ -47,7 +47,7 @@ def test_static_scratch_entry_matches_regular_entry_twice(cuda_device):
         expected = _C.decode_attention(q, k, v, sel, q4, k4, v4, qs, ks, vs, is_mx=False, is_bf16=False, num_splits=splits)
         out = torch.full((batch, hkv, group, 128), float("nan"), device=cuda_device, dtype=torch.float16)
         rc = lib.ta100_decode_attention_static(ptr(q), ptr(k), ptr(v), ptr(sel), sel.size(1), ptr(q4), ptr(k4), ptr(v4),
-                                               ptr(qs), ptr(ks), ptr(vs), None, 0, ptr(out), batch, hkv, group, seq, seq,
+                                               ptr(qs), ptr(ks), ptr(vs), None, 0, 0, ptr(out), batch, hkv, group, seq, seq,
                                                128, 0, 0, splits, stream)
         assert rc == 0, lib.ta100_status_string(rc)
         torch.cuda.synchronize()

@@ -50,8 +50,10 @@ namespace {
 constexpr int QTILE = 128;
 constexpr int STEP = 64;
 constexpr int NSETS = 4;             // softmax warp sets = S buffers = P tiles
-constexpr int NSLOTS = 6;            // K/V ring slots
-constexpr int SLOT_BYTES = 16384;    // one FP4 sub-step (K4, V4, scale atoms) or one 16-bit K or V tile
+constexpr int NSLOTS = 10;           // K/V ring slots
+constexpr int SLOT_BYTES = 10240;    // one FP4 sub-step (K4, V4, scale atoms) or one 64-channel half of a 16-bit K or V tile
+constexpr int REC_BYTES = 9728;      // packed FP4 record of one (KV head, sub-step): K4 4096 | K scale atoms 1024 | V4 4096 | V scale atom 512
+constexpr int REC_K_BYTES = 5120;    // its K part; the V part is the rest
 constexpr int PSET_BYTES = 16384;    // P tile of a set: 4 KB of e2m1 or 16 KB of 16-bit values
 constexpr int NUM_THREADS = 32 * (3 + 4 * NSETS);   // 608; registers are handed out to 20 warps' worth: 96 per thread
 constexpr int SCHED_CAP = 2944;      // sub-step list entries per work item
@@ -78,8 +80,7 @@ struct PrefillParams {
     int n_qtiles, n_items, nsteps_total, nkb;
     const int32_t* sel;
     const uint8_t* q_sf;
-    const uint8_t* k_sf;
-    const uint8_t* v_sf;
+    const uint8_t* kv_rec;   // packed K/V records, one per (KV head, sub-step)
     uint16_t* out;
     int* status;
     float c2;  // (1/sqrt(d)) * log2(e)
@@ -101,7 +102,7 @@ struct Smem {
     static constexpr int SCHED = XCH + sizeof(float) * 4 * NSETS * 32 * 5;   // SCHED_CAP x u16
     static constexpr int TOTAL = SCHED + SCHED_CAP * 2;
     // inside an FP4 slot
-    static constexpr int K4 = 0, V4 = 4096, KSF = 8192, VSF = 9216;
+    static constexpr int K4 = 0, KSF = 4096, V4 = 5120, VSF = 9216;   // K part [0, REC_K_BYTES), V part behind it
     static_assert(Q16 % 1024 == 0 && P % 1024 == 0 && SLOTS % 1024 == 0, "swizzled tiles need 1024-byte alignment");
     static_assert(TOTAL <= 227 * 1024, "one CTA must fit the SM's shared memory");
 };
@@ -110,9 +111,9 @@ struct Bars {
     uint64_t q_full, q_empty;
     uint64_t sched_full, sched_empty;
     uint64_t o_full;                                   // last P V of the item complete
-    uint64_t slot_full[NSLOTS], slot_empty[NSLOTS];
+    uint64_t k_full[NSLOTS], v_full[NSLOTS], slot_empty[NSLOTS];   // K part / V part of a slot landed; slot released
     uint64_t s_full[NSETS], s_free[NSETS];
-    uint64_t p_full[NSETS], p_free[NSETS];
+    uint64_t p_full[NSETS][2], p_free[NSETS][2];       // P tile in buffer (use & 1) written; the P V that read it complete
     uint64_t mch[4][NSETS];                            // row maxima of (row group, set) published
     uint64_t trans[4];                                 // row sums of a row group published for the state rounding
     uint64_t lend[4];                                  // ... and for the end of the item
@@ -135,13 +136,17 @@ struct ItemInfo {
     int h, t, kvh;
 };
 
+// Work items in launch order: all items of one KV head (its query heads x all q tiles, longest = latest tiles
+// first) before the next KV head's.  The CTAs that run at the same time then read the K/V of one or two KV heads
+// only, which stay in L2 while every q tile of those heads streams over them.
 __device__ __forceinline__ ItemInfo decode_item(const PrefillParams& p, int item) {
-    const int hq_flat = p.batch * p.hq_per_b;
+    const int per_kv = p.n_qtiles * p.group;
     ItemInfo it;
-    it.t = p.n_qtiles - 1 - item / hq_flat;  // longest (latest) tiles first
-    it.h = item % hq_flat;
-    const int b = it.h / p.hq_per_b;
-    it.kvh = b * p.hkv_per_b + (it.h % p.hq_per_b) / p.group;
+    it.kvh = item / per_kv;                       // flat (batch, KV head)
+    const int rem = item - it.kvh * per_kv;
+    it.t = p.n_qtiles - 1 - rem / p.group;
+    const int b = it.kvh / p.hkv_per_b;
+    it.h = b * p.hq_per_b + (it.kvh - b * p.hkv_per_b) * p.group + rem % p.group;
     return it;
 }
 
@@ -304,8 +309,7 @@ __device__ __forceinline__ float exp_scaled_64(float (&s)[STEP], float c2, float
 
 template <int D, bool MX, bool BF16, bool CAUSAL, bool KPERM>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4, const __grid_constant__ CUtensorMap mapK4,
-               const __grid_constant__ CUtensorMap mapV4, const __grid_constant__ CUtensorMap mapQ16,
+prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4, const __grid_constant__ CUtensorMap mapQ16,
                const __grid_constant__ CUtensorMap mapK16, const __grid_constant__ CUtensorMap mapV16) {
     using L = Smem<D>;
     constexpr int QK_ATOMS = MX ? 1 : D / 64;     // 512-byte scale atoms per tile for Q and K
@@ -339,14 +343,17 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
         mbar_init(smem_u32(&bars.sched_empty), 2 + 4 * NSETS);
         mbar_init(smem_u32(&bars.o_full), 1);
         for (int i = 0; i < NSLOTS; ++i) {
-            mbar_init(smem_u32(&bars.slot_full[i]), 1);
+            mbar_init(smem_u32(&bars.k_full[i]), 1);
+            mbar_init(smem_u32(&bars.v_full[i]), 1);
             mbar_init(smem_u32(&bars.slot_empty[i]), 1);
         }
         for (int i = 0; i < NSETS; ++i) {
             mbar_init(smem_u32(&bars.s_full[i]), 1);
             mbar_init(smem_u32(&bars.s_free[i]), 128);
-            mbar_init(smem_u32(&bars.p_full[i]), 128);
-            mbar_init(smem_u32(&bars.p_free[i]), 1);
+            mbar_init(smem_u32(&bars.p_full[i][0]), 128);
+            mbar_init(smem_u32(&bars.p_full[i][1]), 128);
+            mbar_init(smem_u32(&bars.p_free[i][0]), 1);
+            mbar_init(smem_u32(&bars.p_free[i][1]), 1);
         }
         for (int g = 0; g < 4; ++g) {
             for (int i = 0; i < NSETS; ++i) mbar_init(smem_u32(&bars.mch[g][i]), 32);
@@ -372,7 +379,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
     if (warp == 0) {
         // =========================== producer ===========================
         if (lane == 0) {
-            tma_prefetch_desc(&mapQ4); tma_prefetch_desc(&mapK4); tma_prefetch_desc(&mapV4);
+            tma_prefetch_desc(&mapQ4);
             tma_prefetch_desc(&mapQ16); tma_prefetch_desc(&mapK16); tma_prefetch_desc(&mapV16);
         }
         uint32_t gslot = 0;
@@ -413,27 +420,28 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                     ok = mbar_wait(smem_u32(&bars.slot_empty[slot]), ((gslot / NSLOTS) & 1) ^ 1, abortp, budget);
                     if (!ok) break;
                     if (lane == 0) {
-                        const uint32_t bar = smem_u32(&bars.slot_full[slot]);
                         const uint32_t sa = sbase + L::SLOTS + slot * SLOT_BYTES;
-                        mbar_expect_tx(bar, STEP * ROW4 + D * 32 + QK_ATOMS * 512 + 512);
-                        tma_load_3d(sa + L::K4, &mapK4, bar, 0, st * STEP, it.kvh);
-                        tma_load_3d(sa + L::V4, &mapV4, bar, st * (STEP / 2), 0, it.kvh);
-                        bulk_load(sa + L::KSF, p.k_sf + (static_cast<long long>(it.kvh) * p.nsteps_total + st) * QK_ATOMS * 512,
-                                  QK_ATOMS * 512, bar);
-                        bulk_load(sa + L::VSF, p.v_sf + (static_cast<long long>(it.kvh) * p.nsteps_total + st) * 512, 512, bar);
+                        const uint8_t* rec = p.kv_rec + (static_cast<long long>(it.kvh) * p.nsteps_total + st) * REC_BYTES;
+                        // one contiguous record (K4 and V4 tiles already in their swizzled shared-memory order + scale
+                        // atoms), copied in two parts so that each issuer waits for its own operands only
+                        const uint32_t kbar = smem_u32(&bars.k_full[slot]), vbar = smem_u32(&bars.v_full[slot]);
+                        mbar_expect_tx(kbar, REC_K_BYTES);
+                        bulk_load(sa, rec, REC_K_BYTES, kbar);
+                        mbar_expect_tx(vbar, REC_BYTES - REC_K_BYTES);
+                        bulk_load(sa + REC_K_BYTES, rec + REC_K_BYTES, REC_BYTES - REC_K_BYTES, vbar);
                     }
                     gslot += 1;
                 } else {
-                    for (int which = 0; which < 2 && ok; ++which) {  // K tile, then V tile
+                    for (int part = 0; part < 2 * HALVES && ok; ++part) {  // K tile, then V tile, one slot per 64-channel half
+                        const int which = part / HALVES, hf = part % HALVES;
                         const uint32_t slot = gslot % NSLOTS;
                         ok = mbar_wait(smem_u32(&bars.slot_empty[slot]), ((gslot / NSLOTS) & 1) ^ 1, abortp, budget);
                         if (!ok) break;
                         if (lane == 0) {
-                            const uint32_t bar = smem_u32(&bars.slot_full[slot]);
+                            const uint32_t bar = smem_u32(which ? &bars.v_full[slot] : &bars.k_full[slot]);
                             const uint32_t sa = sbase + L::SLOTS + slot * SLOT_BYTES;
-                            mbar_expect_tx(bar, STEP * D * 2);
-                            for (int hf = 0; hf < HALVES; ++hf)
-                                tma_load_3d(sa + hf * STEP * 128, which ? &mapV16 : &mapK16, bar, hf * 64, st * STEP, it.kvh);
+                            mbar_expect_tx(bar, STEP * 128);
+                            tma_load_3d(sa, which ? &mapV16 : &mapK16, bar, hf * 64, st * STEP, it.kvh);
                         }
                         gslot += 1;
                     }
@@ -442,11 +450,24 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
         }
     } else if (warp == 1) {
         // =========================== S = Q K^T issuer ===========================
-        uint32_t gsub = 0, gslot = 0;     // sub-steps and ring slots consumed so far by this CTA
+        // This warp (and the next) is a serial instruction stream that every sub-step of the CTA passes through, so its
+        // loop is kept lean: ring position and phase are running counters, all operands are warp-uniform, and the
+        // tcgen05 instructions of a sub-step are issued together by one elected lane.
+        uint32_t gsub = 0;                // sub-steps consumed so far by this CTA
+        uint32_t slot = 0, kpar = 0;      // ring position; bit s of kpar = parity of the next K-part fill of slot s
         int n_item = 0;
         bool ok = true;
         const uint32_t idesc_qk4 = make_idesc_fp4(128, STEP, MX ? 1 : 0, 0, 0);
         const uint32_t idesc_qk16 = make_idesc_f16(128, STEP, BF16 ? 1 : 0, 0, 0);
+        const uint32_t bar_k_full = smem_u32(&bars.k_full[0]), bar_slot_empty = smem_u32(&bars.slot_empty[0]);
+        const uint32_t bar_s_full = smem_u32(&bars.s_full[0]), bar_s_free = smem_u32(&bars.s_free[0]);
+        const uint64_t qd0 = make_smem_desc(sbase + L::Q4, 16, SBO_QK, SWZ_QK);             // + 2 per 32-byte K block
+        const uint64_t kd0 = make_smem_desc(sbase + L::SLOTS + L::K4, 16, SBO_QK, SWZ_QK);  // + slot * SLOT_BYTES / 16
+        const uint64_t sfd0 = make_smem_desc(sbase + L::SLOTS + L::KSF, 0, 128, SWZ_NONE);
+        auto next_slot = [&]() { if (++slot == NSLOTS) slot = 0; };
+        // K parts (FP4 records, 16-bit K tiles) land on k_full, V parts on v_full: this warp only ever waits on k_full and
+        // the other issuer on v_full, each keeping the parity of every slot's next fill of its kind.
+        auto wait_k = [&]() { const bool r = mbar_wait(bar_k_full + slot * 8, (kpar >> slot) & 1u, abortp, budget); kpar ^= 1u << slot; return r; };
         for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
             ok = mbar_wait(smem_u32(&bars.sched_full), n_item & 1, abortp, budget);
             if (!ok) break;
@@ -461,38 +482,52 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                 const uint32_t e = sched[i];
                 const bool fp16 = e & E_FP16;
                 const uint32_t set = gsub & (NSETS - 1), use = gsub / NSETS;
-                const uint32_t slot = gslot % NSLOTS;
-                ok = mbar_wait(smem_u32(&bars.slot_full[slot]), (gslot / NSLOTS) & 1, abortp, budget) &&
-                     mbar_wait(smem_u32(&bars.s_free[set]), (use & 1) ^ 1, abortp, budget);
-                if (!ok) break;
-                tc_fence_after_sync();
-                const uint32_t sa = sbase + L::SLOTS + slot * SLOT_BYTES;
                 const uint32_t d_t = tmem + TM_S + set * STEP;
+                const bool last = i + 1 == n;
                 if (!fp16) {
+                    ok = wait_k() && mbar_wait(bar_s_free + set * 8, (use & 1) ^ 1, abortp, budget);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t soff = slot * (SLOT_BYTES / 16);
                     const uint32_t sfb = tmem + TM_SFB_K + set * 8;
-                    for (int a = 0; a < QK_ATOMS; ++a)
-                        tmem_cp_sf_elect(sfb + a * 4, make_smem_desc(sa + L::KSF + a * 512, 0, 128, SWZ_NONE));
-                    for (int kb = 0; kb < KBLK; ++kb) {
-                        const uint64_t ad = make_smem_desc(sbase + L::Q4 + kb * 32, 16, SBO_QK, SWZ_QK);
-                        const uint64_t bd = make_smem_desc(sa + L::K4 + kb * 32, 16, SBO_QK, SWZ_QK);
-                        if constexpr (MX)
-                            mma_mxfp4_elect(d_t, ad, bd, make_idesc_fp4(128, STEP, 1, kb * 2, kb * 2), tmem + TM_SFA_Q, sfb, kb > 0);
-                        else
-                            mma_nvfp4_elect(d_t, ad, bd, idesc_qk4, tmem + TM_SFA_Q + kb * 4, sfb + kb * 4, kb > 0);
+                    if (elect_one()) {
+                        for (int a = 0; a < QK_ATOMS; ++a) tmem_cp_sf(sfb + a * 4, sfd0 + soff + a * 32);
+                        for (int kb = 0; kb < KBLK; ++kb) {
+                            if constexpr (MX)
+                                mma_mxfp4(d_t, qd0 + kb * 2, kd0 + soff + kb * 2, make_idesc_fp4(128, STEP, 1, kb * 2, kb * 2),
+                                          tmem + TM_SFA_Q, sfb, kb > 0);
+                            else
+                                mma_nvfp4(d_t, qd0 + kb * 2, kd0 + soff + kb * 2, idesc_qk4, tmem + TM_SFA_Q + kb * 4, sfb + kb * 4, kb > 0);
+                        }
+                        tc_commit(bar_s_full + set * 8);
+                        if (last) tc_commit(smem_u32(&bars.q_empty));
                     }
+                    __syncwarp();
+                    next_slot();
                 } else {
+                    // K tile: one slot per 64-channel half
+                    uint32_t kslot[HALVES];
+                    for (int hf = 0; hf < HALVES && ok; ++hf) {
+                        kslot[hf] = slot;
+                        ok = wait_k();
+                        next_slot();
+                    }
+                    if (ok) ok = mbar_wait(bar_s_free + set * 8, (use & 1) ^ 1, abortp, budget);
+                    if (!ok) break;
+                    tc_fence_after_sync();
 #pragma unroll 1
                     for (int ks = 0; ks < D / 16; ++ks) {
                         const uint32_t hf = ks / 4, kk = ks % 4;
                         const uint64_t ad = make_smem_desc(sbase + L::Q16 + hf * QTILE * 128 + kk * 32, 16, 1024, SWZ_128B);
-                        const uint64_t bd = make_smem_desc(sa + hf * STEP * 128 + kk * 32, 16, 1024, SWZ_128B);
+                        const uint64_t bd = make_smem_desc(sbase + L::SLOTS + kslot[hf] * SLOT_BYTES + kk * 32, 16, 1024, SWZ_128B);
                         mma_f16_elect(d_t, ad, bd, idesc_qk16, ks > 0);
                     }
-                    tc_commit_elect(smem_u32(&bars.slot_empty[slot]));  // the K tile is free once S is computed
+                    for (int hf = 0; hf < HALVES; ++hf)             // the K tile is free once S is computed
+                        tc_commit_elect(bar_slot_empty + kslot[hf] * 8);
+                    tc_commit_elect(bar_s_full + set * 8);
+                    if (last) tc_commit_elect(smem_u32(&bars.q_empty));
+                    for (int hf = 0; hf < HALVES; ++hf) next_slot();          // the V tile's slots
                 }
-                tc_commit_elect(smem_u32(&bars.s_full[set]));
-                if (i + 1 == n) tc_commit_elect(smem_u32(&bars.q_empty));
-                gslot += fp16 ? 2 : 1;
                 ++gsub;
             }
             if (lane == 0) mbar_arrive(smem_u32(&bars.sched_empty));
@@ -500,11 +535,19 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
     } else if (warp == 2) {
         // =========================== O += P V issuer ===========================
         tmem_cp_sf_elect(tmem + TM_SFA_P, make_smem_desc(sbase + L::CSF, 0, 128, SWZ_NONE));
-        uint32_t gsub = 0, gslot = 0;
+        uint32_t gsub = 0;
+        uint32_t slot = 0, vpar = 0;      // ring position; bit s of vpar = parity of the next V-part fill of slot s
         int n_item = 0;
         bool ok = true;
         const uint32_t idesc_pv4 = make_idesc_fp4(128, D, MX ? 1 : 0, 0, 0);
-        const uint32_t idesc_pv16 = make_idesc_f16(128, D, BF16 ? 1 : 0, 0, 1);
+        const uint32_t idesc_pv16 = make_idesc_f16(128, 64, BF16 ? 1 : 0, 0, 1), idesc_pv16w = make_idesc_f16(128, D, BF16 ? 1 : 0, 0, 1);
+        const uint32_t bar_v_full = smem_u32(&bars.v_full[0]), bar_slot_empty = smem_u32(&bars.slot_empty[0]);
+        const uint32_t bar_p_full = smem_u32(&bars.p_full[0][0]), bar_p_free = smem_u32(&bars.p_free[0][0]);
+        const uint64_t pd0 = make_smem_desc(sbase + L::P, 16, 256, SWZ_32B);                 // + set * PSET_BYTES / 16 + buffer * 256
+        const uint64_t vd0 = make_smem_desc(sbase + L::SLOTS + L::V4, 16, 256, SWZ_32B);     // + slot * SLOT_BYTES / 16
+        const uint64_t sfd0 = make_smem_desc(sbase + L::SLOTS + L::VSF, 0, 128, SWZ_NONE);
+        auto next_slot = [&]() { if (++slot == NSLOTS) slot = 0; };
+        auto wait_v = [&]() { const bool r = mbar_wait(bar_v_full + slot * 8, (vpar >> slot) & 1u, abortp, budget); vpar ^= 1u << slot; return r; };
         for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
             ok = mbar_wait(smem_u32(&bars.sched_full), n_item & 1, abortp, budget);
             if (!ok) break;
@@ -512,37 +555,64 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
             for (int i = 0; i < n && ok; ++i) {
                 const uint32_t e = sched[i];
                 const bool fp16 = e & E_FP16;
-                const uint32_t set = gsub & (NSETS - 1), use = gsub / NSETS;
-                // this warp looks at every phase of every slot barrier, also the K tile's of a 16-bit sub-step
-                ok = mbar_wait(smem_u32(&bars.slot_full[gslot % NSLOTS]), (gslot / NSLOTS) & 1, abortp, budget);
-                const uint32_t pv_slot = fp16 ? gslot + 1 : gslot;
-                if (ok && fp16) ok = mbar_wait(smem_u32(&bars.slot_full[pv_slot % NSLOTS]), (pv_slot / NSLOTS) & 1, abortp, budget);
-                if (ok) ok = mbar_wait(smem_u32(&bars.p_full[set]), use & 1, abortp, budget);
-                if (!ok) break;
-                tc_fence_after_sync();
-                const uint32_t sa = sbase + L::SLOTS + (pv_slot % NSLOTS) * SLOT_BYTES;
-                const uint32_t pa = sbase + L::P + set * PSET_BYTES;
-                const uint32_t d_t = tmem + TM_O;
+                const uint32_t set = gsub & (NSETS - 1), use = gsub / NSETS, pb = set * 2 + (use & 1);
                 const uint32_t acc = i > 0 ? 1u : 0u;
+                const bool last = i + 1 == n;
                 if (!fp16) {
+                    ok = wait_v() && mbar_wait(bar_p_full + pb * 8, (use >> 1) & 1, abortp, budget);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t soff = slot * (SLOT_BYTES / 16);
                     const uint32_t sfb = tmem + TM_SFB_V + set * 4;
-                    tmem_cp_sf_elect(sfb, make_smem_desc(sa + L::VSF, 0, 128, SWZ_NONE));
-                    const uint64_t ad = make_smem_desc(pa, 16, 256, SWZ_32B);
-                    const uint64_t bd = make_smem_desc(sa + L::V4, 16, 256, SWZ_32B);
-                    if constexpr (MX) mma_mxfp4_elect(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
-                    else mma_nvfp4_elect(d_t, ad, bd, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
-                } else {
-#pragma unroll 1
-                    for (int ks = 0; ks < STEP / 16; ++ks) {
-                        const uint64_t ad = make_smem_desc(pa + ks * 32, 16, 1024, SWZ_128B);
-                        const uint64_t bd = make_smem_desc(sa + ks * 2048, STEP * 128, 1024, SWZ_128B);
-                        mma_f16_elect(d_t, ad, bd, idesc_pv16, (acc == 0 && ks == 0) ? 0 : 1);
+                    const uint64_t ad = pd0 + set * (PSET_BYTES / 16) + (use & 1) * 256;
+                    if (elect_one()) {
+                        tmem_cp_sf(sfb, sfd0 + soff);
+                        if constexpr (MX) mma_mxfp4(tmem + TM_O, ad, vd0 + soff, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
+                        else mma_nvfp4(tmem + TM_O, ad, vd0 + soff, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
+                        tc_commit(bar_slot_empty + slot * 8);
+                        tc_commit(bar_p_free + pb * 8);
+                        if (last) tc_commit(smem_u32(&bars.o_full));
                     }
+                    __syncwarp();
+                    next_slot();
+                } else {
+                    for (int hf = 0; hf < HALVES; ++hf) next_slot();          // the K tile's slots
+                    uint32_t vslot[HALVES];
+                    for (int hf = 0; hf < HALVES && ok; ++hf) {
+                        vslot[hf] = slot;
+                        ok = wait_v();
+                        next_slot();
+                    }
+                    if (ok) ok = mbar_wait(bar_p_full + pb * 8, (use >> 1) & 1, abortp, budget);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t pa = sbase + L::P + set * PSET_BYTES;
+                    // The V tile's 64-channel halves sit in separate slots.  Neighbouring slots make one MN-major operand
+                    // (leading-dimension offset = the slot size) for N = D MMAs; across the ring's wrap it is one
+                    // N = 64 chain per half.
+                    if (HALVES == 1 || vslot[HALVES - 1] == vslot[0] + HALVES - 1) {
+                        const uint32_t va = sbase + L::SLOTS + vslot[0] * SLOT_BYTES;
+#pragma unroll 1
+                        for (int ks = 0; ks < STEP / 16; ++ks) {
+                            const uint64_t ad = make_smem_desc(pa + ks * 32, 16, 1024, SWZ_128B);
+                            const uint64_t bd = make_smem_desc(va + ks * 2048, SLOT_BYTES, 1024, SWZ_128B);
+                            mma_f16_elect(tmem + TM_O, ad, bd, idesc_pv16w, (acc == 0 && ks == 0) ? 0 : 1);
+                        }
+                    } else {
+                        for (int hf = 0; hf < HALVES; ++hf) {
+                            const uint32_t va = sbase + L::SLOTS + vslot[hf] * SLOT_BYTES;
+#pragma unroll 1
+                            for (int ks = 0; ks < STEP / 16; ++ks) {
+                                const uint64_t ad = make_smem_desc(pa + ks * 32, 16, 1024, SWZ_128B);
+                                const uint64_t bd = make_smem_desc(va + ks * 2048, 16, 1024, SWZ_128B);
+                                mma_f16_elect(tmem + TM_O + hf * 64, ad, bd, idesc_pv16, (acc == 0 && ks == 0) ? 0 : 1);
+                            }
+                        }
+                    }
+                    for (int hf = 0; hf < HALVES; ++hf) tc_commit_elect(bar_slot_empty + vslot[hf] * 8);
+                    tc_commit_elect(bar_p_free + pb * 8);
+                    if (last) tc_commit_elect(smem_u32(&bars.o_full));
                 }
-                tc_commit_elect(smem_u32(&bars.slot_empty[pv_slot % NSLOTS]));
-                tc_commit_elect(smem_u32(&bars.p_free[set]));
-                if (i + 1 == n) tc_commit_elect(smem_u32(&bars.o_full));
-                gslot += fp16 ? 2 : 1;
                 ++gsub;
             }
             if (lane == 0) mbar_arrive(smem_u32(&bars.sched_empty));
@@ -559,7 +629,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
         uint8_t* const ptile = smem + L::P + set * PSET_BYTES;
         uint32_t gsub0 = 0;                       // CTA-wide index of the item's first sub-step
         int n_item = 0, n_nonempty = 0, n_trans = 0;
-        bool ok = true;
+        bool ok = true, prev_wide = false;      // prev_wide: this set's previous sub-step wrote a 16-bit P tile
         for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
             const ItemInfo it = decode_item(p, item);
             ok = mbar_wait(smem_u32(&bars.sched_full), n_item & 1, abortp, budget);
@@ -634,9 +704,15 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                 const bool transition = fp16 && has_trans && i == n_fp4;
                 const bool need_rescale = __any_sync(0xFFFFFFFFu, changed && i > 0);
 
-                // the P tile of this set is free once the P V of its previous sub-step completed
-                ok = mbar_wait(smem_u32(&bars.p_free[set]), (use & 1) ^ 1, abortp, budget);
+                // The set's P memory holds two FP4 tiles (buffer use & 1) or one 16-bit tile that spans both.  Buffer
+                // b is free once the P V of the set's sub-step two uses ago completed; a 16-bit tile - this one or the
+                // previous one - also involves the other buffer, whose latest reader is the previous use.
+                const uint32_t pbuf = use & 1;
+                ok = mbar_wait(smem_u32(&bars.p_free[set][pbuf]), ((use >> 1) & 1) ^ 1, abortp, budget);
+                if (ok && (fp16 || prev_wide) && use > 0)
+                    ok = mbar_wait(smem_u32(&bars.p_free[set][pbuf ^ 1]), ((use - 1) >> 1) & 1, abortp, budget);
                 if (!ok) return false;
+                prev_wide = fp16;
                 if constexpr (!fp16) {
                     uint32_t w[STEP / 8];
                     if (part) {
@@ -654,7 +730,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                     }
                     // 128 rows x 32 bytes, 32-byte swizzle
                     const uint32_t r8 = row & 7;
-                    uint8_t* base = ptile + (row >> 3) * 256 + r8 * 32;
+                    uint8_t* base = ptile + pbuf * 4096 + (row >> 3) * 256 + r8 * 32;
                     const uint32_t x = (r8 >> 2) & 1;
                     *reinterpret_cast<uint4*>(base + ((0 ^ x) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
                     *reinterpret_cast<uint4*>(base + ((1 ^ x) * 16)) = make_uint4(w[4], w[5], w[6], w[7]);
@@ -695,10 +771,12 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                 // issuer adds this sub-step's P V only after the arrival below.  Only a moved maximum (or the state
                 // rounding) needs that wait: waiting every time would chain every sub-step behind the completion of
                 // the one before it.  This warp does not see every phase of that barrier, but it has seen (above,
-                // on its own p_free) the P V of sub-step gsub-4 complete, so the P V of gsub-5, committed earlier by
-                // the same thread, has completed as well and the barrier is in the phase asked for or past it.
+                // on its own buffer) the P V of sub-step gsub-8 complete, so the P V of gsub-9 - the previous reader
+                // of the buffer asked about, committed earlier by the same thread - has completed as well and the
+                // barrier is in the phase asked for or past it.
                 if (gsub > 0 && (need_rescale || transition)) {
-                    ok = mbar_wait(smem_u32(&bars.p_free[prev_set]), ((gsub - 1) / NSETS) & 1, abortp, budget);
+                    const uint32_t puse = (gsub - 1) / NSETS;
+                    ok = mbar_wait(smem_u32(&bars.p_free[prev_set][puse & 1]), (puse >> 1) & 1, abortp, budget);
                     if (!ok) return false;
                 }
                 if (transition) {
@@ -727,20 +805,27 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                     }
                     tmem_wait_st();
                 } else if (need_rescale) {
+                    // 64 columns per tensor-memory round trip (the scores' registers are free by now): this block sits
+                    // on the chain that orders consecutive sub-steps, so its length counts
                     tc_fence_after_sync();
 #pragma unroll 1
-                    for (int c = 0; c < D; c += 32) {
-                        uint32_t ra[32];
+                    for (int c = 0; c < D; c += 64) {
+                        uint32_t ra[32], rb[32];
                         tmem_ld32(tmem + lane_addr + TM_O + c, ra);
+                        tmem_ld32(tmem + lane_addr + TM_O + c + 32, rb);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) ra[j] = __float_as_uint(__uint_as_float(ra[j]) * rescale_o);
+                        for (int j = 0; j < 32; ++j) {
+                            ra[j] = __float_as_uint(__uint_as_float(ra[j]) * rescale_o);
+                            rb[j] = __float_as_uint(__uint_as_float(rb[j]) * rescale_o);
+                        }
                         tmem_st32(tmem + lane_addr + TM_O + c, ra);
+                        tmem_st32(tmem + lane_addr + TM_O + c + 32, rb);
                     }
                     tmem_wait_st();
                 }
                 tc_fence_before_sync();
-                mbar_arrive(smem_u32(&bars.p_full[set]));
+                mbar_arrive(smem_u32(&bars.p_full[set][pbuf]));
                 return true;
             };
             {
@@ -839,30 +924,64 @@ __global__ void retile_row_scales_kernel(const uint8_t* __restrict__ src, uint8_
     }
 }
 
-// v_scale_t [heads, D, pg] -> atoms [heads, nsteps, 512]: scale(d = 32*m1+m0, step*per + j)
-__global__ void retile_v_scales_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int heads, int d,
-                                       int pg, int nsteps, int per) {
-    const long long total = static_cast<long long>(heads) * nsteps * 128;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int wi = static_cast<int>(i & 127);
-        const int m0 = wi >> 2, m1 = wi & 3;
-        const long long rest = i >> 7;
-        const int step = static_cast<int>(rest % nsteps);
-        const int head = static_cast<int>(rest / nsteps);
-        const int ch = 32 * m1 + m0;
+// ---------------------------------------------------------------------------
+// K/V packing for the attention kernel: one contiguous REC_BYTES record per (KV head, 64-token sub-step), laid out
+// exactly as the kernel's ring slot: the K4 tile [64 keys x D/2 bytes] and the V4 tile [D channels x 32 bytes] in
+// their swizzled shared-memory order (so that a plain bulk copy lands them ready for the tensor core: a tiled copy
+// of 32- and 64-byte rows costs the copy engine a request per row, which is what held the whole kernel back), and
+// the K and V block scales as 512-byte tcgen05 atoms  atom[m0 * 16 + m1 * 4 + j] = scale(row 32 * m1 + m0, j).
+// One CTA of 256 threads per record.
+// ---------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(256)
+pack_kv_records_kernel(const uint8_t* __restrict__ k4, const uint8_t* __restrict__ ks, const uint8_t* __restrict__ v4t,
+                       const uint8_t* __restrict__ vst, uint8_t* __restrict__ rec, int skv, long long kv_cap, int P, int nsteps,
+                       int is_mx) {
+    constexpr int ROW4 = D / 2, CPR = ROW4 / 16;            // bytes and 16-byte chunks per K4 row
+    const int st = blockIdx.x, head = blockIdx.y, t = threadIdx.x;
+    uint8_t* out = rec + (static_cast<long long>(head) * nsteps + st) * REC_BYTES;
+    const int G = is_mx ? 32 : 16, spr = D / G, atoms = is_mx ? 1 : D / 64, per_atom = is_mx ? spr : 4;
+    // K4: 64 rows; chunk c of row r goes to chunk c ^ f(r) (64-byte rows: f = (r >> 1) & 3; 32-byte rows: (r >> 2) & 1)
+    for (int i = t; i < STEP * CPR; i += 256) {
+        const int r = i / CPR, c = i % CPR;
+        const long long row = static_cast<long long>(st) * STEP + r;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (row < skv) val = *reinterpret_cast<const uint4*>(k4 + (head * kv_cap + row) * ROW4 + c * 16);
+        const int cs = CPR == 4 ? (c ^ ((r >> 1) & 3)) : (c ^ ((r >> 2) & 1));
+        *reinterpret_cast<uint4*>(out + r * ROW4 + cs * 16) = val;
+    }
+    // V4: D channel rows of 32 bytes (64 tokens), 32-byte swizzle
+    for (int i = t; i < D * 2; i += 256) {
+        const int r = i >> 1, c = i & 1;
+        const uint4 val = *reinterpret_cast<const uint4*>(v4t + (static_cast<long long>(head) * D + r) * (P / 2) + st * 32 + c * 16);
+        *reinterpret_cast<uint4*>(out + 5120 + r * 32 + ((c ^ ((r >> 2) & 1)) * 16)) = val;
+    }
+    // K scale atoms
+    for (int i = t; i < atoms * 128; i += 256) {
+        const int wi = i & 127, atom = i >> 7, m0 = wi >> 2, m1 = wi & 3;
+        const int r_in = 32 * m1 + m0;
+        const long long row = static_cast<long long>(st) * STEP + r_in;
         uint32_t word = 0;
-        if (ch < d) {
-            const uint8_t* s = src + (static_cast<long long>(head) * d + ch) * pg + step * per;
-            for (int j = 0; j < per; ++j)
-                if (step * per + j < pg) word |= static_cast<uint32_t>(s[j]) << (8 * j);
+        if (r_in < STEP && row < skv) {
+            const uint8_t* src = ks + (head * kv_cap + row) * spr + atom * per_atom;
+            for (int j = 0; j < per_atom; ++j) word |= static_cast<uint32_t>(src[j]) << (8 * j);
         }
-        reinterpret_cast<uint32_t*>(dst)[i] = word;
+        reinterpret_cast<uint32_t*>(out + 4096)[i] = word;
+    }
+    // V scale atom: scale(channel 32 * m1 + m0, token group st * per + j)
+    if (t < 128) {
+        const int m0 = t >> 2, m1 = t & 3, ch = 32 * m1 + m0, per = STEP / G, pg = P / G;
+        uint32_t word = 0;
+        if (ch < D) {
+            const uint8_t* src = vst + (static_cast<long long>(head) * D + ch) * pg + st * per;
+            for (int j = 0; j < per; ++j) word |= static_cast<uint32_t>(src[j]) << (8 * j);
+        }
+        reinterpret_cast<uint32_t*>(out + 9216)[t] = word;
     }
 }
 
 struct WsLayout {
-    size_t q_sf, k_sf, v_sf, status, total;
+    size_t q_sf, kv_rec, status, total;
 };
 
 WsLayout ws_layout(int hq_flat, int hkv_flat, int sq, int skv, int d, int is_mx) {
@@ -870,9 +989,8 @@ WsLayout ws_layout(int hq_flat, int hkv_flat, int sq, int skv, int d, int is_mx)
     const size_t n_qtiles = cdiv(sq, QTILE), nsteps = cdiv(skv, STEP);
     WsLayout w;
     w.q_sf = 0;
-    w.k_sf = w.q_sf + static_cast<size_t>(hq_flat) * n_qtiles * atoms * 512;
-    w.v_sf = w.k_sf + static_cast<size_t>(hkv_flat) * nsteps * atoms * 512;
-    w.status = w.v_sf + static_cast<size_t>(hkv_flat) * nsteps * 512;
+    w.kv_rec = w.q_sf + static_cast<size_t>(hq_flat) * n_qtiles * atoms * 512;
+    w.status = w.kv_rec + static_cast<size_t>(hkv_flat) * nsteps * REC_BYTES;
     w.total = w.status + 256;
     return w;
 }
@@ -885,7 +1003,7 @@ int launch_prefill_t(const PrefillParams& p, const CUtensorMap* maps, int grid, 
     if (e != cudaSuccess) return static_cast<int>(e);
     e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (e != cudaSuccess) return static_cast<int>(e);
-    kern<<<grid, NUM_THREADS, smem, stream>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);
+    kern<<<grid, NUM_THREADS, smem, stream>>>(p, maps[0], maps[3], maps[4], maps[5]);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -927,12 +1045,15 @@ int prefill_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const
         long long words = static_cast<long long>(hq_flat) * n_qtiles * atoms * 128;
         retile_row_scales_kernel<<<grid_for(words, 256, 8), 256, 0, stream>>>(
             static_cast<const uint8_t*>(qs), ws + w.q_sf, hq_flat, sq, sq, spr, QTILE, n_qtiles, atoms, per_atom);
-        words = static_cast<long long>(hkv_flat) * nsteps * atoms * 128;
-        retile_row_scales_kernel<<<grid_for(words, 256, 8), 256, 0, stream>>>(
-            static_cast<const uint8_t*>(ks), ws + w.k_sf, hkv_flat, skv, kv_cap, spr, STEP, nsteps, atoms, per_atom);
-        words = static_cast<long long>(hkv_flat) * nsteps * 128;
-        retile_v_scales_kernel<<<grid_for(words, 256, 8), 256, 0, stream>>>(
-            static_cast<const uint8_t*>(vst), ws + w.v_sf, hkv_flat, d, P / G, nsteps, STEP / G);
+        const dim3 pgrid(nsteps, hkv_flat);
+        if (d == 128)
+            pack_kv_records_kernel<128><<<pgrid, 256, 0, stream>>>(
+                static_cast<const uint8_t*>(k4), static_cast<const uint8_t*>(ks), static_cast<const uint8_t*>(v4t),
+                static_cast<const uint8_t*>(vst), ws + w.kv_rec, skv, kv_cap, P, nsteps, is_mx);
+        else
+            pack_kv_records_kernel<64><<<pgrid, 256, 0, stream>>>(
+                static_cast<const uint8_t*>(k4), static_cast<const uint8_t*>(ks), static_cast<const uint8_t*>(v4t),
+                static_cast<const uint8_t*>(vst), ws + w.kv_rec, skv, kv_cap, P, nsteps, is_mx);
         e = cudaGetLastError();
         if (e != cudaSuccess) return static_cast<int>(e);
     }
@@ -947,19 +1068,6 @@ int prefill_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const
             uint64_t str[2] = {static_cast<uint64_t>(d / 2), static_cast<uint64_t>(sq) * (d / 2)};
             uint32_t box[3] = {static_cast<uint32_t>(d / 2), QTILE, 1};
             rc |= make_tensor_map(&maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, q4, dims, str, box, sw4);
-        }
-        {
-            uint64_t dims[3] = {static_cast<uint64_t>(d / 2), static_cast<uint64_t>(skv), static_cast<uint64_t>(hkv_flat)};
-            uint64_t str[2] = {static_cast<uint64_t>(d / 2), static_cast<uint64_t>(kv_cap) * (d / 2)};
-            uint32_t box[3] = {static_cast<uint32_t>(d / 2), STEP, 1};
-            rc |= make_tensor_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, k4, dims, str, box, sw4);
-        }
-        {
-            uint64_t dims[3] = {static_cast<uint64_t>(P / 2), static_cast<uint64_t>(d), static_cast<uint64_t>(hkv_flat)};
-            uint64_t str[2] = {static_cast<uint64_t>(P / 2), static_cast<uint64_t>(d) * (P / 2)};
-            uint32_t box[3] = {STEP / 2, static_cast<uint32_t>(d), 1};
-            rc |= make_tensor_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, v4t, dims, str, box,
-                                  CU_TENSOR_MAP_SWIZZLE_32B);
         }
         if (width > 0) {
             const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -987,7 +1095,7 @@ int prefill_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const
     p.causal = causal; p.round_partial = round_partial; p.out_seq_major = out_seq_major ? 1 : 0;
     p.n_qtiles = n_qtiles; p.n_items = n_qtiles * hq_flat; p.nsteps_total = nsteps; p.nkb = skv / block;
     p.sel = static_cast<const int32_t*>(sel);
-    p.q_sf = ws + w.q_sf; p.k_sf = ws + w.k_sf; p.v_sf = ws + w.v_sf;
+    p.q_sf = ws + w.q_sf; p.kv_rec = ws + w.kv_rec;
     p.out = static_cast<uint16_t*>(out);
     p.status = reinterpret_cast<int*>(ws + w.status);
     p.c2 = static_cast<float>((1.0 / sqrt(static_cast<double>(d))) * 1.4426950408889634);
