@@ -50,8 +50,8 @@ namespace {
 constexpr int QTILE = 128;
 constexpr int STEP = 64;
 constexpr int NSETS = 4;             // softmax warp sets = S buffers = P tiles
-constexpr int NSLOTS = 10;           // K/V ring slots
-constexpr int SLOT_BYTES = 10240;    // one FP4 sub-step (K4, V4, scale atoms) or one 64-channel half of a 16-bit K or V tile
+constexpr int NSLOTS = 6;            // K/V ring slots
+constexpr int SLOT_BYTES = 16384;    // one FP4 sub-step (K4, V4, scale atoms) or one 16-bit K or V tile
 constexpr int REC_BYTES = 9728;      // packed FP4 record of one (KV head, sub-step): K4 4096 | K scale atoms 1024 | V4 4096 | V scale atom 512
 constexpr int REC_K_BYTES = 5120;    // its K part; the V part is the rest
 constexpr int PSET_BYTES = 16384;    // P tile of a set: 4 KB of e2m1 or 16 KB of 16-bit values
@@ -432,16 +432,16 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                     }
                     gslot += 1;
                 } else {
-                    for (int part = 0; part < 2 * HALVES && ok; ++part) {  // K tile, then V tile, one slot per 64-channel half
-                        const int which = part / HALVES, hf = part % HALVES;
+                    for (int which = 0; which < 2 && ok; ++which) {  // K tile, then V tile
                         const uint32_t slot = gslot % NSLOTS;
                         ok = mbar_wait(smem_u32(&bars.slot_empty[slot]), ((gslot / NSLOTS) & 1) ^ 1, abortp, budget);
                         if (!ok) break;
                         if (lane == 0) {
                             const uint32_t bar = smem_u32(which ? &bars.v_full[slot] : &bars.k_full[slot]);
                             const uint32_t sa = sbase + L::SLOTS + slot * SLOT_BYTES;
-                            mbar_expect_tx(bar, STEP * 128);
-                            tma_load_3d(sa, which ? &mapV16 : &mapK16, bar, hf * 64, st * STEP, it.kvh);
+                            mbar_expect_tx(bar, STEP * D * 2);
+                            for (int hf = 0; hf < HALVES; ++hf)
+                                tma_load_3d(sa + hf * STEP * 128, which ? &mapV16 : &mapK16, bar, hf * 64, st * STEP, it.kvh);
                         }
                         gslot += 1;
                     }
@@ -505,28 +505,23 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                     __syncwarp();
                     next_slot();
                 } else {
-                    // K tile: one slot per 64-channel half
-                    uint32_t kslot[HALVES];
-                    for (int hf = 0; hf < HALVES && ok; ++hf) {
-                        kslot[hf] = slot;
-                        ok = wait_k();
-                        next_slot();
-                    }
-                    if (ok) ok = mbar_wait(bar_s_free + set * 8, (use & 1) ^ 1, abortp, budget);
+                    const uint32_t kslot = slot;
+                    ok = wait_k() && mbar_wait(bar_s_free + set * 8, (use & 1) ^ 1, abortp, budget);
                     if (!ok) break;
+                    next_slot();
                     tc_fence_after_sync();
 #pragma unroll 1
                     for (int ks = 0; ks < D / 16; ++ks) {
                         const uint32_t hf = ks / 4, kk = ks % 4;
                         const uint64_t ad = make_smem_desc(sbase + L::Q16 + hf * QTILE * 128 + kk * 32, 16, 1024, SWZ_128B);
-                        const uint64_t bd = make_smem_desc(sbase + L::SLOTS + kslot[hf] * SLOT_BYTES + kk * 32, 16, 1024, SWZ_128B);
+                        const uint64_t bd = make_smem_desc(sbase + L::SLOTS + kslot * SLOT_BYTES + hf * STEP * 128 + kk * 32, 16, 1024,
+                                                           SWZ_128B);
                         mma_f16_elect(d_t, ad, bd, idesc_qk16, ks > 0);
                     }
-                    for (int hf = 0; hf < HALVES; ++hf)             // the K tile is free once S is computed
-                        tc_commit_elect(bar_slot_empty + kslot[hf] * 8);
+                    tc_commit_elect(bar_slot_empty + kslot * 8);    // the K tile is free once S is computed
                     tc_commit_elect(bar_s_full + set * 8);
                     if (last) tc_commit_elect(smem_u32(&bars.q_empty));
-                    for (int hf = 0; hf < HALVES; ++hf) next_slot();          // the V tile's slots
+                    next_slot();                                    // the V tile's slot
                 }
                 ++gsub;
             }
@@ -540,7 +535,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
         int n_item = 0;
         bool ok = true;
         const uint32_t idesc_pv4 = make_idesc_fp4(128, D, MX ? 1 : 0, 0, 0);
-        const uint32_t idesc_pv16 = make_idesc_f16(128, 64, BF16 ? 1 : 0, 0, 1), idesc_pv16w = make_idesc_f16(128, D, BF16 ? 1 : 0, 0, 1);
+        const uint32_t idesc_pv16 = make_idesc_f16(128, D, BF16 ? 1 : 0, 0, 1);
         const uint32_t bar_v_full = smem_u32(&bars.v_full[0]), bar_slot_empty = smem_u32(&bars.slot_empty[0]);
         const uint32_t bar_p_full = smem_u32(&bars.p_full[0][0]), bar_p_free = smem_u32(&bars.p_free[0][0]);
         const uint64_t pd0 = make_smem_desc(sbase + L::P, 16, 256, SWZ_32B);                 // + set * PSET_BYTES / 16 + buffer * 256
@@ -576,40 +571,21 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                     __syncwarp();
                     next_slot();
                 } else {
-                    for (int hf = 0; hf < HALVES; ++hf) next_slot();          // the K tile's slots
-                    uint32_t vslot[HALVES];
-                    for (int hf = 0; hf < HALVES && ok; ++hf) {
-                        vslot[hf] = slot;
-                        ok = wait_v();
-                        next_slot();
-                    }
-                    if (ok) ok = mbar_wait(bar_p_full + pb * 8, (use >> 1) & 1, abortp, budget);
+                    next_slot();                                    // the K tile's slot
+                    const uint32_t vslot = slot;
+                    ok = wait_v() && mbar_wait(bar_p_full + pb * 8, (use >> 1) & 1, abortp, budget);
                     if (!ok) break;
+                    next_slot();
                     tc_fence_after_sync();
                     const uint32_t pa = sbase + L::P + set * PSET_BYTES;
-                    // The V tile's 64-channel halves sit in separate slots.  Neighbouring slots make one MN-major operand
-                    // (leading-dimension offset = the slot size) for N = D MMAs; across the ring's wrap it is one
-                    // N = 64 chain per half.
-                    if (HALVES == 1 || vslot[HALVES - 1] == vslot[0] + HALVES - 1) {
-                        const uint32_t va = sbase + L::SLOTS + vslot[0] * SLOT_BYTES;
+                    const uint32_t va = sbase + L::SLOTS + vslot * SLOT_BYTES;
 #pragma unroll 1
-                        for (int ks = 0; ks < STEP / 16; ++ks) {
-                            const uint64_t ad = make_smem_desc(pa + ks * 32, 16, 1024, SWZ_128B);
-                            const uint64_t bd = make_smem_desc(va + ks * 2048, SLOT_BYTES, 1024, SWZ_128B);
-                            mma_f16_elect(tmem + TM_O, ad, bd, idesc_pv16w, (acc == 0 && ks == 0) ? 0 : 1);
-                        }
-                    } else {
-                        for (int hf = 0; hf < HALVES; ++hf) {
-                            const uint32_t va = sbase + L::SLOTS + vslot[hf] * SLOT_BYTES;
-#pragma unroll 1
-                            for (int ks = 0; ks < STEP / 16; ++ks) {
-                                const uint64_t ad = make_smem_desc(pa + ks * 32, 16, 1024, SWZ_128B);
-                                const uint64_t bd = make_smem_desc(va + ks * 2048, 16, 1024, SWZ_128B);
-                                mma_f16_elect(tmem + TM_O + hf * 64, ad, bd, idesc_pv16, (acc == 0 && ks == 0) ? 0 : 1);
-                            }
-                        }
+                    for (int ks = 0; ks < STEP / 16; ++ks) {
+                        const uint64_t ad = make_smem_desc(pa + ks * 32, 16, 1024, SWZ_128B);
+                        const uint64_t bd = make_smem_desc(va + ks * 2048, STEP * 128, 1024, SWZ_128B);
+                        mma_f16_elect(tmem + TM_O, ad, bd, idesc_pv16, (acc == 0 && ks == 0) ? 0 : 1);
                     }
-                    for (int hf = 0; hf < HALVES; ++hf) tc_commit_elect(bar_slot_empty + vslot[hf] * 8);
+                    tc_commit_elect(bar_slot_empty + vslot * 8);
                     tc_commit_elect(bar_p_free + pb * 8);
                     if (last) tc_commit_elect(smem_u32(&bars.o_full));
                 }
