@@ -50,6 +50,18 @@ int ta100_version(void);
 const char* ta100_status_string(int status);
 
 /*
+ * Diagnostics for the give-up path of the attention kernels (no counterpart in the reference, whose kernels
+ * wait without bound).  Every device-side wait in this library is bounded by a cycle budget; when one runs
+ * out the kernel raises a CTA-wide flag, every role drains, tensor memory is released and the launch's
+ * status word reports TA100_ERR_DEVICE_TIMEOUT (ta100_prefill_status / ta100_decode_status).
+ *   budget_cycles  cycle budget of later launches (<= 0 restores the default of 1e9 cycles)
+ *   skip_loads     non-zero: the producer warps of later attention launches issue no copies at all, so the
+ *                  consumers' waits run out while nothing asynchronous is in flight
+ * Process-wide, not thread-safe: meant for tests only.
+ */
+int ta100_debug_set_wait(long long budget_cycles, int skip_loads);
+
+/*
  * Quantise x [bs, seq, head_dim] (16-bit) to packed FP4 codes and block scales.
  * layout: 0 plain rows, 1 rows permuted inside every 32-row group (physical row p
  * holds logical row (p/8)*2 + ((p%8)/2)*8 + p%2), 2 transposed, 3 transposed +

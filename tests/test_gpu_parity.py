@@ -838,6 +838,40 @@ def test_decode_through_public_api_and_reference_named_ops(cuda_device):
     assert (out4.float().cpu() - ref4.float()).abs().max().item() <= FP16_MAX_ABS
 
 
+def test_bounded_waits_give_up_cleanly(cuda_device):
+    """Every device-side wait is bounded.  With the producers switched off (they copy nothing, so nothing
+    asynchronous is in flight) and a budget of 200k cycles the consumers' waits run out: the kernels drain, free
+    their tensor memory and report TA100_ERR_DEVICE_TIMEOUT through the status calls; the next normal launch gives
+    the result it gave before."""
+    torch.manual_seed(15)
+    ext = _ext()
+    q = torch.randn(1, 4, 512, 128, device=cuda_device).half()
+    k = torch.randn(1, 2, 512, 128, device=cuda_device).half()
+    v = torch.randn(1, 2, 512, 128, device=cuda_device).half()
+    q4, qs = ext.nvfp4_quantize(q)
+    k4, ks = ext.nvfp4_quantize_permuted(k)
+    v4, vs = ext.nvfp4_quantize_transposed(v)
+    prefill = lambda: ext.prefill_attention(None, None, None, None, q4, k4, v4, qs, ks, vs, causal=True, is_mx=False,
+                                            check_status=True)
+    want_p = prefill()
+    qd = torch.randn(1, 2, 4, 128, device=cuda_device).half()
+    qd4, qds = ext.nvfp4_quantize(qd)
+    kd4, kds = ext.nvfp4_quantize(k)
+    decode = lambda: ext.decode_attention(None, None, None, None, qd4, kd4, v4, qds, kds, vs, is_mx=False, num_splits=2,
+                                          check_status=True)
+    want_d = decode()
+    try:
+        ext.debug_set_wait(200_000, skip_loads=True)
+        with pytest.raises(RuntimeError, match="timed out"):
+            prefill()
+        with pytest.raises(RuntimeError, match="timed out"):
+            decode()
+    finally:
+        ext.debug_set_wait(0, skip_loads=False)
+    assert torch.equal(prefill(), want_p)
+    assert torch.equal(decode(), want_d)
+
+
 def test_argument_errors_raise(cuda_device):
     ext = _ext()
     x = torch.randn(1, 1, 64, 96, device=cuda_device).half()

@@ -679,6 +679,13 @@ def cached_decode_step(q_grouped, k_hi, v_hi, k_packed, k_scale, v_packed_t, v_s
     return out, sel_out
 
 
+def debug_set_wait(budget_cycles: int = 0, skip_loads: bool = False) -> None:
+    """Diagnostics: the cycle budget of the bounded device-side waits of later launches (0 = default) and a switch
+    that makes the attention kernels' producer warps copy nothing, so that the waits run out (tests of the
+    give-up path).  Process-wide."""
+    _lib.check(_lib.load().ta100_debug_set_wait(int(budget_cycles), int(bool(skip_loads))), "debug_set_wait")
+
+
 def decode_status(device=None) -> None:
     """Raises ``RuntimeError`` if a bounded wait inside a decode kernel ran out on ``device`` since the
     last call (synchronises with the current stream)."""

@@ -37,6 +37,7 @@ SIGNATURES = {
     "ta100_decode_attention": (_c_int, [_c_vp] * 4 + [_c_int] + [_c_vp] * 7 + [_c_int] * 2 + [_c_vp] * 3 + [_c_int] * 10
                                + [_c_vp]),
     "ta100_decode_status": (_c_int, [_c_vp]),
+    "ta100_debug_set_wait": (_c_int, [_c_ll, _c_int]),
     "ta100_merge_partials": (_c_int, [_c_vp, _c_vp, _c_vp, _c_int, _c_ll, _c_ll, _c_ll] + [_c_int] * 5 + [_c_vp]),
     "ta100_decode_static_scratch_bytes": (_c_sz, []),
     "ta100_decode_attention_static": (_c_int, [_c_vp] * 4 + [_c_int] + [_c_vp] * 7 + [_c_int] * 2 + [_c_vp] + [_c_int] * 9

@@ -37,12 +37,23 @@ int cache_append_dispatch(const void*, const void*, void*, void*, void*, void*, 
                           int, int, int, int, int, int, int, int, int, cudaStream_t);
 }  // namespace ta100
 
+namespace ta100 {
+long long g_wait_budget_cycles = DEFAULT_WAIT_BUDGET;
+int g_test_skip_loads = 0;
+}  // namespace ta100
+
 using namespace ta100;
 static inline cudaStream_t S(void* s) { return static_cast<cudaStream_t>(s); }
 
 extern "C" {
 
 int ta100_version(void) { return 100; }
+
+int ta100_debug_set_wait(long long budget_cycles, int skip_loads) {
+    g_wait_budget_cycles = budget_cycles > 0 ? budget_cycles : DEFAULT_WAIT_BUDGET;
+    g_test_skip_loads = skip_loads ? 1 : 0;
+    return TA100_OK;
+}
 
 const char* ta100_status_string(int status) {
     switch (status) {

@@ -27,6 +27,13 @@ enum Status : int {
 
 constexpr int NUM_SMS_HINT = 148;
 
+// Diagnostics (see ta100_debug_set_wait): the cycle budget of every bounded device-side wait, and a switch that
+// makes the producer warps of the attention kernels issue no copies at all, so that the consumers' waits run
+// out with nothing asynchronous in flight - the only way to exercise the give-up path without a fault.
+constexpr long long DEFAULT_WAIT_BUDGET = 1000000000LL;
+extern long long g_wait_budget_cycles;
+extern int g_test_skip_loads;
+
 __host__ __device__ constexpr int cdiv(int a, int b) { return (a + b - 1) / b; }
 
 // Row permutation inside every group of 32 rows used by the "permuted" K layout.

@@ -83,6 +83,7 @@ struct DecodeParams {
     float c2;               // (1/sqrt(d)) * log2(e)
     float sm_scale;         // 1/sqrt(d)
     long long budget;
+    int skip_loads;         // diagnostics: the producer issues no copies
 };
 
 template <int D>
@@ -330,8 +331,8 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
             mbar_arrive(smem_u32(&bars.f_full[slot]));
             return true;
         };
-        bool ok = true;
-        {
+        bool ok = !p.skip_loads;   // diagnostics: with skip_loads nothing is copied and the consumers' bounded waits run out
+        if (ok) {
             uint32_t kwa[4] = {0, 0, 0, 0}, vwa[4] = {0, 0, 0, 0}, kwb[4] = {0, 0, 0, 0}, vwb[4] = {0, 0, 0, 0};
             load_sf(0, kwa, vwa);
             load_sf(1, kwb, vwb);
@@ -718,6 +719,13 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, DTM_COLS);
+    if (bars.abort_flag != 0) {
+        // a chain that gave up contributes nothing: neutral partials (row max -FLT_MAX, row sum 0) instead of
+        // whatever the scratch memory held
+        const long long pbase = (static_cast<long long>(h) * p.splits + split) * G;
+        for (int i = tid; i < G * D; i += DEC_THREADS) p.part_o[pbase * D + i] = 0.0f;
+        for (int i = tid; i < G; i += DEC_THREADS) { p.part_ml[(pbase + i) * 2] = -FLT_MAX; p.part_ml[(pbase + i) * 2 + 1] = 0.0f; }
+    }
     if (tid == 0 && bars.abort_flag != 0) atomicCAS(&g_decode_status, 0, bars.abort_code != 0 ? bars.abort_code : 99);
     if (tid == 0 && bars.bad_entry != 0) atomicCAS(&g_decode_status, 0, STATUS_BAD_PAGE);
 }
@@ -899,7 +907,8 @@ int decode_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const 
     p.vs_row_stride = P / GRP;
     p.sm_scale = static_cast<float>(1.0 / sqrt(static_cast<double>(d)));
     p.c2 = static_cast<float>((1.0 / sqrt(static_cast<double>(d))) * 1.4426950408889634);
-    p.budget = 1000000000LL;
+    p.budget = g_wait_budget_cycles;
+    p.skip_loads = g_test_skip_loads;
     const dim3 grid(splits, heads);
 #define TA100_DEC(DD, MXX, BFF)                                                                               \
     do {                                                                                                      \

@@ -85,6 +85,7 @@ struct PrefillParams {
     int* status;
     float c2;  // (1/sqrt(d)) * log2(e)
     long long budget;
+    int skip_loads;  // diagnostics: the producer issues no copies
 };
 
 // shared-memory carve-up (offsets from a 1024-byte aligned base)
@@ -397,6 +398,7 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
             __syncwarp();
             __threadfence_block();
             if (lane == 0) mbar_arrive(smem_u32(&bars.sched_full));
+            if (p.skip_loads) break;   // diagnostics: nothing is copied, the consumers' bounded waits run out
             const bool has_sel = p.width > 0;
             // ---- Q tile ----
             ok = mbar_wait(smem_u32(&bars.q_empty), (n_item & 1) ^ 1, abortp, budget);
@@ -1075,7 +1077,8 @@ int prefill_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const
     p.out = static_cast<uint16_t*>(out);
     p.status = reinterpret_cast<int*>(ws + w.status);
     p.c2 = static_cast<float>((1.0 / sqrt(static_cast<double>(d))) * 1.4426950408889634);
-    p.budget = 1000000000LL;
+    p.budget = g_wait_budget_cycles;
+    p.skip_loads = g_test_skip_loads;
 
     int dev = 0, sms = NUM_SMS_HINT;
     cudaGetDevice(&dev);
