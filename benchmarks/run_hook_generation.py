@@ -5,8 +5,10 @@
 
 Prefill of ``--prompt`` uniform-random token ids, then ``--new-tokens`` greedy decode steps over a
 ``ThriftAttentionCache`` (NVFP4, block-mean top-10 % of 64-token blocks), and the same weights with Transformers' own
-exact attention (``sdpa``, ``DynamicCache``) for scale.  Prints one JSON line.  Logits parity of this path against
-the CPU oracle is covered at reduced sizes by tests/test_gpu_hf_model.py.
+exact attention (``sdpa``, ``DynamicCache``) for scale.  Prints one JSON line.  The warm-up pass of each arm doubles as a logits
+comparison: the hooked model is fed the tokens the exact-attention model chose, and the last-position logits of the
+prefill and of every decode step are compared (cosine similarity, largest difference, agreement of the arg-max).  Logits
+parity of this path against the CPU oracle is covered at reduced sizes by tests/test_gpu_hf_model.py.
 """
 from __future__ import annotations
 
@@ -22,7 +24,7 @@ import torch  # noqa: E402
 FRACTION = 0.10
 
 
-def run_hf(prompt_len: int, new_tokens: int, layers: int) -> None:
+def run_hf(prompt_len: int, new_tokens: int, layers: int, fraction: float = FRACTION) -> None:
     """End to end through the Transformers hook on a random-init decoder of the Llama-3-8B shape (d_model 4096,
     32 q / 8 kv heads x 128, SwiGLU 14336, RoPE theta 5e5, vocab 128256, fp16): prefill of `prompt_len` uniform
     random token ids, then `new_tokens` greedy decode steps over a ThriftAttentionCache, NVFP4 with the top 10 %
@@ -37,7 +39,7 @@ def run_hf(prompt_len: int, new_tokens: int, layers: int) -> None:
 
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
-    name = register_transformers_attention(TransformersAttentionConfig(name="thrift_bench_hf", fraction=FRACTION))
+    name = register_transformers_attention(TransformersAttentionConfig(name="thrift_bench_hf", fraction=fraction))
     cfg = transformers.LlamaConfig(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=layers,
                                    num_attention_heads=32, num_key_value_heads=8, head_dim=128, rope_theta=500000.0,
                                    max_position_embeddings=max(131072, prompt_len + new_tokens), tie_word_embeddings=False)
@@ -47,7 +49,9 @@ def run_hf(prompt_len: int, new_tokens: int, layers: int) -> None:
         model = transformers.LlamaForCausalLM(cfg).half().eval()
     ids = torch.randint(0, 128256, (1, prompt_len), generator=torch.Generator().manual_seed(1)).to(device)
 
-    def generate(use_hook: bool):
+    def generate(use_hook: bool, forced=None, keep=None):
+        """One prefill + decode pass.  `forced`: token ids to feed instead of the arg-max; `keep`: list that receives the
+        last-position logits (fp32, on the host) and the chosen tokens of every step."""
         with torch.no_grad():
             if use_hook:
                 model.config._attn_implementation = name
@@ -64,31 +68,48 @@ def run_hf(prompt_len: int, new_tokens: int, layers: int) -> None:
                 out = model(input_ids=inputs, past_key_values=cache, cache_position=pos0, use_cache=True, logits_to_keep=1)
                 if prep is not None:
                     prep.trim_padding()
-                tok = out.logits[:, -1].argmax(-1, keepdim=True)
+                def pick(step):
+                    if keep is not None:
+                        keep.append((out.logits[0, -1].float().cpu(), int(out.logits[0, -1].argmax())))
+                    if forced is not None:
+                        return torch.tensor([[forced[step]]], device=device)
+                    return out.logits[:, -1].argmax(-1, keepdim=True)
+
+                tok = pick(0)
                 ev[1].record()
                 for step in range(new_tokens):
                     out = model(input_ids=tok, past_key_values=cache,
                                 cache_position=torch.tensor([prompt_len + step], device=device), use_cache=True)
-                    tok = out.logits[:, -1].argmax(-1, keepdim=True)
+                    tok = pick(step + 1)
                 ev[2].record()
             torch.cuda.synchronize()
             assert torch.isfinite(out.logits).all()
             return ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])
 
-    generate(True)                                           # warm-up (library handles, allocator, workspaces)
-    pre, dec = generate(True)
-    torch.cuda.empty_cache()
+    exact, ours = [], []
     try:
-        generate(False)
+        generate(False, keep=exact)                          # warm-up; its logits and tokens are the comparison's reference
         pre_x, dec_x = generate(False)
     except torch.OutOfMemoryError:
         pre_x = dec_x = float("nan")
+        exact = []
+    torch.cuda.empty_cache()
+    generate(True, forced=[t for _, t in exact] if exact else None, keep=ours)   # warm-up (library handles, workspaces)
+    pre, dec = generate(True)
+    logits = None
+    if exact:
+        cos = [float(torch.nn.functional.cosine_similarity(a, b, dim=0)) for (a, _), (b, _) in zip(exact, ours)]
+        logits = {"steps_compared": len(cos), "cosine_min": min(cos), "cosine_mean": sum(cos) / len(cos),
+                  "max_abs_diff": max(float((a - b).abs().max()) for (a, _), (b, _) in zip(exact, ours)),
+                  "exact_logit_abs_max": max(float(a.abs().max()) for a, _ in exact),
+                  "argmax_agreement": sum(int(x[1] == y[1]) for x, y in zip(exact, ours)) / len(cos)}
     print(json.dumps({
         "case": f"Transformers hook, Llama-3-8B-shaped decoder ({layers} layers, random init, fp16): prefill {prompt_len} "
-                f"tokens + {new_tokens} greedy decode steps, NVFP4 + block-mean top-{FRACTION:.0%}",
+                f"tokens + {new_tokens} greedy decode steps, NVFP4 + block-mean top-{fraction:.0%}",
         "prefill_ms": pre, "prefill_tokens_per_s": prompt_len / pre * 1e3,
         "decode_ms_per_token": dec / new_tokens, "decode_tokens_per_s": new_tokens / dec * 1e3,
         "sdpa_prefill_ms": pre_x, "sdpa_decode_ms_per_token": dec_x / new_tokens,
+        "logits_vs_exact_attention": logits,
         "peak_memory_gib": torch.cuda.max_memory_allocated(device) / 2 ** 30}), flush=True)
 
 
@@ -97,8 +118,9 @@ def main() -> None:
     ap.add_argument("--prompt", type=int, default=65536)
     ap.add_argument("--new-tokens", type=int, default=256)
     ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--fraction", type=float, default=FRACTION, help="share of the key blocks kept in 16 bit (1.0: all of them)")
     args = ap.parse_args()
-    run_hf(args.prompt, args.new_tokens, args.layers)
+    run_hf(args.prompt, args.new_tokens, args.layers, args.fraction)
 
 
 if __name__ == "__main__":

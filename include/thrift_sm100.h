@@ -75,6 +75,20 @@ int ta100_quantize(const void* x, void* codes, void* scales, long long bs, int s
                    int is_bf16, int layout, void* stream);
 
 /*
+ * Q, K and V of one attention call quantised by ONE launch (three parts of one grid):
+ *   q [bs_q, seq_q, D]   -> q_codes [bs_q, seq_q, D/2],  q_scales [bs_q, seq_q, D/G]     (plain rows)
+ *   k [bs_kv, seq_kv, D] -> k_codes [bs_kv, seq_kv, D/2], k_scales [bs_kv, seq_kv, D/G]  (rows; permuted as layout 1 of
+ *                           ta100_quantize when k_permuted != 0: the prefill kernel's K layout)
+ *   v [bs_kv, seq_kv, D] -> v_codes_t [bs_kv, D, P/2],    v_scales_t [bs_kv, D, P/G], P = seq_kv rounded up to 128
+ * Outputs are bit-identical to three ta100_quantize calls with layouts 0, k_permuted and 2.
+ * Replaces the three launches of QuantFormat.quantize_qkv / quantize_single_query_qkv
+ * (src/thriftattention/quant/formats.py:55-79 of the reference).
+ */
+int ta100_quantize_qkv(const void* q, const void* k, const void* v, void* q_codes, void* q_scales, void* k_codes,
+                       void* k_scales, void* v_codes_t, void* v_scales_t, long long bs_q, int seq_q, long long bs_kv,
+                       int seq_kv, int head_dim, int is_mxfp4, int is_bf16, int k_permuted, void* stream);
+
+/*
  * Per-block statistics of x [heads, seq, head_dim]: fp32 mean cast to the 16-bit
  * type, min and max, each [heads, seq/block, head_dim]; any output may be NULL.
  * Replaces the PyTorch pre-reductions of the reference (block_means,

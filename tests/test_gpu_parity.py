@@ -52,6 +52,29 @@ def test_quantiser_bit_exact(cuda_device, dtype, fmt, layout, op, shape):
     assert torch.equal(_u8(scale).cpu(), _u8(scale_ref))
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+@pytest.mark.parametrize("k_permuted", [True, False])
+@pytest.mark.parametrize("hq,hkv,sq,skv,d", [(4, 2, 200, 200, 128), (2, 2, 64, 320, 64), (8, 1, 1, 1000, 128)])
+def test_one_launch_qkv_quantiser_bit_exact(cuda_device, dtype, fmt, k_permuted, hq, hkv, sq, skv, d):
+    """The fused launch against the oracle, tensor by tensor (ragged lengths, GQA, a single query row)."""
+    from thriftattention_b200 import _C
+
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(2, hq, sq, d, generator=g).to(dtype)
+    k = torch.randn(2, hkv, skv, d, generator=g).to(dtype)
+    v = torch.randn(2, hkv, skv, d, generator=g).to(dtype)
+    k[0, 0, :3] = 0.0
+    v[1, -1, 5] *= 1000.0
+    got = _C.quantize_qkv(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), is_mx=fmt == "mxfp4",
+                          is_bf16=dtype == torch.bfloat16, k_permuted=k_permuted)
+    want = [oracle.quantize(q, fmt, "plain"), oracle.quantize(k, fmt, "permuted" if k_permuted else "plain"),
+            oracle.quantize(v, fmt, "transposed")]
+    for i, (codes_ref, scale_ref) in enumerate(want):
+        assert torch.equal(got[i].cpu(), codes_ref), f"codes of tensor {i}"
+        assert torch.equal(_u8(got[3 + i]).cpu(), _u8(scale_ref)), f"scales of tensor {i}"
+
+
 def test_quantiser_e2m1_ties_and_saturation(cuda_device):
     # values that sit exactly on e2m1 rounding ties once divided by a power-of-two scale
     base = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -6.0])

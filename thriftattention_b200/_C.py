@@ -64,6 +64,33 @@ def _quantize(x: torch.Tensor, is_bf16: bool, is_mx: bool, layout: int):
     return [codes, scales.view(_scale_dtype(is_mx))]
 
 
+def quantize_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_mx: bool, is_bf16: bool, k_permuted: bool):
+    """Q (rows), K (rows, permuted for the prefill kernel if ``k_permuted``) and V (transposed) in one launch; returns
+    ``(q_codes, k_codes, v_codes_t, q_scales, k_scales, v_scales_t)`` - the order of ``QuantFormat.quantize_qkv``
+    (src/thriftattention/quant/formats.py:55-79 of the reference, three launches there)."""
+    for name, x in (("q", q), ("k", k), ("v", v)):
+        _check(x.is_cuda and x.is_contiguous() and x.dim() == 4, f"{name} must be a contiguous 4D CUDA tensor")
+        _check(x.dtype == (torch.bfloat16 if is_bf16 else torch.float16), f"{name} dtype must match is_bf16")
+    _check(k.shape == v.shape, "k and v must have the same shape")
+    _check(q.shape[0] == k.shape[0] and q.shape[3] == k.shape[3], "q and k must agree in batch and head_dim")
+    b, hq, sq, d = q.shape
+    _, hkv, skv, _ = k.shape
+    _check(d in (64, 128), f"head_dim must be 64 or 128, got {d}")
+    g = 32 if is_mx else 16
+    padded = (skv + 127) // 128 * 128
+    u8 = dict(dtype=torch.uint8, device=q.device)
+    q4, qs = torch.empty(b, hq, sq, d // 2, **u8), torch.empty(b, hq, sq, d // g, **u8)
+    k4, ks = torch.empty(b, hkv, skv, d // 2, **u8), torch.empty(b, hkv, skv, d // g, **u8)
+    v4, vs = torch.empty(b, hkv, d, padded // 2, **u8), torch.empty(b, hkv, d, padded // g, **u8)
+    with torch.cuda.device(q.device):
+        rc = _lib.load().ta100_quantize_qkv(_ptr(q), _ptr(k), _ptr(v), _ptr(q4), _ptr(qs), _ptr(k4), _ptr(ks), _ptr(v4),
+                                            _ptr(vs), b * hq, sq, b * hkv, skv, d, int(is_mx), int(is_bf16),
+                                            int(k_permuted), _stream(q))
+    _lib.check(rc, "quantize_qkv")
+    sd = _scale_dtype(is_mx)
+    return q4, k4, v4, qs.view(sd), ks.view(sd), vs.view(sd)
+
+
 def nvfp4_quantize(x, is_bf16=False):
     return _quantize(x, is_bf16, False, 0)
 

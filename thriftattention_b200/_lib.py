@@ -19,6 +19,7 @@ SIGNATURES = {
     "ta100_version": (_c_int, []),
     "ta100_status_string": (ctypes.c_char_p, [_c_int]),
     "ta100_quantize": (_c_int, [_c_vp, _c_vp, _c_vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp]),
+    "ta100_quantize_qkv": (_c_int, [_c_vp] * 9 + [_c_ll, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp]),
     "ta100_block_stats": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_vp]),
     "ta100_cache_append": (_c_int, [_c_vp] * 11 + [_c_ll] + [_c_int] * 9 + [_c_vp]),
     "ta100_select_prefill": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp] + [_c_int] * 11 + [_c_vp]),

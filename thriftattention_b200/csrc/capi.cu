@@ -6,6 +6,8 @@
 
 namespace ta100 {
 int quantize_dispatch(const void*, void*, void*, long long, int, int, int, int, int, cudaStream_t);
+int quantize_qkv_dispatch(const void*, const void*, const void*, void*, void*, void*, void*, void*, void*, long long, int,
+                          long long, int, int, int, int, int, cudaStream_t);
 int block_stats_dispatch(const void*, void*, void*, void*, long long, int, int, int, int, cudaStream_t);
 int select_prefill_dispatch(const void*, const void*, const void*, void*, int, int, int, int, int, int, int, int, int, int,
                             int, cudaStream_t);
@@ -77,6 +79,13 @@ const char* ta100_status_string(int status) {
 int ta100_quantize(const void* x, void* codes, void* scales, long long bs, int seq, int head_dim, int is_mxfp4,
                    int is_bf16, int layout, void* stream) {
     return quantize_dispatch(x, codes, scales, bs, seq, head_dim, is_mxfp4, is_bf16, layout, S(stream));
+}
+
+int ta100_quantize_qkv(const void* q, const void* k, const void* v, void* q_codes, void* q_scales, void* k_codes,
+                       void* k_scales, void* v_codes_t, void* v_scales_t, long long bs_q, int seq_q, long long bs_kv,
+                       int seq_kv, int head_dim, int is_mxfp4, int is_bf16, int k_permuted, void* stream) {
+    return quantize_qkv_dispatch(q, k, v, q_codes, q_scales, k_codes, k_scales, v_codes_t, v_scales_t, bs_q, seq_q, bs_kv,
+                                 seq_kv, head_dim, is_mxfp4, is_bf16, k_permuted, S(stream));
 }
 
 int ta100_block_stats(const void* x, void* mean, void* mn, void* mx, long long heads, int seq, int head_dim, int block,

@@ -13,16 +13,16 @@ namespace ta100 {
 // Row layouts.  x [bs, seq, d] -> codes [bs, seq, d/2], scales [bs, seq, d/G].
 // One thread per group; consecutive threads take consecutive groups so loads,
 // code stores and scale stores are all contiguous across a warp.
+// `cta` of `n_cta` CTAs work on the tensor (the whole grid, or the part of a fused launch that is given to it).
 template <bool MX, bool BF16, bool PERMUTED>
-__global__ void __launch_bounds__(256) quantize_rows_kernel(const uint16_t* __restrict__ x,
-                                                            uint8_t* __restrict__ codes,
-                                                            uint8_t* __restrict__ scales, long long bs_seq,
-                                                            int seq, int d) {
+__device__ __forceinline__ void quantize_rows_body(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes,
+                                                   uint8_t* __restrict__ scales, long long bs_seq, int seq, int d,
+                                                   unsigned cta, unsigned n_cta) {
     constexpr int G = MX ? 32 : 16;
     const int groups_per_row = d / G;
     const long long total = bs_seq * groups_per_row;
-    for (long long gid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; gid < total;
-         gid += static_cast<long long>(gridDim.x) * blockDim.x) {
+    for (long long gid = cta * static_cast<long long>(blockDim.x) + threadIdx.x; gid < total;
+         gid += static_cast<long long>(n_cta) * blockDim.x) {
         const long long row = gid / groups_per_row;
         const int c = static_cast<int>(gid - row * groups_per_row);
         long long src_row = row;
@@ -58,16 +58,23 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const uint16_t* __re
     }
 }
 
+template <bool MX, bool BF16, bool PERMUTED>
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const uint16_t* __restrict__ x,
+                                                            uint8_t* __restrict__ codes,
+                                                            uint8_t* __restrict__ scales, long long bs_seq,
+                                                            int seq, int d) {
+    quantize_rows_body<MX, BF16, PERMUTED>(x, codes, scales, bs_seq, seq, d, blockIdx.x, gridDim.x);
+}
+
 // Transposed layout for V.  x [bs, seq, d] -> codes [bs, d, P/2], scales [bs, d, P/G],
 // P = ceil(seq/128)*128; groups run along the sequence; rows >= seq are zero.
 // One CTA stages a 128-token x d tile in shared memory, quantises down the
 // columns and stages the packed result so that global stores are 16-byte wide
 // and contiguous per channel row.
 template <int D, bool MX, bool BF16, bool PERMUTED>
-__global__ void __launch_bounds__(256) quantize_transposed_kernel(const uint16_t* __restrict__ x,
-                                                                  uint8_t* __restrict__ codes,
-                                                                  uint8_t* __restrict__ scales, int bs, int seq,
-                                                                  int padded) {
+__device__ __forceinline__ void quantize_transposed_body(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes,
+                                                         uint8_t* __restrict__ scales, int bs, int seq, int padded,
+                                                         unsigned cta, unsigned n_cta) {
     constexpr int G = MX ? 32 : 16;
     constexpr int TOK = 128;
     constexpr int GROUPS = TOK / G;  // per channel per tile
@@ -77,7 +84,7 @@ __global__ void __launch_bounds__(256) quantize_transposed_kernel(const uint16_t
     __shared__ __align__(16) uint8_t out_scales[D][8];
 
     const int tiles_per_b = padded / TOK;
-    for (int work = blockIdx.x; work < bs * tiles_per_b; work += gridDim.x) {
+    for (int work = cta; work < bs * tiles_per_b; work += n_cta) {
         const int b = work / tiles_per_b;
         const int t = work - b * tiles_per_b;
         const int tok0 = t * TOK;
@@ -128,6 +135,36 @@ __global__ void __launch_bounds__(256) quantize_transposed_kernel(const uint16_t
         }
         __syncthreads();
     }
+}
+
+template <int D, bool MX, bool BF16, bool PERMUTED>
+__global__ void __launch_bounds__(256) quantize_transposed_kernel(const uint16_t* __restrict__ x,
+                                                                  uint8_t* __restrict__ codes,
+                                                                  uint8_t* __restrict__ scales, int bs, int seq,
+                                                                  int padded) {
+    quantize_transposed_body<D, MX, BF16, PERMUTED>(x, codes, scales, bs, seq, padded, blockIdx.x, gridDim.x);
+}
+
+// Q, K and V of one attention call in ONE launch: the grid is split into three parts, each running one of the
+// bodies above on its tensor (Q rows, K rows - permuted for the prefill kernel, plain for decode - and V transposed).
+struct QkvParams {
+    const uint16_t *q, *k, *v;
+    uint8_t *q_codes, *q_scales, *k_codes, *k_scales, *v_codes, *v_scales;
+    long long q_rows, k_rows;   // bs * seq of Q and of K
+    int seq_q, seq_kv, bs_kv, padded_kv, d;
+    unsigned n_q, n_k, n_v;     // CTAs per part
+};
+
+template <int D, bool MX, bool BF16, bool KPERM>
+__global__ void __launch_bounds__(256) quantize_qkv_kernel(const QkvParams p) {
+    const unsigned b = blockIdx.x;
+    if (b < p.n_q)
+        quantize_rows_body<MX, BF16, false>(p.q, p.q_codes, p.q_scales, p.q_rows, p.seq_q, p.d, b, p.n_q);
+    else if (b < p.n_q + p.n_k)
+        quantize_rows_body<MX, BF16, KPERM>(p.k, p.k_codes, p.k_scales, p.k_rows, p.seq_kv, p.d, b - p.n_q, p.n_k);
+    else
+        quantize_transposed_body<D, MX, BF16, false>(p.v, p.v_codes, p.v_scales, p.bs_kv, p.seq_kv, p.padded_kv,
+                                                     b - p.n_q - p.n_k, p.n_v);
 }
 
 template <bool MX, bool BF16>
@@ -186,6 +223,46 @@ int quantize_dispatch(const void* x, void* codes, void* scales, long long bs, in
     if (is_mx) return is_bf16 ? TA100_T(64, true, true) : TA100_T(64, true, false);
     return is_bf16 ? TA100_T(64, false, true) : TA100_T(64, false, false);
 #undef TA100_T
+}
+
+// See include/thrift_sm100.h (ta100_quantize_qkv) for the contract.
+int quantize_qkv_dispatch(const void* q, const void* k, const void* v, void* q_codes, void* q_scales, void* k_codes,
+                          void* k_scales, void* v_codes_t, void* v_scales_t, long long bs_q, int seq_q, long long bs_kv,
+                          int seq_kv, int d, int is_mx, int is_bf16, int k_permuted, cudaStream_t stream) {
+    if (!q || !k || !v || !q_codes || !q_scales || !k_codes || !k_scales || !v_codes_t || !v_scales_t) return TA100_ERR_NULL;
+    if (d != 64 && d != 128) return TA100_ERR_UNSUPPORTED;
+    if (bs_q <= 0 || bs_kv <= 0 || seq_q <= 0 || seq_kv <= 0) return TA100_ERR_SHAPE;
+    if (bs_kv > 0x7FFFFFFF) return TA100_ERR_LIMIT;
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+         reinterpret_cast<uintptr_t>(q_codes) | reinterpret_cast<uintptr_t>(k_codes) | reinterpret_cast<uintptr_t>(v_codes_t)) & 15)
+        return TA100_ERR_ALIGN;
+    const int G = is_mx ? 32 : 16;
+    QkvParams p;
+    p.q = static_cast<const uint16_t*>(q); p.k = static_cast<const uint16_t*>(k); p.v = static_cast<const uint16_t*>(v);
+    p.q_codes = static_cast<uint8_t*>(q_codes); p.q_scales = static_cast<uint8_t*>(q_scales);
+    p.k_codes = static_cast<uint8_t*>(k_codes); p.k_scales = static_cast<uint8_t*>(k_scales);
+    p.v_codes = static_cast<uint8_t*>(v_codes_t); p.v_scales = static_cast<uint8_t*>(v_scales_t);
+    p.q_rows = bs_q * seq_q; p.k_rows = bs_kv * seq_kv;
+    p.seq_q = seq_q; p.seq_kv = seq_kv; p.bs_kv = static_cast<int>(bs_kv); p.padded_kv = cdiv(seq_kv, 128) * 128; p.d = d;
+    p.n_q = static_cast<unsigned>(grid_for(p.q_rows * (d / G), 256, 16));
+    p.n_k = static_cast<unsigned>(grid_for(p.k_rows * (d / G), 256, 16));
+    const long long v_work = bs_kv * (p.padded_kv / 128);
+    p.n_v = static_cast<unsigned>(v_work < NUM_SMS_HINT * 4LL ? v_work : NUM_SMS_HINT * 4LL);
+    const unsigned grid = p.n_q + p.n_k + p.n_v;
+#define TA100_QKV(DD, MXX, BFF)                                                                    \
+    do {                                                                                           \
+        if (k_permuted) quantize_qkv_kernel<DD, MXX, BFF, true><<<grid, 256, 0, stream>>>(p);      \
+        else quantize_qkv_kernel<DD, MXX, BFF, false><<<grid, 256, 0, stream>>>(p);                \
+    } while (0)
+    if (d == 128) {
+        if (is_mx) { if (is_bf16) TA100_QKV(128, true, true); else TA100_QKV(128, true, false); }
+        else { if (is_bf16) TA100_QKV(128, false, true); else TA100_QKV(128, false, false); }
+    } else {
+        if (is_mx) { if (is_bf16) TA100_QKV(64, true, true); else TA100_QKV(64, true, false); }
+        else { if (is_bf16) TA100_QKV(64, false, true); else TA100_QKV(64, false, false); }
+    }
+#undef TA100_QKV
+    return static_cast<int>(cudaGetLastError());
 }
 
 }  // namespace ta100

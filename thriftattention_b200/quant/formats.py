@@ -39,6 +39,9 @@ class _Fp4Format:
         return self._op("")(x, is_bf16=is_bf16)
 
     def _pack(self, q, k, v, k_suffix: str, is_bf16: bool) -> PackedQKV:
+        if q.is_cuda and all(t.dim() == 4 and t.is_contiguous() for t in (q, k, v)) and k.shape == v.shape:
+            from thriftattention_b200 import _C          # one launch for the three tensors
+            return _C.quantize_qkv(q, k, v, is_mx=self.name == "mxfp4", is_bf16=is_bf16, k_permuted=k_suffix == "_permuted")
         q_packed, q_scale = self._op("")(q, is_bf16=is_bf16)
         k_packed, k_scale = self._op(k_suffix)(k, is_bf16=is_bf16)
         v_packed_t, v_scale_t = self._op("_transposed")(v, is_bf16=is_bf16)
