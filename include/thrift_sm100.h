@@ -122,6 +122,24 @@ int ta100_cache_append(const void* k_new, const void* v_new, void* k_hi, void* v
                        int is_bf16, int flags, void* stream);
 
 /*
+ * The same append into a PAGED cache: the layout ta100_decode_attention reads through a page table.
+ *   page_table     int32 [batch, max_pages]: physical page of logical 64-token page j of sequence b; entries that
+ *                  the token range [start, start + count) (and, for V, its G-token groups) touches must be valid
+ *                  pages in [0, pool_pages) - a row whose page is not is skipped
+ *   k_hi, v_hi     [pool_pages, hkv, 64, D] 16-bit;  k_codes [pool_pages, hkv, 64, D/2], k_scales [.., 64, D/G]
+ *   v_codes, v_scales  [pool_pages, hkv, D, 32], [pool_pages, hkv, D, 64/G]  (transposed inside a page)
+ *   k_mean, k_min, k_max [batch*hkv, stat_blocks, D] by LOGICAL block, as for the contiguous cache
+ *   k_new, v_new   [batch*hkv, count, D]
+ * Growing a sequence is appending page ids to its row of the table; nothing is copied.  A page handed to a
+ * sequence must hold zeros (the kernels read the rows behind the logical length as zero rows).  No counterpart
+ * in the reference, whose cache grows by copying capacity-strided slabs (transformers_cache.py:255-306).
+ */
+int ta100_cache_append_paged(const void* k_new, const void* v_new, void* k_hi, void* v_hi, void* k_codes, void* k_scales,
+                             void* v_codes, void* v_scales, void* k_mean, void* k_min, void* k_max, const void* page_table,
+                             int max_pages, int pool_pages, int batch, int hkv, int stat_blocks, int start, int k_count,
+                             int v_count, int head_dim, int stat_block, int is_mxfp4, int is_bf16, int flags, void* stream);
+
+/*
  * Prefill block selection.  q_mean [heads, nq, D]; k_a / k_b [heads/group, nk, D].
  * quest = 0: score = q_mean . k_a (k_a = block means); quest = 1: Quest bound with
  * k_a = block minima, k_b = block maxima.  causal: blocks kb <= qb only.

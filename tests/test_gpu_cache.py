@@ -22,16 +22,19 @@ def _check_layer_against_oracle(layer, k_ref, v_ref, fmt):
     n = layer.seq_len
     g = 32 if fmt == "mxfp4" else 16
     assert torch.equal(layer.key_view().cpu(), k_ref) and torch.equal(layer.value_view().cpu(), v_ref)
+    k_packed, v_packed_t, k_scale, v_scale_t = layer.packed_views()      # strided views of a slab layer, gathers of a paged one
     codes, scales = oracle.quantize(k_ref, fmt, "plain")
-    assert torch.equal(layer.k_packed[:, :, :n].cpu(), codes)
-    assert torch.equal(_u8(layer.k_scale[:, :, :n]), _u8(scales))
+    assert torch.equal(k_packed[:, :, :n].cpu(), codes)
+    assert torch.equal(_u8(k_scale[:, :, :n]), _u8(scales))
     # V groups: tokens beyond n inside the last group are zero rows of the cache
     ng = -(-n // g) * g
     v_pad = torch.zeros(v_ref.shape[0], v_ref.shape[1], ng, v_ref.shape[3], dtype=v_ref.dtype)
     v_pad[:, :, :n] = v_ref
     vcodes, vscales = oracle.quantize(v_pad, fmt, "transposed")
-    assert torch.equal(layer.v_packed_t[:, :, :, : ng // 2].cpu(), vcodes[:, :, :, : ng // 2])
-    assert torch.equal(_u8(layer.v_scale_t[:, :, :, : ng // g]), _u8(vscales[:, :, :, : ng // g]))
+    assert torch.equal(v_packed_t[:, :, :, : ng // 2].cpu(), vcodes[:, :, :, : ng // 2])
+    assert torch.equal(_u8(v_scale_t[:, :, :, : ng // g]), _u8(vscales[:, :, :, : ng // g]))
+    # ... and the rest of the rounded views are zero rows
+    assert k_packed[:, :, n:].sum() == 0 and v_packed_t[:, :, :, ng // 2:].sum() == 0
     nb = n // 64
     if nb:
         mean, lo, hi = oracle.block_stats(k_ref[:, :, : nb * 64], 64)
@@ -40,10 +43,11 @@ def _check_layer_against_oracle(layer, k_ref, v_ref, fmt):
             assert torch.equal(layer.k_min[:, :, :nb].cpu(), lo) and torch.equal(layer.k_max[:, :, :nb].cpu(), hi)
 
 
+@pytest.mark.parametrize("paged", [False, True])
 @pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("d", [128, 64])
-def test_append_any_chunking_is_bit_exact(fmt, dtype, d):
+def test_append_any_chunking_is_bit_exact(fmt, dtype, d, paged):
     torch.manual_seed(5)
     total = 700
     k = (torch.randn(2, 3, total, d) * 1.5).to(dtype)
@@ -52,15 +56,21 @@ def test_append_any_chunking_is_bit_exact(fmt, dtype, d):
     v[1, 2, 32:64, 5] = 0
     k[0, 1, 7, :16] = 5000.0                  # beyond 448 * 6: the scale saturates
     for chunks in ([700], [1] * 40 + [660], [70, 1, 1, 57, 3, 200, 33, 31, 1, 303], [64, 64, 128, 444]):
-        layer = tc.ThriftAttentionCacheLayer(quant_format=fmt, track_minmax=True)
+        kind = tc.PagedThriftAttentionCacheLayer if paged else tc.ThriftAttentionCacheLayer
+        layer = kind(quant_format=fmt, track_minmax=True)
         pos = 0
         for c in chunks:
             layer.update(k[:, :, pos:pos + c].to(DEV), v[:, :, pos:pos + c].to(DEV))
             pos += c
             if c > 1 or pos % 16 == 0:
                 _check_layer_against_oracle(layer, k[:, :, :pos], v[:, :, :pos], fmt)
-        assert pos == total and layer.capacity in (768, 1024)
+        assert pos == total and layer.capacity in ((704,) if paged else (768, 1024))
         _check_layer_against_oracle(layer, k, v, fmt)
+        if paged:
+            # every sequence has its own 11 pages, none of them the zero page, and the table says so
+            table = layer.page_table.cpu()
+            used = table[:, :11].flatten().tolist()
+            assert len(set(used)) == 22 and min(used) >= 1 and bool((table[:, 11:] == -1).all())
 
 
 def test_append_with_fixed_capacity_and_positions():
@@ -253,3 +263,100 @@ def test_fused_decode_step_equals_the_operator_path(monkeypatch, fmt, selection,
         assert torch.equal(fused, plain)
         assert torch.equal(caches[0].layer(0).selected_blocks, caches[1].layer(0).selected_blocks)
     _C.decode_status(DEV)
+
+
+# ------------------------------------------------------------------------------- the paged layout
+def test_paged_layer_positions_crop_reset_and_batch_surgery():
+    """Overwrites by position, crop (pages go back to the free list as zeros), decode after a crop, reset, and the
+    beam / batch operations (a selected sequence becomes a copy on pages of its own)."""
+    torch.manual_seed(21)
+    k = torch.randn(2, 2, 300, 128).half()
+    v = torch.randn(2, 2, 300, 128).half()
+    layer = tc.PagedThriftAttentionCacheLayer(max_cache_len=320, track_minmax=True)
+    layer.update(k[:, :, :150].to(DEV), v[:, :, :150].to(DEV), {"cache_position": torch.arange(150, device=DEV)})
+    pool_pages = layer.k_pool.shape[0]
+    assert pool_pages == 1 + 2 * 5 and layer.page_table.shape == (2, 5)
+    k2, v2 = k.clone(), v.clone()
+    k2[:, :, 60:90] = torch.randn(2, 2, 30, 128).half()
+    v2[:, :, 60:90] = torch.randn(2, 2, 30, 128).half()
+    layer.update(k2[:, :, 60:90].to(DEV), v2[:, :, 60:90].to(DEV), {"cache_position": torch.arange(60, 90)})
+    layer.update(k2[:, :, 150:].to(DEV), v2[:, :, 150:].to(DEV))
+    assert layer.seq_len == 300 and layer.k_pool.shape[0] == pool_pages          # grown by page ids, not by copying
+    n = layer.seq_len
+    kp, vp, ks, _ = layer.packed_views()
+    codes, scales = oracle.quantize(k2, "nvfp4", "plain")
+    assert torch.equal(kp[:, :, :n].cpu(), codes) and torch.equal(_u8(ks[:, :, :n]), _u8(scales))
+    v_pad = torch.zeros(2, 2, 304, 128).half()
+    v_pad[:, :, :300] = v2
+    assert torch.equal(vp[:, :, :, :152].cpu(), oracle.quantize(v_pad, "nvfp4", "transposed")[0][:, :, :, :152])
+
+    layer.crop(70)
+    assert layer.seq_len == 70 and len(layer._free) == 10 - 2 * 2
+    _check_layer_against_oracle(layer, k2[:, :, :70], v2[:, :, :70], "nvfp4")
+    free = torch.tensor(layer._free, device=DEV)
+    assert all(_u8(pool[free]).sum() == 0 for pool in layer._pools())               # released pages hold zeros
+    layer.update(k2[:, :, 100:101].to(DEV), v2[:, :, 100:101].to(DEV))
+    k3 = torch.cat([k2[:, :, :70], k2[:, :, 100:101]], 2)
+    v3 = torch.cat([v2[:, :, :70], v2[:, :, 100:101]], 2)
+    _check_layer_against_oracle(layer, k3, v3, "nvfp4")
+
+    layer.batch_repeat_interleave(2)                                                 # [s0, s0, s1, s1]
+    assert layer.batch_size() == 4
+    _check_layer_against_oracle(layer, k3.repeat_interleave(2, 0), v3.repeat_interleave(2, 0), "nvfp4")
+    used = layer.page_table[:, :2].flatten().tolist()
+    assert len(set(used)) == 8                                                       # no page is shared
+    layer.reorder(torch.tensor([3, 0]))
+    _check_layer_against_oracle(layer, k3[[1, 0]], v3[[1, 0]], "nvfp4")
+    layer.update(k2[[1, 0], :, 200:203].to(DEV), v2[[1, 0], :, 200:203].to(DEV))   # the copies grow on their own pages
+    _check_layer_against_oracle(layer, torch.cat([k3[[1, 0]], k2[[1, 0], :, 200:203]], 2),
+                                torch.cat([v3[[1, 0]], v2[[1, 0], :, 200:203]], 2), "nvfp4")
+    layer.reset()
+    assert layer.seq_len == 0 and sorted(layer._free) == list(range(1, layer.k_pool.shape[0]))
+    layer.update(k[:, :, :10].to(DEV), v[:, :, :10].to(DEV))
+    _check_layer_against_oracle(layer, k[:, :, :10], v[:, :, :10], "nvfp4")
+
+
+def test_paged_layer_without_a_length_bound_grows_its_pool():
+    torch.manual_seed(22)
+    k = torch.randn(1, 2, 1000, 64).to(torch.bfloat16)
+    v = torch.randn(1, 2, 1000, 64).to(torch.bfloat16)
+    layer = tc.PagedThriftAttentionCacheLayer(quant_format="mxfp4")
+    pos = 0
+    for c in (10, 200, 1, 789):
+        layer.update(k[:, :, pos:pos + c].to(DEV), v[:, :, pos:pos + c].to(DEV))
+        pos += c
+    assert layer.k_pool.shape[0] >= 17 and layer.page_table.shape[1] >= 16
+    _check_layer_against_oracle(layer, k, v, "mxfp4")
+
+
+@pytest.mark.parametrize("fmt,selection,dtype", [("nvfp4", "block_mean", torch.float16), ("mxfp4", "quest", torch.bfloat16)])
+def test_paged_cache_decode_and_prefill_equal_the_slab_cache(fmt, selection, dtype):
+    """Same appends into a slab cache and a paged cache: the decode step (which reads the pools through the page
+    table) and the prefill over the cache return the same bytes."""
+    torch.manual_seed(23)
+    b, hq, hkv, n, d = 2, 8, 2, 64 * 9 + 17, 128
+    k = torch.randn(b, hkv, n, d).to(dtype)
+    v = torch.randn(b, hkv, n, d).to(dtype)
+    cfg = ta.AttentionConfig(selection=selection, top_k=3, quant_format=fmt, sink_blocks=1, local_blocks=1)
+    caches = [ta.ThriftAttentionCache(config=cfg, paged=paged) for paged in (False, True)]
+    for cache in caches:
+        pos = 0
+        for c in (500, 1, 1, n - 502):
+            cache.update(k[:, :, pos:pos + c].to(DEV), v[:, :, pos:pos + c].to(DEV), 0)
+            pos += c
+    assert isinstance(caches[1].layers[0], tc.PagedThriftAttentionCacheLayer)
+    q = torch.randn(b, hq, 1, d).to(dtype).to(DEV)
+    outs = [tc.cached_decode_attention(q, cache, 0, cfg) for cache in caches]
+    assert torch.equal(outs[0], outs[1])
+    cfg4 = ta.AttentionConfig(method="fp4", quant_format=fmt)
+    outs = [tc.cached_decode_attention(q, cache, 0, cfg4) for cache in caches]
+    assert torch.equal(outs[0], outs[1])
+    ta._extension.get_extension().decode_status(DEV)
+
+    qp = torch.randn(b, hq, 64 * 10, d).to(dtype).to(DEV)
+    pre = []
+    for cache in caches:
+        cache.crop(0)
+        cache.update(k[:, :, :640].to(DEV), v[:, :, :640].to(DEV), 0)
+        pre.append(tc.cached_prefill_attention(qp, cache, 0, cfg))
+    assert torch.equal(pre[0], pre[1])

@@ -520,12 +520,14 @@ def test_public_attention_api(cuda_device):
         ta.attention(q, k, v)
 
 
-def test_prefill_long_context_slice_matches_oracle(cuda_device):
-    """Configuration-2 shape (32q/8kv, 32768 tokens, 128-token blocks, top-10%, outlier keys): the whole
-    problem runs on the GPU, the oracle recomputes one q head's selection and a slice of its rows."""
+@pytest.mark.parametrize("S,top_k_expected", [(32768, 13), (131072, 53)])
+def test_prefill_long_context_slice_matches_oracle(cuda_device, S, top_k_expected):
+    """Configuration-2 shape (32q/8kv, 32768 tokens) and the benchmark's own (131072 tokens): 128-token blocks,
+    top-10%, outlier keys.  The whole problem runs on the GPU, the oracle recomputes one q head's selection and
+    slices of its rows."""
     import thriftattention_b200 as ta
 
-    S, block = 32768, 128
+    block = 128
     g = torch.Generator(device=cuda_device).manual_seed(0)
     q = torch.randn(1, 32, S, 128, device=cuda_device, dtype=torch.float16, generator=g)
     k = torch.randn(1, 8, S, 128, device=cuda_device, dtype=torch.float16, generator=g)
@@ -534,16 +536,38 @@ def test_prefill_long_context_slice_matches_oracle(cuda_device):
     cfg = ta.AttentionConfig(selection="quest", fraction=0.10, block_size=block, quant_format="nvfp4")
     out = ta.attention(q, k, v, config=cfg)
     top_k = oracle.resolve_top_k(S // block, causal=True, fraction=0.10)
-    assert top_k == 13
+    assert top_k == top_k_expected
     for head in (5, 30):
         qh, kh, vh = q[:, head:head + 1].cpu(), k[:, head // 4:head // 4 + 1].cpu(), v[:, head // 4:head // 4 + 1].cpu()
         qm, = oracle.block_stats(qh, block, ("mean",))
         kmin, kmax = oracle.block_stats(kh, block, ("min", "max"))
         sel = oracle.select_prefill(qm, kmin, kmax, k=top_k, causal=True)
-        for lo in (0, 16384, S - 256):
+        for lo in (0, S // 2, S - 256):
             ref = oracle.prefill_attention(qh, kh, vh, sel, fmt="nvfp4", block=block, causal=True, rows=(lo, lo + 256))
             err = (out[0, head, lo:lo + 256].float().cpu() - ref[0, 0, lo:lo + 256].float()).abs()
             assert err.max().item() <= FP16_MAX_ABS and err.mean().item() <= MEAN_ABS
+
+
+def test_prefill_at_benchmark_size_scales_exactly_with_v(cuda_device):
+    """Size-independent property at the benchmark's size (32q/8kv x 131072): V enters the result linearly and its
+    block scales are floating point, so doubling V (a power of two: every scale byte moves by one exponent step,
+    every code stays) must double the output values bit for bit."""
+    import thriftattention_b200 as ta
+
+    S = 131072
+    g = torch.Generator(device=cuda_device).manual_seed(7)
+    q = torch.randn(1, 32, S, 128, device=cuda_device, dtype=torch.float16, generator=g)
+    k = torch.randn(1, 8, S, 128, device=cuda_device, dtype=torch.float16, generator=g)
+    v = torch.randn(1, 8, S, 128, device=cuda_device, dtype=torch.float16, generator=g)
+    cfg = ta.AttentionConfig(selection="quest", fraction=0.10, block_size=128, quant_format="nvfp4")
+    out1 = ta.attention(q, k, v, config=cfg)
+    out2 = ta.attention(q, k, v * 2, config=cfg)
+    assert torch.isfinite(out1).all()
+    # the only roundings that do not commute with the doubling are those of subnormal fp16 values (the rounded state
+    # between the two phases, the output itself): a handful of near-zero elements may differ by one subnormal step
+    diff = (out1.float() * 2 - out2.float()).abs()
+    assert float((diff > 0).float().mean()) < 1e-4
+    assert float(diff.max()) <= 2.0 ** -12
 
 
 # ------------------------------------------------------------------------------------ decode attention

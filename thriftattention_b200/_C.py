@@ -207,6 +207,51 @@ def cache_append(k_new, v_new, k_hi, v_hi, k_codes, k_scales, v_codes_t, v_scale
     _lib.check(rc, "cache_append")
 
 
+def cache_append_paged(k_new, v_new, k_hi, v_hi, k_codes, k_scales, v_codes, v_scales, page_table, *, start, k_count=None,
+                       v_count=None, k_mean=None, k_min=None, k_max=None, is_mx=False, stat_block=64, keep_k=False,
+                       keep_v=False):
+    """``cache_append`` into page pools behind ``page_table`` int32 [B, max_pages] (the layout ``decode_attention``
+    reads): ``k_hi`` / ``v_hi`` [pool, Hkv, 64, D], ``k_codes`` [pool, Hkv, 64, D/2], ``v_codes`` [pool, Hkv, D, 32] and
+    their scales; statistics [B, Hkv, blocks, D] by logical block.  ``k_new`` / ``v_new`` [B, Hkv, T, D]."""
+    _check(k_hi.is_cuda and k_hi.dim() == 4 and k_hi.is_contiguous() and k_hi.shape[2] == 64,
+           "k pool must be a contiguous CUDA tensor [pool_pages, kv_heads, 64, head_dim]")
+    pool, hkv, _, d = k_hi.shape
+    _check(k_hi.dtype in (torch.float16, torch.bfloat16), "KV cache tensors must be float16 or bfloat16")
+    is_bf16 = k_hi.dtype == torch.bfloat16
+    g = 32 if is_mx else 16
+    _check(page_table.is_cuda and page_table.dtype == torch.int32 and page_table.dim() == 2 and page_table.is_contiguous(),
+           "page_table must be a contiguous int32 CUDA tensor [batch, max_pages]")
+    b, max_pages = page_table.shape
+    expect = {"v_hi": (v_hi, (pool, hkv, 64, d)), "k_codes": (k_codes, (pool, hkv, 64, d // 2)),
+              "k_scales": (k_scales, (pool, hkv, 64, d // g)), "v_codes": (v_codes, (pool, hkv, d, 32)),
+              "v_scales": (v_scales, (pool, hkv, d, 64 // g))}
+    for name, (t, shape) in expect.items():
+        _check(t.is_cuda and t.is_contiguous() and tuple(t.shape) == shape, f"{name} must be contiguous {shape}")
+    for name, new, count in (("key_states", k_new, k_count), ("value_states", v_new, v_count)):
+        if new is not None:
+            _check(new.is_cuda and new.is_contiguous() and new.dtype == k_hi.dtype and new.dim() == 4
+                   and new.shape[0] == b and new.shape[1] == hkv and new.shape[3] == d,
+                   f"{name} must be contiguous [batch, kv_heads, tokens, head_dim] CUDA tensors of the cache dtype")
+            _check(count is None or count == new.shape[2], f"{name} count does not match its tensor")
+    k_count = k_new.shape[2] if k_new is not None else int(k_count or 0)
+    v_count = v_new.shape[2] if v_new is not None else int(v_count or 0)
+    _check(int(start) + max(k_count, v_count) <= max_pages * 64, "the token range exceeds the page table")
+    stat_blocks = 1
+    for name, t in (("k_mean", k_mean), ("k_min", k_min), ("k_max", k_max)):
+        if t is not None:
+            _check(t.is_cuda and t.is_contiguous() and t.dim() == 4 and t.shape[0] == b and t.shape[1] == hkv and t.shape[3] == d
+                   and t.dtype == k_hi.dtype, f"{name} must be contiguous [B, Hkv, blocks, D] of the cache dtype")
+            stat_blocks = t.shape[2]
+    flags = (1 if keep_k else 0) | (2 if keep_v else 0)
+    with torch.cuda.device(k_hi.device):
+        rc = _lib.load().ta100_cache_append_paged(_ptr(k_new), _ptr(v_new), _ptr(k_hi), _ptr(v_hi), _ptr(k_codes),
+                                                  _ptr(k_scales), _ptr(v_codes), _ptr(v_scales), _ptr(k_mean), _ptr(k_min),
+                                                  _ptr(k_max), _ptr(page_table), max_pages, pool, b, hkv, stat_blocks,
+                                                  int(start), k_count, v_count, d, stat_block, int(is_mx), int(is_bf16),
+                                                  flags, _stream(k_hi))
+    _lib.check(rc, "cache_append_paged")
+
+
 def select_prefill_blocks(q_mean, k_a, k_b, topk_count, causal=True, is_bf16=False, sink=0, local=0):
     """Per-q-block selection.  ``k_b is None`` -> block-mean score with ``k_a = k_mean``;
     otherwise Quest with ``k_a = k_min``, ``k_b = k_max``.  K statistics may be given per

@@ -22,6 +22,7 @@ SIGNATURES = {
     "ta100_quantize_qkv": (_c_int, [_c_vp] * 9 + [_c_ll, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp]),
     "ta100_block_stats": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_vp]),
     "ta100_cache_append": (_c_int, [_c_vp] * 11 + [_c_ll] + [_c_int] * 9 + [_c_vp]),
+    "ta100_cache_append_paged": (_c_int, [_c_vp] * 12 + [_c_int] * 13 + [_c_vp]),
     "ta100_select_prefill": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp] + [_c_int] * 11 + [_c_vp]),
     "ta100_select_decode": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp] + [_c_int] * 11 + [_c_vp]),
     "ta100_local_block_topk": (_c_int, [_c_vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_vp]),

@@ -14,6 +14,10 @@
 // Work is cut into independent CTA-sized items (K row bundles, 128-token V tiles, statistics
 // blocks); an item reads new rows from the inputs and old rows from the cache, never a row that
 // another item of the same launch writes, so no ordering between CTAs is needed.
+//
+// Two addressings of the cache tensors: capacity-strided slabs [heads, cap, ...], or pools of 64-token pages
+// ([pool_pages, hkv, 64, ...]; V codes [pool_pages, hkv, D, 32]) behind a page table [batch, max_pages], the
+// layout the decode kernel reads.  The statistics stay indexed by logical block in both.
 #include "common.cuh"
 
 namespace ta100 {
@@ -31,6 +35,9 @@ struct AppendParams {
     uint16_t* k_min;
     uint16_t* k_max;
     int start, k_count, v_count, cap;
+    const int32_t* page_table;    // paged addressing: [batch, max_pages] -> physical page; nullptr = slabs
+    int max_pages, pool_pages, hkv;
+    int stat_blocks;              // statistics blocks per head in k_mean / k_min / k_max (their row stride)
     int k_keep, v_keep;           // with a null input: 1 = re-quantise the cached rows, 0 = store zero rows
     int n_k_items, n_v_items, n_s_items;
     int k_loop;                   // K row bundles per K item (more than one for bulk appends)
@@ -38,21 +45,35 @@ struct AppendParams {
     int s_first, stat_block;
 };
 
-// 16-byte chunk `cv` of token `tok`: from the new rows when the token is being appended, else from the cache.
-template <int D>
-__device__ __forceinline__ uint4 row_chunk(const uint16_t* __restrict__ fresh, const uint16_t* cache, int keep,
-                                           int start, int count, int cap, long long head, int tok, int cv,
-                                           bool& is_new) {
-    is_new = false;
-    if (tok >= start && tok < start + count && !(fresh == nullptr && keep)) {
-        is_new = true;
-        if (fresh == nullptr) return make_uint4(0u, 0u, 0u, 0u);
-        return __ldg(reinterpret_cast<const uint4*>(fresh + (head * count + (tok - start)) * D) + cv);
-    }
-    return *(reinterpret_cast<const uint4*>(cache + (head * cap + tok) * D) + cv);
+// Row of token `tok` of `head` in a [.., tokens, X]-shaped cache tensor (16-bit rows, K codes, K scales), in rows;
+// -1 if the page table has no valid page there (the access is then skipped).
+template <bool PAGED>
+__device__ __forceinline__ long long cache_row(const AppendParams& p, long long head, int tok) {
+    if constexpr (!PAGED) return head * p.cap + tok;
+    const long long b = head / p.hkv, h = head - b * p.hkv;
+    const int pg = tok >> 6;
+    if (pg >= p.max_pages) return -1;
+    const int page = p.page_table[b * p.max_pages + pg];
+    if (page < 0 || page >= p.pool_pages) return -1;
+    return (static_cast<long long>(page) * p.hkv + h) * 64 + (tok & 63);
 }
 
-template <int D, bool MX, bool BF16>
+// 16-byte chunk `cv` of token `tok`: from the new rows when the token is being appended, else from the cache.
+template <int D, bool PAGED>
+__device__ __forceinline__ uint4 row_chunk(const AppendParams& p, const uint16_t* __restrict__ fresh, const uint16_t* cache,
+                                           int keep, int count, long long head, int tok, int cv, bool& is_new) {
+    is_new = false;
+    if (tok >= p.start && tok < p.start + count && !(fresh == nullptr && keep)) {
+        is_new = true;
+        if (fresh == nullptr) return make_uint4(0u, 0u, 0u, 0u);
+        return __ldg(reinterpret_cast<const uint4*>(fresh + (head * count + (tok - p.start)) * D) + cv);
+    }
+    const long long row = cache_row<PAGED>(p, head, tok);
+    if (row < 0) return make_uint4(0u, 0u, 0u, 0u);
+    return *(reinterpret_cast<const uint4*>(cache + row * D) + cv);
+}
+
+template <int D, bool MX, bool BF16, bool PAGED>
 __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p) {
     constexpr int G = MX ? 32 : 16;
     constexpr int GPR = D / G;        // groups per row
@@ -75,17 +96,18 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p)
             const int tok = p.start + row;
             uint32_t raw[G / 2];
             bool is_new = false;
+            const long long krow = cache_row<PAGED>(p, head, tok);
+            if (krow < 0) continue;
 #pragma unroll
             for (int i = 0; i < G / 8; ++i) {
-                const uint4 t = row_chunk<D>(p.k_new, p.k_hi, p.k_keep, p.start, p.k_count, p.cap, head, tok,
-                                             c * (G / 8) + i, is_new);
+                const uint4 t = row_chunk<D, PAGED>(p, p.k_new, p.k_hi, p.k_keep, p.k_count, head, tok, c * (G / 8) + i, is_new);
                 raw[4 * i + 0] = t.x; raw[4 * i + 1] = t.y; raw[4 * i + 2] = t.z; raw[4 * i + 3] = t.w;
-                if (is_new) *(reinterpret_cast<uint4*>(p.k_hi + (head * p.cap + tok) * D) + c * (G / 8) + i) = t;
+                if (is_new) *(reinterpret_cast<uint4*>(p.k_hi + krow * D) + c * (G / 8) + i) = t;
             }
             uint32_t out[G / 8];
             uint8_t sb;
             quantise_group_regs<MX, BF16>(raw, out, sb);
-            const long long gid = (head * p.cap + tok) * GPR + c;
+            const long long gid = krow * GPR + c;
             if constexpr (MX) *reinterpret_cast<uint4*>(p.k_codes + gid * 16) = make_uint4(out[0], out[1], out[2], out[3]);
             else *reinterpret_cast<uint2*>(p.k_codes + gid * 8) = make_uint2(out[0], out[1]);
             p.k_scales[gid] = sb;
@@ -106,8 +128,11 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p)
             const int r = i / VEC, cv = i % VEC;
             const int tok = lo + r;
             bool is_new;
-            const uint4 val = row_chunk<D>(p.v_new, p.v_hi, p.v_keep, p.start, p.v_count, p.cap, head, tok, cv, is_new);
-            if (is_new) *(reinterpret_cast<uint4*>(p.v_hi + (head * p.cap + tok) * D) + cv) = val;
+            const uint4 val = row_chunk<D, PAGED>(p, p.v_new, p.v_hi, p.v_keep, p.v_count, head, tok, cv, is_new);
+            if (is_new) {
+                const long long vrow = cache_row<PAGED>(p, head, tok);
+                if (vrow >= 0) *(reinterpret_cast<uint4*>(p.v_hi + vrow * D) + cv) = val;
+            }
             *reinterpret_cast<uint4*>(&tile[tok - tok0][cv * 8]) = val;
         }
         __syncthreads();
@@ -135,12 +160,27 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p)
         const int n_pieces = (hi - lo) / 16;
         for (int i = tid; i < D * n_pieces; i += 128) {
             const int ch = i / n_pieces, pc = pc_first + i % n_pieces;
-            *reinterpret_cast<uint2*>(p.v_codes + (head * D + ch) * (p.cap / 2) + tok0 / 2 + pc * 8) =
-                *reinterpret_cast<const uint2*>(&out_codes[ch][pc * 8]);
+            long long dst;
+            if constexpr (PAGED) {
+                const long long row = cache_row<true>(p, head, tok0 + pc * 16);    // page row of the piece's first token
+                if (row < 0) continue;
+                dst = ((row >> 6) * D + ch) * 32 + (row & 63) / 2;                   // [page, h, D, 32]: (page * hkv + h) = row / 64
+            } else {
+                dst = (head * D + ch) * (p.cap / 2) + tok0 / 2 + pc * 8;
+            }
+            *reinterpret_cast<uint2*>(p.v_codes + dst) = *reinterpret_cast<const uint2*>(&out_codes[ch][pc * 8]);
         }
         for (int i = tid; i < D * n_groups; i += 128) {
             const int ch = i / n_groups, g = g_first + i % n_groups;
-            p.v_scales[(head * D + ch) * (p.cap / G) + tok0 / G + g] = out_scales[ch][g];
+            long long dst;
+            if constexpr (PAGED) {
+                const long long row = cache_row<true>(p, head, tok0 + g * G);
+                if (row < 0) continue;
+                dst = ((row >> 6) * D + ch) * (64 / G) + (row & 63) / G;
+            } else {
+                dst = (head * D + ch) * (p.cap / G) + tok0 / G + g;
+            }
+            p.v_scales[dst] = out_scales[ch][g];
         }
         return;
     }
@@ -161,8 +201,7 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p)
             for (int i = 0; i < 8; ++i) { sum[i] = 0.0f; lo[i] = INFINITY; hi[i] = -INFINITY; }
             for (int r = rg; r < p.stat_block; r += 8) {
                 bool is_new;
-                const uint4 v = row_chunk<D>(p.k_new, p.k_hi, p.k_keep, p.start, p.k_count, p.cap, head,
-                                             blk * p.stat_block + r, cc, is_new);
+                const uint4 v = row_chunk<D, PAGED>(p, p.k_new, p.k_hi, p.k_keep, p.k_count, head, blk * p.stat_block + r, cc, is_new);
                 const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -190,7 +229,7 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p)
                 l = fminf(l, s_min[g][tid]);
                 h = fmaxf(h, s_max[g][tid]);
             }
-            const long long o = (head * (p.cap / p.stat_block) + blk) * D + tid;
+            const long long o = (head * p.stat_blocks + blk) * D + tid;
             if (p.k_mean) p.k_mean[o] = In16<BF16>::from_f(__fdiv_rn(total, static_cast<float>(p.stat_block)));
             if (p.k_min) p.k_min[o] = In16<BF16>::from_f(l);
             if (p.k_max) p.k_max[o] = In16<BF16>::from_f(h);
@@ -198,11 +237,20 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p)
     }
 }
 
+// Contiguous slabs: page_table = nullptr (max_pages, pool_pages, hkv, stat_blocks ignored; the statistics have
+// capacity / stat_block blocks per head).  Paged pools: capacity = max_pages * 64 is the logical bound.
 int cache_append_dispatch(const void* k_new, const void* v_new, void* k_hi, void* v_hi, void* k_codes, void* k_scales,
                           void* v_codes_t, void* v_scales_t, void* k_mean, void* k_min, void* k_max, long long heads,
                           int start, int k_count, int v_count, int capacity, int head_dim, int stat_block, int is_mx,
-                          int is_bf16, int flags, cudaStream_t stream) {
+                          int is_bf16, int flags, const void* page_table, int max_pages, int pool_pages, int hkv,
+                          int stat_blocks, cudaStream_t stream) {
     if (head_dim != 64 && head_dim != 128) return TA100_ERR_UNSUPPORTED;
+    if (page_table) {
+        if (max_pages <= 0 || pool_pages <= 0 || hkv <= 0 || heads % hkv != 0 || stat_blocks <= 0) return TA100_ERR_SHAPE;
+        if (max_pages > 0x7FFFFFFF / 64) return TA100_ERR_LIMIT;
+        capacity = max_pages * 64;
+        if (capacity % 128 != 0) capacity += 64;     // only bounds the logical token range below
+    }
     if (heads < 0 || start < 0 || k_count < 0 || v_count < 0 || capacity <= 0 || capacity % 128 != 0)
         return TA100_ERR_SHAPE;
     if (stat_block != 64 && stat_block != 128) return TA100_ERR_SHAPE;
@@ -229,6 +277,9 @@ int cache_append_dispatch(const void* k_new, const void* v_new, void* k_hi, void
     p.k_min = static_cast<uint16_t*>(k_min);
     p.k_max = static_cast<uint16_t*>(k_max);
     p.start = start; p.k_count = k_count; p.v_count = v_count; p.cap = capacity;
+    p.page_table = static_cast<const int32_t*>(page_table);
+    p.max_pages = max_pages; p.pool_pages = pool_pages; p.hkv = hkv;
+    p.stat_blocks = page_table ? stat_blocks : capacity / stat_block;
     p.k_keep = (flags & 1) ? 1 : 0;
     p.v_keep = (flags & 2) ? 1 : 0;
     p.stat_block = stat_block;
@@ -247,7 +298,11 @@ int cache_append_dispatch(const void* k_new, const void* v_new, void* k_hi, void
     }
     const long long grid = heads * (p.n_k_items + p.n_v_items + p.n_s_items);
     if (grid > 0x7FFFFFFFLL) return TA100_ERR_LIMIT;
-#define TA100_APPEND(DD, MXX, BFF) cache_append_kernel<DD, MXX, BFF><<<static_cast<unsigned>(grid), 128, 0, stream>>>(p)
+#define TA100_APPEND(DD, MXX, BFF)                                                                              \
+    do {                                                                                                        \
+        if (page_table) cache_append_kernel<DD, MXX, BFF, true><<<static_cast<unsigned>(grid), 128, 0, stream>>>(p);  \
+        else cache_append_kernel<DD, MXX, BFF, false><<<static_cast<unsigned>(grid), 128, 0, stream>>>(p);       \
+    } while (0)
     if (head_dim == 128) {
         if (is_mx) { if (is_bf16) TA100_APPEND(128, true, true); else TA100_APPEND(128, true, false); }
         else { if (is_bf16) TA100_APPEND(128, false, true); else TA100_APPEND(128, false, false); }

@@ -36,7 +36,7 @@ int decode_static_dispatch(const void*, const void*, const void*, const void*, i
                            const void*, const void*, const void*, const void*, int, int, void*, int, int, int, int, int, int, int,
                            int, int, cudaStream_t);
 int cache_append_dispatch(const void*, const void*, void*, void*, void*, void*, void*, void*, void*, void*, void*, long long,
-                          int, int, int, int, int, int, int, int, int, cudaStream_t);
+                          int, int, int, int, int, int, int, int, int, const void*, int, int, int, int, cudaStream_t);
 }  // namespace ta100
 
 namespace ta100 {
@@ -99,7 +99,18 @@ int ta100_cache_append(const void* k_new, const void* v_new, void* k_hi, void* v
                        int is_bf16, int flags, void* stream) {
     return cache_append_dispatch(k_new, v_new, k_hi, v_hi, k_codes, k_scales, v_codes_t, v_scales_t, k_mean, k_min, k_max,
                                  heads, start, k_count, v_count, capacity, head_dim, stat_block, is_mxfp4, is_bf16, flags,
-                                 S(stream));
+                                 nullptr, 0, 0, 0, 0, S(stream));
+}
+
+int ta100_cache_append_paged(const void* k_new, const void* v_new, void* k_hi, void* v_hi, void* k_codes, void* k_scales,
+                             void* v_codes, void* v_scales, void* k_mean, void* k_min, void* k_max, const void* page_table,
+                             int max_pages, int pool_pages, int batch, int hkv, int stat_blocks, int start, int k_count,
+                             int v_count, int head_dim, int stat_block, int is_mxfp4, int is_bf16, int flags, void* stream) {
+    if (!page_table) return TA100_ERR_NULL;
+    if (batch <= 0 || hkv <= 0) return TA100_ERR_SHAPE;
+    return cache_append_dispatch(k_new, v_new, k_hi, v_hi, k_codes, k_scales, v_codes, v_scales, k_mean, k_min, k_max,
+                                 static_cast<long long>(batch) * hkv, start, k_count, v_count, 0, head_dim, stat_block,
+                                 is_mxfp4, is_bf16, flags, page_table, max_pages, pool_pages, hkv, stat_blocks, S(stream));
 }
 
 int ta100_select_prefill(const void* q_mean, const void* k_a, const void* k_b, void* out, int heads, int group, int nq,

@@ -384,6 +384,284 @@ class ThriftAttentionCacheLayer:
         self.selected_blocks = None
 
 
+def _raw(tensor: torch.Tensor) -> torch.Tensor:
+    """fp8 scale tensors as bytes (indexing, concatenation and fills are not implemented for fp8 on every build)."""
+    return tensor if tensor.dtype in (torch.float16, torch.bfloat16, torch.uint8) else tensor.view(torch.uint8)
+
+
+@dataclass
+class PagedThriftAttentionCacheLayer(ThriftAttentionCacheLayer):
+    """The same layer over POOLS of 64-token pages behind a page table - the layout the decode kernel reads
+    (``decode_attention(..., page_table=)``) and ``cache_append_paged`` writes.
+
+    * pools (one set per layer): 16-bit K/V ``[pages, Hkv, 64, D]``, K codes ``[pages, Hkv, 64, D/2]`` + scales,
+      V codes transposed inside a page ``[pages, Hkv, D, 32]`` + scales; ``page_table`` int32 ``[B, max_pages]``.
+      With ``max_cache_len`` the pool holds every sequence at that length from the first append on; otherwise it
+      starts small and doubles (the one place a copy is made) when the free list runs dry;
+    * a sequence grows by taking page ids from the free list - nothing is moved (the reference, and the
+      capacity-strided layer above, copy the whole slab: transformers_cache.py:255-306);
+    * free pages hold zeros, so the rows behind the logical length read as zero rows, as the kernels expect;
+      physical page 0 is never handed out and stays zero (what a gather reads where a sequence has no page);
+    * block statistics stay indexed by logical block (``[B, Hkv, blocks, D]``, grown by doubling: 1/64 of K);
+    * the decode step reads the pools in place.  Whatever wants contiguous tensors (a prefill over the cache,
+      ``key_view`` / ``value_view``, the legacy-cache export) gets them by a gather, cached until the next change.
+    """
+
+    k_pool: torch.Tensor | None = None
+    v_pool: torch.Tensor | None = None
+    k4_pool: torch.Tensor | None = None
+    ks_pool: torch.Tensor | None = None
+    v4_pool: torch.Tensor | None = None
+    vs_pool: torch.Tensor | None = None
+    page_table: torch.Tensor | None = None          # device int32 [B, max_pages]; -1 = no page
+    _pages: list | None = None                      # host mirror: per sequence, its page ids in order
+    _free: list | None = None
+    _gathered: dict | None = None
+
+    # ------------------------------------------------------------------------------------------ shape helpers
+    def _pools(self) -> tuple[torch.Tensor, ...]:
+        return (self.k_pool, self.v_pool, self.k4_pool, self.ks_pool, self.v4_pool, self.vs_pool)
+
+    def batch_size(self) -> int | None:
+        return None if self._pages is None else len(self._pages)
+
+    def kv_heads(self) -> int:
+        if self.k_pool is None:
+            raise RuntimeError("ThriftAttention cache layer has not been initialized")
+        return int(self.k_pool.shape[1])
+
+    # ------------------------------------------------------------------------------------------ page management
+    def _new_pools(self, pages: int, heads: int, head_dim: int, dtype: torch.dtype, device) -> dict[str, torch.Tensor]:
+        g = _group_size(self.quant_format)
+        u8 = dict(device=device, dtype=torch.uint8)
+        return {"k_pool": torch.zeros(pages, heads, PAGE, head_dim, device=device, dtype=dtype),
+                "v_pool": torch.zeros(pages, heads, PAGE, head_dim, device=device, dtype=dtype),
+                "k4_pool": torch.zeros(pages, heads, PAGE, head_dim // 2, **u8),
+                "ks_pool": torch.zeros(pages, heads, PAGE, head_dim // g, **u8).view(_scale_dtype(self.quant_format)),
+                "v4_pool": torch.zeros(pages, heads, head_dim, PAGE // 2, **u8),
+                "vs_pool": torch.zeros(pages, heads, head_dim, PAGE // g, **u8).view(_scale_dtype(self.quant_format))}
+
+    def _grow_pool(self, extra_pages: int) -> None:
+        old = int(self.k_pool.shape[0])
+        fresh = self._new_pools(extra_pages, self.k_pool.shape[1], self.k_pool.shape[3], self.k_pool.dtype, self.k_pool.device)
+        for name, tensor in fresh.items():
+            cur = getattr(self, name)
+            setattr(self, name, torch.cat([_raw(cur), _raw(tensor)]).view(cur.dtype))
+        self._free.extend(range(old, old + extra_pages))
+
+    def _take_pages(self, count: int) -> list[int]:
+        if count > len(self._free):
+            self._grow_pool(max(count - len(self._free), int(self.k_pool.shape[0])))
+        taken, self._free = self._free[:count], self._free[count:]
+        return taken
+
+    def _release_pages(self, pages: list[int]) -> None:
+        """Back to the free list, as zeros."""
+        if not pages:
+            return
+        idx = torch.tensor(pages, device=self.k_pool.device, dtype=torch.long)
+        for pool in self._pools():
+            _raw(pool).index_fill_(0, idx, 0)
+        self._free.extend(pages)
+
+    def _upload_table(self) -> None:
+        """Host page lists -> device table.  The table is as wide as ``max_cache_len`` needs when that is known, else
+        it doubles when a sequence outgrows it."""
+        need = max(2, max(len(row) for row in self._pages))
+        width = int(self.page_table.shape[1]) if self.page_table is not None else 0
+        if self.max_cache_len is not None:
+            width = max(width, (self.max_cache_len + PAGE - 1) // PAGE)
+        if width < need:
+            width = max(need, 2 * width)
+        host = torch.full((len(self._pages), width), -1, dtype=torch.int32)
+        for b, row in enumerate(self._pages):
+            if row:
+                host[b, : len(row)] = torch.tensor(row, dtype=torch.int32)
+        self.page_table = host.to(self.k_pool.device)
+
+    def _ensure_capacity(self, like: torch.Tensor, required: int) -> None:
+        batch, heads, _, head_dim = like.shape
+        if self.k_pool is None:
+            per_seq = (self.max_cache_len + PAGE - 1) // PAGE if self.max_cache_len is not None else 2 * ((required + PAGE - 1) // PAGE)
+            for name, tensor in self._new_pools(1 + batch * max(per_seq, 1), heads, head_dim, like.dtype, like.device).items():
+                setattr(self, name, tensor)
+            self._pages = [[] for _ in range(batch)]
+            self._free = list(range(1, int(self.k_pool.shape[0])))          # page 0: the zero page
+        else:
+            if batch != len(self._pages) or heads != self.k_pool.shape[1]:
+                raise ValueError("ThriftAttentionCache batch/head shape changed unexpectedly")
+            if like.dtype != self.k_pool.dtype:
+                raise ValueError("ThriftAttentionCache dtype changed unexpectedly")
+        need = max(1, (required + PAGE - 1) // PAGE)
+        changed = self.page_table is None
+        for row in self._pages:
+            if len(row) < need:
+                row.extend(self._take_pages(need - len(row)))
+                changed = True
+        if changed:
+            self._upload_table()
+        # statistics by logical block
+        blocks = int(self.page_table.shape[1])
+        if self.k_mean is None or self.k_mean.shape[2] < blocks:
+            names = ("k_mean", "k_min", "k_max") if self.track_minmax else ("k_mean",)
+            for name in names:
+                fresh = torch.zeros(batch, heads, blocks, head_dim, device=like.device, dtype=like.dtype)
+                cur = getattr(self, name)
+                if cur is not None:
+                    fresh[:, :, : cur.shape[2]] = cur
+                setattr(self, name, fresh)
+        self.capacity = need * PAGE
+        self.selected_blocks = None
+
+    # ------------------------------------------------------------------------------------------ update
+    def update(self, key_states: torch.Tensor, value_states: torch.Tensor,
+               cache_kwargs: dict[str, Any] | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """Append through the page table (one launch).  Returns the logical 16-bit K/V - gathered, which costs a
+        copy of the layer; callers that read the cache in place (the registered attention function does) should
+        pass ``cache_kwargs={"thrift_return_new_states": True}`` or use ``append``, and get the new rows back."""
+        self.append(key_states, value_states, cache_kwargs)
+        if cache_kwargs is not None and cache_kwargs.get("thrift_return_new_states"):
+            return key_states, value_states
+        return self.key_view(), self.value_view()
+
+    def append(self, key_states: torch.Tensor, value_states: torch.Tensor, cache_kwargs: dict[str, Any] | None = None) -> None:
+        if key_states.ndim != 4 or value_states.ndim != 4:
+            raise ValueError("KV cache tensors must be [batch, heads, seq, head_dim]")
+        if key_states.shape != value_states.shape:
+            raise ValueError("key_states and value_states must have identical shapes")
+        if key_states.dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError("KV cache tensors must be float16 or bfloat16")
+        if key_states.dtype != value_states.dtype:
+            raise ValueError("key_states and value_states must have the same dtype")
+        start = _cache_position_start(cache_kwargs, self.seq_len)
+        token_count = key_states.shape[2]
+        end = start + token_count
+        if self.max_cache_len is not None and end > self.max_cache_len:
+            raise ValueError(f"ThriftAttentionCache length {end} exceeds max_cache_len={self.max_cache_len}")
+        self._ensure_capacity(key_states, end)
+        self.seq_len = max(self.seq_len, end)
+        if token_count:
+            self._append(key_states.contiguous(), value_states.contiguous(), start)
+
+    def _append(self, key_states: torch.Tensor | None, value_states: torch.Tensor | None, start: int, *,
+                k_count: int | None = None, v_count: int | None = None, keep_k: bool = False, keep_v: bool = False,
+                stats: bool = True) -> None:
+        self._gathered = None
+        get_extension().cache_append_paged(
+            key_states, value_states, self.k_pool, self.v_pool, self.k4_pool, self.ks_pool, self.v4_pool, self.vs_pool,
+            self.page_table, start=start, k_count=k_count, v_count=v_count,
+            k_mean=self.k_mean if stats else None, k_min=self.k_min if stats else None,
+            k_max=self.k_max if stats else None, is_mx=self.quant_format == "mxfp4", stat_block=PAGE,
+            keep_k=keep_k, keep_v=keep_v)
+
+    # ------------------------------------------------------------------------------------------- views (gathers)
+    def _gather(self, name: str, tokens: int) -> torch.Tensor:
+        """Contiguous ``[B, Hkv, tokens, X]`` (or ``[B, Hkv, D, tokens/2 | tokens/G]`` for V codes and scales) of the
+        first ``tokens`` token positions; positions without a page read as zeros."""
+        if self.k_pool is None or self.page_table is None:
+            raise RuntimeError("ThriftAttention cache layer has not been initialized")
+        self._gathered = self._gathered or {}
+        key = (name, tokens)
+        if key in self._gathered:
+            return self._gathered[key]
+        pool = getattr(self, name)
+        n = (tokens + PAGE - 1) // PAGE
+        have = min(n, int(self.page_table.shape[1]))
+        picked = _raw(pool)[self.page_table[:, :have].long().clamp_min(0)]      # [B, have, Hkv, 64 | D, X]; no page -> page 0
+        if have < n:
+            pad = torch.zeros(picked.shape[0], n - have, *picked.shape[2:], device=picked.device, dtype=picked.dtype)
+            picked = torch.cat([picked, pad], dim=1)
+        if name in ("v4_pool", "vs_pool"):
+            if tokens % PAGE:
+                raise ValueError("transposed V views are cut at page boundaries")
+            out = picked.permute(0, 2, 3, 1, 4).reshape(picked.shape[0], picked.shape[2], picked.shape[3], -1)
+        else:
+            out = picked.permute(0, 2, 1, 3, 4).reshape(picked.shape[0], picked.shape[2], n * PAGE, picked.shape[4])[:, :, :tokens]
+        out = out.contiguous().view(pool.dtype)
+        self._gathered[key] = out
+        return out
+
+    def key_view(self) -> torch.Tensor:
+        return self._gather("k_pool", self.seq_len)
+
+    def value_view(self) -> torch.Tensor:
+        return self._gather("v_pool", self.seq_len)
+
+    def packed_views(self) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+        kernel_len = self.kernel_len()
+        v_len = _round_up(kernel_len, CAPACITY_QUANTUM)
+        return (self._gather("k4_pool", kernel_len), self._gather("v4_pool", v_len),
+                self._gather("ks_pool", kernel_len), self._gather("vs_pool", v_len))
+
+    def hi_kernel_views(self) -> tuple[torch.Tensor, torch.Tensor]:
+        n = self.kernel_len()
+        return self._gather("k_pool", n), self._gather("v_pool", n)
+
+    # ------------------------------------------------------------------------- batch-dimension surgery
+    def batch_repeat_interleave(self, repeats: int) -> None:
+        if self._pages is None:
+            return
+        self._index_select_batch(torch.arange(len(self._pages)).repeat_interleave(repeats))
+
+    def _index_select_batch(self, indices: torch.Tensor) -> None:
+        """New sequence i becomes a COPY of old sequence indices[i] (beams diverge afterwards, so pages are not shared)."""
+        if self._pages is None:
+            return
+        self._gathered = None
+        rows = [int(i) for i in indices.tolist()]
+        new_pages = [self._take_pages(len(self._pages[src])) for src in rows]
+        dst = [pg for row in new_pages for pg in row]
+        src = [pg for r in rows for pg in self._pages[r]]
+        if dst:
+            di = torch.tensor(dst, device=self.k_pool.device, dtype=torch.long)
+            si = torch.tensor(src, device=self.k_pool.device, dtype=torch.long)
+            for pool in self._pools():
+                raw = _raw(pool)
+                raw.index_copy_(0, di, raw.index_select(0, si))
+        old = [pg for row in self._pages for pg in row]
+        self._pages = new_pages
+        self._release_pages(old)
+        sel = indices.to(self.k_pool.device)
+        for name in ("k_mean", "k_min", "k_max"):
+            tensor = getattr(self, name)
+            if tensor is not None:
+                setattr(self, name, tensor.index_select(0, sel))
+        self._upload_table()
+        self.selected_blocks = None
+
+    # ------------------------------------------------------------------------------------ crop / reset
+    def crop(self, max_length: int) -> None:
+        if max_length < 0:
+            max_length = max(self.seq_len + max_length, 0)
+        new_len = min(self.seq_len, max_length)
+        if new_len < self.seq_len and self._pages is not None:
+            self._gathered = None
+            keep = max(1, (new_len + PAGE - 1) // PAGE)
+            dropped = [pg for row in self._pages for pg in row[keep:]]
+            self._pages = [row[:keep] for row in self._pages]
+            self._release_pages(dropped)
+            self._upload_table()
+            key_end = keep * PAGE
+            if new_len < key_end:
+                # zero rows behind the new length inside the last page, codes and scales re-derived from them
+                self._append(None, None, new_len, k_count=key_end - new_len, v_count=key_end - new_len, stats=False)
+            self.capacity = keep * PAGE
+        self.seq_len = new_len
+
+    def reset(self) -> None:
+        if self._pages is not None:
+            self._gathered = None
+            dropped = [pg for row in self._pages for pg in row]
+            self._pages = [[] for _ in self._pages]
+            self._release_pages(dropped)
+            self.page_table = None
+        self.seq_len = 0
+        self.capacity = 0
+
+    def _zero_physical_tail(self, logical_len: int) -> None:       # the slab layer's helper; crop above does the work
+        raise NotImplementedError
+
+
 class ThriftAttentionCache:
     """Cache object handed to ``model(..., past_key_values=cache)``: one ``ThriftAttentionCacheLayer``
     per attention layer plus the Transformers cache protocol (``update``, ``get_seq_length``,
@@ -391,19 +669,23 @@ class ThriftAttentionCache:
     directly instead of subclassing, because the base-class constructor differs between
     Transformers releases (transformers_cache.py:478-567)."""
 
-    def __init__(self, *, config: AttentionConfig | None = None, max_cache_len: int | None = None) -> None:
+    def __init__(self, *, config: AttentionConfig | None = None, max_cache_len: int | None = None,
+                 paged: bool = False) -> None:
+        """``paged=True`` keeps every layer in pools of 64-token pages behind a page table
+        (``PagedThriftAttentionCacheLayer``) instead of capacity-strided slabs."""
         self.config = config or AttentionConfig()
         self._max_cache_len = max_cache_len
+        self.paged = bool(paged)
         self.layers: list[ThriftAttentionCacheLayer] = []
         self._seen_tokens = 0
         self.prefill_real_seq_len: int | None = None
 
     @classmethod
     def from_model(cls, model: object, *, config: AttentionConfig | None = None,
-                   max_cache_len: int | None = None) -> "ThriftAttentionCache":
+                   max_cache_len: int | None = None, paged: bool = False) -> "ThriftAttentionCache":
         if max_cache_len is None:
             max_cache_len = getattr(getattr(model, "config", None), "max_position_embeddings", None)
-        return cls(config=config, max_cache_len=max_cache_len)
+        return cls(config=config, max_cache_len=max_cache_len, paged=paged)
 
     # ------------------------------------------------------------------------------------ properties
     @property
@@ -429,7 +711,10 @@ class ThriftAttentionCache:
     @property
     def max_batch_size(self) -> int | None:
         for layer in self.layers:
-            if layer.k_fp16 is not None:
+            if isinstance(layer, PagedThriftAttentionCacheLayer):
+                if layer.batch_size() is not None:
+                    return layer.batch_size()
+            elif layer.k_fp16 is not None:
                 return int(layer.k_fp16.shape[0])
         return None
 
@@ -439,14 +724,18 @@ class ThriftAttentionCache:
         if layer_idx is None:
             raise ValueError("ThriftAttentionCache.update requires layer_idx")
         layer = self.layer(layer_idx)
+        if self.paged and get_active_thriftattention_cache() is self:
+            # the registered attention function reads the pools in place: spare the gather of the full K/V
+            cache_kwargs = dict(cache_kwargs or {}, thrift_return_new_states=True)
         key, value = layer.update(key_states, value_states, cache_kwargs)
         if layer_idx == 0:
             self._seen_tokens = layer.seq_len
         return key, value
 
     def layer(self, layer_idx: int) -> ThriftAttentionCacheLayer:
+        kind = PagedThriftAttentionCacheLayer if self.paged else ThriftAttentionCacheLayer
         while len(self.layers) <= layer_idx:
-            self.layers.append(ThriftAttentionCacheLayer(
+            self.layers.append(kind(
                 max_cache_len=self._max_cache_len,
                 quant_format=self.config.quant_format,
                 track_minmax=self.config.selection == "quest"))
@@ -529,9 +818,12 @@ def cached_decode_attention(query: torch.Tensor, cache: ThriftAttentionCache, la
 
     q = query.contiguous()
     is_bf16 = q.dtype == torch.bfloat16
-    kv_heads = layer.key_view().shape[1]
+    paged = isinstance(layer, PagedThriftAttentionCacheLayer)
+    kv_heads = layer.kv_heads() if paged else layer.key_view().shape[1]
     q_grouped = _group_single_query(q, kv_heads)
     fmt = quant_format.name
+    if paged:
+        return _ungroup_single_query(_paged_decode_step(q_grouped, layer, config, quant_format), q.shape[1])
     if config.method == "thrift":
         fused = _fused_decode_step(q_grouped, layer, config, fmt)
         if fused is not None:
@@ -552,6 +844,21 @@ def cached_decode_attention(query: torch.Tensor, cache: ThriftAttentionCache, la
         q_grouped, layer.key_view(), layer.value_view(), selected_blocks, q_packed, k_packed, v_packed_t, q_scale,
         k_scale, v_scale_t, is_bf16)
     return _ungroup_single_query(out, q.shape[1])
+
+
+def _paged_decode_step(q_grouped: torch.Tensor, layer: "PagedThriftAttentionCacheLayer", config: AttentionConfig,
+                       quant_format) -> torch.Tensor:
+    """The decode step over a paged layer: quantise q, select blocks from the (logical) statistics, then split-KV
+    attention that reads the page pools in place through the layer's page table."""
+    if config.method not in ("thrift", "fp4"):
+        raise ValueError(f"unsupported ThriftAttention method {config.method!r}")
+    is_bf16 = q_grouped.dtype == torch.bfloat16
+    q_packed, q_scale = quant_format.quantize(q_grouped, is_bf16=is_bf16)
+    selected = select_cached_decode_blocks(q_grouped, layer, config) if config.method == "thrift" else None
+    return get_extension().decode_attention(
+        q_grouped, layer.k_pool, layer.v_pool, selected, q_packed, layer.k4_pool, layer.v4_pool, q_scale, layer.ks_pool,
+        layer.vs_pool, is_mx=quant_format.name == "mxfp4", is_bf16=is_bf16, kv_len=layer.kernel_len(),
+        page_table=layer.page_table)
 
 
 def _fused_decode_step(q_grouped: torch.Tensor, layer: ThriftAttentionCacheLayer, config: AttentionConfig,
