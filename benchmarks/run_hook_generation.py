@@ -24,7 +24,7 @@ import torch  # noqa: E402
 FRACTION = 0.10
 
 
-def run_hf(prompt_len: int, new_tokens: int, layers: int, fraction: float = FRACTION) -> None:
+def run_hf(prompt_len: int, new_tokens: int, layers: int, fraction: float = FRACTION, paged: bool = False) -> None:
     """End to end through the Transformers hook on a random-init decoder of the Llama-3-8B shape (d_model 4096,
     32 q / 8 kv heads x 128, SwiGLU 14336, RoPE theta 5e5, vocab 128256, fp16): prefill of `prompt_len` uniform
     random token ids, then `new_tokens` greedy decode steps over a ThriftAttentionCache, NVFP4 with the top 10 %
@@ -55,7 +55,7 @@ def run_hf(prompt_len: int, new_tokens: int, layers: int, fraction: float = FRAC
         with torch.no_grad():
             if use_hook:
                 model.config._attn_implementation = name
-                prep = prepare_transformers_generation_cache(model, ids, max_new_tokens=new_tokens)
+                prep = prepare_transformers_generation_cache(model, ids, max_new_tokens=new_tokens, paged=paged)
                 ctx, cache, inputs, pos0 = prep.activate(), prep.past_key_values, prep.input_ids, prep.cache_position
             else:
                 model.config._attn_implementation = "sdpa"
@@ -105,7 +105,7 @@ def run_hf(prompt_len: int, new_tokens: int, layers: int, fraction: float = FRAC
                   "argmax_agreement": sum(int(x[1] == y[1]) for x, y in zip(exact, ours)) / len(cos)}
     print(json.dumps({
         "case": f"Transformers hook, Llama-3-8B-shaped decoder ({layers} layers, random init, fp16): prefill {prompt_len} "
-                f"tokens + {new_tokens} greedy decode steps, NVFP4 + block-mean top-{fraction:.0%}",
+                f"tokens + {new_tokens} greedy decode steps, NVFP4 + block-mean top-{fraction:.0%}" + (", paged cache" if paged else ""),
         "prefill_ms": pre, "prefill_tokens_per_s": prompt_len / pre * 1e3,
         "decode_ms_per_token": dec / new_tokens, "decode_tokens_per_s": new_tokens / dec * 1e3,
         "sdpa_prefill_ms": pre_x, "sdpa_decode_ms_per_token": dec_x / new_tokens,
@@ -119,8 +119,9 @@ def main() -> None:
     ap.add_argument("--new-tokens", type=int, default=256)
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--fraction", type=float, default=FRACTION, help="share of the key blocks kept in 16 bit (1.0: all of them)")
+    ap.add_argument("--paged", action="store_true", help="keep the cache in page pools behind a page table")
     args = ap.parse_args()
-    run_hf(args.prompt, args.new_tokens, args.layers, args.fraction)
+    run_hf(args.prompt, args.new_tokens, args.layers, args.fraction, args.paged)
 
 
 if __name__ == "__main__":

@@ -327,6 +327,17 @@ int ta100_cached_decode_step(const void* q, void* q4, void* qs, const void* k_hi
                              int head_dim, int is_mxfp4, int is_bf16, int splits, void* stream);
 
 /*
+ * The same step over a PAGED cache (pools and page table as for ta100_decode_attention; the block statistics are
+ * indexed by logical block as above).  What a paged ThriftAttentionCache layer calls once per layer and token.
+ */
+int ta100_cached_decode_step_paged(const void* q, void* q4, void* qs, const void* k_hi, const void* v_hi, const void* k4,
+                                   const void* ks, const void* v4, const void* vs, const void* page_table, int max_pages,
+                                   int pool_pages, const void* stat_a, const void* stat_b, void* sel, void* out,
+                                   void* part_o, void* part_ml, int batch, int hkv, int group, int kv_len,
+                                   int stat_cap_blocks, int n_select_blocks, int top_k, int sink, int local, int head_dim,
+                                   int is_mxfp4, int is_bf16, int splits, void* stream);
+
+/*
  * The merge of one producer's chains that stays a partial: part_o [flat_kv_heads, splits, group, D],
  * part_ml [.., 2] -> out_o [flat_kv_heads, 1, group, D] (fp32, units of C), out_ml [flat_kv_heads, 1, group, 2]
  * (row maximum, row sum), i.e. the same arrays with splits = 1.  A GPU that holds a slice of the KV sequence

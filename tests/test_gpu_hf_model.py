@@ -68,7 +68,7 @@ def _tiny_llama(name):
     return transformers.LlamaForCausalLM(cfg).half().eval().to(DEV)
 
 
-def _hook_against_oracle(model_factory, hook_name, fraction, vocab, prompt_len, new_tokens, padding, layers):
+def _hook_against_oracle(model_factory, hook_name, fraction, vocab, prompt_len, new_tokens, padding, layers, paged=False):
     from thriftattention_b200._extension import get_extension
 
     name = register_transformers_attention(TransformersAttentionConfig(name=hook_name, fraction=fraction))
@@ -84,7 +84,8 @@ def _hook_against_oracle(model_factory, hook_name, fraction, vocab, prompt_len, 
     ids = torch.randint(0, vocab, (1, prompt_len), generator=torch.Generator().manual_seed(1)).to(DEV)
 
     # ---------------- run A: the registered sm_100a path over a ThriftAttentionCache
-    prep = prepare_transformers_generation_cache(model, ids, max_new_tokens=new_tokens)
+    prep = prepare_transformers_generation_cache(model, ids, max_new_tokens=new_tokens, paged=paged)
+    assert prep.past_key_values.paged == paged
     assert (prep.padding, prep.padded_length) == (padding, prompt_len + padding)
     count = resolve_top_k(prompt_len // 64, causal=True, fraction=fraction)
     assert prep.config.top_k == count
@@ -128,6 +129,11 @@ def _hook_against_oracle(model_factory, hook_name, fraction, vocab, prompt_len, 
 
 def test_llama_prefill_and_decode_through_the_hook():
     _hook_against_oracle(_tiny_llama, "thrift_hf_test", 0.25, 512, 300, 3, 20, 2)
+
+
+def test_llama_prefill_and_decode_through_the_hook_over_a_paged_cache():
+    """The same run with the cache in page pools: prompt padding cropped inside a page, decode through the page table."""
+    _hook_against_oracle(_tiny_llama, "thrift_hf_test_paged", 0.25, 512, 300, 3, 20, 2, paged=True)
 
 
 def _llama3_8b_shaped(name):

@@ -702,8 +702,9 @@ _decode_step_splits: dict = {}
 
 
 def cached_decode_step(q_grouped, k_hi, v_hi, k_packed, k_scale, v_packed_t, v_scale_t, stat_a, stat_b, *, kv_len, n_select_blocks,
-                       top_k, sink=0, local=0, is_mx=False, sel_out=None):
-    """One decode step over a contiguous cache in ONE library call (quantise q, select, attend, merge).
+                       top_k, sink=0, local=0, is_mx=False, sel_out=None, page_table=None):
+    """One decode step over a contiguous cache in ONE library call (quantise q, select, attend, merge).  With
+    ``page_table`` (int32 [B, max_pages]) the cache tensors are the page pools of ``decode_attention``.
 
     ``q_grouped`` [B, Hkv, G, D]; the cache tensors are the capacity-sized buffers themselves (not views):
     ``k_hi`` / ``v_hi`` [B, Hkv, cap, D], ``k_packed`` [B, Hkv, cap, D/2], ``v_packed_t`` [B, Hkv, D, cap/2] and their
@@ -738,6 +739,19 @@ def cached_decode_step(q_grouped, k_hi, v_hi, k_packed, k_scale, v_packed_t, v_s
         sel_out = torch.empty(b * hkv, width, dtype=torch.int32, device=dev)
     out = torch.empty(b, hkv, g, d, dtype=q_grouped.dtype, device=dev)
     vp = ctypes.c_void_p
+    if page_table is not None:
+        with torch.cuda.device(dev):
+            rc = lib.ta100_cached_decode_step_paged(
+                vp(q_grouped.data_ptr()), vp(q4.data_ptr()), vp(qs.data_ptr()), vp(k_hi.data_ptr()), vp(v_hi.data_ptr()),
+                vp(k_packed.data_ptr()), vp(k_scale.data_ptr()), vp(v_packed_t.data_ptr()), vp(v_scale_t.data_ptr()),
+                vp(page_table.data_ptr()), page_table.shape[1], k_packed.shape[0],
+                vp(stat_a.data_ptr()) if width else None, vp(stat_b.data_ptr()) if (width and stat_b is not None) else None,
+                vp(sel_out.data_ptr()), vp(out.data_ptr()), vp(part_o.data_ptr()), vp(part_ml.data_ptr()), b, hkv, g, kv_len,
+                stat_a.shape[2] if stat_a is not None else 0, n_select_blocks, top_k, sink, local, d, int(is_mx),
+                int(is_bf16), splits, vp(torch.cuda.current_stream(dev).cuda_stream))
+        if rc:
+            _lib.check(rc, "cached_decode_step")
+        return out, sel_out
     with torch.cuda.device(dev):
         rc = lib.ta100_cached_decode_step(
             vp(q_grouped.data_ptr()), vp(q4.data_ptr()), vp(qs.data_ptr()), vp(k_hi.data_ptr()), vp(v_hi.data_ptr()),

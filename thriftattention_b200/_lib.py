@@ -31,6 +31,7 @@ SIGNATURES = {
     "ta100_merge_page_candidates": (_c_int, [_c_vp, _c_vp] + [_c_int] * 8 + [_c_vp]),
     "ta100_reduce_partials": (_c_int, [_c_vp] * 4 + [_c_ll] + [_c_int] * 3 + [_c_vp]),
     "ta100_cached_decode_step": (_c_int, [_c_vp] * 15 + [_c_int] * 14 + [_c_vp]),
+    "ta100_cached_decode_step_paged": (_c_int, [_c_vp] * 10 + [_c_int] * 2 + [_c_vp] * 6 + [_c_int] * 13 + [_c_vp]),
     "ta100_prefill_workspace_bytes": (_c_sz, [_c_int] * 7),
     "ta100_prefill_attention": (_c_int, [_c_vp] * 4 + [_c_int, _c_int] + [_c_vp] * 8 + [_c_sz] + [_c_int] * 14 + [_c_vp]),
     "ta100_prefill_status": (_c_int, [_c_vp] + [_c_int] * 7 + [_c_vp]),

@@ -198,6 +198,27 @@ int ta100_cached_decode_step(const void* q, void* q4, void* qs, const void* k_hi
                            part_ml, batch, hkv, group, kv_len, kv_cap, head_dim, is_mxfp4, is_bf16, splits, 1, S(stream));
 }
 
+int ta100_cached_decode_step_paged(const void* q, void* q4, void* qs, const void* k_hi, const void* v_hi, const void* k4,
+                                   const void* ks, const void* v4, const void* vs, const void* page_table, int max_pages,
+                                   int pool_pages, const void* stat_a, const void* stat_b, void* sel, void* out,
+                                   void* part_o, void* part_ml, int batch, int hkv, int group, int kv_len,
+                                   int stat_cap_blocks, int n_select_blocks, int top_k, int sink, int local, int head_dim,
+                                   int is_mxfp4, int is_bf16, int splits, void* stream) {
+    if (!page_table) return TA100_ERR_NULL;
+    const long long flat = static_cast<long long>(batch) * hkv;
+    int rc = quantize_dispatch(q, q4, qs, flat, group, head_dim, is_mxfp4, is_bf16, 0, S(stream));
+    if (rc != TA100_OK) return rc;
+    const int width = top_k + sink + local;
+    if (width > 0) {
+        rc = select_decode_dispatch(q, stat_a, stat_b, sel, nullptr, static_cast<int>(flat), group, n_select_blocks,
+                                    stat_cap_blocks, head_dim, top_k, stat_b != nullptr, is_bf16, sink, local, 0, S(stream));
+        if (rc != TA100_OK) return rc;
+    }
+    return decode_dispatch(q, k_hi, v_hi, width > 0 ? sel : nullptr, width, q4, k4, v4, qs, ks, vs, page_table, max_pages,
+                           pool_pages, out, part_o, part_ml, batch, hkv, group, kv_len, kv_len, head_dim, is_mxfp4, is_bf16,
+                           splits, 1, S(stream));
+}
+
 int ta100_decode_status(void* stream) { return decode_status(S(stream)); }
 
 int ta100_merge_partials(const void* part_o, const void* part_ml, void* out, int shards, long long shard_stride_o,

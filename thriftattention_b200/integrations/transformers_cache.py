@@ -823,7 +823,10 @@ def cached_decode_attention(query: torch.Tensor, cache: ThriftAttentionCache, la
     q_grouped = _group_single_query(q, kv_heads)
     fmt = quant_format.name
     if paged:
-        return _ungroup_single_query(_paged_decode_step(q_grouped, layer, config, quant_format), q.shape[1])
+        fused = _fused_decode_step(q_grouped, layer, config, fmt) if config.method == "thrift" else None
+        if fused is None:
+            fused = _paged_decode_step(q_grouped, layer, config, quant_format)
+        return _ungroup_single_query(fused, q.shape[1])
     if config.method == "thrift":
         fused = _fused_decode_step(q_grouped, layer, config, fmt)
         if fused is not None:
@@ -880,6 +883,12 @@ def _fused_decode_step(q_grouped: torch.Tensor, layer: ThriftAttentionCacheLayer
     sink = max(0, min(getattr(config, "sink_blocks", 0), complete_blocks - selected_count - local))
     if selected_count == 0:
         sink = local = 0
+    if isinstance(layer, PagedThriftAttentionCacheLayer):
+        out, layer.selected_blocks = step(q_grouped, layer.k_pool, layer.v_pool, layer.k4_pool, layer.ks_pool, layer.v4_pool,
+                                          layer.vs_pool, stat_a, stat_b, kv_len=layer.kernel_len(),
+                                          n_select_blocks=complete_blocks, top_k=selected_count, sink=sink, local=local,
+                                          is_mx=fmt == "mxfp4", sel_out=layer.selected_blocks, page_table=layer.page_table)
+        return out
     out, layer.selected_blocks = step(q_grouped, layer.k_fp16, layer.v_fp16, layer.k_packed, layer.k_scale,
                                       layer.v_packed_t, layer.v_scale_t, stat_a, stat_b, kv_len=layer.kernel_len(),
                                       n_select_blocks=complete_blocks, top_k=selected_count, sink=sink, local=local,
@@ -910,15 +919,18 @@ def cached_prefill_attention(query: torch.Tensor, cache: ThriftAttentionCache, l
         common["seq_major_out"] = True
 
     if config.method == "fp4":
-        return ext.prefill_attention(None, None, None, None, q_packed, k_packed, v_packed_t, q_scale, k_scale,
-                                     v_scale_t, **common)
-    if config.method != "thrift":
+        out = ext.prefill_attention(None, None, None, None, q_packed, k_packed, v_packed_t, q_scale, k_scale,
+                                    v_scale_t, **common)
+    elif config.method != "thrift":
         raise ValueError(f"unsupported ThriftAttention method {config.method!r}")
-
-    selected_blocks = select_cached_prefill_blocks(q, layer.key_view(), layer, config,
-                                                   real_q_len=cache.prefill_real_seq_len, is_bf16=is_bf16)
-    return ext.prefill_attention(q, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale,
-                                 v_scale_t, **common)
+    else:
+        selected_blocks = select_cached_prefill_blocks(q, layer.key_view(), layer, config,
+                                                       real_q_len=cache.prefill_real_seq_len, is_bf16=is_bf16)
+        out = ext.prefill_attention(q, k_hi, v_hi, selected_blocks, q_packed, k_packed, v_packed_t, q_scale, k_scale,
+                                    v_scale_t, **common)
+    if isinstance(layer, PagedThriftAttentionCacheLayer):
+        layer._gathered = None          # the contiguous copies made for this call (the stream keeps them alive until it ran)
+    return out
 
 
 # ------------------------------------------------------------------------------------------------
