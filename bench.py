@@ -38,10 +38,11 @@ HQ, HKV, SEQ, D = 32, 8, 131072, 128
 BLOCK = 128
 METRIC = "prefill_attention_tflops_128k_top10pct_nvfp4"
 FP4_TO_BF16_PEAK_RATIO = 4.0  # dense FP4 : dense bf16 tensor peak on B200 (9 : 2.25 PFLOP/s nominal)
-# DRAM bytes of one prefill_kernel launch on the small profiler case (1 x 16q/4kv x 8192 x 128, 2.79e11 algorithmic
-# FLOP; dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture summarised under profiles/); scaled to a
-# launch of the timed workload by the FLOPs it processes (K/V re-reads grow with the q-tile count like the FLOPs).
-SMALL_CASE_DRAM_BYTES, SMALL_CASE_FLOPS = 65.0e6, 2.79e11
+# DRAM bytes of one prefill_kernel launch over all 32 q heads of the timed workload: dram__bytes_read.sum (4.23 GB) +
+# dram__bytes_write.sum (1.31 GB) of a one-pass ncu capture of this very command (summarised under profiles/).  A rank
+# of an N-GPU run, a q-head chunk or a KV-head group launch processes a share of the heads and moves that share of
+# the bytes (every head's work is the same), so the figure is scaled by the FLOPs of the launch.
+BENCH_DRAM_BYTES, BENCH_FLOPS = 5.54e9, 1.4093e14
 
 
 def algorithmic_flops(hq: int, seq: int, d: int, block: int) -> float:
@@ -503,7 +504,7 @@ def run_ours(args) -> dict:
         per_rank_flops = total_flops / world
         achieved = per_rank_flops / (attn_ms.item() * 1e-3) / 1e12
         launches_per_kernel = len(chunks)
-        traffic = SMALL_CASE_DRAM_BYTES * (per_rank_flops / launches_per_kernel) / SMALL_CASE_FLOPS
+        traffic = BENCH_DRAM_BYTES * (per_rank_flops / launches_per_kernel) / BENCH_FLOPS
         metric = METRIC if headline else f"prefill_attention_tflops_128k_top{fraction * 100:g}pct_mxfp4_bf16"
         result = {
             "metric": metric, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -521,7 +522,7 @@ def run_ours(args) -> dict:
             "gpu_launches": 10 * len(chunks) * args.steps,
             "roofline": {"bound": "tensor", "kernel": "prefill_kernel (fused FP4 + f16 tcgen05 attention)",
                          "achieved": achieved, "peak": blended_peak, "unit": "TFLOP/s", "frac": achieved / blended_peak,
-                         "traffic": traffic, "traffic_note": "bytes per launch, scaled from the small-case ncu capture by FLOPs",
+                         "traffic": traffic, "traffic_note": "bytes per launch: one-pass ncu capture of this workload (all 32 q heads), scaled by the share of the heads a launch processes",
                          "kernel_ms": attn_ms.item(), "launches_per_step": launches_per_kernel,
                          "peak_source": f"{peak_src} x blended FP4/f16 mix (FP4 peak taken as {FP4_TO_BF16_PEAK_RATIO:g}x bf16; "
                                         f"16-bit FLOP share {share16:.3f})"},

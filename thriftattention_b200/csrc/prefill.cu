@@ -8,10 +8,12 @@
 // Both phases share one online softmax whose accumulator O lives in tensor memory
 // for the whole item.
 //
-// The softmax is what bounds this kernel (one ex2 per score on a unit that retires
-// 16 per cycle and SM), and a warp that runs a sub-step spends more time waiting -
-// for S to land in tensor memory, for the previous P V to finish, for its own
-// dependent instructions - than it spends in that unit.  So the sub-steps of an
+// What bounds this kernel is neither the tensor pipe (a sub-step's FP4 MMAs take ~130
+// cycles) nor the special-function unit (one ex2 per score, 512 cycles per sub-step
+// at 16 per cycle and SM; measured: removing every ex2 changes nothing) but the time
+// one sub-step takes to pass through a softmax warp: that warp spends more time
+// waiting - for S to land in tensor memory, for the previous P V to finish, for its
+// own dependent instructions - than it spends computing.  So the sub-steps of an
 // item are dealt round robin to FOUR sets of softmax warps: sub-step n of the CTA
 // belongs to set n mod 4, has its own S buffer in tensor memory (4 x 64 columns)
 // and its own P tile in shared memory, and each scheduler of the SM holds four
@@ -24,7 +26,7 @@
 //   * the row sum, which every set keeps for its own sub-steps (relative to the
 //     maximum it saw last) and which is added up once per item.
 //
-// Warp roles (640 threads): warp 0 = TMA producer (it also builds the item's
+// Warp roles (608 threads): warp 0 = TMA producer (it also builds the item's
 // sub-step list in shared memory), warp 1 = issuer of the S = Q K^T MMAs and
 // tensor-memory owner, warp 2 = issuer of the O += P V MMAs, warps 3..18 =
 // softmax (one thread per q row; warp w owns tensor-memory lanes 32*(w%4)..+31
