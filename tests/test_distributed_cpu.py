@@ -22,11 +22,37 @@ def test_head_shard_plan():
 
 
 def test_page_shard_plan_covers_every_page_once():
-    for n, w in ((2048, 8), (2047, 4), (5, 8), (64, 1)):
+    for n, w in ((2048, 8), (2047, 4), (5, 8), (64, 1), (100, 3), (700, 5), (64, 4)):
         shards = tad.plan_page_shards(n, w)
         assert shards[0].page_begin == 0 and shards[-1].page_end == n
         assert all(a.page_end == b.page_begin for a, b in zip(shards, shards[1:]))
         assert sum(s.num_pages for s in shards) == n
+        assert all(s.page_begin % 32 == 0 for s in shards if s.num_pages)       # the tie-break needs aligned starts
+    assert [s.num_pages for s in tad.plan_page_shards(2048, 8)] == [256] * 8
+    assert [(s.page_begin, s.page_end) for s in tad.plan_page_shards(100, 3)] == [(0, 32), (32, 64), (64, 100)]
+    assert [s.num_pages for s in tad.plan_page_shards(64, 4)] == [32, 0, 32, 0]   # fewer than 32 pages per rank: empty shards
+
+
+def test_local_cut_then_merge_resolves_exact_ties_like_the_global_rule():
+    """Every score equal: each shard keeps its top c by the tie-break on LOCAL ids (what the selection kernel does),
+    the merge ranks the union by the tie-break on global ids.  With shard starts at multiples of 32 that is the
+    global rule's own answer; an unaligned start (the even split of 100 pages over 3 ranks starts a shard at 33)
+    loses a page the global rule keeps."""
+    n, k = 100, 7
+    want = tad.merge_topk_candidates(torch.zeros(1, n), torch.arange(n, dtype=torch.int32).view(1, n), k)
+
+    def via_shards(bounds):
+        parts = []
+        for lo, hi in bounds:
+            m = hi - lo
+            local = tad.merge_topk_candidates(torch.zeros(1, m), torch.arange(m, dtype=torch.int32).view(1, m), min(k, m))
+            parts.append(local + lo)
+        pages = torch.cat(parts, 1)
+        return tad.merge_topk_candidates(torch.zeros(1, pages.shape[1]), pages, k)
+
+    aligned = [(s.page_begin, s.page_end) for s in tad.plan_page_shards(n, 3)]
+    assert torch.equal(via_shards(aligned), want)
+    assert not torch.equal(via_shards([(0, 33), (33, 66), (66, 100)]), want)
 
 
 def test_merge_topk_candidates_matches_global_topk_and_kernel_tie_order():

@@ -928,7 +928,18 @@ int select_decode_dispatch(const void* q, const void* ka, const void* kb, void* 
 // union with the single-GPU key (score descending, then the tie-break rank of the GLOBAL page id) gives the
 // single-GPU selection.  One CTA per row writes this shard's part of it as local page ids:
 //   out[row] = [ this shard's forced pages | -1 ... up to sink+local | pick j if it lies in this shard else -1 ]
-// Shard r owns pages [r * total / world, (r + 1) * total / world).
+// Shard r owns pages [shard_page_begin(r), shard_page_begin(r + 1)): the even split r * total / world with every
+// inner boundary moved to the nearest multiple of 32 pages.  The selection kernel cuts and orders exact ties by
+// (bit-reversed page mod 32, page div 32) of its LOCAL page ids; with shard starts that are multiples of 32 this is
+// the order of the global ids, so a tie at a shard's own cut is resolved as the single-GPU kernel resolves it.
+// (A shard may come out empty when there are fewer than 32 pages per shard.)
+__host__ __device__ inline int shard_page_begin(int r, int world, int total_pages) {
+    if (r <= 0) return 0;
+    if (r >= world) return total_pages;
+    const long long even = static_cast<long long>(r) * total_pages / world;
+    const long long aligned = (even + 16) / 32 * 32;
+    return static_cast<int>(aligned < total_pages ? aligned : total_pages);
+}
 constexpr int MERGE_CAP = 2048;
 __global__ void __launch_bounds__(256)
 merge_page_candidates_kernel(const int32_t* __restrict__ gathered, int32_t* __restrict__ out, int rows, int world,
@@ -947,7 +958,7 @@ merge_page_candidates_kernel(const int32_t* __restrict__ gathered, int32_t* __re
             const int page = base[0];
             const float score = __int_as_float(base[plane]);
             if (page >= 0 && score < FLT_MAX && score > -FLT_MAX)
-                key = seld_key(score, page + static_cast<int>(static_cast<long long>(r) * total_pages / world));
+                key = seld_key(score, page + shard_page_begin(r, world, total_pages));
         }
         keys[i] = key;
     }
@@ -962,8 +973,8 @@ merge_page_candidates_kernel(const int32_t* __restrict__ gathered, int32_t* __re
             }
         }
     __syncthreads();
-    const int begin = static_cast<int>(static_cast<long long>(rank) * total_pages / world);
-    const int end = static_cast<int>(static_cast<long long>(rank + 1) * total_pages / world);
+    const int begin = shard_page_begin(rank, world, total_pages);
+    const int end = shard_page_begin(rank + 1, world, total_pages);
     const int out_width = sink + local + top_k;
     int32_t* orow = out + static_cast<long long>(row) * out_width;
     const int32_t* mine = gathered + static_cast<long long>(rank) * 2 * plane + static_cast<long long>(row) * width;

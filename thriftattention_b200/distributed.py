@@ -102,16 +102,30 @@ class PageShard:
         return self.page_end - self.page_begin
 
 
+def _shard_page_begin(r: int, world: int, num_pages: int) -> int:
+    """Start of shard ``r``: the even split ``r * n / N`` with every inner boundary moved to the nearest multiple of
+    32 pages (the rule of ``merge_page_candidates``).  The selection kernel orders exact ties by (bit-reversed page
+    mod 32, page div 32) of its LOCAL page ids; a shard start that is a multiple of 32 makes that the order of the
+    global ids, so a tie at a shard's own cut is resolved as the single-GPU kernel resolves it."""
+    if r <= 0:
+        return 0
+    if r >= world:
+        return num_pages
+    return min((r * num_pages // world + 16) // 32 * 32, num_pages)
+
+
 def plan_page_shards(num_pages: int, world: int) -> list[PageShard]:
-    """Contiguous split of ``num_pages`` pages; the same rule as the in-kernel chains
-    (shard r covers [r*n/N, (r+1)*n/N))."""
+    """Contiguous split of ``num_pages`` pages with shard starts at multiples of 32 pages (see
+    ``_shard_page_begin``).  With fewer than about 32 pages per rank some shards are empty; they take part in the
+    exchanges with no candidates and a neutral partial."""
     if world < 1:
         raise ValueError("world must be positive")
-    return [PageShard(r, world, r * num_pages // world, (r + 1) * num_pages // world) for r in range(world)]
+    return [PageShard(r, world, _shard_page_begin(r, world, num_pages), _shard_page_begin(r + 1, world, num_pages))
+            for r in range(world)]
 
 
 def _max_shard_pages(total_pages: int, world: int) -> int:
-    return max((r + 1) * total_pages // world - r * total_pages // world for r in range(world))
+    return max(s.num_pages for s in plan_page_shards(total_pages, world))
 
 
 def _bitrev5(x: torch.Tensor) -> torch.Tensor:
@@ -190,17 +204,27 @@ def select_pages_sharded(q_grouped, k_a, k_b, *, shard: PageShard, total_pages: 
     send_width = min(n_sink, _max_shard_pages(total_pages, shard.world)) + \
         min(total_pages - local_lo, _max_shard_pages(total_pages, shard.world)) + \
         min(k_glob, _max_shard_pages(total_pages, shard.world))
+    if shard.page_begin % 32 and shard.num_pages:
+        raise ValueError("a KV-sequence shard must start at a multiple of 32 pages (use plan_page_shards)")
     if q_grouped.is_cuda and world * send_width <= 2048:
         # one buffer, one all-gather, one merge kernel
         buf = torch.empty(2, rows, send_width, dtype=torch.int32, device=dev)
-        ext.select_decode_blocks(q_grouped, k_a, k_b, cand, n_local, q_grouped.dtype == torch.bfloat16, sink=my_sink,
-                                 local=my_local, out=buf[0], return_scores=True, scores_out=buf[1].view(torch.float32),
-                                 row_width=send_width)
+        if n_local == 0:
+            buf[0].fill_(-1)                                            # an empty shard: no candidates
+            buf[1].view(torch.float32).fill_(-torch.finfo(torch.float32).max)
+        else:
+            ext.select_decode_blocks(q_grouped, k_a, k_b, cand, n_local, q_grouped.dtype == torch.bfloat16, sink=my_sink,
+                                     local=my_local, out=buf[0], return_scores=True,
+                                     scores_out=buf[1].view(torch.float32), row_width=send_width)
         gathered = _all_gather_stack(buf, group) if world > 1 else buf.unsqueeze(0)
         return ext.merge_page_candidates(gathered.contiguous(), rank=shard.rank, total_pages=total_pages, top_k=top_k,
                                          sink=sink, local=local)
-    sel, scores = ext.select_decode_blocks(q_grouped, k_a, k_b, cand, n_local, q_grouped.dtype == torch.bfloat16,
-                                           sink=my_sink, local=my_local, return_scores=True)
+    if n_local == 0:
+        sel = torch.full((rows, 0), -1, dtype=torch.int32, device=dev)
+        scores = torch.zeros(rows, 0, dtype=torch.float32, device=dev)
+    else:
+        sel, scores = ext.select_decode_blocks(q_grouped, k_a, k_b, cand, n_local, q_grouped.dtype == torch.bfloat16,
+                                               sink=my_sink, local=my_local, return_scores=True)
     forced = sel[:, : my_sink + my_local]
     c_pages = sel[:, my_sink + my_local: my_sink + my_local + cand]
     c_scores = scores[:, my_sink + my_local: my_sink + my_local + cand]
@@ -240,7 +264,10 @@ def decode_kv_sharded(q, k_local, v_local, *, shard: PageShard, total_pages: int
     q_grouped = q.reshape(b, hkv, hq // hkv, d).contiguous()
     k_local, v_local = k_local.contiguous(), v_local.contiguous()
     # 1. local page statistics, 2. kernel-scored candidates + exchange, 3. identical global selection everywhere
-    if selection == "quest":
+    empty = shard.num_pages == 0
+    if empty:
+        k_a = k_b = None
+    elif selection == "quest":
         _, k_a, k_b = ext.block_stats(k_local, 64, minmax=True)
     else:
         k_a, _, _ = ext.block_stats(k_local, 64, mean=True)
@@ -248,14 +275,17 @@ def decode_kv_sharded(q, k_local, v_local, *, shard: PageShard, total_pages: int
     local_sel = select_pages_sharded(q_grouped, k_a, k_b, shard=shard, total_pages=total_pages, top_k=top_k,
                                      sink=sink_blocks, local=local_blocks, group=group)
     # 4. local split-KV attention -> partials, 5. exchange + merge
-    quant = getattr(ext, f"{quant_format}_quantize")
-    quant_t = getattr(ext, f"{quant_format}_quantize_transposed")
-    q4, qs = quant(q_grouped, is_bf16)
-    k4, ks = quant(k_local, is_bf16)
-    v4, vs = quant_t(v_local, is_bf16)
+    run_decode = None                    # an empty shard contributes a neutral partial
+    if not empty:
+        quant = getattr(ext, f"{quant_format}_quantize")
+        quant_t = getattr(ext, f"{quant_format}_quantize_transposed")
+        q4, qs = quant(q_grouped, is_bf16)
+        k4, ks = quant(k_local, is_bf16)
+        v4, vs = quant_t(v_local, is_bf16)
+        run_decode = lambda **kw: ext.decode_attention(q_grouped, k_local, v_local, local_sel, q4, k4, v4, qs, ks, vs,  # noqa: E731
+                                                       is_mx=is_mx, is_bf16=is_bf16, allow_padded_selection=True, **kw)
     out = decode_partials_exchange_merge(
-        lambda **kw: ext.decode_attention(q_grouped, k_local, v_local, local_sel, q4, k4, v4, qs, ks, vs, is_mx=is_mx,
-                                          is_bf16=is_bf16, allow_padded_selection=True, **kw),
+        run_decode,
         heads=b * hkv, group_size=hq // hkv, head_dim=d, shard=shard, total_pages=total_pages, num_splits=num_splits,
         is_mx=is_mx, is_bf16=is_bf16, device=q.device, group=group)
     return out.reshape(b, hq, 1, d)
@@ -267,7 +297,8 @@ def decode_partials_exchange_merge(run_decode, *, heads: int, group_size: int, h
     buffer, LSE merge on every rank.
 
     ``run_decode(num_splits=, return_partials=True)`` launches the local decode kernel and returns
-    ``(out, part_o, part_ml)``; every rank may use its own chain count.  Returns ``[heads, group_size, head_dim]``."""
+    ``(out, part_o, part_ml)``; every rank may use its own chain count.  ``run_decode=None`` (a rank without pages)
+    contributes the neutral partial o = 0, m = -FLT_MAX, l = 0.  Returns ``[heads, group_size, head_dim]``."""
     from thriftattention_b200._extension import get_extension
 
     ext = get_extension()
@@ -278,8 +309,12 @@ def decode_partials_exchange_merge(run_decode, *, heads: int, group_size: int, h
     flat = torch.empty(n_o + n_ml, dtype=torch.float32, device=device)
     mine_o = flat[:n_o].view(heads, 1, group_size, head_dim)
     mine_ml = flat[n_o:].view(heads, 1, group_size, 2)
-    _, part_o, part_ml = run_decode(num_splits=num_splits, return_partials=True)
-    ext.reduce_decode_partials(part_o, part_ml, out=(mine_o, mine_ml))
+    if run_decode is None:
+        flat.zero_()
+        mine_ml[..., 0] = -torch.finfo(torch.float32).max
+    else:
+        _, part_o, part_ml = run_decode(num_splits=num_splits, return_partials=True)
+        ext.reduce_decode_partials(part_o, part_ml, out=(mine_o, mine_ml))
     gathered = _all_gather_stack(flat, group) if world > 1 else flat.unsqueeze(0)        # [world, n_o + n_ml]
     all_o = gathered[:, :n_o].view(world, heads, 1, group_size, head_dim)
     all_ml = gathered[:, n_o:].view(world, heads, 1, group_size, 2)
