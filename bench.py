@@ -289,6 +289,22 @@ def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_g
     gq.manual_seed(99)                                                             # the query is replicated
     q = torch.empty(DEC_BATCH, HKV, DEC_GROUP, D, dtype=torch.float16, device=device).normal_(generator=gq)
     splits_local = max(1, min(_C.decode_pick_splits(DEC_BATCH * HKV, n_local), n_local))
+    # The two exchanges of a sharded step (page candidates, one partial per head: < 1 MB each) go through the library's
+    # own peer-memory kernel; TA100_BENCH_EXCHANGE=nccl keeps them on the process group's all-gather.
+    exchange, exchange_kind = None, "none (one GPU)"
+    if world > 1:
+        exchange_kind = "nccl all_gather"
+        if os.environ.get("TA100_BENCH_EXCHANGE", "peer") != "nccl":
+            try:
+                exchange = tad.PeerExchange(1 << 20, device=device)
+                exchange_kind = "peer stores over NVLink (ta100_peer_all_gather)"
+            except Exception as exc:                              # noqa: BLE001 - any refusal means the collective
+                if rank == 0:
+                    print(f"peer exchange not available ({type(exc).__name__}: {exc}); using NCCL", file=sys.stderr)
+        ready = torch.tensor([1 if exchange is not None else 0], device=device)
+        dist.all_reduce(ready, op=dist.ReduceOp.MIN)              # all ranks or none
+        if ready.item() == 0:
+            exchange, exchange_kind = None, "nccl all_gather"
 
     def step():
         q4, qs = _C.nvfp4_quantize(q)
@@ -297,12 +313,12 @@ def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_g
             return _C.decode_attention(q, k_hi, v_hi, sel, q4, k4, v4, qs, ks, vs, is_mx=False, is_bf16=False,
                                        kv_len=n_local * 64, page_table=table, allow_padded_selection=True)
         sel = tad.select_pages_sharded(q, k_min, k_max, shard=shard, total_pages=pages, top_k=top_k, sink=DEC_SINK,
-                                       local=DEC_LOCAL)
+                                       local=DEC_LOCAL, exchange=exchange)
         return tad.decode_partials_exchange_merge(
             lambda **kw: _C.decode_attention(q, k_hi, v_hi, sel, q4, k4, v4, qs, ks, vs, is_mx=False, is_bf16=False,
                                              kv_len=n_local * 64, page_table=table, allow_padded_selection=True, **kw),
             heads=DEC_BATCH * HKV, group_size=DEC_GROUP, head_dim=D, shard=shard, total_pages=pages, num_splits=0,
-            is_mx=False, is_bf16=False, device=device)
+            is_mx=False, is_bf16=False, device=device, exchange=exchange)
 
     def barrier():
         if world > 1:
@@ -354,6 +370,8 @@ def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_g
         marks[i + 1].record()
     barrier()
     _C.decode_status()
+    if exchange is not None:
+        exchange.check()
     per_step = [marks[i].elapsed_time(marks[i + 1]) for i in range(n_steps)]
     ms = torch.tensor([marks[0].elapsed_time(marks[-1]) / n_steps], device=device, dtype=torch.float64)
     if world > 1:
@@ -370,7 +388,7 @@ def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_g
     return {"us_per_step": ms.item() * 1e3, "value": gbs, "unit": "GB/s", "bytes_per_step": step_bytes,
             "frac_of_hbm_peak": gbs / (hbm_gbs * world), "hbm_peak_gbs_per_gpu": hbm_gbs,
             "us_per_step_rank0": {k: (v * 1e3 if k != "n" else v) for k, v in stats.items()},
-            "check": check,
+            "check": check, "exchange": exchange_kind,
             "workload": f"paged decode {DEC_BATCH} seq x {DEC_SEQ} tokens, {HQ}q/{HKV}kv x {D}, NVFP4 + fp16 shadow, Quest "
                         f"{top_k} + {DEC_SINK} sink + {DEC_LOCAL} recent of {pages} pages in 16 bits; step = quantise q + "
                         f"select + attend + merge; KV sequence split over {world} GPU(s)",

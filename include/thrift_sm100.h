@@ -299,6 +299,35 @@ int ta100_decode_attention_static(const void* q_hi, const void* k_hi, const void
 int ta100_decode_status(void* stream);
 
 /*
+ * All-gather of a small per-rank buffer over NVLink peer memory in one kernel launch per rank - the exchange step of
+ * the KV-sequence-sharded decode (page candidates; one (o, m, l) partial per head), where a library collective is
+ * pure latency.  One process per GPU:
+ *   ta100_peer_exchange_create   allocates this rank's region for `world` (<= 8) ranks x slot_bytes (a multiple of
+ *                                16) and returns its 64-byte CUDA IPC handle; the ranks exchange the handles by any
+ *                                means (e.g. an all-gather of bytes) and
+ *   ta100_peer_exchange_open     map every peer's region (close / destroy undo the two).
+ *   ta100_peer_all_gather        src [bytes] (<= slot_bytes, multiple of 16) of every rank -> out [world, bytes] on
+ *                                every rank.  regions = host array of `world` device pointers, index = rank, own
+ *                                region included.  The kernel stores src into slot `rank` of every region (plain
+ *                                16-byte peer stores; no multicast, no loads from peer memory), publishes a flag on
+ *                                every peer, waits with a cycle budget for the flags of all ranks in its own region
+ *                                and copies the gathered rows to out.  The step counter lives in the region, so the
+ *                                launch has the same arguments every step and replays from a CUDA graph.  Every rank
+ *                                must call it the same number of times; the kernels of the ranks wait for each
+ *                                other, so each rank needs a GPU of its own.
+ *   ta100_peer_exchange_status   synchronises and returns TA100_ERR_DEVICE_TIMEOUT if a wait ran out (a peer never
+ *                                arrived: out then holds zeros), clearing the mark.
+ * No counterpart in the reference, which is single-GPU.
+ */
+int ta100_peer_exchange_create(int world, long long slot_bytes, void** region, unsigned char* handle64);
+int ta100_peer_exchange_open(const unsigned char* handle64, void** region);
+int ta100_peer_exchange_close(void* region);
+int ta100_peer_exchange_destroy(void* region);
+int ta100_peer_all_gather(const void* src, void* out, long long bytes, long long slot_bytes, int world, int rank,
+                          void* const* regions, void* stream);
+int ta100_peer_exchange_status(void* region, int world, long long slot_bytes, void* stream);
+
+/*
  * Log-sum-exp merge of decode partials from `shards` producers (e.g. GPUs that each hold a slice
  * of the KV sequence): part_o [shards, flat_kv_heads, splits, group, D], part_ml [.., 2] ->
  * out [flat_kv_heads, group, D].  shard_stride_o / shard_stride_ml: floats between consecutive shards (0 = densely

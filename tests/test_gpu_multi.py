@@ -1,5 +1,6 @@
 """Two-GPU tests (skipped on a single-GPU machine): head-sharded prefill and KV-sequence-sharded
-decode over NCCL, checked against the CPU oracle.  NVLS is switched off for the test processes."""
+decode over NCCL, checked against the CPU oracle, and the library's own peer-memory all-gather against the
+collective.  NVLS is switched off for the test processes."""
 import os
 import socket
 
@@ -71,6 +72,40 @@ def _worker(rank, world, port, results):
         err = (out_d.float().cpu() - ref_d.float()).abs()
         res["decode"] = err.max().item() <= 2e-3 and err.mean().item() <= 2e-4
         res["decode_err"] = err.max().item()
+        # ---- the library's own all-gather over peer memory: equals the collective's, step after step (both parities of
+        #      its double buffer, payloads of different sizes), also when replayed from a CUDA graph; and the sharded
+        #      decode through it returns the same bytes as through NCCL ----
+        ex = tad.PeerExchange(1 << 16, device=dev)
+        same = True
+        for step in range(5):
+            x = torch.full((3, 257 + step, 4), float(rank * 100 + step), device=dev) + torch.arange(4, device=dev)
+            x = x[:, : 256 + 4 * (step % 2)].contiguous()
+            want = tad._all_gather_stack(x)
+            got = ex.all_gather(x)
+            same = same and got.shape == want.shape and bool(torch.equal(got, want))
+        xg = torch.zeros(64, 4, device=dev)
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            ex.all_gather(xg)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        with torch.cuda.graph(graph):
+            yg = ex.all_gather(xg)
+        for step in range(4):
+            xg.fill_(float(10 * step + rank))
+            graph.replay()
+            torch.cuda.synchronize(dev)
+            same = same and bool((yg[0] == 10 * step).all()) and bool((yg[1] == 10 * step + 1).all())
+        res["peer_all_gather"] = same
+        out_p = tad.decode_kv_sharded(qd.to(dev), kd[:, :, lo:hi].contiguous().to(dev), vd[:, :, lo:hi].contiguous().to(dev),
+                                      shard=shard, total_pages=64, top_k=6, num_splits=splits, sink_blocks=1,
+                                      local_blocks=2, exchange=ex)
+        res["decode_through_peer_exchange"] = bool(torch.equal(out_p, out_d))
+        ex.check()
+        ex.close()
         results.put((rank, res))
     except Exception as exc:
         results.put((rank, repr(exc)))
@@ -97,3 +132,4 @@ def test_two_gpu_prefill_and_decode():
         assert results[rank]["prefill"], results[rank]
         assert results[rank]["selection_exact"] and results[rank]["forced_exact"], results[rank]
         assert results[rank]["decode"], results[rank]
+        assert results[rank]["peer_all_gather"] and results[rank]["decode_through_peer_exchange"], results[rank]

@@ -23,6 +23,12 @@ SIGNATURES = {
     "ta100_block_stats": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_vp]),
     "ta100_cache_append": (_c_int, [_c_vp] * 11 + [_c_ll] + [_c_int] * 9 + [_c_vp]),
     "ta100_cache_append_paged": (_c_int, [_c_vp] * 12 + [_c_int] * 13 + [_c_vp]),
+    "ta100_peer_exchange_create": (_c_int, [_c_int, _c_ll, ctypes.POINTER(_c_vp), ctypes.c_char_p]),
+    "ta100_peer_exchange_open": (_c_int, [ctypes.c_char_p, ctypes.POINTER(_c_vp)]),
+    "ta100_peer_exchange_close": (_c_int, [_c_vp]),
+    "ta100_peer_exchange_destroy": (_c_int, [_c_vp]),
+    "ta100_peer_all_gather": (_c_int, [_c_vp, _c_vp, _c_ll, _c_ll, _c_int, _c_int, ctypes.POINTER(_c_vp), _c_vp]),
+    "ta100_peer_exchange_status": (_c_int, [_c_vp, _c_int, _c_ll, _c_vp]),
     "ta100_select_prefill": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp] + [_c_int] * 11 + [_c_vp]),
     "ta100_select_decode": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp] + [_c_int] * 11 + [_c_vp]),
     "ta100_local_block_topk": (_c_int, [_c_vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_vp]),

@@ -35,6 +35,13 @@ size_t decode_static_scratch_bytes();
 int decode_static_dispatch(const void*, const void*, const void*, const void*, int, const void*, const void*, const void*,
                            const void*, const void*, const void*, const void*, int, int, void*, int, int, int, int, int, int, int,
                            int, int, cudaStream_t);
+size_t peer_exchange_region_bytes(int, long long);
+int peer_exchange_create(int, long long, void**, unsigned char*);
+int peer_exchange_open(const unsigned char*, void**);
+int peer_exchange_close(void*);
+int peer_exchange_destroy(void*);
+int peer_all_gather_dispatch(const void*, void*, long long, long long, int, int, void* const*, cudaStream_t);
+int peer_exchange_status(void*, int, long long, cudaStream_t);
 int cache_append_dispatch(const void*, const void*, void*, void*, void*, void*, void*, void*, void*, void*, void*, long long,
                           int, int, int, int, int, int, int, int, int, const void*, int, int, int, int, cudaStream_t);
 }  // namespace ta100
@@ -220,6 +227,20 @@ int ta100_cached_decode_step_paged(const void* q, void* q4, void* qs, const void
 }
 
 int ta100_decode_status(void* stream) { return decode_status(S(stream)); }
+
+int ta100_peer_exchange_create(int world, long long slot_bytes, void** region, unsigned char* handle64) {
+    return peer_exchange_create(world, slot_bytes, region, handle64);
+}
+int ta100_peer_exchange_open(const unsigned char* handle64, void** region) { return peer_exchange_open(handle64, region); }
+int ta100_peer_exchange_close(void* region) { return peer_exchange_close(region); }
+int ta100_peer_exchange_destroy(void* region) { return peer_exchange_destroy(region); }
+int ta100_peer_all_gather(const void* src, void* out, long long bytes, long long slot_bytes, int world, int rank,
+                          void* const* regions, void* stream) {
+    return peer_all_gather_dispatch(src, out, bytes, slot_bytes, world, rank, regions, S(stream));
+}
+int ta100_peer_exchange_status(void* region, int world, long long slot_bytes, void* stream) {
+    return peer_exchange_status(region, world, slot_bytes, S(stream));
+}
 
 int ta100_merge_partials(const void* part_o, const void* part_ml, void* out, int shards, long long shard_stride_o,
                          long long shard_stride_ml, long long flat_kv_heads, int splits, int group, int head_dim,

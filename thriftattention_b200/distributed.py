@@ -23,8 +23,103 @@ import torch
 import torch.distributed as dist
 
 
-def _all_gather_stack(x: torch.Tensor, group=None) -> torch.Tensor:
-    """``all_gather`` of equally shaped tensors, stacked on a new leading rank dimension."""
+class PeerExchange:
+    """All-gather of small per-rank buffers by this library's own kernel over NVLink peer memory
+    (``ta100_peer_all_gather``): every rank stores its rows straight into every peer's region and waits, with a
+    budget, for the peers' flags - one launch per rank and exchange instead of a latency-bound library collective.
+
+    Collective constructor (every rank of ``group`` calls it): allocates this rank's region for payloads of up to
+    ``max_bytes`` per rank, exchanges the CUDA IPC handles through ``torch.distributed`` and maps the peers' regions.
+    One process per GPU; the ranks' kernels wait for each other.  ``all_gather`` must be called the same number of
+    times on every rank; it is a plain kernel launch and can be captured in a CUDA graph."""
+
+    def __init__(self, max_bytes: int, group=None, device=None) -> None:
+        import ctypes
+
+        from thriftattention_b200 import _lib
+
+        self._lib = _lib.load()
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("PeerExchange serves at most 8 ranks")
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.slot_bytes = (int(max_bytes) + 15) // 16 * 16
+        own = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            _lib.check(self._lib.ta100_peer_exchange_create(self.world, self.slot_bytes, ctypes.byref(own), handle),
+                       "peer_exchange_create")
+        self._own = own
+        mine = torch.frombuffer(bytearray(handle.raw), dtype=torch.uint8).to(self.device)
+        handles = torch.empty(self.world, 64, dtype=torch.uint8, device=self.device)
+        dist.all_gather_into_tensor(handles.view(-1), mine, group=group)
+        handles = handles.cpu()
+        self._opened: list = []
+        regions = (ctypes.c_void_p * self.world)()
+        for r in range(self.world):
+            if r == self.rank:
+                regions[r] = own.value
+                continue
+            ptr = ctypes.c_void_p()
+            with torch.cuda.device(self.device):
+                _lib.check(self._lib.ta100_peer_exchange_open(bytes(handles[r].tolist()), ctypes.byref(ptr)),
+                           "peer_exchange_open")
+            regions[r] = ptr.value
+            self._opened.append(ptr)
+        self._regions = regions
+        dist.barrier(group=group)            # every region is mapped everywhere before the first store
+
+    def all_gather(self, x: torch.Tensor) -> torch.Tensor:
+        """``x`` (contiguous, CUDA, a multiple of 16 bytes, the same shape on every rank) -> ``[world, *x.shape]``."""
+        import ctypes
+
+        from thriftattention_b200 import _lib
+
+        nbytes = x.numel() * x.element_size()
+        if not (x.is_cuda and x.is_contiguous()) or nbytes % 16 or nbytes > self.slot_bytes or nbytes == 0:
+            raise ValueError("PeerExchange.all_gather needs a contiguous CUDA tensor of 16..slot_bytes bytes (multiple of 16)")
+        out = torch.empty((self.world, *x.shape), dtype=x.dtype, device=x.device)
+        with torch.cuda.device(x.device):
+            rc = self._lib.ta100_peer_all_gather(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()), nbytes,
+                                                 self.slot_bytes, self.world, self.rank, self._regions,
+                                                 ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream))
+        _lib.check(rc, "peer_all_gather")
+        return out
+
+    def check(self) -> None:
+        """Synchronises; raises if a wait for a peer ran out since the last check."""
+        import ctypes
+
+        from thriftattention_b200 import _lib
+
+        with torch.cuda.device(self.device):
+            rc = self._lib.ta100_peer_exchange_status(self._own, self.world, self.slot_bytes,
+                                                      ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        _lib.check(rc, "peer_all_gather (device)")
+
+    def close(self) -> None:
+        """Collective: unmaps the peers' regions and frees this rank's (after every rank is done with them)."""
+        if self._own is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        with torch.cuda.device(self.device):
+            for ptr in self._opened:
+                self._lib.ta100_peer_exchange_close(ptr)
+            dist.barrier(group=self.group)
+            self._lib.ta100_peer_exchange_destroy(self._own)
+        self._own, self._opened = None, []
+
+
+def _all_gather_stack(x: torch.Tensor, group=None, exchange: "PeerExchange | None" = None) -> torch.Tensor:
+    """``all_gather`` of equally shaped tensors, stacked on a new leading rank dimension (through ``exchange``'s
+    peer-memory kernel when one is given and the tensor fits it, else the process group's collective)."""
+    if exchange is not None and x.is_cuda and x.is_contiguous():
+        nbytes = x.numel() * x.element_size()
+        if 0 < nbytes <= exchange.slot_bytes and nbytes % 16 == 0:
+            return exchange.all_gather(x)
     world = dist.get_world_size(group)
     x = x.contiguous()
     flat = torch.empty((world * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
@@ -177,7 +272,7 @@ def exchange_partials(part_o: torch.Tensor, part_ml: torch.Tensor, group=None):
 
 
 def select_pages_sharded(q_grouped, k_a, k_b, *, shard: PageShard, total_pages: int, top_k: int, sink: int = 0,
-                         local: int = 0, group=None) -> torch.Tensor:
+                         local: int = 0, group=None, exchange: "PeerExchange | None" = None) -> torch.Tensor:
     """Global page selection when every rank holds the statistics of its own pages only.
 
     ``k_a`` / ``k_b`` ``[B, Hkv, shard.num_pages(+), D]``: block means (``k_b is None``) or Quest minima / maxima
@@ -216,7 +311,7 @@ def select_pages_sharded(q_grouped, k_a, k_b, *, shard: PageShard, total_pages: 
             ext.select_decode_blocks(q_grouped, k_a, k_b, cand, n_local, q_grouped.dtype == torch.bfloat16, sink=my_sink,
                                      local=my_local, out=buf[0], return_scores=True,
                                      scores_out=buf[1].view(torch.float32), row_width=send_width)
-        gathered = _all_gather_stack(buf, group) if world > 1 else buf.unsqueeze(0)
+        gathered = _all_gather_stack(buf, group, exchange) if world > 1 else buf.unsqueeze(0)
         return ext.merge_page_candidates(gathered.contiguous(), rank=shard.rank, total_pages=total_pages, top_k=top_k,
                                          sink=sink, local=local)
     if n_local == 0:
@@ -246,7 +341,7 @@ def select_pages_sharded(q_grouped, k_a, k_b, *, shard: PageShard, total_pages: 
 
 def decode_kv_sharded(q, k_local, v_local, *, shard: PageShard, total_pages: int, top_k: int, quant_format="nvfp4",
                       num_splits: int = 0, group=None, selection: str = "quest", sink_blocks: int = 0,
-                      local_blocks: int = 0):
+                      local_blocks: int = 0, exchange: "PeerExchange | None" = None):
     """One decode step with the KV sequence sharded over ranks.
 
     ``q`` ``[B, Hq, 1, D]`` replicated; ``k_local`` / ``v_local`` ``[B, Hkv, shard.num_pages*64, D]`` are this
@@ -273,7 +368,7 @@ def decode_kv_sharded(q, k_local, v_local, *, shard: PageShard, total_pages: int
         k_a, _, _ = ext.block_stats(k_local, 64, mean=True)
         k_b = None
     local_sel = select_pages_sharded(q_grouped, k_a, k_b, shard=shard, total_pages=total_pages, top_k=top_k,
-                                     sink=sink_blocks, local=local_blocks, group=group)
+                                     sink=sink_blocks, local=local_blocks, group=group, exchange=exchange)
     # 4. local split-KV attention -> partials, 5. exchange + merge
     run_decode = None                    # an empty shard contributes a neutral partial
     if not empty:
@@ -287,12 +382,13 @@ def decode_kv_sharded(q, k_local, v_local, *, shard: PageShard, total_pages: int
     out = decode_partials_exchange_merge(
         run_decode,
         heads=b * hkv, group_size=hq // hkv, head_dim=d, shard=shard, total_pages=total_pages, num_splits=num_splits,
-        is_mx=is_mx, is_bf16=is_bf16, device=q.device, group=group)
+        is_mx=is_mx, is_bf16=is_bf16, device=q.device, group=group, exchange=exchange)
     return out.reshape(b, hq, 1, d)
 
 
 def decode_partials_exchange_merge(run_decode, *, heads: int, group_size: int, head_dim: int, shard: PageShard,
-                                   total_pages: int, num_splits: int, is_mx: bool, is_bf16: bool, device, group=None):
+                                   total_pages: int, num_splits: int, is_mx: bool, is_bf16: bool, device, group=None,
+                                   exchange: "PeerExchange | None" = None):
     """Local split-KV attention, the rank's chains reduced to one partial per head, ONE ``all_gather`` of that
     buffer, LSE merge on every rank.
 
@@ -315,7 +411,7 @@ def decode_partials_exchange_merge(run_decode, *, heads: int, group_size: int, h
     else:
         _, part_o, part_ml = run_decode(num_splits=num_splits, return_partials=True)
         ext.reduce_decode_partials(part_o, part_ml, out=(mine_o, mine_ml))
-    gathered = _all_gather_stack(flat, group) if world > 1 else flat.unsqueeze(0)        # [world, n_o + n_ml]
+    gathered = _all_gather_stack(flat, group, exchange) if world > 1 else flat.unsqueeze(0)   # [world, n_o + n_ml]
     all_o = gathered[:, :n_o].view(world, heads, 1, group_size, head_dim)
     all_ml = gathered[:, n_o:].view(world, heads, 1, group_size, 2)
     return ext.merge_decode_partials(all_o, all_ml, is_mx=is_mx, is_bf16=is_bf16)
