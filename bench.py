@@ -289,12 +289,12 @@ def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_g
     gq.manual_seed(99)                                                             # the query is replicated
     q = torch.empty(DEC_BATCH, HKV, DEC_GROUP, D, dtype=torch.float16, device=device).normal_(generator=gq)
     splits_local = max(1, min(_C.decode_pick_splits(DEC_BATCH * HKV, n_local), n_local))
-    # The two exchanges of a sharded step (page candidates, one partial per head: < 1 MB each) go through the library's
-    # own peer-memory kernel; TA100_BENCH_EXCHANGE=nccl keeps them on the process group's all-gather.
+    # The two exchanges of a sharded step (page candidates, one partial per head: < 1 MB each) go through the process
+    # group's all-gather, or with TA100_BENCH_EXCHANGE=peer through the library's own peer-memory kernel.
     exchange, exchange_kind = None, "none (one GPU)"
     if world > 1:
         exchange_kind = "nccl all_gather"
-        if os.environ.get("TA100_BENCH_EXCHANGE", "peer") != "nccl":
+        if os.environ.get("TA100_BENCH_EXCHANGE", "nccl") == "peer":
             try:
                 exchange = tad.PeerExchange(1 << 20, device=device)
                 exchange_kind = "peer stores over NVLink (ta100_peer_all_gather)"
