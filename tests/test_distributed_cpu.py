@@ -124,3 +124,49 @@ def test_two_rank_exchange_over_gloo():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert sorted(results) == [(0, True, True, True), (1, True, True, True)]
+
+
+def _silent_peer_worker(rank, world, port, q):
+    """Rank 1 joins the group and then never takes part in the exchange; rank 0 must get an error, not a hang."""
+    import datetime
+    import time
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    try:
+        if rank == 1:
+            time.sleep(8)                      # alive, but silent, for longer than the group's timeout
+            q.put((rank, "silent"))
+            return
+        po = torch.zeros(2, 1, 4, 8)
+        pml = torch.zeros(2, 1, 4, 2)
+        t0 = time.time()
+        try:
+            tad.exchange_partials(po, pml)
+            q.put((rank, "returned"))
+        except Exception as exc:               # the collective gives up after the group's timeout
+            q.put((rank, f"error after {time.time() - t0:.0f}s: {type(exc).__name__}"))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:                      # the group is broken on the rank that timed out
+            pass
+
+
+def test_a_rank_that_never_sends_its_partials_is_an_error_on_its_peer_not_a_hang():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_silent_peer_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        results = dict(q.get(timeout=60) for _ in procs)
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    assert results[1] == "silent"
+    assert results[0].startswith("error after"), results[0]
