@@ -325,6 +325,55 @@ def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_g
             dist.barrier()
         torch.cuda.synchronize()
 
+    def time_pieces(reps: int = 10) -> dict:
+        """The sharded step launched piece by piece (eagerly, so launch gaps are inside the figures) with CUDA events
+        between the pieces: median microseconds per piece on this rank."""
+        n_sink = min(DEC_SINK, pages)
+        local_lo = max(pages - DEC_LOCAL, n_sink)
+        my_sink = max(0, min(n_sink, shard.page_end) - shard.page_begin)
+        my_local = max(0, shard.page_end - max(local_lo, shard.page_begin))
+        k_glob = min(top_k, max(pages - n_sink - (pages - local_lo), 0))
+        cand = min(k_glob, max(n_local - my_sink - my_local, 0))
+        biggest = max(sh.num_pages for sh in tad.plan_page_shards(pages, world))
+        width = min(n_sink, biggest) + min(pages - local_lo, biggest) + min(k_glob, biggest)
+        rows = heads = DEC_BATCH * HKV
+        n_o, n_ml = heads * DEC_GROUP * D, heads * DEC_GROUP * 2
+        names = ["quantise_q", "select", "gather1", "merge_candidates", "attend", "reduce", "gather2", "merge"]
+        samples = {n: [] for n in names}
+        for _ in range(reps + 2):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
+            if world > 1:
+                dist.barrier()
+            ev[0].record()
+            q4, qs = _C.nvfp4_quantize(q)
+            ev[1].record()
+            buf = torch.empty(2, rows, width, dtype=torch.int32, device=device)
+            _C.select_decode_blocks(q, k_min, k_max, cand, n_local, False, sink=my_sink, local=my_local, out=buf[0],
+                                    return_scores=True, scores_out=buf[1].view(torch.float32), row_width=width)
+            ev[2].record()
+            gathered = tad._all_gather_stack(buf, None, exchange)
+            ev[3].record()
+            sel = _C.merge_page_candidates(gathered.contiguous(), rank=rank, total_pages=pages, top_k=top_k, sink=DEC_SINK,
+                                           local=DEC_LOCAL)
+            ev[4].record()
+            _, part_o, part_ml = _C.decode_attention(q, k_hi, v_hi, sel, q4, k4, v4, qs, ks, vs, is_mx=False, is_bf16=False,
+                                                     kv_len=n_local * 64, page_table=table, allow_padded_selection=True,
+                                                     return_partials=True)
+            ev[5].record()
+            flat = torch.empty(n_o + n_ml, dtype=torch.float32, device=device)
+            _C.reduce_decode_partials(part_o, part_ml, out=(flat[:n_o].view(heads, 1, DEC_GROUP, D),
+                                                            flat[n_o:].view(heads, 1, DEC_GROUP, 2)))
+            ev[6].record()
+            allp = tad._all_gather_stack(flat, None, exchange)
+            ev[7].record()
+            _C.merge_decode_partials(allp[:, :n_o].view(world, heads, 1, DEC_GROUP, D),
+                                     allp[:, n_o:].view(world, heads, 1, DEC_GROUP, 2), is_mx=False, is_bf16=False)
+            ev[8].record()
+            torch.cuda.synchronize()
+            for j, n in enumerate(names):
+                samples[n].append(ev[j].elapsed_time(ev[j + 1]) * 1e3)
+        return {n: round(sorted(v[2:])[len(v[2:]) // 2], 1) for n, v in samples.items()}
+
     for _ in range(max(warmup, 3)):
         step()
     barrier()
@@ -381,6 +430,8 @@ def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_g
     barrier()
     check = check_decode_rows(out, q, k_hi, v_hi, table, world=world, rank=rank, pages=pages, top_k=top_k,
                               splits_local=splits_local)
+    pieces = time_pieces() if world > 1 else None
+    barrier()
     n16 = top_k + DEC_SINK + DEC_LOCAL
     step_bytes = DEC_BATCH * HKV * ((pages - n16) * 9216 + n16 * 32768 + pages * 512)
     gbs = step_bytes / (ms.item() * 1e-3) / 1e9
@@ -388,7 +439,7 @@ def run_decode_leg(device, world: int, rank: int, steps: int, warmup: int, hbm_g
     return {"us_per_step": ms.item() * 1e3, "value": gbs, "unit": "GB/s", "bytes_per_step": step_bytes,
             "frac_of_hbm_peak": gbs / (hbm_gbs * world), "hbm_peak_gbs_per_gpu": hbm_gbs,
             "us_per_step_rank0": {k: (v * 1e3 if k != "n" else v) for k, v in stats.items()},
-            "check": check, "exchange": exchange_kind,
+            "check": check, "exchange": exchange_kind, "pieces_us_rank0_eager": pieces,
             "workload": f"paged decode {DEC_BATCH} seq x {DEC_SEQ} tokens, {HQ}q/{HKV}kv x {D}, NVFP4 + fp16 shadow, Quest "
                         f"{top_k} + {DEC_SINK} sink + {DEC_LOCAL} recent of {pages} pages in 16 bits; step = quantise q + "
                         f"select + attend + merge; KV sequence split over {world} GPU(s)",
