@@ -548,6 +548,34 @@ def test_prefill_long_context_slice_matches_oracle(cuda_device, S, top_k_expecte
             assert err.max().item() <= FP16_MAX_ABS and err.mean().item() <= MEAN_ABS
 
 
+@pytest.mark.parametrize("fmt,dtype,d,block,hq,hkv", [("mxfp4", torch.bfloat16, 128, 128, 32, 8), ("nvfp4", torch.float16, 64, 64, 8, 8)])
+def test_prefill_long_context_slices_other_formats(cuda_device, fmt, dtype, d, block, hq, hkv):
+    """32,768 tokens in the other format / type / head size / block size combinations: bf16 + MXFP4 with 128-token
+    blocks (the long-context configuration's shape), and head_dim 64 with 64-token blocks and no query grouping (the
+    reference's acceptance shape).  Oracle rows at the start, middle and end of one head."""
+    import thriftattention_b200 as ta
+
+    S = 32768
+    g = torch.Generator(device=cuda_device).manual_seed(2)
+    q = torch.randn(1, hq, S, d, device=cuda_device, dtype=torch.float32, generator=g).to(dtype)
+    k = torch.randn(1, hkv, S, d, device=cuda_device, dtype=torch.float32, generator=g).to(dtype)
+    v = torch.randn(1, hkv, S, d, device=cuda_device, dtype=torch.float32, generator=g).to(dtype)
+    k[:, :, :, torch.tensor([1, 17, 33, 60], device=cuda_device)] *= 10
+    cfg = ta.AttentionConfig(selection="quest", fraction=0.05, block_size=block, quant_format=fmt)
+    out = ta.attention(q, k, v, config=cfg)
+    top_k = oracle.resolve_top_k(S // block, causal=True, fraction=0.05)
+    head = hq - 3
+    grp = hq // hkv
+    qh, kh, vh = q[:, head:head + 1].cpu(), k[:, head // grp:head // grp + 1].cpu(), v[:, head // grp:head // grp + 1].cpu()
+    qm, = oracle.block_stats(qh, block, ("mean",))
+    kmin, kmax = oracle.block_stats(kh, block, ("min", "max"))
+    sel = oracle.select_prefill(qm, kmin, kmax, k=top_k, causal=True)
+    for lo in (0, S // 2, S - 256):
+        ref = oracle.prefill_attention(qh, kh, vh, sel, fmt=fmt, block=block, causal=True, rows=(lo, lo + 256))
+        err = (out[0, head, lo:lo + 256].float().cpu() - ref[0, 0, lo:lo + 256].float()).abs()
+        assert err.max().item() <= _tol(dtype, ref[0, 0, lo:lo + 256]) and err.mean().item() <= MEAN_ABS
+
+
 def test_prefill_at_benchmark_size_scales_exactly_with_v(cuda_device):
     """Size-independent property at the benchmark's size (32q/8kv x 131072): V enters the result linearly and its
     block scales are floating point, so doubling V (a power of two: every scale byte moves by one exponent step,
