@@ -26,17 +26,18 @@
 //   * the row sum, which every set keeps for its own sub-steps (relative to the
 //     maximum it saw last) and which is added up once per item.
 //
-// Warp roles (608 threads): warp 0 = TMA producer (it also builds the item's
-// sub-step list in shared memory), warp 1 = issuer of the S = Q K^T MMAs and
-// tensor-memory owner, warp 2 = issuer of the O += P V MMAs, warps 3..18 =
-// softmax (one thread per q row; warp w owns tensor-memory lanes 32*(w%4)..+31
-// and belongs to set (w-3)/4).
+// Warp roles (640 threads): warp 0 = producer (bulk copies of the packed K/V records, TMA for
+// Q and the 16-bit tiles; it also builds the item's sub-step list in shared memory), warps 1
+// and 2 = issuers of the S = Q K^T MMAs (even and odd sub-steps; warp 1 owns tensor memory),
+// warp 3 = issuer of the O += P V MMAs, warps 4..19 = softmax (one thread per q row; warp w
+// owns tensor-memory lanes 32*(w%4)..+31 and belongs to set (w-4)/4).
 //
 // Every mbarrier wait is bounded; a timeout raises a CTA-wide abort flag, all
 // roles drain, tensor memory is released and a status word is set.  A parity
 // wait is only sound for a waiter that sees every phase of its barrier, so every
 // waiter here waits on each phase of the barriers it uses, also where the value
-// behind the barrier is not needed.
+// behind the barrier is not needed - or, where noted, asks only about a phase that
+// it knows to be the barrier's current or previous one.
 #include <cfloat>
 #include <climits>
 #include <type_traits>
@@ -55,15 +56,15 @@ constexpr int NSETS = 4;             // softmax warp sets = S buffers = P tiles
 constexpr int NSLOTS = 6;            // K/V ring slots
 constexpr int SLOT_BYTES = 16384;    // one FP4 sub-step (K4, V4, scale atoms) or one 16-bit K or V tile
 constexpr int REC_BYTES = 9728;      // packed FP4 record of one (KV head, sub-step): K4 4096 | K scale atoms 1024 | V4 4096 | V scale atom 512
-constexpr int REC_K_BYTES = 5120;    // its K part; the V part is the rest
 constexpr int PSET_BYTES = 16384;    // P tile of a set: 4 KB of e2m1 or 16 KB of 16-bit values
-constexpr int NUM_THREADS = 32 * (3 + 4 * NSETS);   // 608; registers are handed out to 20 warps' worth: 96 per thread
+constexpr int NUM_THREADS = 32 * (4 + 4 * NSETS);   // 640 = 20 warps: 96 registers per thread
 constexpr int SCHED_CAP = 2944;      // sub-step list entries per work item
 
 // tensor-memory columns (all 512 of the SM)
 constexpr uint32_t TM_O = 0;         // 128 columns
 constexpr uint32_t TM_S = 128;       // NSETS buffers of 64 columns
-constexpr uint32_t TM_SFA_Q = 384;   // up to 8 columns
+constexpr uint32_t TM_SFA_Q = 384;   // up to 8 columns (issuer 0's copy; issuer 1's is TM_SFA_Q1)
+constexpr uint32_t TM_SFA_Q1 = 448;
 constexpr uint32_t TM_SFA_P = 392;   // 4 columns, constant
 constexpr uint32_t TM_SFB_K = 400;   // NSETS buffers of 8 columns
 constexpr uint32_t TM_SFB_V = 432;   // NSETS buffers of 4 columns
@@ -105,7 +106,7 @@ struct Smem {
     static constexpr int SCHED = XCH + sizeof(float) * 4 * NSETS * 32 * 5;   // SCHED_CAP x u16
     static constexpr int TOTAL = SCHED + SCHED_CAP * 2;
     // inside an FP4 slot
-    static constexpr int K4 = 0, KSF = 4096, V4 = 5120, VSF = 9216;   // K part [0, REC_K_BYTES), V part behind it
+    static constexpr int K4 = 0, KSF = 4096, V4 = 5120, VSF = 9216;   // the record's layout: K4, K scale atoms, V4, V scale atom
     static_assert(Q16 % 1024 == 0 && P % 1024 == 0 && SLOTS % 1024 == 0, "swizzled tiles need 1024-byte alignment");
     static_assert(TOTAL <= 227 * 1024, "one CTA must fit the SM's shared memory");
 };
@@ -121,6 +122,7 @@ struct Bars {
     uint64_t trans[4];                                 // row sums of a row group published for the state rounding
     uint64_t lend[4];                                  // ... and for the end of the item
     int sched_n, sched_na;                             // entries; entries before the first 16-bit one
+    uint32_t slot_last[NSLOTS];                        // producer's note of who used a slot last
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -341,11 +343,12 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
 
     if (tid == 0) {
         mbar_init(smem_u32(&bars.q_full), 1);
-        mbar_init(smem_u32(&bars.q_empty), 1);
+        mbar_init(smem_u32(&bars.q_empty), 2);
         mbar_init(smem_u32(&bars.sched_full), 1);
-        mbar_init(smem_u32(&bars.sched_empty), 2 + 4 * NSETS);
+        mbar_init(smem_u32(&bars.sched_empty), 3 + 4 * NSETS);
         mbar_init(smem_u32(&bars.o_full), 1);
         for (int i = 0; i < NSLOTS; ++i) {
+            bars.slot_last[i] = 0u;
             mbar_init(smem_u32(&bars.k_full[i]), 1);
             mbar_init(smem_u32(&bars.v_full[i]), 1);
             mbar_init(smem_u32(&bars.slot_empty[i]), 1);
@@ -385,9 +388,32 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
             tma_prefetch_desc(&mapQ4);
             tma_prefetch_desc(&mapQ16); tma_prefetch_desc(&mapK16); tma_prefetch_desc(&mapV16);
         }
-        uint32_t gslot = 0;
+        uint32_t gslot = 0, gsub = 0;     // slots filled / sub-steps loaded so far by this CTA
+        uint32_t epar = 0;                // bit s: parity of the next release of slot s through slot_empty
         int n_item = 0;
         bool ok = true;
+        // A slot is free again when its last reader is done.  For an FP4 record that is the P V of its sub-step, whose
+        // completion the issuer already signals on p_free (for the softmax warps); for a 16-bit tile the issuer that
+        // read it commits slot_empty.  bars.slot_last[s] notes which: 0 = never used, bit 31 = slot_empty, else
+        // 1 + the CTA-wide index of the sub-step.  When this warp asks about the sub-step's p_free phase, the next
+        // phase of that barrier belongs to a sub-step 8 later, which is not even loaded yet: the barrier is in the
+        // phase asked for or the one after it.
+        auto wait_slot = [&](const uint32_t slot) -> bool {
+            const uint32_t last = bars.slot_last[slot];
+            if (last == 0u) return true;
+            if (last & 0x80000000u) {
+                const bool r = mbar_wait(smem_u32(&bars.slot_empty[slot]), (epar >> slot) & 1u, abortp, budget);
+                epar ^= 1u << slot;
+                return r;
+            }
+            const uint32_t u = last - 1u, set = u & (NSETS - 1), use = u / NSETS;
+            return mbar_wait(smem_u32(&bars.p_free[set][use & 1]), (use >> 1) & 1, abortp, budget);
+        };
+        auto note_slot = [&](const uint32_t slot, const uint32_t v) {
+            __syncwarp();
+            if (lane == 0) bars.slot_last[slot] = v;
+            __syncwarp();
+        };
         for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
             const ItemInfo it = decode_item(p, item);
             // ---- sub-step list (consumers must be done with the previous one) ----
@@ -416,29 +442,26 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                         tma_load_3d(sbase + L::Q16 + hf * QTILE * 128, &mapQ16, bar, hf * 64, it.t * QTILE, it.h);
             }
             // ---- K/V sub-steps ----
-            for (int i = 0; i < n && ok; ++i) {
+            for (int i = 0; i < n && ok; ++i, ++gsub) {
                 const uint32_t e = sched[i];
                 const int st = e & 0xFFF;
                 if (!(e & E_FP16)) {
                     const uint32_t slot = gslot % NSLOTS;
-                    ok = mbar_wait(smem_u32(&bars.slot_empty[slot]), ((gslot / NSLOTS) & 1) ^ 1, abortp, budget);
+                    ok = wait_slot(slot);
                     if (!ok) break;
                     if (lane == 0) {
-                        const uint32_t sa = sbase + L::SLOTS + slot * SLOT_BYTES;
-                        const uint8_t* rec = p.kv_rec + (static_cast<long long>(it.kvh) * p.nsteps_total + st) * REC_BYTES;
-                        // one contiguous record (K4 and V4 tiles already in their swizzled shared-memory order + scale
-                        // atoms), copied in two parts so that each issuer waits for its own operands only
-                        const uint32_t kbar = smem_u32(&bars.k_full[slot]), vbar = smem_u32(&bars.v_full[slot]);
-                        mbar_expect_tx(kbar, REC_K_BYTES);
-                        bulk_load(sa, rec, REC_K_BYTES, kbar);
-                        mbar_expect_tx(vbar, REC_BYTES - REC_K_BYTES);
-                        bulk_load(sa + REC_K_BYTES, rec + REC_K_BYTES, REC_BYTES - REC_K_BYTES, vbar);
+                        // one contiguous record: K4 and V4 tiles already in their swizzled shared-memory order + scale atoms
+                        const uint32_t bar = smem_u32(&bars.k_full[slot]);
+                        mbar_expect_tx(bar, REC_BYTES);
+                        bulk_load(sbase + L::SLOTS + slot * SLOT_BYTES,
+                                  p.kv_rec + (static_cast<long long>(it.kvh) * p.nsteps_total + st) * REC_BYTES, REC_BYTES, bar);
                     }
+                    note_slot(slot, gsub + 1u);
                     gslot += 1;
                 } else {
                     for (int which = 0; which < 2 && ok; ++which) {  // K tile, then V tile
                         const uint32_t slot = gslot % NSLOTS;
-                        ok = mbar_wait(smem_u32(&bars.slot_empty[slot]), ((gslot / NSLOTS) & 1) ^ 1, abortp, budget);
+                        ok = wait_slot(slot);
                         if (!ok) break;
                         if (lane == 0) {
                             const uint32_t bar = smem_u32(which ? &bars.v_full[slot] : &bars.k_full[slot]);
@@ -447,17 +470,23 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                             for (int hf = 0; hf < HALVES; ++hf)
                                 tma_load_3d(sa + hf * STEP * 128, which ? &mapV16 : &mapK16, bar, hf * 64, st * STEP, it.kvh);
                         }
+                        note_slot(slot, 0x80000000u);
                         gslot += 1;
                     }
                 }
             }
         }
-    } else if (warp == 1) {
-        // =========================== S = Q K^T issuer ===========================
-        // This warp (and the next) is a serial instruction stream that every sub-step of the CTA passes through, so its
-        // loop is kept lean: ring position and phase are running counters, all operands are warp-uniform, and the
-        // tcgen05 instructions of a sub-step are issued together by one elected lane.
-        uint32_t gsub = 0;                // sub-steps consumed so far by this CTA
+    } else if (warp == 1 || warp == 2) {
+        // =========================== S = Q K^T issuers ===========================
+        // An issuer is a serial instruction stream that its sub-steps pass through one by one, and between the
+        // softmax warps of its scheduler it gets an issue slot only every few cycles: a loop of some fifty
+        // instructions bounds the whole CTA.  So there are two of these (S buffers are independent of each other):
+        // issuer w takes the sub-steps whose CTA-wide index is w modulo 2 and walks past the others, keeping only the
+        // ring position and the K-fill parities up to date.  Each has its own copy of Q's scale factors in tensor
+        // memory, because tcgen05.cp and tcgen05.mma are ordered only within one thread.
+        const uint32_t me = warp - 1;
+        const uint32_t tm_sfa_q = tmem + (me ? TM_SFA_Q1 : TM_SFA_Q);
+        uint32_t gsub = 0;                // sub-steps walked so far by this CTA
         uint32_t slot = 0, kpar = 0;      // ring position; bit s of kpar = parity of the next K-part fill of slot s
         int n_item = 0;
         bool ok = true;
@@ -469,9 +498,9 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
         const uint64_t kd0 = make_smem_desc(sbase + L::SLOTS + L::K4, 16, SBO_QK, SWZ_QK);  // + slot * SLOT_BYTES / 16
         const uint64_t sfd0 = make_smem_desc(sbase + L::SLOTS + L::KSF, 0, 128, SWZ_NONE);
         auto next_slot = [&]() { if (++slot == NSLOTS) slot = 0; };
-        // K parts (FP4 records, 16-bit K tiles) land on k_full, V parts on v_full: this warp only ever waits on k_full and
-        // the other issuer on v_full, each keeping the parity of every slot's next fill of its kind.
-        auto wait_k = [&]() { const bool r = mbar_wait(bar_k_full + slot * 8, (kpar >> slot) & 1u, abortp, budget); kpar ^= 1u << slot; return r; };
+        // FP4 records and 16-bit K tiles land on k_full, 16-bit V tiles on v_full.  The parity of a slot's next K fill
+        // is kept for every fill, also those of the other issuer's sub-steps; a slot is not filled again before the
+        // sub-step that used it is through, so the barrier asked about is in the phase asked for or the one after it.
         for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
             ok = mbar_wait(smem_u32(&bars.sched_full), n_item & 1, abortp, budget);
             if (!ok) break;
@@ -479,41 +508,45 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
             ok = mbar_wait(smem_u32(&bars.q_full), n_item & 1, abortp, budget);
             if (!ok) break;
             tc_fence_after_sync();
-            for (int a = 0; a < QK_ATOMS; ++a)
-                tmem_cp_sf_elect(tmem + TM_SFA_Q + a * 4, make_smem_desc(sbase + L::QSF + a * 512, 0, 128, SWZ_NONE));
-            if (n == 0 && lane == 0) mbar_arrive(smem_u32(&bars.q_empty));
-            for (int i = 0; i < n && ok; ++i) {
+            // index of this issuer's last sub-step of the item (Q is released behind it)
+            int my_last = n - 1;
+            if (((gsub + static_cast<uint32_t>(my_last)) & 1u) != me) my_last -= 1;
+            if (my_last >= 0) {
+                for (int a = 0; a < QK_ATOMS; ++a)
+                    tmem_cp_sf_elect(tm_sfa_q + a * 4, make_smem_desc(sbase + L::QSF + a * 512, 0, 128, SWZ_NONE));
+            } else if (lane == 0) {
+                mbar_arrive(smem_u32(&bars.q_empty));
+            }
+            for (int i = 0; i < n && ok; ++i, ++gsub) {
                 const uint32_t e = sched[i];
                 const bool fp16 = e & E_FP16;
+                const uint32_t kslot = slot, kp = (kpar >> slot) & 1u;
+                kpar ^= 1u << slot;
+                next_slot();
+                if (fp16) next_slot();                              // the V tile's slot
+                if ((gsub & 1u) != me) continue;
                 const uint32_t set = gsub & (NSETS - 1), use = gsub / NSETS;
                 const uint32_t d_t = tmem + TM_S + set * STEP;
-                const bool last = i + 1 == n;
+                ok = mbar_wait(bar_k_full + kslot * 8, kp, abortp, budget) && mbar_wait(bar_s_free + set * 8, (use & 1) ^ 1, abortp, budget);
+                if (!ok) break;
+                tc_fence_after_sync();
                 if (!fp16) {
-                    ok = wait_k() && mbar_wait(bar_s_free + set * 8, (use & 1) ^ 1, abortp, budget);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    const uint32_t soff = slot * (SLOT_BYTES / 16);
+                    const uint32_t soff = kslot * (SLOT_BYTES / 16);
                     const uint32_t sfb = tmem + TM_SFB_K + set * 8;
                     if (elect_one()) {
                         for (int a = 0; a < QK_ATOMS; ++a) tmem_cp_sf(sfb + a * 4, sfd0 + soff + a * 32);
                         for (int kb = 0; kb < KBLK; ++kb) {
                             if constexpr (MX)
                                 mma_mxfp4(d_t, qd0 + kb * 2, kd0 + soff + kb * 2, make_idesc_fp4(128, STEP, 1, kb * 2, kb * 2),
-                                          tmem + TM_SFA_Q, sfb, kb > 0);
+                                          tm_sfa_q, sfb, kb > 0);
                             else
-                                mma_nvfp4(d_t, qd0 + kb * 2, kd0 + soff + kb * 2, idesc_qk4, tmem + TM_SFA_Q + kb * 4, sfb + kb * 4, kb > 0);
+                                mma_nvfp4(d_t, qd0 + kb * 2, kd0 + soff + kb * 2, idesc_qk4, tm_sfa_q + kb * 4, sfb + kb * 4, kb > 0);
                         }
                         tc_commit(bar_s_full + set * 8);
-                        if (last) tc_commit(smem_u32(&bars.q_empty));
+                        if (i == my_last) tc_commit(smem_u32(&bars.q_empty));
                     }
                     __syncwarp();
-                    next_slot();
                 } else {
-                    const uint32_t kslot = slot;
-                    ok = wait_k() && mbar_wait(bar_s_free + set * 8, (use & 1) ^ 1, abortp, budget);
-                    if (!ok) break;
-                    next_slot();
-                    tc_fence_after_sync();
 #pragma unroll 1
                     for (int ks = 0; ks < D / 16; ++ks) {
                         const uint32_t hf = ks / 4, kk = ks % 4;
@@ -524,83 +557,84 @@ prefill_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ4,
                     }
                     tc_commit_elect(bar_slot_empty + kslot * 8);    // the K tile is free once S is computed
                     tc_commit_elect(bar_s_full + set * 8);
-                    if (last) tc_commit_elect(smem_u32(&bars.q_empty));
-                    next_slot();                                    // the V tile's slot
+                    if (i == my_last) tc_commit_elect(smem_u32(&bars.q_empty));
                 }
-                ++gsub;
             }
             if (lane == 0) mbar_arrive(smem_u32(&bars.sched_empty));
         }
-    } else if (warp == 2) {
+    } else if (warp == 3) {
         // =========================== O += P V issuer ===========================
+        // One thread issues every P V of the CTA, in list order (they add into the same accumulator), so this loop is
+        // kept as short as it can be: an FP4 sub-step needs no wait for its V tile (it came with the K tile, which the
+        // other issuer waited for before S, and P, existed) and no commit for its slot (the producer watches p_free).
         tmem_cp_sf_elect(tmem + TM_SFA_P, make_smem_desc(sbase + L::CSF, 0, 128, SWZ_NONE));
         uint32_t gsub = 0;
-        uint32_t slot = 0, vpar = 0;      // ring position; bit s of vpar = parity of the next V-part fill of slot s
+        uint32_t slot = 0, vpar = 0;      // ring position; bit s of vpar = parity of the next V-tile fill of slot s
         int n_item = 0;
         bool ok = true;
         const uint32_t idesc_pv4 = make_idesc_fp4(128, D, MX ? 1 : 0, 0, 0);
         const uint32_t idesc_pv16 = make_idesc_f16(128, D, BF16 ? 1 : 0, 0, 1);
         const uint32_t bar_v_full = smem_u32(&bars.v_full[0]), bar_slot_empty = smem_u32(&bars.slot_empty[0]);
         const uint32_t bar_p_full = smem_u32(&bars.p_full[0][0]), bar_p_free = smem_u32(&bars.p_free[0][0]);
+        const uint32_t bar_o_full = smem_u32(&bars.o_full);
         const uint64_t pd0 = make_smem_desc(sbase + L::P, 16, 256, SWZ_32B);                 // + set * PSET_BYTES / 16 + buffer * 256
         const uint64_t vd0 = make_smem_desc(sbase + L::SLOTS + L::V4, 16, 256, SWZ_32B);     // + slot * SLOT_BYTES / 16
         const uint64_t sfd0 = make_smem_desc(sbase + L::SLOTS + L::VSF, 0, 128, SWZ_NONE);
         auto next_slot = [&]() { if (++slot == NSLOTS) slot = 0; };
-        auto wait_v = [&]() { const bool r = mbar_wait(bar_v_full + slot * 8, (vpar >> slot) & 1u, abortp, budget); vpar ^= 1u << slot; return r; };
         for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++n_item) {
             ok = mbar_wait(smem_u32(&bars.sched_full), n_item & 1, abortp, budget);
             if (!ok) break;
-            const int n = bars.sched_n;
-            for (int i = 0; i < n && ok; ++i) {
-                const uint32_t e = sched[i];
-                const bool fp16 = e & E_FP16;
+            const int n = bars.sched_n, n_fp4 = bars.sched_na;
+            int i = 0;
+            // ---- FP4 sub-steps ----
+            for (; i < n_fp4; ++i, ++gsub) {
                 const uint32_t set = gsub & (NSETS - 1), use = gsub / NSETS, pb = set * 2 + (use & 1);
-                const uint32_t acc = i > 0 ? 1u : 0u;
-                const bool last = i + 1 == n;
-                if (!fp16) {
-                    ok = wait_v() && mbar_wait(bar_p_full + pb * 8, (use >> 1) & 1, abortp, budget);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    const uint32_t soff = slot * (SLOT_BYTES / 16);
-                    const uint32_t sfb = tmem + TM_SFB_V + set * 4;
-                    const uint64_t ad = pd0 + set * (PSET_BYTES / 16) + (use & 1) * 256;
-                    if (elect_one()) {
-                        tmem_cp_sf(sfb, sfd0 + soff);
-                        if constexpr (MX) mma_mxfp4(tmem + TM_O, ad, vd0 + soff, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
-                        else mma_nvfp4(tmem + TM_O, ad, vd0 + soff, idesc_pv4, tmem + TM_SFA_P, sfb, acc);
-                        tc_commit(bar_slot_empty + slot * 8);
-                        tc_commit(bar_p_free + pb * 8);
-                        if (last) tc_commit(smem_u32(&bars.o_full));
-                    }
-                    __syncwarp();
-                    next_slot();
-                } else {
-                    next_slot();                                    // the K tile's slot
-                    const uint32_t vslot = slot;
-                    ok = wait_v() && mbar_wait(bar_p_full + pb * 8, (use >> 1) & 1, abortp, budget);
-                    if (!ok) break;
-                    next_slot();
-                    tc_fence_after_sync();
-                    const uint32_t pa = sbase + L::P + set * PSET_BYTES;
-                    const uint32_t va = sbase + L::SLOTS + vslot * SLOT_BYTES;
-#pragma unroll 1
-                    for (int ks = 0; ks < STEP / 16; ++ks) {
-                        const uint64_t ad = make_smem_desc(pa + ks * 32, 16, 1024, SWZ_128B);
-                        const uint64_t bd = make_smem_desc(va + ks * 2048, STEP * 128, 1024, SWZ_128B);
-                        mma_f16_elect(tmem + TM_O, ad, bd, idesc_pv16, (acc == 0 && ks == 0) ? 0 : 1);
-                    }
-                    tc_commit_elect(bar_slot_empty + vslot * 8);
-                    tc_commit_elect(bar_p_free + pb * 8);
-                    if (last) tc_commit_elect(smem_u32(&bars.o_full));
+                ok = mbar_wait(bar_p_full + pb * 8, (use >> 1) & 1, abortp, budget);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t soff = slot * (SLOT_BYTES / 16);
+                const uint32_t sfb = tmem + TM_SFB_V + set * 4;
+                const uint64_t ad = pd0 + set * (PSET_BYTES / 16) + (use & 1) * 256;
+                if (elect_one()) {
+                    tmem_cp_sf(sfb, sfd0 + soff);
+                    if constexpr (MX) mma_mxfp4(tmem + TM_O, ad, vd0 + soff, idesc_pv4, tmem + TM_SFA_P, sfb, i > 0);
+                    else mma_nvfp4(tmem + TM_O, ad, vd0 + soff, idesc_pv4, tmem + TM_SFA_P, sfb, i > 0);
+                    tc_commit(bar_p_free + pb * 8);
+                    if (i + 1 == n) tc_commit(bar_o_full);
                 }
-                ++gsub;
+                __syncwarp();
+                next_slot();
             }
+            // ---- 16-bit sub-steps ----
+            for (; i < n && ok; ++i, ++gsub) {
+                const uint32_t set = gsub & (NSETS - 1), use = gsub / NSETS, pb = set * 2 + (use & 1);
+                next_slot();                                    // the K tile's slot
+                const uint32_t vslot = slot;
+                ok = mbar_wait(bar_v_full + vslot * 8, (vpar >> vslot) & 1u, abortp, budget) &&
+                     mbar_wait(bar_p_full + pb * 8, (use >> 1) & 1, abortp, budget);
+                vpar ^= 1u << vslot;
+                if (!ok) break;
+                next_slot();
+                tc_fence_after_sync();
+                const uint32_t pa = sbase + L::P + set * PSET_BYTES;
+                const uint32_t va = sbase + L::SLOTS + vslot * SLOT_BYTES;
+#pragma unroll 1
+                for (int ks = 0; ks < STEP / 16; ++ks) {
+                    const uint64_t ad = make_smem_desc(pa + ks * 32, 16, 1024, SWZ_128B);
+                    const uint64_t bd = make_smem_desc(va + ks * 2048, STEP * 128, 1024, SWZ_128B);
+                    mma_f16_elect(tmem + TM_O, ad, bd, idesc_pv16, (i == 0 && ks == 0) ? 0 : 1);
+                }
+                tc_commit_elect(bar_slot_empty + vslot * 8);
+                tc_commit_elect(bar_p_free + pb * 8);
+                if (i + 1 == n) tc_commit_elect(bar_o_full);
+            }
+            if (!ok) break;
             if (lane == 0) mbar_arrive(smem_u32(&bars.sched_empty));
         }
     } else {
         // =========================== softmax ===========================
         const int g = warp & 3;                   // 32-row group = tensor-memory sub-partition
-        const uint32_t set = (warp - 3) >> 2;     // this warp runs the sub-steps with (CTA-wide index) mod 4 == set
+        const uint32_t set = (warp - 4) >> 2;     // this warp runs the sub-steps with (CTA-wide index) mod 4 == set
         const uint32_t prev_set = (set + NSETS - 1) & (NSETS - 1);
         const int row = g * 32 + lane;            // row inside the q tile
         const int half = g >> 1;                  // 0: rows 0..63, 1: rows 64..127
