@@ -784,26 +784,29 @@ __global__ void __launch_bounds__(128) reduce_partials_kernel(const float* __res
 
 }  // namespace
 
-// Chains per (sequence, KV head): enough CTAs to fill the GPU (two per SM) in whole waves.
+// Chains per (sequence, KV head).  A chain costs a fixed set-up (tensor-memory allocation, zeroed operand tiles,
+// page list, filling and draining the page ring: measured as about the time of 15 pages) plus its pages, and the CTAs
+// run in waves of two per SM; the count that minimises waves x (set-up + pages per chain) wins, the smaller count on
+// a tie.  With many heads and short sequences that is ONE chain per head (256 heads x 256 pages: 209 us against 251
+// with eight chains), with few heads it is as many chains as fill the GPU once.
 int decode_pick_splits(int heads, int npages) {
     int sms = NUM_SMS_HINT;
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (heads < 1) heads = 1;
     const long long resident = 2LL * sms;
+    constexpr int SETUP_PAGES = 15;
     int lo = cdiv(npages, DEC_LIST_CAP);
     if (lo < 1) lo = 1;
     int hi = npages < 64 ? npages : 64;
     if (hi < lo) hi = lo;
     int best = lo;
-    double best_eff = -1.0;
+    long long best_cost = -1;
     for (int s = lo; s <= hi; ++s) {
         const long long ctas = static_cast<long long>(heads) * s;
         const long long waves = (ctas + resident - 1) / resident;
-        const double eff = static_cast<double>(ctas) / static_cast<double>(waves * resident);
-        if (eff > best_eff + 1e-9) { best_eff = eff; best = s; }
-        // the first split count that fills at least two waves to 95 % is good enough
-        if (eff >= 0.95 && ctas >= 2 * resident) { best = s; break; }
+        const long long cost = waves * (SETUP_PAGES + cdiv(npages, s));
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
         if (npages / s < 8) break;   // chains shorter than 8 pages are mostly set-up
     }
     return best;
