@@ -360,3 +360,118 @@ def test_paged_cache_decode_and_prefill_equal_the_slab_cache(fmt, selection, dty
         cache.update(k[:, :, :640].to(DEV), v[:, :, :640].to(DEV), 0)
         pre.append(tc.cached_prefill_attention(qp, cache, 0, cfg))
     assert torch.equal(pre[0], pre[1])
+
+
+# ------------------------------------------------------------------------------- the length in device memory
+def _layer_buffers(layer):
+    names = (("k_pool", "v_pool", "k4_pool", "ks_pool", "v4_pool", "vs_pool") if isinstance(layer, tc.PagedThriftAttentionCacheLayer)
+             else ("k_fp16", "v_fp16", "k_packed", "k_scale", "v_packed_t", "v_scale_t"))
+    return {n: getattr(layer, n) for n in names + ("k_mean", "k_min", "k_max") if getattr(layer, n) is not None}
+
+
+@pytest.mark.parametrize("paged,fmt,selection,dtype,d,prompt,steps,max_len",
+                         [(False, "nvfp4", "block_mean", torch.float16, 128, 40, 150, 1024),
+                          (True, "nvfp4", "quest", torch.bfloat16, 128, 40, 150, 1024),
+                          (True, "mxfp4", "block_mean", torch.float16, 64, 40, 150, 1024),
+                          (False, "mxfp4", "quest", torch.bfloat16, 64, 40, 150, 1024),
+                          # around 256 complete blocks, where the selection kernel changes from one exact pass to
+                          # tensor-core scores + exact re-scoring of the candidates
+                          (True, "nvfp4", "block_mean", torch.float16, 128, 64 * 256 - 30, 100, 64 * 264),
+                          (False, "nvfp4", "quest", torch.float16, 128, 64 * 256 - 30, 100, 64 * 264)])
+def test_generation_step_with_device_length_replays_from_one_graph(monkeypatch, paged, fmt, selection, dtype, d, prompt,
+                                                                   steps, max_len):
+    """append + decode step of a layer, with the sequence length read from device memory, are captured in ONE CUDA
+    graph and replayed for 100 - 150 tokens - across page boundaries, growing selected / forced block counts, a prompt
+    shorter than one block - and give, token by token, the bytes of update + cached_decode_attention (whose
+    launches take the length from the host) run with the same chain count; the caches end up identical too."""
+    from thriftattention_b200 import _C
+
+    torch.manual_seed(5)
+    b, hq, hkv, chains = 2, 8, 2, 4
+    cfg = ta.AttentionConfig(selection=selection, fraction=0.3, quant_format=fmt, sink_blocks=1, local_blocks=1)
+    caches = [ta.ThriftAttentionCache(config=cfg, max_cache_len=max_len, paged=paged) for _ in range(2)]
+    k0 = torch.randn(b, hkv, prompt, d, device=DEV).to(dtype)
+    v0 = torch.randn(b, hkv, prompt, d, device=DEV).to(dtype)
+    for c in caches:
+        c.update(k0, v0, 0)
+    host, graphed = caches
+    layer = graphed.layer(0)
+    layer.reserve(max_len)
+    for pages in range(1, max_len // 64 + 1):      # the host-length path: same chains as the graph's launch
+        monkeypatch.setitem(_C._decode_step_splits, (b * hkv, pages), min(chains, pages))
+
+    length = torch.tensor([prompt], dtype=torch.int32, device=DEV)
+    q_in = torch.zeros(b, hq, 1, d, device=DEV, dtype=dtype)
+    k_in = torch.zeros(b, hkv, 1, d, device=DEV, dtype=dtype)
+    v_in = torch.zeros(b, hkv, 1, d, device=DEV, dtype=dtype)
+    out_buf = torch.zeros(b, hq, 1, d, device=DEV, dtype=dtype)
+
+    def step():
+        res = tc.device_length_decode_step(q_in, k_in, v_in, graphed, 0, cfg, length, max_len=max_len, splits=chains, out=out_buf)
+        _C.advance_length(length, 1, max_len)
+        return res
+
+    # one eager step on throw-away state (kernel attributes, scratch buffers), then restore and capture
+    saved = {n: t.clone() for n, t in _layer_buffers(layer).items()}
+    step()
+    torch.cuda.synchronize()
+    for n, t in _layer_buffers(layer).items():
+        t.view(torch.uint8).copy_(saved[n].view(torch.uint8))
+    length.fill_(prompt)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        res = step()
+    assert res.data_ptr() == out_buf.data_ptr()
+    length.fill_(prompt)
+    for n, t in _layer_buffers(layer).items():
+        t.view(torch.uint8).copy_(saved[n].view(torch.uint8))
+
+    for t in range(steps):
+        q = torch.randn(b, hq, 1, d, device=DEV).to(dtype)
+        k1 = torch.randn(b, hkv, 1, d, device=DEV).to(dtype)
+        v1 = torch.randn(b, hkv, 1, d, device=DEV).to(dtype)
+        q_in.copy_(q); k_in.copy_(k1); v_in.copy_(v1)
+        graph.replay()
+        host.update(k1, v1, 0)
+        want = tc.cached_decode_attention(q, host, 0, cfg)
+        assert torch.equal(out_buf, want), f"token {prompt + t}"
+        want_sel = host.layer(0).selected_blocks
+        got_sel = layer.selected_blocks
+        if want_sel is not None and want_sel.numel():
+            assert torch.equal(got_sel[:, : want_sel.shape[1]], want_sel), f"token {prompt + t}"
+            assert bool((got_sel[:, want_sel.shape[1]:] == -1).all())
+    assert int(length.item()) == prompt + steps
+    a, g = _layer_buffers(host.layer(0)), _layer_buffers(layer)
+    if paged:
+        tokens = (prompt + steps + 63) // 64 * 64
+        layer._gathered = None
+        for n in ("k_pool", "v_pool", "k4_pool", "ks_pool", "v4_pool", "vs_pool"):     # the page ids differ: compare by position
+            assert torch.equal(host.layer(0)._gather(n, tokens).view(torch.uint8), layer._gather(n, tokens).view(torch.uint8)), n
+        for n in ("k_mean", "k_min", "k_max"):
+            if n in a:
+                assert torch.equal(a[n][:, :, : tokens // 64], g[n][:, :, : tokens // 64]), n
+    else:
+        for n in a:
+            assert torch.equal(a[n].view(torch.uint8), g[n].view(torch.uint8)), n
+    _C.decode_status(DEV)
+
+
+def test_device_length_append_beyond_the_capacity_stores_nothing():
+    from thriftattention_b200 import _C
+
+    torch.manual_seed(6)
+    cfg = ta.AttentionConfig(selection="block_mean", top_k=2, quant_format="nvfp4")
+    cache = ta.ThriftAttentionCache(config=cfg, max_cache_len=128)
+    k = torch.randn(1, 2, 100, 128, device=DEV, dtype=torch.float16)
+    cache.update(k, k, 0)
+    layer = cache.layer(0)
+    before = {n: t.clone() for n, t in _layer_buffers(layer).items()}
+    length = torch.tensor([128], dtype=torch.int32, device=DEV)
+    one = torch.randn(1, 2, 1, 128, device=DEV, dtype=torch.float16)
+    _C.cache_append_at(one, one, layer.k_fp16, layer.v_fp16, layer.k_packed, layer.k_scale, layer.v_packed_t, layer.v_scale_t,
+                       length, k_mean=layer.k_mean)
+    _C.advance_length(length, 1, 128)
+    torch.cuda.synchronize()
+    assert int(length.item()) == 128
+    for n, t in _layer_buffers(layer).items():
+        assert torch.equal(t.view(torch.uint8), before[n].view(torch.uint8)), n

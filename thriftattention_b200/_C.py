@@ -765,6 +765,131 @@ def cached_decode_step(q_grouped, k_hi, v_hi, k_packed, k_scale, v_packed_t, v_s
     return out, sel_out
 
 
+def _check_length(length: torch.Tensor, device) -> None:
+    _check(isinstance(length, torch.Tensor) and length.is_cuda and length.device == device and length.dtype == torch.int32
+           and length.numel() == 1, "the device-side length must be a one-element int32 CUDA tensor on the cache's device")
+
+
+def cache_append_at(k_new, v_new, k_hi, v_hi, k_codes, k_scales, v_codes, v_scales, length, *, offset=0, page_table=None,
+                    k_mean=None, k_min=None, k_max=None, is_mx=False, stat_block=64):
+    """``cache_append`` (or, with ``page_table``, ``cache_append_paged``) at token position ``length[0] + offset``, where
+    ``length`` is a one-element int32 tensor ON THE GPU: the launch is the same whatever the position, so it can be
+    captured in a CUDA graph and replayed for every token.  A range that would end beyond the capacity is not stored.
+    ``k_new`` / ``v_new`` [B, Hkv, T, D]."""
+    _check(k_hi.is_cuda and k_hi.dim() == 4 and k_hi.is_contiguous() and k_hi.dtype in (torch.float16, torch.bfloat16),
+           "k cache must be a contiguous 4D float16 / bfloat16 CUDA tensor")
+    _check_length(length, k_hi.device)
+    paged = page_table is not None
+    g = 32 if is_mx else 16
+    d = k_hi.shape[3]
+    if paged:
+        pool, hkv = k_hi.shape[0], k_hi.shape[1]
+        _check(k_hi.shape[2] == 64 and page_table.is_cuda and page_table.dtype == torch.int32 and page_table.dim() == 2
+               and page_table.is_contiguous(), "paged append expects pools [pool, Hkv, 64, D] and an int32 page table")
+        b, max_pages = page_table.shape
+        cap = 0
+        expect = {"v_hi": (v_hi, (pool, hkv, 64, d)), "k_codes": (k_codes, (pool, hkv, 64, d // 2)),
+                  "k_scales": (k_scales, (pool, hkv, 64, d // g)), "v_codes": (v_codes, (pool, hkv, d, 32)),
+                  "v_scales": (v_scales, (pool, hkv, d, 64 // g))}
+    else:
+        b, hkv, cap, _ = k_hi.shape
+        pool = max_pages = 0
+        expect = {"v_hi": (v_hi, (b, hkv, cap, d)), "k_codes": (k_codes, (b, hkv, cap, d // 2)),
+                  "k_scales": (k_scales, (b, hkv, cap, d // g)), "v_codes": (v_codes, (b, hkv, d, cap // 2)),
+                  "v_scales": (v_scales, (b, hkv, d, cap // g))}
+    for name, (t, shape) in expect.items():
+        _check(t.is_cuda and t.is_contiguous() and tuple(t.shape) == shape, f"{name} must be contiguous {shape}")
+    for name, new in (("key_states", k_new), ("value_states", v_new)):
+        _check(new is not None and new.is_cuda and new.is_contiguous() and new.dtype == k_hi.dtype and new.dim() == 4
+               and new.shape[0] == b and new.shape[1] == hkv and new.shape[3] == d,
+               f"{name} must be contiguous [batch, kv_heads, tokens, head_dim] CUDA tensors of the cache dtype")
+    stat_blocks = 1
+    for name, t in (("k_mean", k_mean), ("k_min", k_min), ("k_max", k_max)):
+        if t is not None:
+            _check(t.is_cuda and t.is_contiguous() and t.dim() == 4 and t.shape[0] == b and t.shape[1] == hkv
+                   and t.shape[3] == d and t.dtype == k_hi.dtype and (paged or t.shape[2] == cap // stat_block),
+                   f"{name} must be contiguous [B, Hkv, blocks, D] of the cache dtype")
+            stat_blocks = t.shape[2]
+    with torch.cuda.device(k_hi.device):
+        rc = _lib.load().ta100_cache_append_at(
+            _ptr(k_new), _ptr(v_new), _ptr(k_hi), _ptr(v_hi), _ptr(k_codes), _ptr(k_scales), _ptr(v_codes), _ptr(v_scales),
+            _ptr(k_mean), _ptr(k_min), _ptr(k_max), _ptr(page_table), max_pages, pool, b, hkv, stat_blocks, cap, _ptr(length),
+            int(offset), k_new.shape[2], v_new.shape[2], d, stat_block, int(is_mx), int(k_hi.dtype == torch.bfloat16), 0,
+            _stream(k_hi))
+    _lib.check(rc, "cache_append_at")
+
+
+def advance_length(length: torch.Tensor, count: int, limit: int) -> None:
+    """``length[0] = min(length[0] + count, limit)`` in stream order (one tiny launch): the end of a generation step
+    whose kernels read the length on the GPU."""
+    _check_length(length, length.device)
+    with torch.cuda.device(length.device):
+        rc = _lib.load().ta100_advance_length(_ptr(length), int(count), int(limit), _stream(length))
+    _lib.check(rc, "advance_length")
+
+
+def decode_step_row_width(max_len: int, *, top_k=None, fraction=None, sink=0, local=0) -> int:
+    """Width of the selection rows ``cached_decode_step_at`` needs for sequences of up to ``max_len`` tokens."""
+    from .selection.counts import resolve_top_k
+
+    n = max_len // 64
+    return max(1, resolve_top_k(n, causal=False, top_k=top_k, fraction=fraction) + int(sink) + int(local))
+
+
+def cached_decode_step_at(q_grouped, k_hi, v_hi, k_packed, k_scale, v_packed, v_scale, stat_a, stat_b, length, *, offset,
+                          max_len, top_k=None, fraction=None, sink=0, local=0, is_mx=False, splits=None, sel_out=None,
+                          out=None, page_table=None):
+    """``cached_decode_step`` over ``length[0] + offset`` cached tokens, ``length`` being a one-element int32 tensor ON
+    THE GPU.  The kernels derive the page count, the number of complete blocks and the selected / forced block counts
+    (the rule of ``cached_decode_attention``: ``top_k`` blocks or ``fraction`` of the complete ones, ``local`` then
+    ``sink`` forced blocks as far as there is room) from it when they start, so the same launches serve every length
+    up to ``max_len`` (a multiple of 64) and replay from one CUDA graph across tokens.  Contiguous cache tensors as
+    for ``cached_decode_step``; with ``page_table`` the page pools.  ``splits`` chains per KV head (default: the
+    choice for ``max_len``).  Returns ``(out [B, Hkv, G, D], selected [B*Hkv, row width])``, rows -1 padded."""
+    b, hkv, g, d = q_grouped.shape
+    dev = q_grouped.device
+    is_bf16 = q_grouped.dtype == torch.bfloat16
+    _check(q_grouped.is_cuda and q_grouped.is_contiguous() and max_len % 64 == 0 and max_len > 0 and 1 <= g <= 16,
+           "cached_decode_step_at expects a contiguous CUDA query [B, Hkv, G <= 16, D] and max_len in whole pages")
+    _check_length(length, dev)
+    _check(stat_a is not None and k_hi is not None and v_hi is not None, "the statistics and the 16-bit caches are required")
+    paged = page_table is not None
+    cap = max_len if paged else k_packed.shape[2]
+    _check(cap >= max_len, "max_len exceeds the cache capacity")
+    width = decode_step_row_width(max_len, top_k=top_k, fraction=fraction, sink=sink, local=local)
+    lib = _lib.load()
+    pages = max_len // 64
+    if splits is None:
+        splits = max(1, min(lib.ta100_decode_pick_splits(b * hkv, pages), pages))
+    skey = (dev.index, b, hkv, g, d, splits, is_mx)
+    scratch = _decode_step_scratch.get(skey)
+    if scratch is None:
+        grp = 32 if is_mx else 16
+        scratch = (torch.empty(b, hkv, g, d // 2, dtype=torch.uint8, device=dev),
+                   torch.empty(b, hkv, g, d // grp, dtype=torch.uint8, device=dev),
+                   torch.empty(b * hkv, splits, g, d, dtype=torch.float32, device=dev),
+                   torch.empty(b * hkv, splits, g, 2, dtype=torch.float32, device=dev))
+        _decode_step_scratch[skey] = scratch
+    q4, qs, part_o, part_ml = scratch
+    if sel_out is None or tuple(sel_out.shape) != (b * hkv, width):
+        sel_out = torch.empty(b * hkv, width, dtype=torch.int32, device=dev)
+    if out is None:
+        out = torch.empty(b, hkv, g, d, dtype=q_grouped.dtype, device=dev)
+    vp = ctypes.c_void_p
+    with torch.cuda.device(dev):
+        rc = lib.ta100_cached_decode_step_at(
+            vp(q_grouped.data_ptr()), vp(q4.data_ptr()), vp(qs.data_ptr()), vp(k_hi.data_ptr()), vp(v_hi.data_ptr()),
+            vp(k_packed.data_ptr()), vp(k_scale.data_ptr()), vp(v_packed.data_ptr()), vp(v_scale.data_ptr()),
+            _ptr(page_table), page_table.shape[1] if paged else 0, k_packed.shape[0] if paged else 0,
+            vp(stat_a.data_ptr()), _ptr(stat_b), vp(sel_out.data_ptr()), width, vp(out.data_ptr()), vp(part_o.data_ptr()),
+            vp(part_ml.data_ptr()), b, hkv, g, vp(length.data_ptr()), int(offset), max_len, cap, stat_a.shape[2],
+            -1 if top_k is None else int(top_k), float(0.05 if fraction is None else fraction), int(sink), int(local), d,
+            int(is_mx), int(is_bf16), splits, vp(torch.cuda.current_stream(dev).cuda_stream))
+    if rc:
+        _lib.check(rc, "cached_decode_step_at")
+    return out, sel_out
+
+
 def debug_set_wait(budget_cycles: int = 0, skip_loads: bool = False) -> None:
     """Diagnostics: the cycle budget of the bounded device-side waits of later launches (0 = default) and a switch
     that makes the attention kernels' producer warps copy nothing, so that the waits run out (tests of the

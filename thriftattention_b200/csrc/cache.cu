@@ -35,6 +35,8 @@ struct AppendParams {
     uint16_t* k_min;
     uint16_t* k_max;
     int start, k_count, v_count, cap;
+    const int32_t* start_dev;     // null, or the append position in device memory: the kernel uses *start_dev + start
+                                  // and the item counts below are upper bounds
     const int32_t* page_table;    // paged addressing: [batch, max_pages] -> physical page; nullptr = slabs
     int max_pages, pool_pages, hkv;
     int stat_blocks;              // statistics blocks per head in k_mean / k_min / k_max (their row stride)
@@ -74,8 +76,28 @@ __device__ __forceinline__ uint4 row_chunk(const AppendParams& p, const uint16_t
 }
 
 template <int D, bool MX, bool BF16, bool PAGED>
-__global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p) {
+__global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams launch) {
     constexpr int G = MX ? 32 : 16;
+    AppendParams p = launch;
+    int n_v_real = p.n_v_items, n_s_real = p.n_s_items;
+    if (launch.start_dev != nullptr) {
+        // the position comes from device memory: the launch was cut for the worst case, the real ranges follow here
+        p.start = __ldg(launch.start_dev) + launch.start;
+        const int longest = p.k_count > p.v_count ? p.k_count : p.v_count;
+        if (p.start < 0 || p.start > p.cap - longest) return;     // beyond the capacity: nothing is stored
+        n_v_real = 0;
+        n_s_real = 0;
+        if (p.v_count > 0) {
+            p.v_begin = p.start / G * G;
+            p.v_end = cdiv(p.start + p.v_count, G) * G;
+            n_v_real = cdiv(p.v_end, 128) - p.v_begin / 128;
+        }
+        if (p.k_count > 0 && (p.k_mean || p.k_min || p.k_max)) {
+            p.s_first = p.start / p.stat_block;
+            const int last = (p.start + p.k_count) / p.stat_block;
+            n_s_real = last > p.s_first ? last - p.s_first : 0;
+        }
+    }
     constexpr int GPR = D / G;        // groups per row
     constexpr int ROWS = 128 / GPR;   // K rows per item
     constexpr int VEC = D / 8;        // 16-byte chunks per row
@@ -117,6 +139,7 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p)
     it -= p.n_k_items;
 
     if (it < p.n_v_items) {
+        if (it >= n_v_real) return;
         // ---------------------------------------------------------------- V: groups of one 128-token tile
         auto tile = reinterpret_cast<uint16_t(*)[D + 8]>(smem);
         auto out_codes = reinterpret_cast<uint8_t(*)[64]>(smem + TILE_BYTES);
@@ -186,7 +209,7 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p)
     }
     it -= p.n_v_items;
 
-    {
+    if (it < n_s_real) {
         // ---------------------------------------------------------------- statistics of one completed block
         // Same summation order as block_stats_kernel: eight row groups (row mod 8) accumulate in ascending
         // row order, the eight partial sums are added left to right, then divided by the block length.
@@ -243,7 +266,7 @@ int cache_append_dispatch(const void* k_new, const void* v_new, void* k_hi, void
                           void* v_codes_t, void* v_scales_t, void* k_mean, void* k_min, void* k_max, long long heads,
                           int start, int k_count, int v_count, int capacity, int head_dim, int stat_block, int is_mx,
                           int is_bf16, int flags, const void* page_table, int max_pages, int pool_pages, int hkv,
-                          int stat_blocks, cudaStream_t stream) {
+                          int stat_blocks, const void* start_dev, cudaStream_t stream) {
     if (head_dim != 64 && head_dim != 128) return TA100_ERR_UNSUPPORTED;
     if (page_table) {
         if (max_pages <= 0 || pool_pages <= 0 || hkv <= 0 || heads % hkv != 0 || stat_blocks <= 0) return TA100_ERR_SHAPE;
@@ -254,7 +277,7 @@ int cache_append_dispatch(const void* k_new, const void* v_new, void* k_hi, void
     if (heads < 0 || start < 0 || k_count < 0 || v_count < 0 || capacity <= 0 || capacity % 128 != 0)
         return TA100_ERR_SHAPE;
     if (stat_block != 64 && stat_block != 128) return TA100_ERR_SHAPE;
-    if (static_cast<long long>(start) + (k_count > v_count ? k_count : v_count) > capacity) return TA100_ERR_SHAPE;
+    if (!start_dev && static_cast<long long>(start) + (k_count > v_count ? k_count : v_count) > capacity) return TA100_ERR_SHAPE;
     if (k_count > 0 && (!k_hi || !k_codes || !k_scales)) return TA100_ERR_NULL;
     if (v_count > 0 && (!v_hi || !v_codes_t || !v_scales_t)) return TA100_ERR_NULL;
     const uintptr_t all = reinterpret_cast<uintptr_t>(k_new) | reinterpret_cast<uintptr_t>(v_new) |
@@ -277,6 +300,7 @@ int cache_append_dispatch(const void* k_new, const void* v_new, void* k_hi, void
     p.k_min = static_cast<uint16_t*>(k_min);
     p.k_max = static_cast<uint16_t*>(k_max);
     p.start = start; p.k_count = k_count; p.v_count = v_count; p.cap = capacity;
+    p.start_dev = static_cast<const int32_t*>(start_dev);
     p.page_table = static_cast<const int32_t*>(page_table);
     p.max_pages = max_pages; p.pool_pages = pool_pages; p.hkv = hkv;
     p.stat_blocks = page_table ? stat_blocks : capacity / stat_block;
@@ -286,15 +310,22 @@ int cache_append_dispatch(const void* k_new, const void* v_new, void* k_hi, void
     const int rows_per_item = 128 / (head_dim / G);
     p.k_loop = k_count >= 2048 ? 8 : 1;
     p.n_k_items = cdiv(k_count, rows_per_item * p.k_loop);
-    if (v_count > 0) {
-        p.v_begin = start / G * G;
-        p.v_end = cdiv(start + v_count, G) * G;
-        p.n_v_items = cdiv(p.v_end, 128) - p.v_begin / 128;
-    }
-    if (k_count > 0 && (k_mean || k_min || k_max)) {
-        p.s_first = start / stat_block;
-        const int last = (start + k_count) / stat_block;
-        p.n_s_items = last > p.s_first ? last - p.s_first : 0;
+    if (start_dev) {
+        // wherever the range starts: its V groups reach at most G - 1 tokens beyond either end, and it completes at
+        // most one statistics block more than it has whole blocks
+        if (v_count > 0) p.n_v_items = (v_count + 2 * (G - 1) - 1) / 128 + 2;
+        if (k_count > 0 && (k_mean || k_min || k_max)) p.n_s_items = k_count / stat_block + 1;
+    } else {
+        if (v_count > 0) {
+            p.v_begin = start / G * G;
+            p.v_end = cdiv(start + v_count, G) * G;
+            p.n_v_items = cdiv(p.v_end, 128) - p.v_begin / 128;
+        }
+        if (k_count > 0 && (k_mean || k_min || k_max)) {
+            p.s_first = start / stat_block;
+            const int last = (start + k_count) / stat_block;
+            p.n_s_items = last > p.s_first ? last - p.s_first : 0;
+        }
     }
     const long long grid = heads * (p.n_k_items + p.n_v_items + p.n_s_items);
     if (grid > 0x7FFFFFFFLL) return TA100_ERR_LIMIT;
@@ -311,6 +342,21 @@ int cache_append_dispatch(const void* k_new, const void* v_new, void* k_hi, void
         else { if (is_bf16) TA100_APPEND(64, false, true); else TA100_APPEND(64, false, false); }
     }
 #undef TA100_APPEND
+    return static_cast<int>(cudaGetLastError());
+}
+
+namespace {
+__global__ void advance_length_kernel(int32_t* len, int count, int limit) {
+    const long long v = static_cast<long long>(*len) + count;
+    *len = static_cast<int32_t>(v > limit ? limit : (v < 0 ? 0 : v));
+}
+}  // namespace
+
+// *len_dev = min(*len_dev + count, limit): the end of a generation step whose kernels read the length on the GPU.
+int advance_length_dispatch(void* len_dev, int count, int limit, cudaStream_t stream) {
+    if (!len_dev) return TA100_ERR_NULL;
+    if (limit < 0) return TA100_ERR_SHAPE;
+    advance_length_kernel<<<1, 1, 0, stream>>>(static_cast<int32_t*>(len_dev), count, limit);
     return static_cast<int>(cudaGetLastError());
 }
 

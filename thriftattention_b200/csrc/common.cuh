@@ -36,6 +36,54 @@ extern int g_test_skip_loads;
 
 __host__ __device__ constexpr int cdiv(int a, int b) { return (a + b - 1) / b; }
 
+// Sequence length kept in DEVICE memory.  A generation loop whose launches must not change from token to token
+// (one CUDA graph replayed for every token) stores the number of tokens in the cache in one int32 on the GPU;
+// the append, selection and attention kernels read it when they start and derive from it what the host
+// otherwise passes as launch parameters.  len == nullptr: the launch parameters hold.
+struct DynLength {
+    const int32_t* len;   // tokens in the cache when the step began (before its append)
+    int offset;           // added to *len: the tokens this step has appended before the reading kernel runs
+    int top_k;            // >= 0: that many blocks (at most the complete ones); < 0: `share` of them
+    double share;         // fraction of the complete 64-token blocks that are selected
+    int sink, local;      // configured numbers of forced first / last blocks
+};
+
+__host__ __device__ inline long long round_half_even(double x) {
+#ifdef __CUDA_ARCH__
+    return __double2ll_rn(x);
+#else
+    const double f = static_cast<double>(static_cast<long long>(x));   // x >= 0 here
+    const double r = x - f;
+    long long v = static_cast<long long>(f);
+    if (r > 0.5 || (r == 0.5 && (v & 1))) ++v;
+    return v;
+#endif
+}
+
+// Blocks scored (n), selected by score (k) and forced (sink, local) for `tokens` cached tokens: the rule of the
+// cache's decode step - k = top_k or max(1, round-half-even(share * n)) capped by n; the last `local` and first
+// `sink` blocks are forced as far as n - k leaves room, local first; nothing is forced when k == 0.
+__host__ __device__ inline void dyn_select_counts(const DynLength& d, int tokens, int max_blocks, int& n, int& k, int& sink,
+                                                  int& local) {
+    n = tokens / 64;
+    if (n > max_blocks) n = max_blocks;
+    if (n < 0) n = 0;
+    if (d.top_k >= 0) k = d.top_k < n ? d.top_k : n;
+    else if (n <= 0 || !(d.share > 0.0)) k = 0;
+    else if (d.share >= 1.0) k = n;
+    else {
+        long long r = round_half_even(d.share * static_cast<double>(n));
+        if (r > n) r = n;
+        if (r < 1) r = 1;
+        k = static_cast<int>(r);
+    }
+    local = d.local < n - k ? d.local : n - k;
+    if (local < 0) local = 0;
+    sink = d.sink < n - k - local ? d.sink : n - k - local;
+    if (sink < 0) sink = 0;
+    if (k == 0) { sink = 0; local = 0; }
+}
+
 // Row permutation inside every group of 32 rows used by the "permuted" K layout.
 __host__ __device__ constexpr int perm32(int x) { return (x / 8) * 2 + ((x % 8) / 2) * 8 + (x % 2); }
 

@@ -492,10 +492,16 @@ __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const ui
                                                                         const uint16_t* __restrict__ ka,
                                                                         const uint16_t* __restrict__ kb,
                                                                         int32_t* __restrict__ out,
-                                                                        float* __restrict__ out_scores, int group, int nk,
-                                                                        int cap_blocks, int k, int sink, int local,
-                                                                        int out_stride) {
+                                                                        float* __restrict__ out_scores, int group,
+                                                                        int nk_arg, int cap_blocks, int k_arg, int sink_arg,
+                                                                        int local_arg, int out_stride, const DynLength dyn) {
     using L = SeldSmem<D>;
+    // block counts: launch parameters, or derived from the sequence length in device memory
+    int nk = nk_arg, k = k_arg, sink = sink_arg, local = local_arg;
+    if (dyn.len != nullptr) {
+        dyn_select_counts(dyn, max(0, __ldg(dyn.len) + dyn.offset), min(cap_blocks, 2048), nk, k, sink, local);
+        k = min(k, max(0, out_stride - sink - local));   // the host sizes the rows for the longest sequence
+    }
     constexpr int VEC = D / 8;            // 16-byte chunks per statistics row
     constexpr int NARR = QUEST ? 2 : 1;
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -888,16 +894,27 @@ int select_prefill_dispatch(const void* q_mean, const void* ka, const void* kb, 
     return static_cast<int>(cudaGetLastError());
 }
 
+// dyn (may be null): the block counts come from a sequence length in device memory; nk is then the largest block
+// count the launch has to cope with, k / sink / local are ignored and out_stride (> 0) is the row width.
 int select_decode_dispatch(const void* q, const void* ka, const void* kb, void* out, void* out_scores, int flat_heads, int group, int nk,
                            int cap_blocks, int d, int k, int quest, int is_bf16, int sink, int local, int out_stride,
-                           cudaStream_t stream) {
+                           const DynLength* dyn, cudaStream_t stream) {
     if (!q || !ka || !out || (quest && !kb)) return TA100_ERR_NULL;
+    DynLength dl{};
+    if (dyn && dyn->len) {
+        dl = *dyn;
+        if (out_stride <= 0 || dl.sink < 0 || dl.local < 0) return TA100_ERR_SHAPE;
+        int n = 0, kk = 0, sk = 0, lc = 0;
+        dyn_select_counts(dl, nk * 64, cap_blocks < 2048 ? cap_blocks : 2048, n, kk, sk, lc);
+        if (out_stride < kk + dl.sink + dl.local) return TA100_ERR_SHAPE;   // counts only grow with the length
+        k = kk; sink = 0; local = 0;
+    }
     if (out_stride == 0) out_stride = sink + local + k;
     if (out_stride < sink + local + k) return TA100_ERR_SHAPE;
     if (d != 64 && d != 128) return TA100_ERR_UNSUPPORTED;
     if (nk > 2048 || nk < 0 || k < 0 || nk > cap_blocks || group <= 0) return TA100_ERR_SHAPE;
-    if ((sink + local) == 0 && k > nk) return TA100_ERR_SHAPE;
-    if (sink + local + k == 0 || flat_heads == 0) return TA100_OK;
+    if (!dl.len && (sink + local) == 0 && k > nk) return TA100_ERR_SHAPE;
+    if (flat_heads == 0 || (!dl.len && sink + local + k == 0)) return TA100_OK;
     if (group > SELD_MAX_GROUP) return TA100_ERR_LIMIT;
 #define TA100_SELD(DD, BFF, QQ)                                                                                \
     do {                                                                                                       \
@@ -906,7 +923,7 @@ int select_decode_dispatch(const void* q, const void* ka, const void* kb, void* 
         select_decode_kernel<DD, BFF, QQ><<<flat_heads, SELD_THREADS, smem, stream>>>(                         \
             static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(ka), static_cast<const uint16_t*>(kb), \
             static_cast<int32_t*>(out), static_cast<float*>(out_scores), group, nk, cap_blocks, k, sink, local, \
-            out_stride);                                                                                       \
+            out_stride, dl);                                                                                   \
     } while (0)
     if (d == 128) {
         if (is_bf16) { if (quest) TA100_SELD(128, true, true); else TA100_SELD(128, true, false); }

@@ -322,6 +322,14 @@ class ThriftAttentionCacheLayer:
         self._append(None, None, start, k_count=end - start, v_count=0, keep_k=True)
 
     # ---------------------------------------------------------------------------------------- capacity
+    def reserve(self, tokens: int) -> None:
+        """Room for ``tokens`` tokens now, so that later appends neither move nor re-allocate anything (what a
+        generation step captured in a CUDA graph needs).  The layer must already hold its first tokens."""
+        if self.k_fp16 is None:
+            raise RuntimeError("ThriftAttention cache layer has not been initialized")
+        b, h, _, d = self.k_fp16.shape
+        self._ensure_capacity(torch.empty(b, h, 0, d, dtype=self.k_fp16.dtype, device=self.k_fp16.device), tokens)
+
     def _ensure_capacity(self, like: torch.Tensor, required: int) -> None:
         """Allocate or grow every tensor to hold ``required`` tokens.  The first allocation takes
         ``max_cache_len`` when it is known, else 64 tokens; later ones double; the result is rounded up to
@@ -477,7 +485,20 @@ class PagedThriftAttentionCacheLayer(ThriftAttentionCacheLayer):
         for b, row in enumerate(self._pages):
             if row:
                 host[b, : len(row)] = torch.tensor(row, dtype=torch.int32)
-        self.page_table = host.to(self.k_pool.device)
+        if self.page_table is not None and tuple(self.page_table.shape) == tuple(host.shape):
+            self.page_table.copy_(host)      # in place: launches captured in a CUDA graph keep reading this tensor
+        else:
+            self.page_table = host.to(self.k_pool.device)
+
+    def reserve(self, tokens: int) -> None:
+        """Pages for ``tokens`` tokens per sequence now (taken from the pool and entered in the page table), so that
+        later appends change nothing on the host side.  The layer must already hold its first tokens."""
+        if self.k_pool is None:
+            raise RuntimeError("ThriftAttention cache layer has not been initialized")
+        _, h, _, d = self.k_pool.shape
+        capacity = self.capacity
+        self._ensure_capacity(torch.empty(len(self._pages), h, 0, d, dtype=self.k_pool.dtype, device=self.k_pool.device), tokens)
+        self.capacity = max(capacity, self.capacity)
 
     def _ensure_capacity(self, like: torch.Tensor, required: int) -> None:
         batch, heads, _, head_dim = like.shape
@@ -894,6 +915,54 @@ def _fused_decode_step(q_grouped: torch.Tensor, layer: ThriftAttentionCacheLayer
                                       n_select_blocks=complete_blocks, top_k=selected_count, sink=sink, local=local,
                                       is_mx=fmt == "mxfp4", sel_out=layer.selected_blocks)
     return out
+
+
+def device_length_decode_step(query: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
+                              cache: ThriftAttentionCache, layer_idx: int, config: AttentionConfig, length: torch.Tensor, *,
+                              max_len: int, splits: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One layer of one generation step with the sequence length kept ON THE GPU: stores the token's
+    ``key_states`` / ``value_states`` ``[B, Hkv, 1, D]`` at position ``length[0]`` of layer ``layer_idx`` and returns
+    the attention of ``query`` ``[B, Hq, 1, D]`` over the ``length[0] + 1`` cached tokens.
+
+    ``length`` is a one-element int32 CUDA tensor.  No launch depends on its value (the kernels read it), so the
+    calls of all layers followed by one ``advance_length(length, 1, max_len)`` can be captured in a CUDA graph once
+    and replayed for every token; the result is bit for bit the one of ``update`` + ``cached_decode_attention`` run
+    with the same chain count.  The reference keeps the length in Python (transformers_cache.py:64-84), which rules
+    that out.  Requirements: the layer holds its prompt (filled through ``update``) and room for ``max_len`` tokens
+    (``reserve``; ``max_len`` a multiple of 64); ``method="thrift"`` with block-mean or Quest selection over 64-token
+    blocks.  The layer's Python-side ``seq_len`` is not touched: set it from ``length`` when leaving the graph."""
+    layer = cache.layer(layer_idx)
+    quant_format = _layer_format(layer, config)
+    if config.method != "thrift" or config.selection not in ("block_mean", "quest") or config.block_size != PAGE:
+        raise ValueError("the device-length step supports method='thrift' with block_mean / quest selection and 64-token blocks")
+    paged = isinstance(layer, PagedThriftAttentionCacheLayer)
+    quest = config.selection == "quest"
+    stat_a, stat_b = (layer.k_min, layer.k_max) if quest else (layer.k_mean, None)
+    if stat_a is None or (quest and stat_b is None):
+        raise RuntimeError("ThriftAttention cache layer has not been initialized")
+    if paged:
+        bufs = (layer.k_pool, layer.v_pool, layer.k4_pool, layer.ks_pool, layer.v4_pool, layer.vs_pool)
+        table = layer.page_table
+        room = min(len(row) for row in layer._pages) * PAGE
+        layer._gathered = None
+    else:
+        bufs = (layer.k_fp16, layer.v_fp16, layer.k_packed, layer.k_scale, layer.v_packed_t, layer.v_scale_t)
+        table = None
+        room = layer.capacity
+    if max_len % PAGE != 0 or max_len <= 0 or room < max_len:
+        raise ValueError(f"the layer holds room for {room} tokens, max_len={max_len} asked (a multiple of {PAGE}): call reserve()")
+    q = query.contiguous()
+    q_grouped = _group_single_query(q, bufs[0].shape[1])
+    ext = get_extension()
+    is_mx = quant_format.name == "mxfp4"
+    ext.cache_append_at(key_states.contiguous(), value_states.contiguous(), *bufs, length, offset=0, page_table=table,
+                        k_mean=layer.k_mean, k_min=layer.k_min, k_max=layer.k_max, is_mx=is_mx, stat_block=PAGE)
+    grouped_out = None if out is None else _group_single_query(out, bufs[0].shape[1])
+    result, layer.selected_blocks = ext.cached_decode_step_at(
+        q_grouped, *bufs, stat_a, stat_b, length, offset=key_states.shape[2], max_len=max_len, top_k=config.top_k,
+        fraction=config.fraction, sink=getattr(config, "sink_blocks", 0), local=getattr(config, "local_blocks", 0),
+        is_mx=is_mx, splits=splits, sel_out=layer.selected_blocks, out=grouped_out, page_table=table)
+    return _ungroup_single_query(result, q.shape[1])
 
 
 def cached_prefill_attention(query: torch.Tensor, cache: ThriftAttentionCache, layer_idx: int,
