@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """End-to-end generation through the Transformers attention hook on a random-init decoder of the Llama-3-8B shape.
 
-  python benchmarks/run_hook_generation.py [--prompt 65536] [--new-tokens 256] [--layers 32]
+  python benchmarks/run_hook_generation.py [--prompt 65536] [--new-tokens 256] [--layers 32] [--paged] [--graph]
 
 Prefill of ``--prompt`` uniform-random token ids, then ``--new-tokens`` greedy decode steps over a
 ``ThriftAttentionCache`` (NVFP4, block-mean top-10 % of 64-token blocks), and the same weights with Transformers' own
@@ -24,7 +24,8 @@ import torch  # noqa: E402
 FRACTION = 0.10
 
 
-def run_hf(prompt_len: int, new_tokens: int, layers: int, fraction: float = FRACTION, paged: bool = False) -> None:
+def run_hf(prompt_len: int, new_tokens: int, layers: int, fraction: float = FRACTION, paged: bool = False,
+           graphed: bool = False) -> None:
     """End to end through the Transformers hook on a random-init decoder of the Llama-3-8B shape (d_model 4096,
     32 q / 8 kv heads x 128, SwiGLU 14336, RoPE theta 5e5, vocab 128256, fp16): prefill of `prompt_len` uniform
     random token ids, then `new_tokens` greedy decode steps over a ThriftAttentionCache, NVFP4 with the top 10 %
@@ -86,6 +87,42 @@ def run_hf(prompt_len: int, new_tokens: int, layers: int, fraction: float = FRAC
             assert torch.isfinite(out.logits).all()
             return ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])
 
+    def generate_graphed():
+        """Prefill as above, then the decode loop as ONE CUDA graph replayed per token: the cache keeps its length on
+        the GPU (enable_device_length), the graph holds a whole single-token forward pass plus the arg-max fed back."""
+        with torch.no_grad():
+            model.config._attn_implementation = name
+            prep = prepare_transformers_generation_cache(model, ids, max_new_tokens=new_tokens + 8, paged=paged)
+            cache = prep.past_key_values
+            with prep.activate():
+                out = model(input_ids=prep.input_ids, past_key_values=cache, cache_position=prep.cache_position, use_cache=True,
+                            logits_to_keep=1)
+                prep.trim_padding()
+                tok = out.logits[:, -1].argmax(-1, keepdim=True).clone()
+                cache.enable_device_length()
+
+                def step():
+                    pos = cache.device_positions()
+                    o = model(input_ids=tok, past_key_values=cache, cache_position=pos, position_ids=pos.view(1, 1), use_cache=True)
+                    tok.copy_(o.logits[:, -1].argmax(-1, keepdim=True))
+                    cache.advance_device_length()
+
+                step()
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    step()
+                for _ in range(3):
+                    graph.replay()
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+                ev[0].record()
+                for _ in range(new_tokens):
+                    graph.replay()
+                ev[1].record()
+                torch.cuda.synchronize()
+                assert cache.disable_device_length() == prompt_len + new_tokens + 4
+            return ev[0].elapsed_time(ev[1])
+
     exact, ours = [], []
     try:
         generate(False, keep=exact)                          # warm-up; its logits and tokens are the comparison's reference
@@ -96,6 +133,8 @@ def run_hf(prompt_len: int, new_tokens: int, layers: int, fraction: float = FRAC
     torch.cuda.empty_cache()
     generate(True, forced=[t for _, t in exact] if exact else None, keep=ours)   # warm-up (library handles, workspaces)
     pre, dec = generate(True)
+    torch.cuda.empty_cache()
+    dec_graph = generate_graphed() if graphed else None
     logits = None
     if exact:
         cos = [float(torch.nn.functional.cosine_similarity(a, b, dim=0)) for (a, _), (b, _) in zip(exact, ours)]
@@ -108,6 +147,7 @@ def run_hf(prompt_len: int, new_tokens: int, layers: int, fraction: float = FRAC
                 f"tokens + {new_tokens} greedy decode steps, NVFP4 + block-mean top-{fraction:.0%}" + (", paged cache" if paged else ""),
         "prefill_ms": pre, "prefill_tokens_per_s": prompt_len / pre * 1e3,
         "decode_ms_per_token": dec / new_tokens, "decode_tokens_per_s": new_tokens / dec * 1e3,
+        "graph_decode_ms_per_token": None if dec_graph is None else dec_graph / new_tokens,
         "sdpa_prefill_ms": pre_x, "sdpa_decode_ms_per_token": dec_x / new_tokens,
         "logits_vs_exact_attention": logits,
         "peak_memory_gib": torch.cuda.max_memory_allocated(device) / 2 ** 30}), flush=True)
@@ -120,8 +160,10 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--fraction", type=float, default=FRACTION, help="share of the key blocks kept in 16 bit (1.0: all of them)")
     ap.add_argument("--paged", action="store_true", help="keep the cache in page pools behind a page table")
+    ap.add_argument("--graph", action="store_true",
+                    help="also time the decode loop as one CUDA graph per token (cache length kept on the GPU)")
     args = ap.parse_args()
-    run_hf(args.prompt, args.new_tokens, args.layers, args.fraction, args.paged)
+    run_hf(args.prompt, args.new_tokens, args.layers, args.fraction, args.paged, args.graph)
 
 
 if __name__ == "__main__":

@@ -171,3 +171,71 @@ def test_hook_rejects_what_the_kernels_cannot_serve():
     assert out.shape == (1, 128, 4, 128) and weights is None and torch.isfinite(out).all()
 
 
+
+
+@pytest.mark.parametrize("paged", [False, True])
+def test_whole_model_decode_step_replays_from_one_cuda_graph(monkeypatch, paged):
+    """Device-length mode of the cache: ONE CUDA graph holds a single-token forward pass of the whole model (embedding,
+    every layer's projections, cache append and attention through the registered function, head, arg-max fed back as
+    the next input) and is replayed per token.  The logits of every step equal, bit for bit, those of the eager loop
+    over a second cache (Python-side lengths) that runs the attention kernel with the same chain count."""
+    from thriftattention_b200 import _C
+
+    name = register_transformers_attention(TransformersAttentionConfig(name="thrift_graph_test", fraction=0.25))
+    model = _tiny_llama(name)
+    prompt_len, new_tokens, chains = 300, 100, 2
+    ids = torch.randint(0, 512, (1, prompt_len), generator=torch.Generator().manual_seed(3)).to(DEV)
+    hkv = model.config.num_key_value_heads
+    for pages in range(1, 16):
+        monkeypatch.setitem(_C._decode_step_splits, (hkv, pages), min(chains, pages))
+
+    def prefill():
+        prep = prepare_transformers_generation_cache(model, ids, max_new_tokens=new_tokens + 8, paged=paged)
+        with prep.activate():
+            out = model(input_ids=prep.input_ids, past_key_values=prep.past_key_values, cache_position=prep.cache_position,
+                        use_cache=True, logits_to_keep=1)
+            prep.trim_padding()
+        return prep, out.logits[:, -1].argmax(-1, keepdim=True)
+
+    with torch.no_grad():
+        # eager loop, lengths in Python
+        prep, tok = prefill()
+        want = []
+        with prep.activate():
+            for step in range(new_tokens):
+                pos = torch.tensor([prompt_len + step], device=DEV)
+                out = model(input_ids=tok, past_key_values=prep.past_key_values, cache_position=pos,
+                            position_ids=pos.view(1, 1), use_cache=True)
+                want.append(out.logits[0, -1].clone())
+                tok = out.logits[:, -1].argmax(-1, keepdim=True)
+
+        # graph loop, length on the GPU
+        prep, tok = prefill()
+        cache = prep.past_key_values
+        cache.enable_device_length(splits=chains)
+        static_tok = tok.clone()
+        logits_buf = torch.zeros(512, device=DEV, dtype=torch.float16)
+
+        def step():
+            pos = cache.device_positions()
+            out = model(input_ids=static_tok, past_key_values=cache, cache_position=pos, position_ids=pos.view(1, 1),
+                        use_cache=True)
+            logits_buf.copy_(out.logits[0, -1])
+            static_tok.copy_(out.logits[:, -1].argmax(-1, keepdim=True))
+            cache.advance_device_length()
+
+        got = []
+        with prep.activate():
+            step()                                   # eager, in device-length mode: libraries warm, first token
+            got.append(logits_buf.clone())
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            for _ in range(new_tokens - 1):
+                graph.replay()
+                got.append(logits_buf.clone())
+        assert cache.disable_device_length() == prompt_len + new_tokens
+    for i, (a, b) in enumerate(zip(want, got)):
+        assert torch.equal(a, b), f"decode step {i}"
+    _C.decode_status(torch.device(DEV))

@@ -700,6 +700,78 @@ class ThriftAttentionCache:
         self.layers: list[ThriftAttentionCacheLayer] = []
         self._seen_tokens = 0
         self.prefill_real_seq_len: int | None = None
+        # device-length mode (enable_device_length): the number of cached tokens lives in this one-element int32
+        # CUDA tensor and the decode launches no longer depend on it
+        self.device_length: torch.Tensor | None = None
+        self.device_max_len = 0
+        self.device_splits: int | None = None
+
+    # ------------------------------------------------------------------------- length in device memory
+    def enable_device_length(self, max_len: int | None = None, splits: int | None = None) -> torch.Tensor:
+        """Switch the decode steps of this cache to a sequence length kept ON THE GPU, so that a whole single-token
+        forward pass of the model - every layer's append + attention through the registered attention function - can
+        be captured in a CUDA graph once and replayed for every token.
+
+        Call it after the prefill.  Every layer gets room for ``max_len`` tokens now (default: ``max_cache_len``
+        rounded up to whole 64-token pages).  From here on ``update`` with one new token (while this cache is the
+        active one) stores nothing and hands the new rows on, and the attention function appends and attends through
+        ``device_length_decode_step``; the caller feeds the model ``position_ids`` / ``cache_position`` derived from
+        the returned tensor (``device_positions``) and ends every forward pass with ``advance_device_length()``.
+        The Python-side lengths go stale meanwhile; ``sync_device_length`` / ``disable_device_length`` refresh them.
+        An attention mask handed to a single-token step is ignored in this mode (all sequences of the cache have the
+        same length, every cached token is visible).
+        ``splits``: chains per KV head of the attention kernel (default: the choice for ``max_len``)."""
+        if not self.layers or self.layers[0].seq_len == 0:
+            raise RuntimeError("enable_device_length needs a filled cache (call it after the prefill)")
+        tokens = self.layers[0].seq_len
+        if any(layer.seq_len != tokens for layer in self.layers):
+            raise RuntimeError("the layers of the cache hold different numbers of tokens")
+        if max_len is None:
+            if self._max_cache_len is None:
+                raise ValueError("enable_device_length needs max_len or a cache built with max_cache_len")
+            max_len = self._max_cache_len
+        max_len = _round_up(int(max_len), PAGE)
+        if max_len < tokens:
+            raise ValueError(f"max_len={max_len} is below the {tokens} tokens already cached")
+        for layer in self.layers:
+            layer.reserve(max_len)
+        first = self.layers[0]
+        device = (first.k_pool if isinstance(first, PagedThriftAttentionCacheLayer) else first.k_fp16).device
+        self.device_length = torch.tensor([tokens], dtype=torch.int32, device=device)
+        self.device_max_len = max_len
+        self.device_splits = splits
+        return self.device_length
+
+    def device_positions(self) -> torch.Tensor:
+        """``cache_position`` of the next token, ``[1]`` int64, computed on the GPU from the device-side length
+        (``.view(1, 1)`` of it is the ``position_ids`` of a batch whose sequences have the same length)."""
+        if self.device_length is None:
+            raise RuntimeError("the cache is not in device-length mode")
+        return self.device_length.to(torch.long)
+
+    def advance_device_length(self, count: int = 1) -> None:
+        """End of a forward pass in device-length mode: length += count (one tiny launch, capturable)."""
+        if self.device_length is None:
+            raise RuntimeError("the cache is not in device-length mode")
+        get_extension().advance_length(self.device_length, count, self.device_max_len)
+
+    def sync_device_length(self) -> int:
+        """Read the device-side length back (a synchronisation) and bring the Python-side lengths up to date."""
+        if self.device_length is None:
+            raise RuntimeError("the cache is not in device-length mode")
+        tokens = int(self.device_length.item())
+        for layer in self.layers:
+            layer.seq_len = tokens
+            if isinstance(layer, PagedThriftAttentionCacheLayer):
+                layer._gathered = None
+        self._seen_tokens = tokens
+        return tokens
+
+    def disable_device_length(self) -> int:
+        """Back to lengths kept in Python; returns the number of cached tokens."""
+        tokens = self.sync_device_length()
+        self.device_length = None
+        return tokens
 
     @classmethod
     def from_model(cls, model: object, *, config: AttentionConfig | None = None,
@@ -745,6 +817,11 @@ class ThriftAttentionCache:
         if layer_idx is None:
             raise ValueError("ThriftAttentionCache.update requires layer_idx")
         layer = self.layer(layer_idx)
+        if (self.device_length is not None and key_states.shape[2] == 1 and layer.seq_len > 0
+                and get_active_thriftattention_cache() is self):
+            # device-length mode: the registered attention function appends these rows itself, at the position it
+            # reads on the GPU (device_length_decode_step)
+            return key_states, value_states
         if self.paged and get_active_thriftattention_cache() is self:
             # the registered attention function reads the pools in place: spare the gather of the full K/V
             cache_kwargs = dict(cache_kwargs or {}, thrift_return_new_states=True)
