@@ -49,9 +49,8 @@ constexpr int DEC_SLOT16_BYTES = 16384; //   one K or V page
 constexpr int DEC_RING_BYTES = 49152;
 static_assert(DEC_NS4 * DEC_SLOT4_BYTES <= DEC_RING_BYTES && DEC_NS16 * DEC_SLOT16_BYTES <= DEC_RING_BYTES, "ring size");
 static_assert(DEC_SLOT4_BYTES % 512 == 0, "FP4 slots keep the 64-byte-swizzle alignment");
-constexpr int DEC_SF_AHEAD = 2;         // pages between the request for an FP4 page's block scales and their use
 constexpr int DEC_LIST_CAP = 1024;      // pages per chain
-static_assert(DEC_LIST_CAP * 4 <= DEC_RING_BYTES, "the idle page ring stages a chain's page-table entries");
+static_assert(2 * DEC_LIST_CAP * 4 <= DEC_RING_BYTES, "the idle page ring stages a chain's page-table entries and 16-bit keys");
 constexpr int DEC_MAX_GROUP = 16;
 
 // tensor-memory columns (256 allocated per CTA)
@@ -162,9 +161,10 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 // pool, the logical page for a contiguous cache — with L_FP16 set on 16-bit pages.
 // A page-table entry outside [0, pool_pages) never becomes a key: the page is left out of the chain
 // (nothing is read for it) and *bad_entry is raised so that the host learns of it.
-// `stage` (shared memory, p_end - p_begin words) receives the chain's page-table entries in one sweep of independent
-// loads before the two passes read them: fetched inside the passes, every 32 pages would cost a round trip to
-// global memory (the ballot keeps the loads of consecutive iterations from overlapping).
+// `stage` (shared memory, 2 x DEC_LIST_CAP words) first receives the chain's page-table entries in one sweep of
+// independent loads (fetched inside the sweep below, every 32 pages would cost a round trip to global memory); its
+// second half collects the keys of the selected pages while one sweep over the pages writes the FP4 keys straight
+// into the list, and is appended to the list at the end.
 __device__ void build_page_list(const DecodeParams& p, int h, int b, int kvh, int p_begin, int p_end, uint32_t* bits,
                                 uint32_t* list, int32_t* stage, int& n_fp4, int& n_total, int lane, int* bad_entry) {
     for (int i = lane; i < 64; i += 32) bits[i] = 0u;
@@ -179,30 +179,34 @@ __device__ void build_page_list(const DecodeParams& p, int h, int b, int kvh, in
         if (id >= p_begin && id < p_end) atomicOr(&bits[id >> 5], 1u << (id & 31));
     }
     __syncwarp();
-    int n = 0;
-    for (int pass = 0; pass < 2; ++pass) {
-        for (int base = p_begin; base < p_end; base += 32) {
-            const int pg = base + lane;
-            const bool valid = pg < p_end;
-            const bool is_sel = valid && ((bits[pg >> 5] >> (pg & 31)) & 1u);
-            bool take = valid && (is_sel == (pass == 1));
-            uint32_t key = static_cast<uint32_t>(pg);
-            if (take && p.page_table) {
-                const int entry = stage[pg - p_begin];
-                if (entry < 0 || entry >= p.pool_pages) {
-                    take = false;
-                    *bad_entry = 1;
-                } else {
-                    key = static_cast<uint32_t>(entry) * static_cast<uint32_t>(p.hkv) + static_cast<uint32_t>(kvh);
-                }
+    uint32_t* hi = reinterpret_cast<uint32_t*>(stage) + DEC_LIST_CAP;
+    const uint32_t below = (1u << lane) - 1u;
+    int n4 = 0, n16 = 0;
+    for (int base = p_begin; base < p_end; base += 32) {
+        const int pg = base + lane;
+        bool take = pg < p_end;
+        const bool is_sel = take && ((bits[pg >> 5] >> (pg & 31)) & 1u);
+        uint32_t key = static_cast<uint32_t>(pg);
+        if (take && p.page_table) {
+            const int entry = stage[pg - p_begin];
+            if (entry < 0 || entry >= p.pool_pages) {
+                take = false;
+                *bad_entry = 1;
+            } else {
+                key = static_cast<uint32_t>(entry) * static_cast<uint32_t>(p.hkv) + static_cast<uint32_t>(kvh);
             }
-            const uint32_t mask = __ballot_sync(0xFFFFFFFFu, take);
-            if (take) list[n + __popc(mask & ((1u << lane) - 1u))] = key | (pass ? L_FP16 : 0u);
-            n += __popc(mask);
         }
-        if (pass == 0) n_fp4 = n;
+        const uint32_t m4 = __ballot_sync(0xFFFFFFFFu, take && !is_sel);
+        const uint32_t m16 = __ballot_sync(0xFFFFFFFFu, take && is_sel);
+        if (take && !is_sel) list[n4 + __popc(m4 & below)] = key;
+        if (take && is_sel) hi[n16 + __popc(m16 & below)] = key | L_FP16;
+        n4 += __popc(m4);
+        n16 += __popc(m16);
     }
-    n_total = n;
+    __syncwarp();
+    for (int i = lane; i < n16; i += 32) list[n4 + i] = hi[i];
+    n_fp4 = n4;
+    n_total = n4 + n16;
 }
 
 template <int D, bool MX, bool BF16>
@@ -290,7 +294,7 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
             if (p.width > 0) { tma_prefetch_desc(&mapK16); tma_prefetch_desc(&mapV16); }
         }
         int n_fp4 = 0, n = 0;
-        // the page ring is idle until the first copy below: its first 4 KB stage the page-table entries
+        // the page ring is idle until the first copy below: its first 8 KB serve the list builder as scratch
         build_page_list(p, h, b, kvh, p_begin, p_end, reinterpret_cast<uint32_t*>(smem + L::BITS), list,
                         reinterpret_cast<int32_t*>(smem + L::SLOTS), n_fp4, n, lane, &bars.bad_entry);
         if (lane == 0) { bars.n_fp4 = n_fp4; bars.n_total = n; }
@@ -298,7 +302,7 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
         fence_proxy_async_smem();    // the staged entries were written and read through the generic proxy; copies follow
         __threadfence_block();
         if (lane == 0) mbar_arrive(smem_u32(&bars.list_full));
-        // ---- FP4 pages: TMA for the codes; the lanes fetch the page's block scales DEC_SF_AHEAD pages ahead and store
+        // ---- FP4 pages: TMA for the codes; the lanes fetch the page's block scales two pages ahead and store
         //      them in atom order (word m0 * 4 + m1 holds the scales of row / channel 32 * m1 + m0) ----
         // K scales: D / GRP bytes per token row = KROW_WORDS 32-bit words (one 16-bit word for MXFP4 at D = 64);
         // V scales: PAGE / GRP bytes per channel row and page (4 NVFP4, 2 MXFP4)
@@ -358,22 +362,20 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
         };
         bool ok = !p.skip_loads;   // diagnostics: with skip_loads nothing is copied and the consumers' bounded waits run out
         if (ok) {
-            // the scales of page i + DEC_SF_AHEAD are requested when page i is handed over (measured: one or two pages
-            // ahead give the same step time, three or four are 3 % slower - this warp is not what limits a chain)
-            uint32_t kw[DEC_SF_AHEAD][4], vw[DEC_SF_AHEAD][4];
-#pragma unroll
-            for (int j = 0; j < DEC_SF_AHEAD; ++j) {
-#pragma unroll
-                for (int w = 0; w < 4; ++w) { kw[j][w] = 0u; vw[j][w] = 0u; }
-                load_sf(j, kw[j], vw[j]);
-            }
-            for (int i = 0; i < n_fp4 && ok; i += DEC_SF_AHEAD) {
-#pragma unroll
-                for (int j = 0; j < DEC_SF_AHEAD; ++j) {
-                    if (ok && i + j < n_fp4) {
-                        ok = fp4_step(i + j, kw[j], vw[j]);
-                        if (ok) load_sf(i + j + DEC_SF_AHEAD, kw[j], vw[j]);
-                    }
+            // the scales of page i + 2 are requested when page i is handed over.  Measured: requests three or four
+            // pages ahead make the step 3 - 11 % slower, and so does this loop written over an array of register sets
+            // instead of the two named ones - keep it as it is.
+            uint32_t kwa[4] = {0, 0, 0, 0}, vwa[4] = {0, 0, 0, 0}, kwb[4] = {0, 0, 0, 0}, vwb[4] = {0, 0, 0, 0};
+            load_sf(0, kwa, vwa);
+            load_sf(1, kwb, vwb);
+            for (int i = 0; i < n_fp4 && ok; i += 2) {
+                ok = fp4_step(i, kwa, vwa);
+                if (!ok) break;
+                load_sf(i + 2, kwa, vwa);
+                if (i + 1 < n_fp4) {
+                    ok = fp4_step(i + 1, kwb, vwb);
+                    if (!ok) break;
+                    load_sf(i + 3, kwb, vwb);
                 }
             }
         }
