@@ -369,29 +369,30 @@ int ta100_cached_decode_step_paged(const void* q, void* q4, void* qs, const void
 /*
  * A generation step whose launches do not change from token to token.
  *
- * The three entries below read the number of cached tokens from ONE int32 in device memory (len_dev) instead of
+ * The three entries below read the number of cached tokens from device memory (len_dev: ONE int32 for the whole
+ * batch with len_count = 1, or one per sequence with len_count = batch - a ragged batch) instead of
  * taking it as an argument, so that append + decode step of every layer, captured once in a CUDA graph, replay for
  * every later token: nothing on the host depends on the length any more (with a paged cache the page table is the
  * only other thing that changes, once per 64 tokens, in place).  A step is
- *     for every layer: ta100_cache_append_at(.., len_dev, 0, 1, 1, ..); ta100_cached_decode_step_at(.., len_dev, 1, ..)
- *     ta100_advance_length(len_dev, 1, capacity)
+ *     for every layer: ta100_cache_append_at(.., len_dev, n, 0, 1, 1, ..); ta100_cached_decode_step_at(.., len_dev, n, 1, ..)
+ *     ta100_advance_length(len_dev, n, 1, capacity)
  * and computes bit for bit what ta100_cache_append[_paged] + ta100_cached_decode_step[_paged] compute when they are
  * given the same length, block counts and chain count as launch parameters.
  * No counterpart in the reference, whose cache keeps its length in Python (transformers_cache.py:64-84).
  *
  * ta100_cache_append_at: the append of ta100_cache_append (page_table NULL; capacity = tokens per head of the slabs)
- * or ta100_cache_append_paged (page_table given; capacity ignored) at position *start_dev + start_offset.  A range
- * that would end beyond the capacity is not stored at all.
+ * or ta100_cache_append_paged (page_table given; capacity ignored) at position start_dev[sequence or 0] +
+ * start_offset.  A range that would end beyond the capacity is not stored at all.
  */
 int ta100_cache_append_at(const void* k_new, const void* v_new, void* k_hi, void* v_hi, void* k_codes, void* k_scales,
                           void* v_codes, void* v_scales, void* k_mean, void* k_min, void* k_max, const void* page_table,
                           int max_pages, int pool_pages, int batch, int hkv, int stat_blocks, int capacity,
-                          const void* start_dev, int start_offset, int k_count, int v_count, int head_dim, int stat_block,
-                          int is_mxfp4, int is_bf16, int flags, void* stream);
+                          const void* start_dev, int start_count, int start_offset, int k_count, int v_count, int head_dim,
+                          int stat_block, int is_mxfp4, int is_bf16, int flags, void* stream);
 
 /*
  * ta100_cached_decode_step_at: the step of ta100_cached_decode_step (page_table NULL) or _paged over
- * tokens = *len_dev + len_offset cached tokens.  On the device: the kernel length is tokens rounded up to whole pages
+ * tokens = len_dev[sequence or 0] + len_offset cached tokens.  On the device: the kernel length is tokens rounded up to whole pages
  * (at least one), the blocks scored are the complete ones, n = tokens / 64; top_k >= 0 selects min(top_k, n) of
  * them, top_k < 0 selects max(1, round-half-even(fraction * n)) (0 when n == 0); the last `local` and then the first
  * `sink` blocks are forced as far as n minus the selected count leaves room (none when nothing is selected) - the
@@ -408,11 +409,12 @@ int ta100_cached_decode_step_at(const void* q, void* q4, void* qs, const void* k
                                 const void* ks, const void* v4, const void* vs, const void* page_table, int max_pages,
                                 int pool_pages, const void* stat_a, const void* stat_b, void* sel, int sel_stride, void* out,
                                 void* part_o, void* part_ml, int batch, int hkv, int group, const void* len_dev,
-                                int len_offset, int max_len, int kv_cap, int stat_cap_blocks, int top_k, double fraction,
-                                int sink, int local, int head_dim, int is_mxfp4, int is_bf16, int splits, void* stream);
+                                int len_count, int len_offset, int max_len, int kv_cap, int stat_cap_blocks, int top_k,
+                                double fraction, int sink, int local, int head_dim, int is_mxfp4, int is_bf16, int splits,
+                                void* stream);
 
-/* *len_dev = min(*len_dev + count, limit), in stream order: the end of a step. */
-int ta100_advance_length(void* len_dev, int count, int limit, void* stream);
+/* len_dev[i] = min(len_dev[i] + count, limit) for i < len_count, in stream order: the end of a step. */
+int ta100_advance_length(void* len_dev, int len_count, int count, int limit, void* stream);
 
 /*
  * The merge of one producer's chains that stays a partial: part_o [flat_kv_heads, splits, group, D],

@@ -47,15 +47,17 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert lib.ta100_prefill_workspace_bytes(1, 32, 8, 131072, 131072, 128, 0) > 0
     assert lib.ta100_decode_workspace_bytes(256, 4, 128, 16) == 256 * 16 * 4 * 130 * 4
     # the entries that read the sequence length from device memory insist on that pointer (and its alignment)
-    assert lib.ta100_advance_length(None, 1, 128, None) == -1
-    assert lib.ta100_cache_append_at(p, p, p, p, p, p, p, p, None, None, None, None, 0, 0, 1, 1, 1, 128, None, 0, 1, 1, 128, 64,
+    assert lib.ta100_advance_length(None, 1, 1, 128, None) == -1
+    assert lib.ta100_cache_append_at(p, p, p, p, p, p, p, p, None, None, None, None, 0, 0, 1, 1, 1, 128, None, 1, 0, 1, 1, 128, 64,
                                      0, 0, 0, None) == -1
     odd = ctypes.c_void_p(p.value + 2)
-    assert lib.ta100_cache_append_at(p, p, p, p, p, p, p, p, None, None, None, None, 0, 0, 1, 1, 1, 128, odd, 0, 1, 1, 128, 64,
+    assert lib.ta100_cache_append_at(p, p, p, p, p, p, p, p, None, None, None, None, 0, 0, 1, 1, 1, 128, odd, 1, 0, 1, 1, 128, 64,
                                      0, 0, 0, None) == -4
-    assert lib.ta100_cached_decode_step_at(p, p, p, p, p, p, p, p, p, None, 0, 0, p, None, p, 4, p, p, p, 1, 1, 4, None, 1, 128,
+    assert lib.ta100_cache_append_at(p, p, p, p, p, p, p, p, None, None, None, None, 0, 0, 2, 1, 1, 128, p, 3, 0, 1, 1, 128, 64,
+                                     0, 0, 0, None) == -2      # three lengths for a batch of two
+    assert lib.ta100_cached_decode_step_at(p, p, p, p, p, p, p, p, p, None, 0, 0, p, None, p, 4, p, p, p, 1, 1, 4, None, 1, 1, 128,
                                            128, 2, 1, 0.0, 0, 0, 128, 0, 0, 1, None) == -1
-    assert lib.ta100_cached_decode_step_at(p, p, p, p, p, p, p, p, p, None, 0, 0, p, None, p, 4, p, p, p, 1, 1, 4, p, 1, 100,
+    assert lib.ta100_cached_decode_step_at(p, p, p, p, p, p, p, p, p, None, 0, 0, p, None, p, 4, p, p, p, 1, 1, 4, p, 1, 1, 100,
                                            128, 2, 1, 0.0, 0, 0, 128, 0, 0, 1, None) == -2      # max_len not in whole pages
 
 

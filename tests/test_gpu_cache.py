@@ -475,3 +475,80 @@ def test_device_length_append_beyond_the_capacity_stores_nothing():
     assert int(length.item()) == 128
     for n, t in _layer_buffers(layer).items():
         assert torch.equal(t.view(torch.uint8), before[n].view(torch.uint8)), n
+
+
+@pytest.mark.parametrize("paged", [False, True])
+def test_ragged_batch_with_one_device_length_per_sequence(monkeypatch, paged):
+    """Three sequences of different lengths in one batch, their lengths in an int32 tensor on the GPU: one graph of
+    append + decode step serves them all, and every sequence gets, token by token, the bytes of the host-length calls
+    made for that sequence alone."""
+    from thriftattention_b200 import _C
+
+    torch.manual_seed(9)
+    b, hkv, g, d, max_len, chains, steps = 3, 2, 4, 128, 1024, 3, 70
+    prompts = [30, 250, 601]
+    dtype = torch.float16
+    cfg = ta.AttentionConfig(selection="quest", fraction=0.2, quant_format="nvfp4", sink_blocks=1, local_blocks=2)
+    # the batch cache (its Python-side length is not used) and one reference cache per sequence
+    batch_cache = ta.ThriftAttentionCache(config=cfg, max_cache_len=max_len, paged=paged)
+    refs = [ta.ThriftAttentionCache(config=cfg, max_cache_len=max_len, paged=paged) for _ in range(b)]
+    longest = max(prompts)
+    k0 = torch.randn(b, hkv, longest, d, device=DEV).to(dtype)
+    v0 = torch.randn(b, hkv, longest, d, device=DEV).to(dtype)
+    batch_cache.update(torch.zeros_like(k0[:, :, :1]), torch.zeros_like(v0[:, :, :1]), 0)     # allocates the layer
+    layer = batch_cache.layer(0)
+    layer.reserve(max_len)
+    bufs = ((layer.k_pool, layer.v_pool, layer.k4_pool, layer.ks_pool, layer.v4_pool, layer.vs_pool) if paged else
+            (layer.k_fp16, layer.v_fp16, layer.k_packed, layer.k_scale, layer.v_packed_t, layer.v_scale_t))
+    table = layer.page_table if paged else None
+    stats = dict(k_mean=layer.k_mean, k_min=layer.k_min, k_max=layer.k_max)
+    # prompts: sequence i alone, through the host-length append on its own slice of the batch cache
+    for i, n in enumerate(prompts):
+        refs[i].update(k0[i:i + 1, :, :n], v0[i:i + 1, :, :n], 0)
+        sl = {name: t[i:i + 1] for name, t in stats.items() if t is not None}
+        if paged:
+            _C.cache_append_paged(k0[i:i + 1, :, :n].contiguous(), v0[i:i + 1, :, :n].contiguous(), *bufs, table[i:i + 1], start=0,
+                                  is_mx=False, stat_block=64, **sl)
+        else:
+            _C.cache_append(k0[i:i + 1, :, :n].contiguous(), v0[i:i + 1, :, :n].contiguous(), *[t[i:i + 1] for t in bufs], start=0,
+                            is_mx=False, stat_block=64, **sl)
+    for pages in range(1, max_len // 64 + 1):
+        monkeypatch.setitem(_C._decode_step_splits, (hkv, pages), min(chains, pages))
+
+    lengths = torch.tensor(prompts, dtype=torch.int32, device=DEV)
+    q_in = torch.zeros(b, hkv, g, d, device=DEV, dtype=dtype)
+    k_in = torch.zeros(b, hkv, 1, d, device=DEV, dtype=dtype)
+    v_in = torch.zeros(b, hkv, 1, d, device=DEV, dtype=dtype)
+    out_buf = torch.zeros(b, hkv, g, d, device=DEV, dtype=dtype)
+    sel_buf = None
+
+    def step():
+        nonlocal sel_buf
+        _C.cache_append_at(k_in, v_in, *bufs, lengths, offset=0, page_table=table, is_mx=False, stat_block=64, **stats)
+        _, sel_buf = _C.cached_decode_step_at(q_in, *bufs, layer.k_min, layer.k_max, lengths, offset=1, max_len=max_len,
+                                              fraction=0.2, sink=1, local=2, is_mx=False, splits=chains, sel_out=sel_buf,
+                                              out=out_buf, page_table=table)
+        _C.advance_length(lengths, 1, max_len)
+
+    saved = {i: t.clone() for i, t in enumerate(list(bufs) + [t for t in stats.values() if t is not None])}
+    step()                                                  # eager once (kernel attributes, scratch), then undo it
+    torch.cuda.synchronize()
+    for i, t in enumerate(list(bufs) + [t for t in stats.values() if t is not None]):
+        t.view(torch.uint8).copy_(saved[i].view(torch.uint8))
+    lengths.copy_(torch.tensor(prompts, dtype=torch.int32))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+
+    for t in range(steps):
+        q = torch.randn(b, hkv * g, 1, d, device=DEV).to(dtype)
+        k1 = torch.randn(b, hkv, 1, d, device=DEV).to(dtype)
+        v1 = torch.randn(b, hkv, 1, d, device=DEV).to(dtype)
+        q_in.copy_(q.reshape(b, hkv, g, d)); k_in.copy_(k1); v_in.copy_(v1)
+        graph.replay()
+        for i in range(b):
+            refs[i].update(k1[i:i + 1], v1[i:i + 1], 0)
+            want = tc.cached_decode_attention(q[i:i + 1], refs[i], 0, cfg)
+            assert torch.equal(out_buf[i].reshape(1, hkv * g, 1, d), want), f"sequence {i}, token {prompts[i] + t}"
+    assert lengths.tolist() == [n + steps for n in prompts]
+    _C.decode_status(DEV)

@@ -765,20 +765,23 @@ def cached_decode_step(q_grouped, k_hi, v_hi, k_packed, k_scale, v_packed_t, v_s
     return out, sel_out
 
 
-def _check_length(length: torch.Tensor, device) -> None:
+def _check_length(length: torch.Tensor, device, batch: int | None = None) -> int:
+    """The device-side length: int32 on the cache's device, one element (every sequence has that length) or one per
+    sequence (a ragged batch).  Returns the element count."""
     _check(isinstance(length, torch.Tensor) and length.is_cuda and length.device == device and length.dtype == torch.int32
-           and length.numel() == 1, "the device-side length must be a one-element int32 CUDA tensor on the cache's device")
+           and length.is_contiguous() and (length.numel() == 1 or batch is None or length.numel() == batch),
+           "the device-side length must be a contiguous int32 CUDA tensor on the cache's device with one element, or one per sequence")
+    return int(length.numel())
 
 
 def cache_append_at(k_new, v_new, k_hi, v_hi, k_codes, k_scales, v_codes, v_scales, length, *, offset=0, page_table=None,
                     k_mean=None, k_min=None, k_max=None, is_mx=False, stat_block=64):
     """``cache_append`` (or, with ``page_table``, ``cache_append_paged``) at token position ``length[0] + offset``, where
-    ``length`` is a one-element int32 tensor ON THE GPU: the launch is the same whatever the position, so it can be
-    captured in a CUDA graph and replayed for every token.  A range that would end beyond the capacity is not stored.
+    ``length`` is an int32 tensor ON THE GPU (one element, or one per sequence for a ragged batch): the launch is the
+    same whatever the position, so it can be captured in a CUDA graph and replayed for every token.  A range that would end beyond the capacity is not stored.
     ``k_new`` / ``v_new`` [B, Hkv, T, D]."""
     _check(k_hi.is_cuda and k_hi.dim() == 4 and k_hi.is_contiguous() and k_hi.dtype in (torch.float16, torch.bfloat16),
            "k cache must be a contiguous 4D float16 / bfloat16 CUDA tensor")
-    _check_length(length, k_hi.device)
     paged = page_table is not None
     g = 32 if is_mx else 16
     d = k_hi.shape[3]
@@ -803,6 +806,7 @@ def cache_append_at(k_new, v_new, k_hi, v_hi, k_codes, k_scales, v_codes, v_scal
         _check(new is not None and new.is_cuda and new.is_contiguous() and new.dtype == k_hi.dtype and new.dim() == 4
                and new.shape[0] == b and new.shape[1] == hkv and new.shape[3] == d,
                f"{name} must be contiguous [batch, kv_heads, tokens, head_dim] CUDA tensors of the cache dtype")
+    n_len = _check_length(length, k_hi.device, b)
     stat_blocks = 1
     for name, t in (("k_mean", k_mean), ("k_min", k_min), ("k_max", k_max)):
         if t is not None:
@@ -814,17 +818,17 @@ def cache_append_at(k_new, v_new, k_hi, v_hi, k_codes, k_scales, v_codes, v_scal
         rc = _lib.load().ta100_cache_append_at(
             _ptr(k_new), _ptr(v_new), _ptr(k_hi), _ptr(v_hi), _ptr(k_codes), _ptr(k_scales), _ptr(v_codes), _ptr(v_scales),
             _ptr(k_mean), _ptr(k_min), _ptr(k_max), _ptr(page_table), max_pages, pool, b, hkv, stat_blocks, cap, _ptr(length),
-            int(offset), k_new.shape[2], v_new.shape[2], d, stat_block, int(is_mx), int(k_hi.dtype == torch.bfloat16), 0,
+            n_len, int(offset), k_new.shape[2], v_new.shape[2], d, stat_block, int(is_mx), int(k_hi.dtype == torch.bfloat16), 0,
             _stream(k_hi))
     _lib.check(rc, "cache_append_at")
 
 
 def advance_length(length: torch.Tensor, count: int, limit: int) -> None:
-    """``length[0] = min(length[0] + count, limit)`` in stream order (one tiny launch): the end of a generation step
-    whose kernels read the length on the GPU."""
-    _check_length(length, length.device)
+    """``length[i] = min(length[i] + count, limit)`` for every element, in stream order (one tiny launch): the end of a
+    generation step whose kernels read the length on the GPU."""
+    n_len = _check_length(length, length.device)
     with torch.cuda.device(length.device):
-        rc = _lib.load().ta100_advance_length(_ptr(length), int(count), int(limit), _stream(length))
+        rc = _lib.load().ta100_advance_length(_ptr(length), n_len, int(count), int(limit), _stream(length))
     _lib.check(rc, "advance_length")
 
 
@@ -839,8 +843,8 @@ def decode_step_row_width(max_len: int, *, top_k=None, fraction=None, sink=0, lo
 def cached_decode_step_at(q_grouped, k_hi, v_hi, k_packed, k_scale, v_packed, v_scale, stat_a, stat_b, length, *, offset,
                           max_len, top_k=None, fraction=None, sink=0, local=0, is_mx=False, splits=None, sel_out=None,
                           out=None, page_table=None):
-    """``cached_decode_step`` over ``length[0] + offset`` cached tokens, ``length`` being a one-element int32 tensor ON
-    THE GPU.  The kernels derive the page count, the number of complete blocks and the selected / forced block counts
+    """``cached_decode_step`` over ``length[0] + offset`` cached tokens, ``length`` being an int32 tensor ON THE GPU
+    with one element - or one per sequence: sequence ``i`` of a ragged batch then holds ``length[i] + offset`` tokens.  The kernels derive the page count, the number of complete blocks and the selected / forced block counts
     (the rule of ``cached_decode_attention``: ``top_k`` blocks or ``fraction`` of the complete ones, ``local`` then
     ``sink`` forced blocks as far as there is room) from it when they start, so the same launches serve every length
     up to ``max_len`` (a multiple of 64) and replay from one CUDA graph across tokens.  Contiguous cache tensors as
@@ -851,7 +855,7 @@ def cached_decode_step_at(q_grouped, k_hi, v_hi, k_packed, k_scale, v_packed, v_
     is_bf16 = q_grouped.dtype == torch.bfloat16
     _check(q_grouped.is_cuda and q_grouped.is_contiguous() and max_len % 64 == 0 and max_len > 0 and 1 <= g <= 16,
            "cached_decode_step_at expects a contiguous CUDA query [B, Hkv, G <= 16, D] and max_len in whole pages")
-    _check_length(length, dev)
+    n_len = _check_length(length, dev, b)
     _check(stat_a is not None and k_hi is not None and v_hi is not None, "the statistics and the 16-bit caches are required")
     paged = page_table is not None
     cap = max_len if paged else k_packed.shape[2]
@@ -882,7 +886,7 @@ def cached_decode_step_at(q_grouped, k_hi, v_hi, k_packed, k_scale, v_packed, v_
             vp(k_packed.data_ptr()), vp(k_scale.data_ptr()), vp(v_packed.data_ptr()), vp(v_scale.data_ptr()),
             _ptr(page_table), page_table.shape[1] if paged else 0, k_packed.shape[0] if paged else 0,
             vp(stat_a.data_ptr()), _ptr(stat_b), vp(sel_out.data_ptr()), width, vp(out.data_ptr()), vp(part_o.data_ptr()),
-            vp(part_ml.data_ptr()), b, hkv, g, vp(length.data_ptr()), int(offset), max_len, cap, stat_a.shape[2],
+            vp(part_ml.data_ptr()), b, hkv, g, vp(length.data_ptr()), n_len, int(offset), max_len, cap, stat_a.shape[2],
             -1 if top_k is None else int(top_k), float(0.05 if fraction is None else fraction), int(sink), int(local), d,
             int(is_mx), int(is_bf16), splits, vp(torch.cuda.current_stream(dev).cuda_stream))
     if rc:

@@ -23,10 +23,10 @@ SIGNATURES = {
     "ta100_block_stats": (_c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_vp]),
     "ta100_cache_append": (_c_int, [_c_vp] * 11 + [_c_ll] + [_c_int] * 9 + [_c_vp]),
     "ta100_cache_append_paged": (_c_int, [_c_vp] * 12 + [_c_int] * 13 + [_c_vp]),
-    "ta100_cache_append_at": (_c_int, [_c_vp] * 12 + [_c_int] * 6 + [_c_vp] + [_c_int] * 8 + [_c_vp]),
-    "ta100_advance_length": (_c_int, [_c_vp, _c_int, _c_int, _c_vp]),
+    "ta100_cache_append_at": (_c_int, [_c_vp] * 12 + [_c_int] * 6 + [_c_vp] + [_c_int] * 9 + [_c_vp]),
+    "ta100_advance_length": (_c_int, [_c_vp, _c_int, _c_int, _c_int, _c_vp]),
     "ta100_cached_decode_step_at": (_c_int, [_c_vp] * 10 + [_c_int] * 2 + [_c_vp] * 3 + [_c_int] + [_c_vp] * 3 + [_c_int] * 3
-                                    + [_c_vp] + [_c_int] * 5 + [ctypes.c_double] + [_c_int] * 6 + [_c_vp]),
+                                    + [_c_vp] + [_c_int] * 6 + [ctypes.c_double] + [_c_int] * 6 + [_c_vp]),
     "ta100_peer_exchange_create": (_c_int, [_c_int, _c_ll, ctypes.POINTER(_c_vp), ctypes.c_char_p]),
     "ta100_peer_exchange_open": (_c_int, [ctypes.c_char_p, ctypes.POINTER(_c_vp)]),
     "ta100_peer_exchange_close": (_c_int, [_c_vp]),

@@ -35,8 +35,9 @@ struct AppendParams {
     uint16_t* k_min;
     uint16_t* k_max;
     int start, k_count, v_count, cap;
-    const int32_t* start_dev;     // null, or the append position in device memory: the kernel uses *start_dev + start
+    const int32_t* start_dev;     // null, or the append position(s) in device memory: the kernel uses that + start
                                   // and the item counts below are upper bounds
+    int start_per_seq;            // 0: start_dev[0] for every sequence; 1: start_dev[head / hkv]
     const int32_t* page_table;    // paged addressing: [batch, max_pages] -> physical page; nullptr = slabs
     int max_pages, pool_pages, hkv;
     int stat_blocks;              // statistics blocks per head in k_mean / k_min / k_max (their row stride)
@@ -82,7 +83,8 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams la
     int n_v_real = p.n_v_items, n_s_real = p.n_s_items;
     if (launch.start_dev != nullptr) {
         // the position comes from device memory: the launch was cut for the worst case, the real ranges follow here
-        p.start = __ldg(launch.start_dev) + launch.start;
+        const long long head0 = blockIdx.x / (launch.n_k_items + launch.n_v_items + launch.n_s_items);
+        p.start = __ldg(launch.start_dev + (launch.start_per_seq ? head0 / launch.hkv : 0)) + launch.start;
         const int longest = p.k_count > p.v_count ? p.k_count : p.v_count;
         if (p.start < 0 || p.start > p.cap - longest) return;     // beyond the capacity: nothing is stored
         n_v_real = 0;
@@ -266,7 +268,7 @@ int cache_append_dispatch(const void* k_new, const void* v_new, void* k_hi, void
                           void* v_codes_t, void* v_scales_t, void* k_mean, void* k_min, void* k_max, long long heads,
                           int start, int k_count, int v_count, int capacity, int head_dim, int stat_block, int is_mx,
                           int is_bf16, int flags, const void* page_table, int max_pages, int pool_pages, int hkv,
-                          int stat_blocks, const void* start_dev, cudaStream_t stream) {
+                          int stat_blocks, const void* start_dev, int start_per_seq, cudaStream_t stream) {
     if (head_dim != 64 && head_dim != 128) return TA100_ERR_UNSUPPORTED;
     if (page_table) {
         if (max_pages <= 0 || pool_pages <= 0 || hkv <= 0 || heads % hkv != 0 || stat_blocks <= 0) return TA100_ERR_SHAPE;
@@ -301,6 +303,8 @@ int cache_append_dispatch(const void* k_new, const void* v_new, void* k_hi, void
     p.k_max = static_cast<uint16_t*>(k_max);
     p.start = start; p.k_count = k_count; p.v_count = v_count; p.cap = capacity;
     p.start_dev = static_cast<const int32_t*>(start_dev);
+    p.start_per_seq = (start_dev && start_per_seq) ? 1 : 0;
+    if (p.start_per_seq && (hkv <= 0 || heads % hkv != 0)) return TA100_ERR_SHAPE;
     p.page_table = static_cast<const int32_t*>(page_table);
     p.max_pages = max_pages; p.pool_pages = pool_pages; p.hkv = hkv;
     p.stat_blocks = page_table ? stat_blocks : capacity / stat_block;
@@ -346,17 +350,20 @@ int cache_append_dispatch(const void* k_new, const void* v_new, void* k_hi, void
 }
 
 namespace {
-__global__ void advance_length_kernel(int32_t* len, int count, int limit) {
-    const long long v = static_cast<long long>(*len) + count;
-    *len = static_cast<int32_t>(v > limit ? limit : (v < 0 ? 0 : v));
+__global__ void advance_length_kernel(int32_t* len, int n, int count, int limit) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const long long v = static_cast<long long>(len[i]) + count;
+        len[i] = static_cast<int32_t>(v > limit ? limit : (v < 0 ? 0 : v));
+    }
 }
 }  // namespace
 
-// *len_dev = min(*len_dev + count, limit): the end of a generation step whose kernels read the length on the GPU.
-int advance_length_dispatch(void* len_dev, int count, int limit, cudaStream_t stream) {
+// len_dev[i] = min(len_dev[i] + count, limit) for the n lengths: the end of a generation step whose kernels read the
+// length on the GPU.
+int advance_length_dispatch(void* len_dev, int n, int count, int limit, cudaStream_t stream) {
     if (!len_dev) return TA100_ERR_NULL;
-    if (limit < 0) return TA100_ERR_SHAPE;
-    advance_length_kernel<<<1, 1, 0, stream>>>(static_cast<int32_t*>(len_dev), count, limit);
+    if (limit < 0 || n < 1) return TA100_ERR_SHAPE;
+    advance_length_kernel<<<1, 128, 0, stream>>>(static_cast<int32_t*>(len_dev), n, count, limit);
     return static_cast<int>(cudaGetLastError());
 }
 

@@ -26,7 +26,7 @@ int decode_pick_splits(int, int);
 size_t decode_workspace_bytes(int, int, int, int);
 int decode_dispatch(const void*, const void*, const void*, const void*, int, const void*, const void*, const void*,
                     const void*, const void*, const void*, const void*, int, int, void*, void*, void*, int, int, int, int, int,
-                    int, int, int, int, int, const void*, int, cudaStream_t);
+                    int, int, int, int, int, const void*, int, int, cudaStream_t);
 int merge_dispatch(const void*, const void*, void*, int, long long, long long, long long, int, int, int, int, int,
                    cudaStream_t);
 int reduce_partials_dispatch(const void*, const void*, void*, void*, long long, int, int, int, cudaStream_t);
@@ -43,9 +43,9 @@ int peer_exchange_destroy(void*);
 int peer_all_gather_dispatch(const void*, void*, long long, long long, int, int, void* const*, cudaStream_t);
 int peer_exchange_status(void*, int, long long, cudaStream_t);
 int cache_append_dispatch(const void*, const void*, void*, void*, void*, void*, void*, void*, void*, void*, void*, long long,
-                          int, int, int, int, int, int, int, int, int, const void*, int, int, int, int, const void*,
+                          int, int, int, int, int, int, int, int, int, const void*, int, int, int, int, const void*, int,
                           cudaStream_t);
-int advance_length_dispatch(void*, int, int, cudaStream_t);
+int advance_length_dispatch(void*, int, int, int, cudaStream_t);
 }  // namespace ta100
 
 namespace ta100 {
@@ -108,7 +108,7 @@ int ta100_cache_append(const void* k_new, const void* v_new, void* k_hi, void* v
                        int is_bf16, int flags, void* stream) {
     return cache_append_dispatch(k_new, v_new, k_hi, v_hi, k_codes, k_scales, v_codes_t, v_scales_t, k_mean, k_min, k_max,
                                  heads, start, k_count, v_count, capacity, head_dim, stat_block, is_mxfp4, is_bf16, flags,
-                                 nullptr, 0, 0, 0, 0, nullptr, S(stream));
+                                 nullptr, 0, 0, 0, 0, nullptr, 0, S(stream));
 }
 
 int ta100_cache_append_paged(const void* k_new, const void* v_new, void* k_hi, void* v_hi, void* k_codes, void* k_scales,
@@ -119,25 +119,26 @@ int ta100_cache_append_paged(const void* k_new, const void* v_new, void* k_hi, v
     if (batch <= 0 || hkv <= 0) return TA100_ERR_SHAPE;
     return cache_append_dispatch(k_new, v_new, k_hi, v_hi, k_codes, k_scales, v_codes, v_scales, k_mean, k_min, k_max,
                                  static_cast<long long>(batch) * hkv, start, k_count, v_count, 0, head_dim, stat_block,
-                                 is_mxfp4, is_bf16, flags, page_table, max_pages, pool_pages, hkv, stat_blocks, nullptr,
+                                 is_mxfp4, is_bf16, flags, page_table, max_pages, pool_pages, hkv, stat_blocks, nullptr, 0,
                                  S(stream));
 }
 
 int ta100_cache_append_at(const void* k_new, const void* v_new, void* k_hi, void* v_hi, void* k_codes, void* k_scales,
                           void* v_codes, void* v_scales, void* k_mean, void* k_min, void* k_max, const void* page_table,
                           int max_pages, int pool_pages, int batch, int hkv, int stat_blocks, int capacity,
-                          const void* start_dev, int start_offset, int k_count, int v_count, int head_dim, int stat_block,
-                          int is_mxfp4, int is_bf16, int flags, void* stream) {
+                          const void* start_dev, int start_count, int start_offset, int k_count, int v_count, int head_dim,
+                          int stat_block, int is_mxfp4, int is_bf16, int flags, void* stream) {
     if (!start_dev) return TA100_ERR_NULL;
     if (reinterpret_cast<uintptr_t>(start_dev) & 3) return TA100_ERR_ALIGN;
+    if (start_count != 1 && start_count != batch) return TA100_ERR_SHAPE;
     return cache_append_dispatch(k_new, v_new, k_hi, v_hi, k_codes, k_scales, v_codes, v_scales, k_mean, k_min, k_max,
                                  static_cast<long long>(batch) * hkv, start_offset, k_count, v_count,
                                  page_table ? 0 : capacity, head_dim, stat_block, is_mxfp4, is_bf16, flags, page_table,
-                                 max_pages, pool_pages, hkv, stat_blocks, start_dev, S(stream));
+                                 max_pages, pool_pages, hkv, stat_blocks, start_dev, start_count > 1 ? 1 : 0, S(stream));
 }
 
-int ta100_advance_length(void* len_dev, int count, int limit, void* stream) {
-    return advance_length_dispatch(len_dev, count, limit, S(stream));
+int ta100_advance_length(void* len_dev, int len_count, int count, int limit, void* stream) {
+    return advance_length_dispatch(len_dev, len_count, count, limit, S(stream));
 }
 
 int ta100_select_prefill(const void* q_mean, const void* k_a, const void* k_b, void* out, int heads, int group, int nq,
@@ -204,7 +205,7 @@ int ta100_decode_attention(const void* q_hi, const void* k_hi, const void* v_hi,
                            int write_out, void* stream) {
     return decode_dispatch(q_hi, k_hi, v_hi, sel, width, q4, k4, v4, qs, ks, vs, page_table, max_pages, pool_pages, out, part_o,
                            part_ml, batch, hkv, group, kv_len, kv_cap, head_dim, is_mxfp4, is_bf16, splits, write_out,
-                           nullptr, 0, S(stream));
+                           nullptr, 0, 0, S(stream));
 }
 
 int ta100_cached_decode_step(const void* q, void* q4, void* qs, const void* k_hi, const void* v_hi, const void* k4,
@@ -223,7 +224,7 @@ int ta100_cached_decode_step(const void* q, void* q4, void* qs, const void* k_hi
         if (rc != TA100_OK) return rc;
     }
     return decode_dispatch(q, k_hi, v_hi, width > 0 ? sel : nullptr, width, q4, k4, v4t, qs, ks, vst, nullptr, 0, 0, out, part_o,
-                           part_ml, batch, hkv, group, kv_len, kv_cap, head_dim, is_mxfp4, is_bf16, splits, 1, nullptr, 0,
+                           part_ml, batch, hkv, group, kv_len, kv_cap, head_dim, is_mxfp4, is_bf16, splits, 1, nullptr, 0, 0,
                            S(stream));
 }
 
@@ -246,23 +247,26 @@ int ta100_cached_decode_step_paged(const void* q, void* q4, void* qs, const void
     }
     return decode_dispatch(q, k_hi, v_hi, width > 0 ? sel : nullptr, width, q4, k4, v4, qs, ks, vs, page_table, max_pages,
                            pool_pages, out, part_o, part_ml, batch, hkv, group, kv_len, kv_len, head_dim, is_mxfp4, is_bf16,
-                           splits, 1, nullptr, 0, S(stream));
+                           splits, 1, nullptr, 0, 0, S(stream));
 }
 
 int ta100_cached_decode_step_at(const void* q, void* q4, void* qs, const void* k_hi, const void* v_hi, const void* k4,
                                 const void* ks, const void* v4, const void* vs, const void* page_table, int max_pages,
                                 int pool_pages, const void* stat_a, const void* stat_b, void* sel, int sel_stride, void* out,
                                 void* part_o, void* part_ml, int batch, int hkv, int group, const void* len_dev,
-                                int len_offset, int max_len, int kv_cap, int stat_cap_blocks, int top_k, double fraction,
-                                int sink, int local, int head_dim, int is_mxfp4, int is_bf16, int splits, void* stream) {
+                                int len_count, int len_offset, int max_len, int kv_cap, int stat_cap_blocks, int top_k,
+                                double fraction, int sink, int local, int head_dim, int is_mxfp4, int is_bf16, int splits,
+                                void* stream) {
     if (!len_dev || !stat_a || !sel) return TA100_ERR_NULL;
     if (reinterpret_cast<uintptr_t>(len_dev) & 3) return TA100_ERR_ALIGN;
     if (max_len <= 0 || max_len % 64 != 0 || sel_stride <= 0) return TA100_ERR_SHAPE;
+    if ((len_count != 1 && len_count != batch) || hkv <= 0) return TA100_ERR_SHAPE;
     const long long flat = static_cast<long long>(batch) * hkv;
     int rc = quantize_dispatch(q, q4, qs, flat, group, head_dim, is_mxfp4, is_bf16, 0, S(stream));
     if (rc != TA100_OK) return rc;
     DynLength dyn{};
     dyn.len = static_cast<const int32_t*>(len_dev);
+    dyn.hkv_per_seq = len_count > 1 ? hkv : 0;
     dyn.offset = len_offset;
     dyn.top_k = top_k;
     dyn.share = fraction;
@@ -273,7 +277,7 @@ int ta100_cached_decode_step_at(const void* q, void* q4, void* qs, const void* k
     if (rc != TA100_OK) return rc;
     return decode_dispatch(q, k_hi, v_hi, sel, sel_stride, q4, k4, v4, qs, ks, vs, page_table, max_pages, pool_pages, out,
                            part_o, part_ml, batch, hkv, group, max_len, page_table ? max_len : kv_cap, head_dim, is_mxfp4,
-                           is_bf16, splits, 1, len_dev, len_offset, S(stream));
+                           is_bf16, splits, 1, len_dev, len_count > 1 ? 1 : 0, len_offset, S(stream));
 }
 
 int ta100_decode_status(void* stream) { return decode_status(S(stream)); }

@@ -41,8 +41,9 @@ __host__ __device__ constexpr int cdiv(int a, int b) { return (a + b - 1) / b; }
 // the append, selection and attention kernels read it when they start and derive from it what the host
 // otherwise passes as launch parameters.  len == nullptr: the launch parameters hold.
 struct DynLength {
-    const int32_t* len;   // tokens in the cache when the step began (before its append)
-    int offset;           // added to *len: the tokens this step has appended before the reading kernel runs
+    const int32_t* len;   // tokens in the cache when the step began (before its append): one int, or one per sequence
+    int hkv_per_seq;      // 0: len[0] holds for every sequence; else KV heads per sequence - flat KV head h reads len[h / hkv_per_seq]
+    int offset;           // added to the length: the tokens this step has appended before the reading kernel runs
     int top_k;            // >= 0: that many blocks (at most the complete ones); < 0: `share` of them
     double share;         // fraction of the complete 64-token blocks that are selected
     int sink, local;      // configured numbers of forced first / last blocks

@@ -79,8 +79,9 @@ struct DecodeParams {
     const int32_t* page_table;  // [batch, max_pages] or null
     float* part_o;          // [heads, splits, G, D]
     float* part_ml;         // [heads, splits, G, 2]
-    const int32_t* len_dev; // null, or the sequence length in device memory: npages is then only the upper bound
-    int len_offset;         // added to *len_dev
+    const int32_t* len_dev; // null, or the sequence length(s) in device memory: npages is then only the upper bound
+    int len_per_seq;        // 0: len_dev[0] for every sequence; 1: len_dev[sequence]
+    int len_offset;         // added to the length
     int heads, hkv, G, npages, cap_pages, max_pages, pool_pages, width, splits;
     int vs_row_stride;      // bytes between channel rows of vs (contiguous layout)
     float c2;               // (1/sqrt(d)) * log2(e)
@@ -241,7 +242,8 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
     const int b = h / p.hkv, kvh = h - b * p.hkv;
     const int G = p.G;
     int npages = p.npages;
-    if (p.len_dev != nullptr) npages = min(npages, max(1, cdiv(max(0, __ldg(p.len_dev) + p.len_offset), PAGE)));
+    if (p.len_dev != nullptr)
+        npages = min(npages, max(1, cdiv(max(0, __ldg(p.len_dev + (p.len_per_seq ? b : 0)) + p.len_offset), PAGE)));
     const int p_begin = static_cast<int>(static_cast<long long>(split) * npages / p.splits);
     const int p_end = static_cast<int>(static_cast<long long>(split + 1) * npages / p.splits);
     const bool paged = p.page_table != nullptr;
@@ -871,8 +873,8 @@ int decode_status(cudaStream_t stream) {
 int decode_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const void* sel, int width, const void* q4,
                     const void* k4, const void* v4, const void* qs, const void* ks, const void* vs, const void* page_table,
                     int max_pages, int pool_pages, void* out, void* part_o, void* part_ml, int batch, int hkv, int G, int kv_len,
-                    int kv_cap, int d, int is_mx, int is_bf16, int splits, int write_out, const void* len_dev, int len_offset,
-                    cudaStream_t stream) {
+                    int kv_cap, int d, int is_mx, int is_bf16, int splits, int write_out, const void* len_dev, int len_per_seq,
+                    int len_offset, cudaStream_t stream) {
     if (!q4 || !k4 || !v4 || !qs || !ks || !vs || !part_o || !part_ml) return TA100_ERR_NULL;
     if (write_out && !out) return TA100_ERR_NULL;
     if (width > 0 && (!q_hi || !k_hi || !v_hi || !sel)) return TA100_ERR_NULL;
@@ -938,7 +940,7 @@ int decode_dispatch(const void* q_hi, const void* k_hi, const void* v_hi, const 
     p.ks = static_cast<const uint8_t*>(ks); p.vs = static_cast<const uint8_t*>(vs);
     p.sel = static_cast<const int32_t*>(sel); p.page_table = static_cast<const int32_t*>(page_table);
     p.part_o = static_cast<float*>(part_o); p.part_ml = static_cast<float*>(part_ml);
-    p.len_dev = static_cast<const int32_t*>(len_dev); p.len_offset = len_offset;
+    p.len_dev = static_cast<const int32_t*>(len_dev); p.len_per_seq = len_per_seq ? 1 : 0; p.len_offset = len_offset;
     p.heads = heads; p.hkv = hkv; p.G = G; p.npages = npages; p.cap_pages = kv_cap / PAGE; p.max_pages = max_pages; p.pool_pages = pool_pages;
     p.width = width; p.splits = splits;
     p.vs_row_stride = P / GRP;
@@ -1075,7 +1077,7 @@ int decode_static_dispatch(const void* q_hi, const void* k_hi, const void* v_hi,
     if (rc != TA100_OK) return rc;
     unsigned char* b = static_cast<unsigned char*>(base);
     return decode_dispatch(q_hi, k_hi, v_hi, sel, width, q4, k4, v4, qs, ks, vs, page_table, max_pages, pool_pages, out, b, b + off_ml,
-                           batch, hkv, G, kv_len, kv_cap, d, is_mx, is_bf16, splits, 1, nullptr, 0, stream);
+                           batch, hkv, G, kv_len, kv_cap, d, is_mx, is_bf16, splits, 1, nullptr, 0, 0, stream);
 }
 
 }  // namespace ta100

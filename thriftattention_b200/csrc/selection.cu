@@ -499,7 +499,8 @@ __global__ void __launch_bounds__(SELD_THREADS, 2) select_decode_kernel(const ui
     // block counts: launch parameters, or derived from the sequence length in device memory
     int nk = nk_arg, k = k_arg, sink = sink_arg, local = local_arg;
     if (dyn.len != nullptr) {
-        dyn_select_counts(dyn, max(0, __ldg(dyn.len) + dyn.offset), min(cap_blocks, 2048), nk, k, sink, local);
+        const int seq = dyn.hkv_per_seq > 0 ? static_cast<int>(blockIdx.x) / dyn.hkv_per_seq : 0;
+        dyn_select_counts(dyn, max(0, __ldg(dyn.len + seq) + dyn.offset), min(cap_blocks, 2048), nk, k, sink, local);
         k = min(k, max(0, out_stride - sink - local));   // the host sizes the rows for the longest sequence
     }
     constexpr int VEC = D / 8;            // 16-byte chunks per statistics row
