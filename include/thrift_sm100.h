@@ -413,6 +413,14 @@ int ta100_cached_decode_step_at(const void* q, void* q4, void* qs, const void* k
                                 double fraction, int sink, int local, int head_dim, int is_mxfp4, int is_bf16, int splits,
                                 void* stream);
 
+/*
+ * The block counts ta100_cached_decode_step_at derives on the device for `tokens` cached tokens, computed on the host
+ * (no GPU needed): counts4 = {complete blocks scored (at most 2048), blocks selected by score, forced sink blocks,
+ * forced local blocks}.  Sizing helper (the widest selection row is counts4[1] + sink + local at the longest length)
+ * and the statement of the rule that tests compare with resolve_top_k (src/thriftattention/selection/counts.py).
+ */
+int ta100_decode_step_counts(int tokens, int top_k, double fraction, int sink, int local, int* counts4);
+
 /* len_dev[i] = min(len_dev[i] + count, limit) for i < len_count, in stream order: the end of a step. */
 int ta100_advance_length(void* len_dev, int len_count, int count, int limit, void* stream);
 

@@ -70,3 +70,28 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "_LIB_PATH", tmp_path / "nope.so")
     with pytest.raises(ImportError, match="not built"):
         _lib.load()
+
+
+def test_device_side_block_counts_follow_the_python_rule():
+    """The counts the device-length decode step derives from the length (restated for the host in
+    ta100_decode_step_counts) equal what cached_decode_attention computes in Python - resolve_top_k with its
+    round-half-to-even, then local and sink blocks as far as there is room - for every length and a spread of
+    fractions, ties included."""
+    from thriftattention_b200 import _lib
+    from thriftattention_b200.selection import resolve_top_k
+
+    lib = _lib.load()
+    out = (ctypes.c_int * 4)()
+    cases = [(None, f, s, l) for f in (0.0, 0.05, 0.1, 0.25, 0.3, 0.5, 0.75, 1.0) for s, l in ((0, 0), (1, 1), (4, 16))]
+    cases += [(k, None, s, l) for k in (0, 1, 7, 300) for s, l in ((0, 0), (2, 3))]
+    for top_k, fraction, sink_cfg, local_cfg in cases:
+        for blocks in list(range(0, 70)) + [255, 256, 257, 1023, 2047, 2048]:
+            for extra in (0, 63):
+                assert lib.ta100_decode_step_counts(blocks * 64 + extra, -1 if top_k is None else top_k,
+                                                    0.05 if fraction is None else fraction, sink_cfg, local_cfg, out) == 0
+                k = resolve_top_k(blocks, causal=False, top_k=top_k, fraction=fraction)
+                local = max(0, min(local_cfg, blocks - k))
+                sink = max(0, min(sink_cfg, blocks - k - local))
+                if k == 0:
+                    sink = local = 0
+                assert list(out) == [blocks, k, sink, local], (top_k, fraction, sink_cfg, local_cfg, blocks)

@@ -24,6 +24,7 @@ SIGNATURES = {
     "ta100_cache_append": (_c_int, [_c_vp] * 11 + [_c_ll] + [_c_int] * 9 + [_c_vp]),
     "ta100_cache_append_paged": (_c_int, [_c_vp] * 12 + [_c_int] * 13 + [_c_vp]),
     "ta100_cache_append_at": (_c_int, [_c_vp] * 12 + [_c_int] * 6 + [_c_vp] + [_c_int] * 9 + [_c_vp]),
+    "ta100_decode_step_counts": (_c_int, [_c_int, _c_int, ctypes.c_double, _c_int, _c_int, ctypes.POINTER(_c_int)]),
     "ta100_advance_length": (_c_int, [_c_vp, _c_int, _c_int, _c_int, _c_vp]),
     "ta100_cached_decode_step_at": (_c_int, [_c_vp] * 10 + [_c_int] * 2 + [_c_vp] * 3 + [_c_int] + [_c_vp] * 3 + [_c_int] * 3
                                     + [_c_vp] + [_c_int] * 6 + [ctypes.c_double] + [_c_int] * 6 + [_c_vp]),

@@ -137,6 +137,18 @@ int ta100_cache_append_at(const void* k_new, const void* v_new, void* k_hi, void
                                  max_pages, pool_pages, hkv, stat_blocks, start_dev, start_count > 1 ? 1 : 0, S(stream));
 }
 
+int ta100_decode_step_counts(int tokens, int top_k, double fraction, int sink, int local, int* counts4) {
+    if (!counts4) return TA100_ERR_NULL;
+    if (tokens < 0 || sink < 0 || local < 0) return TA100_ERR_SHAPE;
+    DynLength d{};
+    d.top_k = top_k;
+    d.share = fraction;
+    d.sink = sink;
+    d.local = local;
+    dyn_select_counts(d, tokens, 2048, counts4[0], counts4[1], counts4[2], counts4[3]);
+    return TA100_OK;
+}
+
 int ta100_advance_length(void* len_dev, int len_count, int count, int limit, void* stream) {
     return advance_length_dispatch(len_dev, len_count, count, limit, S(stream));
 }
