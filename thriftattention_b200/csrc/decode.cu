@@ -101,7 +101,7 @@ struct DecSmem {
     static constexpr int LIST = PSF + 1024;               // DEC_LIST_CAP x u32
     static constexpr int BITS = LIST + DEC_LIST_CAP * 4;  // 64 words: selected pages of the chain
     static constexpr int BARS = BITS + 256;
-    static constexpr int TOTAL = BARS + 1024;
+    static constexpr int TOTAL = BARS + 2048;
     // inside an FP4 slot
     static constexpr int K4 = 0, V4 = 4096, KSF = 8192, VSF = 9216;
     static_assert(Q16 % 1024 == 0 && P % 1024 == 0 && SLOTS % 1024 == 0, "swizzled tiles need 1024-byte alignment");
@@ -125,8 +125,10 @@ struct DecBars {
     int bad_entry;      // a page-table entry pointed outside the pool
     float m_row[DEC_MAX_GROUP];
     float l_part[4][DEC_MAX_GROUP];
+    uint64_t x_full;            // every softmax thread has published its quarter's maximum of the page
+    float xch[2][4][32];        // [page parity][column quarter][head]: the quarters' maxima, exchanged between the warps
 };
-static_assert(sizeof(DecBars) <= 1024, "barrier block must fit its shared-memory slot");
+static_assert(sizeof(DecBars) <= 2048, "barrier block must fit its shared-memory slot");
 
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -262,6 +264,7 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
         mbar_init(smem_u32(&bars.s_full), 1);
         mbar_init(smem_u32(&bars.s_free), 128);
         mbar_init(smem_u32(&bars.epi_full), 128);
+        mbar_init(smem_u32(&bars.x_full), 128);
         for (int i = 0; i < DEC_NS4; ++i) {
             mbar_init(smem_u32(&bars.f_full[i]), 33);   // lane 0's expect_tx arrival + one arrival per lane
             mbar_init(smem_u32(&bars.f_empty[i]), 1);
@@ -512,8 +515,11 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
         // =========================== softmax ===========================
         const int sub = warp & 3;                   // tensor-memory sub-partition of this warp
         const int row = sub * 32 + lane;            // tile row = tensor-memory lane = index among the 128 threads
-        const int cq = lane & 3;                    // column quarter handled by this thread
-        const int g = (lane >> 2) * 4 + sub;        // query head of this row
+        // Every query head occupies four rows of the tile, one per warp (rows g, 32 + g, 64 + g, 96 + g), and warp w
+        // works on columns [16 w, 16 w + 16) of every head: the tensor-memory load of a warp takes one column address,
+        // so a warp that needed all four quarters would load 64 columns per thread and keep 16.
+        const int cq = sub;                         // column quarter handled by this warp
+        const int g = lane;                         // query head of this row
         const bool active = g < G;
         const uint32_t lane_addr = static_cast<uint32_t>(sub * 32) << 16;
         const bool has_sel = p.width > 0;
@@ -574,21 +580,15 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
             tc_fence_after_sync();
             float s[16];
             {
-                uint32_t r0[16], r1[16], r2[16], r3[16];
-                tmem_ld16(tmem + lane_addr + DTM_S, r0);
-                tmem_ld16(tmem + lane_addr + DTM_S + 16, r1);
-                tmem_ld16(tmem + lane_addr + DTM_S + 32, r2);
-                tmem_ld16(tmem + lane_addr + DTM_S + 48, r3);
+                uint32_t r[16];
+                tmem_ld16(tmem + lane_addr + DTM_S + 16 * cq, r);
                 tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const uint32_t lo = (cq & 1) ? r1[j] : r0[j], hi = (cq & 1) ? r3[j] : r2[j];
-                    s[j] = __uint_as_float((cq & 2) ? hi : lo);
-                }
+                for (int j = 0; j < 16; ++j) s[j] = __uint_as_float(r[j]);
             }
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&bars.s_free));
-            // running maximum of the whole page row (the four quarters sit in neighbouring lanes)
+            // running maximum of the whole page row: this quarter first
             // the P buffer of this step was last read by the PV of step i - 2: poll once now, look at the answer
             // only when the buffer is about to be written
             const uint32_t buf = i & 1;
@@ -596,10 +596,18 @@ decode_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK4, c
             bool pf_ready = mbar_try_wait(smem_u32(&bars.p_free[buf]), pf_parity);
             float mx = fmaxf(max3(max3(s[0], s[1], s[2]), max3(s[3], s[4], s[5]), max3(s[6], s[7], s[8])),
                              max3(max3(s[9], s[10], s[11]), max3(s[12], s[13], s[14]), s[15]));
+            // the other three quarters' maxima come from the other warps: published in shared memory, a barrier that
+            // all 128 threads arrive at once per page (bounded wait, like every other), two buffers by page parity
             float mx_grp = mx;   // maximum of this thread's scale group: its 16 columns, 32 for MXFP4
-            if constexpr (MX) mx_grp = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+            {
+                float(*xq)[32] = bars.xch[i & 1];
+                xq[cq][lane] = mx;
+                mbar_arrive(smem_u32(&bars.x_full));
+                ok = waitc(25, &bars.x_full, i & 1);
+                if (!ok) break;
+                if constexpr (MX) mx_grp = fmaxf(mx, xq[cq ^ 1][lane]);
+                mx = fmaxf(max3(xq[0][lane], xq[1][lane], xq[2][lane]), xq[3][lane]);
+            }
             const float m_new = fmaxf(m_run, mx);
             const bool changed = active && i > 0 && m_new > m_run;
             const float rescale = ex2((m_run - m_new) * p.c2);
