@@ -10,13 +10,14 @@
 //   * S = Q K^T and O += P V are tcgen05 MMAs — block-scaled FP4 (the tensor core
 //     applies the E4M3 / E8M0 scales) or f16/bf16 — with accumulators in tensor memory.
 // The query group is tiny (G <= 16 heads), the MMA tile has 128 rows: every head is
-// stored FOUR times, in rows 32*w + 4*i + c (head g = 4*i + w, c = 0..3), and the thread
-// that owns row (g, c) handles token columns [16c, 16c+16) of each page.  Its P row is
+// stored FOUR times, in rows 32*c + g (c = 0..3: one row per softmax warp), and the thread
+// that owns row (g, c) handles token columns [16c, 16c+16) of each page - a warp's
+// tensor-memory load takes one column address, so the quarter is the warp's.  Its P row is
 // zero outside those columns, so the four O rows of a head are partial sums that are
 // added once, at the end of the chain.  All four use the running row maximum of the
 // whole 64-token page, as the reference does, because the quantisation of P
 // (dynamic scale per 16 / 32 tokens, codes computed with the un-rounded scale) depends
-// on it.
+// on it: the warps exchange their quarters' maxima through shared memory once per page.
 //
 // Warp roles (224 threads): warp 0 = page list + TMA producer (its 32 lanes also bring the K
 // and V block scales of every page into the 512-byte atom order the tensor core reads),
