@@ -620,7 +620,20 @@ def main():
     ap.add_argument("--workload", default="headline", choices=["headline", "mxfp4-bf16"],
                     help="headline = fp16 / NVFP4 top-10 %% prefill + the decode step; mxfp4-bf16 = the bf16 / MXFP4 prefill")
     ap.add_argument("--fraction", type=float, default=0.10, help="share of 128-token blocks kept in bf16 (mxfp4-bf16 workload)")
+    ap.add_argument("--hf", action="store_true",
+                    help="instead of the headline: generation through the Transformers hook on a random-init decoder of the "
+                         "Llama-3-8B shape (65,536-token prompt, 256 decode steps; eager loop and one CUDA graph per token) - "
+                         "what benchmarks/run_hook_generation.py --graph prints")
     args = ap.parse_args()
+    if args.hf:
+        import importlib.util
+
+        spec = importlib.util.spec_from_file_location(
+            "run_hook_generation", os.path.join(os.path.dirname(os.path.abspath(__file__)), "benchmarks", "run_hook_generation.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mod.run_hf(65536, 256, 32, graphed=True)
+        return
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     if result:
         print(json.dumps(result), flush=True)
