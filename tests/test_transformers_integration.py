@@ -589,3 +589,22 @@ def test_cache_position_is_read_once_per_forward():
     with pytest.raises(ValueError, match="contiguous cache_position"):
         cache_mod._cache_position_start({"cache_position": torch.tensor([3, 5])}, 0)
     assert cache_mod._cache_position_start(None, 7) == 7 and cache_mod._cache_position_start({"cache_position": 4}, 7) == 4
+
+
+def test_device_length_mode_refuses_updates_it_cannot_serve():
+    """With the length kept on the GPU the Python-side lengths are stale: anything but the single-token step of the
+    active cache (which the attention function appends itself) is an error, not a silent write at a wrong position."""
+    cache = ThriftAttentionCache(config=AttentionConfig(), max_cache_len=128)
+    with pytest.raises(RuntimeError, match="filled cache"):
+        cache.enable_device_length()
+    cache.layers.append(cache_mod.ThriftAttentionCacheLayer(max_cache_len=128, quant_format="nvfp4", track_minmax=False))
+    cache.layers[0].seq_len = 5
+    cache.device_length = torch.zeros(1, dtype=torch.int32)
+    k = torch.zeros(1, 2, 3, 128, dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="device-length mode"):
+        cache.update(k, k, 0)                                  # three tokens
+    with pytest.raises(RuntimeError, match="device-length mode"):
+        cache.update(k[:, :, :1], k[:, :, :1], 0)              # one token, but the cache is not the active one
+    with cache_mod.use_thriftattention_cache(cache):
+        got_k, got_v = cache.update(k[:, :, :1], k[:, :, :1], 0)
+    assert got_k.data_ptr() == k.data_ptr() and cache.layers[0].seq_len == 5     # handed on, nothing stored

@@ -817,10 +817,13 @@ class ThriftAttentionCache:
         if layer_idx is None:
             raise ValueError("ThriftAttentionCache.update requires layer_idx")
         layer = self.layer(layer_idx)
-        if (self.device_length is not None and key_states.shape[2] == 1 and layer.seq_len > 0
-                and get_active_thriftattention_cache() is self):
-            # device-length mode: the registered attention function appends these rows itself, at the position it
-            # reads on the GPU (device_length_decode_step)
+        if self.device_length is not None:
+            if key_states.shape[2] != 1 or layer.seq_len == 0 or get_active_thriftattention_cache() is not self:
+                raise RuntimeError("the cache is in device-length mode, which serves single-token steps through the registered "
+                                   "attention function only (the Python-side lengths are stale): call disable_device_length() "
+                                   "before any other update")
+            # the registered attention function appends these rows itself, at the position it reads on the GPU
+            # (device_length_decode_step)
             return key_states, value_states
         if self.paged and get_active_thriftattention_cache() is self:
             # the registered attention function reads the pools in place: spare the gather of the full K/V
