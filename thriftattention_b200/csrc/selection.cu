@@ -260,6 +260,16 @@ __device__ __forceinline__ void topk_dispatch(const float* scores, int n, int k,
 constexpr int SEL_WARPS = 8;
 constexpr int SEL_KTILE = 32;
 
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))),
+                 "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+
 template <int D>
 struct SelpSmem {
     static constexpr int ROW = D * 2 + 16;                    // padded statistics row: 16-byte reads by 32 lanes do not collide
@@ -267,7 +277,7 @@ struct SelpSmem {
     static constexpr int QF = SEL_WARPS * D * 4;              // q rows as fp32
     static constexpr int QM = SEL_WARPS * (D / 2) * 4;        // Quest masks, one 16-bit mask per channel
     static constexpr int TOPK = SEL_WARPS * (256 * 4 + SELP_CAND * 8);   // per warp: histogram / candidates, keys
-    static int total(int nk_pad) { return SEL_WARPS * nk_pad * 4 + 2 * TILE + QF + QM + TOPK; }
+    static int total(int nk_pad) { return SEL_WARPS * nk_pad * 4 + 4 * TILE + QF + QM + TOPK; }   // two stages of [A | B]
 };
 
 // packed fp32x2 arithmetic (two partial sums per instruction) and 16-bit pair -> fp32 pair
@@ -345,9 +355,8 @@ __global__ void __launch_bounds__(SEL_WARPS * 32) select_prefill_kernel(
     extern __shared__ __align__(16) uint8_t smem_raw[];
     float* scores = reinterpret_cast<float*>(smem_raw);                              // [SEL_WARPS][nk_pad]
     const int nk_pad = (nk + 31) & ~31;
-    uint8_t* s_ka = smem_raw + SEL_WARPS * nk_pad * 4;                                // [SEL_KTILE] padded rows
-    uint8_t* s_kb = s_ka + L::TILE;
-    float* qf = reinterpret_cast<float*>(s_kb + L::TILE);                             // [SEL_WARPS][D]
+    uint8_t* s_tiles = smem_raw + SEL_WARPS * nk_pad * 4;                             // [2 stages][A | B][SEL_KTILE] padded rows
+    float* qf = reinterpret_cast<float*>(s_tiles + 4 * L::TILE);                      // [SEL_WARPS][D]
     uint32_t* qm = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(qf) + L::QF);   // [SEL_WARPS][D/2]
     unsigned long long* tk_keys = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(qm) + L::QM) +
                                   (threadIdx.x / 32) * SELP_CAND;
@@ -381,24 +390,37 @@ __global__ void __launch_bounds__(SEL_WARPS * 32) select_prefill_kernel(
         float* my = scores + warp * nk_pad;
         const float4* qrow = reinterpret_cast<const float4*>(qf + warp * D);
         const uint4* mrow = reinterpret_cast<const uint4*>(qm + warp * (D / 2));
-        for (int b0 = 0; b0 < nk_need; b0 += SEL_KTILE) {
+        // The statistics of 32 key blocks at a time stream through two shared-memory stages: tile t + 1 is on its way
+        // (cp.async) while the warps score tile t.
+        const int n_tiles = cdiv(nk_need, SEL_KTILE);
+        auto issue = [&](int t) {
+            const int b0 = t * SEL_KTILE;
             const int nb = min(SEL_KTILE, nk_need - b0);
-            __syncthreads();
+            uint8_t* sa = s_tiles + (t & 1) * 2 * L::TILE;
             for (int i = threadIdx.x; i < nb * (D / 8); i += blockDim.x) {
                 const int r = i / (D / 8), c = i - r * (D / 8);
                 const long long g = (static_cast<long long>(kvh) * nk + b0 + r) * D + c * 8;
-                *reinterpret_cast<uint4*>(s_ka + r * L::ROW + c * 16) = __ldg(reinterpret_cast<const uint4*>(ka + g));
-                if constexpr (QUEST)
-                    *reinterpret_cast<uint4*>(s_kb + r * L::ROW + c * 16) = __ldg(reinterpret_cast<const uint4*>(kb + g));
+                cp_async16(sa + r * L::ROW + c * 16, ka + g);
+                if constexpr (QUEST) cp_async16(sa + L::TILE + r * L::ROW + c * 16, kb + g);
             }
+            cp_async_commit();
+        };
+        __syncthreads();                 // the previous item's readers are done with both stages
+        if (n_tiles > 0) issue(0);
+        for (int t = 0; t < n_tiles; ++t) {
+            if (t + 1 < n_tiles) { issue(t + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
             __syncthreads();
+            const int b0 = t * SEL_KTILE;
+            const int nb = min(SEL_KTILE, nk_need - b0);
+            const uint8_t* sa = s_tiles + (t & 1) * 2 * L::TILE;
             // one key block per lane
             const int b = b0 + lane;
             if (lane < nb && b < nvalid) {
-                const float s = thread_score<D, BF16, QUEST>(qrow, mrow, reinterpret_cast<const uint4*>(s_ka + lane * L::ROW),
-                                                             reinterpret_cast<const uint4*>(s_kb + lane * L::ROW));
+                const float s = thread_score<D, BF16, QUEST>(qrow, mrow, reinterpret_cast<const uint4*>(sa + lane * L::ROW),
+                                                             reinterpret_cast<const uint4*>(sa + L::TILE + lane * L::ROW));
                 my[b] = (b < n_sink || b >= local_lo) ? -FLT_MAX : s;
             }
+            __syncthreads();             // before this stage is refilled (tile t + 2)
         }
         __syncwarp();
         if (active) {
@@ -427,15 +449,6 @@ __global__ void __launch_bounds__(SEL_WARPS * 32) select_prefill_kernel(
 constexpr int SELD_THREADS = 256;
 constexpr int SELD_TILE = 64;       // pages per tile
 constexpr int SELD_MAX_GROUP = 16;
-
-__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))),
-                 "l"(src)
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 constexpr int SELD_CAND_CAP = 512;   // exact re-scoring handles at most this many candidates
 
